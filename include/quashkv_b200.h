@@ -1,0 +1,202 @@
+/*
+ * quashkv_b200 — C ABI of the B200 (sm_100a) compressed-KV hot path.
+ *
+ * Every entry point takes raw DEVICE pointers, explicit sizes and a CUDA stream
+ * (passed as void*; NULL = the legacy default stream).  A call validates its
+ * arguments on the host, enqueues kernels on the stream and returns:
+ * QKV_OK (0) or a negative QKV_E* code when nothing was launched.  Unless a
+ * comment says otherwise no entry point allocates, frees or synchronises, and
+ * the library keeps no state between calls: the caller owns inputs, outputs and
+ * workspaces (sizes from the *_workspace_bytes functions).
+ *
+ * "Reference" citations are file:line inside the QuashKV project
+ * (package directory quashkv/).
+ *
+ * Conventions
+ *   dtype        QKV_F32 / QKV_BF16 / QKV_F16 — storage type of a float tensor;
+ *                arithmetic is always fp32 (bf16/f16 inputs are upcast exactly,
+ *                as the reference's callers do with .float()).
+ *   codes        one uint8 per coordinate ("unpacked"), or "packed": an
+ *                LSB-first stream of w-bit fields per row, ceil(d*w/8) bytes
+ *                (reference packing.py:22-94).
+ *   rows         vector n of a call lives at row  (n / seg_len) * seg_stride +
+ *                seg_off + (n % seg_len)  of the code/norm planes.  With
+ *                seg_len = n_vec, seg_stride = 0, seg_off = 0 the planes are
+ *                dense.  This lets a caller append to, or read from, a
+ *                [segments, capacity, bytes] cache in place.
+ *   Pi           (d,d) row-major fp32 rotation; rotate = x @ Pi^T, un-rotate = y @ Pi.
+ *   d            1..128 for compress/decompress; a multiple of 32 up to 128 for
+ *                attention and the index scan.
+ */
+#ifndef QUASHKV_B200_H
+#define QUASHKV_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QKV_ABI_VERSION 1
+
+enum { QKV_F32 = 0, QKV_BF16 = 1, QKV_F16 = 2 };
+
+enum {
+  QKV_OK = 0,
+  QKV_ENULL = -1,      /* a required pointer is NULL */
+  QKV_EDIM = -2,       /* unsupported d / sizes */
+  QKV_EBITS = -3,      /* unsupported bit width */
+  QKV_EDTYPE = -4,     /* unknown dtype enum */
+  QKV_EALIGN = -5,     /* pointer or row pitch not aligned as documented */
+  QKV_EWORKSPACE = -6, /* workspace too small / too large for the static scratch */
+  QKV_ELAUNCH = -7,    /* cudaGetLastError() after launch was not cudaSuccess */
+  QKV_EARG = -8        /* inconsistent arguments */
+};
+
+typedef struct {
+  int64_t seg_len;    /* vectors per segment (>=1) */
+  int64_t seg_stride; /* rows between segment starts */
+  int64_t seg_off;    /* first row inside each segment */
+} qkv_rows_t;
+
+/* ---- diagnostics --------------------------------------------------------------------- */
+int qkv_abi_version(void);
+const char* qkv_strerror(int code);
+
+/* ---- bit packing (reference packing.py:22-94 pack_bits, :97-159 unpack_bits) ------------ */
+/* codes (n_rows,d) uint8 -> packed (n_rows, ceil(d*bits/8)).  bits in 1..4. */
+int qkv_pack(const uint8_t* codes, uint8_t* packed, int64_t n_rows, int d, int bits, void* stream);
+int qkv_unpack(const uint8_t* packed, uint8_t* codes, int64_t n_rows, int d, int bits, void* stream);
+
+/* ---- compress ------------------------------------------------------------------------------
+ * normalise -> rotate by Pi -> count boundaries below each rotated coordinate.
+ * Replaces MSEQuantizer.compress (reference quantizer.py:113-131) and
+ * fused_compress_mse (triton_kernels/compress.py:210-249).
+ *   x          (n_vec, d) rows of pitch x_pitch ELEMENTS, dtype x_dtype
+ *   boundaries (n_bounds) ascending fp32, n_bounds = 2^bits - 1
+ *   codes_out  packed != 0: rows of ceil(d*bits/8) bytes; else rows of d bytes
+ *   norms_out  fp32, one per row (norm clamped below at 1e-8 like the reference)
+ */
+int qkv_compress_mse(const void* x, int x_dtype, int64_t x_pitch, int64_t n_vec, int d,
+                     const float* Pi, const float* boundaries, int bits,
+                     uint8_t* codes_out, int packed, float* norms_out,
+                     qkv_rows_t rows, void* stream);
+
+/* Two-stage key quantiser: codes at `mse_bits`, then the sign bit of
+ * (x_rot - centroid) * S with ">= 0" -> 1.  Replaces InnerProductQuantizer.compress
+ * (reference quantizer.py:211-242) and fused_compress_ip (compress.py:252-303).
+ * signs_out: packed != 0 -> ceil(d/8) bytes per row, else d bytes of 0/1. */
+int qkv_compress_ip(const void* x, int x_dtype, int64_t x_pitch, int64_t n_vec, int d,
+                    const float* Pi, const float* boundaries, const float* centroids, int mse_bits,
+                    const float* S,
+                    uint8_t* codes_out, uint8_t* signs_out, int packed, float* norms_out,
+                    qkv_rows_t rows, void* stream);
+
+/* Per-channel bit allocation.  Replaces MixedPrecisionMSEQuantizer.compress
+ * (reference mixed_precision.py:130-158).  is_outlier (d) uint8 selects, per
+ * rotated channel, the outlier table (bits_out) or the regular table (bits_reg).
+ * Unpacked output: d bytes per row, as the reference returns.  Packed output (a
+ * layout the reference does not define): the outlier channels' codes in channel
+ * order as a bits_out stream, ceil(n_out*bits_out/8) bytes, followed by the
+ * regular channels' codes as a bits_reg stream. */
+int qkv_compress_mixed(const void* x, int x_dtype, int64_t x_pitch, int64_t n_vec, int d,
+                       const float* Pi, const uint8_t* is_outlier,
+                       const float* bounds_out, int bits_out,
+                       const float* bounds_reg, int bits_reg,
+                       uint8_t* codes_out, int packed, float* norms_out,
+                       qkv_rows_t rows, void* stream);
+/* Bytes per packed mixed row for n_out outlier channels among d. */
+int64_t qkv_mixed_row_bytes(int d, int n_out, int bits_out, int bits_reg);
+
+/* ---- decompress ----------------------------------------------------------------------------
+ * centroid gather -> un-rotate -> rescale.  Replaces MSEQuantizer.decompress
+ * (reference quantizer.py:133-147), fused_decompress_mse (decompress.py:194-232)
+ * and, with signs == NULL on key codes, the key path of
+ * QuashKVCache._decompress_engine (integrations/hf_cache.py:96-121).
+ * With signs != NULL it adds qjl_scale * S * (2*sign-1) before the rotation:
+ * fused_decompress_ip (decompress.py:235-285).
+ *   out (n_vec, d) rows of pitch out_pitch elements, dtype out_dtype (dense, row n). */
+int qkv_decompress(const uint8_t* codes, const uint8_t* signs, int packed, const float* norms,
+                   qkv_rows_t rows, int64_t n_vec, int d,
+                   const float* Pi, const float* centroids, int bits,
+                   const float* S, float qjl_scale,
+                   void* out, int out_dtype, int64_t out_pitch, void* stream);
+
+/* Mixed-precision decompress (reference mixed_precision.py:160-187). */
+int qkv_decompress_mixed(const uint8_t* codes, int packed, const float* norms,
+                         qkv_rows_t rows, int64_t n_vec, int d,
+                         const float* Pi, const uint8_t* is_outlier,
+                         const float* cents_out, int bits_out,
+                         const float* cents_reg, int bits_reg,
+                         void* out, int out_dtype, int64_t out_pitch, void* stream);
+
+/* ---- attention over the packed cache ---------------------------------------------------------
+ * Replaces QuashKVEngine.attention (reference engine.py:204-299) and
+ * fused_quantized_attention (triton_kernels/attention.py:307-394), reading
+ * PACKED planes and never materialising keys or values.
+ *
+ * Cache planes, one segment per (batch, kv head), `capacity` rows per segment:
+ *   k_codes  [B*Hkv, capacity, d*(key_bits-1)/8]   k_signs [B*Hkv, capacity, d/8]
+ *   k_norms  [B*Hkv, capacity] fp32
+ *   v_codes  [B*Hkv, capacity, d*val_bits/8]        v_norms [B*Hkv, capacity] fp32
+ * Rows 0..kv_len-1 of each segment are attended.  All plane base pointers must be
+ * 16-byte aligned.
+ *   q        (B, Hq, q_len, d) contiguous, dtype q_dtype;  query head h reads kv
+ *            head h / (Hq/Hkv)  (Hq/Hkv = 1 is the reference's case)
+ *   causal   query row i sits at position kv_len - q_len + i and sees rows <= it
+ *            (reference engine.py:273-279)
+ *   out      (B, Hq, q_len, d) fp32 contiguous
+ *   workspace  qkv_attention_workspace_bytes(...) bytes, 16-byte aligned; holds the
+ *            rotated queries and the per-split partial (max, sum, accumulator).
+ */
+typedef struct {
+  const uint8_t* k_codes;
+  const uint8_t* k_signs;
+  const float* k_norms;
+  const uint8_t* v_codes;
+  const float* v_norms;
+  int64_t capacity;
+} qkv_cache_t;
+
+size_t qkv_attention_workspace_bytes(int B, int Hq, int Hkv, int q_len, int64_t kv_len, int d);
+int qkv_attention(const void* q, int q_dtype, qkv_cache_t cache,
+                  int B, int Hq, int Hkv, int q_len, int64_t kv_len, int d,
+                  int key_bits, int val_bits,
+                  const float* Pi, const float* key_centroids, const float* val_centroids,
+                  const float* S, float qjl_scale, float scale, int causal,
+                  float* out, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- index scan ------------------------------------------------------------------------------
+ * Replaces QuashIndex.search (reference nn_search/index.py:121-163):
+ * score[m,n] = norm_n * (q_rot_m . c[code_n] + qjl_scale * sum(|q_rot_m| * S * (2*sign_n-1))),
+ * then the k largest per query, descending; equal scores are ordered by lower id.
+ *   db_codes [N, d*(bits-1)/8], db_signs [N, d/8] packed, db_norms [N] fp32
+ *   queries  (M, d) fp32 contiguous
+ *   id_base  added to every returned id (a shard's first global row)
+ *   out_scores (M,k) fp32, out_ids (M,k) int64;  k <= QKV_INDEX_MAX_K and k <= N
+ * qkv_index_scores writes the dense (M,N) score matrix instead (for k above the limit). */
+#define QKV_INDEX_MAX_K 128
+size_t qkv_index_workspace_bytes(int64_t N, int M, int d, int k);
+int qkv_index_scan_topk(const float* queries, int M, int d,
+                        const uint8_t* db_codes, const uint8_t* db_signs, const float* db_norms,
+                        int64_t N, int bits,
+                        const float* Pi, const float* centroids, const float* S, float qjl_scale,
+                        int k, int64_t id_base, float* out_scores, int64_t* out_ids,
+                        void* workspace, size_t workspace_bytes, void* stream);
+int qkv_index_scores(const float* queries, int M, int d,
+                     const uint8_t* db_codes, const uint8_t* db_signs, const float* db_norms,
+                     int64_t N, int bits,
+                     const float* Pi, const float* centroids, const float* S, float qjl_scale,
+                     float* out_scores, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Merge per-shard candidate lists: in (M, n_lists*k_in) -> out (M, k_out), higher score
+ * first, then lower id.  The reference has no sharded search; this is the step after an
+ * all-gather of every shard's qkv_index_scan_topk result. */
+int qkv_topk_merge(const float* in_scores, const int64_t* in_ids, int M, int64_t n_cand,
+                   int k_out, float* out_scores, int64_t* out_ids, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QUASHKV_B200_H */

@@ -1,0 +1,406 @@
+// Attention over the packed compressed cache (generic path: any key/value bit width,
+// d in {32,64,96,128}, grouped-query heads, q_len >= 1, optional causal mask).
+//
+// Three kernels per call:
+//   1. rotate_queries: q_rot = q @ Pi^T once per query row; stores q_rot*scale and
+//      qjl_scale*scale*|q_rot|*S so that the streaming loop needs no other constants.
+//   2. attend_split: grid (split, query tile, batch*kv_head).  A warp step covers 8 tokens
+//      (d>=96) / 16 (d=64) / 32 (d=32): lane = (token, 32-coordinate slot).  Each lane reads
+//      its slot's words of the key-code, sign and value-code rows (adjacent lanes read
+//      adjacent words, so a warp load covers whole contiguous rows), scores 4 query rows in
+//      the rotated domain, runs an online softmax and accumulates sum_k p_k * v_norm_k *
+//      c_V[code] in the ROTATED domain in registers.  Per split it writes (max, sum, acc[d]).
+//   3. merge_splits: combines the splits of a query row and applies Pi once
+//      (out = (acc / sum) @ Pi), which equals un-rotating every value first because the
+//      rotation is linear.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace qkv {
+
+constexpr int kQT = 4;          // query rows per CTA
+constexpr int kAttnWarps = 4;
+constexpr int kMaxSplits = 64;
+
+struct AttnArgs {
+  qkv_cache_t cache;
+  int B, Hq, Hkv, G, q_len, d, causal;
+  int64_t kv_len;
+  const float* qk;      // [rows][2][d]
+  const float* kcent; const float* vcent;
+  float* part;          // [rows][n_splits][d+2]
+  int n_splits; int64_t split_len;
+};
+
+struct AttnPlan { int n_splits; int64_t split_len; int n_qtiles; int64_t rows; size_t qk_bytes, part_bytes; };
+
+static AttnPlan make_plan(int B, int Hq, int Hkv, int q_len, int64_t kv_len, int d) {
+  AttnPlan p;
+  const int G = Hq / (Hkv > 0 ? Hkv : 1);
+  const int nq = G * q_len;
+  p.n_qtiles = (nq + kQT - 1) / kQT;
+  p.rows = static_cast<int64_t>(B) * Hq * q_len;
+  const int nsp = d >= 96 ? 4 : (d == 64 ? 2 : 1);
+  const int64_t chunk = static_cast<int64_t>(kAttnWarps) * (32 / nsp);   // tokens per CTA pass
+  const int64_t ctas = static_cast<int64_t>(B) * Hkv * p.n_qtiles;
+  int64_t want = (4 * kNumSMs + ctas - 1) / (ctas > 0 ? ctas : 1);
+  const int64_t max_by_len = (kv_len + 4 * chunk - 1) / (4 * chunk);
+  if (want > max_by_len) want = max_by_len;
+  if (want > kMaxSplits) want = kMaxSplits;
+  if (want < 1) want = 1;
+  int64_t len = (kv_len + want - 1) / want;
+  len = (len + chunk - 1) / chunk * chunk;
+  if (len < chunk) len = chunk;
+  p.split_len = len;
+  p.n_splits = static_cast<int>((kv_len + len - 1) / len);
+  if (p.n_splits < 1) p.n_splits = 1;
+  p.qk_bytes = static_cast<size_t>(p.rows) * 2 * d * sizeof(float);
+  p.qk_bytes = (p.qk_bytes + 255) / 256 * 256;
+  p.part_bytes = static_cast<size_t>(p.rows) * p.n_splits * (d + 2) * sizeof(float);
+  return p;
+}
+
+// One warp per query row.
+__global__ void rotate_queries_kernel(const void* __restrict__ q, int q_dtype, int64_t rows, int d,
+                                      const float* __restrict__ Pi, const float* __restrict__ S,
+                                      float qjl_scale, float scale, float* __restrict__ qk) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  float x[4];
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int j = lane + 32 * t;
+    x[t] = (j < d) ? load_float(q, q_dtype, row * d + j) : 0.f;
+  }
+  for (int i = 0; i < d; ++i) {
+    float s = 0.f;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int j = lane + 32 * t;
+      if (j < d) s = fmaf(x[t], Pi[i * d + j], s);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(QKV_FULL_MASK, s, o);
+    if (lane == 0) {
+      qk[row * 2 * d + i] = s * scale;
+      qk[row * 2 * d + d + i] = (qjl_scale * scale) * (fabsf(s) * S[i]);
+    }
+  }
+}
+
+// Field c (compile-time) of a W-bit stream held in words w[0..W).
+template <int W>
+__device__ __forceinline__ uint32_t field32(const uint32_t (&w)[W], int c) {
+  const int bit = c * W, wi = bit >> 5, sh = bit & 31;
+  uint32_t v = w[wi] >> sh;
+  if (sh + W > 32) v |= w[(wi + 1 < W) ? wi + 1 : wi] << (32 - sh);
+  return v & ((1u << W) - 1u);
+}
+
+template <int WK, int WV>
+__global__ void __launch_bounds__(kAttnWarps * 32) attend_split_kernel(AttnArgs a) {
+  __shared__ float4 qa[4 * 33];
+  __shared__ float4 wa[4 * 33];
+  __shared__ float kc_s[16];
+  __shared__ float vc_s[16];
+  __shared__ float red_m[kAttnWarps][kQT];
+  __shared__ float red_l[kAttnWarps][kQT];
+  __shared__ float red_acc[kAttnWarps][kQT][kMaxD];
+
+  const int d = a.d;
+  const int nsp = d >= 96 ? 4 : (d == 64 ? 2 : 1);     // lanes per token
+  const int tps = 32 / nsp;                            // tokens per warp step
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int slot = lane % nsp, ts = lane / nsp;
+  const bool slot_live = slot * 32 < d;
+
+  const int split = blockIdx.x, qtile = blockIdx.y;
+  const int seg = blockIdx.z;                 // b * Hkv + hkv
+  const int b = seg / a.Hkv, hkv = seg % a.Hkv;
+  const int nq = a.G * a.q_len;
+
+  // ---- stage the query tile: qa[slot*33 + c] = (q0, q1, q2, q3) of coordinate slot*32+c ----
+  int64_t qrow[kQT];
+  int limit[kQT];
+#pragma unroll
+  for (int q = 0; q < kQT; ++q) {
+    const int r = qtile * kQT + q;
+    if (r < nq) {
+      const int g = r / a.q_len, qi = r % a.q_len;
+      qrow[q] = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
+      limit[q] = a.causal ? static_cast<int>(a.kv_len - a.q_len + qi) : static_cast<int>(a.kv_len - 1);
+    } else {
+      qrow[q] = -1;
+      limit[q] = -1;
+    }
+  }
+  for (int j = threadIdx.x; j < 128; j += blockDim.x) {
+    float qv[kQT], wv[kQT];
+#pragma unroll
+    for (int q = 0; q < kQT; ++q) {
+      const bool ok = qrow[q] >= 0 && j < d;
+      qv[q] = ok ? a.qk[qrow[q] * 2 * d + j] : 0.f;
+      wv[q] = ok ? a.qk[qrow[q] * 2 * d + d + j] : 0.f;
+    }
+    const int jj = (j >> 5) * 33 + (j & 31);
+    qa[jj] = make_float4(qv[0], qv[1], qv[2], qv[3]);
+    wa[jj] = make_float4(wv[0], wv[1], wv[2], wv[3]);
+  }
+  if (threadIdx.x < 16) {
+    kc_s[threadIdx.x] = threadIdx.x < (1 << WK) ? a.kcent[threadIdx.x] : 0.f;
+    vc_s[threadIdx.x] = threadIdx.x < (1 << WV) ? a.vcent[threadIdx.x] : 0.f;
+  }
+  __syncthreads();
+
+  const int64_t t_begin = split * a.split_len;
+  int64_t t_end = t_begin + a.split_len;
+  if (t_end > a.kv_len) t_end = a.kv_len;
+
+  const int words_k = (d >> 5) * WK, words_v = (d >> 5) * WV, words_s = d >> 5;
+  const int64_t seg_row0 = static_cast<int64_t>(seg) * a.cache.capacity;
+  const uint32_t* kcode = reinterpret_cast<const uint32_t*>(a.cache.k_codes) + seg_row0 * words_k;
+  const uint32_t* ksign = reinterpret_cast<const uint32_t*>(a.cache.k_signs) + seg_row0 * words_s;
+  const uint32_t* vcode = reinterpret_cast<const uint32_t*>(a.cache.v_codes) + seg_row0 * words_v;
+  const float* knorm = a.cache.k_norms + seg_row0;
+  const float* vnorm = a.cache.v_norms + seg_row0;
+
+  float m_run[kQT], l_run[kQT], acc[kQT][32];
+#pragma unroll
+  for (int q = 0; q < kQT; ++q) {
+    m_run[q] = -INFINITY;
+    l_run[q] = 0.f;
+#pragma unroll
+    for (int c = 0; c < 32; ++c) acc[q][c] = 0.f;
+  }
+
+  for (int64_t t0 = t_begin + static_cast<int64_t>(warp) * tps; t0 < t_end;
+       t0 += static_cast<int64_t>(kAttnWarps) * tps) {
+    const int64_t tok = t0 + ts;
+    const bool live = tok < t_end && slot_live;
+    uint32_t kw[WK], vw[WV], sw = 0;
+    float kn = 0.f, vn = 0.f;
+#pragma unroll
+    for (int i = 0; i < WK; ++i) kw[i] = live ? __ldg(kcode + tok * words_k + slot * WK + i) : 0u;
+#pragma unroll
+    for (int i = 0; i < WV; ++i) vw[i] = live ? __ldg(vcode + tok * words_v + slot * WV + i) : 0u;
+    if (live) sw = __ldg(ksign + tok * words_s + slot);
+    if (tok < t_end) {                       // every lane of a token, so the softmax stays warp-uniform
+      kn = __ldg(knorm + tok);
+      vn = __ldg(vnorm + tok);
+    }
+    // ---- partial scores over this lane's 32 coordinates -----------------------------------
+    float s[kQT] = {0.f, 0.f, 0.f, 0.f};
+    if (live) {
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const float kc = kc_s[field32<WK>(kw, c)];
+        const float4 qv = qa[slot * 33 + c];
+        const float4 wv = wa[slot * 33 + c];
+        const bool pos = (sw >> c) & 1u;
+        s[0] = fmaf(qv.x, kc, s[0]) + (pos ? wv.x : -wv.x);
+        s[1] = fmaf(qv.y, kc, s[1]) + (pos ? wv.y : -wv.y);
+        s[2] = fmaf(qv.z, kc, s[2]) + (pos ? wv.z : -wv.z);
+        s[3] = fmaf(qv.w, kc, s[3]) + (pos ? wv.w : -wv.w);
+      }
+    }
+    for (int o = 1; o < nsp; o <<= 1) {
+#pragma unroll
+      for (int q = 0; q < kQT; ++q) s[q] += __shfl_xor_sync(QKV_FULL_MASK, s[q], o);
+    }
+    // ---- online softmax --------------------------------------------------------------------
+    float sc[kQT], mx[kQT];
+    bool grew = false;
+#pragma unroll
+    for (int q = 0; q < kQT; ++q) {
+      const bool vis = tok < t_end && tok <= limit[q];
+      sc[q] = vis ? kn * s[q] : -INFINITY;
+      mx[q] = sc[q];
+    }
+    for (int o = nsp; o < 32; o <<= 1) {
+#pragma unroll
+      for (int q = 0; q < kQT; ++q) mx[q] = fmaxf(mx[q], __shfl_xor_sync(QKV_FULL_MASK, mx[q], o));
+    }
+#pragma unroll
+    for (int q = 0; q < kQT; ++q) grew |= mx[q] > m_run[q];
+    if (grew) {                                   // warp-uniform: mx and m_run are
+#pragma unroll
+      for (int q = 0; q < kQT; ++q) {
+        if (mx[q] > m_run[q]) {
+          const float alpha = (m_run[q] == -INFINITY) ? 0.f : expf(m_run[q] - mx[q]);
+          m_run[q] = mx[q];
+          l_run[q] *= alpha;
+#pragma unroll
+          for (int c = 0; c < 32; ++c) acc[q][c] *= alpha;
+        }
+      }
+    }
+    float pv[kQT];
+#pragma unroll
+    for (int q = 0; q < kQT; ++q) {
+      const float p = (sc[q] == -INFINITY) ? 0.f : expf(sc[q] - m_run[q]);
+      l_run[q] += p;
+      pv[q] = p * vn;
+    }
+    // ---- values: acc[q][c] += p * v_norm * c_V[code] ------------------------------------------
+    if (live) {
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const float vc = vc_s[field32<WV>(vw, c)];
+#pragma unroll
+        for (int q = 0; q < kQT; ++q) acc[q][c] = fmaf(pv[q], vc, acc[q][c]);
+      }
+    }
+  }
+
+  // ---- reduce over the token lanes of the warp, then over warps -------------------------------
+  for (int o = nsp; o < 32; o <<= 1) {
+#pragma unroll
+    for (int q = 0; q < kQT; ++q) {
+      l_run[q] += __shfl_xor_sync(QKV_FULL_MASK, l_run[q], o);
+#pragma unroll
+      for (int c = 0; c < 32; ++c) acc[q][c] += __shfl_xor_sync(QKV_FULL_MASK, acc[q][c], o);
+    }
+  }
+  if (ts == 0) {
+#pragma unroll
+    for (int q = 0; q < kQT; ++q) {
+      if (slot == 0) { red_m[warp][q] = m_run[q]; red_l[warp][q] = l_run[q]; }
+      if (slot_live) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) red_acc[warp][q][slot * 32 + c] = acc[q][c];
+      }
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < kQT * (d + 2); idx += blockDim.x) {
+    const int q = idx / (d + 2), e = idx % (d + 2);
+    if (qrow[q] < 0) continue;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, red_m[w][q]);
+    float v = 0.f;
+    if (e == 0) {
+      v = M;
+    } else {
+#pragma unroll
+      for (int w = 0; w < kAttnWarps; ++w) {
+        const float f = (red_m[w][q] == -INFINITY) ? 0.f : expf(red_m[w][q] - M);
+        v += f * (e == 1 ? red_l[w][q] : red_acc[w][q][e - 2]);
+      }
+    }
+    a.part[(qrow[q] * a.n_splits + split) * (d + 2) + e] = v;
+  }
+}
+
+// One CTA per query row: combine splits, normalise, un-rotate.
+__global__ void merge_splits_kernel(const float* __restrict__ part, int n_splits, int d,
+                                    const float* __restrict__ Pi, float* __restrict__ out) {
+  __shared__ float vec[kMaxD];
+  __shared__ float wsplit[kMaxSplits];
+  __shared__ float inv_l;
+  const int64_t row = blockIdx.x;
+  const float* p = part + row * n_splits * (d + 2);
+  if (threadIdx.x == 0) {
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, p[s * (d + 2)]);
+    float L = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float m = p[s * (d + 2)];
+      const float f = (m == -INFINITY) ? 0.f : expf(m - M);
+      wsplit[s] = f;
+      L += f * p[s * (d + 2) + 1];
+    }
+    inv_l = 1.f / fmaxf(L, 1e-30f);
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < d; j += blockDim.x) {
+    float v = 0.f;
+    for (int s = 0; s < n_splits; ++s) v += wsplit[s] * p[s * (d + 2) + 2 + j];
+    vec[j] = v * inv_l;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float o = 0.f;
+    for (int j = 0; j < d; ++j) o = fmaf(vec[j], Pi[j * d + i], o);
+    out[row * d + i] = o;
+  }
+}
+
+// Host-side launcher shared with the index scan.
+int launch_rotate_queries(const void* q, int q_dtype, int64_t rows, int d, const float* Pi, const float* S,
+                          float qjl_scale, float scale, float* qk, cudaStream_t st) {
+  const int warps = 4;
+  rotate_queries_kernel<<<static_cast<unsigned>((rows + warps - 1) / warps), warps * 32, 0, st>>>(
+      q, q_dtype, rows, d, Pi, S, qjl_scale, scale, qk);
+  return check_launch();
+}
+
+typedef void (*AttnKernel)(AttnArgs);
+
+template <int WK>
+static AttnKernel pick_v(int wv) {
+  switch (wv) {
+    case 1: return attend_split_kernel<WK, 1>;
+    case 2: return attend_split_kernel<WK, 2>;
+    case 3: return attend_split_kernel<WK, 3>;
+    default: return attend_split_kernel<WK, 4>;
+  }
+}
+
+static AttnKernel pick(int wk, int wv) {
+  switch (wk) {
+    case 1: return pick_v<1>(wv);
+    case 2: return pick_v<2>(wv);
+    default: return pick_v<3>(wv);
+  }
+}
+
+}  // namespace qkv
+
+using namespace qkv;
+
+extern "C" size_t qkv_attention_workspace_bytes(int B, int Hq, int Hkv, int q_len, int64_t kv_len, int d) {
+  if (B < 1 || Hq < 1 || Hkv < 1 || q_len < 1 || kv_len < 1 || d < 32) return 0;
+  const AttnPlan p = make_plan(B, Hq, Hkv, q_len, kv_len, d);
+  return p.qk_bytes + p.part_bytes;
+}
+
+extern "C" int qkv_attention(const void* q, int q_dtype, qkv_cache_t cache,
+                             int B, int Hq, int Hkv, int q_len, int64_t kv_len, int d,
+                             int key_bits, int val_bits,
+                             const float* Pi, const float* key_centroids, const float* val_centroids,
+                             const float* S, float qjl_scale, float scale, int causal,
+                             float* out, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!q || !cache.k_codes || !cache.k_signs || !cache.k_norms || !cache.v_codes || !cache.v_norms ||
+      !Pi || !key_centroids || !val_centroids || !S || !out || !workspace)
+    return QKV_ENULL;
+  if (q_dtype != QKV_F32 && q_dtype != QKV_BF16 && q_dtype != QKV_F16) return QKV_EDTYPE;
+  if (d < 32 || d > kMaxD || (d & 31)) return QKV_EDIM;
+  if (B < 1 || Hq < 1 || Hkv < 1 || q_len < 1 || kv_len < 1 || kv_len > cache.capacity ||
+      kv_len > 0x7fffffff || Hq % Hkv != 0)
+    return QKV_EDIM;
+  if (key_bits < 2 || key_bits > 4 || val_bits < 1 || val_bits > 4) return QKV_EBITS;
+  if (causal && q_len > kv_len) return QKV_EARG;
+  const uintptr_t al = reinterpret_cast<uintptr_t>(cache.k_codes) | reinterpret_cast<uintptr_t>(cache.k_signs) |
+                       reinterpret_cast<uintptr_t>(cache.v_codes) | reinterpret_cast<uintptr_t>(workspace);
+  if (al & 15u) return QKV_EALIGN;
+  const AttnPlan p = make_plan(B, Hq, Hkv, q_len, kv_len, d);
+  if (workspace_bytes < p.qk_bytes + p.part_bytes) return QKV_EWORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  float* qk = reinterpret_cast<float*>(workspace);
+  float* part = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + p.qk_bytes);
+  int rc = launch_rotate_queries(q, q_dtype, p.rows, d, Pi, S, qjl_scale, scale, qk, st);
+  if (rc) return rc;
+
+  AttnArgs a{};
+  a.cache = cache; a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.G = Hq / Hkv; a.q_len = q_len; a.d = d;
+  a.causal = causal; a.kv_len = kv_len; a.qk = qk; a.kcent = key_centroids; a.vcent = val_centroids;
+  a.part = part; a.n_splits = p.n_splits; a.split_len = p.split_len;
+  const dim3 grid(p.n_splits, p.n_qtiles, B * Hkv);
+  pick(key_bits - 1, val_bits)<<<grid, kAttnWarps * 32, 0, st>>>(a);
+  merge_splits_kernel<<<static_cast<unsigned>(p.rows), 128, 0, st>>>(part, p.n_splits, d, Pi, out);
+  return check_launch();
+}

@@ -1,0 +1,236 @@
+"""QuashKVEngine: compressed KV storage and attention over it.
+
+Same constructor, methods and error texts as the reference's engine
+(quashkv/engine.py:54-360).  What differs is underneath:
+
+* storage is always the packed form, kept in five pre-allocated planes
+  ``[batch*heads, capacity, bytes]`` that grow geometrically; ``append`` compresses
+  straight into the tail of the planes (no per-call block tensors, no
+  concatenation);
+* ``attention`` is one call of the packed-cache attention kernel (online softmax,
+  split over the KV length, values accumulated in the rotated domain);
+* ``_cache`` is a list of per-append block *views* built on demand: packed views of
+  the planes when ``pack_storage=True``, unpacked copies when ``False`` (what the
+  reference stores), so code that inspects blocks keeps working.
+
+Query heads may outnumber KV heads (grouped-query attention, query head h reads KV
+head h // group); the reference requires equal counts.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import ops
+from .constants import DEFAULT_SEED, DEFAULT_TOTAL_BITS
+from .quantizer import InnerProductQuantizer, MSEQuantizer
+
+
+@dataclass
+class CompressedKVBlock:
+    """One appended block (field meaning as in reference engine.py:30-51)."""
+    mse_indices: torch.Tensor
+    qjl_signs: torch.Tensor
+    key_norms: torch.Tensor
+    val_indices: torch.Tensor
+    val_norms: torch.Tensor
+    seq_len: int
+    packed: bool = False
+
+
+class QuashKVEngine:
+    def __init__(self, head_dim: int = 128, key_bits: int = DEFAULT_TOTAL_BITS,
+                 value_bits: int = DEFAULT_TOTAL_BITS, seed: int = DEFAULT_SEED,
+                 device="cpu", pack_storage: bool = False):
+        self.head_dim, self.key_bits, self.value_bits, self.seed = head_dim, key_bits, value_bits, seed
+        self.device = torch.device(device)
+        self.pack_storage = pack_storage
+        self.key_quantizer = InnerProductQuantizer(d=head_dim, total_bits=key_bits, seed=seed, device=device)
+        self.value_quantizer = MSEQuantizer(d=head_dim, bits=value_bits, seed=seed, device=device)
+        self._planes = None          # dict of the five planes
+        self._shape = None           # (batch, heads)
+        self._capacity = 0
+        self._total_tokens = 0
+        self._block_lens: list[int] = []
+        self._block_cache = None
+
+    # ---- compression ------------------------------------------------------------------------
+    def compress_keys(self, keys: torch.Tensor):
+        return self.key_quantizer.compress(keys)
+
+    def compress_values(self, values: torch.Tensor):
+        return self.value_quantizer.compress(values)
+
+    # ---- storage ----------------------------------------------------------------------------
+    def _row_bytes(self):
+        d = self.head_dim
+        return (ops.packed_row_bytes(d, self.key_bits - 1), ops.packed_row_bytes(d, 1),
+                ops.packed_row_bytes(d, self.value_bits))
+
+    def _allocate(self, segments: int, capacity: int, device) -> dict:
+        pk, ps, pv = self._row_bytes()
+        u8 = dict(dtype=torch.uint8, device=device)
+        f32 = dict(dtype=torch.float32, device=device)
+        return {
+            "k_codes": torch.zeros((segments, capacity, pk), **u8),
+            "k_signs": torch.zeros((segments, capacity, ps), **u8),
+            "k_norms": torch.zeros((segments, capacity), **f32),
+            "v_codes": torch.zeros((segments, capacity, pv), **u8),
+            "v_norms": torch.zeros((segments, capacity), **f32),
+        }
+
+    def reserve(self, batch: int, heads: int, capacity: int, device=None) -> None:
+        """Pre-size the planes (optional; ``append`` grows them as needed)."""
+        device = torch.device(device) if device is not None else self.device
+        if self._planes is None:
+            self._shape = (batch, heads)
+            self._planes = self._allocate(batch * heads, capacity, device)
+            self._capacity = capacity
+        elif capacity > self._capacity:
+            grown = self._allocate(self._shape[0] * self._shape[1], capacity, self._planes["k_norms"].device)
+            for name, plane in self._planes.items():
+                grown[name][:, :self._total_tokens] = plane[:, :self._total_tokens]
+            self._planes, self._capacity = grown, capacity
+            self._block_cache = None
+
+    def append(self, keys: torch.Tensor, values: torch.Tensor) -> None:
+        """Compress (batch, heads, seq, head_dim) keys and values and add them to the cache."""
+        ops._need_cuda(keys, "QuashKVEngine.append")
+        B, H, S, D = keys.shape
+        if D != self.head_dim or values.shape != keys.shape:
+            raise ValueError(f"Expected keys and values of shape (B, H, S, {self.head_dim})")
+        if self._planes is None:
+            self.reserve(B, H, max(64, S), keys.device)
+        elif (B, H) != self._shape:
+            raise ValueError(f"Cache holds (batch, heads) = {self._shape}, got {(B, H)}")
+        need = self._total_tokens + S
+        if need > self._capacity:
+            self.reserve(B, H, max(need, 2 * self._capacity))
+        kq, vq = self.key_quantizer, self.value_quantizer
+        Pi, k_bounds, k_cents, Sgn = kq._on(keys.device)
+        _, v_bounds, _ = vq._on(keys.device)
+        p = self._planes
+        ops.append_kv(keys, values, Pi, k_bounds, k_cents, Sgn, kq.mse_bits, v_bounds, self.value_bits,
+                      p["k_codes"], p["k_signs"], p["k_norms"], p["v_codes"], p["v_norms"], self._total_tokens)
+        self._block_lens.append(S)
+        self._total_tokens = need
+        self._block_cache = None
+
+    def clear(self) -> None:
+        self._total_tokens = 0
+        self._block_lens = []
+        self._block_cache = None
+
+    @property
+    def total_tokens(self) -> int:
+        return self._total_tokens
+
+    @property
+    def num_blocks(self) -> int:
+        return len(self._block_lens)
+
+    @property
+    def _cache(self) -> list:
+        """Per-append blocks, (B, H, seq, ...) tensors like the reference keeps."""
+        if self._block_cache is None:
+            blocks, off = [], 0
+            B, H = self._shape if self._shape else (0, 0)
+            for n in self._block_lens:
+                p = self._planes
+                view = lambda t: t[:, off:off + n].reshape(B, H, n, *t.shape[2:])  # noqa: E731
+                mse, sgn, val = view(p["k_codes"]), view(p["k_signs"]), view(p["v_codes"])
+                if not self.pack_storage:
+                    d = self.head_dim
+                    mse = ops.unpack(mse, self.key_bits - 1, d)
+                    sgn = ops.unpack(sgn, 1, d)
+                    val = ops.unpack(val, self.value_bits, d)
+                blocks.append(CompressedKVBlock(mse, sgn, view(p["k_norms"]), val, view(p["v_norms"]), n,
+                                                self.pack_storage))
+                off += n
+            self._block_cache = blocks
+        return self._block_cache
+
+    def _unpack_block(self, block: CompressedKVBlock):
+        """(mse_indices, qjl_signs, val_indices) as one uint8 per coordinate."""
+        if not block.packed:
+            return block.mse_indices, block.qjl_signs, block.val_indices
+        d = self.head_dim
+        return (ops.unpack(block.mse_indices, self.key_bits - 1, d), ops.unpack(block.qjl_signs, 1, d),
+                ops.unpack(block.val_indices, self.value_bits, d))
+
+    # ---- attention --------------------------------------------------------------------------
+    def attention(self, queries: torch.Tensor, scale: Optional[float] = None, causal: bool = False) -> torch.Tensor:
+        """queries (batch, q_heads, q_len, head_dim) -> (batch, q_heads, q_len, head_dim) fp32.
+
+        With ``causal`` the q_len queries are the last q_len positions of the cache."""
+        if not self._block_lens:
+            raise ValueError("No compressed KV blocks in cache. Call append() first.")
+        ops._need_cuda(queries, "QuashKVEngine.attention")
+        if scale is None:
+            scale = 1.0 / math.sqrt(self.head_dim)
+        B, Hq, Q, D = queries.shape
+        Bc, Hkv = self._shape
+        if B != Bc or D != self.head_dim or Hq % Hkv != 0:
+            raise ValueError(f"queries {tuple(queries.shape)} do not match a cache of batch {Bc}, "
+                             f"{Hkv} KV heads, head_dim {self.head_dim}")
+        kq, vq = self.key_quantizer, self.value_quantizer
+        Pi, _, k_cents, Sgn = kq._on(queries.device)
+        _, _, v_cents = vq._on(queries.device)
+        p = self._planes
+        return ops.attention(queries, p["k_codes"], p["k_signs"], p["k_norms"], p["v_codes"], p["v_norms"],
+                             self._total_tokens, Hkv, self.key_bits, self.value_bits, Pi, k_cents, v_cents,
+                             Sgn, kq.qjl_scale, float(scale), bool(causal))
+
+    # ---- decompression of the whole cache (used by the HF-style cache) ----------------------------
+    def decompress_all(self, with_signs: bool = False, out_dtype=torch.float32):
+        """(keys, values) of shape (batch, heads, total_tokens, head_dim).  Keys use the code
+        centroids only unless ``with_signs`` adds the sign term."""
+        B, H = self._shape
+        n, d, p = self._total_tokens, self.head_dim, self._planes
+        kq, vq = self.key_quantizer, self.value_quantizer
+        dev = p["k_norms"].device
+        Pi, _, k_cents, Sgn = kq._on(dev)
+        _, _, v_cents = vq._on(dev)
+        keys = ops.decompress_rows(p["k_codes"], p["k_norms"], Pi, k_cents, kq.mse_bits, d, B * H, n,
+                                   self._capacity, 0, signs=p["k_signs"] if with_signs else None,
+                                   S=Sgn if with_signs else None, qjl_scale=kq.qjl_scale, out_dtype=out_dtype)
+        vals = ops.decompress_rows(p["v_codes"], p["v_norms"], Pi, v_cents, self.value_bits, d, B * H, n,
+                                   self._capacity, 0, out_dtype=out_dtype)
+        return keys.reshape(B, H, n, d), vals.reshape(B, H, n, d)
+
+    # ---- statistics (formulas of reference engine.py:305-337) -------------------------------------
+    def compression_ratio(self, original_dtype: torch.dtype = torch.float16) -> float:
+        if not self._block_lens:
+            return 1.0
+        orig_bits = torch.finfo(original_dtype).bits
+        per_token = 2 * self.head_dim * orig_bits
+        compressed = self.key_bits * self.head_dim + 32 + self.value_bits * self.head_dim + 32
+        return per_token / compressed
+
+    def actual_memory_bytes(self) -> int:
+        """Bytes of the stored blocks: packed rows, or one byte per coordinate when
+        ``pack_storage=False`` (what the reference would hold), plus fp32 norms."""
+        if not self._block_lens:
+            return 0
+        B, H = self._shape
+        d = self.head_dim
+        pk, ps, pv = self._row_bytes() if self.pack_storage else (d, d, d)
+        return B * H * self._total_tokens * (pk + ps + pv + 8)
+
+    def to(self, device) -> "QuashKVEngine":
+        self.device = torch.device(device)
+        self.key_quantizer.to(device)
+        self.value_quantizer.to(device)
+        if self._planes is not None:
+            self._planes = {k: v.to(device) for k, v in self._planes.items()}
+            self._block_cache = None
+        return self
+
+    def __repr__(self) -> str:
+        return (f"QuashKVEngine(head_dim={self.head_dim}, key_bits={self.key_bits}, "
+                f"value_bits={self.value_bits}, cached_tokens={self._total_tokens}, "
+                f"blocks={len(self._block_lens)}, device={self.device})")

@@ -1,0 +1,417 @@
+"""PyTorch custom ops (namespace ``quashkv_b200``) over the C ABI of libquashkv_b200.so.
+
+Each op allocates its outputs and workspace with torch, passes raw device
+pointers and the current CUDA stream to one ``extern "C"`` entry point, and
+returns.  Only a CUDA implementation is registered: calling an op on CPU
+tensors raises from the dispatcher, there is no fallback.
+
+Plain Python wrappers of the same names (``ops.compress_mse(...)``) are what the
+host classes call; they normalise shapes and dtypes and then invoke the
+registered op.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import Cache, Rows
+
+_DT = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _lib.F16}
+
+
+def packed_row_bytes(d: int, bits: int) -> int:
+    """Bytes of one packed row: 3-bit rows are whole 8-field groups (3 bytes each), like the
+    reference's pack_bits (quashkv/packing.py:61-81); otherwise ceil(d*bits/8)."""
+    if bits == 8:
+        return d
+    return 3 * ((d + 7) // 8) if bits == 3 else (d * bits + 7) // 8
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream(t: torch.Tensor):
+    return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _f32(t: torch.Tensor) -> torch.Tensor:
+    return t.detach().to(torch.float32).contiguous()
+
+
+def _flat(x: torch.Tensor):
+    d = x.shape[-1]
+    if x.dtype not in _DT:
+        x = x.float()
+    return x.detach().reshape(-1, d).contiguous(), d
+
+
+def _dense(n: int) -> Rows:
+    return Rows(max(n, 1), 0, 0)
+
+
+# ---------------------------------------------------------------------------------------------
+# op implementations (CUDA only)
+# ---------------------------------------------------------------------------------------------
+
+@torch.library.custom_op("quashkv_b200::pack", mutates_args=(), device_types="cuda")
+def _pack(codes: torch.Tensor, bits: int) -> torch.Tensor:
+    d = codes.shape[-1]
+    flat = codes.reshape(-1, d).contiguous()
+    out = torch.empty((flat.shape[0], packed_row_bytes(d, bits)), dtype=torch.uint8, device=codes.device)
+    with torch.cuda.device(codes.device):
+        _lib.check(_lib.lib().qkv_pack(_p(flat), _p(out), flat.shape[0], d, bits, _stream(codes)), "pack")
+    return out.reshape(*codes.shape[:-1], -1)
+
+
+@_pack.register_fake
+def _(codes, bits):
+    return codes.new_empty((*codes.shape[:-1], packed_row_bytes(codes.shape[-1], bits)))
+
+
+@torch.library.custom_op("quashkv_b200::unpack", mutates_args=(), device_types="cuda")
+def _unpack(packed: torch.Tensor, bits: int, d: int) -> torch.Tensor:
+    flat = packed.reshape(-1, packed.shape[-1])
+    need = packed_row_bytes(d, bits)
+    if flat.shape[1] < need:
+        raise ValueError(f"packed rows of {flat.shape[1]} bytes cannot hold {d} fields of {bits} bits")
+    flat = flat[:, :need].contiguous()
+    out = torch.empty((flat.shape[0], d), dtype=torch.uint8, device=packed.device)
+    with torch.cuda.device(packed.device):
+        _lib.check(_lib.lib().qkv_unpack(_p(flat), _p(out), flat.shape[0], d, bits, _stream(packed)), "unpack")
+    return out.reshape(*packed.shape[:-1], d)
+
+
+@_unpack.register_fake
+def _(packed, bits, d):
+    return packed.new_empty((*packed.shape[:-1], d))
+
+
+@torch.library.custom_op("quashkv_b200::compress_mse", mutates_args=(), device_types="cuda")
+def _compress_mse(x: torch.Tensor, Pi: torch.Tensor, boundaries: torch.Tensor, bits: int,
+                  packed: bool) -> tuple[torch.Tensor, torch.Tensor]:
+    flat, d = _flat(x)
+    n = flat.shape[0]
+    width = packed_row_bytes(d, bits) if packed else d
+    codes = torch.empty((n, width), dtype=torch.uint8, device=x.device)
+    norms = torch.empty((n,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().qkv_compress_mse(
+            _p(flat), _DT[flat.dtype], d, n, d, _p(_f32(Pi)), _p(_f32(boundaries)), bits,
+            _p(codes), int(packed), _p(norms), _dense(n), _stream(x)), "compress_mse")
+    return codes.reshape(*x.shape[:-1], width), norms.reshape(x.shape[:-1])
+
+
+@_compress_mse.register_fake
+def _(x, Pi, boundaries, bits, packed):
+    d = x.shape[-1]
+    width = packed_row_bytes(d, bits) if packed else d
+    return (x.new_empty((*x.shape[:-1], width), dtype=torch.uint8),
+            x.new_empty(x.shape[:-1], dtype=torch.float32))
+
+
+@torch.library.custom_op("quashkv_b200::compress_ip", mutates_args=(), device_types="cuda")
+def _compress_ip(x: torch.Tensor, Pi: torch.Tensor, boundaries: torch.Tensor, centroids: torch.Tensor,
+                 S: torch.Tensor, mse_bits: int, packed: bool) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    flat, d = _flat(x)
+    n = flat.shape[0]
+    cw = packed_row_bytes(d, mse_bits) if packed else d
+    sw = packed_row_bytes(d, 1) if packed else d
+    codes = torch.empty((n, cw), dtype=torch.uint8, device=x.device)
+    signs = torch.empty((n, sw), dtype=torch.uint8, device=x.device)
+    norms = torch.empty((n,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().qkv_compress_ip(
+            _p(flat), _DT[flat.dtype], d, n, d, _p(_f32(Pi)), _p(_f32(boundaries)), _p(_f32(centroids)),
+            mse_bits, _p(_f32(S)), _p(codes), _p(signs), int(packed), _p(norms), _dense(n), _stream(x)),
+            "compress_ip")
+    lead = x.shape[:-1]
+    return codes.reshape(*lead, cw), signs.reshape(*lead, sw), norms.reshape(lead)
+
+
+@_compress_ip.register_fake
+def _(x, Pi, boundaries, centroids, S, mse_bits, packed):
+    d = x.shape[-1]
+    cw = packed_row_bytes(d, mse_bits) if packed else d
+    sw = packed_row_bytes(d, 1) if packed else d
+    return (x.new_empty((*x.shape[:-1], cw), dtype=torch.uint8),
+            x.new_empty((*x.shape[:-1], sw), dtype=torch.uint8),
+            x.new_empty(x.shape[:-1], dtype=torch.float32))
+
+
+@torch.library.custom_op("quashkv_b200::append_kv", mutates_args=("k_codes", "k_signs", "k_norms", "v_codes", "v_norms"),
+                         device_types="cuda")
+def _append_kv(keys: torch.Tensor, values: torch.Tensor, Pi: torch.Tensor,
+               k_bounds: torch.Tensor, k_cents: torch.Tensor, S: torch.Tensor, mse_bits: int,
+               v_bounds: torch.Tensor, val_bits: int,
+               k_codes: torch.Tensor, k_signs: torch.Tensor, k_norms: torch.Tensor,
+               v_codes: torch.Tensor, v_norms: torch.Tensor, offset: int) -> None:
+    """Compress (B,H,S,d) keys and values straight into the packed cache planes
+    [B*H, capacity, ...] at rows offset..offset+S of every (batch, head) segment."""
+    kf, d = _flat(keys)
+    vf, _ = _flat(values)
+    s_new = keys.shape[-2]
+    cap = k_norms.shape[-1]
+    rows = Rows(s_new, cap, offset)
+    Pi32 = _f32(Pi)
+    with torch.cuda.device(keys.device):
+        L = _lib.lib()
+        _lib.check(L.qkv_compress_ip(
+            _p(kf), _DT[kf.dtype], d, kf.shape[0], d, _p(Pi32), _p(_f32(k_bounds)), _p(_f32(k_cents)), mse_bits,
+            _p(_f32(S)), _p(k_codes), _p(k_signs), 1, _p(k_norms), rows, _stream(keys)), "append keys")
+        _lib.check(L.qkv_compress_mse(
+            _p(vf), _DT[vf.dtype], d, vf.shape[0], d, _p(Pi32), _p(_f32(v_bounds)), val_bits,
+            _p(v_codes), 1, _p(v_norms), rows, _stream(keys)), "append values")
+
+
+@torch.library.custom_op("quashkv_b200::compress_ip_into", mutates_args=("codes", "signs", "norms"),
+                         device_types="cuda")
+def _compress_ip_into(x: torch.Tensor, Pi: torch.Tensor, boundaries: torch.Tensor, centroids: torch.Tensor,
+                      S: torch.Tensor, mse_bits: int, codes: torch.Tensor, signs: torch.Tensor,
+                      norms: torch.Tensor, offset: int) -> None:
+    """Compress (N,d) vectors into packed planes [capacity, bytes] at rows offset..offset+N."""
+    flat, d = _flat(x)
+    n = flat.shape[0]
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().qkv_compress_ip(
+            _p(flat), _DT[flat.dtype], d, n, d, _p(_f32(Pi)), _p(_f32(boundaries)), _p(_f32(centroids)),
+            mse_bits, _p(_f32(S)), _p(codes), _p(signs), 1, _p(norms), Rows(max(n, 1), 0, offset),
+            _stream(x)), "compress_ip_into")
+
+
+@torch.library.custom_op("quashkv_b200::compress_mixed", mutates_args=(), device_types="cuda")
+def _compress_mixed(x: torch.Tensor, Pi: torch.Tensor, is_outlier: torch.Tensor,
+                    bounds_out: torch.Tensor, bits_out: int, bounds_reg: torch.Tensor, bits_reg: int,
+                    packed: bool) -> tuple[torch.Tensor, torch.Tensor]:
+    flat, d = _flat(x)
+    n = flat.shape[0]
+    mask = is_outlier.to(torch.uint8).contiguous()
+    n_out = int(mask.sum().item()) if packed else 0
+    width = int(_lib.lib().qkv_mixed_row_bytes(d, n_out, bits_out, bits_reg)) if packed else d
+    codes = torch.empty((n, width), dtype=torch.uint8, device=x.device)
+    norms = torch.empty((n,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().qkv_compress_mixed(
+            _p(flat), _DT[flat.dtype], d, n, d, _p(_f32(Pi)), _p(mask), _p(_f32(bounds_out)), bits_out,
+            _p(_f32(bounds_reg)), bits_reg, _p(codes), int(packed), _p(norms), _dense(n), _stream(x)),
+            "compress_mixed")
+    return codes.reshape(*x.shape[:-1], width), norms.reshape(x.shape[:-1])
+
+
+@torch.library.custom_op("quashkv_b200::decompress", mutates_args=(), device_types="cuda")
+def _decompress(codes: torch.Tensor, signs: Optional[torch.Tensor], norms: torch.Tensor, Pi: torch.Tensor,
+                centroids: torch.Tensor, bits: int, S: Optional[torch.Tensor], qjl_scale: float,
+                packed: bool, d: int, seg_len: int, seg_stride: int, seg_off: int, n_vec: int,
+                out_dtype: torch.dtype) -> torch.Tensor:
+    """Rows of the code/norm planes are addressed with (seg_len, seg_stride, seg_off); the
+    output is dense (n_vec, d)."""
+    out = torch.empty((n_vec, d), dtype=out_dtype, device=codes.device)
+    with torch.cuda.device(codes.device):
+        _lib.check(_lib.lib().qkv_decompress(
+            _p(codes), _p(signs), int(packed), _p(norms), Rows(seg_len, seg_stride, seg_off), n_vec, d,
+            _p(_f32(Pi)), _p(_f32(centroids)), bits, _p(None if S is None else _f32(S)), float(qjl_scale),
+            _p(out), _DT[out_dtype], d, _stream(codes)), "decompress")
+    return out
+
+
+@_decompress.register_fake
+def _(codes, signs, norms, Pi, centroids, bits, S, qjl_scale, packed, d, seg_len, seg_stride, seg_off,
+      n_vec, out_dtype):
+    return codes.new_empty((n_vec, d), dtype=out_dtype)
+
+
+@torch.library.custom_op("quashkv_b200::decompress_mixed", mutates_args=(), device_types="cuda")
+def _decompress_mixed(codes: torch.Tensor, norms: torch.Tensor, Pi: torch.Tensor, is_outlier: torch.Tensor,
+                      cents_out: torch.Tensor, bits_out: int, cents_reg: torch.Tensor, bits_reg: int,
+                      packed: bool, d: int) -> torch.Tensor:
+    flat = codes.reshape(-1, codes.shape[-1]).contiguous()
+    n = flat.shape[0]
+    out = torch.empty((n, d), dtype=torch.float32, device=codes.device)
+    with torch.cuda.device(codes.device):
+        _lib.check(_lib.lib().qkv_decompress_mixed(
+            _p(flat), int(packed), _p(_f32(norms).reshape(-1)), _dense(n), n, d, _p(_f32(Pi)),
+            _p(is_outlier.to(torch.uint8).contiguous()), _p(_f32(cents_out)), bits_out,
+            _p(_f32(cents_reg)), bits_reg, _p(out), _lib.F32, d, _stream(codes)), "decompress_mixed")
+    return out.reshape(*codes.shape[:-1], d)
+
+
+@torch.library.custom_op("quashkv_b200::attention", mutates_args=(), device_types="cuda")
+def _attention(q: torch.Tensor, k_codes: torch.Tensor, k_signs: torch.Tensor, k_norms: torch.Tensor,
+               v_codes: torch.Tensor, v_norms: torch.Tensor, kv_len: int, n_kv_heads: int,
+               key_bits: int, val_bits: int, Pi: torch.Tensor, key_centroids: torch.Tensor,
+               val_centroids: torch.Tensor, S: torch.Tensor, qjl_scale: float, scale: float,
+               causal: bool) -> torch.Tensor:
+    """q (B,Hq,Q,d); planes [B*Hkv, capacity, bytes] packed; returns (B,Hq,Q,d) fp32."""
+    B, Hq, Q, d = q.shape
+    if q.dtype not in _DT:
+        q = q.float()
+    qc = q.detach().contiguous()
+    cap = k_norms.shape[-1]
+    out = torch.empty((B, Hq, Q, d), dtype=torch.float32, device=q.device)
+    L = _lib.lib()
+    ws_bytes = L.qkv_attention_workspace_bytes(B, Hq, n_kv_heads, Q, kv_len, d)
+    ws = torch.empty((max(ws_bytes, 16),), dtype=torch.uint8, device=q.device)
+    cache = Cache(k_codes.data_ptr(), k_signs.data_ptr(), k_norms.data_ptr(), v_codes.data_ptr(),
+                  v_norms.data_ptr(), cap)
+    with torch.cuda.device(q.device):
+        _lib.check(L.qkv_attention(
+            _p(qc), _DT[qc.dtype], cache, B, Hq, n_kv_heads, Q, kv_len, d, key_bits, val_bits,
+            _p(_f32(Pi)), _p(_f32(key_centroids)), _p(_f32(val_centroids)), _p(_f32(S)),
+            float(qjl_scale), float(scale), int(causal), _p(out), _p(ws), ws_bytes, _stream(q)), "attention")
+    return out
+
+
+@_attention.register_fake
+def _(q, k_codes, k_signs, k_norms, v_codes, v_norms, kv_len, n_kv_heads, key_bits, val_bits, Pi,
+      key_centroids, val_centroids, S, qjl_scale, scale, causal):
+    return q.new_empty(q.shape, dtype=torch.float32)
+
+
+@torch.library.custom_op("quashkv_b200::index_scan_topk", mutates_args=(), device_types="cuda")
+def _index_scan_topk(queries: torch.Tensor, db_codes: torch.Tensor, db_signs: torch.Tensor,
+                     db_norms: torch.Tensor, n_vectors: int, bits: int, Pi: torch.Tensor,
+                     centroids: torch.Tensor, S: torch.Tensor, qjl_scale: float, k: int,
+                     id_base: int) -> tuple[torch.Tensor, torch.Tensor]:
+    qf = _f32(queries)
+    M, d = qf.shape
+    scores = torch.empty((M, k), dtype=torch.float32, device=qf.device)
+    ids = torch.empty((M, k), dtype=torch.int64, device=qf.device)
+    L = _lib.lib()
+    ws_bytes = L.qkv_index_workspace_bytes(n_vectors, M, d, k)
+    ws = torch.empty((max(ws_bytes, 16),), dtype=torch.uint8, device=qf.device)
+    with torch.cuda.device(qf.device):
+        _lib.check(L.qkv_index_scan_topk(
+            _p(qf), M, d, _p(db_codes), _p(db_signs), _p(db_norms), n_vectors, bits, _p(_f32(Pi)),
+            _p(_f32(centroids)), _p(_f32(S)), float(qjl_scale), k, id_base, _p(scores), _p(ids),
+            _p(ws), ws_bytes, _stream(qf)), "index_scan_topk")
+    return scores, ids
+
+
+@_index_scan_topk.register_fake
+def _(queries, db_codes, db_signs, db_norms, n_vectors, bits, Pi, centroids, S, qjl_scale, k, id_base):
+    M = queries.shape[0]
+    return queries.new_empty((M, k), dtype=torch.float32), queries.new_empty((M, k), dtype=torch.int64)
+
+
+@torch.library.custom_op("quashkv_b200::index_scores", mutates_args=(), device_types="cuda")
+def _index_scores(queries: torch.Tensor, db_codes: torch.Tensor, db_signs: torch.Tensor,
+                  db_norms: torch.Tensor, n_vectors: int, bits: int, Pi: torch.Tensor,
+                  centroids: torch.Tensor, S: torch.Tensor, qjl_scale: float) -> torch.Tensor:
+    qf = _f32(queries)
+    M, d = qf.shape
+    out = torch.empty((M, n_vectors), dtype=torch.float32, device=qf.device)
+    L = _lib.lib()
+    ws_bytes = L.qkv_index_workspace_bytes(n_vectors, M, d, 1)
+    ws = torch.empty((max(ws_bytes, 16),), dtype=torch.uint8, device=qf.device)
+    with torch.cuda.device(qf.device):
+        _lib.check(L.qkv_index_scores(
+            _p(qf), M, d, _p(db_codes), _p(db_signs), _p(db_norms), n_vectors, bits, _p(_f32(Pi)),
+            _p(_f32(centroids)), _p(_f32(S)), float(qjl_scale), _p(out), _p(ws), ws_bytes, _stream(qf)),
+            "index_scores")
+    return out
+
+
+@torch.library.custom_op("quashkv_b200::topk_merge", mutates_args=(), device_types="cuda")
+def _topk_merge(scores: torch.Tensor, ids: torch.Tensor, k: int) -> tuple[torch.Tensor, torch.Tensor]:
+    s = _f32(scores)
+    i = ids.to(torch.int64).contiguous()
+    M, n_cand = s.shape
+    out_s = torch.empty((M, k), dtype=torch.float32, device=s.device)
+    out_i = torch.empty((M, k), dtype=torch.int64, device=s.device)
+    with torch.cuda.device(s.device):
+        _lib.check(_lib.lib().qkv_topk_merge(_p(s), _p(i), M, n_cand, k, _p(out_s), _p(out_i), _stream(s)),
+                   "topk_merge")
+    return out_s, out_i
+
+
+@_topk_merge.register_fake
+def _(scores, ids, k):
+    M = scores.shape[0]
+    return scores.new_empty((M, k), dtype=torch.float32), ids.new_empty((M, k), dtype=torch.int64)
+
+
+# ---------------------------------------------------------------------------------------------
+# public wrappers
+# ---------------------------------------------------------------------------------------------
+
+def _need_cuda(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(
+            f"quashkv_b200.{what}: expected a CUDA tensor, got device '{t.device}'. The hot path runs "
+            "only as sm_100a kernels; there is no CPU implementation.")
+
+
+def pack(codes, bits):
+    if bits == 8:
+        return codes
+    if bits not in (1, 2, 3, 4):
+        raise ValueError(f"Unsupported bits: {bits}")
+    _need_cuda(codes, "pack")
+    return _pack(codes, bits)
+
+
+def unpack(packed, bits, d):
+    if bits == 8:
+        return packed
+    if bits not in (1, 2, 3, 4):
+        raise ValueError(f"Unsupported bits: {bits}")
+    _need_cuda(packed, "unpack")
+    return _unpack(packed, bits, d)
+
+
+def compress_mse(x, Pi, boundaries, bits, packed=False):
+    _need_cuda(x, "compress_mse")
+    return _compress_mse(x, Pi, boundaries, bits, packed)
+
+
+def compress_ip(x, Pi, boundaries, centroids, S, mse_bits, packed=False):
+    _need_cuda(x, "compress_ip")
+    return _compress_ip(x, Pi, boundaries, centroids, S, mse_bits, packed)
+
+
+def compress_mixed(x, Pi, is_outlier, bounds_out, bits_out, bounds_reg, bits_reg, packed=False):
+    _need_cuda(x, "compress_mixed")
+    return _compress_mixed(x, Pi, is_outlier, bounds_out, bits_out, bounds_reg, bits_reg, packed)
+
+
+def decompress(codes, norms, Pi, centroids, bits, *, signs=None, S=None, qjl_scale=0.0, packed=False,
+               d=None, out_dtype=torch.float32):
+    """Dense planes: codes (..., d) or (..., packed bytes), norms (...)."""
+    _need_cuda(codes, "decompress")
+    if d is None:
+        d = codes.shape[-1]
+    lead = codes.shape[:-1]
+    flat = codes.reshape(-1, codes.shape[-1]).contiguous()
+    sflat = None if signs is None else signs.reshape(-1, signs.shape[-1]).contiguous()
+    n = flat.shape[0]
+    out = _decompress(flat, sflat, _f32(norms).reshape(-1), Pi, centroids, bits, S, qjl_scale, packed, d,
+                      max(n, 1), 0, 0, n, out_dtype)
+    return out.reshape(*lead, d)
+
+
+def decompress_rows(codes, norms, Pi, centroids, bits, d, n_seg, seg_len, seg_stride, seg_off, *,
+                    signs=None, S=None, qjl_scale=0.0, out_dtype=torch.float32):
+    """Packed cache planes [n_seg, capacity, bytes]: rows seg_off..seg_off+seg_len of each segment."""
+    _need_cuda(codes, "decompress_rows")
+    return _decompress(codes, signs, norms, Pi, centroids, bits, S, qjl_scale, True, d,
+                       seg_len, seg_stride, seg_off, n_seg * seg_len, out_dtype)
+
+
+def decompress_mixed(codes, norms, Pi, is_outlier, cents_out, bits_out, cents_reg, bits_reg, packed=False,
+                     d=None):
+    _need_cuda(codes, "decompress_mixed")
+    return _decompress_mixed(codes, norms, Pi, is_outlier, cents_out, bits_out, cents_reg, bits_reg, packed,
+                             codes.shape[-1] if d is None else d)
+
+
+append_kv = _append_kv
+compress_ip_into = _compress_ip_into
+attention = _attention
+index_scan_topk = _index_scan_topk
+index_scores = _index_scores
+topk_merge = _topk_merge
+INDEX_MAX_K = _lib.INDEX_MAX_K

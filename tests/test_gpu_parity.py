@@ -1,0 +1,565 @@
+"""Parity of the CUDA path with the CPU oracle and the reference-generated golden vectors.
+
+Every call goes through the C ABI of libquashkv_b200.so (via the custom ops).  Bars:
+packed bytes, codes, sign bits and top-k ids bit-exact except ties at decision boundaries
+(each mismatch is shown to sit within 1e-6 of a boundary in fp64, and the count is
+reported); norms within 2 fp32 steps; reconstructions and attention outputs within 1e-3
+relative L2 for fp32 inputs and 1e-2 for bf16 (observed values are ~1e-6).
+"""
+
+import ctypes
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import quashkv_b200 as qk
+from quashkv_b200 import _lib, ops
+from quashkv_b200.integrations.hf_cache import QuashKVCache
+from quashkv_b200.triton_kernels import (CompressedBlock, fused_compress_ip, fused_compress_mse,
+                                         fused_decompress_ip, fused_decompress_mse,
+                                         fused_quantized_attention)
+from oracle import quashkv_oracle as orc
+from helpers import code_ties, rel_l2, t, ulp_diff
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+TIE_TOL = 1e-6
+FP32_TOL = 1e-3
+BF16_TOL = 1e-2
+
+
+def assert_codes(x, Pi, bounds, got, want, what, **kw):
+    n_bad, n, dist = code_ties(x, Pi, bounds, got, want, **kw)
+    print(f"[ties] {what}: {n_bad} of {n} differ, max fp64 distance to boundary {dist:.3e}")
+    assert n_bad <= max(2, 2e-5 * n), f"{what}: {n_bad}/{n} mismatches"
+    assert dist < TIE_TOL, f"{what}: mismatch {dist} away from any boundary is not a tie"
+
+
+def consts(golden, d, seed, kbits, vbits=None):
+    c = golden("constants")
+    out = dict(Pi=t(c[f"Pi_d{d}_s{seed}"]), S=t(c[f"S_d{d}_s{seed}"]),
+               kc=t(c[f"cent_d{d}_b{kbits - 1}"]), kb=t(c[f"bnd_d{d}_b{kbits - 1}"]))
+    if vbits:
+        out.update(vc=t(c[f"cent_d{d}_b{vbits}"]), vb=t(c[f"bnd_d{d}_b{vbits}"]))
+    return out
+
+
+def pin_rotation(obj, Pi):
+    """Use the golden rotation (QR may round differently on another host)."""
+    for q in (getattr(obj, "key_quantizer", None), getattr(obj, "value_quantizer", None),
+              getattr(obj, "quantizer", None), obj):
+        if q is None:
+            continue
+        m = getattr(q, "mse_quantizer", q)
+        if hasattr(m, "Pi"):
+            m.Pi = Pi.to(m.Pi.device)
+
+
+# ---------------------------------------------------------------------------------------------
+# packing
+# ---------------------------------------------------------------------------------------------
+
+def test_pack_unpack_bytes_match_reference(golden):
+    g = golden("packing")
+    assert qk.pack_bits(torch.arange(8, dtype=torch.uint8, device=DEV)[None], 3).cpu().tolist() == [[0x88, 0xC6, 0xFA]]
+    assert qk.pack_bits(torch.tensor([[0, 1, 2, 3]], dtype=torch.uint8, device=DEV), 2).cpu().tolist() == [[0xE4]]
+    assert qk.pack_bits(torch.tensor([[1, 2]], dtype=torch.uint8, device=DEV), 4).cpu().tolist() == [[0x21]]
+    for bits in (1, 2, 3, 4):
+        for d in (128, 64, 63, 65, 100, 127, 129, 8, 1):
+            codes, packed = t(g[f"codes_b{bits}_d{d}"]), t(g[f"packed_b{bits}_d{d}"])
+            got = qk.pack_bits(codes.to(DEV), bits)
+            assert got.shape == packed.shape and torch.equal(got.cpu(), packed), (bits, d)
+            back = qk.unpack_bits(packed.to(DEV), bits, d)
+            assert torch.equal(back.cpu(), codes), (bits, d)
+    x = torch.randint(0, 255, (4, 7), dtype=torch.uint8, device=DEV)
+    assert qk.pack_bits(x, 8) is x and qk.unpack_bits(x, 8, 7) is x
+    empty = torch.zeros((0, 64), dtype=torch.uint8, device=DEV)
+    assert qk.pack_bits(empty, 3).shape == (0, 24)
+
+
+# ---------------------------------------------------------------------------------------------
+# quantiser classes and the functional fused_* API
+# ---------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_mse_quantizer_all_widths(golden, d):
+    g, c = golden("quantizers"), golden("constants")
+    x = t(g[f"x_d{d}"])                      # includes a zero row, a 1e-12 row and a one-hot row
+    Pi = t(c[f"Pi_d{d}_s42"])
+    for bits in (1, 2, 3, 4):
+        q = qk.MSEQuantizer(d, bits, seed=42)
+        pin_rotation(q, Pi)
+        idx, nrm = q.compress(x.to(DEV))
+        assert idx.dtype == torch.uint8 and idx.shape == x.shape and nrm.shape == x.shape[:-1]
+        assert_codes(x, Pi, t(c[f"bnd_d{d}_b{bits}"]), idx, t(g[f"mse_idx_d{d}_b{bits}"]), f"mse d={d} b={bits}")
+        assert ulp_diff(nrm, t(g[f"mse_norm_d{d}_b{bits}"])) <= 2
+        # packed output is the reference's pack_bits of the unpacked output
+        pk, nrm2 = q.compress_packed(x.to(DEV))
+        assert torch.equal(pk.cpu(), orc.pack_bits(idx.cpu(), bits)) and torch.equal(nrm, nrm2)
+        # decompress the reference's codes
+        gold_idx, gold_nrm = t(g[f"mse_idx_d{d}_b{bits}"]), t(g[f"mse_norm_d{d}_b{bits}"])
+        rec = q.decompress(gold_idx.to(DEV), gold_nrm.to(DEV))
+        assert rel_l2(rec, t(g[f"mse_rec_d{d}_b{bits}"])) < 1e-5
+        rec_p = q.decompress_packed(orc.pack_bits(gold_idx, bits).to(DEV), gold_nrm.to(DEV))
+        assert torch.equal(rec_p, rec)
+        f_idx, f_nrm = fused_compress_mse(x.to(DEV), Pi.to(DEV), q.codebook.boundaries.to(DEV))
+        assert torch.equal(f_idx, idx) and torch.equal(f_nrm, nrm)
+        f_rec = fused_decompress_mse(gold_idx.to(DEV), gold_nrm.to(DEV), Pi.to(DEV), q.codebook.centroids.to(DEV))
+        assert torch.equal(f_rec, rec)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_ip_quantizer_all_widths(golden, d):
+    g, c = golden("quantizers"), golden("constants")
+    x, Pi, S = t(g[f"x_d{d}"]), t(c[f"Pi_d{d}_s42"]), t(c[f"S_d{d}_s42"])
+    for bits in (2, 3, 4):
+        q = qk.InnerProductQuantizer(d, bits, seed=42)
+        pin_rotation(q, Pi)
+        cent, bnd = t(c[f"cent_d{d}_b{bits - 1}"]), t(c[f"bnd_d{d}_b{bits - 1}"])
+        mse, sg, nrm = q.compress(x.to(DEV))
+        want_mse, want_sg = t(g[f"ip_mse_d{d}_b{bits}"]), t(g[f"ip_qjl_d{d}_b{bits}"])
+        assert_codes(x, Pi, bnd, mse, want_mse, f"ip codes d={d} b={bits}")
+        same_code = (mse.cpu() == want_mse)
+        n_bad, n, dist = code_ties(x, Pi, None, torch.where(same_code, sg.cpu(), want_sg), want_sg, kind="sign",
+                                   centroids=cent, codes_for_resid=want_mse)
+        print(f"[ties] ip signs d={d} b={bits}: {n_bad} of {n}, max |residual| {dist:.3e}")
+        assert n_bad <= 2 and dist < TIE_TOL
+        assert ulp_diff(nrm, t(g[f"ip_norm_d{d}_b{bits}"])) <= 2
+        pm, ps, _ = q.compress_packed(x.to(DEV))
+        assert torch.equal(pm.cpu(), orc.pack_bits(mse.cpu(), bits - 1))
+        assert torch.equal(ps.cpu(), orc.pack_bits(sg.cpu(), 1))
+        rec = fused_decompress_ip(want_mse.to(DEV), want_sg.to(DEV), t(g[f"ip_norm_d{d}_b{bits}"]).to(DEV),
+                                  Pi.to(DEV), cent.to(DEV), S.to(DEV), q.qjl_scale)
+        assert rel_l2(rec, t(g[f"ip_rec_d{d}_b{bits}"])) < 1e-5
+        f = fused_compress_ip(x.to(DEV), Pi.to(DEV), bnd.to(DEV), S.to(DEV), cent.to(DEV))
+        assert torch.equal(f[0], mse) and torch.equal(f[1], sg) and torch.equal(f[2], nrm)
+        # decompress_for_dot against the oracle's score of one query per key
+        qrot = torch.randn(x.shape, generator=torch.Generator().manual_seed(5))
+        want = want_nrm = t(g[f"ip_norm_d{d}_b{bits}"])
+        want = want_nrm * ((qrot * cent[want_mse.long()]).sum(-1)
+                           + q.qjl_scale * (qrot.abs() * (want_sg.float() * 2 - 1) * S).sum(-1))
+        got = q.decompress_for_dot(want_mse.to(DEV), want_sg.to(DEV), want_nrm.to(DEV), qrot.to(DEV))
+        assert rel_l2(got, want) < 1e-5
+
+
+def test_half_precision_inputs_are_exact_upcasts(golden):
+    c = golden("constants")
+    Pi, bnd = t(c["Pi_d128_s42"]), t(c["bnd_d128_b3"])
+    x = torch.randn(777, 128, generator=torch.Generator().manual_seed(8))
+    for dt in (torch.bfloat16, torch.float16):
+        xl = x.to(dt)
+        a = ops.compress_mse(xl.to(DEV), Pi.to(DEV), bnd.to(DEV), 3, packed=True)
+        b = ops.compress_mse(xl.float().to(DEV), Pi.to(DEV), bnd.to(DEV), 3, packed=True)
+        assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+        want, wn = orc.compress_mse(xl.float(), Pi, bnd)
+        assert_codes(xl.float(), Pi, bnd, ops.unpack(a[0], 3, 128), want, f"{dt} input")
+    # low-precision output of decompress
+    idx, nrm = orc.compress_mse(x, Pi, bnd)
+    ref = orc.decompress_mse(idx, nrm, Pi, t(c["cent_d128_b3"]))
+    out = ops.decompress(idx.to(DEV), nrm.to(DEV), Pi.to(DEV), t(c["cent_d128_b3"]).to(DEV), 3,
+                         out_dtype=torch.bfloat16)
+    assert out.dtype == torch.bfloat16 and rel_l2(out.float(), ref) < BF16_TOL
+
+
+def test_shapes_ragged_and_empty(golden):
+    c = golden("constants")
+    for d in (64, 96, 128):
+        q = qk.MSEQuantizer(d, 3, seed=42)
+        pin_rotation(q, t(c[f"Pi_d{d}_s42"]))
+        for shape in ((1, d), (2, 3, 5, d), (65, d), (0, d)):
+            x = torch.randn(*shape, generator=torch.Generator().manual_seed(1))
+            idx, nrm = q.compress(x.to(DEV))
+            assert idx.shape == x.shape and nrm.shape == x.shape[:-1]
+            if x.numel():
+                want, wn = orc.compress_mse(x, q.Pi.cpu(), q.codebook.boundaries.cpu())
+                assert_codes(x, q.Pi.cpu(), q.codebook.boundaries.cpu(), idx, want, f"shape {shape}")
+                assert rel_l2(q.decompress(idx, nrm), orc.decompress_mse(idx.cpu(), nrm.cpu(), q.Pi.cpu(),
+                                                                        q.codebook.centroids.cpu())) < 1e-5
+    # non-contiguous input
+    q = qk.MSEQuantizer(64, 3, seed=42)
+    x = torch.randn(4, 6, 64).transpose(0, 1)
+    a = q.compress(x.to(DEV))[0]
+    b = q.compress(x.contiguous().to(DEV))[0]
+    assert torch.equal(a, b)
+    # dimension that is not a multiple of 32 still compresses and round-trips
+    q = qk.MSEQuantizer(100, 3, seed=1)
+    x = torch.randn(33, 100)
+    idx, nrm = q.compress(x.to(DEV))
+    want, _ = orc.compress_mse(x, q.Pi, q.codebook.boundaries)
+    assert_codes(x, q.Pi, q.codebook.boundaries, idx, want, "d=100")
+    pk, _ = q.compress_packed(x.to(DEV))
+    assert pk.shape == (33, 39) and torch.equal(pk.cpu(), orc.pack_bits(idx.cpu(), 3))
+
+
+# ---------------------------------------------------------------------------------------------
+# mixed precision
+# ---------------------------------------------------------------------------------------------
+
+def test_mixed_precision(golden):
+    g, c = golden("mixed"), golden("constants")
+    x, Pi = t(g["x"]), t(c["Pi_d128_s42"])
+    mp = qk.MixedPrecisionMSEQuantizer(128, 3, 2, 32, seed=42)
+    pin_rotation(mp, Pi)
+    un, _ = mp.compress(x[:64].to(DEV))
+    assert_codes(x[:64], Pi, t(c["bnd_d128_b2"]), un, t(g["codes_uncal"]), "mixed uncalibrated")
+    mp.calibrate(x[:1024].to(DEV))
+    assert mp._outlier_indices.cpu().tolist() == g["channels"].tolist()
+    codes, norms = mp.compress(x[1024:].to(DEV))
+    want = t(g["codes"])
+    mask = mp._outlier_mask.cpu()
+    xs = x[1024:]
+    assert_codes(xs, Pi, t(c["bnd_d128_b3"]), torch.where(mask, codes.cpu(), want), want, "mixed outlier ch")
+    assert_codes(xs, Pi, t(c["bnd_d128_b2"]), torch.where(~mask, codes.cpu(), want), want, "mixed regular ch")
+    assert ulp_diff(norms, t(g["norms"])) <= 2
+    rec = mp.decompress(want.to(DEV), t(g["norms"]).to(DEV))
+    assert rel_l2(rec, t(g["rec"])) < 1e-5
+    # packed mixed row: outlier channels (3-bit stream) then regular channels (2-bit stream)
+    pk, _ = mp.compress(xs.to(DEV), packed=True)
+    assert pk.shape[-1] == 12 + 24
+    cc = codes.cpu()
+    layout = torch.cat([orc.pack_bits(cc[:, mask], 3), orc.pack_bits(cc[:, ~mask], 2)], dim=1)
+    assert torch.equal(pk.cpu(), layout)
+    assert torch.equal(mp.decompress(pk, norms, packed=True), mp.decompress(codes, norms))
+    ipq = qk.MixedPrecisionIPQuantizer(128, 3, 2, 32, seed=42)
+    ipq.set_outlier_channels(mp._outlier_indices)
+    m, s, n = ipq.compress(xs[:32].to(DEV))
+    assert m.shape == s.shape == (32, 128) and int(s.max()) <= 1 and ipq.effective_bits == pytest.approx(2.25)
+
+
+# ---------------------------------------------------------------------------------------------
+# engine: configuration 1 and the multi-block / causal / other-width cases
+# ---------------------------------------------------------------------------------------------
+
+def test_config1_engine(golden):
+    g = golden("config1")
+    k = consts(golden, 128, 0, 3, 3)
+    K, V, Q = t(g["K"]), t(g["V"]), t(g["Q"])
+    eng = qk.QuashKVEngine(128, 3, 3, seed=0, pack_storage=True)
+    pin_rotation(eng, k["Pi"])
+    eng.append(K.to(DEV), V.to(DEV))
+    blk = eng._cache[0]
+    assert blk.packed and blk.mse_indices.shape == (1, 8, 512, 32) and blk.qjl_signs.shape == (1, 8, 512, 16)
+    assert blk.val_indices.shape == (1, 8, 512, 48) and blk.key_norms.shape == (1, 8, 512)
+    mse, sg, val = eng._unpack_block(blk)
+    want_mse, want_sg = orc.unpack_bits(t(g["mse_plane"]), 2, 128), orc.unpack_bits(t(g["qjl_plane"]), 1, 128)
+    want_val = orc.unpack_bits(t(g["val_plane"]), 3, 128)
+    assert_codes(K, k["Pi"], k["kb"], mse, want_mse, "C1 key codes")
+    assert_codes(V, k["Pi"], k["vb"], val, want_val, "C1 value codes")
+    agree = mse.cpu() == want_mse
+    n_bad, n, dist = code_ties(K, k["Pi"], None, torch.where(agree, sg.cpu(), want_sg), want_sg, kind="sign",
+                               centroids=k["kc"], codes_for_resid=want_mse)
+    print(f"[ties] C1 sign bits: {n_bad} of {n}, max |residual| {dist:.3e}")
+    assert n_bad <= 2 and dist < TIE_TOL
+    n_byte = sum(int((a.cpu() != t(g[b])).sum()) for a, b in
+                 ((blk.mse_indices, "mse_plane"), (blk.qjl_signs, "qjl_plane"), (blk.val_indices, "val_plane")))
+    print(f"[ties] C1 packed bytes differing from the reference: {n_byte} of {512 * 8 * 96}")
+    assert ulp_diff(blk.key_norms, t(g["key_norms"])) <= 2 and ulp_diff(blk.val_norms, t(g["val_norms"])) <= 2
+    out = eng.attention(Q.to(DEV))
+    assert out.shape == (1, 8, 1, 128) and out.dtype == torch.float32
+    err = rel_l2(out, t(g["out"]))
+    print(f"[parity] C1 attention rel-L2 vs reference: {err:.3e}")
+    assert err < FP32_TOL
+    err = rel_l2(eng.attention(t(g["Qg"]).to(DEV)), t(g["out_gqa"]))
+    print(f"[parity] C1 grouped-query (32 on 8) rel-L2: {err:.3e}")
+    assert err < FP32_TOL
+    assert eng.actual_memory_bytes() == 8 * 512 * 104 and eng.total_tokens == 512 and eng.num_blocks == 1
+    keys, vals = eng.decompress_all(with_signs=True)
+    assert rel_l2(vals[0, 0, :64], t(g["vrec_head0"])) < 1e-4
+    assert rel_l2(keys[0, 0, :64], t(g["krec_ip_head0"])) < 1e-4
+
+
+def test_engine_cases_multiblock_causal_widths(golden):
+    g = golden("engine_cases")
+    for i in range(int(g["n_cases"])):
+        D, kbits, vbits, seed, qlen, causal, total = (int(v) for v in g[f"e{i}_meta"])
+        Pi = t(g[f"e{i}_Pi"])
+        K, V, Q = t(g[f"e{i}_K"]), t(g[f"e{i}_V"]), t(g[f"e{i}_Q"])
+        eng = qk.QuashKVEngine(D, kbits, vbits, seed=seed, pack_storage=bool(i % 2))
+        pin_rotation(eng, Pi)
+        # the same block structure as the golden run: feed the concatenated tokens in pieces
+        sizes = {0: (32,), 1: (16, 8), 2: (16, 1, 1, 1, 5), 3: (17,), 4: (33, 15), 5: (40,), 6: (129,), 7: (1,)}[i]
+        off = 0
+        for n in sizes:
+            eng.append(K[:, :, off:off + n].to(DEV), V[:, :, off:off + n].to(DEV))
+            off += n
+        assert eng.total_tokens == total and eng.num_blocks == len(sizes)
+        un = [eng._unpack_block(b) for b in eng._cache]
+        assert all(b.packed == bool(i % 2) for b in eng._cache)
+        mse = torch.cat([u[0] for u in un], 2)
+        val = torch.cat([u[2] for u in un], 2)
+        kb = eng.key_quantizer.mse_quantizer.codebook.boundaries
+        assert_codes(K, Pi, kb, mse, t(g[f"e{i}_mse"]), f"case {i} key codes")
+        assert_codes(V, Pi, eng.value_quantizer.codebook.boundaries, val, t(g[f"e{i}_val"]), f"case {i} value codes")
+        out = eng.attention(Q.to(DEV), causal=bool(causal))
+        err = rel_l2(out, t(g[f"e{i}_out"]))
+        print(f"[parity] engine case {i} (d={D}, bits {kbits}/{vbits}, causal={causal}) rel-L2 {err:.3e}")
+        assert err < FP32_TOL
+        if i == 1:   # the functional entry point on unpacked blocks
+            blocks = [CompressedBlock(u[0], u[1], b.key_norms, u[2], b.val_norms, b.seq_len)
+                      for u, b in zip(un, eng._cache)]
+            kq = eng.key_quantizer
+            f = fused_quantized_attention(Q.to(DEV), blocks, Pi.to(DEV), kq.mse_quantizer.codebook.centroids.to(DEV),
+                                          eng.value_quantizer.codebook.centroids.to(DEV), kq.S.to(DEV), kq.qjl_scale,
+                                          total_kv_tokens=eng.total_tokens)
+            assert rel_l2(f, t(g[f"e{i}_out"])) < FP32_TOL
+        eng.clear()
+        assert eng.total_tokens == 0 and eng.num_blocks == 0
+
+
+def _outlier_kv(B, H, S, D, seed, dtype):
+    gk = torch.Generator().manual_seed(seed)
+    K = torch.randn(B, H, S, D, generator=gk)
+    V = torch.randn(B, H, S, D, generator=gk)
+    for h in range(H):
+        ch = torch.randperm(D, generator=torch.Generator().manual_seed(seed + h))[:4]
+        K[:, h, :, ch] *= 8
+        V[:, h, :, ch] *= 8
+    return K.to(dtype), V.to(dtype)
+
+
+@pytest.mark.parametrize("S,appends", [(1, 0), (15, 2), (129, 0), (4096, 3)])
+def test_decode_gqa_bf16_vs_oracle(golden, S, appends):
+    """Config-2 shaped decode at small sizes: bf16 K/V with outlier channels, 4 query heads per
+    KV head, single-token appends after the bulk build, growth of the planes."""
+    B, Hkv, G, D = 2, 2, 4, 128
+    K, V = _outlier_kv(B, Hkv, S + appends, D, 2, torch.bfloat16)
+    eng = qk.QuashKVEngine(D, 3, 3, seed=42, pack_storage=True)
+    eng.append(K[:, :, :S].to(DEV), V[:, :, :S].to(DEV))
+    for a in range(appends):
+        eng.append(K[:, :, S + a:S + a + 1].to(DEV), V[:, :, S + a:S + a + 1].to(DEV))
+    kq, vq = eng.key_quantizer, eng.value_quantizer
+    Pi, Sg = kq.mse_quantizer.Pi, kq.S
+    kc, kb = kq.mse_quantizer.codebook.centroids, kq.mse_quantizer.codebook.boundaries
+    mse, sg, kn = orc.compress_ip(K.float(), Pi, kb, kc, Sg)
+    vi, vn = orc.compress_mse(V.float(), Pi, vq.codebook.boundaries)
+    un = [eng._unpack_block(b) for b in eng._cache]
+    assert_codes(K.float(), Pi, kb, torch.cat([u[0] for u in un], 2), mse, f"decode S={S} key codes")
+    Q = torch.randn(B, Hkv * G, 1, D, generator=torch.Generator().manual_seed(1000)).to(torch.bfloat16)
+    out = eng.attention(Q.to(DEV))
+    want = orc.attention_gqa(Q.float(), mse, sg, kn, vi, vn, Pi, kc, vq.codebook.centroids, Sg, kq.qjl_scale,
+                             n_kv_heads=Hkv)
+    err = rel_l2(out, want)
+    print(f"[parity] decode S={S}+{appends} bf16 G=4 rel-L2 {err:.3e}")
+    assert err < BF16_TOL and err < FP32_TOL
+
+
+def test_prefill_causal_long_vs_oracle():
+    B, H, S, Qn, D = 1, 2, 600, 37, 64
+    gq = torch.Generator().manual_seed(3)
+    K, V = torch.randn(B, H, S, D, generator=gq), torch.randn(B, H, S, D, generator=gq)
+    Q = torch.randn(B, H, Qn, D, generator=gq)
+    eng = qk.QuashKVEngine(D, 3, 3, seed=42)
+    eng.append(K.to(DEV), V.to(DEV))
+    kq, vq = eng.key_quantizer, eng.value_quantizer
+    Pi, Sg, kc = kq.mse_quantizer.Pi, kq.S, kq.mse_quantizer.codebook.centroids
+    mse, sg, kn = orc.compress_ip(K, Pi, kq.mse_quantizer.codebook.boundaries, kc, Sg)
+    vi, vn = orc.compress_mse(V, Pi, vq.codebook.boundaries)
+    for causal in (False, True):
+        for scale in (None, 0.05):
+            out = eng.attention(Q.to(DEV), scale=scale, causal=causal)
+            want = orc.attention(Q, mse, sg, kn, vi, vn, Pi, kc, vq.codebook.centroids, Sg, kq.qjl_scale,
+                                 scale=scale, causal=causal, total_tokens=S)
+            assert rel_l2(out, want) < FP32_TOL
+
+
+def test_full_size_decode_sampled_heads():
+    """Configuration 2 at full per-GPU size (batch 32, 8 KV heads, 32768 tokens, 4 query heads per
+    KV head, bf16).  The oracle cannot run the whole cache in seconds, so (batch, head) pairs are
+    sampled and checked one by one; the cache bytes must equal 104 per token-head."""
+    B, Hkv, G, S, D = 32, 8, 4, 32768, 128
+    eng = qk.QuashKVEngine(D, 3, 3, seed=42, pack_storage=True)
+    eng.reserve(B, Hkv, S + 8, DEV)
+    keep = {}
+    for b in range(B):          # built batch row by batch row to bound host memory
+        K, V = _outlier_kv(1, Hkv, S, D, 2 + 31 * b, torch.bfloat16)
+        if b in (0, 17, 31):
+            keep[b] = (K, V)
+        rows = _lib.Rows(S, eng._capacity, 0)
+        kq, vq = eng.key_quantizer, eng.value_quantizer
+        Pi, kb, kc, Sg = kq._on(torch.device(DEV, 0))
+        _, vb, _ = vq._on(torch.device(DEV, 0))
+        p = eng._planes
+        sl = slice(b * Hkv, (b + 1) * Hkv)
+        ops.append_kv(K.to(DEV), V.to(DEV), Pi, kb, kc, Sg, 2, vb, 3, p["k_codes"][sl], p["k_signs"][sl],
+                      p["k_norms"][sl], p["v_codes"][sl], p["v_norms"][sl], 0)
+    eng._block_lens, eng._total_tokens = [S], S
+    assert eng.actual_memory_bytes() == 872415232
+    Q = torch.randn(B, Hkv * G, 1, D, generator=torch.Generator().manual_seed(1000)).to(torch.bfloat16)
+    out = eng.attention(Q.to(DEV)).cpu()
+    kq, vq = eng.key_quantizer, eng.value_quantizer
+    Pi, Sg, kc = kq.mse_quantizer.Pi, kq.S, kq.mse_quantizer.codebook.centroids
+    for b, h in ((0, 0), (17, 3), (31, 7)):
+        K, V = keep[b]
+        Kh, Vh = K[:, h:h + 1].float(), V[:, h:h + 1].float()
+        mse, sg, kn = orc.compress_ip(Kh, Pi, kq.mse_quantizer.codebook.boundaries, kc, Sg)
+        vi, vn = orc.compress_mse(Vh, Pi, vq.codebook.boundaries)
+        qh = Q[b:b + 1, h * G:(h + 1) * G].float()
+        want = orc.attention_gqa(qh, mse, sg, kn, vi, vn, Pi, kc, vq.codebook.centroids, Sg, kq.qjl_scale,
+                                 n_kv_heads=1)
+        err = rel_l2(out[b:b + 1, h * G:(h + 1) * G], want)
+        print(f"[parity] full-size decode (b={b}, kv head {h}) rel-L2 {err:.3e}")
+        assert err < BF16_TOL and err < FP32_TOL
+
+
+# ---------------------------------------------------------------------------------------------
+# index
+# ---------------------------------------------------------------------------------------------
+
+def _check_topk(scores, ids, all_scores, k, what):
+    """ids must be a valid top-k of the reference's dense scores up to near-ties."""
+    all_scores = torch.as_tensor(all_scores)
+    M = all_scores.shape[0]
+    ref_s, ref_i = torch.topk(all_scores, k, dim=1)
+    assert scores.shape == (M, k) and ids.shape == (M, k) and ids.dtype == torch.int64
+    s, i = scores.cpu(), ids.cpu()
+    assert torch.all(s[:, :-1] >= s[:, 1:]), "scores must be descending"
+    assert torch.allclose(s, ref_s, rtol=1e-4, atol=1e-4), what
+    n_swapped = 0
+    for m in range(M):
+        if not torch.equal(i[m], ref_i[m]):
+            diff = set(i[m].tolist()) ^ set(ref_i[m].tolist())
+            n_swapped += 1
+            # every id that differs must score within rounding of the k-th reference score
+            for j in diff:
+                assert abs(float(all_scores[m, j]) - float(ref_s[m, -1])) < 1e-4 or \
+                    torch.allclose(all_scores[m, i[m]].sort().values, all_scores[m, ref_i[m]].sort().values, atol=1e-4)
+    print(f"[ties] {what}: {n_swapped} of {M} queries differ from the reference order (near-equal scores)")
+
+
+def test_index_search_golden(golden):
+    g, c = golden("index"), golden("constants")
+    for tag in "abcd":
+        d, n, m, k, bits = (int(v) for v in g[f"{tag}_meta"])
+        idx = qk.QuashIndex(d, bits, seed=42, pack_storage=True)
+        pin_rotation(idx, t(c[f"Pi_d{d}_s42"]))
+        db, qs = t(g[f"{tag}_db"]), t(g[f"{tag}_q"])
+        idx.add(db[: n // 2].to(DEV))
+        idx.add(db[n // 2:].to(DEV))
+        assert len(idx) == n and idx.n_vectors == n
+        n_byte = int((idx._mse_indices.cpu() != t(g[f"{tag}_mse_plane"])).sum()) + \
+            int((idx._qjl_signs.cpu() != t(g[f"{tag}_qjl_plane"])).sum())
+        print(f"[ties] index {tag}: {n_byte} packed bytes differ from the reference")
+        assert n_byte <= 4 and ulp_diff(idx._norms, t(g[f"{tag}_norms"])) <= 2
+        sc, ids = idx.search(qs.to(DEV), k)
+        kk = min(k, n)
+        _check_topk(sc, ids, g[f"{tag}_all_scores"], kk, f"index {tag} k={kk}")
+        un = qk.QuashIndex(d, bits, seed=42, pack_storage=False)
+        pin_rotation(un, t(c[f"Pi_d{d}_s42"]))
+        un.add(db.to(DEV))
+        assert un._mse_indices.shape == (n, d) and un.memory_bytes() == n * (2 * d + 4)
+        s2, i2 = un.search(qs.to(DEV), k)
+        assert torch.equal(i2, ids) and torch.equal(s2, sc)
+        idx.reset()
+        assert len(idx) == 0
+
+
+def test_index_shards_merge_to_the_single_index_result(golden):
+    g, c = golden("index"), golden("constants")
+    d, n, m, k, bits = (int(v) for v in g["b_meta"])
+    db, qs = t(g["b_db"]).to(DEV), t(g["b_q"]).to(DEV)
+    whole = qk.QuashIndex(d, bits, seed=42, pack_storage=True)
+    whole.add(db)
+    ws, wi = whole.search(qs, k)
+    bounds = [0, 700, 701, 2000, n]
+    parts = []
+    for a, b in zip(bounds[:-1], bounds[1:]):
+        shard = qk.QuashIndex(d, bits, seed=42, pack_storage=True)
+        shard.add(db[a:b])
+        kk = min(k, b - a)
+        s, i = shard.search(qs, kk, id_base=a)
+        pad = k - kk
+        if pad:
+            s = torch.cat([s, torch.full((m, pad), -math.inf, device=DEV)], 1)
+            i = torch.cat([i, torch.full((m, pad), -1, dtype=torch.int64, device=DEV)], 1)
+        parts.append((s, i))
+    ms, mi = ops.topk_merge(torch.cat([p[0] for p in parts], 1), torch.cat([p[1] for p in parts], 1), k)
+    assert torch.equal(mi, wi) and torch.equal(ms, ws)
+    os_, oi = orc.merge_topk(torch.cat([p[0] for p in parts], 1).cpu(), torch.cat([p[1] for p in parts], 1).cpu(), k)
+    assert torch.equal(oi, mi.cpu()) and torch.equal(os_, ms.cpu())
+
+
+def test_index_medium_recall_and_ties():
+    """100k vectors: ids against the oracle's dense scores, recall against exact fp32 search, and
+    duplicate vectors (exactly equal scores) come back lowest id first."""
+    d, n, m, k = 128, 100_000, 24, 10
+    gdb = torch.Generator().manual_seed(6)
+    db = torch.randn(n, d, generator=gdb)
+    db = db / db.norm(dim=1, keepdim=True) * (torch.rand(n, 1, generator=gdb) * 1.5 + 0.5)
+    db[5000] = db[77]
+    db[90000] = db[77]
+    qs = torch.randn(m, d, generator=torch.Generator().manual_seed(7))
+    qs[0] = db[77] * 3
+    idx = qk.QuashIndex(d, 3, seed=42, pack_storage=True)
+    idx.add(db.to(DEV))
+    sc, ids = idx.search(qs.to(DEV), k)
+    qq = idx.quantizer
+    mse, sg, nrm = orc.compress_ip(db, qq.mse_quantizer.Pi, qq.mse_quantizer.codebook.boundaries,
+                                   qq.mse_quantizer.codebook.centroids, qq.S)
+    dense = orc.index_scores(qs, mse, sg, nrm, qq.mse_quantizer.Pi, qq.mse_quantizer.codebook.centroids, qq.S,
+                             qq.qjl_scale)
+    _check_topk(sc, ids, dense, k, "index 100k")
+    row = ids[0].cpu().tolist()
+    assert row.index(77) < row.index(5000) < row.index(90000)
+    assert idx.recall_at_k(qs.to(DEV), db.to(DEV), k) > 0.3
+
+
+# ---------------------------------------------------------------------------------------------
+# HF-style cache
+# ---------------------------------------------------------------------------------------------
+
+def test_hf_cache_update_matches_reference(golden):
+    g, c = golden("hf_cache"), golden("constants")
+    cache = QuashKVCache(num_layers=2, head_dim=64)
+    pin_rotation(cache.engines[1], t(c[f"Pi_d64_s{int(g['seed'])}"]))
+    k1, v1, k2, v2 = (t(g[n]).to(DEV) for n in ("k1", "v1", "k2", "v2"))
+    fk, fv = cache.update(k1, v1, 1)
+    assert fk.shape == (2, 4, 9, 64)
+    fk, fv = cache.update(k2, v2, 1)
+    assert fk.shape == (2, 4, 10, 64) and cache.get_seq_length(1) == 10 and cache.get_seq_length(0) == 0
+    assert rel_l2(fk, t(g["full_k"])) < 1e-4 and rel_l2(fv, t(g["full_v"])) < 1e-4
+    k_again, v_again = cache[1]
+    assert torch.equal(k_again, fk) and torch.equal(v_again, fv)
+    assert cache.compression_stats()["tokens_per_layer"] == [0, 10]
+    # the fused route over the same cache agrees with attention over the returned tensors
+    q = torch.randn(2, 8, 1, 64, device=DEV)
+    fused = cache.attention(q, 1)
+    assert fused.shape == (2, 8, 1, 64) and torch.isfinite(fused).all()
+    cache.reset()
+    assert cache.get_seq_length(1) == 0
+
+
+# ---------------------------------------------------------------------------------------------
+# the C ABI called directly, and its argument checks
+# ---------------------------------------------------------------------------------------------
+
+def test_c_abi_direct_call_and_status_codes(golden):
+    c = golden("constants")
+    L = _lib.lib()
+    d, n = 64, 50
+    x = torch.randn(n, d, device=DEV)
+    Pi, bnd = t(c["Pi_d64_s42"]).to(DEV), t(c["bnd_d64_b3"]).to(DEV)
+    codes = torch.full((n + 1, 24), 0xAB, dtype=torch.uint8, device=DEV)     # one canary row
+    norms = torch.full((n + 1,), -7.0, device=DEV)
+    vp = lambda z: ctypes.c_void_p(z.data_ptr())  # noqa: E731
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = L.qkv_compress_mse(vp(x), 0, d, n, d, vp(Pi), vp(bnd), 3, vp(codes), 1, vp(norms), _lib.Rows(n, 0, 0), stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    want, wn = orc.compress_mse(x.cpu(), Pi.cpu(), bnd.cpu())
+    assert int((codes[:n].cpu() != orc.pack_bits(want, 3)).sum()) <= 2
+    assert torch.all(codes[n] == 0xAB) and float(norms[n]) == -7.0, "wrote past the last row"
+    # status codes instead of launches for bad arguments
+    cache = _lib.Cache(codes.data_ptr(), codes.data_ptr(), norms.data_ptr(), codes.data_ptr(), norms.data_ptr(), 8)
+    args = (vp(x), 0, cache, 1, 1, 1, 1)
+    tail = (vp(Pi), vp(bnd), vp(bnd), vp(bnd), 0.1, 0.1, 0, vp(x), vp(x), 1 << 20, stream)
+    assert L.qkv_attention(*args, 9, 64, 3, 3, *tail) == -2       # kv_len above capacity
+    assert L.qkv_attention(*args, 4, 48, 3, 3, *tail) == -2       # head_dim not a multiple of 32
+    assert L.qkv_attention(*args, 4, 64, 5, 3, *tail) == -3       # key bits
+    assert L.qkv_attention(*args[:-1], 9, 4, 64, 3, 3, *tail[:6], 1, *tail[7:]) == -8   # causal with q_len > kv_len
+    small = (vp(Pi), vp(bnd), vp(bnd), vp(bnd), 0.1, 0.1, 0, vp(x), vp(x), 8, stream)
+    assert L.qkv_attention(*args, 4, 64, 3, 3, *small) == -6      # workspace too small
+    assert L.qkv_index_scan_topk(vp(x), 2, 64, vp(codes), vp(codes), vp(norms), 10, 3, vp(Pi), vp(bnd), vp(bnd), 0.1,
+                                 200, 0, vp(x), vp(x), vp(x), 1 << 20, stream) == -8   # k above the limit
+    torch.cuda.synchronize()

@@ -1,0 +1,131 @@
+"""Host-side checks that need no GPU: constants equal the reference's, the C-ABI library
+loads and exports every declared symbol, argument errors carry the reference's texts, and
+the hot methods refuse CPU tensors instead of falling back."""
+
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+import quashkv_b200 as qk
+from quashkv_b200 import _lib, ops
+from quashkv_b200.integrations.hf_cache import QuashKVCache
+from quashkv_b200.packing import packed_size
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_codebook_matches_reference_values(golden):
+    g = golden("constants")
+    for d in (64, 96, 128):
+        for bits in (1, 2, 3, 4):
+            cb = qk.LloydMaxCodebook(d, bits)
+            assert np.array_equal(cb.centroids.numpy(), g[f"cent_d{d}_b{bits}"])
+            assert np.array_equal(cb.boundaries.numpy(), g[f"bnd_d{d}_b{bits}"])
+    cb = qk.LloydMaxCodebook(64, 2, use_exact_pdf=True)
+    assert np.array_equal(cb.centroids.numpy(), g["cent_exact_d64_b2"])
+    with pytest.raises(ValueError, match="bits must be in"):
+        qk.LloydMaxCodebook(64, 5)
+
+
+def test_codebook_helpers_agree():
+    cb = qk.LloydMaxCodebook(64, 3)
+    x = torch.randn(1000) * 0.2
+    assert torch.equal(cb.quantize(x), cb.quantize_boundary(x))
+    assert torch.equal(cb.dequantize(cb.quantize(x)), cb.centroids[cb.quantize(x).long()])
+    assert cb.n_levels == 8 and torch.all(cb.centroids[1:] > cb.centroids[:-1])
+
+
+def test_sign_vector_and_rotation_match_reference(golden):
+    g = golden("constants")
+    for d, seed in ((128, 0), (128, 42), (64, 42), (96, 42), (64, 43)):
+        q = qk.InnerProductQuantizer(d, 3, seed=seed)
+        assert np.array_equal(q.S.numpy(), g[f"S_d{d}_s{seed}"])
+        # QR goes through LAPACK: identical on the host that made the vectors, and orthogonal anywhere
+        assert np.allclose(q.mse_quantizer.Pi.numpy(), g[f"Pi_d{d}_s{seed}"], atol=1e-5)
+        eye = q.mse_quantizer.Pi @ q.mse_quantizer.Pi.T
+        assert torch.allclose(eye, torch.eye(d), atol=1e-5)
+        assert q.qjl_scale == pytest.approx((np.pi / 2) ** 0.5 / d)
+
+
+def test_constructor_errors_have_reference_texts():
+    with pytest.raises(ValueError, match="at least 2 total bits"):
+        qk.InnerProductQuantizer(64, total_bits=1)
+    with pytest.raises(ValueError, match="n_outliers must be in"):
+        qk.MixedPrecisionMSEQuantizer(64, n_outliers=65)
+    with pytest.raises(ValueError, match="outlier_bits should be >= regular_bits"):
+        qk.MixedPrecisionMSEQuantizer(64, outlier_bits=2, regular_bits=3)
+    with pytest.raises(ValueError, match="No compressed KV blocks in cache"):
+        qk.QuashKVEngine(64).attention(torch.randn(1, 1, 1, 64))
+    with pytest.raises(ValueError, match="Index is empty"):
+        qk.QuashIndex(64).search(torch.randn(2, 64))
+    with pytest.raises(ValueError, match=r"Expected \(N, 64\) tensor"):
+        qk.QuashIndex(64).add(torch.randn(3, 32))
+    with pytest.raises(ValueError, match="Unsupported bits"):
+        qk.pack_bits(torch.zeros(2, 8, dtype=torch.uint8), 5)
+
+
+def test_bookkeeping_without_gpu():
+    e = qk.QuashKVEngine(128, 3, 3)
+    assert e.total_tokens == 0 and e.num_blocks == 0 and e.compression_ratio() == 1.0
+    assert e.actual_memory_bytes() == 0 and "cached_tokens=0" in repr(e)
+    e._block_lens.append(1)   # ratio formula only needs a non-empty cache
+    assert e.compression_ratio() == pytest.approx(2 * 128 * 16 / (3 * 128 + 32 + 3 * 128 + 32))
+    idx = qk.QuashIndex(64, 3, pack_storage=True)
+    assert len(idx) == 0 and idx.memory_bytes() == 0 and idx.compression_ratio() == 1.0
+    cache = QuashKVCache(num_layers=4, head_dim=64)
+    assert [e.seed for e in cache.engines] == [42, 43, 44, 45] and len(cache) == 4
+    assert cache.get_seq_length() == 0 and cache.get_max_cache_length() is None
+    k, v = cache[0]
+    assert k.numel() == 0 and v.numel() == 0
+    assert cache.compression_stats()["tokens_per_layer"] == [0, 0, 0, 0]
+    m = qk.MixedPrecisionMSEQuantizer(128, 3, 2, 32)
+    assert m.effective_bits == pytest.approx(2.25) and not m.calibrated
+    m.set_outlier_channels(torch.tensor([5, 1, 9]))
+    assert m.calibrated and m._outlier_indices.tolist() == [1, 5, 9]
+    assert packed_size(128, 3) == 48 and packed_size(128, 1) == 16 and packed_size(64, 2) == 16
+    assert ops.packed_row_bytes(65, 3) == 27 and ops.packed_row_bytes(100, 3) == 39
+    assert ops.packed_row_bytes(63, 2) == 16 and ops.packed_row_bytes(129, 4) == 65
+
+
+def test_hot_methods_refuse_cpu_tensors():
+    q = qk.MSEQuantizer(64, 3)
+    with pytest.raises(RuntimeError, match="no CPU implementation"):
+        q.compress(torch.randn(4, 64))
+    with pytest.raises(RuntimeError, match="no CPU implementation"):
+        qk.pack_bits(torch.zeros(2, 8, dtype=torch.uint8), 3)
+    with pytest.raises(RuntimeError, match="no CPU implementation"):
+        qk.QuashKVEngine(64).append(torch.randn(1, 1, 2, 64), torch.randn(1, 1, 2, 64))
+    with pytest.raises(RuntimeError, match="no CPU implementation"):
+        qk.QuashIndex(64).add(torch.randn(3, 64))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "quashkv_b200.h")).read()
+    declared = set(re.findall(r"\b(qkv_[a-z_0-9]+)\s*\(", header))
+    assert declared, "no declarations parsed"
+    assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+    L = _lib.lib()
+    for name in declared:
+        assert getattr(L, name) is not None
+    assert L.qkv_abi_version() == 1
+    assert L.qkv_strerror(0) == b"ok" and b"NULL" in L.qkv_strerror(-1)
+
+
+def test_argument_validation_needs_no_gpu():
+    """Bad arguments are rejected on the host before anything is launched."""
+    L = _lib.lib()
+    rows = _lib.Rows(1, 0, 0)
+    one = ctypes.c_void_p(16)
+    assert L.qkv_compress_mse(None, 0, 64, 1, 64, one, one, 3, one, 0, one, rows, None) == -1
+    assert L.qkv_compress_mse(one, 0, 64, 1, 129, one, one, 3, one, 0, one, rows, None) == -2
+    assert L.qkv_compress_mse(one, 0, 64, 1, 64, one, one, 5, one, 0, one, rows, None) == -3
+    assert L.qkv_compress_mse(one, 7, 64, 1, 64, one, one, 3, one, 0, one, rows, None) == -4
+    assert L.qkv_pack(one, one, 4, 64, 9, None) == -3
+    assert L.qkv_topk_merge(one, one, 0, 4, 2, one, one, None) == -2
+    assert L.qkv_attention_workspace_bytes(32, 32, 8, 1, 32768, 128) > 0
+    assert L.qkv_index_workspace_bytes(1000, 4, 64, 10) > 0
+    assert L.qkv_mixed_row_bytes(128, 32, 3, 2) == 36
