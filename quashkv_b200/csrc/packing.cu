@@ -63,10 +63,10 @@ extern "C" const char* qkv_strerror(int code) {
 }
 
 extern "C" int qkv_pack(const uint8_t* codes, uint8_t* packed, int64_t n_rows, int d, int bits, void* stream) {
-  if (!codes || !packed) return QKV_ENULL;
   if (bits < 1 || bits > 4) return QKV_EBITS;
   if (d < 1 || n_rows < 0) return QKV_EDIM;
-  if (n_rows == 0) return QKV_OK;
+  if (n_rows == 0) return QKV_OK;          // nothing to do; empty tensors have no storage
+  if (!codes || !packed) return QKV_ENULL;
   const int row_bytes = packed_row_bytes(d, bits);
   pack_kernel<<<grid_for(n_rows * row_bytes), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       codes, packed, n_rows, d, bits, row_bytes);
@@ -74,10 +74,10 @@ extern "C" int qkv_pack(const uint8_t* codes, uint8_t* packed, int64_t n_rows, i
 }
 
 extern "C" int qkv_unpack(const uint8_t* packed, uint8_t* codes, int64_t n_rows, int d, int bits, void* stream) {
-  if (!codes || !packed) return QKV_ENULL;
   if (bits < 1 || bits > 4) return QKV_EBITS;
   if (d < 1 || n_rows < 0) return QKV_EDIM;
-  if (n_rows == 0) return QKV_OK;
+  if (n_rows == 0) return QKV_OK;          // nothing to do; empty tensors have no storage
+  if (!codes || !packed) return QKV_ENULL;
   const int row_bytes = packed_row_bytes(d, bits);
   unpack_kernel<<<grid_for(n_rows * d), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       packed, codes, n_rows, d, bits, row_bytes);

@@ -367,7 +367,7 @@ static int launch_by_nt(const Args& a, int d, int64_t n_vec, cudaStream_t st, K1
 }
 
 static int check_common(const void* x, int dtype, int64_t n_vec, int d, const float* Pi) {
-  if (!x || !Pi) return QKV_ENULL;
+  if ((!x && n_vec != 0) || !Pi) return QKV_ENULL;
   if (dtype != QKV_F32 && dtype != QKV_BF16 && dtype != QKV_F16) return QKV_EDTYPE;
   if (d < 1 || d > kMaxD || n_vec < 0) return QKV_EDIM;
   return QKV_OK;
@@ -393,7 +393,7 @@ extern "C" int qkv_compress_mse(const void* x, int x_dtype, int64_t x_pitch, int
                                 qkv_rows_t rows, void* stream) {
   int rc = check_common(x, x_dtype, n_vec, d, Pi);
   if (rc) return rc;
-  if (!boundaries || !codes_out || !norms_out) return QKV_ENULL;
+  if (!boundaries || ((!codes_out || !norms_out) && n_vec != 0)) return QKV_ENULL;
   if (bits < 1 || bits > 4) return QKV_EBITS;
   if ((rc = check_rows(rows))) return rc;
   CompressArgs a{};
@@ -410,7 +410,7 @@ extern "C" int qkv_compress_ip(const void* x, int x_dtype, int64_t x_pitch, int6
                                qkv_rows_t rows, void* stream) {
   int rc = check_common(x, x_dtype, n_vec, d, Pi);
   if (rc) return rc;
-  if (!boundaries || !centroids || !S || !codes_out || !signs_out || !norms_out) return QKV_ENULL;
+  if (!boundaries || !centroids || !S || ((!codes_out || !signs_out || !norms_out) && n_vec != 0)) return QKV_ENULL;
   if (mse_bits < 1 || mse_bits > 4) return QKV_EBITS;
   if ((rc = check_rows(rows))) return rc;
   CompressArgs a{};
@@ -429,7 +429,7 @@ extern "C" int qkv_compress_mixed(const void* x, int x_dtype, int64_t x_pitch, i
                                   qkv_rows_t rows, void* stream) {
   int rc = check_common(x, x_dtype, n_vec, d, Pi);
   if (rc) return rc;
-  if (!is_outlier || !bounds_out || !bounds_reg || !codes_out || !norms_out) return QKV_ENULL;
+  if (!is_outlier || !bounds_out || !bounds_reg || ((!codes_out || !norms_out) && n_vec != 0)) return QKV_ENULL;
   if (bits_out < 1 || bits_out > 4 || bits_reg < 1 || bits_reg > 4) return QKV_EBITS;
   if ((rc = check_rows(rows))) return rc;
   CompressArgs a{};
@@ -452,7 +452,7 @@ extern "C" int qkv_decompress(const uint8_t* codes, const uint8_t* signs, int pa
                               void* out, int out_dtype, int64_t out_pitch, void* stream) {
   int rc = check_common(codes, out_dtype, n_vec, d, Pi);
   if (rc) return rc;
-  if (!norms || !centroids || !out || (signs && !S)) return QKV_ENULL;
+  if (!centroids || ((!norms || !out) && n_vec != 0) || (signs && !S)) return QKV_ENULL;
   if (bits < 1 || bits > 4) return QKV_EBITS;
   if ((rc = check_rows(rows))) return rc;
   if (n_vec == 0) return QKV_OK;
@@ -472,7 +472,7 @@ extern "C" int qkv_decompress_mixed(const uint8_t* codes, int packed, const floa
                                     void* out, int out_dtype, int64_t out_pitch, void* stream) {
   int rc = check_common(codes, out_dtype, n_vec, d, Pi);
   if (rc) return rc;
-  if (!norms || !is_outlier || !cents_out || !cents_reg || !out) return QKV_ENULL;
+  if (!is_outlier || !cents_out || !cents_reg || ((!norms || !out) && n_vec != 0)) return QKV_ENULL;
   if (bits_out < 1 || bits_out > 4 || bits_reg < 1 || bits_reg > 4) return QKV_EBITS;
   if ((rc = check_rows(rows))) return rc;
   if (n_vec == 0) return QKV_OK;

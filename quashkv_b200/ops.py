@@ -65,7 +65,7 @@ def _pack(codes: torch.Tensor, bits: int) -> torch.Tensor:
     out = torch.empty((flat.shape[0], packed_row_bytes(d, bits)), dtype=torch.uint8, device=codes.device)
     with torch.cuda.device(codes.device):
         _lib.check(_lib.lib().qkv_pack(_p(flat), _p(out), flat.shape[0], d, bits, _stream(codes)), "pack")
-    return out.reshape(*codes.shape[:-1], -1)
+    return out.reshape(*codes.shape[:-1], out.shape[1])
 
 
 @_pack.register_fake
