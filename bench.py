@@ -221,6 +221,7 @@ def run_ours(args):
 
     # ---- build the cache: bf16 K/V -> packed planes, batch row by batch row ----------------------
     eng = qk.QuashKVEngine(D, KEY_BITS, VAL_BITS, seed=42, device=device, pack_storage=True)
+    B = args.batch
     eng.reserve(B, HKV, S, device)
     kq, vq = eng.key_quantizer, eng.value_quantizer
     from quashkv_b200 import ops
@@ -308,13 +309,15 @@ def run_ours(args):
     if os.path.exists(traffic_file):
         with open(traffic_file) as f:
             line["roofline"]["traffic"] = json.load(f).get("dram_bytes_per_launch")
-    if world == 1:
+    if B != 32:
+        line["config"]["workload"] = WORKLOAD + f"_REDUCED_batch{B}"
+    if world == 1 and not args.no_cpu:
         gbs, sec, threads = time_cpu(3, 1)
         line["cpu_baseline"] = {
             "value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
             "sample": "one batch element (8 KV heads x 32768 tokens, 32 query heads) per pass, mean of 3 passes"}
-        if not args.no_extras:
-            line["extra"] = extras(device)
+    if world == 1 and not args.no_extras:
+        line["extra"] = extras(device)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -327,8 +330,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--batch", type=int, default=B,
+                    help="batch elements in the cache (default 32 = the benchmark workload; smaller for profiler captures)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.batch == B:
+        args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    else:   # a reduced case for profiling: not a benchmark number
+        args.no_extras = True
     if args.impl == "reference":
         run_reference(args)
     else:
