@@ -14,52 +14,11 @@
 //      (out = (acc / sum) @ Pi), which equals un-rotating every value first because the
 //      rotation is linear.
 #include <math.h>
+#include <stdlib.h>
 
-#include "common.cuh"
+#include "attention_common.cuh"
 
 namespace qkv {
-
-constexpr int kQT = 4;          // query rows per CTA
-constexpr int kAttnWarps = 4;
-constexpr int kMaxSplits = 64;
-
-struct AttnArgs {
-  qkv_cache_t cache;
-  int B, Hq, Hkv, G, q_len, d, causal;
-  int64_t kv_len;
-  const float* qk;      // [rows][2][d]
-  const float* kcent; const float* vcent;
-  float* part;          // [rows][n_splits][d+2]
-  int n_splits; int64_t split_len;
-};
-
-struct AttnPlan { int n_splits; int64_t split_len; int n_qtiles; int64_t rows; size_t qk_bytes, part_bytes; };
-
-static AttnPlan make_plan(int B, int Hq, int Hkv, int q_len, int64_t kv_len, int d) {
-  AttnPlan p;
-  const int G = Hq / (Hkv > 0 ? Hkv : 1);
-  const int nq = G * q_len;
-  p.n_qtiles = (nq + kQT - 1) / kQT;
-  p.rows = static_cast<int64_t>(B) * Hq * q_len;
-  const int nsp = d >= 96 ? 4 : (d == 64 ? 2 : 1);
-  const int64_t chunk = static_cast<int64_t>(kAttnWarps) * (32 / nsp);   // tokens per CTA pass
-  const int64_t ctas = static_cast<int64_t>(B) * Hkv * p.n_qtiles;
-  int64_t want = (4 * kNumSMs + ctas - 1) / (ctas > 0 ? ctas : 1);
-  const int64_t max_by_len = (kv_len + 4 * chunk - 1) / (4 * chunk);
-  if (want > max_by_len) want = max_by_len;
-  if (want > kMaxSplits) want = kMaxSplits;
-  if (want < 1) want = 1;
-  int64_t len = (kv_len + want - 1) / want;
-  len = (len + chunk - 1) / chunk * chunk;
-  if (len < chunk) len = chunk;
-  p.split_len = len;
-  p.n_splits = static_cast<int>((kv_len + len - 1) / len);
-  if (p.n_splits < 1) p.n_splits = 1;
-  p.qk_bytes = static_cast<size_t>(p.rows) * 2 * d * sizeof(float);
-  p.qk_bytes = (p.qk_bytes + 255) / 256 * 256;
-  p.part_bytes = static_cast<size_t>(p.rows) * p.n_splits * (d + 2) * sizeof(float);
-  return p;
-}
 
 // One warp per query row.
 __global__ void rotate_queries_kernel(const void* __restrict__ q, int q_dtype, int64_t rows, int d,
@@ -364,7 +323,7 @@ using namespace qkv;
 extern "C" size_t qkv_attention_workspace_bytes(int B, int Hq, int Hkv, int q_len, int64_t kv_len, int d) {
   if (B < 1 || Hq < 1 || Hkv < 1 || q_len < 1 || kv_len < 1 || d < 32) return 0;
   const AttnPlan p = make_plan(B, Hq, Hkv, q_len, kv_len, d);
-  return p.qk_bytes + p.part_bytes;
+  return kAttnHeaderBytes + p.qk_bytes + p.part_bytes;
 }
 
 extern "C" int qkv_attention(const void* q, int q_dtype, qkv_cache_t cache,
@@ -387,11 +346,16 @@ extern "C" int qkv_attention(const void* q, int q_dtype, qkv_cache_t cache,
                        reinterpret_cast<uintptr_t>(cache.v_codes) | reinterpret_cast<uintptr_t>(workspace);
   if (al & 15u) return QKV_EALIGN;
   const AttnPlan p = make_plan(B, Hq, Hkv, q_len, kv_len, d);
-  if (workspace_bytes < p.qk_bytes + p.part_bytes) return QKV_EWORKSPACE;
+  if (workspace_bytes < kAttnHeaderBytes + p.qk_bytes + p.part_bytes) return QKV_EWORKSPACE;
+  // QUASHKV_B200_GENERIC_ATTENTION=1 routes every call to the generic kernel (for A/B checks).
+  const char* env = getenv("QUASHKV_B200_GENERIC_ATTENTION");
+  const bool force_generic = env && env[0] == '1';
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-  float* qk = reinterpret_cast<float*>(workspace);
-  float* part = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + p.qk_bytes);
+  unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
+  uint32_t* tables = reinterpret_cast<uint32_t*>(ws);
+  float* qk = reinterpret_cast<float*>(ws + kAttnHeaderBytes);
+  float* part = reinterpret_cast<float*>(ws + kAttnHeaderBytes + p.qk_bytes);
   int rc = launch_rotate_queries(q, q_dtype, p.rows, d, Pi, S, qjl_scale, scale, qk, st);
   if (rc) return rc;
 
@@ -399,8 +363,14 @@ extern "C" int qkv_attention(const void* q, int q_dtype, qkv_cache_t cache,
   a.cache = cache; a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.G = Hq / Hkv; a.q_len = q_len; a.d = d;
   a.causal = causal; a.kv_len = kv_len; a.qk = qk; a.kcent = key_centroids; a.vcent = val_centroids;
   a.part = part; a.n_splits = p.n_splits; a.split_len = p.split_len;
-  const dim3 grid(p.n_splits, p.n_qtiles, B * Hkv);
-  pick(key_bits - 1, val_bits)<<<grid, kAttnWarps * 32, 0, st>>>(a);
+  if (mma_path_ok(d, key_bits, val_bits, a.G, q_len) && !force_generic) {
+    a.tables = tables;
+    if ((rc = launch_prepare_tables(key_centroids, val_centroids, tables, st))) return rc;
+    if ((rc = launch_attend_mma(a, st))) return rc;
+  } else {
+    const dim3 grid(p.n_splits, p.n_qtiles, B * Hkv);
+    pick(key_bits - 1, val_bits)<<<grid, kAttnWarps * 32, 0, st>>>(a);
+  }
   merge_splits_kernel<<<static_cast<unsigned>(p.rows), 128, 0, st>>>(part, p.n_splits, d, Pi, out);
   return check_launch();
 }

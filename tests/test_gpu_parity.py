@@ -345,6 +345,34 @@ def test_decode_gqa_bf16_vs_oracle(golden, S, appends):
     assert err < BF16_TOL and err < FP32_TOL
 
 
+@pytest.mark.parametrize("G,q_len,causal", [(4, 1, False), (8, 1, False), (4, 2, True), (1, 8, True), (2, 3, False)])
+def test_tensor_core_decode_path_vs_generic_and_oracle(G, q_len, causal, monkeypatch):
+    """head_dim 128 with 3/3 bits and at most 8 query rows per KV head takes the tensor-core kernel;
+    it must agree with the oracle and with the generic kernel on the same cache (ragged length, so
+    the last tile and the last split are partial)."""
+    B, Hkv, S, D = 2, 3, 1000 + 13, 128
+    K, V = _outlier_kv(B, Hkv, S, D, 5, torch.float32)
+    eng = qk.QuashKVEngine(D, 3, 3, seed=42, pack_storage=True)
+    eng.append(K.to(DEV), V.to(DEV))
+    Q = torch.randn(B, Hkv * G, q_len, D, generator=torch.Generator().manual_seed(9))
+    fast = eng.attention(Q.to(DEV), causal=causal)
+    monkeypatch.setenv("QUASHKV_B200_GENERIC_ATTENTION", "1")
+    slow = eng.attention(Q.to(DEV), causal=causal)
+    monkeypatch.delenv("QUASHKV_B200_GENERIC_ATTENTION")
+    kq, vq = eng.key_quantizer, eng.value_quantizer
+    Pi, Sg, kc = kq.mse_quantizer.Pi, kq.S, kq.mse_quantizer.codebook.centroids
+    mse, sg, kn = orc.compress_ip(K, Pi, kq.mse_quantizer.codebook.boundaries, kc, Sg)
+    vi, vn = orc.compress_mse(V, Pi, vq.codebook.boundaries)
+    planes = (mse, sg, kn, vi, vn, Pi, kc, vq.codebook.centroids, Sg, kq.qjl_scale)
+    # fold the group into the query axis per KV head; causal rows keep their own positions
+    want = torch.empty(B, Hkv * G, q_len, D)
+    for g in range(G):
+        want[:, g::G] = orc.attention(Q[:, g::G], *planes, causal=causal, total_tokens=S)
+    e_fast, e_slow = rel_l2(fast, want), rel_l2(slow, want)
+    print(f"[parity] G={G} q_len={q_len} causal={causal}: tensor-core rel-L2 {e_fast:.3e}, generic {e_slow:.3e}")
+    assert e_slow < 1e-5 and e_fast < FP32_TOL
+
+
 def test_prefill_causal_long_vs_oracle():
     B, H, S, Qn, D = 1, 2, 600, 37, 64
     gq = torch.Generator().manual_seed(3)
