@@ -26,7 +26,26 @@ namespace qkv {
 constexpr int kMmaWarps = 4;
 constexpr int kTile = 16;                 // tokens per warp step
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kSignMag = 1.0f / 64.0f;  // sign operand magnitude; the weights carry x64
+
+// Sign bits become MMA operands without a per-pair shift: a masked single bit at position p of a
+// 16-bit half IS an fp16 number (0 when clear, v1(p) when set: 2, 2^-7, 2^-11, 2^-13, 2^-14 and
+// the subnormals 2^-15, 2^-16 for p = 14..8), so `word & mask` is the operand and the weight
+// carries 2 / v1(p); the constant -sum(w) goes into the accumulator's initial value.  Bit 15 (the
+// fp16 sign) cannot be used, so four copies of the word (as is, <<7, >>1, <<13) bring all 16
+// bit pairs (j, j+16) to positions 8..14.  Pair t of a 32-coordinate slice:
+//   t 0..6 : word,      p = 8+t,  coordinates (8+t, 24+t)      t 14: word>>1,  p = 14, (15, 31)
+//   t 7..13: word<<7,   p = 1+t,  coordinates (t-6, t+10)      t 15: word<<13, p = 13, (0, 16)
+__host__ __device__ constexpr int sign_pos(int t) { return t < 7 ? 8 + t : (t < 14 ? 1 + t : (t == 14 ? 14 : 13)); }
+__host__ __device__ constexpr int sign_coord(int t) { return t < 7 ? 8 + t : (t < 14 ? t - 6 : (t == 14 ? 15 : 0)); }
+__host__ __device__ constexpr float sign_v1(int p) {
+  return p == 14 ? 2.f : (p == 13 ? 0.0078125f : (p == 12 ? 4.8828125e-4f : 1.f / static_cast<float>(1 << (24 - p))));
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
 
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -152,6 +171,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 3) attend_decode_mma_kernel(At
   constexpr int D = 128;
   __shared__ float q_s[8][2 * D];                    // [query row][q_rot*scale | sign weights]
   __shared__ float red[kMmaWarps][8][D + 2];         // per warp and query: max, sum, accumulator
+  __shared__ float wsum[8];                          // sum of the sign weights per query row
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gid = lane >> 2, tig = lane & 3;
@@ -168,6 +188,12 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 3) attend_decode_mma_kernel(At
       v = a.qk[qrow * 2 * D + e];
     }
     q_s[r][e] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x < 8) {
+    float t = 0.f;
+    for (int j = 0; j < D; ++j) t += q_s[threadIdx.x][D + j];
+    wsum[threadIdx.x] = t * kLog2e;
   }
   __syncthreads();
 
@@ -195,10 +221,12 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 3) attend_decode_mma_kernel(At
       qb[s][1] = pack_half2(v[2], v[3]);
       ql[s][0] = pack_half2(r[0], r[1]);
       ql[s][1] = pack_half2(r[2], r[3]);
-      const int j = 32 * tig + 2 * s;
-      const float f = -kLog2e / kSignMag;     // a set sign bit makes the operand negative
-      wb[s][0] = pack_half2(w[j] * f, w[j + 16] * f);
-      wb[s][1] = pack_half2(w[j + 1] * f, w[j + 17] * f);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {           // pairs t = 2s, 2s+1 of this lane's 32 coordinates
+        const int t = 2 * s + h, j = 32 * tig + sign_coord(t);
+        const float f = 2.f * kLog2e / sign_v1(sign_pos(t));
+        wb[s][h] = pack_half2(w[j] * f, w[j + 16] * f);
+      }
     }
   }
   // ---- PRMT look-up tables: low and high bytes of the fp16 centroids ---------------------------
@@ -230,6 +258,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 3) attend_decode_mma_kernel(At
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   const int odd16 = (gid & 1) * 16;
 
+  const float ci0 = -wsum[2 * tig], ci1 = -wsum[2 * tig + 1];   // accumulator start: -sum of sign weights
   TileRegs cur, nxt;
   int64_t t0 = t_begin + static_cast<int64_t>(warp) * kTile;
   if (t0 < t_end) load_tile(cur, p, t0, t_end, gid, tig);
@@ -238,7 +267,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 3) attend_decode_mma_kernel(At
     if (tn < t_end) load_tile(nxt, p, tn, t_end, gid, tig);
 
     // ---- scores: 8 MMAs on key codes, 8 on sign bits --------------------------------------------
-    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    float c[4] = {ci0, ci1, ci0, ci1};
 #pragma unroll
     for (int word = 0; word < 2; ++word) {
       const uint32_t w0 = word ? cur.kc[0].y : cur.kc[0].x;
@@ -249,26 +278,33 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 3) attend_decode_mma_kernel(At
       for (int grp = 0; grp < 4; ++grp) {
         const uint32_t s0 = (grp >> 1 ? y0 : x0) >> (16 * (grp & 1));
         const uint32_t s1 = (grp >> 1 ? y1 : x1) >> (16 * (grp & 1));
-        const uint32_t lo0 = __byte_perm(kt_lo, kt_hi, s0), hi0 = __byte_perm(kt_hi, kt_lo, s0);
-        const uint32_t lo1 = __byte_perm(kt_lo, kt_hi, s1), hi1 = __byte_perm(kt_hi, kt_lo, s1);
+        const uint32_t lo0 = prmt(kt_lo, kt_hi, s0), hi0 = prmt(kt_hi, kt_lo, s0);
+        const uint32_t lo1 = prmt(kt_lo, kt_hi, s1), hi1 = prmt(kt_hi, kt_lo, s1);
         uint32_t af[4];
-        af[0] = __byte_perm(lo0, hi0, 0x5140);
-        af[1] = __byte_perm(lo1, hi1, 0x5140);
-        af[2] = __byte_perm(lo0, hi0, 0x7362);
-        af[3] = __byte_perm(lo1, hi1, 0x7362);
+        af[0] = prmt(lo0, hi0, 0x5140);
+        af[1] = prmt(lo1, hi1, 0x5140);
+        af[2] = prmt(lo0, hi0, 0x7362);
+        af[3] = prmt(lo1, hi1, 0x7362);
         mma16816(c, af, qb[word * 4 + grp][0], qb[word * 4 + grp][1]);
         mma16816(c, af, ql[word * 4 + grp][0], ql[word * 4 + grp][1]);
       }
     }
+    {
+      const uint32_t cp0[4] = {cur.ks[0], cur.ks[0] << 7, cur.ks[0] >> 1, cur.ks[0] << 13};
+      const uint32_t cp1[4] = {cur.ks[1], cur.ks[1] << 7, cur.ks[1] >> 1, cur.ks[1] << 13};
 #pragma unroll
-    for (int s = 0; s < 8; ++s) {
-      constexpr uint32_t kMag = 0x24002400u;      // fp16 1/64 in both halves
-      uint32_t af[4];
-      af[0] = ((cur.ks[0] << (15 - 2 * s)) & 0x80008000u) | kMag;
-      af[1] = ((cur.ks[1] << (15 - 2 * s)) & 0x80008000u) | kMag;
-      af[2] = ((cur.ks[0] << (14 - 2 * s)) & 0x80008000u) | kMag;
-      af[3] = ((cur.ks[1] << (14 - 2 * s)) & 0x80008000u) | kMag;
-      mma16816(c, af, wb[s][0], wb[s][1]);
+      for (int s = 0; s < 8; ++s) {
+        uint32_t af[4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int t = 2 * s + h;
+          const int cpy = t < 7 ? 0 : (t < 14 ? 1 : t - 12);
+          const uint32_t mask = 0x00010001u << sign_pos(t);
+          af[2 * h] = cp0[cpy] & mask;
+          af[2 * h + 1] = cp1[cpy] & mask;
+        }
+        mma16816(c, af, wb[s][0], wb[s][1]);
+      }
     }
 
     // ---- online softmax on the accumulator fragment (log2 domain) ------------------------------
@@ -320,15 +356,15 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 3) attend_decode_mma_kernel(At
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const uint32_t pick = i | ((4 + i) << 4);
-        const uint32_t sAB = __byte_perm(nib[0][grp], nib[1][grp], pick);
-        const uint32_t sCD = __byte_perm(nib[2][grp], nib[3][grp], pick);
-        const uint32_t loAB = __byte_perm(vt_lo[0], vt_lo[1], sAB), hiAB = __byte_perm(vt_hi[0], vt_hi[1], sAB);
-        const uint32_t loCD = __byte_perm(vt_lo[0], vt_lo[1], sCD), hiCD = __byte_perm(vt_hi[0], vt_hi[1], sCD);
+        const uint32_t sAB = prmt(nib[0][grp], nib[1][grp], pick);
+        const uint32_t sCD = prmt(nib[2][grp], nib[3][grp], pick);
+        const uint32_t loAB = prmt(vt_lo[0], vt_lo[1], sAB), hiAB = prmt(vt_hi[0], vt_hi[1], sAB);
+        const uint32_t loCD = prmt(vt_lo[0], vt_lo[1], sCD), hiCD = prmt(vt_hi[0], vt_hi[1], sCD);
         uint32_t af[4];
-        af[0] = __byte_perm(loAB, hiAB, 0x6240);
-        af[1] = __byte_perm(loAB, hiAB, 0x7351);
-        af[2] = __byte_perm(loCD, hiCD, 0x6240);
-        af[3] = __byte_perm(loCD, hiCD, 0x7351);
+        af[0] = prmt(loAB, hiAB, 0x6240);
+        af[1] = prmt(loAB, hiAB, 0x7351);
+        af[2] = prmt(loCD, hiCD, 0x6240);
+        af[3] = prmt(loCD, hiCD, 0x7351);
         mma16816(O[grp * 4 + i], af, pb0, pb1);
       }
     }
