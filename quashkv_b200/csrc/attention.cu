@@ -20,31 +20,60 @@
 
 namespace qkv {
 
-// One warp per query row.
-__global__ void rotate_queries_kernel(const void* __restrict__ q, int q_dtype, int64_t rows, int d,
-                                      const float* __restrict__ Pi, const float* __restrict__ S,
-                                      float qjl_scale, float scale, float* __restrict__ qk) {
-  const int lane = threadIdx.x & 31;
-  const int64_t row = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  float x[4];
-#pragma unroll
-  for (int t = 0; t < 4; ++t) {
-    const int j = lane + 32 * t;
-    x[t] = (j < d) ? load_float(q, q_dtype, row * d + j) : 0.f;
+// q_rot = q @ Pi^T for 4 query rows per CTA.  Thread i owns output coordinate i and streams row i of Pi
+// with 16-byte loads (independent loads, no barriers), every element feeding 4 rows.
+constexpr int kRowsPerCta = 4;
+__global__ void __launch_bounds__(128) rotate_queries_kernel(const void* __restrict__ q, int q_dtype, int64_t rows,
+                                                             int d, const float* __restrict__ Pi,
+                                                             const float* __restrict__ S, float qjl_scale,
+                                                             float scale, float* __restrict__ qk,
+                                                             const float* __restrict__ kcent,
+                                                             const float* __restrict__ vcent,
+                                                             uint32_t* __restrict__ tables) {
+  if (tables != nullptr && blockIdx.x == gridDim.x - 1) {   // one extra CTA: look-up tables of the
+    prepare_tables_cta(kcent, vcent, tables);               // tensor-core path
+    return;
   }
-  for (int i = 0; i < d; ++i) {
-    float s = 0.f;
+  __shared__ __align__(16) float x_s[kRowsPerCta][kMaxD];
+  const int i = threadIdx.x;
+  const int64_t row0 = static_cast<int64_t>(blockIdx.x) * kRowsPerCta;
+  for (int idx = threadIdx.x; idx < kRowsPerCta * kMaxD; idx += blockDim.x) {
+    const int r = idx / kMaxD, j = idx % kMaxD;
+    x_s[r][j] = (row0 + r < rows && j < d) ? load_float(q, q_dtype, (row0 + r) * d + j) : 0.f;
+  }
+  __syncthreads();
+  if (i >= d) return;
+  float acc[kRowsPerCta];
 #pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      const int j = lane + 32 * t;
-      if (j < d) s = fmaf(x[t], Pi[i * d + j], s);
+  for (int r = 0; r < kRowsPerCta; ++r) acc[r] = 0.f;
+  const float* prow = Pi + static_cast<int64_t>(i) * d;
+  if ((d & 3) == 0) {
+    const float4* p4 = reinterpret_cast<const float4*>(prow);
+#pragma unroll 8
+    for (int j4 = 0; j4 < d / 4; ++j4) {
+      const float4 m = __ldg(p4 + j4);
+#pragma unroll
+      for (int r = 0; r < kRowsPerCta; ++r) {
+        const float4 x = *reinterpret_cast<const float4*>(&x_s[r][4 * j4]);
+        acc[r] = fmaf(x.x, m.x, acc[r]);
+        acc[r] = fmaf(x.y, m.y, acc[r]);
+        acc[r] = fmaf(x.z, m.z, acc[r]);
+        acc[r] = fmaf(x.w, m.w, acc[r]);
+      }
     }
+  } else {
+    for (int j = 0; j < d; ++j) {
+      const float m = __ldg(prow + j);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(QKV_FULL_MASK, s, o);
-    if (lane == 0) {
-      qk[row * 2 * d + i] = s * scale;
-      qk[row * 2 * d + d + i] = (qjl_scale * scale) * (fabsf(s) * S[i]);
+      for (int r = 0; r < kRowsPerCta; ++r) acc[r] = fmaf(x_s[r][j], m, acc[r]);
+    }
+  }
+  const float sg = S[i];
+#pragma unroll
+  for (int r = 0; r < kRowsPerCta; ++r) {
+    if (row0 + r < rows) {
+      qk[(row0 + r) * 2 * d + i] = acc[r] * scale;
+      qk[(row0 + r) * 2 * d + d + i] = (qjl_scale * scale) * (fabsf(acc[r]) * sg);
     }
   }
 }
@@ -253,47 +282,76 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attend_split_kernel(AttnArgs 
   }
 }
 
-// One CTA per query row: combine splits, normalise, un-rotate.
-__global__ void merge_splits_kernel(const float* __restrict__ part, int n_splits, int d,
-                                    const float* __restrict__ Pi, float* __restrict__ out) {
-  __shared__ float vec[kMaxD];
-  __shared__ float wsplit[kMaxSplits];
-  __shared__ float inv_l;
-  const int64_t row = blockIdx.x;
-  const float* p = part + row * n_splits * (d + 2);
-  if (threadIdx.x == 0) {
+// A few query rows per CTA: combine the splits of each row, normalise, then un-rotate; thread i owns output
+// coordinate i and reads row j of Pi coalesced, each element feeding every row of the CTA.
+__global__ void __launch_bounds__(128) merge_splits_kernel(const float* __restrict__ part, int64_t rows,
+                                                           int n_splits, int d, const float* __restrict__ Pi,
+                                                           float* __restrict__ out) {
+  __shared__ float vec[kRowsPerCta][kMaxD];
+  __shared__ float wsplit[kRowsPerCta][kMaxSplits];
+  __shared__ float inv_l[kRowsPerCta];
+  const int64_t row0 = static_cast<int64_t>(blockIdx.x) * kRowsPerCta;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int r = warp; r < kRowsPerCta; r += blockDim.x >> 5) {     // a warp per row: weights of its splits
+    if (row0 + r >= rows) continue;
+    const float* p = part + (row0 + r) * n_splits * (d + 2);
     float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, p[s * (d + 2)]);
+    for (int s = lane; s < n_splits; s += 32) M = fmaxf(M, p[s * (d + 2)]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(QKV_FULL_MASK, M, o));
     float L = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
+    for (int s = lane; s < n_splits; s += 32) {
       const float m = p[s * (d + 2)];
       const float f = (m == -INFINITY) ? 0.f : expf(m - M);
-      wsplit[s] = f;
+      wsplit[r][s] = f;
       L += f * p[s * (d + 2) + 1];
     }
-    inv_l = 1.f / fmaxf(L, 1e-30f);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(QKV_FULL_MASK, L, o);
+    if (lane == 0) inv_l[r] = 1.f / fmaxf(L, 1e-30f);
   }
   __syncthreads();
-  for (int j = threadIdx.x; j < d; j += blockDim.x) {
+  for (int idx = threadIdx.x; idx < kRowsPerCta * d; idx += blockDim.x) {
+    const int r = idx / d, j = idx % d;
     float v = 0.f;
-    for (int s = 0; s < n_splits; ++s) v += wsplit[s] * p[s * (d + 2) + 2 + j];
-    vec[j] = v * inv_l;
+    if (row0 + r < rows) {
+      const float* p = part + (row0 + r) * n_splits * (d + 2);
+      for (int s = 0; s < n_splits; ++s) v += wsplit[r][s] * p[s * (d + 2) + 2 + j];
+      v *= inv_l[r];
+    }
+    vec[r][j] = v;
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    float o = 0.f;
-    for (int j = 0; j < d; ++j) o = fmaf(vec[j], Pi[j * d + i], o);
-    out[row * d + i] = o;
+  const int i = threadIdx.x;
+  if (i < d) {
+    float o[kRowsPerCta];
+#pragma unroll
+    for (int r = 0; r < kRowsPerCta; ++r) o[r] = 0.f;
+#pragma unroll 8
+    for (int j = 0; j < d; ++j) {
+      const float m = __ldg(Pi + j * d + i);
+#pragma unroll
+      for (int r = 0; r < kRowsPerCta; ++r) o[r] = fmaf(vec[r][j], m, o[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < kRowsPerCta; ++r)
+      if (row0 + r < rows) out[(row0 + r) * d + i] = o[r];
   }
 }
 
 // Host-side launcher shared with the index scan.
+static int launch_rotate(const void* q, int q_dtype, int64_t rows, int d, const float* Pi, const float* S,
+                         float qjl_scale, float scale, float* qk, const float* kcent, const float* vcent,
+                         uint32_t* tables, cudaStream_t st) {
+  const unsigned ctas = static_cast<unsigned>((rows + kRowsPerCta - 1) / kRowsPerCta) + (tables ? 1u : 0u);
+  rotate_queries_kernel<<<ctas, 128, 0, st>>>(q, q_dtype, rows, d, Pi, S, qjl_scale, scale, qk, kcent, vcent,
+                                              tables);
+  return check_launch();
+}
+
 int launch_rotate_queries(const void* q, int q_dtype, int64_t rows, int d, const float* Pi, const float* S,
                           float qjl_scale, float scale, float* qk, cudaStream_t st) {
-  const int warps = 4;
-  rotate_queries_kernel<<<static_cast<unsigned>((rows + warps - 1) / warps), warps * 32, 0, st>>>(
-      q, q_dtype, rows, d, Pi, S, qjl_scale, scale, qk);
-  return check_launch();
+  return launch_rotate(q, q_dtype, rows, d, Pi, S, qjl_scale, scale, qk, nullptr, nullptr, nullptr, st);
 }
 
 typedef void (*AttnKernel)(AttnArgs);
@@ -347,30 +405,35 @@ extern "C" int qkv_attention(const void* q, int q_dtype, qkv_cache_t cache,
   if (al & 15u) return QKV_EALIGN;
   const AttnPlan p = make_plan(B, Hq, Hkv, q_len, kv_len, d);
   if (workspace_bytes < kAttnHeaderBytes + p.qk_bytes + p.part_bytes) return QKV_EWORKSPACE;
-  // QUASHKV_B200_GENERIC_ATTENTION=1 routes every call to the generic kernel (for A/B checks).
-  const char* env = getenv("QUASHKV_B200_GENERIC_ATTENTION");
-  const bool force_generic = env && env[0] == '1';
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
   unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
   uint32_t* tables = reinterpret_cast<uint32_t*>(ws);
   float* qk = reinterpret_cast<float*>(ws + kAttnHeaderBytes);
   float* part = reinterpret_cast<float*>(ws + kAttnHeaderBytes + p.qk_bytes);
-  int rc = launch_rotate_queries(q, q_dtype, p.rows, d, Pi, S, qjl_scale, scale, qk, st);
+  // QUASHKV_B200_GENERIC_ATTENTION=1 routes every call to the generic kernel (for A/B checks).
+  const char* env = getenv("QUASHKV_B200_GENERIC_ATTENTION");
+  const bool force_generic = env && env[0] == '1';
+  // the tensor-core path copies 16-byte chunks of every plane, norms included
+  const bool chunks_ok = cache.capacity % 4 == 0 &&
+      ((reinterpret_cast<uintptr_t>(cache.k_norms) | reinterpret_cast<uintptr_t>(cache.v_norms)) & 15u) == 0;
+  const bool use_mma = mma_path_ok(d, key_bits, val_bits, Hq / Hkv, q_len) && chunks_ok && !force_generic;
+  int rc = launch_rotate(q, q_dtype, p.rows, d, Pi, S, qjl_scale, scale, qk, key_centroids, val_centroids,
+                         use_mma ? tables : nullptr, st);
   if (rc) return rc;
 
   AttnArgs a{};
   a.cache = cache; a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.G = Hq / Hkv; a.q_len = q_len; a.d = d;
   a.causal = causal; a.kv_len = kv_len; a.qk = qk; a.kcent = key_centroids; a.vcent = val_centroids;
   a.part = part; a.n_splits = p.n_splits; a.split_len = p.split_len;
-  if (mma_path_ok(d, key_bits, val_bits, a.G, q_len) && !force_generic) {
+  if (use_mma) {
     a.tables = tables;
-    if ((rc = launch_prepare_tables(key_centroids, val_centroids, tables, st))) return rc;
     if ((rc = launch_attend_mma(a, st))) return rc;
   } else {
     const dim3 grid(p.n_splits, p.n_qtiles, B * Hkv);
     pick(key_bits - 1, val_bits)<<<grid, kAttnWarps * 32, 0, st>>>(a);
   }
-  merge_splits_kernel<<<static_cast<unsigned>(p.rows), 128, 0, st>>>(part, p.n_splits, d, Pi, out);
+  merge_splits_kernel<<<static_cast<unsigned>((p.rows + kRowsPerCta - 1) / kRowsPerCta), 128, 0, st>>>(
+      part, p.rows, p.n_splits, d, Pi, out);
   return check_launch();
 }

@@ -1,6 +1,8 @@
 // Declarations shared by the generic and the tensor-core attention kernels.
 #pragma once
 
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace qkv {
@@ -33,11 +35,22 @@ inline AttnPlan make_plan(int B, int Hq, int Hkv, int q_len, int64_t kv_len, int
   (void)d;
   const int64_t chunk = 128;   // a multiple of every kernel's tokens per CTA pass (32..128)
   const int64_t ctas = static_cast<int64_t>(B) * Hkv * p.n_qtiles;
-  int64_t want = (8 * kNumSMs + ctas - 1) / (ctas > 0 ? ctas : 1);
+  // Number of KV splits: at least ~6 CTAs per SM in total, then the count in [lo, 2 lo] whose
+  // CTA total fills whole waves best (4 resident CTAs per SM), so that the last wave is not idle.
+  int64_t lo = (6 * kNumSMs + ctas - 1) / (ctas > 0 ? ctas : 1);
   const int64_t max_by_len = (kv_len + 4 * chunk - 1) / (4 * chunk);
-  if (want > max_by_len) want = max_by_len;
-  if (want > kMaxSplits) want = kMaxSplits;
-  if (want < 1) want = 1;
+  int64_t cap = max_by_len < kMaxSplits ? max_by_len : kMaxSplits;
+  if (cap < 1) cap = 1;
+  if (lo > cap) lo = cap;
+  if (lo < 1) lo = 1;
+  int64_t want = lo;
+  double best = -1.0;
+  for (int64_t n = lo; n <= 2 * lo + 1 && n <= cap; ++n) {
+    const double waves = static_cast<double>(ctas * n) / (4.0 * kNumSMs);
+    const double whole = static_cast<double>(static_cast<int64_t>(waves + 0.999999));
+    const double eff = waves / (whole > 0 ? whole : 1.0);
+    if (eff > best + 1e-9) { best = eff; want = n; }
+  }
   int64_t len = (kv_len + want - 1) / want;
   len = (len + chunk - 1) / chunk * chunk;
   if (len < chunk) len = chunk;
@@ -54,8 +67,58 @@ inline AttnPlan make_plan(int B, int Hq, int Hkv, int q_len, int64_t kv_len, int
 // Tensor-core decode path (attention_mma.cu): usable when mma_path_ok() holds.
 bool mma_path_ok(int d, int key_bits, int val_bits, int group, int q_len);
 int launch_attend_mma(const AttnArgs& a, cudaStream_t st);
-// Fills the 8-word table block: centroids scaled by a factor in [1,2) chosen so that all of them
-// round to fp16 with the smallest relative error, split into low / high byte tables for PRMT.
-int launch_prepare_tables(const float* kcent, const float* vcent, uint32_t* tables, cudaStream_t st);
+
+// Look-up tables of the tensor-core path, built by one CTA of 128 threads.  For each table the scale
+// s in [1,2) (512 candidates, 4 per thread) is chosen that makes the largest relative fp16 rounding
+// error of s*c_i smallest, so the systematic error of the fp16 operands drops well below 2^-12.
+// tables[0..1] key centroids as fp16 pairs, [2..3] value low bytes, [4..5] value high bytes,
+// [6] 1/key scale, [7] 1/value scale (floats).
+__device__ inline void prepare_tables_cta(const float* __restrict__ kcent, const float* __restrict__ vcent,
+                                          uint32_t* __restrict__ tables) {
+  __shared__ float cand_err[2][128];
+  __shared__ float cand_s[2][128];
+  const int tid = threadIdx.x;
+  for (int tb = 0; tb < 2; ++tb) {
+    const float* cent = tb ? vcent : kcent;
+    const int n = tb ? 8 : 4;
+    float c[8];
+    for (int i = 0; i < 8; ++i) c[i] = i < n ? cent[i] : 0.f;
+    float best_err = 1e30f, best_s = 1.f;
+    for (int k = 0; k < 4; ++k) {
+      const float s = 1.f + static_cast<float>(tid + 128 * k) * (1.f / 512.f);
+      float err = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float v = c[i] * s;
+        if (v != 0.f) err = fmaxf(err, fabsf(__half2float(__float2half_rn(v)) - v) / fabsf(v));
+      }
+      if (err < best_err) { best_err = err; best_s = s; }
+    }
+    cand_err[tb][tid] = best_err;
+    cand_s[tb][tid] = best_s;
+  }
+  __syncthreads();
+  if (tid != 0) return;
+  float sc[2];
+  for (int tb = 0; tb < 2; ++tb) {
+    float e = 1e30f, s = 1.f;
+    for (int i = 0; i < 128; ++i)
+      if (cand_err[tb][i] < e || (cand_err[tb][i] == e && cand_s[tb][i] < s)) { e = cand_err[tb][i]; s = cand_s[tb][i]; }
+    sc[tb] = s;
+  }
+  uint32_t t[6] = {0, 0, 0, 0, 0, 0};
+  for (int i = 0; i < 4; ++i) {   // whole fp16 values: entries 0,1 in word 0, entries 2,3 in word 1
+    const uint32_t h = __half_as_ushort(__float2half_rn(kcent[i] * sc[0]));
+    t[i >> 1] |= h << (16 * (i & 1));
+  }
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t h = __half_as_ushort(__float2half_rn(vcent[i] * sc[1]));
+    t[2 + (i >> 2)] |= (h & 0xFFu) << (8 * (i & 3));
+    t[4 + (i >> 2)] |= (h >> 8) << (8 * (i & 3));
+  }
+  for (int i = 0; i < 6; ++i) tables[i] = t[i];
+  tables[6] = __float_as_uint(1.f / sc[0]);
+  tables[7] = __float_as_uint(1.f / sc[1]);
+}
 
 }  // namespace qkv

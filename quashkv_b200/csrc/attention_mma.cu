@@ -18,6 +18,7 @@
 // Output: the same per-split partials (max, sum, rotated accumulator) as the generic kernel,
 // merged and un-rotated by merge_splits_kernel.
 #include <math.h>
+#include <stdlib.h>
 
 #include "attention_common.cuh"
 
@@ -71,12 +72,17 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// 8 three-bit fields (24 bits) -> 8 nibbles: sum c_k 8^k  ->  sum c_k 16^k.
-__device__ __forceinline__ uint32_t spread3to4(uint32_t g) {
-  g = g + 15u * (g & 0xFFF000u);          // 12-bit halves to 16-bit stride
-  g = g + 3u * (g & 0x0FC00FC0u);         // 6-bit pairs to 8-bit stride
-  return g + (g & 0x38383838u);           // 3-bit fields to 4-bit stride
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, int src_bytes) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(gsrc), "r"(src_bytes) : "memory");
 }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+constexpr int kStages = 4;                  // tiles in flight per warp (3 ahead of the one in use)
+constexpr int kStageBytes = 512 + 256 + 768 + 64 + 64;   // codes, signs, value codes, 2 x 16 norms
+constexpr int kOffKs = 512, kOffV = 768, kOffKn = 1536, kOffVn = 1600;
 
 struct TileRegs {
   uint2 kc[2];      // key codes: this lane's 8 bytes of rows gid, gid+8
@@ -89,89 +95,16 @@ struct MmaPtrs {
   const uint8_t* kcode; const uint8_t* ksign; const uint8_t* vcode; const float* knorm; const float* vnorm;
 };
 
-__device__ __forceinline__ void load_tile(TileRegs& r, const MmaPtrs& p, int64_t t0, int64_t t_end, int gid,
-                                          int tig) {
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int64_t tok = t0 + gid + 8 * h;
-    if (tok < t_end) {
-      r.kc[h] = __ldg(reinterpret_cast<const uint2*>(p.kcode + tok * 32) + tig);
-      r.ks[h] = __ldg(reinterpret_cast<const uint32_t*>(p.ksign + tok * 16) + tig);
-      r.kn[h] = __ldg(p.knorm + tok);
-      r.vn[h] = __ldg(p.vnorm + tok);
-    } else {
-      r.kc[h] = make_uint2(0u, 0u);
-      r.ks[h] = 0u;
-      r.kn[h] = 0.f;
-      r.vn[h] = 0.f;
-    }
-  }
-  const int wo = (3 * gid) >> 1;           // first word of this lane's 48 bits (coords 16 gid ..)
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const int64_t tok = t0 + 2 * tig + (k & 1) + 8 * (k >> 1);
-    if (tok < t_end) {
-      const uint32_t* row = reinterpret_cast<const uint32_t*>(p.vcode + tok * 48);
-      r.v[k][0] = __ldg(row + wo);
-      r.v[k][1] = __ldg(row + wo + 1);
-    } else {
-      r.v[k][0] = 0u;
-      r.v[k][1] = 0u;
-    }
-  }
-}
-
-// One warp: for a table of n centroids find the scale s in [1,2) (2048 candidates) that makes the
-// largest relative fp16 rounding error of s*c_i smallest, so that the systematic error of the
-// fp16 operand tables drops well below 2^-12.
-__device__ float best_fp16_scale(const float* cent, int n, int lane) {
-  float best_err = 1e30f, best_s = 1.f;
-  for (int k = 0; k < 64; ++k) {
-    const float s = 1.f + static_cast<float>(lane + 32 * k) * (1.f / 2048.f);
-    float err = 0.f;
-    for (int i = 0; i < n; ++i) {
-      const float v = cent[i] * s;
-      if (v != 0.f) err = fmaxf(err, fabsf(__half2float(__float2half_rn(v)) - v) / fabsf(v));
-    }
-    if (err < best_err) { best_err = err; best_s = s; }
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float e2 = __shfl_xor_sync(QKV_FULL_MASK, best_err, o);
-    const float s2 = __shfl_xor_sync(QKV_FULL_MASK, best_s, o);
-    if (e2 < best_err || (e2 == best_err && s2 < best_s)) { best_err = e2; best_s = s2; }
-  }
-  return best_s;
-}
-
-// tables[0..1] key low/high bytes, [2..3] value low bytes, [4..5] value high bytes,
-// [6] 1/key scale, [7] 1/value scale (floats).
-__global__ void prepare_tables_kernel(const float* __restrict__ kcent, const float* __restrict__ vcent,
-                                      uint32_t* __restrict__ tables) {
-  const int lane = threadIdx.x;
-  const float sk = best_fp16_scale(kcent, 4, lane), sv = best_fp16_scale(vcent, 8, lane);
-  if (lane != 0) return;
-  uint32_t t[6] = {0, 0, 0, 0, 0, 0};
-  for (int i = 0; i < 4; ++i) {
-    const uint32_t h = __half_as_ushort(__float2half_rn(kcent[i] * sk));
-    t[0] |= (h & 0xFFu) << (8 * i);
-    t[1] |= (h >> 8) << (8 * i);
-  }
-  for (int i = 0; i < 8; ++i) {
-    const uint32_t h = __half_as_ushort(__float2half_rn(vcent[i] * sv));
-    t[2 + (i >> 2)] |= (h & 0xFFu) << (8 * (i & 3));
-    t[4 + (i >> 2)] |= (h >> 8) << (8 * (i & 3));
-  }
-  for (int i = 0; i < 6; ++i) tables[i] = t[i];
-  tables[6] = __float_as_uint(1.f / sk);
-  tables[7] = __float_as_uint(1.f / sv);
-}
-
-__global__ void __launch_bounds__(kMmaWarps * 32, 3) attend_decode_mma_kernel(AttnArgs a) {
+__global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(AttnArgs a) {
   constexpr int D = 128;
   __shared__ float q_s[8][2 * D];                    // [query row][q_rot*scale | sign weights]
-  __shared__ float red[kMmaWarps][8][D + 2];         // per warp and query: max, sum, accumulator
+  // the per-warp staging rings of the token loop and the end-of-kernel reduction share storage
+  constexpr int kRingBytes = kMmaWarps * kStages * kStageBytes;
+  constexpr int kRedBytes = kMmaWarps * 8 * (D + 2) * 4;
+  __shared__ __align__(16) unsigned char pool[kRingBytes > kRedBytes ? kRingBytes : kRedBytes];
+  float (*red)[8][D + 2] = reinterpret_cast<float (*)[8][D + 2]>(pool);   // [warp][query][max, sum, acc]
   __shared__ float wsum[8];                          // sum of the sign weights per query row
+  __shared__ uint2 bop[24][32];                      // B operands per k-step and lane: 8 query-high, 8 query-low, 8 sign
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gid = lane >> 2, tig = lane & 3;
@@ -202,35 +135,35 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 3) attend_decode_mma_kernel(At
   // base = 32 tig + 16 word, o = 8*(grp&1) + (grp>>1): the order in which the PRMT decode below
   // produces them.  Sign k-step s covers 32 tig + {2s, 2s+16 | 2s+1, 2s+17}.
   const float inv_sk = __uint_as_float(a.tables[6]), inv_sv = __uint_as_float(a.tables[7]);
-  uint32_t qb[8][2], ql[8][2], wb[8][2];      // query high part, low part (q - fp16(q)), sign weights
-  {
+  {                                 // the operands depend on the lane only: each warp builds two k-steps
     const float qf = kLog2e * inv_sk;
     const float* q = q_s[gid];
     const float* w = q_s[gid] + D;
 #pragma unroll
-    for (int s = 0; s < 8; ++s) {
+    for (int s = warp; s < 8; s += kMmaWarps) {
       const int word = s >> 2, grp = s & 3;
-      const int c0 = 32 * tig + 16 * word + 8 * (grp & 1) + (grp >> 1);
+      const int c0 = 32 * tig + 16 * word + grp;        // k-step s: coordinates c0 + {0, 4 | 8, 12}
       float v[4], r[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        v[e] = q[c0 + 2 * e] * qf;
+        v[e] = q[c0 + 4 * e] * qf;
         r[e] = v[e] - __half2float(__float2half_rn(v[e]));
       }
-      qb[s][0] = pack_half2(v[0], v[1]);
-      qb[s][1] = pack_half2(v[2], v[3]);
-      ql[s][0] = pack_half2(r[0], r[1]);
-      ql[s][1] = pack_half2(r[2], r[3]);
+      bop[s][lane] = make_uint2(pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
+      bop[8 + s][lane] = make_uint2(pack_half2(r[0], r[1]), pack_half2(r[2], r[3]));
+      uint32_t wq[2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {           // pairs t = 2s, 2s+1 of this lane's 32 coordinates
         const int t = 2 * s + h, j = 32 * tig + sign_coord(t);
         const float f = 2.f * kLog2e / sign_v1(sign_pos(t));
-        wb[s][h] = pack_half2(w[j] * f, w[j + 16] * f);
+        wq[h] = pack_half2(w[j] * f, w[j + 16] * f);
       }
+      bop[16 + s][lane] = make_uint2(wq[0], wq[1]);
     }
   }
+  __syncthreads();
   // ---- PRMT look-up tables: low and high bytes of the fp16 centroids ---------------------------
-  const uint32_t kt_lo = a.tables[0], kt_hi = a.tables[1];
+  const uint32_t kt_a = a.tables[0], kt_b = a.tables[1];     // fp16 key centroids 0,1 | 2,3
   const uint32_t vt_lo[2] = {a.tables[2], a.tables[3]}, vt_hi[2] = {a.tables[4], a.tables[5]};
   // causal limits of this lane's two query columns (2 tig, 2 tig + 1)
   int lim[2];
@@ -251,42 +184,115 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 3) attend_decode_mma_kernel(At
   const int64_t t_begin = split * a.split_len;
   int64_t t_end = t_begin + a.split_len;
   if (t_end > a.kv_len) t_end = a.kv_len;
+  const int n_valid = static_cast<int>(t_end - t_begin);        // tokens of this split
+  // positions relative to the split start, as 32-bit values
+  int lim_rel[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int64_t d = static_cast<int64_t>(lim[e]) - t_begin;
+    lim_rel[e] = lim[e] == 0x7fffffff ? 0x7fffffff : (d < -1 ? -1 : static_cast<int>(d));
+  }
 
   float O[8][4];
 #pragma unroll
   for (int i = 0; i < 8; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   const int odd16 = (gid & 1) * 16;
-
   const float ci0 = -wsum[2 * tig], ci1 = -wsum[2 * tig + 1];   // accumulator start: -sum of sign weights
-  TileRegs cur, nxt;
-  int64_t t0 = t_begin + static_cast<int64_t>(warp) * kTile;
-  if (t0 < t_end) load_tile(cur, p, t0, t_end, gid, tig);
-  for (; t0 < t_end; t0 += kMmaWarps * kTile) {
-    const int64_t tn = t0 + kMmaWarps * kTile;
-    if (tn < t_end) load_tile(nxt, p, tn, t_end, gid, tig);
 
+  // ---- cp.async ring: each lane copies up to four 16-byte chunks of a tile (104 chunks) ----------
+  const int64_t t_first = t_begin + static_cast<int64_t>(warp) * kTile;
+  constexpr int kStep = kMmaWarps * kTile;                       // tokens between a warp's tiles
+  const int first_rel = warp * kTile;
+  const int n_it = first_rel < n_valid ? (n_valid - first_rel + kStep - 1) / kStep : 0;
+  unsigned char* ring = pool + warp * (kStages * kStageBytes);
+  const unsigned char* src0[4];      // chunk source at tile 0
+  int dst_off[4], tok_off[4], stride[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int c = lane + 32 * k;
+    if (c < 32) {            // key codes: two chunks per token row
+      tok_off[k] = c >> 1; stride[k] = kStep * 32; dst_off[k] = c * 16;
+      src0[k] = p.kcode + (t_first + (c >> 1)) * 32 + (c & 1) * 16;
+    } else if (c < 48) {     // sign bits: one chunk per token
+      const int r = c - 32;
+      tok_off[k] = r; stride[k] = kStep * 16; dst_off[k] = kOffKs + r * 16;
+      src0[k] = p.ksign + (t_first + r) * 16;
+    } else if (c < 96) {     // value codes: three chunks per token
+      const int i = c - 48;
+      tok_off[k] = i / 3; stride[k] = kStep * 48; dst_off[k] = kOffV + i * 16;
+      src0[k] = p.vcode + (t_first + i / 3) * 48 + (i % 3) * 16;
+    } else {                 // norms: four tokens per chunk (c < 104 holds data)
+      const int j = (c - 96) & 3, which = (c - 96) >> 2;
+      tok_off[k] = 4 * j; stride[k] = kStep * 4;
+      dst_off[k] = (which ? kOffVn : kOffKn) + j * 16;
+      src0[k] = reinterpret_cast<const unsigned char*>((which ? p.vnorm : p.knorm) + t_first + 4 * j);
+    }
+  }
+  auto issue = [&](int it) {
+    if (it < n_it) {
+      const int rel = first_rel + it * kStep;
+      unsigned char* stage = ring + (it % kStages) * kStageBytes;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (k < 3 || lane < 8) {
+          const bool ok = rel + tok_off[k] < n_valid;      // rows past the split are zero-filled, not read
+          cp_async16(stage + dst_off[k], ok ? src0[k] + static_cast<int64_t>(it) * stride[k] : src0[k], ok ? 16 : 0);
+        }
+      }
+    }
+    cp_async_commit();                                      // one group per tile slot, even when empty
+  };
+  auto fetch = [&](TileRegs& T, int it) {                  // this lane's fragment slice of a staged tile
+    const unsigned char* stage = ring + (it % kStages) * kStageBytes;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      T.kc[h] = *reinterpret_cast<const uint2*>(stage + (gid + 8 * h) * 32 + tig * 8);
+      T.ks[h] = *reinterpret_cast<const uint32_t*>(stage + kOffKs + (gid + 8 * h) * 16 + tig * 4);
+      T.kn[h] = *reinterpret_cast<const float*>(stage + kOffKn + (gid + 8 * h) * 4);
+      T.vn[h] = *reinterpret_cast<const float*>(stage + kOffVn + (gid + 8 * h) * 4);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int tok = 2 * tig + (k & 1) + 8 * (k >> 1);
+      const uint32_t* row = reinterpret_cast<const uint32_t*>(stage + kOffV + tok * 48) + ((3 * gid) >> 1);
+      T.v[k][0] = row[0];
+      T.v[k][1] = row[1];
+    }
+  };
+
+  // 8 three-bit fields (24 bits) -> 8 nibbles, sum c_k 8^k -> sum c_k 16^k, in three halving steps
+  auto spread = [](uint32_t g) {
+    g = g + 15u * (g & 0xFFF000u);          // 12-bit halves to 16-bit stride
+    g = g + 3u * (g & 0x0FC00FC0u);         // 6-bit pairs to 8-bit stride
+    return g + (g & 0x38383838u);           // 3-bit fields to 4-bit stride
+  };
+
+  auto process = [&](const TileRegs& cur, int it) {
+    const int rel = first_rel + it * kStep;
+    const bool masked = a.causal || rel + kTile > n_valid;      // warp-uniform
     // ---- scores: 8 MMAs on key codes, 8 on sign bits --------------------------------------------
     float c[4] = {ci0, ci1, ci0, ci1};
 #pragma unroll
     for (int word = 0; word < 2; ++word) {
       const uint32_t w0 = word ? cur.kc[0].y : cur.kc[0].x;
       const uint32_t w1 = word ? cur.kc[1].y : cur.kc[1].x;
-      const uint32_t x0 = w0 & 0x33333333u, y0 = (w0 >> 2) & 0x33333333u;
-      const uint32_t x1 = w1 & 0x33333333u, y1 = (w1 >> 2) & 0x33333333u;
+      // Codes r, 4+r, 8+r, 12+r of a word sit in its four bytes after a shift by 2r.  The 2-bit table
+      // fits PRMT's 8 source bytes as (lo,hi) pairs, so selector byte 0x10 + 0x22*code picks a whole
+      // fp16: one multiply-add builds four selector bytes, one PRMT yields a half2 operand.
 #pragma unroll
       for (int grp = 0; grp < 4; ++grp) {
-        const uint32_t s0 = (grp >> 1 ? y0 : x0) >> (16 * (grp & 1));
-        const uint32_t s1 = (grp >> 1 ? y1 : x1) >> (16 * (grp & 1));
-        const uint32_t lo0 = prmt(kt_lo, kt_hi, s0), hi0 = prmt(kt_hi, kt_lo, s0);
-        const uint32_t lo1 = prmt(kt_lo, kt_hi, s1), hi1 = prmt(kt_hi, kt_lo, s1);
+        const uint32_t y0 = (w0 >> (2 * grp)) & 0x03030303u, y1 = (w1 >> (2 * grp)) & 0x03030303u;
+        const uint32_t sl0 = y0 * 0x22u + 0x10101010u, sh0 = sl0 >> 16;
+        const uint32_t sl1 = y1 * 0x22u + 0x10101010u, sh1 = sl1 >> 16;
         uint32_t af[4];
-        af[0] = prmt(lo0, hi0, 0x5140);
-        af[1] = prmt(lo1, hi1, 0x5140);
-        af[2] = prmt(lo0, hi0, 0x7362);
-        af[3] = prmt(lo1, hi1, 0x7362);
-        mma16816(c, af, qb[word * 4 + grp][0], qb[word * 4 + grp][1]);
-        mma16816(c, af, ql[word * 4 + grp][0], ql[word * 4 + grp][1]);
+        af[0] = prmt(kt_a, kt_b, sl0);
+        af[1] = prmt(kt_a, kt_b, sl1);
+        af[2] = prmt(kt_a, kt_b, sh0);
+        af[3] = prmt(kt_a, kt_b, sh1);
+        const uint2 bh = bop[word * 4 + grp][lane], bl = bop[8 + word * 4 + grp][lane];
+        mma16816(c, af, bh.x, bh.y);
+        mma16816(c, af, bl.x, bl.y);
       }
     }
     {
@@ -303,17 +309,20 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 3) attend_decode_mma_kernel(At
           af[2 * h] = cp0[cpy] & mask;
           af[2 * h + 1] = cp1[cpy] & mask;
         }
-        mma16816(c, af, wb[s][0], wb[s][1]);
+        const uint2 bw = bop[16 + s][lane];
+        mma16816(c, af, bw.x, bw.y);
       }
     }
 
     // ---- online softmax on the accumulator fragment (log2 domain) ------------------------------
-    const int64_t tokA = t0 + gid, tokB = tokA + 8;
-    float sc[4];
-    sc[0] = (tokA < t_end && tokA <= lim[0]) ? c[0] * cur.kn[0] : -INFINITY;
-    sc[1] = (tokA < t_end && tokA <= lim[1]) ? c[1] * cur.kn[0] : -INFINITY;
-    sc[2] = (tokB < t_end && tokB <= lim[0]) ? c[2] * cur.kn[1] : -INFINITY;
-    sc[3] = (tokB < t_end && tokB <= lim[1]) ? c[3] * cur.kn[1] : -INFINITY;
+    float sc[4] = {c[0] * cur.kn[0], c[1] * cur.kn[0], c[2] * cur.kn[1], c[3] * cur.kn[1]};
+    if (masked) {
+      const int tokA = rel + gid, tokB = tokA + 8;
+      if (!(tokA < n_valid && tokA <= lim_rel[0])) sc[0] = -INFINITY;
+      if (!(tokA < n_valid && tokA <= lim_rel[1])) sc[1] = -INFINITY;
+      if (!(tokB < n_valid && tokB <= lim_rel[0])) sc[2] = -INFINITY;
+      if (!(tokB < n_valid && tokB <= lim_rel[1])) sc[3] = -INFINITY;
+    }
     float mx[2] = {fmaxf(sc[0], sc[2]), fmaxf(sc[1], sc[3])};
 #pragma unroll
     for (int o = 4; o < 32; o <<= 1) {
@@ -348,8 +357,8 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 3) attend_decode_mma_kernel(At
     for (int k = 0; k < 4; ++k) {
       const uint32_t lo = __funnelshift_r(cur.v[k][0], cur.v[k][1], odd16);
       const uint32_t hi = cur.v[k][1] >> odd16;
-      nib[k][0] = spread3to4(lo & 0xFFFFFFu);
-      nib[k][1] = spread3to4(__funnelshift_r(lo, hi, 24) & 0xFFFFFFu);
+      nib[k][0] = spread(lo & 0xFFFFFFu);
+      nib[k][1] = spread(__funnelshift_r(lo, hi, 24) & 0xFFFFFFu);
     }
 #pragma unroll
     for (int grp = 0; grp < 2; ++grp) {
@@ -368,8 +377,21 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 3) attend_decode_mma_kernel(At
         mma16816(O[grp * 4 + i], af, pb0, pb1);
       }
     }
-    cur = nxt;
+  };
+
+#pragma unroll
+  for (int i = 0; i < kStages - 1; ++i) issue(i);
+  for (int it = 0; it < n_it; ++it) {
+    issue(it + kStages - 1);              // refills the slot that tile it-1 used
+    cp_async_wait<kStages - 1>();         // this lane's chunks of tile `it` have landed
+    __syncwarp();                         // ... and every other lane's
+    TileRegs cur;
+    fetch(cur, it);
+    __syncwarp();                         // all reads of the slot are done before it is refilled
+    process(cur, it);
   }
+  cp_async_wait<0>();
+  __syncthreads();                        // the reduction buffer below reuses the ring storage
 
   // ---- per-warp results to shared memory: column sums over the token lanes, then all warps ------
 #pragma unroll
@@ -415,11 +437,6 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 3) attend_decode_mma_kernel(At
 
 bool mma_path_ok(int d, int key_bits, int val_bits, int group, int q_len) {
   return d == 128 && key_bits == 3 && val_bits == 3 && group * q_len <= 8;
-}
-
-int launch_prepare_tables(const float* kcent, const float* vcent, uint32_t* tables, cudaStream_t st) {
-  prepare_tables_kernel<<<1, 32, 0, st>>>(kcent, vcent, tables);
-  return check_launch();
 }
 
 int launch_attend_mma(const AttnArgs& a, cudaStream_t st) {

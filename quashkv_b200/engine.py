@@ -86,6 +86,7 @@ class QuashKVEngine:
     def reserve(self, batch: int, heads: int, capacity: int, device=None) -> None:
         """Pre-size the planes (optional; ``append`` grows them as needed)."""
         device = torch.device(device) if device is not None else self.device
+        capacity = -(-capacity // 64) * 64      # whole 64-row groups keep every plane row 16-byte aligned
         if self._planes is None:
             self._shape = (batch, heads)
             self._planes = self._allocate(batch * heads, capacity, device)
