@@ -167,6 +167,29 @@ int qkv_attention(const void* q, int q_dtype, qkv_cache_t cache,
                   const float* S, float qjl_scale, float scale, int causal,
                   float* out, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Same computation as qkv_attention for callers that cannot hand over a workspace because they
+ * are not allowed to allocate device memory when the call is made: a serving loop that has
+ * given all of HBM to a fixed memory plan, a plugin invoked under a framework that forbids
+ * cudaMalloc on its streams, code that runs between "begin capture" and "end capture" of a
+ * stream.  This entry point has no counterpart in the reference.  The rotated queries and the
+ * per-split partial results live in a fixed array inside the library image
+ * (QKV_ATTENTION_STATIC_SCRATCH_BYTES per GPU that loads the library, held until the process
+ * exits); the call allocates nothing, on the host or the device, and returns QKV_EWORKSPACE
+ * when qkv_attention_workspace_bytes(...) for the given shape exceeds that size.
+ * The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress) and remembers it; make that first call outside any stream capture.
+ * All calls on a device share the one array: two calls whose kernels can overlap on the GPU
+ * (different streams, no dependency) race on it and must be ordered by the caller.  Nothing in
+ * the array needs clearing between calls; every word that is read is written first by the
+ * same call. */
+#define QKV_ATTENTION_STATIC_SCRATCH_BYTES (8u << 20)
+int qkv_attention_static_scratch(const void* q, int q_dtype, qkv_cache_t cache,
+                                 int B, int Hq, int Hkv, int q_len, int64_t kv_len, int d,
+                                 int key_bits, int val_bits,
+                                 const float* Pi, const float* key_centroids, const float* val_centroids,
+                                 const float* S, float qjl_scale, float scale, int causal,
+                                 float* out, void* stream);
+
 /* ---- index scan ------------------------------------------------------------------------------
  * Replaces QuashIndex.search (reference nn_search/index.py:121-163):
  * score[m,n] = norm_n * (q_rot_m . c[code_n] + qjl_scale * sum(|q_rot_m| * S * (2*sign_n-1))),

@@ -44,6 +44,8 @@ SIGNATURES = {
     "qkv_attention_workspace_bytes": (_sz, [_i, _i, _i, _i, _i64, _i]),
     "qkv_attention": (_i, [_vp, _i, Cache, _i, _i, _i, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _f, _f, _i,
                            _vp, _vp, _sz, _vp]),
+    "qkv_attention_static_scratch": (_i, [_vp, _i, Cache, _i, _i, _i, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp,
+                                          _f, _f, _i, _vp, _vp]),
     "qkv_index_workspace_bytes": (_sz, [_i64, _i, _i, _i]),
     "qkv_index_scan_topk": (_i, [_vp, _i, _i, _vp, _vp, _vp, _i64, _i, _vp, _vp, _vp, _f, _i, _i64, _vp, _vp,
                                  _vp, _sz, _vp]),

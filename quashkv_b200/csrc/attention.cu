@@ -437,3 +437,34 @@ extern "C" int qkv_attention(const void* q, int q_dtype, qkv_cache_t cache,
       part, p.rows, p.n_splits, d, Pi, out);
   return check_launch();
 }
+
+// ---- attention without a caller-provided workspace ------------------------------------------------
+// The scratch array is part of the library image, so no allocation call is ever made for it.  In
+// host code the symbol is only a handle: its device address comes from cudaGetSymbolAddress, asked
+// once per device (with that device current) and kept in a small table.
+namespace {
+__device__ __align__(256) unsigned char g_attention_scratch[QKV_ATTENTION_STATIC_SCRATCH_BYTES];
+constexpr int kMaxDevices = 64;
+void* g_scratch_addr[kMaxDevices] = {};
+}  // namespace
+
+extern "C" int qkv_attention_static_scratch(const void* q, int q_dtype, qkv_cache_t cache,
+                                            int B, int Hq, int Hkv, int q_len, int64_t kv_len, int d,
+                                            int key_bits, int val_bits,
+                                            const float* Pi, const float* key_centroids,
+                                            const float* val_centroids, const float* S, float qjl_scale,
+                                            float scale, int causal, float* out, void* stream) {
+  if (B < 1 || Hq < 1 || Hkv < 1 || q_len < 1 || kv_len < 1 || d < 32 || d > kMaxD) return QKV_EDIM;
+  const size_t need = qkv_attention_workspace_bytes(B, Hq, Hkv, q_len, kv_len, d);
+  if (need == 0 || need > QKV_ATTENTION_STATIC_SCRATCH_BYTES) return QKV_EWORKSPACE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return QKV_EARG;
+  void* ptr = __atomic_load_n(&g_scratch_addr[dev], __ATOMIC_ACQUIRE);
+  if (ptr == nullptr) {   // first call on this device; concurrent first calls all obtain the same address
+    if (cudaGetSymbolAddress(&ptr, g_attention_scratch) != cudaSuccess || ptr == nullptr) return QKV_ELAUNCH;
+    __atomic_store_n(&g_scratch_addr[dev], ptr, __ATOMIC_RELEASE);
+  }
+  return qkv_attention(q, q_dtype, cache, B, Hq, Hkv, q_len, kv_len, d, key_bits, val_bits, Pi, key_centroids,
+                       val_centroids, S, qjl_scale, scale, causal, out, ptr, QKV_ATTENTION_STATIC_SCRATCH_BYTES,
+                       stream);
+}
