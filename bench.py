@@ -333,12 +333,17 @@ def main():
     ap.add_argument("--batch", type=int, default=B,
                     help="batch elements in the cache (default 32 = the benchmark workload; smaller for profiler captures)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--extras-only", action="store_true",
+                    help="run only the secondary compress / decompress / index measurements (for profiler captures)")
     args = ap.parse_args()
     if args.batch == B:
         args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     else:   # a reduced case for profiling: not a benchmark number
         args.no_extras = True
-    if args.impl == "reference":
+    if args.extras_only:
+        torch.cuda.set_device(0)
+        print(json.dumps({"extra": extras(torch.device("cuda", 0))}))
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -1,0 +1,42 @@
+// Argument blocks shared by the CUDA-core and the tensor-core rotation kernels.
+#pragma once
+
+#include "common.cuh"
+
+namespace qkv {
+
+enum { MODE_MSE = 0, MODE_IP = 1, MODE_MIXED = 2 };
+
+struct CompressArgs {
+  const void* x; int x_dtype; int64_t x_pitch; int64_t n_vec; int d;
+  const float* Pi;
+  int mode;
+  const float* bounds0; int bits0;     // uniform / outlier table
+  const float* bounds1; int bits1;     // regular table (mixed)
+  const float* centroids;              // IP: centroids of table 0
+  const float* S;                      // IP
+  const uint8_t* is_outlier;           // mixed
+  uint8_t* codes; uint8_t* signs; int packed; float* norms;
+  qkv_rows_t rows;
+};
+
+struct DecompressArgs {
+  const uint8_t* codes; const uint8_t* signs; int packed; const float* norms;
+  qkv_rows_t rows; int64_t n_vec; int d;
+  const float* Pi;
+  int mode;                            // MODE_MSE (signs may be set) or MODE_MIXED
+  const float* cents0; int bits0;
+  const float* cents1; int bits1;
+  const uint8_t* is_outlier;
+  const float* S; float qjl_scale;
+  void* out; int out_dtype; int64_t out_pitch;
+};
+
+
+// Tensor-core rotation (rotate_mma.cu): d == 128, uniform bit width.  Returns QKV_OK after launching.
+bool compress_mma_ok(const CompressArgs& a);
+int launch_compress_mma(const CompressArgs& a, cudaStream_t st);
+bool decompress_mma_ok(const DecompressArgs& a);
+int launch_decompress_mma(const DecompressArgs& a, cudaStream_t st);
+
+}  // namespace qkv

@@ -6,40 +6,15 @@
 // output coordinates lane, lane+32, ... so that the matrix row reads are conflict free and
 // every matrix element fetched from shared memory feeds 8 FMAs.  The dot products
 // accumulate in fp32 with FMA in ascending input-coordinate order.
-#include "common.cuh"
+#include <stdlib.h>
+
+#include "rotate_common.cuh"
 
 namespace qkv {
 
 constexpr int kWarps = 8;       // warps per CTA
 constexpr int kVPW = 8;         // vectors rotated together by one warp
 constexpr int kThreads = kWarps * 32;
-
-enum { MODE_MSE = 0, MODE_IP = 1, MODE_MIXED = 2 };
-
-struct CompressArgs {
-  const void* x; int x_dtype; int64_t x_pitch; int64_t n_vec; int d;
-  const float* Pi;
-  int mode;
-  const float* bounds0; int bits0;     // uniform / outlier table
-  const float* bounds1; int bits1;     // regular table (mixed)
-  const float* centroids;              // IP: centroids of table 0
-  const float* S;                      // IP
-  const uint8_t* is_outlier;           // mixed
-  uint8_t* codes; uint8_t* signs; int packed; float* norms;
-  qkv_rows_t rows;
-};
-
-struct DecompressArgs {
-  const uint8_t* codes; const uint8_t* signs; int packed; const float* norms;
-  qkv_rows_t rows; int64_t n_vec; int d;
-  const float* Pi;
-  int mode;                            // MODE_MSE (signs may be set) or MODE_MIXED
-  const float* cents0; int bits0;
-  const float* cents1; int bits1;
-  const uint8_t* is_outlier;
-  const float* S; float qjl_scale;
-  void* out; int out_dtype; int64_t out_pitch;
-};
 
 // Shared-memory carve-up common to both kernels.
 //   mat   [d][DP]            fp32   (DP = 32*NT)
@@ -377,8 +352,15 @@ static int check_rows(const qkv_rows_t& r) {
   return (r.seg_len >= 1 && r.seg_stride >= 0 && r.seg_off >= 0) ? QKV_OK : QKV_EARG;
 }
 
+// QUASHKV_B200_CUDA_CORE_ROTATION=1 keeps every call on the fp32 CUDA-core kernels (for A/B checks).
+static bool cuda_core_only() {
+  const char* e = getenv("QUASHKV_B200_CUDA_CORE_ROTATION");
+  return e && e[0] == '1';
+}
+
 static int run_compress(const CompressArgs& a, cudaStream_t st) {
   if (a.n_vec == 0) return QKV_OK;
+  if (compress_mma_ok(a) && !cuda_core_only()) return launch_compress_mma(a, st);
   return launch_by_nt(a, a.d, a.n_vec, st, compress_kernel<1>, compress_kernel<2>, compress_kernel<3>,
                       compress_kernel<4>);
 }
@@ -460,6 +442,7 @@ extern "C" int qkv_decompress(const uint8_t* codes, const uint8_t* signs, int pa
   a.codes = codes; a.signs = signs; a.packed = packed; a.norms = norms; a.rows = rows;
   a.n_vec = n_vec; a.d = d; a.Pi = Pi; a.mode = MODE_MSE; a.cents0 = centroids; a.bits0 = bits; a.bits1 = 1;
   a.S = S; a.qjl_scale = qjl_scale; a.out = out; a.out_dtype = out_dtype; a.out_pitch = out_pitch;
+  if (decompress_mma_ok(a) && !cuda_core_only()) return launch_decompress_mma(a, static_cast<cudaStream_t>(stream));
   return launch_by_nt(a, d, n_vec, static_cast<cudaStream_t>(stream), decompress_kernel<1>,
                       decompress_kernel<2>, decompress_kernel<3>, decompress_kernel<4>);
 }

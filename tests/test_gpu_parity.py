@@ -163,6 +163,37 @@ def test_half_precision_inputs_are_exact_upcasts(golden):
     assert out.dtype == torch.bfloat16 and rel_l2(out.float(), ref) < BF16_TOL
 
 
+def test_tensor_core_rotation_equals_cuda_core_rotation(golden, monkeypatch):
+    """d = 128 batches rotate on tensor cores (three-term bf16 split) with an fp32 recheck of every
+    coordinate near a decision boundary; the codes, sign bits and norms must be identical to the
+    fp32 CUDA-core kernel's, which the other tests pin to the reference."""
+    c = golden("constants")
+    Pi, S = t(c["Pi_d128_s42"]).to(DEV), t(c["S_d128_s42"]).to(DEV)
+    gen = torch.Generator().manual_seed(77)
+    x = torch.randn(300_000 + 37, 128, generator=gen)
+    x[:, torch.randperm(128, generator=gen)[:4]] *= 8
+    x[5] = 0
+    for dtype in (torch.float32, torch.bfloat16):
+        xd = x.to(dtype).to(DEV)
+        for bits in (2, 3, 4):
+            bnd, cent = t(c[f"bnd_d128_b{bits}"]).to(DEV), t(c[f"cent_d128_b{bits}"]).to(DEV)
+            fast = ops.compress_mse(xd, Pi, bnd, bits, packed=True)
+            fast_ip = ops.compress_ip(xd, Pi, bnd, cent, S, bits, packed=True)
+            rec_fast = ops.decompress(fast[0], fast[1], Pi, cent, bits, packed=True, d=128)
+            monkeypatch.setenv("QUASHKV_B200_CUDA_CORE_ROTATION", "1")
+            slow = ops.compress_mse(xd, Pi, bnd, bits, packed=True)
+            slow_ip = ops.compress_ip(xd, Pi, bnd, cent, S, bits, packed=True)
+            rec_slow = ops.decompress(fast[0], fast[1], Pi, cent, bits, packed=True, d=128)
+            monkeypatch.delenv("QUASHKV_B200_CUDA_CORE_ROTATION")
+            n_code = int((fast[0] != slow[0]).sum()) + int((fast_ip[0] != slow_ip[0]).sum())
+            n_sign = int((fast_ip[1] != slow_ip[1]).sum())
+            print(f"[ties] tensor-core vs CUDA-core rotation, {dtype}, {bits} bits: {n_code} code bytes, "
+                  f"{n_sign} sign bytes differ of {fast[0].numel() + fast_ip[0].numel()}")
+            assert n_code == 0 and n_sign == 0
+            assert torch.equal(fast[1], slow[1]) and torch.equal(fast_ip[2], slow_ip[2])
+            assert rel_l2(rec_fast, rec_slow) < 2e-6
+
+
 def test_shapes_ragged_and_empty(golden):
     c = golden("constants")
     for d in (64, 96, 128):
