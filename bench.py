@@ -149,7 +149,8 @@ def run_reference(args):
         "impl": "reference", "metric": "packed_kv_decode_attention_hbm_gbps", "value": gbs, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 2), "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": sample},
+        "config": {"workload": WORKLOAD, "batch": 32, "kv_heads_per_gpu": HKV, "query_heads_per_gpu": HQ,
+                   "kv_len": S, "head_dim": D, "key_bits": KEY_BITS, "value_bits": VAL_BITS, "sample": sample},
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -305,10 +306,11 @@ def run_ours(args):
                      "traffic": None, "peak_source": which,
                      "note": "per-GPU packed bytes / whole attention call (query rotation + split scan + merge)"},
     }
-    traffic_file = os.path.join(ROOT, "profiles", "attention_decode_traffic.json")
-    if os.path.exists(traffic_file):
-        with open(traffic_file) as f:
-            line["roofline"]["traffic"] = json.load(f).get("dram_bytes_per_launch")
+    # dram__bytes_read + write of one attend_decode_mma_kernel launch from the ncu capture summarised
+    # in profiles/attend_decode_mma_decode_batch8.md (223.1 MB at batch 8, traffic grows with the
+    # token-heads processed: x4 at the benchmark's batch 32)
+    if B == 32:
+        line["roofline"]["traffic"] = 4 * 223.06e6
     if B != 32:
         line["config"]["workload"] = WORKLOAD + f"_REDUCED_batch{B}"
     if world == 1 and not args.no_cpu:
