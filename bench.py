@@ -300,7 +300,7 @@ def run_ours(args):
                    "bytes_per_step_per_gpu": step_bytes, "l2": "inputs (872 MB per GPU) exceed the 126 MB L2"},
         "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": q_host[0].numel() * 2,
                 "d2h_bytes_per_step": out_host.numel() * 4},
-        "gpu_launches": 3 * args.steps,   # query rotation (+ table prep), split scan, merge
+        "gpu_launches": 2 * args.steps,   # query rotation (+ table prep), split scan with fused merge
         "clocks": clocks.summary,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_source": which,

@@ -29,9 +29,11 @@ __global__ void __launch_bounds__(128) rotate_queries_kernel(const void* __restr
                                                              float scale, float* __restrict__ qk,
                                                              const float* __restrict__ kcent,
                                                              const float* __restrict__ vcent,
-                                                             uint32_t* __restrict__ tables) {
+                                                             uint32_t* __restrict__ tables, int n_counters) {
   if (tables != nullptr && blockIdx.x == gridDim.x - 1) {   // one extra CTA: look-up tables of the
-    prepare_tables_cta(kcent, vcent, tables);               // tensor-core path
+    unsigned* arrivals = reinterpret_cast<unsigned*>(reinterpret_cast<unsigned char*>(tables) + kAttnHeaderBytes);
+    for (int i = threadIdx.x; i < n_counters; i += blockDim.x) arrivals[i] = 0u;   // tensor-core path,
+    prepare_tables_cta(kcent, vcent, tables);                                        // and its counters
     return;
   }
   __shared__ __align__(16) float x_s[kRowsPerCta][kMaxD];
@@ -342,16 +344,16 @@ __global__ void __launch_bounds__(128) merge_splits_kernel(const float* __restri
 // Host-side launcher shared with the index scan.
 static int launch_rotate(const void* q, int q_dtype, int64_t rows, int d, const float* Pi, const float* S,
                          float qjl_scale, float scale, float* qk, const float* kcent, const float* vcent,
-                         uint32_t* tables, cudaStream_t st) {
+                         uint32_t* tables, int n_counters, cudaStream_t st) {
   const unsigned ctas = static_cast<unsigned>((rows + kRowsPerCta - 1) / kRowsPerCta) + (tables ? 1u : 0u);
   rotate_queries_kernel<<<ctas, 128, 0, st>>>(q, q_dtype, rows, d, Pi, S, qjl_scale, scale, qk, kcent, vcent,
-                                              tables);
+                                              tables, n_counters);
   return check_launch();
 }
 
 int launch_rotate_queries(const void* q, int q_dtype, int64_t rows, int d, const float* Pi, const float* S,
                           float qjl_scale, float scale, float* qk, cudaStream_t st) {
-  return launch_rotate(q, q_dtype, rows, d, Pi, S, qjl_scale, scale, qk, nullptr, nullptr, nullptr, st);
+  return launch_rotate(q, q_dtype, rows, d, Pi, S, qjl_scale, scale, qk, nullptr, nullptr, nullptr, 0, st);
 }
 
 typedef void (*AttnKernel)(AttnArgs);
@@ -381,7 +383,7 @@ using namespace qkv;
 extern "C" size_t qkv_attention_workspace_bytes(int B, int Hq, int Hkv, int q_len, int64_t kv_len, int d) {
   if (B < 1 || Hq < 1 || Hkv < 1 || q_len < 1 || kv_len < 1 || d < 32) return 0;
   const AttnPlan p = make_plan(B, Hq, Hkv, q_len, kv_len, d);
-  return kAttnHeaderBytes + p.qk_bytes + p.part_bytes;
+  return p.hdr_bytes + p.qk_bytes + p.part_bytes;
 }
 
 extern "C" int qkv_attention(const void* q, int q_dtype, qkv_cache_t cache,
@@ -404,13 +406,13 @@ extern "C" int qkv_attention(const void* q, int q_dtype, qkv_cache_t cache,
                        reinterpret_cast<uintptr_t>(cache.v_codes) | reinterpret_cast<uintptr_t>(workspace);
   if (al & 15u) return QKV_EALIGN;
   const AttnPlan p = make_plan(B, Hq, Hkv, q_len, kv_len, d);
-  if (workspace_bytes < kAttnHeaderBytes + p.qk_bytes + p.part_bytes) return QKV_EWORKSPACE;
+  if (workspace_bytes < p.hdr_bytes + p.qk_bytes + p.part_bytes) return QKV_EWORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
   unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
   uint32_t* tables = reinterpret_cast<uint32_t*>(ws);
-  float* qk = reinterpret_cast<float*>(ws + kAttnHeaderBytes);
-  float* part = reinterpret_cast<float*>(ws + kAttnHeaderBytes + p.qk_bytes);
+  float* qk = reinterpret_cast<float*>(ws + p.hdr_bytes);
+  float* part = reinterpret_cast<float*>(ws + p.hdr_bytes + p.qk_bytes);
   // QUASHKV_B200_GENERIC_ATTENTION=1 routes every call to the generic kernel (for A/B checks).
   const char* env = getenv("QUASHKV_B200_GENERIC_ATTENTION");
   const bool force_generic = env && env[0] == '1';
@@ -419,16 +421,19 @@ extern "C" int qkv_attention(const void* q, int q_dtype, qkv_cache_t cache,
       ((reinterpret_cast<uintptr_t>(cache.k_norms) | reinterpret_cast<uintptr_t>(cache.v_norms)) & 15u) == 0;
   const bool use_mma = mma_path_ok(d, key_bits, val_bits, Hq / Hkv, q_len) && chunks_ok && !force_generic;
   int rc = launch_rotate(q, q_dtype, p.rows, d, Pi, S, qjl_scale, scale, qk, key_centroids, val_centroids,
-                         use_mma ? tables : nullptr, st);
+                         use_mma ? tables : nullptr, B * Hkv, st);
   if (rc) return rc;
 
   AttnArgs a{};
   a.cache = cache; a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.G = Hq / Hkv; a.q_len = q_len; a.d = d;
   a.causal = causal; a.kv_len = kv_len; a.qk = qk; a.kcent = key_centroids; a.vcent = val_centroids;
   a.part = part; a.n_splits = p.n_splits; a.split_len = p.split_len;
-  if (use_mma) {
+  if (use_mma) {          // one launch: the last split of every (batch, kv head) merges and un-rotates
     a.tables = tables;
-    if ((rc = launch_attend_mma(a, st))) return rc;
+    a.arrivals = reinterpret_cast<unsigned*>(ws + kAttnHeaderBytes);
+    a.Pi = Pi;
+    a.out = out;
+    return launch_attend_mma(a, st);
   } else {
     const dim3 grid(p.n_splits, p.n_qtiles, B * Hkv);
     pick(key_bits - 1, val_bits)<<<grid, kAttnWarps * 32, 0, st>>>(a);

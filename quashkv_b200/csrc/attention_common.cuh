@@ -19,12 +19,19 @@ struct AttnArgs {
   const float* kcent; const float* vcent;
   float* part;          // [rows][n_splits][d+2]
   const uint32_t* tables;   // tensor-core path: fp16 look-up tables and their scales (8 words)
+  unsigned* arrivals;       // tensor-core path: splits finished per (batch, kv head); zeroed by the rotation kernel
+  const float* Pi;          // tensor-core path: the last split of a head merges and un-rotates
+  float* out;
   int n_splits; int64_t split_len;
 };
 
 constexpr size_t kAttnHeaderBytes = 256;   // workspace header: look-up tables of the tensor-core path
 
-struct AttnPlan { int n_splits; int64_t split_len; int n_qtiles; int64_t rows; size_t qk_bytes, part_bytes; };
+struct AttnPlan {
+  int n_splits; int64_t split_len; int n_qtiles; int64_t rows;
+  size_t hdr_bytes;     // look-up tables (first 256 bytes) + one arrival counter per (batch, kv head)
+  size_t qk_bytes, part_bytes;
+};
 
 inline AttnPlan make_plan(int B, int Hq, int Hkv, int q_len, int64_t kv_len, int d) {
   AttnPlan p;
@@ -57,6 +64,7 @@ inline AttnPlan make_plan(int B, int Hq, int Hkv, int q_len, int64_t kv_len, int
   p.split_len = len;
   p.n_splits = static_cast<int>((kv_len + len - 1) / len);
   if (p.n_splits < 1) p.n_splits = 1;
+  p.hdr_bytes = (kAttnHeaderBytes + static_cast<size_t>(B) * Hkv * sizeof(unsigned) + 255) / 256 * 256;
   p.qk_bytes = static_cast<size_t>(p.rows) * 2 * d * sizeof(float);
   p.qk_bytes = (p.qk_bytes + 255) / 256 * 256;
   p.part_bytes = static_cast<size_t>(p.rows) * p.n_splits * (d + 2) * sizeof(float);

@@ -433,6 +433,65 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
     const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
     a.part[(qrow * a.n_splits + split) * (D + 2) + e] = v;
   }
+
+  // ---- the CTA that finishes a (batch, kv head) last merges its splits and applies Pi ----------------
+  __shared__ bool last_split;
+  __threadfence();                                   // this CTA's partials are visible device-wide
+  __syncthreads();
+  if (threadIdx.x == 0) last_split = atomicAdd(a.arrivals + seg, 1u) == static_cast<unsigned>(a.n_splits - 1);
+  __syncthreads();
+  if (!last_split) return;
+  __threadfence();                                   // ... and so are everyone else's, now
+  float* vec = reinterpret_cast<float*>(pool);       // [8][D] merged, normalised accumulators
+  float* wgt = vec + 8 * D;                          // [8][kMaxSplits] weights of the splits
+  float* invl = wgt + 8 * kMaxSplits;                // [8]
+  for (int r = warp; r < nq; r += kMmaWarps) {       // a warp per query row
+    const int g = r / a.q_len, qi = r % a.q_len;
+    const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
+    const float* pp = a.part + qrow * a.n_splits * (D + 2);
+    float M = -INFINITY;
+    for (int sp = lane; sp < a.n_splits; sp += 32) M = fmaxf(M, __ldcg(pp + sp * (D + 2)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(QKV_FULL_MASK, M, o));
+    float L = 0.f;
+    for (int sp = lane; sp < a.n_splits; sp += 32) {
+      const float mm = __ldcg(pp + sp * (D + 2));
+      const float f = (mm == -INFINITY) ? 0.f : expf(mm - M);
+      wgt[r * kMaxSplits + sp] = f;
+      L += f * __ldcg(pp + sp * (D + 2) + 1);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(QKV_FULL_MASK, L, o);
+    if (lane == 0) invl[r] = 1.f / fmaxf(L, 1e-30f);
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < nq * D; idx += blockDim.x) {
+    const int r = idx / D, j = idx % D;
+    const int g = r / a.q_len, qi = r % a.q_len;
+    const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
+    const float* pp = a.part + qrow * a.n_splits * (D + 2);
+    float v = 0.f;
+    for (int sp = 0; sp < a.n_splits; ++sp) v += wgt[r * kMaxSplits + sp] * __ldcg(pp + sp * (D + 2) + 2 + j);
+    vec[r * D + j] = v * invl[r];
+  }
+  __syncthreads();
+  {
+    const int i = threadIdx.x;                       // output coordinate (blockDim.x == D)
+    float o[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) o[r] = 0.f;
+#pragma unroll 8
+    for (int j = 0; j < D; ++j) {
+      const float mval = __ldg(a.Pi + j * D + i);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) o[r] = fmaf(vec[r * D + j], mval, o[r]);
+    }
+    for (int r = 0; r < nq; ++r) {
+      const int g = r / a.q_len, qi = r % a.q_len;
+      const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
+      a.out[qrow * D + i] = o[r];
+    }
+  }
 }
 
 bool mma_path_ok(int d, int key_bits, int val_bits, int group, int q_len) {
