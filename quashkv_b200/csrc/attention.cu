@@ -351,6 +351,12 @@ static int launch_rotate(const void* q, int q_dtype, int64_t rows, int d, const 
   return check_launch();
 }
 
+int launch_rotate_with_tables(const void* q, int q_dtype, int64_t rows, int d, const float* Pi, const float* S,
+                              float qjl_scale, float scale, float* qk, const float* kcent, const float* vcent,
+                              uint32_t* tables, cudaStream_t st) {
+  return launch_rotate(q, q_dtype, rows, d, Pi, S, qjl_scale, scale, qk, kcent, vcent, tables, 0, st);
+}
+
 int launch_rotate_queries(const void* q, int q_dtype, int64_t rows, int d, const float* Pi, const float* S,
                           float qjl_scale, float scale, float* qk, cudaStream_t st) {
   return launch_rotate(q, q_dtype, rows, d, Pi, S, qjl_scale, scale, qk, nullptr, nullptr, nullptr, 0, st);

@@ -89,6 +89,20 @@ __device__ __forceinline__ void store_packed_words(uint32_t mine, int w, uint8_t
 int launch_rotate_queries(const void* q, int q_dtype, int64_t rows, int d, const float* Pi, const float* S,
                           float qjl_scale, float scale, float* qk, cudaStream_t st);
 
+// Same, with one extra CTA that builds the fp16 look-up tables of the tensor-core kernels (8 words
+// at `tables`, see prepare_tables_cta) from the key / value centroids.  Defined in attention.cu.
+int launch_rotate_with_tables(const void* q, int q_dtype, int64_t rows, int d, const float* Pi, const float* S,
+                              float qjl_scale, float scale, float* qk, const float* kcent, const float* vcent,
+                              uint32_t* tables, cudaStream_t st);
+
+// Tensor-core index scan (index_scan_mma.cu).
+bool index_mma_ok(int d, int bits, int64_t N, int k, const void* codes, const void* signs, const void* norms);
+size_t index_mma_workspace_bytes(int64_t N, int M, int k);
+int launch_index_scan_mma(const float* queries, int M, const uint8_t* codes, const uint8_t* signs,
+                          const float* norms, int64_t N, const float* Pi, const float* cent, const float* S,
+                          float qjl_scale, int k, int64_t id_base, float* out_scores, int64_t* out_ids,
+                          void* workspace, size_t workspace_bytes, cudaStream_t st);
+
 inline int check_launch() { return cudaGetLastError() == cudaSuccess ? QKV_OK : QKV_ELAUNCH; }
 
 }  // namespace qkv

@@ -10,6 +10,7 @@
 //
 // Order everywhere: higher score first, equal scores by lower id.
 #include <math.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -275,7 +276,9 @@ using namespace qkv;
 extern "C" size_t qkv_index_workspace_bytes(int64_t N, int M, int d, int k) {
   if (N < 1 || M < 1 || d < 32 || k < 1) return 0;
   const ScanPlan p = make_scan_plan(N, M, d, k);
-  return p.qk_bytes + p.ls_bytes + p.li_bytes;
+  const size_t generic = p.qk_bytes + p.ls_bytes + p.li_bytes;
+  const size_t mma = (d == 128 && k <= QKV_INDEX_MAX_K) ? index_mma_workspace_bytes(N, M, k) : 0;
+  return generic > mma ? generic : mma;      // either path may be taken, depending on bits and alignment
 }
 
 extern "C" int qkv_index_scan_topk(const float* queries, int M, int d,
@@ -288,6 +291,13 @@ extern "C" int qkv_index_scan_topk(const float* queries, int M, int d,
   if (rc) return rc;
   if (!out_scores || !out_ids) return QKV_ENULL;
   if (k < 1 || k > QKV_INDEX_MAX_K || k > N) return QKV_EARG;
+  {   // QUASHKV_B200_CUDA_CORE_SCAN=1 keeps the fp32 CUDA-core scan (for A/B checks)
+    const char* env = getenv("QUASHKV_B200_CUDA_CORE_SCAN");
+    if (!(env && env[0] == '1') && index_mma_ok(d, bits, N, k, db_codes, db_signs, db_norms))
+      return launch_index_scan_mma(queries, M, db_codes, db_signs, db_norms, N, Pi, centroids, S, qjl_scale, k,
+                                   id_base, out_scores, out_ids, workspace, workspace_bytes,
+                                   static_cast<cudaStream_t>(stream));
+  }
   const ScanPlan p = make_scan_plan(N, M, d, k);
   if (workspace_bytes < p.qk_bytes + p.ls_bytes + p.li_bytes) return QKV_EWORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);

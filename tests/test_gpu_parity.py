@@ -572,6 +572,32 @@ def test_index_medium_recall_and_ties():
     assert idx.recall_at_k(qs.to(DEV), db.to(DEV), k) > 0.3
 
 
+def test_index_tensor_core_scan_equals_cuda_core_scan(monkeypatch):
+    """The tensor-core scan only proposes candidates; scores are recomputed with the arithmetic of
+    the CUDA-core kernel, so ids and scores of the two paths must be equal bit for bit.  Ragged
+    sizes, one query, a padded query tile, and the largest k the tensor-core path takes."""
+    d = 128
+    for n, m, ks, seed in [(5003, 65, (1, 10, 48), 1), (4096, 1, (7,), 2), (300_001, 100, (10, 33), 3)]:
+        g = torch.Generator().manual_seed(seed)
+        db = torch.randn(n, d, generator=g) * (torch.rand(n, 1, generator=g) + 0.25)
+        db[3] *= 6.0 / db[3].norm()                  # a long vector and its duplicate: an exact tie at the top
+        db[n // 2] = db[3]
+        qs = torch.randn(m, d, generator=g)
+        qs[0] = db[3]
+        idx = qk.QuashIndex(d, 3, seed=42, pack_storage=True)
+        idx.add(db.to(DEV))
+        for k in ks:
+            monkeypatch.setenv("QUASHKV_B200_CUDA_CORE_SCAN", "1")
+            s0, i0 = idx.search(qs.to(DEV), k, id_base=1000)
+            monkeypatch.setenv("QUASHKV_B200_CUDA_CORE_SCAN", "0")
+            s1, i1 = idx.search(qs.to(DEV), k, id_base=1000)
+            assert torch.equal(i0, i1), f"n={n} m={m} k={k}: {(i0 != i1).sum().item()} ids differ"
+            assert torch.equal(s0, s1)
+            if k >= 2:
+                row = i1[0].cpu().tolist()
+                assert row.index(1003) < row.index(1000 + n // 2)
+
+
 # ---------------------------------------------------------------------------------------------
 # HF-style cache
 # ---------------------------------------------------------------------------------------------
