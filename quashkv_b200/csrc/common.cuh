@@ -103,6 +103,13 @@ int launch_index_scan_mma(const float* queries, int M, const uint8_t* codes, con
                           float qjl_scale, int k, int64_t id_base, float* out_scores, int64_t* out_ids,
                           void* workspace, size_t workspace_bytes, cudaStream_t st);
 
+// CUDA-core scan + merge of exactly the queries whose flag is set (index_scan.cu); `lists` needs
+// index_flagged_list_bytes().  Results of the other queries in out_scores / out_ids stay as they are.
+size_t index_flagged_list_bytes(int64_t N, int M, int k);
+int launch_scan_flagged(const float* qk, int M, int k, const uint8_t* codes, const uint8_t* signs,
+                        const float* norms, int64_t N, const float* cent, int64_t id_base, const int* flags,
+                        void* lists, float* out_scores, int64_t* out_ids, cudaStream_t st);
+
 inline int check_launch() { return cudaGetLastError() == cudaSuccess ? QKV_OK : QKV_ELAUNCH; }
 
 }  // namespace qkv

@@ -29,6 +29,7 @@ struct ScanArgs {
   int64_t id_base;
   float* list_scores; int64_t* list_ids;    // [M][n_slices*k]
   float* dense;                             // [M][N] when DENSE
+  const int* flags;                         // when set: only queries with a non-zero flag are scanned
 };
 
 struct ScanPlan { int n_slices; int64_t slice_len; int n_qtiles; size_t qk_bytes, ls_bytes, li_bytes; };
@@ -93,6 +94,11 @@ __global__ void __launch_bounds__(kScanThreads) index_scan_kernel(ScanArgs a) {
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int slice = blockIdx.x, q0 = blockIdx.y * kMQ;
+  if (a.flags) {                            // CTA-uniform: nothing to do unless one of its queries is flagged
+    bool any = false;
+    for (int q = 0; q < kMQ; ++q) any = any || (q0 + q < a.M && a.flags[q0 + q] != 0);
+    if (!any) return;
+  }
 
   for (int idx = threadIdx.x; idx < d * kMQ; idx += blockDim.x) {
     const int j = idx / kMQ, q = idx % kMQ;
@@ -199,10 +205,10 @@ __global__ void __launch_bounds__(kScanThreads) index_scan_kernel(ScanArgs a) {
 // One warp per query: the r-th output is the best candidate that ranks after output r-1.
 __global__ void topk_merge_kernel(const float* __restrict__ in_s, const int64_t* __restrict__ in_i, int M,
                                   int64_t n_cand, int k_out, float* __restrict__ out_s,
-                                  int64_t* __restrict__ out_i) {
+                                  int64_t* __restrict__ out_i, const int* __restrict__ flags) {
   const int lane = threadIdx.x & 31;
   const int m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (m >= M) return;
+  if (m >= M || (flags && flags[m] == 0)) return;
   const float* s = in_s + static_cast<int64_t>(m) * n_cand;
   const int64_t* ids = in_i + static_cast<int64_t>(m) * n_cand;
   float prev_s = INFINITY; int64_t prev_i = -1; bool have_prev = false;
@@ -267,6 +273,30 @@ static int check_scan(const float* queries, int M, int d, const uint8_t* c, cons
   if ((reinterpret_cast<uintptr_t>(c) | reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(ws)) & 3u)
     return QKV_EALIGN;
   return QKV_OK;
+}
+
+size_t index_flagged_list_bytes(int64_t N, int M, int k) {
+  const ScanPlan p = make_scan_plan(N, M, 128, k);
+  return p.ls_bytes + p.li_bytes;
+}
+
+int launch_scan_flagged(const float* qk, int M, int k, const uint8_t* codes, const uint8_t* signs,
+                        const float* norms, int64_t N, const float* cent, int64_t id_base, const int* flags,
+                        void* lists, float* out_scores, int64_t* out_ids, cudaStream_t st) {
+  const ScanPlan p = make_scan_plan(N, M, 128, k);
+  ScanArgs a{};
+  a.qk = qk; a.M = M; a.d = 128; a.k = k;
+  a.codes = reinterpret_cast<const uint32_t*>(codes); a.signs = reinterpret_cast<const uint32_t*>(signs);
+  a.norms = norms; a.N = N; a.slice_len = p.slice_len; a.n_slices = p.n_slices; a.cent = cent;
+  a.id_base = id_base; a.flags = flags;
+  a.list_scores = reinterpret_cast<float*>(lists);
+  a.list_ids = reinterpret_cast<int64_t*>(reinterpret_cast<unsigned char*>(lists) + p.ls_bytes);
+  const int rc = launch_scan<false>(a, 2, dim3(p.n_slices, p.n_qtiles), st);
+  if (rc) return rc;
+  const int warps = 4;
+  topk_merge_kernel<<<(M + warps - 1) / warps, warps * 32, 0, st>>>(
+      a.list_scores, a.list_ids, M, static_cast<int64_t>(p.n_slices) * k, k, out_scores, out_ids, flags);
+  return check_launch();
 }
 
 }  // namespace qkv
@@ -343,6 +373,6 @@ extern "C" int qkv_topk_merge(const float* in_scores, const int64_t* in_ids, int
   if (M < 1 || n_cand < 1 || k_out < 1) return QKV_EDIM;
   const int warps = 4;
   topk_merge_kernel<<<(M + warps - 1) / warps, warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      in_scores, in_ids, M, n_cand, k_out, out_scores, out_ids);
+      in_scores, in_ids, M, n_cand, k_out, out_scores, out_ids, nullptr);
   return check_launch();
 }

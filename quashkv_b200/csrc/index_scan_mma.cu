@@ -4,13 +4,21 @@
 // (query, database row) pair is a dense contraction whose one operand is decoded on the fly, so it
 // belongs on the tensor cores: database rows are the M dimension (16 per warp tile, decoded in
 // registers exactly like the keys of the decode attention), 32 queries per CTA are the N dimension
-// (their fp16 high + low parts and sign weights sit in shared memory as ready B fragments), K = 256.
-// The fp16 high/low split keeps the approximate score within ~1e-5 relative of the fp32 value.
+// (ready B fragments in shared memory: the unit-normalised rotated query in fp16 and its sign
+// weights), K = 256: 64 MMAs per tile.
 //
-// Exact top-k: the scan keeps, per query, every row whose approximate score is within a small
-// slack of the k-th best approximate score (a superset of the true top-k), the candidates are
-// re-scored with the fp32 arithmetic of the CUDA-core scan kernel, and the merge kernel picks the
-// final k by exact score (ties by lower id).
+// The fp16 scores only PROPOSE candidates; the result is exact.  With queries normalised to unit
+// length the approximate score of a row is within kEps * norm_row of its fp32 score (fp16 rounding
+// of the query, of the four centroids and of the sign weights; products and sums are fp32).  Each
+// accumulator starts at kEps - sum(w), so what the kernel compares and stores is the OPTIMISTIC
+// score u = s~ + kEps * norm.  A row can only belong to the true top-k if u >= T, where T is any
+// lower bound of the k-th best PESSIMISTIC score; the kernel uses T = (k-th best u) - 2 kEps *
+// (largest norm seen), which only ever rises.  Every warp keeps its own candidate buffers (no CTA
+// barrier in the streaming loop); T is shared between the warps of a CTA through a racy maximum.
+// The survivors are re-scored with the fp32 arithmetic of the CUDA-core scan kernel and merged by
+// exact score (ties by lower id).  A query whose candidates do not fit (more than the list holds
+// within the bound of the k-th score: many equal rows), or whose norm is zero or not finite, is
+// flagged, and the CUDA-core scan redoes exactly the flagged queries.
 #include <math.h>
 
 #include "attention_common.cuh"
@@ -20,11 +28,12 @@ namespace qkv {
 
 constexpr int kIQ = 32;                 // queries per CTA
 constexpr int kIWarps = 4;
-constexpr int kICap = 128;              // candidate slots per query in shared memory
-constexpr int kIStages = 4;
+constexpr int kIStages = 3;
 constexpr int kIStageBytes = 512 + 256 + 64;     // 16 rows: codes, signs, norms
-constexpr int kIExtra = 16;             // candidates kept beyond k per (query, slice)
-constexpr float kRelSlack = 2e-4f, kAbsSlack = 1e-6f;
+constexpr int kIExtra = 16;             // list slots beyond k per (query, slice)
+constexpr int kIRoom = 16;              // free slots a warp buffer must have before a tile (16 rows)
+constexpr float kEps = 4e-4f;           // bound of |approximate - fp32 score| / norm for a unit query
+constexpr int64_t kIMaxSlice = 65536;   // rows per slice: candidates are stored as 16-bit offsets
 
 struct ScanMmaArgs {
   const float* qk;       // [M][2][128] rotated queries (scale 1)
@@ -32,24 +41,84 @@ struct ScanMmaArgs {
   const uint8_t* codes; const uint8_t* signs; const float* norms;
   int64_t N; int64_t slice_len; int n_slices;
   const uint32_t* tables;              // key table (fp16 pairs) and 1/scale
-  int64_t id_base;
   float* list_scores; int64_t* list_ids;   // [M][n_slices][k + kIExtra]
+  int* flags;                          // [M] set to 1 for queries the CUDA-core scan must redo
 };
 
 __device__ __forceinline__ bool better(float sa, int ia, float sb, int ib) {
   return sa > sb || (sa == sb && ia < ib);
 }
 
-__global__ void __launch_bounds__(kIWarps * 32, 3) index_scan_mma_kernel(ScanMmaArgs a) {
+// Raises the shared threshold to at least t (bounded retries: the threshold is only a filter).
+__device__ __forceinline__ void raise_threshold(float* thr, float t) {
+  int* p = reinterpret_cast<int*>(thr);
+  int old = *reinterpret_cast<volatile int*>(p);
+  for (int tries = 0; tries < 8 && __int_as_float(old) < t; ++tries) {
+    const int seen = atomicCAS(p, old, __float_as_int(t));
+    if (seen == old) break;
+    old = seen;
+  }
+}
+
+// Warp-wide selection inside one candidate buffer of n <= CAPW entries (optimistic score, row).
+// Ranks every entry (higher score first, equal scores by slot), takes T = (k-th best) - slack
+// (-inf while n < k), and rewrites the buffer as the entries with score >= T in rank order.
+// Returns how many there are; only the first `limit` of them are stored.
+template <int CAPW>
+__device__ __forceinline__ int select_sorted(float* bu, uint16_t* br, int n, int k, float slack, int limit,
+                                             float& T, int lane) {
+  constexpr int ENT = (CAPW + 31) / 32;
+  float u[ENT]; int r[ENT], rank[ENT];
+#pragma unroll
+  for (int e = 0; e < ENT; ++e) {
+    const int slot = lane + 32 * e;
+    u[e] = slot < n ? bu[slot] : -INFINITY;
+    r[e] = slot < n ? br[slot] : 0;
+    rank[e] = 0;
+  }
+  for (int j = 0; j < n; ++j) {
+    const float uj = bu[j];
+#pragma unroll
+    for (int e = 0; e < ENT; ++e) rank[e] += better(uj, j, u[e], lane + 32 * e) ? 1 : 0;
+  }
+  float kth = -INFINITY;
+  if (n >= k) {
+#pragma unroll
+    for (int e = 0; e < ENT; ++e) {
+      const unsigned m = __ballot_sync(QKV_FULL_MASK, lane + 32 * e < n && rank[e] == k - 1);
+      const float v = __shfl_sync(QKV_FULL_MASK, u[e], m ? __ffs(m) - 1 : 0);
+      if (m) kth = v;
+    }
+  }
+  T = n >= k ? kth - slack : -INFINITY;
+  int kept = 0;
+  bool keep[ENT];
+#pragma unroll
+  for (int e = 0; e < ENT; ++e) {
+    keep[e] = lane + 32 * e < n && u[e] >= T;
+    kept += __popc(__ballot_sync(QKV_FULL_MASK, keep[e]));
+  }
+  __syncwarp();
+#pragma unroll
+  for (int e = 0; e < ENT; ++e)
+    if (keep[e] && rank[e] < limit) { bu[rank[e]] = u[e]; br[rank[e]] = static_cast<uint16_t>(r[e]); }
+  __syncwarp();
+  return kept;
+}
+
+template <int CAPW>
+__global__ void __launch_bounds__(kIWarps * 32, CAPW <= 32 ? 4 : (CAPW <= 48 ? 3 : 2))
+index_scan_mma_kernel(ScanMmaArgs a) {
   constexpr int D = 128;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned char* ring_s = smem_raw;                                             // per-warp staging rings
   uint2 (*bop)[kIQ / 8][32] = reinterpret_cast<uint2 (*)[kIQ / 8][32]>(ring_s + kIWarps * kIStages * kIStageBytes);
-  float (*buf_s)[kICap] = reinterpret_cast<float (*)[kICap]>(bop + 24);        // candidate scores per query
-  int (*buf_i)[kICap] = reinterpret_cast<int (*)[kICap]>(buf_s + kIQ);          // candidate rows per query
-  __shared__ float wsum[kIQ];
-  __shared__ float thr[kIQ];
-  __shared__ int cnt[kIQ];
+  float* buf_u = reinterpret_cast<float*>(bop + 16);                            // [query][warp][CAPW]
+  uint16_t* buf_r = reinterpret_cast<uint16_t*>(buf_u + kIWarps * kIQ * CAPW);  // [query][warp][CAPW]
+  __shared__ float init_c[kIQ];          // kEps - sum of the sign weights of the unit query
+  __shared__ float thr[kIQ];             // lower bound of the k-th best pessimistic score
+  __shared__ int cnt[kIWarps][kIQ];
+  __shared__ float nmax_w[kIWarps];
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gid = lane >> 2, tig = lane & 3;
@@ -57,42 +126,40 @@ __global__ void __launch_bounds__(kIWarps * 32, 3) index_scan_mma_kernel(ScanMma
   const float inv_sk = __uint_as_float(a.tables[6]);
   const uint32_t kt_a = a.tables[0], kt_b = a.tables[1];
 
-  // ---- B fragments of the 32 queries (query column n = gid of n-tile nt is query q0 + 8 nt + gid) ----
-  for (int nt = warp; nt < kIQ / 8; nt += kIWarps) {
+  // ---- B fragments: warp w builds n-tile w (query q0 + 8 w + gid; lane tig covers coordinates 32 tig..) ----
+  {
+    const int nt = warp;
     const int m = q0 + 8 * nt + gid;
     const float* q = a.qk + static_cast<int64_t>(m < a.M ? m : 0) * 2 * D;
-    const float live = m < a.M ? 1.f : 0.f;
+    float q2 = 0.f, ws = 0.f;
+    for (int j = 32 * tig; j < 32 * tig + 32; ++j) { q2 = fmaf(q[j], q[j], q2); ws += q[D + j]; }
+    q2 += __shfl_xor_sync(QKV_FULL_MASK, q2, 1); ws += __shfl_xor_sync(QKV_FULL_MASK, ws, 1);
+    q2 += __shfl_xor_sync(QKV_FULL_MASK, q2, 2); ws += __shfl_xor_sync(QKV_FULL_MASK, ws, 2);
+    const float qn = sqrtf(q2);
+    const bool usable = m < a.M && qn > 0.f && qn < INFINITY;
+    const float inv = usable ? 1.f / qn : 0.f;
 #pragma unroll
     for (int s = 0; s < 8; ++s) {
       const int word = s >> 2, grp = s & 3;
       const int c0 = 32 * tig + 16 * word + grp;
-      float v[4], r[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        v[e] = q[c0 + 4 * e] * inv_sk * live;
-        r[e] = v[e] - __half2float(__float2half_rn(v[e]));
-      }
-      bop[s][nt][lane] = make_uint2(pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
-      bop[8 + s][nt][lane] = make_uint2(pack_half2(r[0], r[1]), pack_half2(r[2], r[3]));
+      const float f = inv * inv_sk;
+      bop[s][nt][lane] = make_uint2(pack_half2(q[c0] * f, q[c0 + 4] * f), pack_half2(q[c0 + 8] * f, q[c0 + 12] * f));
       uint32_t wq[2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int t = 2 * s + h, j = 32 * tig + sign_coord(t);
-        const float f = 2.f / sign_v1(sign_pos(t)) * live;
-        wq[h] = pack_half2(q[D + j] * f, q[D + j + 16] * f);
+        const float g = 2.f / sign_v1(sign_pos(t)) * inv;
+        wq[h] = pack_half2(q[D + j] * g, q[D + j + 16] * g);
       }
-      bop[16 + s][nt][lane] = make_uint2(wq[0], wq[1]);
+      bop[8 + s][nt][lane] = make_uint2(wq[0], wq[1]);
+    }
+    if (tig == 0) {
+      init_c[8 * nt + gid] = kEps - ws * inv;
+      thr[8 * nt + gid] = usable ? -INFINITY : INFINITY;      // unusable queries collect nothing
+      if (m < a.M && !usable) a.flags[m] = 1;
     }
   }
-  if (threadIdx.x < kIQ) {
-    const int m = q0 + threadIdx.x;
-    float t = 0.f;
-    if (m < a.M)
-      for (int j = 0; j < D; ++j) t += a.qk[static_cast<int64_t>(m) * 2 * D + D + j];
-    wsum[threadIdx.x] = t;
-    thr[threadIdx.x] = m < a.M ? -INFINITY : INFINITY;     // padding queries never collect candidates
-    cnt[threadIdx.x] = 0;
-  }
+  cnt[warp][lane] = 0;
   __syncthreads();
 
   const int64_t n_begin = slice * a.slice_len;
@@ -100,8 +167,12 @@ __global__ void __launch_bounds__(kIWarps * 32, 3) index_scan_mma_kernel(ScanMma
   if (n_end > a.N) n_end = a.N;
   const int n_valid = static_cast<int>(n_end - n_begin);
   constexpr int kStep = kIWarps * 16;
-  const int n_it = (n_valid + kStep - 1) / kStep;          // CTA passes; every warp takes one tile per pass
+  const int n_it = (n_valid + kStep - 1) / kStep;          // every warp takes one 16-row tile per step
   const int first_rel = warp * 16;
+  constexpr int QS = kIWarps * CAPW;          // slots per query; this warp's CAPW start at warp * CAPW
+  float* my_u = buf_u + warp * CAPW;
+  uint16_t* my_r = buf_r + warp * CAPW;
+  float my_nmax = 0.f;
 
   // ---- cp.async ring: 52 chunks of 16 bytes per tile (32 code, 16 sign, 4 norm) ------------------------
   unsigned char* ring = ring_s + warp * (kIStages * kIStageBytes);
@@ -134,7 +205,7 @@ __global__ void __launch_bounds__(kIWarps * 32, 3) index_scan_mma_kernel(ScanMma
           const int left = n_valid - (rel + tok_off[k]);            // rows of this chunk inside the slice
           const bool ok = left > 0;
           const int bytes = (lane + 32 * k < 48 || left >= 4) ? 16 : 4 * left;   // a norm chunk holds 4 rows
-          cp_async16(stage + dst_off[k], ok ? src0[k] + static_cast<int64_t>(it) * stride[k] : src0[k],
+          cp_async16(stage + dst_off[k], ok ? src0[k] + static_cast<int64_t>(it) * stride[k] : a.codes,
                      ok ? bytes : 0);
         }
       }
@@ -157,12 +228,35 @@ __global__ void __launch_bounds__(kIWarps * 32, 3) index_scan_mma_kernel(ScanMma
       kn[h] = *reinterpret_cast<const float*>(stage + 768 + (gid + 8 * h) * 4);
     }
     __syncwarp();
+    my_nmax = fmaxf(my_nmax, fmaxf(kn[0], kn[1]));
 
     float c[kIQ / 8][4];
 #pragma unroll
     for (int nt = 0; nt < kIQ / 8; ++nt) {
-      c[nt][0] = c[nt][2] = -wsum[8 * nt + 2 * tig];
-      c[nt][1] = c[nt][3] = -wsum[8 * nt + 2 * tig + 1];
+      const float2 i2 = *reinterpret_cast<const float2*>(&init_c[8 * nt + 2 * tig]);
+      c[nt][0] = c[nt][2] = i2.x;
+      c[nt][1] = c[nt][3] = i2.y;
+    }
+    {   // sign part first: its operands need no table look-up
+      const uint32_t cp0[4] = {ks[0], ks[0] << 7, ks[0] >> 1, ks[0] << 13};
+      const uint32_t cp1[4] = {ks[1], ks[1] << 7, ks[1] >> 1, ks[1] << 13};
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        uint32_t af[4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int t = 2 * s + h;
+          const int cpy = t < 7 ? 0 : (t < 14 ? 1 : t - 12);
+          const uint32_t mask = 0x00010001u << sign_pos(t);
+          af[2 * h] = cp0[cpy] & mask;
+          af[2 * h + 1] = cp1[cpy] & mask;
+        }
+#pragma unroll
+        for (int nt = 0; nt < kIQ / 8; ++nt) {
+          const uint2 bw = bop[8 + s][nt][lane];
+          mma16816(c[nt], af, bw.x, bw.y);
+        }
+      }
     }
 #pragma unroll
     for (int word = 0; word < 2; ++word) {
@@ -179,127 +273,109 @@ __global__ void __launch_bounds__(kIWarps * 32, 3) index_scan_mma_kernel(ScanMma
         af[3] = prmt(kt_a, kt_b, sh1);
 #pragma unroll
         for (int nt = 0; nt < kIQ / 8; ++nt) {
-          const uint2 bh = bop[word * 4 + grp][nt][lane], bl = bop[8 + word * 4 + grp][nt][lane];
-          mma16816(c[nt], af, bl.x, bl.y);
+          const uint2 bh = bop[word * 4 + grp][nt][lane];
           mma16816(c[nt], af, bh.x, bh.y);
         }
       }
     }
-    {
-      const uint32_t cp0[4] = {ks[0], ks[0] << 7, ks[0] >> 1, ks[0] << 13};
-      const uint32_t cp1[4] = {ks[1], ks[1] << 7, ks[1] >> 1, ks[1] << 13};
-#pragma unroll
-      for (int s = 0; s < 8; ++s) {
-        uint32_t af[4];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int t = 2 * s + h;
-          const int cpy = t < 7 ? 0 : (t < 14 ? 1 : t - 12);
-          const uint32_t mask = 0x00010001u << sign_pos(t);
-          af[2 * h] = cp0[cpy] & mask;
-          af[2 * h + 1] = cp1[cpy] & mask;
-        }
-#pragma unroll
-        for (int nt = 0; nt < kIQ / 8; ++nt) {
-          const uint2 bw = bop[16 + s][nt][lane];
-          mma16816(c[nt], af, bw.x, bw.y);
-        }
-      }
-    }
-    // ---- candidates: approximate score above the query's running threshold ------------------------------
+    // ---- candidates: optimistic score at or above the query's threshold ---------------------------------
     const int rel = first_rel + it * kStep;
 #pragma unroll
     for (int nt = 0; nt < kIQ / 8; ++nt) {
+      const float2 t2 = *reinterpret_cast<const float2*>(&thr[8 * nt + 2 * tig]);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int q = 8 * nt + 2 * tig + (e & 1), r = rel + gid + 8 * (e >> 1);
-        const float sc = c[nt][e] * kn[e >> 1];
-        if (r < n_valid && sc >= thr[q]) {
-          const int pos = atomicAdd(&cnt[q], 1);
-          if (pos < kICap) { buf_s[q][pos] = sc; buf_i[q][pos] = r; }
+        const float u = c[nt][e] * kn[e >> 1];
+        if (u >= ((e & 1) ? t2.y : t2.x) && r < n_valid) {
+          const int pos = atomicAdd(&cnt[warp][q], 1);
+          if (pos < CAPW) { my_u[q * QS + pos] = u; my_r[q * QS + pos] = static_cast<uint16_t>(r); }
         }
       }
     }
-    // ---- prune the buffers that could overflow on the next pass --------------------------------------------
-    __syncthreads();                               // every warp's pushes of this pass are in
-    const bool need = __syncthreads_or(threadIdx.x < kIQ && cnt[threadIdx.x] > kICap - kStep);
+    __syncwarp();
+    // ---- shrink the buffers that could overflow on the next tile ------------------------------------------
+    unsigned need = __ballot_sync(QKV_FULL_MASK, cnt[warp][lane] > CAPW - kIRoom);
     if (need) {
-      for (int q = warp; q < kIQ; q += kIWarps) {
-        int n = cnt[q] < kICap ? cnt[q] : kICap;
-        if (n <= kICap - kStep) continue;
-        // k-th best approximate score (k selections), then keep everything within the slack of it
-        float kth = -INFINITY;
-        const int kk = n < a.k ? n : a.k;
-        float prev_s = INFINITY; int prev_i = -1;
-        for (int sel = 0; sel < kk; ++sel) {
-          float bs = -INFINITY; int bi = 0x7fffffff;
-          for (int p = lane; p < n; p += 32) {
-            const float s = buf_s[q][p]; const int id = buf_i[q][p];
-            if ((sel == 0 || better(prev_s, prev_i, s, id)) && better(s, id, bs, bi)) { bs = s; bi = id; }
-          }
+      float nm = my_nmax;
 #pragma unroll
-          for (int o = 16; o > 0; o >>= 1) {
-            const float s2 = __shfl_xor_sync(QKV_FULL_MASK, bs, o);
-            const int i2 = __shfl_xor_sync(QKV_FULL_MASK, bi, o);
-            if (better(s2, i2, bs, bi)) { bs = s2; bi = i2; }
-          }
-          prev_s = bs; prev_i = bi; kth = bs;
-        }
-        const float cut = (n >= a.k) ? kth - (kRelSlack * fabsf(kth) + kAbsSlack) : -INFINITY;
-        int kept = 0;
-        for (int p0 = 0; p0 < n; p0 += 32) {          // stable compaction
-          const int p = p0 + lane;
-          const float s = p < n ? buf_s[q][p] : -INFINITY;
-          const int id = p < n ? buf_i[q][p] : -1;
-          const bool keep = p < n && s >= cut;
-          const unsigned m = __ballot_sync(QKV_FULL_MASK, keep);
-          __syncwarp();
-          if (keep) {
-            const int dst = kept + __popc(m & ((1u << lane) - 1u));
-            if (dst < kICap - kStep) { buf_s[q][dst] = s; buf_i[q][dst] = id; }
-          }
-          kept += __popc(m);
-          __syncwarp();
-        }
+      for (int o = 16; o > 0; o >>= 1) nm = fmaxf(nm, __shfl_xor_sync(QKV_FULL_MASK, nm, o));
+      while (need) {
+        const int q = __ffs(need) - 1;
+        need &= need - 1;
+        const int n = cnt[warp][q] < CAPW ? cnt[warp][q] : CAPW;
+        float T;
+        const int kept = select_sorted<CAPW>(my_u + q * QS, my_r + q * QS, n, a.k, 2.f * kEps * nm,
+                                             CAPW - kIRoom, T, lane);
         if (lane == 0) {
-          cnt[q] = kept < kICap - kStep ? kept : kICap - kStep;
-          thr[q] = cut;
+          if (kept > CAPW - kIRoom) {             // more rows within the bound than a buffer holds
+            if (q0 + q < a.M) a.flags[q0 + q] = 1;
+            thr[q] = INFINITY;
+            cnt[warp][q] = 0;
+          } else {
+            cnt[warp][q] = kept;
+            raise_threshold(&thr[q], T);
+          }
         }
       }
+      __syncwarp();
     }
-    __syncthreads();
   }
   cp_async_wait<0>();
+  {
+    float nm = my_nmax;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) nm = fmaxf(nm, __shfl_xor_sync(QKV_FULL_MASK, nm, o));
+    if (lane == 0) nmax_w[warp] = nm;
+  }
+  __syncthreads();
 
-  // ---- per (query, slice): the k + kIExtra best approximate candidates ---------------------------------------
+  // ---- per (query, slice): union of the four warps' candidates, bounded once more, to the list -------------
+  constexpr int ENT = (CAPW + 31) / 32;
   const int out_k = a.k + kIExtra;
+  const float nm_cta = fmaxf(fmaxf(nmax_w[0], nmax_w[1]), fmaxf(nmax_w[2], nmax_w[3]));
   for (int q = warp; q < kIQ; q += kIWarps) {
     if (q0 + q >= a.M) continue;
-    const int n = cnt[q] < kICap ? cnt[q] : kICap;
     const int64_t o = (static_cast<int64_t>(q0 + q) * a.n_slices + slice) * out_k;
-    float prev_s = INFINITY; int prev_i = -1;
-    for (int sel = 0; sel < out_k; ++sel) {
-      float bs = -INFINITY; int bi = 0x7fffffff;
-      for (int p = lane; p < n; p += 32) {
-        const float s = buf_s[q][p]; const int id = buf_i[q][p];
-        if ((sel == 0 || better(prev_s, prev_i, s, id)) && better(s, id, bs, bi)) { bs = s; bi = id; }
-      }
+    const float T0 = thr[q];
+    float u[kIWarps][ENT]; int r[kIWarps][ENT]; bool live[kIWarps][ENT];
 #pragma unroll
-      for (int o2 = 16; o2 > 0; o2 >>= 1) {
-        const float s2 = __shfl_xor_sync(QKV_FULL_MASK, bs, o2);
-        const int i2 = __shfl_xor_sync(QKV_FULL_MASK, bi, o2);
-        if (better(s2, i2, bs, bi)) { bs = s2; bi = i2; }
+    for (int w = 0; w < kIWarps; ++w) {
+      const int n_w = cnt[w][q] < CAPW ? cnt[w][q] : CAPW;
+#pragma unroll
+      for (int e = 0; e < ENT; ++e) {
+        const int slot = lane + 32 * e;
+        u[w][e] = slot < n_w ? buf_u[q * QS + w * CAPW + slot] : -INFINITY;
+        r[w][e] = slot < n_w ? buf_r[q * QS + w * CAPW + slot] : 0;
+        live[w][e] = slot < n_w && u[w][e] >= T0;
       }
-      const bool have = bi != 0x7fffffff;
-      if (lane == 0) {
-        a.list_scores[o + sel] = have ? bs : -INFINITY;
-        a.list_ids[o + sel] = have ? n_begin + bi : -1;       // row index inside the index (id_base added later)
+    }
+    __syncwarp();
+    int total = 0;
+    float* bu = buf_u + q * QS;                // the query's four buffers, as one, now hold the union
+    uint16_t* br = buf_r + q * QS;
+#pragma unroll
+    for (int w = 0; w < kIWarps; ++w) {
+#pragma unroll
+      for (int e = 0; e < ENT; ++e) {
+        const unsigned m = __ballot_sync(QKV_FULL_MASK, live[w][e]);
+        const int dst = total + __popc(m & ((1u << lane) - 1u));
+        if (live[w][e]) { bu[dst] = u[w][e]; br[dst] = static_cast<uint16_t>(r[w][e]); }
+        total += __popc(m);
       }
-      prev_s = bs; prev_i = bi;
-      if (!have) {
-        for (int s2 = sel + 1 + lane; s2 < out_k; s2 += 32) { a.list_scores[o + s2] = -INFINITY; a.list_ids[o + s2] = -1; }
-        break;
-      }
+    }
+    __syncwarp();
+    bool redo = T0 == INFINITY;
+    int kept = 0;
+    if (!redo) {
+      float T;
+      kept = select_sorted<QS>(bu, br, total, a.k, 2.f * kEps * nm_cta, out_k, T, lane);
+      redo = kept > out_k;
+    }
+    if (redo) { kept = 0; if (lane == 0) a.flags[q0 + q] = 1; }
+    for (int s = lane; s < out_k; s += 32) {
+      a.list_scores[o + s] = s < kept ? bu[s] : -INFINITY;
+      a.list_ids[o + s] = s < kept ? n_begin + br[s] : -1;       // row inside the index; the re-scoring adds id_base
     }
   }
 }
@@ -332,17 +408,33 @@ __global__ void index_rescore_kernel(const float* __restrict__ qk, int64_t n_ent
   ids[e] = n + id_base;
 }
 
-constexpr size_t kScanMmaSmem = kIWarps * kIStages * kIStageBytes + 24 * (kIQ / 8) * 32 * 8 + 2 * kIQ * kICap * 4;
+template <int CAPW>
+constexpr size_t scan_mma_smem() {
+  return kIWarps * kIStages * kIStageBytes + 16 * (kIQ / 8) * 32 * 8 + static_cast<size_t>(kIWarps) * kIQ * CAPW * 6;
+}
 
-struct ScanMmaPlan { int n_slices; int64_t slice_len; int n_qtiles; size_t hdr_bytes, qk_bytes, ls_bytes, li_bytes; };
+// Buffer size by k: a warp buffer keeps at most CAPW - kIRoom rows between tiles, and the list of a
+// (query, slice) holds k + kIExtra rows, which must fit one buffer.
+static int capw_for(int k) { return k <= 12 ? 32 : (k <= 28 ? 48 : 80); }
+constexpr int kIMaxK = 48;
+
+struct ScanMmaPlan {
+  int n_slices; int64_t slice_len; int n_qtiles;
+  size_t hdr_bytes, flag_bytes, qk_bytes, ls_bytes, li_bytes, fallback_bytes;
+  size_t total() const { return hdr_bytes + flag_bytes + qk_bytes + ls_bytes + li_bytes + fallback_bytes; }
+};
 
 static ScanMmaPlan make_mma_plan(int64_t N, int M, int k) {
   ScanMmaPlan p;
   p.n_qtiles = (M + kIQ - 1) / kIQ;
-  int64_t want = (3 * kNumSMs * 2 + p.n_qtiles - 1) / p.n_qtiles;      // ~2 waves of 3 CTAs per SM
+  const int capw = capw_for(k);
+  const int ctas_per_sm = capw <= 32 ? 4 : (capw <= 48 ? 3 : 2);
+  int64_t want = (ctas_per_sm * kNumSMs * 2 + p.n_qtiles - 1) / p.n_qtiles;      // about two waves
   const int64_t chunk = 256;
   const int64_t max_by_len = (N + 8 * chunk - 1) / (8 * chunk);
+  const int64_t min_by_len = (N + kIMaxSlice - 1) / kIMaxSlice;
   if (want > max_by_len) want = max_by_len;
+  if (want < min_by_len) want = min_by_len;
   if (want < 1) want = 1;
   int64_t len = (N + want - 1) / want;
   len = (len + chunk - 1) / chunk * chunk;
@@ -350,51 +442,70 @@ static ScanMmaPlan make_mma_plan(int64_t N, int M, int k) {
   p.n_slices = static_cast<int>((N + len - 1) / len);
   const size_t per = static_cast<size_t>(M) * p.n_slices * (k + kIExtra);
   p.hdr_bytes = 256;
+  p.flag_bytes = (static_cast<size_t>(M) * sizeof(int) + 255) / 256 * 256;
   p.qk_bytes = (static_cast<size_t>(M) * 256 * sizeof(float) + 255) / 256 * 256;
   p.ls_bytes = (per * sizeof(float) + 255) / 256 * 256;
-  p.li_bytes = per * sizeof(int64_t);
+  p.li_bytes = (per * sizeof(int64_t) + 255) / 256 * 256;
+  p.fallback_bytes = index_flagged_list_bytes(N, M, k);
   return p;
 }
 
 bool index_mma_ok(int d, int bits, int64_t N, int k, const void* codes, const void* signs, const void* norms) {
   const uintptr_t al = reinterpret_cast<uintptr_t>(codes) | reinterpret_cast<uintptr_t>(signs) |
                        reinterpret_cast<uintptr_t>(norms);
-  return d == 128 && bits == 3 && N >= 4096 && k + kIExtra <= kICap - kIWarps * 16 && (al & 15u) == 0;
+  return d == 128 && bits == 3 && N >= 4096 && k <= kIMaxK && (al & 15u) == 0;
 }
 
 size_t index_mma_workspace_bytes(int64_t N, int M, int k) {
-  const ScanMmaPlan p = make_mma_plan(N, M, k);
-  return p.hdr_bytes + p.qk_bytes + p.ls_bytes + p.li_bytes;
+  return make_mma_plan(N, M, k < kIMaxK ? k : kIMaxK).total();
 }
 
-// Prepares look-up tables in the workspace header, rotates the queries, scans, re-scores, merges.
+template <int CAPW>
+static int launch_scan_mma(const ScanMmaArgs& a, dim3 grid, cudaStream_t st) {
+  if (cudaFuncSetAttribute(index_scan_mma_kernel<CAPW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(scan_mma_smem<CAPW>())) != cudaSuccess)
+    return QKV_ELAUNCH;
+  index_scan_mma_kernel<CAPW><<<grid, kIWarps * 32, scan_mma_smem<CAPW>(), st>>>(a);
+  return QKV_OK;
+}
+
+// Look-up tables into the workspace header, rotate the queries, scan on the tensor cores, re-score
+// the candidates, merge; then the CUDA-core scan and a second merge for the flagged queries only.
 int launch_index_scan_mma(const float* queries, int M, const uint8_t* codes, const uint8_t* signs,
                           const float* norms, int64_t N, const float* Pi, const float* cent, const float* S,
                           float qjl_scale, int k, int64_t id_base, float* out_scores, int64_t* out_ids,
                           void* workspace, size_t workspace_bytes, cudaStream_t st) {
   const ScanMmaPlan p = make_mma_plan(N, M, k);
-  if (workspace_bytes < p.hdr_bytes + p.qk_bytes + p.ls_bytes + p.li_bytes) return QKV_EWORKSPACE;
+  if (workspace_bytes < p.total()) return QKV_EWORKSPACE;
   unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
   uint32_t* tables = reinterpret_cast<uint32_t*>(ws);
-  float* qk = reinterpret_cast<float*>(ws + p.hdr_bytes);
+  int* flags = reinterpret_cast<int*>(ws + p.hdr_bytes);
+  float* qk = reinterpret_cast<float*>(ws + p.hdr_bytes + p.flag_bytes);
+  unsigned char* lists = ws + p.hdr_bytes + p.flag_bytes + p.qk_bytes;
+  if (cudaMemsetAsync(flags, 0, static_cast<size_t>(M) * sizeof(int), st) != cudaSuccess) return QKV_ELAUNCH;
   int rc = launch_rotate_with_tables(queries, QKV_F32, M, 128, Pi, S, qjl_scale, 1.f, qk, cent, cent, tables, st);
   if (rc) return rc;
   ScanMmaArgs a{};
   a.qk = qk; a.M = M; a.k = k; a.codes = codes; a.signs = signs; a.norms = norms; a.N = N;
-  a.slice_len = p.slice_len; a.n_slices = p.n_slices; a.tables = tables; a.id_base = id_base;
-  a.list_scores = reinterpret_cast<float*>(ws + p.hdr_bytes + p.qk_bytes);
-  a.list_ids = reinterpret_cast<int64_t*>(ws + p.hdr_bytes + p.qk_bytes + p.ls_bytes);
-  if (cudaFuncSetAttribute(index_scan_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(kScanMmaSmem)) != cudaSuccess)
-    return QKV_ELAUNCH;
-  index_scan_mma_kernel<<<dim3(p.n_slices, p.n_qtiles), kIWarps * 32, kScanMmaSmem, st>>>(a);
+  a.slice_len = p.slice_len; a.n_slices = p.n_slices; a.tables = tables; a.flags = flags;
+  a.list_scores = reinterpret_cast<float*>(lists);
+  a.list_ids = reinterpret_cast<int64_t*>(lists + p.ls_bytes);
+  const dim3 grid(p.n_slices, p.n_qtiles);
+  switch (capw_for(k)) {
+    case 32: rc = launch_scan_mma<32>(a, grid, st); break;
+    case 48: rc = launch_scan_mma<48>(a, grid, st); break;
+    default: rc = launch_scan_mma<80>(a, grid, st); break;
+  }
+  if (rc) return rc;
   const int per_query = p.n_slices * (k + kIExtra);
   const int64_t entries = static_cast<int64_t>(M) * per_query;
   index_rescore_kernel<<<static_cast<unsigned>((entries + 255) / 256), 256, 0, st>>>(
       qk, entries, per_query, reinterpret_cast<const uint32_t*>(codes), reinterpret_cast<const uint32_t*>(signs),
       norms, cent, id_base, a.list_scores, a.list_ids);
   if ((rc = check_launch())) return rc;
-  return qkv_topk_merge(a.list_scores, a.list_ids, M, per_query, k, out_scores, out_ids, st);
+  if ((rc = qkv_topk_merge(a.list_scores, a.list_ids, M, per_query, k, out_scores, out_ids, st))) return rc;
+  return launch_scan_flagged(qk, M, k, codes, signs, norms, N, cent, id_base, flags,
+                             lists + p.ls_bytes + p.li_bytes, out_scores, out_ids, st);
 }
 
 }  // namespace qkv

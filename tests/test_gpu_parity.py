@@ -572,30 +572,65 @@ def test_index_medium_recall_and_ties():
     assert idx.recall_at_k(qs.to(DEV), db.to(DEV), k) > 0.3
 
 
+def _both_scans(monkeypatch, idx, qs, k, id_base=1000):
+    monkeypatch.setenv("QUASHKV_B200_CUDA_CORE_SCAN", "1")
+    s0, i0 = idx.search(qs, k, id_base=id_base)
+    monkeypatch.setenv("QUASHKV_B200_CUDA_CORE_SCAN", "0")
+    s1, i1 = idx.search(qs, k, id_base=id_base)
+    return s0, i0, s1, i1
+
+
 def test_index_tensor_core_scan_equals_cuda_core_scan(monkeypatch):
     """The tensor-core scan only proposes candidates; scores are recomputed with the arithmetic of
     the CUDA-core kernel, so ids and scores of the two paths must be equal bit for bit.  Ragged
-    sizes, one query, a padded query tile, and the largest k the tensor-core path takes."""
+    sizes, one query, a padded query tile, every buffer size of the tensor-core kernel (k <= 12,
+    <= 28, <= 48), and tiny / huge query norms."""
     d = 128
-    for n, m, ks, seed in [(5003, 65, (1, 10, 48), 1), (4096, 1, (7,), 2), (300_001, 100, (10, 33), 3)]:
+    for n, m, ks, seed in [(5003, 65, (1, 10, 12, 13, 28, 29, 48), 1), (4096, 1, (7,), 2),
+                           (300_001, 100, (10, 33), 3)]:
         g = torch.Generator().manual_seed(seed)
         db = torch.randn(n, d, generator=g) * (torch.rand(n, 1, generator=g) + 0.25)
         db[3] *= 6.0 / db[3].norm()                  # a long vector and its duplicate: an exact tie at the top
         db[n // 2] = db[3]
         qs = torch.randn(m, d, generator=g)
         qs[0] = db[3]
+        if m > 4:
+            qs[1] *= 1e-6
+            qs[2] *= 1e5
         idx = qk.QuashIndex(d, 3, seed=42, pack_storage=True)
         idx.add(db.to(DEV))
         for k in ks:
-            monkeypatch.setenv("QUASHKV_B200_CUDA_CORE_SCAN", "1")
-            s0, i0 = idx.search(qs.to(DEV), k, id_base=1000)
-            monkeypatch.setenv("QUASHKV_B200_CUDA_CORE_SCAN", "0")
-            s1, i1 = idx.search(qs.to(DEV), k, id_base=1000)
+            s0, i0, s1, i1 = _both_scans(monkeypatch, idx, qs.to(DEV), k)
             assert torch.equal(i0, i1), f"n={n} m={m} k={k}: {(i0 != i1).sum().item()} ids differ"
             assert torch.equal(s0, s1)
             if k >= 2:
                 row = i1[0].cpu().tolist()
                 assert row.index(1003) < row.index(1000 + n // 2)
+
+
+def test_index_tensor_core_scan_falls_back_on_crowded_scores(monkeypatch):
+    """Thousands of equal rows put more candidates within the error bound of the k-th score than
+    the tensor-core kernel keeps, and a zero query has no direction to normalise: both are redone
+    by the CUDA-core scan, so the result (lowest ids among equal scores) is still the same; rows in
+    ascending score order (every row a new best) exercise the steady pruning."""
+    d, n, k = 128, 20_000, 10
+    g = torch.Generator().manual_seed(11)
+    db = torch.randn(1, d, generator=g).repeat(n, 1)
+    db[100:200] = torch.randn(100, d, generator=g)
+    qs = torch.randn(40, d, generator=g)
+    qs[5] = 0.0
+    idx = qk.QuashIndex(d, 3, seed=42, pack_storage=True)
+    idx.add(db.to(DEV))
+    s0, i0, s1, i1 = _both_scans(monkeypatch, idx, qs.to(DEV), k, id_base=0)
+    assert torch.equal(i0, i1) and torch.equal(s0, s1)
+    assert i1[5].cpu().tolist() == list(range(k))          # all scores are 0: lowest ids
+    base = torch.randn(1, d, generator=g)
+    db2 = base * torch.linspace(0.5, 2.0, n).unsqueeze(1)   # same direction, growing norm
+    idx2 = qk.QuashIndex(d, 3, seed=42, pack_storage=True)
+    idx2.add(db2.to(DEV))
+    qs2 = torch.cat([base, -base, torch.randn(30, d, generator=g)])
+    s0, i0, s1, i1 = _both_scans(monkeypatch, idx2, qs2.to(DEV), k, id_base=0)
+    assert torch.equal(i0, i1) and torch.equal(s0, s1)
 
 
 # ---------------------------------------------------------------------------------------------
