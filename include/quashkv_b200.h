@@ -219,6 +219,12 @@ int qkv_index_scores(const float* queries, int M, int d,
 int qkv_topk_merge(const float* in_scores, const int64_t* in_ids, int M, int64_t n_cand,
                    int k_out, float* out_scores, int64_t* out_ids, void* stream);
 
+/* Diagnostics, no reference counterpart: how many bounded waits on the tcgen05 tensor core ran out
+ * on the current device since the library was loaded (a CTA that meets one finishes its work with
+ * the fp32 CUDA-core arithmetic, so results stay correct).  0 in a healthy run.  Synchronises the
+ * device. */
+int64_t qkv_tensor_core_timeouts(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -51,6 +51,7 @@ SIGNATURES = {
                                  _vp, _sz, _vp]),
     "qkv_index_scores": (_i, [_vp, _i, _i, _vp, _vp, _vp, _i64, _i, _vp, _vp, _vp, _f, _vp, _vp, _sz, _vp]),
     "qkv_topk_merge": (_i, [_vp, _vp, _i, _i64, _i, _vp, _vp, _vp]),
+    "qkv_tensor_core_timeouts": (_i64, []),
 }
 
 _LIB = None

@@ -1,0 +1,91 @@
+// Pieces shared by the tensor-core rotation kernels (mma.sync and tcgen05): the exact three-way
+// bf16 split, the bucket-table classification of a rotated coordinate, and the fp32 FMA chain that
+// re-derives the few coordinates lying within kRecheckEps of a decision boundary.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "rotate_common.cuh"
+
+namespace qkv {
+
+constexpr int kRD = 128;                    // dimension handled by the tensor-core rotation
+constexpr float kRecheckEps = 1e-5f;
+constexpr int kLutSize = 16384;
+constexpr int kQueueCap = 128;
+
+// x = h + m + l exactly, each term a bf16 (round-to-nearest at every step).
+__device__ __forceinline__ void split3(float x, __nv_bfloat16& h, __nv_bfloat16& m, __nv_bfloat16& l) {
+  h = __float2bfloat16_rn(x);
+  const float r1 = x - __bfloat162float(h);
+  m = __float2bfloat16_rn(r1);
+  l = __float2bfloat16_rn(r1 - __bfloat162float(m));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(__nv_bfloat16 lo, __nv_bfloat16 hi) {
+  return static_cast<uint32_t>(__bfloat16_as_ushort(lo)) | (static_cast<uint32_t>(__bfloat16_as_ushort(hi)) << 16);
+}
+
+__device__ __forceinline__ int bucket_of(float y) {
+  return __float_as_int(fmaf(y, 4096.f, 4096.f + 8388608.f)) & (kLutSize - 1);
+}
+
+template <int BITS>
+__device__ __forceinline__ uint32_t count_bounds(const float* bnd, float y) {
+  uint32_t c = 0;
+#pragma unroll
+  for (int b = 0; b < (1 << BITS) - 1; ++b) c += y > bnd[b] ? 1u : 0u;
+  return c;
+}
+
+// Bucket table: entry k covers y in [(k - 4096.5) / 4096, (k - 4095.5) / 4096); value = code of the
+// bucket's centre, | 0x80 when a boundary (or, for the sign bit, a centroid) could lie inside.
+template <int BITS, bool IP>
+__device__ __forceinline__ void build_bucket_lut(uint8_t* lut, const float* bnd, const float* cent) {
+  constexpr int NB = (1 << BITS) - 1;
+  for (int k = threadIdx.x; k < kLutSize; k += blockDim.x) {
+    uint8_t v = 0x80;
+    if (k <= 8192) {
+      const float lo = (static_cast<float>(k) - 4096.5f) * (1.f / 4096.f);
+      const float hi = (static_cast<float>(k) - 4095.5f) * (1.f / 4096.f);
+      const float margin = kRecheckEps + 2e-6f;
+      bool amb = false;
+      for (int b = 0; b < NB; ++b) amb |= (bnd[b] >= lo - margin && bnd[b] <= hi + margin);
+      if (IP)
+        for (int c = 0; c <= NB; ++c) amb |= (cent[c] >= lo - margin && cent[c] <= hi + margin);
+      const float mid = (static_cast<float>(k) - 4096.f) * (1.f / 4096.f);
+      v = static_cast<uint8_t>(count_bounds<BITS>(bnd, mid) | (amb ? 0x80u : 0u));
+    }
+    lut[k] = v;
+  }
+}
+
+// Rare path of the classification, kept out of line so that the inlined call sites stay small (an
+// unrolled epilogue otherwise outgrows the instruction cache).  Returns code | sign << 8 | near << 16.
+static __device__ __noinline__ uint32_t classify_slow(const float* bnd, const float* cent, float s_col, float y,
+                                                      int nb, int ip) {
+  uint32_t code = 0;
+  bool near = !(fabsf(y) <= 1.5f);
+  for (int b = 0; b < nb; ++b) {
+    code += y > bnd[b] ? 1u : 0u;
+    near |= fabsf(y - bnd[b]) < kRecheckEps;
+  }
+  uint32_t sign = 0;
+  if (ip) {
+    const float resid = y - cent[code];
+    sign = (resid * s_col >= 0.f) ? 1u : 0u;
+    near |= fabsf(resid) < kRecheckEps;
+  }
+  return code | (sign << 8) | (near ? 1u << 16 : 0u);
+}
+
+// x_unit . Pi[col] with the CUDA-core kernel's arithmetic: x/norm, fp32 FMA over ascending coordinate.
+static __device__ __noinline__ float exact_chain(const CompressArgs& a, int64_t n, int col, float norm) {
+  const float* prow = a.Pi + col * kRD;
+  float z = 0.f;
+#pragma unroll 8
+  for (int j = 0; j < kRD; ++j) z = fmaf(load_float(a.x, a.x_dtype, n * a.x_pitch + j) / norm, __ldg(prow + j), z);
+  return z;
+}
+
+}  // namespace qkv

@@ -16,35 +16,19 @@
 // CTA = 8 warps = 4 groups of 32 vectors x 2 halves of the 128 output coordinates; Pi's three bf16
 // planes (padded, 104 KB) stay in shared memory for the CTA's lifetime; a 128-vector tile of
 // x_unit (fp32, 70 KB) is staged per iteration.
-#include <cuda_bf16.h>
-
-#include "rotate_common.cuh"
+#include "rotate_exact.cuh"
 
 namespace qkv {
 
-constexpr int kRD = 128;                    // dimension handled here
 constexpr int kRTile = 128;                 // vectors per CTA tile
 constexpr int kPiStride = kRD + 8;          // bf16 elements per padded Pi row (conflict-free B loads)
 constexpr int kXStride = kRD + 8;           // fp32 elements per padded x row (conflict-free A loads)
-constexpr float kRecheckEps = 1e-5f;
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-// x = h + m + l exactly, each term a bf16 (round-to-nearest at every step).
-__device__ __forceinline__ void split3(float x, __nv_bfloat16& h, __nv_bfloat16& m, __nv_bfloat16& l) {
-  h = __float2bfloat16_rn(x);
-  const float r1 = x - __bfloat162float(h);
-  m = __float2bfloat16_rn(r1);
-  l = __float2bfloat16_rn(r1 - __bfloat162float(m));
-}
-
-__device__ __forceinline__ uint32_t pack_bf16(__nv_bfloat16 lo, __nv_bfloat16 hi) {
-  return static_cast<uint32_t>(__bfloat16_as_ushort(lo)) | (static_cast<uint32_t>(__bfloat16_as_ushort(hi)) << 16);
 }
 
 struct RotSmem {
@@ -147,8 +131,6 @@ __device__ __forceinline__ void rotate_tile(const RotSmem& s, int row0, int col0
 // packs the codes of its quad with two shuffles per word and stores whole words.  Elements that are
 // really within kRecheckEps of a boundary go to a per-warp queue and are recomputed 32 at a time (one
 // per lane) with the fp32 FMA chain; a changed code is patched into the packed row with atomicXor.
-constexpr int kLutSize = 16384;
-constexpr int kQueueCap = 128;
 
 struct CompSmem {
   __nv_bfloat16* pi[3];
@@ -179,18 +161,6 @@ constexpr size_t comp_smem_bytes() {
   return 3 * kRD * kPiStride * 2 + WARPS * kQueueCap * 16 + kLutSize + (16 + 16 + kRD) * 4 + WARPS * 4;
 }
 
-__device__ __forceinline__ int bucket_of(float y) {
-  return __float_as_int(fmaf(y, 4096.f, 4096.f + 8388608.f)) & (kLutSize - 1);
-}
-
-template <int BITS>
-__device__ __forceinline__ uint32_t count_bounds(const float* bnd, float y) {
-  uint32_t c = 0;
-#pragma unroll
-  for (int b = 0; b < (1 << BITS) - 1; ++b) c += y > bnd[b] ? 1u : 0u;
-  return c;
-}
-
 // OR-combine the quad's partial words and store them: lane tig writes words tig, tig+4, ...
 template <int NW>
 __device__ __forceinline__ void quad_store(uint32_t (&W)[NW], uint32_t* dst, int tig, bool live) {
@@ -202,34 +172,6 @@ __device__ __forceinline__ void quad_store(uint32_t (&W)[NW], uint32_t* dst, int
 #pragma unroll
   for (int w = 0; w < NW; ++w)
     if (live && (w & 3) == tig) dst[w] = W[w];
-}
-
-// Rare path of the classification, kept out of line so that the 64 inlined call sites stay small (the
-// unrolled epilogue otherwise outgrows the instruction cache).  Returns code | sign << 8 | near << 16.
-__device__ __noinline__ uint32_t classify_slow(const float* bnd, const float* cent, float s_col, float y, int nb,
-                                               int ip) {
-  uint32_t code = 0;
-  bool near = !(fabsf(y) <= 1.5f);
-  for (int b = 0; b < nb; ++b) {
-    code += y > bnd[b] ? 1u : 0u;
-    near |= fabsf(y - bnd[b]) < kRecheckEps;
-  }
-  uint32_t sign = 0;
-  if (ip) {
-    const float resid = y - cent[code];
-    sign = (resid * s_col >= 0.f) ? 1u : 0u;
-    near |= fabsf(resid) < kRecheckEps;
-  }
-  return code | (sign << 8) | (near ? 1u << 16 : 0u);
-}
-
-// x_unit . Pi[col] with the CUDA-core kernel's arithmetic: x/norm, fp32 FMA over ascending coordinate.
-__device__ __noinline__ float exact_chain(const CompressArgs& a, int64_t n, int col, float norm) {
-  const float* prow = a.Pi + col * kRD;
-  float z = 0.f;
-#pragma unroll 8
-  for (int j = 0; j < kRD; ++j) z = fmaf(load_float(a.x, a.x_dtype, n * a.x_pitch + j) / norm, __ldg(prow + j), z);
-  return z;
 }
 
 template <int BITS, bool IP, int NTERM, int WARPS>
@@ -251,21 +193,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) compress_mma_kernel(CompressArg
   if (threadIdx.x < kRD) s.sgn[threadIdx.x] = IP ? a.S[threadIdx.x] : 0.f;
   if (threadIdx.x < WARPS) s.qcount[threadIdx.x] = 0;
   __syncthreads();
-  for (int k = threadIdx.x; k < kLutSize; k += blockDim.x) {
-    uint8_t v = 0x80;
-    if (k <= 8192) {
-      const float lo = (static_cast<float>(k) - 4096.5f) * (1.f / 4096.f);
-      const float hi = (static_cast<float>(k) - 4095.5f) * (1.f / 4096.f);
-      const float margin = kRecheckEps + 2e-6f;
-      bool amb = false;
-      for (int b = 0; b < NB; ++b) amb |= (s.bnd[b] >= lo - margin && s.bnd[b] <= hi + margin);
-      if (IP)
-        for (int c = 0; c <= NB; ++c) amb |= (s.cent[c] >= lo - margin && s.cent[c] <= hi + margin);
-      const float mid = (static_cast<float>(k) - 4096.f) * (1.f / 4096.f);
-      v = static_cast<uint8_t>(count_bounds<BITS>(s.bnd, mid) | (amb ? 0x80u : 0u));
-    }
-    s.lut[k] = v;
-  }
+  build_bucket_lut<BITS, IP>(s.lut, s.bnd, s.cent);
   __syncthreads();
 
   uint4* queue = s.queue + warp * kQueueCap;

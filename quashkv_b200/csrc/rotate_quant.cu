@@ -358,8 +358,15 @@ static bool cuda_core_only() {
   return e && e[0] == '1';
 }
 
+// QUASHKV_B200_NO_TCGEN05=1 keeps the tensor-core rotation on the mma.sync kernels (for A/B checks).
+static bool no_tcgen05() {
+  const char* e = getenv("QUASHKV_B200_NO_TCGEN05");
+  return e && e[0] == '1';
+}
+
 static int run_compress(const CompressArgs& a, cudaStream_t st) {
   if (a.n_vec == 0) return QKV_OK;
+  if (compress_umma_ok(a) && !cuda_core_only() && !no_tcgen05()) return launch_compress_umma(a, st);
   if (compress_mma_ok(a) && !cuda_core_only()) return launch_compress_mma(a, st);
   return launch_by_nt(a, a.d, a.n_vec, st, compress_kernel<1>, compress_kernel<2>, compress_kernel<3>,
                       compress_kernel<4>);
@@ -467,3 +474,5 @@ extern "C" int qkv_decompress_mixed(const uint8_t* codes, int packed, const floa
   return launch_by_nt(a, d, n_vec, static_cast<cudaStream_t>(stream), decompress_kernel<1>,
                       decompress_kernel<2>, decompress_kernel<3>, decompress_kernel<4>);
 }
+
+extern "C" int64_t qkv_tensor_core_timeouts(void) { return static_cast<int64_t>(umma_timeouts()); }

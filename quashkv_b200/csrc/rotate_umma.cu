@@ -1,0 +1,457 @@
+// Compress at d = 128 with the rotation on the fifth-generation tensor cores (tcgen05).
+//
+// One CTA per SM walks over tiles of 128 vectors.  The rotation y = x @ Pi^T of a tile is a
+// 128 x 128 x 128 contraction issued by ONE thread as tcgen05.mma instructions (M = 128, N = 128,
+// K = 16 each) whose operands are read from shared memory through matrix descriptors and whose fp32
+// accumulator lives in tensor memory:
+//   * B = Pi, split exactly into three bf16 planes (h + m + l), staged once per CTA in the 128-byte
+//     swizzled K-major layout (96 KB);
+//   * A = the raw vectors.  bf16 input is its own exact single term, so the tile is copied from
+//     global memory straight into the operand layout by cp.async (no register staging, double
+//     buffered); products A*l, A*m, A*h accumulate smallest first: 24 MMAs per tile;
+//   * two accumulators (2 x 128 tensor-memory columns) alternate, so the MMAs of tile t run while
+//     the threads classify tile t-1.
+// The 128 threads then each own one vector: thread r reads row r of the accumulator with
+// tcgen05.ld (32 columns at a time), scales by 1/norm (fp64 sum of squares, as in the CUDA-core
+// kernel), classifies every coordinate through the bucket table, packs 32 codes into whole words
+// and stores the packed row.  Coordinates within kRecheckEps of a decision boundary go to a per-warp
+// queue and are recomputed with the sequential fp32 FMA chain, exactly as in the mma.sync kernel,
+// so the bytes are identical to the CUDA-core kernel's.
+//
+// Every wait on the tensor core is bounded; if one runs out the CTA stops using the tensor core,
+// counts the event and derives its remaining tiles with the fp32 chain alone (slow, still exact).
+#include "rotate_exact.cuh"
+#include "mma_decode.cuh"
+#include "umma.cuh"
+
+namespace qkv {
+
+__device__ unsigned int g_umma_timeouts = 0;
+
+constexpr int kUTile = 128;                       // vectors per tile = MMA M
+constexpr int kUThreads = 512;                    // four threads per vector: 32 output coordinates each
+constexpr int kUWarps = kUThreads / 32;
+constexpr uint32_t kUPlaneBytes = 128 * 128 * 2;  // one bf16 operand tile (two 64-wide K blocks)
+constexpr uint32_t kUTmemCols = 256;
+constexpr int kUQueueCap = 64;
+
+// Bucket table of this kernel: 16384 buckets of width 1/8192 over [-1, 1).  The low nibble of an entry is
+// the code of the bucket; bit 7 flags a bucket whose coordinates need a second look, of kind
+// 0x40 = decision boundary number (entry & 15) lies in or within the recheck margin of the bucket
+//        (code = that number, +1 if y is above it),
+// 0x20 = a centroid does (the sign bit needs the residual test),
+// 0x60 = anything else (edge buckets, two features in one bucket): generic path.
+__device__ __forceinline__ int bucket_fine(float v, float scale) {
+  return __float_as_int(fmaf(v, scale, 8192.f + 8388608.f)) & (kLutSize - 1);
+}
+
+template <int BITS, bool IP>
+__device__ __forceinline__ void build_fine_lut(uint8_t* lut, const float* bnd, const float* cent) {
+  constexpr int NB = (1 << BITS) - 1;
+  for (int k = threadIdx.x; k < kLutSize; k += blockDim.x) {
+    const float lo = (static_cast<float>(k) - 8192.5f) * (1.f / 8192.f);
+    const float hi = (static_cast<float>(k) - 8191.5f) * (1.f / 8192.f);
+    const float margin = kRecheckEps + 2e-6f;
+    int n_b = 0, which = 0, n_c = 0;
+    for (int b = 0; b < NB; ++b)
+      if (bnd[b] >= lo - margin && bnd[b] <= hi + margin) { ++n_b; which = b; }
+    if (IP)
+      for (int c = 0; c <= NB; ++c) n_c += (cent[c] >= lo - margin && cent[c] <= hi + margin) ? 1 : 0;
+    const float mid = (static_cast<float>(k) - 8192.f) * (1.f / 8192.f);
+    uint32_t v = count_bounds<BITS>(bnd, mid);
+    if (k == 0 || k == kLutSize - 1 || n_b > 1 || n_c > 1 || (n_b && n_c)) v |= 0xE0u;
+    else if (n_b) v = static_cast<uint32_t>(which) | 0xC0u;
+    else if (n_c) v |= 0xA0u;
+    lut[k] = static_cast<uint8_t>(v);
+  }
+}
+
+// Flagged buckets (about one coordinate in 150).  Returns code | sign << 8 | near << 16.
+static __device__ __noinline__ uint32_t classify_flagged(const float* bnd, const float* cent, float s_col, float y,
+                                                         uint32_t e, int nb, int ip) {
+  if ((e & 0x60u) == 0x60u) return classify_slow(bnd, cent, s_col, y, nb, ip);
+  uint32_t code = e & 15u;
+  bool near = false;
+  if (e & 0x40u) {
+    const float b = bnd[code];
+    near = fabsf(y - b) < kRecheckEps;
+    code += y > b ? 1u : 0u;
+  }
+  uint32_t sign = 0;
+  if (ip) {
+    const float resid = y - cent[code];
+    sign = (resid * s_col >= 0.f) ? 1u : 0u;
+    near |= fabsf(resid) < kRecheckEps;
+  }
+  return code | (sign << 8) | (near ? 1u << 16 : 0u);
+}
+
+struct UmmaSmem {
+  unsigned char* a[2];      // A tiles (bf16, swizzled), 1024-byte aligned
+  unsigned char* b[3];      // Pi planes h, m, l
+  uint8_t* lut;
+  uint4* queue;             // [warps][kUQueueCap]
+  double* ssq;              // [2 tiles][4 quarters][128 rows] partial sums of squares
+  float* bnd; float* cent; float* sgn;
+  uint32_t* smask;          // [4] bit c of word w: S[32 w + c] < 0
+  int* qcount;              // [warps]
+  uint64_t* mbar;           // [2]
+  uint32_t* tmem_slot;
+  int* dead;
+};
+
+constexpr size_t kUmmaSmemBytes = 1024 + 5 * kUPlaneBytes + kLutSize + kUWarps * kUQueueCap * 16 + 2 * 4 * 128 * 8 +
+                                  (16 + 16 + kRD) * 4 + 16 + kUWarps * 4 + 2 * 8 + 16;
+
+__device__ __forceinline__ UmmaSmem carve_umma(unsigned char* raw) {
+  UmmaSmem s;
+  unsigned char* p = raw + ((1024u - (umma::smem_u32(raw) & 1023u)) & 1023u);
+  s.a[0] = p; s.a[1] = p + kUPlaneBytes;
+  for (int t = 0; t < 3; ++t) s.b[t] = p + (2 + t) * kUPlaneBytes;
+  p += 5 * kUPlaneBytes;
+  s.queue = reinterpret_cast<uint4*>(p); p += kUWarps * kUQueueCap * 16;
+  s.ssq = reinterpret_cast<double*>(p); p += 2 * 4 * 128 * 8;
+  s.lut = p; p += kLutSize;
+  s.bnd = reinterpret_cast<float*>(p); s.cent = s.bnd + 16; s.sgn = s.cent + 16; p += (16 + 16 + kRD) * 4;
+  s.smask = reinterpret_cast<uint32_t*>(p); p += 16;
+  s.mbar = reinterpret_cast<uint64_t*>(p); p += 16;
+  s.qcount = reinterpret_cast<int*>(p); p += kUWarps * 4;
+  s.tmem_slot = reinterpret_cast<uint32_t*>(p);
+  s.dead = reinterpret_cast<int*>(p + 4);
+  return s;
+}
+
+template <int BITS, bool IP>
+__global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const UmmaSmem s = carve_umma(smem_raw);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int trow = 32 * (warp & 3) + lane;          // vector of the tile = tensor-memory lane
+  const int blk = warp >> 2;                        // output coordinates 32 blk .. 32 blk + 31
+  constexpr int NB = (1 << BITS) - 1;
+  constexpr int row_words = (BITS == 3 ? 3 * (kRD / 8) : kRD * BITS / 8) / 4;     // = 4 * BITS
+  const __nv_bfloat16* xg = reinterpret_cast<const __nv_bfloat16*>(a.x);
+
+  // ---- one-time setup: Pi planes, tables, barriers, tensor memory -------------------------------------
+  for (int idx = tid; idx < kRD * kRD; idx += kUThreads) {
+    const int n = idx >> 7, k = idx & 127;
+    __nv_bfloat16 h, m, l;
+    split3(a.Pi[idx], h, m, l);
+    const uint32_t off = umma::sw128_offset(n, k, 128);
+    *reinterpret_cast<__nv_bfloat16*>(s.b[0] + off) = h;
+    *reinterpret_cast<__nv_bfloat16*>(s.b[1] + off) = m;
+    *reinterpret_cast<__nv_bfloat16*>(s.b[2] + off) = l;
+  }
+  if (tid < 16) {
+    s.bnd[tid] = tid < NB ? a.bounds0[tid] : INFINITY;
+    s.cent[tid] = (IP && tid < (1 << BITS)) ? a.centroids[tid] : 0.f;
+  }
+  if (tid < kRD) {
+    const float sv = IP ? a.S[tid] : 0.f;
+    s.sgn[tid] = sv;
+    const uint32_t m = __ballot_sync(QKV_FULL_MASK, sv < 0.f);
+    if (lane == 0) s.smask[warp] = m;
+  }
+  if (tid < kUWarps) s.qcount[tid] = 0;
+  if (tid == 0) {
+    umma::mbar_init(&s.mbar[0], 1);
+    umma::mbar_init(&s.mbar[1], 1);
+    *s.dead = 0;
+  }
+  __syncthreads();
+  build_fine_lut<BITS, IP>(s.lut, s.bnd, s.cent);
+  if (warp == 0) umma::tmem_alloc(s.tmem_slot, kUTmemCols);
+  umma::fence_smem_to_async();
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  const uint32_t tmem_base = *s.tmem_slot;
+  const uint32_t smask = s.smask[blk];
+
+  uint4* queue = s.queue + warp * kUQueueCap;
+  uint32_t* out_codes = reinterpret_cast<uint32_t*>(a.codes);
+  uint32_t* out_signs = reinterpret_cast<uint32_t*>(a.signs);
+
+  // Recompute queued elements with the fp32 FMA chain, one per lane; patch changed codes / signs.
+  auto drain = [&](int count) {
+    __threadfence();
+    __syncwarp();
+    for (int base = 0; base < count; base += 32) {
+      const int i = base + lane;
+      if (i < count) {
+        const uint4 it = queue[i];
+        const int64_t n = it.x;
+        const int col = it.y & 0xFF;
+        const uint32_t old_code = (it.y >> 8) & 0xFF, old_sign = (it.y >> 16) & 1u;
+        const float z = exact_chain(a, n, col, __uint_as_float(it.z));
+        const uint32_t code = count_bounds<BITS>(s.bnd, z);
+        const int64_t row = map_row(a.rows, n);
+        const uint32_t diff = code ^ old_code;
+        if (diff) {
+          const int bit = col * BITS, w = bit >> 5, sh = bit & 31;
+          atomicXor(out_codes + row * row_words + w, diff << sh);
+          if (sh + BITS > 32) atomicXor(out_codes + row * row_words + w + 1, diff >> (32 - sh));
+        }
+        if (IP) {
+          const uint32_t sign = ((z - s.cent[code]) * s.sgn[col] >= 0.f) ? 1u : 0u;
+          if (sign != old_sign) atomicXor(out_signs + row * (kRD / 32) + (col >> 5), 1u << (col & 31));
+        }
+      }
+    }
+    __syncwarp();
+  };
+
+  const int64_t n_tiles = (a.n_vec + kUTile - 1) / kUTile;
+
+  // cp.async of one tile into A[buf]: 2048 chunks of 16 bytes, 8 per thread, coalesced along rows.
+  auto load_tile = [&](int64_t tile, int buf) {
+    const int64_t v0 = tile * kUTile;
+#pragma unroll
+    for (int j = 0; j < 2048 / kUThreads; ++j) {
+      const int p = tid + kUThreads * j;
+      const int r = p >> 4, c16 = p & 15;
+      const int64_t n = v0 + r;
+      const bool live = n < a.n_vec;
+      const __nv_bfloat16* src = xg + (live ? n : 0) * a.x_pitch + c16 * 8;
+      cp_async16(s.a[buf] + umma::sw128_offset(r, c16 * 8, 128), src, live ? 16 : 0);
+    }
+    cp_async_commit();
+  };
+
+  // fp64 sum of squares of this thread's 32 coordinates of row trow of A[buf], left in shared memory.
+  auto part_squares = [&](int buf) {
+    double ss = 0.0;
+#pragma unroll
+    for (int c8 = 0; c8 < 4; ++c8) {
+      const uint4 v = *reinterpret_cast<const uint4*>(s.a[buf] + umma::sw128_offset(trow, 32 * blk + c8 * 8, 128));
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const double lo = static_cast<double>(__uint_as_float(w[i] << 16));
+        const double hi = static_cast<double>(__uint_as_float(w[i] & 0xFFFF0000u));
+        ss += lo * lo + hi * hi;
+      }
+    }
+    s.ssq[(buf * 4 + blk) * 128 + trow] = ss;
+  };
+  auto row_norm = [&](int buf) {
+    const double* q = s.ssq + buf * 4 * 128 + trow;
+    return fmaxf(static_cast<float>(sqrt((q[0] + q[128]) + (q[256] + q[384]))), 1e-8f);
+  };
+
+  // Thread 0: the 24 MMAs of one tile (A * l, A * m, A * h), then the completion arrival.
+  auto issue_mmas = [&](int buf) {
+    constexpr uint32_t idesc = umma::instr_desc(umma::kFmtBF16, 128, 128);
+    const uint32_t d = tmem_base + buf * 128;
+    const uint32_t a_addr = umma::smem_u32(s.a[buf]);
+    bool acc = false;
+#pragma unroll
+    for (int t = 2; t >= 0; --t) {
+      const uint32_t b_addr = umma::smem_u32(s.b[t]);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t off = (ks >> 2) * (128 * 128) + (ks & 3) * 32;
+        umma::mma_f16(d, umma::smem_desc_sw128(a_addr + off), umma::smem_desc_sw128(b_addr + off), idesc, acc);
+        acc = true;
+      }
+    }
+    umma::commit(&s.mbar[buf]);
+  };
+
+  // Classify / pack / store this thread's 32 coordinates of row trow of a finished tile.  use_tmem ==
+  // false: every coordinate by the fp32 chain.  The common path is branch-free: 32 independent table
+  // look-ups whose flag bits are collected in a mask, packing by shifted adds.  Then the warp walks
+  // over the columns in which any of its lanes was flagged (usually one or two): the column is
+  // re-read from tensor memory and the flagged lanes classify it exactly and patch their words.
+  auto epilogue = [&](int64_t tile, int buf, float nrm, bool use_tmem) {
+    const int64_t n = tile * kUTile + trow;
+    const bool live = n < a.n_vec;
+    const int64_t row = live ? map_row(a.rows, n) : 0;
+    const float iv = 1.f / nrm, scale = iv * 8192.f;
+    const int col0 = 32 * blk;
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + buf * 128 + col0;
+    uint32_t fmask = 0, fval = 0, R = 0;
+    uint32_t wb[BITS + 1];
+#pragma unroll
+    for (int w = 0; w <= BITS; ++w) wb[w] = 0u;
+    if (use_tmem) {
+      uint32_t v[32];
+      umma::tmem_ld32(taddr, v);
+      uint32_t fm = 0;                           // flag of coordinate c ends up at bit 31 - c
+      const int8_t* slut = reinterpret_cast<const int8_t*>(s.lut);
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const float raw = __uint_as_float(v[c]);
+        const int e = slut[bucket_fine(raw, scale)];             // sign-extended: negative when flagged
+        fm = __funnelshift_l(static_cast<uint32_t>(e), fm, 1);
+        const uint32_t code = static_cast<uint32_t>(e) & 15u;
+        const int bit = BITS * c, w = bit >> 5, sh = bit & 31;
+        wb[w] += code << sh;                                       // fields are disjoint: add == or
+        if (sh + BITS > 32) wb[w + 1] += code >> (32 - sh);
+        if (IP) R = __funnelshift_l(__float_as_uint(raw * iv - s.cent[code]), R, 1);
+      }
+      const uint32_t mine = __brev(fm);
+      uint32_t cols = __reduce_or_sync(QKV_FULL_MASK, mine);      // columns flagged in any lane
+      while (cols) {
+        const int c = __ffs(cols) - 1;
+        cols &= cols - 1;
+        const float raw = __uint_as_float(umma::tmem_ld1(taddr + c));
+        if ((mine >> c) & 1u) {
+          const int col = col0 + c;
+          const float y = raw * iv;
+          const uint32_t ec = s.lut[bucket_fine(raw, scale)];
+          const uint32_t r = classify_flagged(s.bnd, s.cent, IP ? s.sgn[col] : 0.f, y, ec, NB, IP ? 1 : 0);
+          uint32_t code = r & 0xFFu, sign = (r >> 8) & 1u;
+          if ((r >> 16) && live) {
+            const int slot = atomicAdd(&s.qcount[warp], 1);
+            if (slot < kUQueueCap) {
+              queue[slot] = make_uint4(static_cast<uint32_t>(n), col | (code << 8) | (sign << 16),
+                                       __float_as_uint(nrm), 0u);
+            } else {
+              const float z = exact_chain(a, n, col, nrm);
+              code = count_bounds<BITS>(s.bnd, z);
+              if (IP) sign = ((z - s.cent[code]) * s.sgn[col] >= 0.f) ? 1u : 0u;
+            }
+          }
+          fmask |= 1u << c;
+          fval |= sign << c;
+          const uint32_t diff = code ^ (ec & 15u);
+          const int bit = BITS * c, w = bit >> 5, sh = bit & 31;
+#pragma unroll
+          for (int q = 0; q <= BITS; ++q) {
+            if (q == w) wb[q] ^= diff << sh;
+            if (q == w + 1 && sh + BITS > 32) wb[q] ^= diff >> (32 - sh);
+          }
+        }
+        __syncwarp();
+      }
+    } else {
+#pragma unroll 1
+      for (int c = 0; c < 32; ++c) {
+        const int col = col0 + c;
+        const float z = live ? exact_chain(a, n, col, nrm) : 0.f;
+        const uint32_t code = count_bounds<BITS>(s.bnd, z);
+        if (IP) fval |= (((z - s.cent[code]) * s.sgn[col] >= 0.f) ? 1u : 0u) << c;
+        const int bit = BITS * c, w = bit >> 5, sh = bit & 31;
+#pragma unroll
+        for (int q = 0; q <= BITS; ++q) {
+          if (q == w) wb[q] |= code << sh;
+          if (q == w + 1 && sh + BITS > 32) wb[q] |= code >> (32 - sh);
+        }
+      }
+      fmask = 0xFFFFFFFFu;
+    }
+    if (live) {
+      uint32_t* dst = out_codes + row * row_words + blk * BITS;
+      if (BITS == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(wb[0], wb[1], wb[2], wb[BITS - 1]);
+      else if (BITS == 2) *reinterpret_cast<uint2*>(dst) = make_uint2(wb[0], wb[1]);
+      else {
+#pragma unroll
+        for (int w = 0; w < BITS; ++w) dst[w] = wb[w];
+      }
+      if (IP) {
+        // unflagged coordinates: sign = residual >= 0 exclusive-or S < 0 (a zero residual is always flagged)
+        const uint32_t sw = ~(__brev(R) ^ smask);
+        out_signs[row * (kRD / 32) + blk] = (sw & ~fmask) | fval;
+      }
+      if (blk == 0) a.norms[row] = nrm;
+    }
+    __syncwarp();
+    const int queued = s.qcount[warp];
+    if (queued >= 32) {
+      drain(queued < kUQueueCap ? queued : kUQueueCap);
+      if (lane == 0) s.qcount[warp] = 0;
+      __syncwarp();
+    }
+  };
+
+  // ---- pipeline over this CTA's tiles ------------------------------------------------------------------
+  // iteration i: wait A(i); issue MMAs(i); squares(i); [wait MMAs(i-1); prefetch A(i+1); epilogue(i-1)]
+  uint32_t phase[2] = {0u, 0u};
+  int64_t prev_tile = -1;
+  int i = 0;
+  if (blockIdx.x < n_tiles) load_tile(blockIdx.x, 0);
+  for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++i) {
+    const int buf = i & 1;
+    cp_async_wait<0>();
+    umma::fence_smem_to_async();
+    umma::fence_before_sync();
+    __syncthreads();                      // A(i) complete and visible; epilogue(i-2) has left accumulator `buf`
+    const bool dead = *s.dead != 0;
+    if (tid == 0 && !dead) {
+      umma::fence_after_sync();
+      issue_mmas(buf);
+    }
+    const float norm_prev = prev_tile >= 0 ? row_norm(buf ^ 1) : 1.f;     // squares(i-1) were left before the barrier
+    part_squares(buf);
+    const int64_t next = tile + gridDim.x;
+    if (prev_tile >= 0) {
+      bool ok = !dead;
+      if (ok) {
+        ok = umma::mbar_wait(&s.mbar[buf ^ 1], phase[buf ^ 1]);
+        phase[buf ^ 1] ^= 1u;
+        if (!ok) { *s.dead = 1; atomicAdd(&g_umma_timeouts, 1u); }
+      }
+      umma::fence_after_sync();
+      if (next < n_tiles) load_tile(next, buf ^ 1);       // A(i-1) has been consumed
+      epilogue(prev_tile, buf ^ 1, norm_prev, ok);
+    } else if (next < n_tiles) {
+      load_tile(next, buf ^ 1);
+    }
+    prev_tile = tile;
+  }
+  if (prev_tile >= 0) {
+    const int buf = (i - 1) & 1;
+    __syncthreads();                      // squares of the last tile
+    const float norm_prev = row_norm(buf);
+    bool ok = *s.dead == 0;
+    if (ok) {
+      ok = umma::mbar_wait(&s.mbar[buf], phase[buf]);
+      if (!ok) { *s.dead = 1; atomicAdd(&g_umma_timeouts, 1u); }
+    }
+    umma::fence_after_sync();
+    epilogue(prev_tile, buf, norm_prev, ok);
+  }
+  __syncwarp();
+  const int queued = s.qcount[warp];
+  if (queued > 0) drain(queued < kUQueueCap ? queued : kUQueueCap);
+  umma::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) umma::tmem_dealloc(tmem_base, kUTmemCols);
+}
+
+bool compress_umma_ok(const CompressArgs& a) {
+  const uintptr_t al = reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.codes) |
+                       (a.mode == MODE_IP ? reinterpret_cast<uintptr_t>(a.signs) : 0);
+  return a.d == kRD && a.mode != MODE_MIXED && a.packed && a.x_dtype == QKV_BF16 && a.n_vec >= 1024 &&
+         a.n_vec < (int64_t(1) << 31) && (a.x_pitch & 7) == 0 && (al & 15u) == 0;
+}
+
+template <int BITS, bool IP>
+static int launch_compress_umma_t(const CompressArgs& a, cudaStream_t st) {
+  if (cudaFuncSetAttribute(compress_umma_kernel<BITS, IP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(kUmmaSmemBytes)) != cudaSuccess)
+    return QKV_ELAUNCH;
+  const int64_t tiles = (a.n_vec + kUTile - 1) / kUTile;
+  const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
+  compress_umma_kernel<BITS, IP><<<grid, kUThreads, kUmmaSmemBytes, st>>>(a);
+  return check_launch();
+}
+
+int launch_compress_umma(const CompressArgs& a, cudaStream_t st) {
+  const bool ip = a.mode == MODE_IP;
+  switch (a.bits0) {
+    case 1: return ip ? launch_compress_umma_t<1, true>(a, st) : launch_compress_umma_t<1, false>(a, st);
+    case 2: return ip ? launch_compress_umma_t<2, true>(a, st) : launch_compress_umma_t<2, false>(a, st);
+    case 3: return ip ? launch_compress_umma_t<3, true>(a, st) : launch_compress_umma_t<3, false>(a, st);
+    default: return ip ? launch_compress_umma_t<4, true>(a, st) : launch_compress_umma_t<4, false>(a, st);
+  }
+}
+
+unsigned int umma_timeouts() {
+  unsigned int v = 0;
+  cudaMemcpyFromSymbol(&v, g_umma_timeouts, sizeof(v));
+  return v;
+}
+
+}  // namespace qkv

@@ -1,0 +1,129 @@
+// Fifth-generation tensor-core primitives (tcgen05) for sm_100a: tensor-memory allocation, shared
+// memory matrix descriptors, the single-thread MMA issue, completion through an mbarrier, and the
+// accumulator read-back.  Everything a kernel waits on here has a bounded wait.
+#pragma once
+
+#include <stdint.h>
+
+namespace qkv {
+namespace umma {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ---- mbarrier (CTA-local) ---------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Waits for the phase with the given parity; gives up after ~0.2 s of SM clocks and returns false.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (clock64() - t0 < 400000000LL)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+
+// ---- tensor memory ------------------------------------------------------------------------------------
+// Whole-warp calls.  `slot` is a shared-memory word that receives the base address (lane 0, column c).
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t n_cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(slot)), "r"(n_cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t n_cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(n_cols) : "memory");
+}
+
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+// Makes this thread's shared-memory writes (st.shared, completed cp.async) visible to the tensor core.
+__device__ __forceinline__ void fence_smem_to_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
+// ---- descriptors -----------------------------------------------------------------------------------------
+// K-major operand tile in the 128-byte swizzled layout: row r (M or N index) of a 64-element (bf16 /
+// fp16) K block lives at base + r * 128, its 16-byte chunk c at position c ^ (r & 7); groups of 8
+// rows are 1024 bytes apart; the base is 1024-byte aligned.  A K step of 16 elements inside the
+// block advances the start address by 32 bytes.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(1) << 16) |
+         (static_cast<uint64_t>(1024 >> 4) << 32) | (static_cast<uint64_t>(1) << 46) |
+         (static_cast<uint64_t>(2) << 61);
+}
+
+// Byte offset of element (row, k) of a [rows][64 * n_blocks] 16-bit tile in that layout.
+__host__ __device__ constexpr uint32_t sw128_offset(int row, int k, int rows) {
+  return static_cast<uint32_t>((k >> 6) * rows * 128 + row * 128 + ((((k & 63) >> 3) ^ (row & 7)) << 4) + (k & 7) * 2);
+}
+
+enum { kFmtF16 = 0, kFmtBF16 = 1 };
+
+// Instruction descriptor of kind::f16: fp32 accumulate, both operands K-major, D is M x N.
+__host__ __device__ constexpr uint32_t instr_desc(int fmt_ab, int M, int N) {
+  return (1u << 4) | (static_cast<uint32_t>(fmt_ab) << 7) | (static_cast<uint32_t>(fmt_ab) << 10) |
+         (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem] * B[smem]^T for one K step of 16; issued by ONE thread.
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate ? 1u : 0u)
+      : "memory");
+}
+
+// The barrier gets one arrival when every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+// 32 consecutive fp32 columns of this thread's TMEM lane (warp w of the CTA reads lanes 32 (w % 4) ..).
+// The load and its wait are ONE asm statement: the registers are only defined once the wait has
+// retired, and a separate wait would let the compiler schedule register-only uses ahead of it.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;\n"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+// One fp32 column of this thread's lane (same fused wait).
+__device__ __forceinline__ uint32_t tmem_ld1(uint32_t taddr) {
+  uint32_t v;
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];\n\t"
+      "tcgen05.wait::ld.sync.aligned;\n"
+      : "=r"(v)
+      : "r"(taddr)
+      : "memory");
+  return v;
+}
+
+}  // namespace umma
+}  // namespace qkv

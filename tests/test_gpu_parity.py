@@ -185,6 +185,12 @@ def test_tensor_core_rotation_equals_cuda_core_rotation(golden, monkeypatch):
             slow_ip = ops.compress_ip(xd, Pi, bnd, cent, S, bits, packed=True)
             rec_slow = ops.decompress(fast[0], fast[1], Pi, cent, bits, packed=True, d=128)
             monkeypatch.delenv("QUASHKV_B200_CUDA_CORE_ROTATION")
+            monkeypatch.setenv("QUASHKV_B200_NO_TCGEN05", "1")       # bf16 input: mma.sync instead of tcgen05
+            mid = ops.compress_mse(xd, Pi, bnd, bits, packed=True)
+            mid_ip = ops.compress_ip(xd, Pi, bnd, cent, S, bits, packed=True)
+            monkeypatch.delenv("QUASHKV_B200_NO_TCGEN05")
+            assert torch.equal(mid[0], slow[0]) and torch.equal(mid_ip[0], slow_ip[0])
+            assert torch.equal(mid_ip[1], slow_ip[1]) and torch.equal(mid[1], slow[1])
             n_code = int((fast[0] != slow[0]).sum()) + int((fast_ip[0] != slow_ip[0]).sum())
             n_sign = int((fast_ip[1] != slow_ip[1]).sum())
             print(f"[ties] tensor-core vs CUDA-core rotation, {dtype}, {bits} bits: {n_code} code bytes, "
@@ -192,6 +198,8 @@ def test_tensor_core_rotation_equals_cuda_core_rotation(golden, monkeypatch):
             assert n_code == 0 and n_sign == 0
             assert torch.equal(fast[1], slow[1]) and torch.equal(fast_ip[2], slow_ip[2])
             assert rel_l2(rec_fast, rec_slow) < 2e-6
+    from quashkv_b200 import _lib
+    assert _lib.lib().qkv_tensor_core_timeouts() == 0
 
 
 def test_shapes_ragged_and_empty(golden):
