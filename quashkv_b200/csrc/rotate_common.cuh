@@ -40,6 +40,8 @@ bool decompress_mma_ok(const DecompressArgs& a);
 // tcgen05 rotation (rotate_umma.cu): d == 128, bf16 input, packed output.
 bool compress_umma_ok(const CompressArgs& a);
 int launch_compress_umma(const CompressArgs& a, cudaStream_t st);
+bool decompress_umma_ok(const DecompressArgs& a);
+int launch_decompress_umma(const DecompressArgs& a, cudaStream_t st);
 unsigned int umma_timeouts();             // bounded waits on the tensor core that ran out (device-wide counter)
 int launch_decompress_mma(const DecompressArgs& a, cudaStream_t st);
 

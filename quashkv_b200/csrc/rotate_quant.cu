@@ -449,6 +449,8 @@ extern "C" int qkv_decompress(const uint8_t* codes, const uint8_t* signs, int pa
   a.codes = codes; a.signs = signs; a.packed = packed; a.norms = norms; a.rows = rows;
   a.n_vec = n_vec; a.d = d; a.Pi = Pi; a.mode = MODE_MSE; a.cents0 = centroids; a.bits0 = bits; a.bits1 = 1;
   a.S = S; a.qjl_scale = qjl_scale; a.out = out; a.out_dtype = out_dtype; a.out_pitch = out_pitch;
+  if (decompress_umma_ok(a) && !cuda_core_only() && !no_tcgen05())
+    return launch_decompress_umma(a, static_cast<cudaStream_t>(stream));
   if (decompress_mma_ok(a) && !cuda_core_only()) return launch_decompress_mma(a, static_cast<cudaStream_t>(stream));
   return launch_by_nt(a, d, n_vec, static_cast<cudaStream_t>(stream), decompress_kernel<1>,
                       decompress_kernel<2>, decompress_kernel<3>, decompress_kernel<4>);

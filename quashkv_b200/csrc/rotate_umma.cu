@@ -89,10 +89,8 @@ static __device__ __noinline__ uint32_t classify_flagged(const float* bnd, const
 struct UmmaSmem {
   unsigned char* a[2];      // A tiles (bf16, swizzled), 1024-byte aligned
   unsigned char* b[3];      // Pi planes h, m, l
-  uint8_t* lut;
   uint4* queue;             // [warps][kUQueueCap]
   double* ssq;              // [2 tiles][4 quarters][128 rows] partial sums of squares
-  float* bnd; float* cent; float* sgn;
   uint32_t* smask;          // [4] bit c of word w: S[32 w + c] < 0
   int* qcount;              // [warps]
   uint64_t* mbar;           // [2]
@@ -100,8 +98,9 @@ struct UmmaSmem {
   int* dead;
 };
 
-constexpr size_t kUmmaSmemBytes = 1024 + 5 * kUPlaneBytes + kLutSize + kUWarps * kUQueueCap * 16 + 2 * 4 * 128 * 8 +
-                                  (16 + 16 + kRD) * 4 + 16 + kUWarps * 4 + 2 * 8 + 16;
+// dynamic part; the bucket table and the small tables are static shared arrays (constant addresses)
+constexpr size_t kUmmaSmemBytes = 1024 + 5 * kUPlaneBytes + kUWarps * kUQueueCap * 16 + 2 * 4 * 128 * 8 + 16 +
+                                  kUWarps * 4 + 2 * 8 + 16;
 
 __device__ __forceinline__ UmmaSmem carve_umma(unsigned char* raw) {
   UmmaSmem s;
@@ -111,8 +110,6 @@ __device__ __forceinline__ UmmaSmem carve_umma(unsigned char* raw) {
   p += 5 * kUPlaneBytes;
   s.queue = reinterpret_cast<uint4*>(p); p += kUWarps * kUQueueCap * 16;
   s.ssq = reinterpret_cast<double*>(p); p += 2 * 4 * 128 * 8;
-  s.lut = p; p += kLutSize;
-  s.bnd = reinterpret_cast<float*>(p); s.cent = s.bnd + 16; s.sgn = s.cent + 16; p += (16 + 16 + kRD) * 4;
   s.smask = reinterpret_cast<uint32_t*>(p); p += 16;
   s.mbar = reinterpret_cast<uint64_t*>(p); p += 16;
   s.qcount = reinterpret_cast<int*>(p); p += kUWarps * 4;
@@ -124,6 +121,8 @@ __device__ __forceinline__ UmmaSmem carve_umma(unsigned char* raw) {
 template <int BITS, bool IP>
 __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ int8_t lut_s[kLutSize];
+  __shared__ float bnd_s[16], cent_s[16], sgn_s[kRD];
   const UmmaSmem s = carve_umma(smem_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int trow = 32 * (warp & 3) + lane;          // vector of the tile = tensor-memory lane
@@ -143,12 +142,12 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
     *reinterpret_cast<__nv_bfloat16*>(s.b[2] + off) = l;
   }
   if (tid < 16) {
-    s.bnd[tid] = tid < NB ? a.bounds0[tid] : INFINITY;
-    s.cent[tid] = (IP && tid < (1 << BITS)) ? a.centroids[tid] : 0.f;
+    bnd_s[tid] = tid < NB ? a.bounds0[tid] : INFINITY;
+    cent_s[tid] = (IP && tid < (1 << BITS)) ? a.centroids[tid] : 0.f;
   }
   if (tid < kRD) {
     const float sv = IP ? a.S[tid] : 0.f;
-    s.sgn[tid] = sv;
+    sgn_s[tid] = sv;
     const uint32_t m = __ballot_sync(QKV_FULL_MASK, sv < 0.f);
     if (lane == 0) s.smask[warp] = m;
   }
@@ -159,7 +158,7 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
     *s.dead = 0;
   }
   __syncthreads();
-  build_fine_lut<BITS, IP>(s.lut, s.bnd, s.cent);
+  build_fine_lut<BITS, IP>(reinterpret_cast<uint8_t*>(lut_s), bnd_s, cent_s);
   if (warp == 0) umma::tmem_alloc(s.tmem_slot, kUTmemCols);
   umma::fence_smem_to_async();
   umma::fence_before_sync();
@@ -184,7 +183,7 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
         const int col = it.y & 0xFF;
         const uint32_t old_code = (it.y >> 8) & 0xFF, old_sign = (it.y >> 16) & 1u;
         const float z = exact_chain(a, n, col, __uint_as_float(it.z));
-        const uint32_t code = count_bounds<BITS>(s.bnd, z);
+        const uint32_t code = count_bounds<BITS>(bnd_s, z);
         const int64_t row = map_row(a.rows, n);
         const uint32_t diff = code ^ old_code;
         if (diff) {
@@ -193,7 +192,7 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
           if (sh + BITS > 32) atomicXor(out_codes + row * row_words + w + 1, diff >> (32 - sh));
         }
         if (IP) {
-          const uint32_t sign = ((z - s.cent[code]) * s.sgn[col] >= 0.f) ? 1u : 0u;
+          const uint32_t sign = ((z - cent_s[code]) * sgn_s[col] >= 0.f) ? 1u : 0u;
           if (sign != old_sign) atomicXor(out_signs + row * (kRD / 32) + (col >> 5), 1u << (col & 31));
         }
       }
@@ -278,17 +277,16 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
       uint32_t v[32];
       umma::tmem_ld32(taddr, v);
       uint32_t fm = 0;                           // flag of coordinate c ends up at bit 31 - c
-      const int8_t* slut = reinterpret_cast<const int8_t*>(s.lut);
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
         const float raw = __uint_as_float(v[c]);
-        const int e = slut[bucket_fine(raw, scale)];             // sign-extended: negative when flagged
+        const int e = lut_s[bucket_fine(raw, scale)];             // sign-extended: negative when flagged
         fm = __funnelshift_l(static_cast<uint32_t>(e), fm, 1);
         const uint32_t code = static_cast<uint32_t>(e) & 15u;
         const int bit = BITS * c, w = bit >> 5, sh = bit & 31;
         wb[w] += code << sh;                                       // fields are disjoint: add == or
         if (sh + BITS > 32) wb[w + 1] += code >> (32 - sh);
-        if (IP) R = __funnelshift_l(__float_as_uint(raw * iv - s.cent[code]), R, 1);
+        if (IP) R = __funnelshift_l(__float_as_uint(raw * iv - cent_s[code]), R, 1);
       }
       const uint32_t mine = __brev(fm);
       uint32_t cols = __reduce_or_sync(QKV_FULL_MASK, mine);      // columns flagged in any lane
@@ -299,8 +297,8 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
         if ((mine >> c) & 1u) {
           const int col = col0 + c;
           const float y = raw * iv;
-          const uint32_t ec = s.lut[bucket_fine(raw, scale)];
-          const uint32_t r = classify_flagged(s.bnd, s.cent, IP ? s.sgn[col] : 0.f, y, ec, NB, IP ? 1 : 0);
+          const uint32_t ec = static_cast<uint8_t>(lut_s[bucket_fine(raw, scale)]);
+          const uint32_t r = classify_flagged(bnd_s, cent_s, IP ? sgn_s[col] : 0.f, y, ec, NB, IP ? 1 : 0);
           uint32_t code = r & 0xFFu, sign = (r >> 8) & 1u;
           if ((r >> 16) && live) {
             const int slot = atomicAdd(&s.qcount[warp], 1);
@@ -309,8 +307,8 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
                                        __float_as_uint(nrm), 0u);
             } else {
               const float z = exact_chain(a, n, col, nrm);
-              code = count_bounds<BITS>(s.bnd, z);
-              if (IP) sign = ((z - s.cent[code]) * s.sgn[col] >= 0.f) ? 1u : 0u;
+              code = count_bounds<BITS>(bnd_s, z);
+              if (IP) sign = ((z - cent_s[code]) * sgn_s[col] >= 0.f) ? 1u : 0u;
             }
           }
           fmask |= 1u << c;
@@ -330,8 +328,8 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
       for (int c = 0; c < 32; ++c) {
         const int col = col0 + c;
         const float z = live ? exact_chain(a, n, col, nrm) : 0.f;
-        const uint32_t code = count_bounds<BITS>(s.bnd, z);
-        if (IP) fval |= (((z - s.cent[code]) * s.sgn[col] >= 0.f) ? 1u : 0u) << c;
+        const uint32_t code = count_bounds<BITS>(bnd_s, z);
+        if (IP) fval |= (((z - cent_s[code]) * sgn_s[col] >= 0.f) ? 1u : 0u) << c;
         const int bit = BITS * c, w = bit >> 5, sh = bit & 31;
 #pragma unroll
         for (int q = 0; q <= BITS; ++q) {
@@ -452,6 +450,270 @@ unsigned int umma_timeouts() {
   unsigned int v = 0;
   cudaMemcpyFromSymbol(&v, g_umma_timeouts, sizeof(v));
   return v;
+}
+
+
+// ---- decompress ------------------------------------------------------------------------------------------
+// out = norm * (v @ Pi) with v_i = c[code_i] (+ qjl_scale * S_i * (2 sign_i - 1)): the same 128 x 128 x 128
+// contraction with the roles swapped: A = the decoded rows, written by the threads into the
+// swizzled operand layout, B = Pi^T.  Both operands are split into NT bf16 terms:
+//   NT = 3 (fp32 output): exact split, six products, an fp32-faithful result; one A buffer;
+//   NT = 2 (bf16 output): four products, relative error ~1e-5, far below the bf16 rounding of
+//                         the output; two A buffers, so decoding tile t+1 overlaps the MMAs of tile t.
+// Four threads per row: each decodes 32 coordinates and later scales and stores 32 outputs.
+template <int NT>
+struct DecSmem {
+  static constexpr int NBUF = NT == 2 ? 2 : 1;
+  unsigned char* a[NBUF][NT];
+  unsigned char* b[NT];
+  uint64_t* mbar;           // [2]
+  uint32_t* tmem_slot;
+  int* dead;
+};
+
+template <int NT>
+constexpr size_t dec_smem_bytes() {
+  return 1024 + static_cast<size_t>(DecSmem<NT>::NBUF * NT + NT) * kUPlaneBytes + 2 * 8 + 16;
+}
+
+template <int NT>
+__device__ __forceinline__ DecSmem<NT> carve_dec(unsigned char* raw) {
+  DecSmem<NT> s;
+  unsigned char* p = raw + ((1024u - (umma::smem_u32(raw) & 1023u)) & 1023u);
+  for (int bf = 0; bf < DecSmem<NT>::NBUF; ++bf)
+    for (int t = 0; t < NT; ++t) { s.a[bf][t] = p; p += kUPlaneBytes; }
+  for (int t = 0; t < NT; ++t) { s.b[t] = p; p += kUPlaneBytes; }
+  s.mbar = reinterpret_cast<uint64_t*>(p); p += 16;
+  s.tmem_slot = reinterpret_cast<uint32_t*>(p);
+  s.dead = reinterpret_cast<int*>(p + 4);
+  return s;
+}
+
+// y = Pi^T-rotation of one decoded row by the fp32 chain (only used after a tensor-core timeout).
+static __device__ __noinline__ float decompress_chain(const float* vrow, const float* Pi, int col) {
+  float z = 0.f;
+  for (int i = 0; i < kRD; ++i) z = fmaf(vrow[i], __ldg(Pi + i * kRD + col), z);
+  return z;
+}
+
+template <int BITS, bool SIGNS, int NT>
+__global__ void __launch_bounds__(kUThreads, 1) decompress_umma_kernel(DecompressArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ float cent_s[16], qs_s[kRD];
+  const DecSmem<NT> s = carve_dec<NT>(smem_raw);
+  constexpr int NBUF = DecSmem<NT>::NBUF;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int trow = 32 * (warp & 3) + lane, blk = warp >> 2;
+  constexpr int row_words = 4 * BITS;
+  const uint32_t* codes = reinterpret_cast<const uint32_t*>(a.codes);
+  const uint32_t* signs = reinterpret_cast<const uint32_t*>(a.signs);
+
+  // ---- one-time setup: Pi^T planes (B[n = output j][k = input i] = Pi[i][j]), tables, barriers, TMEM -----
+  for (int idx = tid; idx < kRD * kRD; idx += kUThreads) {
+    const int i = idx >> 7, j = idx & 127;
+    __nv_bfloat16 t3[3];
+    split3(a.Pi[idx], t3[0], t3[1], t3[2]);
+    const uint32_t off = umma::sw128_offset(j, i, 128);
+#pragma unroll
+    for (int t = 0; t < NT; ++t) *reinterpret_cast<__nv_bfloat16*>(s.b[t] + off) = t3[t];
+  }
+  if (tid < 16) cent_s[tid] = tid < (1 << BITS) ? a.cents0[tid] : 0.f;
+  if (tid < kRD) qs_s[tid] = SIGNS ? a.qjl_scale * a.S[tid] : 0.f;
+  if (tid == 0) {
+    umma::mbar_init(&s.mbar[0], 1);
+    umma::mbar_init(&s.mbar[1], 1);
+    *s.dead = 0;
+  }
+  if (warp == 0) umma::tmem_alloc(s.tmem_slot, kUTmemCols);
+  umma::fence_smem_to_async();
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  const uint32_t tmem_base = *s.tmem_slot;
+  const int64_t n_tiles = (a.n_vec + kUTile - 1) / kUTile;
+
+  // Decode this thread's 32 coordinates of row trow into the NT operand planes of A[bf].
+  auto decode_tile = [&](int64_t tile, int bf) {
+    const int64_t n = tile * kUTile + trow;
+    const bool live = n < a.n_vec;
+    const int64_t row = live ? map_row(a.rows, n) : 0;
+    uint32_t w[BITS + 1], sw = 0;
+#pragma unroll
+    for (int q = 0; q < BITS; ++q) w[q] = live ? __ldg(codes + row * row_words + blk * BITS + q) : 0u;
+    w[BITS] = 0u;
+    if (SIGNS) sw = live ? __ldg(signs + row * (kRD / 32) + blk) : 0u;
+#pragma unroll
+    for (int c8 = 0; c8 < 4; ++c8) {
+      uint32_t packed[NT][4];
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        float v[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int c = 8 * c8 + 2 * p + h;
+          const int bit = BITS * c, wi = bit >> 5, sh = bit & 31;
+          uint32_t code = w[wi] >> sh;
+          if (sh + BITS > 32) code |= w[wi + 1] << (32 - sh);
+          code &= (1u << BITS) - 1u;
+          float x = cent_s[code];
+          if (SIGNS) {
+            const float q = qs_s[32 * blk + c];
+            x += ((sw >> c) & 1u) ? q : -q;
+          }
+          v[h] = live ? x : 0.f;
+        }
+        const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[0], v[1]);
+        packed[0][p] = *reinterpret_cast<const uint32_t*>(&h2);
+        const float r0 = v[0] - __bfloat162float(h2.x), r1 = v[1] - __bfloat162float(h2.y);
+        const __nv_bfloat162 m2 = __floats2bfloat162_rn(r0, r1);
+        packed[1][p] = *reinterpret_cast<const uint32_t*>(&m2);
+        if (NT == 3) {
+          const __nv_bfloat162 l2 = __floats2bfloat162_rn(r0 - __bfloat162float(m2.x), r1 - __bfloat162float(m2.y));
+          packed[NT - 1][p] = *reinterpret_cast<const uint32_t*>(&l2);
+        }
+      }
+      const uint32_t off = umma::sw128_offset(trow, 32 * blk + 8 * c8, 128);
+#pragma unroll
+      for (int t = 0; t < NT; ++t)
+        *reinterpret_cast<uint4*>(s.a[bf][t] + off) = make_uint4(packed[t][0], packed[t][1], packed[t][2], packed[t][3]);
+    }
+  };
+
+  // Thread 0: products smallest first, then the completion arrival.
+  auto issue_mmas = [&](int bf, int acc_buf) {
+    constexpr uint32_t idesc = umma::instr_desc(umma::kFmtBF16, 128, 128);
+    const uint32_t d = tmem_base + acc_buf * 128;
+    constexpr int n_prod = NT == 2 ? 4 : 6;
+    constexpr int pa2[4] = {1, 0, 1, 0}, pb2[4] = {1, 1, 0, 0};
+    constexpr int pa3[6] = {1, 2, 0, 1, 0, 0}, pb3[6] = {1, 0, 2, 0, 1, 0};
+    bool acc = false;
+#pragma unroll
+    for (int pr = 0; pr < n_prod; ++pr) {
+      const int ta = NT == 2 ? pa2[pr] : pa3[pr], tb = NT == 2 ? pb2[pr] : pb3[pr];
+      const uint32_t a_addr = umma::smem_u32(s.a[bf][ta]), b_addr = umma::smem_u32(s.b[tb]);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t off = (ks >> 2) * (128 * 128) + (ks & 3) * 32;
+        umma::mma_f16(d, umma::smem_desc_sw128(a_addr + off), umma::smem_desc_sw128(b_addr + off), idesc, acc);
+        acc = true;
+      }
+    }
+    umma::commit(&s.mbar[acc_buf]);
+  };
+
+  // Scale this thread's 32 outputs of row trow by the norm and store them.
+  auto epilogue = [&](int64_t tile, int acc_buf, bool use_tmem) {
+    const int64_t n = tile * kUTile + trow;
+    const bool live = n < a.n_vec;
+    const int64_t row = live ? map_row(a.rows, n) : 0;
+    const float nrm = live ? __ldg(a.norms + row) : 0.f;
+    uint32_t v[32];
+    if (use_tmem) {
+      umma::tmem_ld32(tmem_base + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + acc_buf * 128 + 32 * blk, v);
+    } else if (live) {                                   // tensor core timed out: fp32 chain from the packed row
+      float vrow[kRD];
+      for (int i = 0; i < kRD; ++i) {
+        const uint32_t code = read_field(a.codes + row * (row_words * 4), i * BITS, BITS, row_words * 4);
+        float x = cent_s[code];
+        if (SIGNS) x += ((signs[row * (kRD / 32) + (i >> 5)] >> (i & 31)) & 1u) ? qs_s[i] : -qs_s[i];
+        vrow[i] = x;
+      }
+      for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(decompress_chain(vrow, a.Pi, 32 * blk + c));
+    }
+    if (!live) return;
+    if (a.out_dtype == QKV_F32) {
+      float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + n * a.out_pitch + 32 * blk);
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        dst[q] = make_float4(__uint_as_float(v[4 * q]) * nrm, __uint_as_float(v[4 * q + 1]) * nrm,
+                             __uint_as_float(v[4 * q + 2]) * nrm, __uint_as_float(v[4 * q + 3]) * nrm);
+    } else {
+#pragma unroll
+      for (int c = 0; c < 32; ++c)
+        store_float(a.out, a.out_dtype, n * a.out_pitch + 32 * blk + c, __uint_as_float(v[c]) * nrm);
+    }
+  };
+
+  // ---- pipeline ---------------------------------------------------------------------------------------------
+  // two A buffers: decode(i); issue(i); wait(i-1); epilogue(i-1)     (decode overlaps the MMAs of tile i-1)
+  // one A buffer : wait(i-1); decode(i); issue(i); epilogue(i-1)     (the MMAs of tile i-1 still read A)
+  uint32_t phase[2] = {0u, 0u};
+  int64_t prev_tile = -1;
+  int i = 0;
+  bool prev_ok = true;
+  for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++i) {
+    const int bf = i % NBUF, acc_buf = i & 1;
+    auto wait_prev = [&]() {
+      if (prev_tile < 0) return;
+      prev_ok = *s.dead == 0;
+      if (prev_ok) {
+        prev_ok = umma::mbar_wait(&s.mbar[acc_buf ^ 1], phase[acc_buf ^ 1]);
+        phase[acc_buf ^ 1] ^= 1u;
+        if (!prev_ok) { *s.dead = 1; atomicAdd(&g_umma_timeouts, 1u); }
+      }
+      umma::fence_after_sync();
+    };
+    if (NBUF == 1) wait_prev();
+    decode_tile(tile, bf);
+    umma::fence_smem_to_async();
+    umma::fence_before_sync();
+    __syncthreads();                      // A(i) written; epilogue(i-2) has left accumulator acc_buf
+    if (tid == 0 && *s.dead == 0) {
+      umma::fence_after_sync();
+      issue_mmas(bf, acc_buf);
+    }
+    if (NBUF == 2) wait_prev();
+    if (prev_tile >= 0) epilogue(prev_tile, acc_buf ^ 1, prev_ok);
+    prev_tile = tile;
+  }
+  if (prev_tile >= 0) {
+    const int acc_buf = (i - 1) & 1;
+    bool ok = *s.dead == 0;
+    if (ok) {
+      ok = umma::mbar_wait(&s.mbar[acc_buf], phase[acc_buf]);
+      if (!ok) { *s.dead = 1; atomicAdd(&g_umma_timeouts, 1u); }
+    }
+    umma::fence_after_sync();
+    epilogue(prev_tile, acc_buf, ok);
+  }
+  umma::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) umma::tmem_dealloc(tmem_base, kUTmemCols);
+}
+
+bool decompress_umma_ok(const DecompressArgs& a) {
+  const uintptr_t al = reinterpret_cast<uintptr_t>(a.codes) | reinterpret_cast<uintptr_t>(a.out) |
+                       (a.signs ? reinterpret_cast<uintptr_t>(a.signs) : 0);
+  return a.d == kRD && a.mode != MODE_MIXED && a.packed && a.n_vec >= 1024 && (a.out_pitch & 7) == 0 &&
+         (al & 15u) == 0;
+}
+
+template <int BITS, bool SIGNS, int NT>
+static int launch_decompress_umma_t(const DecompressArgs& a, cudaStream_t st) {
+  constexpr size_t smem = dec_smem_bytes<NT>();
+  if (cudaFuncSetAttribute(decompress_umma_kernel<BITS, SIGNS, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem)) != cudaSuccess)
+    return QKV_ELAUNCH;
+  const int64_t tiles = (a.n_vec + kUTile - 1) / kUTile;
+  const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
+  decompress_umma_kernel<BITS, SIGNS, NT><<<grid, kUThreads, smem, st>>>(a);
+  return check_launch();
+}
+
+template <int BITS>
+static int launch_decompress_umma_b(const DecompressArgs& a, cudaStream_t st) {
+  const bool exact = a.out_dtype == QKV_F32;
+  if (a.signs) return exact ? launch_decompress_umma_t<BITS, true, 3>(a, st) : launch_decompress_umma_t<BITS, true, 2>(a, st);
+  return exact ? launch_decompress_umma_t<BITS, false, 3>(a, st) : launch_decompress_umma_t<BITS, false, 2>(a, st);
+}
+
+int launch_decompress_umma(const DecompressArgs& a, cudaStream_t st) {
+  switch (a.bits0) {
+    case 1: return launch_decompress_umma_b<1>(a, st);
+    case 2: return launch_decompress_umma_b<2>(a, st);
+    case 3: return launch_decompress_umma_b<3>(a, st);
+    default: return launch_decompress_umma_b<4>(a, st);
+  }
 }
 
 }  // namespace qkv
