@@ -33,7 +33,6 @@ constexpr int kUThreads = 512;                    // four threads per vector: 32
 constexpr int kUWarps = kUThreads / 32;
 constexpr uint32_t kUPlaneBytes = 128 * 128 * 2;  // one bf16 operand tile (two 64-wide K blocks)
 constexpr uint32_t kUTmemCols = 256;
-constexpr int kUQueueCap = 64;
 
 // Bucket table of this kernel: 16384 buckets of width 1/8192 over [-1, 1).  The low nibble of an entry is
 // the code of the bucket; bit 7 flags a bucket whose coordinates need a second look, of kind
@@ -86,8 +85,12 @@ static __device__ __noinline__ uint32_t classify_flagged(const float* bnd, const
   return code | (sign << 8) | (near ? 1u << 16 : 0u);
 }
 
+// NT = bf16 terms of the A operand: 1 for bf16 input (two tile buffers), 3 for fp32 / fp16 input (one
+// buffer of three planes; together with Pi's three planes that is 192 KB).
+template <int NT> __host__ __device__ constexpr int queue_cap() { return NT == 1 ? 64 : 32; }
+
 struct UmmaSmem {
-  unsigned char* a[2];      // A tiles (bf16, swizzled), 1024-byte aligned
+  unsigned char* a[2][3];   // A tiles [buffer][term] (bf16, swizzled), 1024-byte aligned
   unsigned char* b[3];      // Pi planes h, m, l
   uint4* queue;             // [warps][kUQueueCap]
   double* ssq;              // [2 tiles][4 quarters][128 rows] partial sums of squares
@@ -99,16 +102,25 @@ struct UmmaSmem {
 };
 
 // dynamic part; the bucket table and the small tables are static shared arrays (constant addresses)
-constexpr size_t kUmmaSmemBytes = 1024 + 5 * kUPlaneBytes + kUWarps * kUQueueCap * 16 + 2 * 4 * 128 * 8 + 16 +
-                                  kUWarps * 4 + 2 * 8 + 16;
+template <int NT>
+constexpr size_t umma_smem_bytes() {
+  return 1024 + (NT == 1 ? 5 : 6) * kUPlaneBytes + kUWarps * queue_cap<NT>() * 16 + 2 * 4 * 128 * 8 + 16 +
+         kUWarps * 4 + 2 * 8 + 16;
+}
 
+template <int NT>
 __device__ __forceinline__ UmmaSmem carve_umma(unsigned char* raw) {
   UmmaSmem s;
   unsigned char* p = raw + ((1024u - (umma::smem_u32(raw) & 1023u)) & 1023u);
-  s.a[0] = p; s.a[1] = p + kUPlaneBytes;
-  for (int t = 0; t < 3; ++t) s.b[t] = p + (2 + t) * kUPlaneBytes;
-  p += 5 * kUPlaneBytes;
-  s.queue = reinterpret_cast<uint4*>(p); p += kUWarps * kUQueueCap * 16;
+  for (int bf = 0; bf < 2; ++bf)
+    for (int t = 0; t < 3; ++t) s.a[bf][t] = nullptr;
+  if (NT == 1) {
+    s.a[0][0] = p; s.a[1][0] = p + kUPlaneBytes; p += 2 * kUPlaneBytes;
+  } else {
+    for (int t = 0; t < 3; ++t) { s.a[0][t] = p; p += kUPlaneBytes; }
+  }
+  for (int t = 0; t < 3; ++t) { s.b[t] = p; p += kUPlaneBytes; }
+  s.queue = reinterpret_cast<uint4*>(p); p += kUWarps * queue_cap<NT>() * 16;
   s.ssq = reinterpret_cast<double*>(p); p += 2 * 4 * 128 * 8;
   s.smask = reinterpret_cast<uint32_t*>(p); p += 16;
   s.mbar = reinterpret_cast<uint64_t*>(p); p += 16;
@@ -118,12 +130,13 @@ __device__ __forceinline__ UmmaSmem carve_umma(unsigned char* raw) {
   return s;
 }
 
-template <int BITS, bool IP>
+template <int BITS, bool IP, int NT>
 __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int8_t lut_s[kLutSize];
   __shared__ float bnd_s[16], cent_s[16], sgn_s[kRD];
-  const UmmaSmem s = carve_umma(smem_raw);
+  const UmmaSmem s = carve_umma<NT>(smem_raw);
+  constexpr int kUQueueCap = queue_cap<NT>();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int trow = 32 * (warp & 3) + lane;          // vector of the tile = tensor-memory lane
   const int blk = warp >> 2;                        // output coordinates 32 blk .. 32 blk + 31
@@ -212,7 +225,7 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
       const int64_t n = v0 + r;
       const bool live = n < a.n_vec;
       const __nv_bfloat16* src = xg + (live ? n : 0) * a.x_pitch + c16 * 8;
-      cp_async16(s.a[buf] + umma::sw128_offset(r, c16 * 8, 128), src, live ? 16 : 0);
+      cp_async16(s.a[buf][0] + umma::sw128_offset(r, c16 * 8, 128), src, live ? 16 : 0);
     }
     cp_async_commit();
   };
@@ -222,7 +235,7 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
     double ss = 0.0;
 #pragma unroll
     for (int c8 = 0; c8 < 4; ++c8) {
-      const uint4 v = *reinterpret_cast<const uint4*>(s.a[buf] + umma::sw128_offset(trow, 32 * blk + c8 * 8, 128));
+      const uint4 v = *reinterpret_cast<const uint4*>(s.a[buf][0] + umma::sw128_offset(trow, 32 * blk + c8 * 8, 128));
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -233,20 +246,61 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
     }
     s.ssq[(buf * 4 + blk) * 128 + trow] = ss;
   };
+  // fp32 / fp16 input: this thread's 32 coordinates of row trow, split exactly into three bf16 terms and
+  // written to the three A planes; their squares go to the partial sums of tile parity `par`.
+  auto load_split_tile = [&](int64_t tile, int par) {
+    const int64_t n = tile * kUTile + trow;
+    const bool live = n < a.n_vec;
+    double ss = 0.0;
+#pragma unroll
+    for (int c8 = 0; c8 < 4; ++c8) {
+      float v[8];
+      if (a.x_dtype == QKV_F32) {
+        const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.x) +
+                                                            (live ? n : 0) * a.x_pitch + 32 * blk + 8 * c8);
+        const float4 u0 = live ? __ldg(src) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 u1 = live ? __ldg(src + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+        v[0] = u0.x; v[1] = u0.y; v[2] = u0.z; v[3] = u0.w; v[4] = u1.x; v[5] = u1.y; v[6] = u1.z; v[7] = u1.w;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          v[e] = live ? load_float(a.x, a.x_dtype, n * a.x_pitch + 32 * blk + 8 * c8 + e) : 0.f;
+      }
+      uint32_t pk[3][4];
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        __nv_bfloat16 h0, m0, l0, h1, m1, l1;
+        split3(v[2 * p], h0, m0, l0);
+        split3(v[2 * p + 1], h1, m1, l1);
+        pk[0][p] = pack_bf16(h0, h1); pk[1][p] = pack_bf16(m0, m1); pk[2][p] = pack_bf16(l0, l1);
+        ss += static_cast<double>(v[2 * p]) * static_cast<double>(v[2 * p]) +
+              static_cast<double>(v[2 * p + 1]) * static_cast<double>(v[2 * p + 1]);
+      }
+      const uint32_t off = umma::sw128_offset(trow, 32 * blk + 8 * c8, 128);
+#pragma unroll
+      for (int t = 0; t < 3; ++t)
+        *reinterpret_cast<uint4*>(s.a[0][t] + off) = make_uint4(pk[t][0], pk[t][1], pk[t][2], pk[t][3]);
+    }
+    s.ssq[(par * 4 + blk) * 128 + trow] = ss;
+  };
   auto row_norm = [&](int buf) {
     const double* q = s.ssq + buf * 4 * 128 + trow;
     return fmaxf(static_cast<float>(sqrt((q[0] + q[128]) + (q[256] + q[384]))), 1e-8f);
   };
 
-  // Thread 0: the 24 MMAs of one tile (A * l, A * m, A * h), then the completion arrival.
-  auto issue_mmas = [&](int buf) {
+  // Thread 0: the MMAs of one tile, smallest products first (bf16 input: A*l, A*m, A*h; split input:
+  // m*m, l*h, h*l, m*h, h*m, h*h), then the completion arrival on the accumulator's barrier.
+  auto issue_mmas = [&](int abuf, int acc_buf) {
     constexpr uint32_t idesc = umma::instr_desc(umma::kFmtBF16, 128, 128);
-    const uint32_t d = tmem_base + buf * 128;
-    const uint32_t a_addr = umma::smem_u32(s.a[buf]);
+    const uint32_t d = tmem_base + acc_buf * 128;
+    constexpr int n_prod = NT == 1 ? 3 : 6;
+    constexpr int pa1[3] = {0, 0, 0}, pb1[3] = {2, 1, 0};
+    constexpr int pa3[6] = {1, 2, 0, 1, 0, 0}, pb3[6] = {1, 0, 2, 0, 1, 0};
     bool acc = false;
 #pragma unroll
-    for (int t = 2; t >= 0; --t) {
-      const uint32_t b_addr = umma::smem_u32(s.b[t]);
+    for (int pr = 0; pr < n_prod; ++pr) {
+      const int ta = NT == 1 ? pa1[pr] : pa3[pr], tb = NT == 1 ? pb1[pr] : pb3[pr];
+      const uint32_t a_addr = umma::smem_u32(s.a[abuf][ta]), b_addr = umma::smem_u32(s.b[tb]);
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
         const uint32_t off = (ks >> 2) * (128 * 128) + (ks & 3) * 32;
@@ -254,7 +308,7 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
         acc = true;
       }
     }
-    umma::commit(&s.mbar[buf]);
+    umma::commit(&s.mbar[acc_buf]);
   };
 
   // Classify / pack / store this thread's 32 coordinates of row trow of a finished tile.  use_tmem ==
@@ -364,51 +418,68 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
   };
 
   // ---- pipeline over this CTA's tiles ------------------------------------------------------------------
-  // iteration i: wait A(i); issue MMAs(i); squares(i); [wait MMAs(i-1); prefetch A(i+1); epilogue(i-1)]
   uint32_t phase[2] = {0u, 0u};
   int64_t prev_tile = -1;
   int i = 0;
-  if (blockIdx.x < n_tiles) load_tile(blockIdx.x, 0);
-  for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++i) {
-    const int buf = i & 1;
-    cp_async_wait<0>();
-    umma::fence_smem_to_async();
-    umma::fence_before_sync();
-    __syncthreads();                      // A(i) complete and visible; epilogue(i-2) has left accumulator `buf`
-    const bool dead = *s.dead != 0;
-    if (tid == 0 && !dead) {
-      umma::fence_after_sync();
-      issue_mmas(buf);
+  auto wait_acc = [&](int acc_buf) {      // bounded wait for the MMAs that write accumulator acc_buf
+    bool ok = *s.dead == 0;
+    if (ok) {
+      ok = umma::mbar_wait(&s.mbar[acc_buf], phase[acc_buf]);
+      phase[acc_buf] ^= 1u;
+      if (!ok) { *s.dead = 1; atomicAdd(&g_umma_timeouts, 1u); }
     }
-    const float norm_prev = prev_tile >= 0 ? row_norm(buf ^ 1) : 1.f;     // squares(i-1) were left before the barrier
-    part_squares(buf);
-    const int64_t next = tile + gridDim.x;
-    if (prev_tile >= 0) {
-      bool ok = !dead;
-      if (ok) {
-        ok = umma::mbar_wait(&s.mbar[buf ^ 1], phase[buf ^ 1]);
-        phase[buf ^ 1] ^= 1u;
-        if (!ok) { *s.dead = 1; atomicAdd(&g_umma_timeouts, 1u); }
+    umma::fence_after_sync();
+    return ok;
+  };
+  if (NT == 1) {
+    // iteration i: wait A(i); issue MMAs(i); squares(i); [wait MMAs(i-1); prefetch A(i+1); epilogue(i-1)]
+    if (blockIdx.x < n_tiles) load_tile(blockIdx.x, 0);
+    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++i) {
+      const int buf = i & 1;
+      cp_async_wait<0>();
+      umma::fence_smem_to_async();
+      umma::fence_before_sync();
+      __syncthreads();                    // A(i) complete and visible; epilogue(i-2) has left accumulator `buf`
+      if (tid == 0 && *s.dead == 0) {
+        umma::fence_after_sync();
+        issue_mmas(buf, buf);
       }
-      umma::fence_after_sync();
-      if (next < n_tiles) load_tile(next, buf ^ 1);       // A(i-1) has been consumed
-      epilogue(prev_tile, buf ^ 1, norm_prev, ok);
-    } else if (next < n_tiles) {
-      load_tile(next, buf ^ 1);
+      const float norm_prev = prev_tile >= 0 ? row_norm(buf ^ 1) : 1.f;   // squares(i-1) were left before the barrier
+      part_squares(buf);
+      const int64_t next = tile + gridDim.x;
+      if (prev_tile >= 0) {
+        const bool ok = wait_acc(buf ^ 1);
+        if (next < n_tiles) load_tile(next, buf ^ 1);     // A(i-1) has been consumed
+        epilogue(prev_tile, buf ^ 1, norm_prev, ok);
+      } else if (next < n_tiles) {
+        load_tile(next, buf ^ 1);
+      }
+      prev_tile = tile;
     }
-    prev_tile = tile;
+  } else {
+    // iteration i: wait MMAs(i-1) (they read the only A buffer); load + split A(i); issue MMAs(i); epilogue(i-1)
+    bool prev_ok = true;
+    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++i) {
+      const int par = i & 1;
+      if (prev_tile >= 0) prev_ok = wait_acc(par ^ 1);
+      load_split_tile(tile, par);
+      umma::fence_smem_to_async();
+      umma::fence_before_sync();
+      __syncthreads();                    // A(i) and its squares complete; epilogue(i-2) has left accumulator `par`
+      if (tid == 0 && *s.dead == 0) {
+        umma::fence_after_sync();
+        issue_mmas(0, par);
+      }
+      if (prev_tile >= 0) epilogue(prev_tile, par ^ 1, row_norm(par ^ 1), prev_ok);
+      prev_tile = tile;
+    }
   }
   if (prev_tile >= 0) {
     const int buf = (i - 1) & 1;
     __syncthreads();                      // squares of the last tile
-    const float norm_prev = row_norm(buf);
-    bool ok = *s.dead == 0;
-    if (ok) {
-      ok = umma::mbar_wait(&s.mbar[buf], phase[buf]);
-      if (!ok) { *s.dead = 1; atomicAdd(&g_umma_timeouts, 1u); }
-    }
-    umma::fence_after_sync();
-    epilogue(prev_tile, buf, norm_prev, ok);
+    const float norm_last = row_norm(buf);
+    const bool ok = wait_acc(buf);
+    epilogue(prev_tile, buf, norm_last, ok);
   }
   __syncwarp();
   const int queued = s.qcount[warp];
@@ -421,19 +492,25 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
 bool compress_umma_ok(const CompressArgs& a) {
   const uintptr_t al = reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.codes) |
                        (a.mode == MODE_IP ? reinterpret_cast<uintptr_t>(a.signs) : 0);
-  return a.d == kRD && a.mode != MODE_MIXED && a.packed && a.x_dtype == QKV_BF16 && a.n_vec >= 1024 &&
-         a.n_vec < (int64_t(1) << 31) && (a.x_pitch & 7) == 0 && (al & 15u) == 0;
+  return a.d == kRD && a.mode != MODE_MIXED && a.packed && a.n_vec >= 1024 && a.n_vec < (int64_t(1) << 31) &&
+         (a.x_pitch & 7) == 0 && (al & 15u) == 0;
+}
+
+template <int BITS, bool IP, int NT>
+static int launch_compress_umma_n(const CompressArgs& a, cudaStream_t st) {
+  constexpr size_t smem = umma_smem_bytes<NT>();
+  if (cudaFuncSetAttribute(compress_umma_kernel<BITS, IP, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem)) != cudaSuccess)
+    return QKV_ELAUNCH;
+  const int64_t tiles = (a.n_vec + kUTile - 1) / kUTile;
+  const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
+  compress_umma_kernel<BITS, IP, NT><<<grid, kUThreads, smem, st>>>(a);
+  return check_launch();
 }
 
 template <int BITS, bool IP>
 static int launch_compress_umma_t(const CompressArgs& a, cudaStream_t st) {
-  if (cudaFuncSetAttribute(compress_umma_kernel<BITS, IP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(kUmmaSmemBytes)) != cudaSuccess)
-    return QKV_ELAUNCH;
-  const int64_t tiles = (a.n_vec + kUTile - 1) / kUTile;
-  const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
-  compress_umma_kernel<BITS, IP><<<grid, kUThreads, kUmmaSmemBytes, st>>>(a);
-  return check_launch();
+  return a.x_dtype == QKV_BF16 ? launch_compress_umma_n<BITS, IP, 1>(a, st) : launch_compress_umma_n<BITS, IP, 3>(a, st);
 }
 
 int launch_compress_umma(const CompressArgs& a, cudaStream_t st) {
