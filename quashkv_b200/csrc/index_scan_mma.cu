@@ -63,10 +63,11 @@ __device__ __forceinline__ void raise_threshold(float* thr, float t) {
 // Warp-wide selection inside one candidate buffer of n <= CAPW entries (optimistic score, row).
 // Ranks every entry (higher score first, equal scores by slot), takes T = (k-th best) - slack
 // (-inf while n < k), and rewrites the buffer as the entries with score >= T in rank order.
-// Returns how many there are; only the first `limit` of them are stored.
+// Returns how many there are; only the first `limit` of them are stored.  `floor` raises T (rows below a
+// bound that is already known need not be kept); T4 = (k4-th best) - slack, from before the raise.
 template <int CAPW>
 __device__ __forceinline__ int select_sorted(float* bu, uint16_t* br, int n, int k, float slack, int limit,
-                                             float& T, int lane) {
+                                             float floor, int k4, float& T, float& T4, int lane) {
   constexpr int ENT = (CAPW + 31) / 32;
   float u[ENT]; int r[ENT], rank[ENT];
 #pragma unroll
@@ -81,16 +82,19 @@ __device__ __forceinline__ int select_sorted(float* bu, uint16_t* br, int n, int
 #pragma unroll
     for (int e = 0; e < ENT; ++e) rank[e] += better(uj, j, u[e], lane + 32 * e) ? 1 : 0;
   }
-  float kth = -INFINITY;
-  if (n >= k) {
+  float kth = -INFINITY, k4th = -INFINITY;
 #pragma unroll
-    for (int e = 0; e < ENT; ++e) {
-      const unsigned m = __ballot_sync(QKV_FULL_MASK, lane + 32 * e < n && rank[e] == k - 1);
-      const float v = __shfl_sync(QKV_FULL_MASK, u[e], m ? __ffs(m) - 1 : 0);
-      if (m) kth = v;
-    }
+  for (int e = 0; e < ENT; ++e) {
+    const bool in = lane + 32 * e < n;
+    const unsigned m = __ballot_sync(QKV_FULL_MASK, in && rank[e] == k - 1);
+    const unsigned m4 = __ballot_sync(QKV_FULL_MASK, in && rank[e] == k4 - 1);
+    const float v = __shfl_sync(QKV_FULL_MASK, u[e], m ? __ffs(m) - 1 : 0);
+    const float v4 = __shfl_sync(QKV_FULL_MASK, u[e], m4 ? __ffs(m4) - 1 : 0);
+    if (m) kth = v;
+    if (m4) k4th = v4;
   }
-  T = n >= k ? kth - slack : -INFINITY;
+  T = fmaxf(n >= k ? kth - slack : -INFINITY, floor);
+  T4 = n >= k4 ? k4th - slack : -INFINITY;
   int kept = 0;
   bool keep[ENT];
 #pragma unroll
@@ -118,6 +122,7 @@ index_scan_mma_kernel(ScanMmaArgs a) {
   __shared__ float init_c[kIQ];          // kEps - sum of the sign weights of the unit query
   __shared__ float thr[kIQ];             // lower bound of the k-th best pessimistic score
   __shared__ int cnt[kIWarps][kIQ];
+  __shared__ float quart[kIWarps][kIQ];  // per warp: lower bound of its ceil(k/4)-th best pessimistic score
   __shared__ float nmax_w[kIWarps];
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -160,7 +165,9 @@ index_scan_mma_kernel(ScanMmaArgs a) {
     }
   }
   cnt[warp][lane] = 0;
+  quart[warp][lane] = -INFINITY;
   __syncthreads();
+  const int k4 = (a.k + 3) / 4;
 
   const int64_t n_begin = slice * a.slice_len;
   int64_t n_end = n_begin + a.slice_len;
@@ -304,9 +311,13 @@ index_scan_mma_kernel(ScanMmaArgs a) {
         const int q = __ffs(need) - 1;
         need &= need - 1;
         const int n = cnt[warp][q] < CAPW ? cnt[warp][q] : CAPW;
-        float T;
+        // Two valid lower bounds of the CTA's k-th best pessimistic score: this warp's own k-th best, and
+        // the smallest of the four warps' ceil(k/4)-th best (each warp then has that many rows at or
+        // above it, and the warps' rows are disjoint).  The second is the tight one: a quarter of the
+        // rows yields the k/4-th best at about the height of the whole CTA's k-th best.
+        float T, T4;
         const int kept = select_sorted<CAPW>(my_u + q * QS, my_r + q * QS, n, a.k, 2.f * kEps * nm,
-                                             CAPW - kIRoom, T, lane);
+                                             CAPW - kIRoom, thr[q], k4, T, T4, lane);
         if (lane == 0) {
           if (kept > CAPW - kIRoom) {             // more rows within the bound than a buffer holds
             if (q0 + q < a.M) a.flags[q0 + q] = 1;
@@ -314,7 +325,12 @@ index_scan_mma_kernel(ScanMmaArgs a) {
             cnt[warp][q] = 0;
           } else {
             cnt[warp][q] = kept;
-            raise_threshold(&thr[q], T);
+            quart[warp][q] = fmaxf(quart[warp][q], T4);
+            const float all4 = fminf(fminf(*reinterpret_cast<volatile float*>(&quart[0][q]),
+                                           *reinterpret_cast<volatile float*>(&quart[1][q])),
+                                     fminf(*reinterpret_cast<volatile float*>(&quart[2][q]),
+                                           *reinterpret_cast<volatile float*>(&quart[3][q])));
+            raise_threshold(&thr[q], fmaxf(T, all4));
           }
         }
       }
@@ -368,8 +384,8 @@ index_scan_mma_kernel(ScanMmaArgs a) {
     bool redo = T0 == INFINITY;
     int kept = 0;
     if (!redo) {
-      float T;
-      kept = select_sorted<QS>(bu, br, total, a.k, 2.f * kEps * nm_cta, out_k, T, lane);
+      float T, T4;
+      kept = select_sorted<QS>(bu, br, total, a.k, 2.f * kEps * nm_cta, out_k, T0, 1, T, T4, lane);
       redo = kept > out_k;
     }
     if (redo) { kept = 0; if (lane == 0) a.flags[q0 + q] = 1; }
