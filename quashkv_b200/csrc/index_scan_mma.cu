@@ -21,94 +21,11 @@
 // flagged, and the CUDA-core scan redoes exactly the flagged queries.
 #include <math.h>
 
-#include "attention_common.cuh"
-#include "mma_decode.cuh"
+#include <stdlib.h>
+
+#include "index_candidates.cuh"
 
 namespace qkv {
-
-constexpr int kIQ = 32;                 // queries per CTA
-constexpr int kIWarps = 4;
-constexpr int kIStages = 3;
-constexpr int kIStageBytes = 512 + 256 + 64;     // 16 rows: codes, signs, norms
-constexpr int kIExtra = 16;             // list slots beyond k per (query, slice)
-constexpr int kIRoom = 16;              // free slots a warp buffer must have before a tile (16 rows)
-constexpr float kEps = 4e-4f;           // bound of |approximate - fp32 score| / norm for a unit query
-constexpr int64_t kIMaxSlice = 65536;   // rows per slice: candidates are stored as 16-bit offsets
-
-struct ScanMmaArgs {
-  const float* qk;       // [M][2][128] rotated queries (scale 1)
-  int M, k;
-  const uint8_t* codes; const uint8_t* signs; const float* norms;
-  int64_t N; int64_t slice_len; int n_slices;
-  const uint32_t* tables;              // key table (fp16 pairs) and 1/scale
-  float* list_scores; int64_t* list_ids;   // [M][n_slices][k + kIExtra]
-  int* flags;                          // [M] set to 1 for queries the CUDA-core scan must redo
-};
-
-__device__ __forceinline__ bool better(float sa, int ia, float sb, int ib) {
-  return sa > sb || (sa == sb && ia < ib);
-}
-
-// Raises the shared threshold to at least t (bounded retries: the threshold is only a filter).
-__device__ __forceinline__ void raise_threshold(float* thr, float t) {
-  int* p = reinterpret_cast<int*>(thr);
-  int old = *reinterpret_cast<volatile int*>(p);
-  for (int tries = 0; tries < 8 && __int_as_float(old) < t; ++tries) {
-    const int seen = atomicCAS(p, old, __float_as_int(t));
-    if (seen == old) break;
-    old = seen;
-  }
-}
-
-// Warp-wide selection inside one candidate buffer of n <= CAPW entries (optimistic score, row).
-// Ranks every entry (higher score first, equal scores by slot), takes T = (k-th best) - slack
-// (-inf while n < k), and rewrites the buffer as the entries with score >= T in rank order.
-// Returns how many there are; only the first `limit` of them are stored.  `floor` raises T (rows below a
-// bound that is already known need not be kept); T4 = (k4-th best) - slack, from before the raise.
-template <int CAPW>
-__device__ __forceinline__ int select_sorted(float* bu, uint16_t* br, int n, int k, float slack, int limit,
-                                             float floor, int k4, float& T, float& T4, int lane) {
-  constexpr int ENT = (CAPW + 31) / 32;
-  float u[ENT]; int r[ENT], rank[ENT];
-#pragma unroll
-  for (int e = 0; e < ENT; ++e) {
-    const int slot = lane + 32 * e;
-    u[e] = slot < n ? bu[slot] : -INFINITY;
-    r[e] = slot < n ? br[slot] : 0;
-    rank[e] = 0;
-  }
-  for (int j = 0; j < n; ++j) {
-    const float uj = bu[j];
-#pragma unroll
-    for (int e = 0; e < ENT; ++e) rank[e] += better(uj, j, u[e], lane + 32 * e) ? 1 : 0;
-  }
-  float kth = -INFINITY, k4th = -INFINITY;
-#pragma unroll
-  for (int e = 0; e < ENT; ++e) {
-    const bool in = lane + 32 * e < n;
-    const unsigned m = __ballot_sync(QKV_FULL_MASK, in && rank[e] == k - 1);
-    const unsigned m4 = __ballot_sync(QKV_FULL_MASK, in && rank[e] == k4 - 1);
-    const float v = __shfl_sync(QKV_FULL_MASK, u[e], m ? __ffs(m) - 1 : 0);
-    const float v4 = __shfl_sync(QKV_FULL_MASK, u[e], m4 ? __ffs(m4) - 1 : 0);
-    if (m) kth = v;
-    if (m4) k4th = v4;
-  }
-  T = fmaxf(n >= k ? kth - slack : -INFINITY, floor);
-  T4 = n >= k4 ? k4th - slack : -INFINITY;
-  int kept = 0;
-  bool keep[ENT];
-#pragma unroll
-  for (int e = 0; e < ENT; ++e) {
-    keep[e] = lane + 32 * e < n && u[e] >= T;
-    kept += __popc(__ballot_sync(QKV_FULL_MASK, keep[e]));
-  }
-  __syncwarp();
-#pragma unroll
-  for (int e = 0; e < ENT; ++e)
-    if (keep[e] && rank[e] < limit) { bu[rank[e]] = u[e]; br[rank[e]] = static_cast<uint16_t>(r[e]); }
-  __syncwarp();
-  return kept;
-}
 
 template <int CAPW>
 __global__ void __launch_bounds__(kIWarps * 32, CAPW <= 32 ? 4 : (CAPW <= 48 ? 3 : 2))
@@ -285,6 +202,12 @@ index_scan_mma_kernel(ScanMmaArgs a) {
         }
       }
     }
+    // ---- the other slices' progress: lane = query --------------------------------------------------------------
+    if ((it & 3) == 0 && q0 + lane < a.M) {
+      const float g = *reinterpret_cast<const volatile float*>(a.gthr + q0 + lane);
+      if (g > thr[lane] && thr[lane] != INFINITY) raise_threshold(&thr[lane], g);
+    }
+    __syncwarp();
     // ---- candidates: optimistic score at or above the query's threshold ---------------------------------
     const int rel = first_rel + it * kStep;
 #pragma unroll
@@ -296,7 +219,12 @@ index_scan_mma_kernel(ScanMmaArgs a) {
         const float u = c[nt][e] * kn[e >> 1];
         if (u >= ((e & 1) ? t2.y : t2.x) && r < n_valid) {
           const int pos = atomicAdd(&cnt[warp][q], 1);
-          if (pos < CAPW) { my_u[q * QS + pos] = u; my_r[q * QS + pos] = static_cast<uint16_t>(r); }
+          if (pos < CAPW) {
+            my_u[q * QS + pos] = u; my_r[q * QS + pos] = static_cast<uint16_t>(r);
+          } else {                                  // full before it could be pruned (see the prune mark): redo the query
+            if (q0 + q < a.M) a.flags[q0 + q] = 1;
+            thr[q] = INFINITY;
+          }
         }
       }
     }
@@ -330,7 +258,9 @@ index_scan_mma_kernel(ScanMmaArgs a) {
                                            *reinterpret_cast<volatile float*>(&quart[1][q])),
                                      fminf(*reinterpret_cast<volatile float*>(&quart[2][q]),
                                            *reinterpret_cast<volatile float*>(&quart[3][q])));
-            raise_threshold(&thr[q], fmaxf(T, all4));
+            const float bound = fmaxf(T, all4);
+            raise_threshold(&thr[q], bound);
+            if (q0 + q < a.M && bound > -INFINITY) publish_bound(a.gthr + q0 + q, bound);
           }
         }
       }
@@ -440,12 +370,20 @@ struct ScanMmaPlan {
   size_t total() const { return hdr_bytes + flag_bytes + qk_bytes + ls_bytes + li_bytes + fallback_bytes; }
 };
 
-static ScanMmaPlan make_mma_plan(int64_t N, int M, int k) {
+// The tcgen05 scan (index_scan_umma.cu) gives the same results but is slower than the mma.sync scan at
+// present, so it only runs when QUASHKV_B200_INDEX_TCGEN05=1 asks for it.
+static bool scan_on_tcgen05(int k) {
+  const char* e = getenv("QUASHKV_B200_INDEX_TCGEN05");
+  return index_umma_ok(k) && e && e[0] == '1';
+}
+
+static ScanMmaPlan make_mma_plan(int64_t N, int M, int k, bool tcgen05) {
   ScanMmaPlan p;
-  p.n_qtiles = (M + kIQ - 1) / kIQ;
+  p.n_qtiles = tcgen05 ? index_umma_qtiles(M) : (M + kIQ - 1) / kIQ;
   const int capw = capw_for(k);
   const int ctas_per_sm = capw <= 32 ? 4 : (capw <= 48 ? 3 : 2);
-  int64_t want = (ctas_per_sm * kNumSMs * 2 + p.n_qtiles - 1) / p.n_qtiles;      // about two waves
+  int64_t want = tcgen05 ? (4 * kNumSMs) / p.n_qtiles                             // one CTA per SM, four rounds
+                         : (ctas_per_sm * kNumSMs * 2 + p.n_qtiles - 1) / p.n_qtiles;   // about two waves
   const int64_t chunk = 256;
   const int64_t max_by_len = (N + 8 * chunk - 1) / (8 * chunk);
   const int64_t min_by_len = (N + kIMaxSlice - 1) / kIMaxSlice;
@@ -458,7 +396,7 @@ static ScanMmaPlan make_mma_plan(int64_t N, int M, int k) {
   p.n_slices = static_cast<int>((N + len - 1) / len);
   const size_t per = static_cast<size_t>(M) * p.n_slices * (k + kIExtra);
   p.hdr_bytes = 256;
-  p.flag_bytes = (static_cast<size_t>(M) * sizeof(int) + 255) / 256 * 256;
+  p.flag_bytes = 2 * ((static_cast<size_t>(M) * sizeof(int) + 255) / 256 * 256);      // flags, then the shared bounds
   p.qk_bytes = (static_cast<size_t>(M) * 256 * sizeof(float) + 255) / 256 * 256;
   p.ls_bytes = (per * sizeof(float) + 255) / 256 * 256;
   p.li_bytes = (per * sizeof(int64_t) + 255) / 256 * 256;
@@ -473,7 +411,10 @@ bool index_mma_ok(int d, int bits, int64_t N, int k, const void* codes, const vo
 }
 
 size_t index_mma_workspace_bytes(int64_t N, int M, int k) {
-  return make_mma_plan(N, M, k < kIMaxK ? k : kIMaxK).total();
+  const int kk = k < kIMaxK ? k : kIMaxK;
+  const size_t a = make_mma_plan(N, M, kk, false).total();
+  const size_t b = index_umma_ok(kk) ? make_mma_plan(N, M, kk, true).total() : 0;
+  return a > b ? a : b;                      // the environment may select either kernel
 }
 
 template <int CAPW>
@@ -491,26 +432,32 @@ int launch_index_scan_mma(const float* queries, int M, const uint8_t* codes, con
                           const float* norms, int64_t N, const float* Pi, const float* cent, const float* S,
                           float qjl_scale, int k, int64_t id_base, float* out_scores, int64_t* out_ids,
                           void* workspace, size_t workspace_bytes, cudaStream_t st) {
-  const ScanMmaPlan p = make_mma_plan(N, M, k);
+  const bool tcgen05 = scan_on_tcgen05(k);
+  const ScanMmaPlan p = make_mma_plan(N, M, k, tcgen05);
   if (workspace_bytes < p.total()) return QKV_EWORKSPACE;
   unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
   uint32_t* tables = reinterpret_cast<uint32_t*>(ws);
   int* flags = reinterpret_cast<int*>(ws + p.hdr_bytes);
   float* qk = reinterpret_cast<float*>(ws + p.hdr_bytes + p.flag_bytes);
   unsigned char* lists = ws + p.hdr_bytes + p.flag_bytes + p.qk_bytes;
-  if (cudaMemsetAsync(flags, 0, static_cast<size_t>(M) * sizeof(int), st) != cudaSuccess) return QKV_ELAUNCH;
+  float* gthr = reinterpret_cast<float*>(ws + p.hdr_bytes + p.flag_bytes / 2);
+  index_init_kernel<<<(M + 255) / 256, 256, 0, st>>>(flags, gthr, M);
   int rc = launch_rotate_with_tables(queries, QKV_F32, M, 128, Pi, S, qjl_scale, 1.f, qk, cent, cent, tables, st);
   if (rc) return rc;
   ScanMmaArgs a{};
   a.qk = qk; a.M = M; a.k = k; a.codes = codes; a.signs = signs; a.norms = norms; a.N = N;
-  a.slice_len = p.slice_len; a.n_slices = p.n_slices; a.tables = tables; a.flags = flags;
+  a.slice_len = p.slice_len; a.n_slices = p.n_slices; a.tables = tables; a.flags = flags; a.gthr = gthr;
   a.list_scores = reinterpret_cast<float*>(lists);
   a.list_ids = reinterpret_cast<int64_t*>(lists + p.ls_bytes);
   const dim3 grid(p.n_slices, p.n_qtiles);
-  switch (capw_for(k)) {
-    case 32: rc = launch_scan_mma<32>(a, grid, st); break;
-    case 48: rc = launch_scan_mma<48>(a, grid, st); break;
-    default: rc = launch_scan_mma<80>(a, grid, st); break;
+  if (tcgen05) {
+    rc = launch_index_scan_umma(a, p.n_qtiles, st);
+  } else {
+    switch (capw_for(k)) {
+      case 32: rc = launch_scan_mma<32>(a, grid, st); break;
+      case 48: rc = launch_scan_mma<48>(a, grid, st); break;
+      default: rc = launch_scan_mma<80>(a, grid, st); break;
+    }
   }
   if (rc) return rc;
   const int per_query = p.n_slices * (k + kIExtra);

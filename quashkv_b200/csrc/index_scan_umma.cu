@@ -1,0 +1,378 @@
+// Index scan on the fifth-generation tensor cores (tcgen05) for dim 128, 3 bits, k <= 12.
+//
+// Same contract as the mma.sync scan (index_scan_mma.cu): approximate fp16 scores only propose
+// candidates under a proven error bound, the survivors are re-scored exactly afterwards.  What
+// changes is who does the contraction.  One CTA per SM owns 64 queries (MMA N) and a slice of the
+// database; per tile of 128 rows (MMA M) the 256 threads decode the packed rows ONCE into the
+// swizzled fp16 operand layout in shared memory (K = 256: 128 centroid values, then the sign bits
+// as the shift-free single-bit fp16 patterns), one thread issues 16 tcgen05.mma (128 x 64 x 16)
+// into one of two tensor-memory accumulators, and while those run the threads read the previous
+// accumulator back (thread = row, 32 query columns per warp) and test every score against the
+// query's threshold.  Decode work per (row, query) pair drops 4x against the mma.sync kernel (one
+// decode serves 64 queries instead of 32 and needs no per-fragment shuffling), the MMAs leave the
+// instruction stream, and the B operand is read by the tensor core instead of by LDS.
+// State: results are identical to the other scans (tests), but with 8 warps per SM and the candidate
+// bookkeeping in the epilogue this first version runs at about half the speed of the mma.sync scan,
+// so it is opt-in (QUASHKV_B200_INDEX_TCGEN05=1).
+//
+// Candidate bookkeeping is the mma.sync kernel's: per (row quarter, query) private buffers, a shared
+// rising threshold, flagged queries redone by the CUDA-core scan.  A warp sees 32 rows per tile, so
+// its first eight tiles are pushed in four lane groups with a prune in between.
+#include "index_candidates.cuh"
+#include "umma.cuh"
+
+namespace qkv {
+
+constexpr int kXQ = 64;                      // queries per CTA = MMA N
+constexpr int kXRows = 128;                  // rows per tile = MMA M
+constexpr int kXThreads = 256;               // warp w: row quarter w & 3 (its TMEM lanes), query block w >> 2
+constexpr int kXCap = 40;                    // candidate slots per (row quarter, query)
+constexpr int kXSlack = 24;                  // a buffer is pruned when fewer slots than this are free: a tile can
+                                             // add 32 rows at once, a handful in practice once the threshold is up
+constexpr uint32_t kXATile = kXRows * 256 * 2;   // 64 KB: four K blocks of 64 fp16
+constexpr uint32_t kXBTile = kXQ * 256 * 2;      // 32 KB
+constexpr uint32_t kXTmemCols = 128;         // two accumulators of 64 columns
+constexpr int kXMaxK = kXCap - kXSlack - 4;  // k + a few extra rows must fit below the prune mark
+
+constexpr size_t kXSmemBytes = 1024 + 2 * kXATile + kXBTile + static_cast<size_t>(kXQ) * 4 * kXCap * 6 + 2 * 8 + 16;
+
+__device__ unsigned int g_index_umma_timeouts = 0;
+
+// K position of the centroid part: k = 16 wd + 4 g + e  <->  coordinate 16 wd + g + 4 e (the order in which
+// one PRMT per pair produces the values of a 32-bit code word).
+__host__ __device__ constexpr int code_coord(int k) { return 16 * (k >> 4) + ((k & 15) >> 2) + 4 * (k & 3); }
+
+__global__ void __launch_bounds__(kXThreads, 1) index_scan_umma_kernel(ScanMmaArgs a) {
+  constexpr int D = 128;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ float2 init_thr[kXQ];        // .x = kEps - sum of sign weights (unit query), .y = threshold
+  __shared__ float inv_s[kXQ];
+  __shared__ int cnt[4][kXQ];
+  __shared__ float quart[4][kXQ];
+  __shared__ float nmax_w[kXThreads / 32];
+  unsigned char* base = smem_raw + ((1024u - (umma::smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* a_tile[2] = {base, base + kXATile};
+  unsigned char* b_tile = base + 2 * kXATile;
+  float* buf_u = reinterpret_cast<float*>(b_tile + kXBTile);                      // [query][row quarter][kXCap]
+  uint16_t* buf_r = reinterpret_cast<uint16_t*>(buf_u + kXQ * 4 * kXCap);
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(buf_r + kXQ * 4 * kXCap);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 2);
+  int* dead = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rq = warp & 3, cb = warp >> 2;
+  const int row = 32 * rq + lane;           // row of the tile = tensor-memory lane
+  const int slice = blockIdx.x, q0 = blockIdx.y * kXQ;
+  const float inv_sk = __uint_as_float(a.tables[6]);
+  const uint32_t kt_a = a.tables[0], kt_b = a.tables[1];
+  constexpr int QS = 4 * kXCap;
+
+  // ---- per query: unit scale, constant term, threshold ----------------------------------------------------
+  if (tid < kXQ) {
+    const int m = q0 + tid;
+    const float* q = a.qk + static_cast<int64_t>(m < a.M ? m : 0) * 2 * D;
+    float q2 = 0.f, ws = 0.f;
+    for (int j = 0; j < D; ++j) { q2 = fmaf(q[j], q[j], q2); ws += q[D + j]; }
+    const float qn = sqrtf(q2);
+    const bool usable = m < a.M && qn > 0.f && qn < INFINITY;
+    const float inv = usable ? 1.f / qn : 0.f;
+    inv_s[tid] = inv;
+    init_thr[tid] = make_float2(kEps - ws * inv, usable ? -INFINITY : INFINITY);
+    if (m < a.M && !usable) a.flags[m] = 1;
+  }
+  for (int i = tid; i < 4 * kXQ; i += kXThreads) { (&cnt[0][0])[i] = 0; (&quart[0][0])[i] = -INFINITY; }
+  if (tid == 0) {
+    umma::mbar_init(&mbar[0], 1);
+    umma::mbar_init(&mbar[1], 1);
+    *dead = 0;
+  }
+  __syncthreads();
+  // ---- B operand: 64 queries x 256 K, fp16, swizzled K-major (four blocks of 64 K = 8 KB each) ------------
+  for (int idx = tid; idx < kXQ * 256; idx += kXThreads) {
+    const int n = idx >> 8, k = idx & 255;
+    const int m = q0 + n;
+    const float* q = a.qk + static_cast<int64_t>(m < a.M ? m : 0) * 2 * D;
+    float v;
+    if (k < 128) {
+      v = q[code_coord(k)] * inv_s[n] * inv_sk;
+    } else {
+      const int kk = k - 128, s = kk >> 5, t = (kk & 31) >> 1, hb = kk & 1;
+      v = q[D + 32 * s + sign_coord(t) + 16 * hb] * inv_s[n] * (2.f / sign_v1(sign_pos(t)));
+    }
+    *reinterpret_cast<__half*>(b_tile + umma::sw128_offset(n, k, kXQ)) = __float2half_rn(v);
+  }
+  if (warp == 0) umma::tmem_alloc(tmem_slot, kXTmemCols);
+  umma::fence_smem_to_async();
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int64_t n_begin = slice * a.slice_len;
+  int64_t n_end = n_begin + a.slice_len;
+  if (n_end > a.N) n_end = a.N;
+  const int n_valid = static_cast<int>(n_end - n_begin);
+  const int n_tiles = (n_valid + kXRows - 1) / kXRows;
+  const uint4* codes = reinterpret_cast<const uint4*>(a.codes);
+  const uint2* signs = reinterpret_cast<const uint2*>(a.signs);
+  float my_nmax = 0.f;
+
+  // raw packed words of this thread's half row: code words 4 cb .. 4 cb + 3, sign words 2 cb, 2 cb + 1
+  auto fetch = [&](int tile, uint4& c, uint2& s, float& kn) {
+    const int r = tile * kXRows + row;
+    const bool ok = r < n_valid;
+    const int64_t n = n_begin + (ok ? r : 0);
+    c = ok ? __ldg(codes + n * 2 + cb) : make_uint4(0u, 0u, 0u, 0u);
+    s = ok ? __ldg(signs + n * 2 + cb) : make_uint2(0u, 0u);
+    kn = ok ? __ldg(a.norms + n) : 0.f;
+  };
+
+  auto decode = [&](const uint4& c, const uint2& s, int buf) {
+    unsigned char* arow = a_tile[buf] + row * 128;
+    const uint32_t cw[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+    for (int wd = 0; wd < 4; ++wd) {
+#pragma unroll
+      for (int gp = 0; gp < 2; ++gp) {
+        uint32_t o[4];
+#pragma unroll
+        for (int g2 = 0; g2 < 2; ++g2) {
+          const int g = 2 * gp + g2;
+          const uint32_t y = (cw[wd] >> (2 * g)) & 0x03030303u;
+          const uint32_t sl = y * 0x22u + 0x10101010u;
+          o[2 * g2] = prmt(kt_a, kt_b, sl);
+          o[2 * g2 + 1] = prmt(kt_a, kt_b, sl >> 16);
+        }
+        const int c16 = 2 * (4 * cb + wd) + gp;            // 16-byte chunk of the row, 0..15
+        *reinterpret_cast<uint4*>(arow + (c16 >> 3) * (kXRows * 128) + (((c16 & 7) ^ (row & 7)) << 4)) =
+            make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+    const uint32_t sw[2] = {s.x, s.y};
+#pragma unroll
+    for (int w2 = 0; w2 < 2; ++w2) {
+      const uint32_t cp[4] = {sw[w2], sw[w2] << 7, sw[w2] >> 1, sw[w2] << 13};
+#pragma unroll
+      for (int qd = 0; qd < 4; ++qd) {
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int t = 4 * qd + e;
+          const int cpy = t < 7 ? 0 : (t < 14 ? 1 : t - 12);
+          o[e] = cp[cpy] & (0x00010001u << sign_pos(t));
+        }
+        const int c16 = 16 + 4 * (2 * cb + w2) + qd;       // chunks 16..31: the sign part
+        *reinterpret_cast<uint4*>(arow + (c16 >> 3) * (kXRows * 128) + (((c16 & 7) ^ (row & 7)) << 4)) =
+            make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  };
+
+  auto issue_mmas = [&](int buf, int acc) {
+    constexpr uint32_t idesc = umma::instr_desc(umma::kFmtF16, kXRows, kXQ);
+    const uint32_t d = tmem_base + acc * kXQ;
+    const uint32_t a_addr = umma::smem_u32(a_tile[buf]), b_addr = umma::smem_u32(b_tile);
+#pragma unroll
+    for (int ks = 0; ks < 16; ++ks) {
+      const uint32_t a_off = (ks >> 2) * (kXRows * 128) + (ks & 3) * 32;
+      const uint32_t b_off = (ks >> 2) * (kXQ * 128) + (ks & 3) * 32;
+      umma::mma_f16(d, umma::smem_desc_sw128(a_addr + a_off), umma::smem_desc_sw128(b_addr + b_off), idesc, ks != 0);
+    }
+    umma::commit(&mbar[acc]);
+  };
+
+  // Shrink this warp's buffers that are close to full (same rule as the mma.sync kernel).
+  auto prune = [&]() {
+    unsigned need = __ballot_sync(QKV_FULL_MASK, cnt[rq][32 * cb + lane] > kXCap - kXSlack);
+    if (!need) return;
+    float nm = my_nmax;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) nm = fmaxf(nm, __shfl_xor_sync(QKV_FULL_MASK, nm, o));
+    const int k4 = (a.k + 3) / 4;
+    while (need) {
+      const int q = 32 * cb + __ffs(need) - 1;
+      need &= need - 1;
+      const int n = cnt[rq][q] < kXCap ? cnt[rq][q] : kXCap;
+      float T, T4;
+      const int kept = select_sorted<kXCap>(buf_u + q * QS + rq * kXCap, buf_r + q * QS + rq * kXCap, n, a.k,
+                                            2.f * kEps * nm, kXCap - kXSlack, init_thr[q].y, k4, T, T4, lane);
+      if (lane == 0) {
+        if (kept > kXCap - kXSlack) {
+          if (q0 + q < a.M) a.flags[q0 + q] = 1;
+          init_thr[q].y = INFINITY;
+          cnt[rq][q] = 0;
+        } else {
+          cnt[rq][q] = kept;
+          quart[rq][q] = fmaxf(quart[rq][q], T4);
+          const float all4 = fminf(fminf(*reinterpret_cast<volatile float*>(&quart[0][q]),
+                                         *reinterpret_cast<volatile float*>(&quart[1][q])),
+                                   fminf(*reinterpret_cast<volatile float*>(&quart[2][q]),
+                                         *reinterpret_cast<volatile float*>(&quart[3][q])));
+          const float bound = fmaxf(T, all4);
+          raise_threshold(&init_thr[q].y, bound);
+          if (q0 + q < a.M && bound > -INFINITY) publish_bound(a.gthr + q0 + q, bound);
+        }
+      }
+    }
+    __syncwarp();
+  };
+
+  // Scores of row `row` against this warp's 32 queries: optimistic score (c + kEps - sum w) * norm.
+  auto epilogue = [&](int tile, int acc, float kn, bool use_tmem) {
+    const int r = tile * kXRows + row;
+    const bool valid = r < n_valid && use_tmem;
+    uint32_t v[32];
+    if (use_tmem) umma::tmem_ld32(tmem_base + (static_cast<uint32_t>(32 * rq) << 16) + acc * kXQ + 32 * cb, v);
+    if (valid) my_nmax = fmaxf(my_nmax, kn);
+    if (q0 + 32 * cb + lane < a.M) {                 // the other slices' progress: lane = query
+      const float g = *reinterpret_cast<const volatile float*>(a.gthr + q0 + 32 * cb + lane);
+      float* mine = &init_thr[32 * cb + lane].y;
+      if (g > *mine && *mine != INFINITY) raise_threshold(mine, g);
+    }
+    __syncwarp();
+    const int n_sub = tile < 8 ? 4 : 1;              // a warp's first rows arrive in four groups of eight lanes
+#pragma unroll 1
+    for (int sub = 0; sub < n_sub; ++sub) {
+      const bool active = valid && (n_sub == 1 || (lane >> 3) == sub);
+#pragma unroll
+      for (int q = 0; q < 32; ++q) {
+        const float2 it = init_thr[32 * cb + q];
+        const float u = (__uint_as_float(v[q]) + it.x) * kn;
+        if (active && u >= it.y) {
+          const int qq = 32 * cb + q;
+          const int pos = atomicAdd(&cnt[rq][qq], 1);
+          if (pos < kXCap) {
+            buf_u[qq * QS + rq * kXCap + pos] = u;
+            buf_r[qq * QS + rq * kXCap + pos] = static_cast<uint16_t>(r);
+          } else {                                    // buffer full before it could be pruned: redo this query
+            if (q0 + qq < a.M) a.flags[q0 + qq] = 1;
+            init_thr[qq].y = INFINITY;
+          }
+        }
+      }
+      __syncwarp();
+      prune();
+    }
+  };
+
+  // ---- pipeline: decode(i); issue(i); wait(i-1); epilogue(i-1) ------------------------------------------------
+  uint32_t phase[2] = {0u, 0u};
+  uint4 rc; uint2 rs; float kn_next = 0.f, kn_cur = 0.f, kn_prev = 0.f;
+  if (n_tiles > 0) fetch(0, rc, rs, kn_next);
+  for (int i = 0; i < n_tiles; ++i) {
+    const int buf = i & 1;
+    decode(rc, rs, buf);
+    kn_prev = kn_cur;
+    kn_cur = kn_next;
+    if (i + 1 < n_tiles) fetch(i + 1, rc, rs, kn_next);
+    umma::fence_smem_to_async();
+    umma::fence_before_sync();
+    __syncthreads();                       // A(i) written; every warp has left accumulator `buf` (epilogue i-2)
+    if (tid == 0 && *dead == 0) {
+      umma::fence_after_sync();
+      issue_mmas(buf, buf);
+    }
+    if (i > 0) {
+      bool ok = *dead == 0;
+      if (ok) {
+        ok = umma::mbar_wait(&mbar[buf ^ 1], phase[buf ^ 1]);
+        phase[buf ^ 1] ^= 1u;
+        if (!ok) *dead = 1;
+      }
+      umma::fence_after_sync();
+      epilogue(i - 1, buf ^ 1, kn_prev, ok);
+    }
+  }
+  if (n_tiles > 0) {
+    const int buf = (n_tiles - 1) & 1;
+    bool ok = *dead == 0;
+    if (ok) {
+      ok = umma::mbar_wait(&mbar[buf], phase[buf]);
+      if (!ok) *dead = 1;
+    }
+    umma::fence_after_sync();
+    epilogue(n_tiles - 1, buf, kn_cur, ok);
+  }
+  {
+    float nm = my_nmax;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) nm = fmaxf(nm, __shfl_xor_sync(QKV_FULL_MASK, nm, o));
+    if (lane == 0) nmax_w[warp] = nm;
+  }
+  umma::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) umma::tmem_dealloc(tmem_base, kXTmemCols);
+  const bool timed_out = *dead != 0;        // the tensor core never answered: every query of this CTA is redone
+  if (timed_out && tid == 0) atomicAdd(&g_index_umma_timeouts, 1u);
+
+  // ---- per (query, slice): union of the four row quarters, bounded once more, to the list -----------------
+  constexpr int ENT = (kXCap + 31) / 32;
+  const int out_k = a.k + kIExtra;
+  float nm_cta = 0.f;
+#pragma unroll
+  for (int w = 0; w < kXThreads / 32; ++w) nm_cta = fmaxf(nm_cta, nmax_w[w]);
+  for (int q = warp; q < kXQ; q += kXThreads / 32) {
+    if (q0 + q >= a.M) continue;
+    const int64_t o = (static_cast<int64_t>(q0 + q) * a.n_slices + slice) * out_k;
+    const float T0 = init_thr[q].y;
+    float u[4][ENT]; int r[4][ENT]; bool live[4][ENT];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const int n_w = cnt[w][q] < kXCap ? cnt[w][q] : kXCap;
+#pragma unroll
+      for (int e = 0; e < ENT; ++e) {
+        const int slot = lane + 32 * e;
+        u[w][e] = slot < n_w ? buf_u[q * QS + w * kXCap + slot] : -INFINITY;
+        r[w][e] = slot < n_w ? buf_r[q * QS + w * kXCap + slot] : 0;
+        live[w][e] = slot < n_w && u[w][e] >= T0;
+      }
+    }
+    __syncwarp();
+    int total = 0;
+    float* bu = buf_u + q * QS;
+    uint16_t* br = buf_r + q * QS;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+#pragma unroll
+      for (int e = 0; e < ENT; ++e) {
+        const unsigned m = __ballot_sync(QKV_FULL_MASK, live[w][e]);
+        const int dst = total + __popc(m & ((1u << lane) - 1u));
+        if (live[w][e]) { bu[dst] = u[w][e]; br[dst] = static_cast<uint16_t>(r[w][e]); }
+        total += __popc(m);
+      }
+    }
+    __syncwarp();
+    bool redo = T0 == INFINITY || timed_out;
+    int kept = 0;
+    if (!redo) {
+      float T, T4;
+      kept = select_sorted<QS>(bu, br, total, a.k, 2.f * kEps * nm_cta, out_k, T0, 1, T, T4, lane);
+      redo = kept > out_k;
+    }
+    if (redo) { kept = 0; if (lane == 0) a.flags[q0 + q] = 1; }
+    for (int s = lane; s < out_k; s += 32) {
+      a.list_scores[o + s] = s < kept ? bu[s] : -INFINITY;
+      a.list_ids[o + s] = s < kept ? n_begin + br[s] : -1;
+    }
+  }
+}
+
+unsigned int index_umma_timeouts() {
+  unsigned int v = 0;
+  cudaMemcpyFromSymbol(&v, g_index_umma_timeouts, sizeof(v));
+  return v;
+}
+
+bool index_umma_ok(int k) { return k <= kXMaxK; }
+
+int index_umma_qtiles(int M) { return (M + kXQ - 1) / kXQ; }
+
+int launch_index_scan_umma(const ScanMmaArgs& a, int n_qtiles, cudaStream_t st) {
+  if (cudaFuncSetAttribute(index_scan_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(kXSmemBytes)) != cudaSuccess)
+    return QKV_ELAUNCH;
+  index_scan_umma_kernel<<<dim3(a.n_slices, n_qtiles), kXThreads, kXSmemBytes, st>>>(a);
+  return QKV_OK;
+}
+
+}  // namespace qkv

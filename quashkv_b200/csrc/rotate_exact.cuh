@@ -88,4 +88,15 @@ static __device__ __noinline__ float exact_chain(const CompressArgs& a, int64_t 
   return z;
 }
 
+// Same chain from scalars (a kernel that passes its argument block by reference forces the whole block
+// into local memory).
+static __device__ __noinline__ float exact_chain_s(const void* x, int x_dtype, int64_t x_pitch, const float* Pi,
+                                                   int64_t n, int col, float norm) {
+  const float* prow = Pi + col * kRD;
+  float z = 0.f;
+#pragma unroll 8
+  for (int j = 0; j < kRD; ++j) z = fmaf(load_float(x, x_dtype, n * x_pitch + j) / norm, __ldg(prow + j), z);
+  return z;
+}
+
 }  // namespace qkv

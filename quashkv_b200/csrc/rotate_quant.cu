@@ -477,4 +477,8 @@ extern "C" int qkv_decompress_mixed(const uint8_t* codes, int packed, const floa
                       decompress_kernel<2>, decompress_kernel<3>, decompress_kernel<4>);
 }
 
-extern "C" int64_t qkv_tensor_core_timeouts(void) { return static_cast<int64_t>(umma_timeouts()); }
+namespace qkv { unsigned int index_umma_timeouts(); }
+
+extern "C" int64_t qkv_tensor_core_timeouts(void) {
+  return static_cast<int64_t>(umma_timeouts()) + static_cast<int64_t>(index_umma_timeouts());
+}

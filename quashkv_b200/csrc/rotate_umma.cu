@@ -195,7 +195,7 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
         const int64_t n = it.x;
         const int col = it.y & 0xFF;
         const uint32_t old_code = (it.y >> 8) & 0xFF, old_sign = (it.y >> 16) & 1u;
-        const float z = exact_chain(a, n, col, __uint_as_float(it.z));
+        const float z = exact_chain_s(a.x, a.x_dtype, a.x_pitch, a.Pi, n, col, __uint_as_float(it.z));
         const uint32_t code = count_bounds<BITS>(bnd_s, z);
         const int64_t row = map_row(a.rows, n);
         const uint32_t diff = code ^ old_code;
@@ -352,15 +352,30 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
           const int col = col0 + c;
           const float y = raw * iv;
           const uint32_t ec = static_cast<uint8_t>(lut_s[bucket_fine(raw, scale)]);
-          const uint32_t r = classify_flagged(bnd_s, cent_s, IP ? sgn_s[col] : 0.f, y, ec, NB, IP ? 1 : 0);
-          uint32_t code = r & 0xFFu, sign = (r >> 8) & 1u;
-          if ((r >> 16) && live) {
+          uint32_t code = ec & 15u, sign = 0;
+          bool near = false;
+          if ((ec & 0x60u) == 0x60u) {                 // edge bucket or two features: generic classification
+            const uint32_t r = classify_slow(bnd_s, cent_s, IP ? sgn_s[col] : 0.f, y, NB, IP ? 1 : 0);
+            code = r & 0xFFu; sign = (r >> 8) & 1u; near = (r >> 16) != 0;
+          } else {
+            if (ec & 0x40u) {                          // one boundary in reach: code = its number, +1 above it
+              const float b = bnd_s[code];
+              near = fabsf(y - b) < kRecheckEps;
+              code += y > b ? 1u : 0u;
+            }
+            if (IP) {
+              const float resid = y - cent_s[code];
+              sign = (resid * sgn_s[col] >= 0.f) ? 1u : 0u;
+              near |= fabsf(resid) < kRecheckEps;
+            }
+          }
+          if (near && live) {
             const int slot = atomicAdd(&s.qcount[warp], 1);
             if (slot < kUQueueCap) {
               queue[slot] = make_uint4(static_cast<uint32_t>(n), col | (code << 8) | (sign << 16),
                                        __float_as_uint(nrm), 0u);
             } else {
-              const float z = exact_chain(a, n, col, nrm);
+              const float z = exact_chain_s(a.x, a.x_dtype, a.x_pitch, a.Pi, n, col, nrm);
               code = count_bounds<BITS>(bnd_s, z);
               if (IP) sign = ((z - cent_s[code]) * sgn_s[col] >= 0.f) ? 1u : 0u;
             }
@@ -381,7 +396,7 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
 #pragma unroll 1
       for (int c = 0; c < 32; ++c) {
         const int col = col0 + c;
-        const float z = live ? exact_chain(a, n, col, nrm) : 0.f;
+        const float z = live ? exact_chain_s(a.x, a.x_dtype, a.x_pitch, a.Pi, n, col, nrm) : 0.f;
         const uint32_t code = count_bounds<BITS>(bnd_s, z);
         if (IP) fval |= (((z - cent_s[code]) * sgn_s[col] >= 0.f) ? 1u : 0u) << c;
         const int bit = BITS * c, w = bit >> 5, sh = bit & 31;
