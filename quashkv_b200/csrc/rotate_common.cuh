@@ -18,6 +18,8 @@ struct CompressArgs {
   const uint8_t* is_outlier;           // mixed
   uint8_t* codes; uint8_t* signs; int packed; float* norms;
   qkv_rows_t rows;
+  int skip_block_aligned;              // mixed, CUDA-core kernel: return if the outlier count is a multiple of 32
+                                       // (the tcgen05 kernel launched before it took that case)
 };
 
 struct DecompressArgs {

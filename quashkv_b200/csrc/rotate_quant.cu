@@ -110,6 +110,7 @@ __global__ void __launch_bounds__(kThreads, 2) compress_kernel(CompressArgs a) {
   build_slots(s, a.mode == MODE_MIXED ? a.is_outlier : nullptr, d);
   __syncthreads();
   const int n_out = (a.mode == MODE_MIXED) ? count_outliers(s, d) : 0;
+  if (a.skip_block_aligned && (n_out & 31) == 0) return;      // uniform over the grid: the tcgen05 kernel did it
 
   float* stage = s.stage + static_cast<size_t>(warp) * d * kVPW;
   uint8_t* cstage = reinterpret_cast<uint8_t*>(stage);   // reused for permuted codes (mixed, packed)
@@ -366,7 +367,16 @@ static bool no_tcgen05() {
 
 static int run_compress(const CompressArgs& a, cudaStream_t st) {
   if (a.n_vec == 0) return QKV_OK;
-  if (compress_umma_ok(a) && !cuda_core_only() && !no_tcgen05()) return launch_compress_umma(a, st);
+  if (compress_umma_ok(a) && !cuda_core_only() && !no_tcgen05()) {
+    const int rc = launch_compress_umma(a, st);
+    if (rc || a.mode != MODE_MIXED) return rc;
+    // Mixed precision: the tcgen05 kernel works only when the outlier count (known on the device) is a
+    // multiple of 32 and returns at once otherwise; the CUDA-core kernel behind it makes the opposite choice.
+    CompressArgs b = a;
+    b.skip_block_aligned = 1;
+    return launch_by_nt(b, b.d, b.n_vec, st, compress_kernel<1>, compress_kernel<2>, compress_kernel<3>,
+                        compress_kernel<4>);
+  }
   if (compress_mma_ok(a) && !cuda_core_only()) return launch_compress_mma(a, st);
   return launch_by_nt(a, a.d, a.n_vec, st, compress_kernel<1>, compress_kernel<2>, compress_kernel<3>,
                       compress_kernel<4>);

@@ -20,6 +20,8 @@
 //
 // Every wait on the tensor core is bounded; if one runs out the CTA stops using the tensor core,
 // counts the event and derives its remaining tiles with the fp32 chain alone (slow, still exact).
+#include <type_traits>
+
 #include "rotate_exact.cuh"
 #include "mma_decode.cuh"
 #include "umma.cuh"
@@ -63,26 +65,6 @@ __device__ __forceinline__ void build_fine_lut(uint8_t* lut, const float* bnd, c
     else if (n_c) v |= 0xA0u;
     lut[k] = static_cast<uint8_t>(v);
   }
-}
-
-// Flagged buckets (about one coordinate in 150).  Returns code | sign << 8 | near << 16.
-static __device__ __noinline__ uint32_t classify_flagged(const float* bnd, const float* cent, float s_col, float y,
-                                                         uint32_t e, int nb, int ip) {
-  if ((e & 0x60u) == 0x60u) return classify_slow(bnd, cent, s_col, y, nb, ip);
-  uint32_t code = e & 15u;
-  bool near = false;
-  if (e & 0x40u) {
-    const float b = bnd[code];
-    near = fabsf(y - b) < kRecheckEps;
-    code += y > b ? 1u : 0u;
-  }
-  uint32_t sign = 0;
-  if (ip) {
-    const float resid = y - cent[code];
-    sign = (resid * s_col >= 0.f) ? 1u : 0u;
-    near |= fabsf(resid) < kRecheckEps;
-  }
-  return code | (sign << 8) | (near ? 1u << 16 : 0u);
 }
 
 // NT = bf16 terms of the A operand: 1 for bf16 input (two tile buffers), 3 for fp32 / fp16 input (one
@@ -130,32 +112,66 @@ __device__ __forceinline__ UmmaSmem carve_umma(unsigned char* raw) {
   return s;
 }
 
-template <int BITS, bool IP, int NT>
+// BITS1 != 0: mixed precision.  Channels flagged in is_outlier use table 0 at BITS, the others table 1 at
+// BITS1, and the packed row is the outlier channels' stream followed by the regular channels' stream.
+// The rows of Pi are staged in THAT order (B row n' = Pi[perm[n']]), so accumulator column n' is
+// stream position n' and every 32-column block belongs to one table; this needs the number of
+// outlier channels to be a multiple of 32 (otherwise the CTA returns at once and the CUDA-core
+// kernel, launched behind it with the same test inverted, does the work).
+template <int BITS, bool IP, int NT, int BITS1 = 0>
 __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArgs a) {
+  constexpr bool MIXED = BITS1 != 0;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ int8_t lut_s[kLutSize];
-  __shared__ float bnd_s[16], cent_s[16], sgn_s[kRD];
+  __shared__ int8_t lut_s[MIXED ? 2 : 1][kLutSize];
+  __shared__ float bnd_s[2][16], cent_s[16], sgn_s[kRD];
+  __shared__ uint8_t perm_s[kRD];
   const UmmaSmem s = carve_umma<NT>(smem_raw);
   constexpr int kUQueueCap = queue_cap<NT>();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int trow = 32 * (warp & 3) + lane;          // vector of the tile = tensor-memory lane
   const int blk = warp >> 2;                        // output coordinates 32 blk .. 32 blk + 31
   constexpr int NB = (1 << BITS) - 1;
-  constexpr int row_words = (BITS == 3 ? 3 * (kRD / 8) : kRD * BITS / 8) / 4;     // = 4 * BITS
   const __nv_bfloat16* xg = reinterpret_cast<const __nv_bfloat16*>(a.x);
+
+  // ---- mixed precision: stream order of the channels -------------------------------------------------------
+  int n_out = MIXED ? 0 : kRD;                      // columns below n_out use table 0
+  if (MIXED) {
+    bool o = false;
+    if (tid < kRD) {
+      o = a.is_outlier[tid] != 0;
+      const uint32_t m = __ballot_sync(QKV_FULL_MASK, o);
+      if (lane == 0) s.smask[warp] = m;
+    }
+    __syncthreads();
+    int before = 0;
+    for (int w = 0; w < 4; ++w) {
+      const int c = __popc(s.smask[w]);
+      n_out += c;
+      if (w < warp) before += c;
+    }
+    if (n_out & 31) return;                         // every thread of every CTA: left to the CUDA-core kernel
+    if (tid < kRD) {
+      before += __popc(s.smask[warp] & ((1u << lane) - 1u));            // outlier channels below this one
+      perm_s[o ? before : n_out + (tid - before)] = static_cast<uint8_t>(tid);
+    }
+    __syncthreads();
+  }
+  const int m_out = n_out >> 5;                     // 32-column blocks of table 0
+  const int row_words = MIXED ? m_out * BITS + (4 - m_out) * BITS1 : 4 * BITS;
 
   // ---- one-time setup: Pi planes, tables, barriers, tensor memory -------------------------------------
   for (int idx = tid; idx < kRD * kRD; idx += kUThreads) {
     const int n = idx >> 7, k = idx & 127;
     __nv_bfloat16 h, m, l;
-    split3(a.Pi[idx], h, m, l);
+    split3(a.Pi[(MIXED ? perm_s[n] : n) * kRD + k], h, m, l);
     const uint32_t off = umma::sw128_offset(n, k, 128);
     *reinterpret_cast<__nv_bfloat16*>(s.b[0] + off) = h;
     *reinterpret_cast<__nv_bfloat16*>(s.b[1] + off) = m;
     *reinterpret_cast<__nv_bfloat16*>(s.b[2] + off) = l;
   }
   if (tid < 16) {
-    bnd_s[tid] = tid < NB ? a.bounds0[tid] : INFINITY;
+    bnd_s[0][tid] = tid < NB ? a.bounds0[tid] : INFINITY;
+    bnd_s[1][tid] = (MIXED && tid < (1 << BITS1) - 1) ? a.bounds1[tid] : INFINITY;
     cent_s[tid] = (IP && tid < (1 << BITS)) ? a.centroids[tid] : 0.f;
   }
   if (tid < kRD) {
@@ -171,7 +187,8 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
     *s.dead = 0;
   }
   __syncthreads();
-  build_fine_lut<BITS, IP>(reinterpret_cast<uint8_t*>(lut_s), bnd_s, cent_s);
+  build_fine_lut<BITS, IP>(reinterpret_cast<uint8_t*>(lut_s[0]), bnd_s[0], cent_s);
+  if (MIXED) build_fine_lut<(MIXED ? BITS1 : 1), false>(reinterpret_cast<uint8_t*>(lut_s[MIXED ? 1 : 0]), bnd_s[1], cent_s);
   if (warp == 0) umma::tmem_alloc(s.tmem_slot, kUTmemCols);
   umma::fence_smem_to_async();
   umma::fence_before_sync();
@@ -195,14 +212,18 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
         const int64_t n = it.x;
         const int col = it.y & 0xFF;
         const uint32_t old_code = (it.y >> 8) & 0xFF, old_sign = (it.y >> 16) & 1u;
-        const float z = exact_chain_s(a.x, a.x_dtype, a.x_pitch, a.Pi, n, col, __uint_as_float(it.z));
-        const uint32_t code = count_bounds<BITS>(bnd_s, z);
+        const int cls = col >= n_out ? 1 : 0;
+        const int bits_c = cls ? BITS1 : BITS;
+        const float z = exact_chain_s(a.x, a.x_dtype, a.x_pitch, a.Pi, n, MIXED ? perm_s[col] : col,
+                                      __uint_as_float(it.z));
+        uint32_t code = 0;
+        for (int b = 0; b < (1 << bits_c) - 1; ++b) code += z > bnd_s[cls][b] ? 1u : 0u;
         const int64_t row = map_row(a.rows, n);
         const uint32_t diff = code ^ old_code;
         if (diff) {
-          const int bit = col * BITS, w = bit >> 5, sh = bit & 31;
+          const int bit = cls ? n_out * BITS + (col - n_out) * BITS1 : col * BITS, w = bit >> 5, sh = bit & 31;
           atomicXor(out_codes + row * row_words + w, diff << sh);
-          if (sh + BITS > 32) atomicXor(out_codes + row * row_words + w + 1, diff >> (32 - sh));
+          if (sh + bits_c > 32) atomicXor(out_codes + row * row_words + w + 1, diff >> (32 - sh));
         }
         if (IP) {
           const uint32_t sign = ((z - cent_s[code]) * sgn_s[col] >= 0.f) ? 1u : 0u;
@@ -212,6 +233,8 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
     }
     __syncwarp();
   };
+  const int cls_blk = blk >= m_out ? 1 : 0;         // table of this thread's 32 columns
+  const int word_off = cls_blk ? m_out * BITS + (blk - m_out) * BITS1 : blk * BITS;
 
   const int64_t n_tiles = (a.n_vec + kUTile - 1) / kUTile;
 
@@ -316,7 +339,11 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
   // look-ups whose flag bits are collected in a mask, packing by shifted adds.  Then the warp walks
   // over the columns in which any of its lanes was flagged (usually one or two): the column is
   // re-read from tensor memory and the flagged lanes classify it exactly and patch their words.
-  auto epilogue = [&](int64_t tile, int buf, float nrm, bool use_tmem) {
+  auto epilogue_t = [&](auto bits_tag, int64_t tile, int buf, float nrm, bool use_tmem) {
+    constexpr int BW = decltype(bits_tag)::value;   // bit width of this thread's columns
+    constexpr int NBW = (1 << BW) - 1;
+    const int8_t* lut_c = lut_s[MIXED ? cls_blk : 0];
+    const float* bnd_c = bnd_s[cls_blk];
     const int64_t n = tile * kUTile + trow;
     const bool live = n < a.n_vec;
     const int64_t row = live ? map_row(a.rows, n) : 0;
@@ -324,9 +351,9 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
     const int col0 = 32 * blk;
     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + buf * 128 + col0;
     uint32_t fmask = 0, fval = 0, R = 0;
-    uint32_t wb[BITS + 1];
+    uint32_t wb[BW + 1];
 #pragma unroll
-    for (int w = 0; w <= BITS; ++w) wb[w] = 0u;
+    for (int w = 0; w <= BW; ++w) wb[w] = 0u;
     if (use_tmem) {
       uint32_t v[32];
       umma::tmem_ld32(taddr, v);
@@ -334,12 +361,12 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
         const float raw = __uint_as_float(v[c]);
-        const int e = lut_s[bucket_fine(raw, scale)];             // sign-extended: negative when flagged
+        const int e = lut_c[bucket_fine(raw, scale)];             // sign-extended: negative when flagged
         fm = __funnelshift_l(static_cast<uint32_t>(e), fm, 1);
         const uint32_t code = static_cast<uint32_t>(e) & 15u;
-        const int bit = BITS * c, w = bit >> 5, sh = bit & 31;
+        const int bit = BW * c, w = bit >> 5, sh = bit & 31;
         wb[w] += code << sh;                                       // fields are disjoint: add == or
-        if (sh + BITS > 32) wb[w + 1] += code >> (32 - sh);
+        if (sh + BW > 32) wb[w + 1] += code >> (32 - sh);
         if (IP) R = __funnelshift_l(__float_as_uint(raw * iv - cent_s[code]), R, 1);
       }
       const uint32_t mine = __brev(fm);
@@ -351,15 +378,15 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
         if ((mine >> c) & 1u) {
           const int col = col0 + c;
           const float y = raw * iv;
-          const uint32_t ec = static_cast<uint8_t>(lut_s[bucket_fine(raw, scale)]);
+          const uint32_t ec = static_cast<uint8_t>(lut_c[bucket_fine(raw, scale)]);
           uint32_t code = ec & 15u, sign = 0;
           bool near = false;
           if ((ec & 0x60u) == 0x60u) {                 // edge bucket or two features: generic classification
-            const uint32_t r = classify_slow(bnd_s, cent_s, IP ? sgn_s[col] : 0.f, y, NB, IP ? 1 : 0);
+            const uint32_t r = classify_slow(bnd_c, cent_s, IP ? sgn_s[col] : 0.f, y, NBW, IP ? 1 : 0);
             code = r & 0xFFu; sign = (r >> 8) & 1u; near = (r >> 16) != 0;
           } else {
             if (ec & 0x40u) {                          // one boundary in reach: code = its number, +1 above it
-              const float b = bnd_s[code];
+              const float b = bnd_c[code];
               near = fabsf(y - b) < kRecheckEps;
               code += y > b ? 1u : 0u;
             }
@@ -375,19 +402,19 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
               queue[slot] = make_uint4(static_cast<uint32_t>(n), col | (code << 8) | (sign << 16),
                                        __float_as_uint(nrm), 0u);
             } else {
-              const float z = exact_chain_s(a.x, a.x_dtype, a.x_pitch, a.Pi, n, col, nrm);
-              code = count_bounds<BITS>(bnd_s, z);
+              const float z = exact_chain_s(a.x, a.x_dtype, a.x_pitch, a.Pi, n, MIXED ? perm_s[col] : col, nrm);
+              code = count_bounds<BW>(bnd_c, z);
               if (IP) sign = ((z - cent_s[code]) * sgn_s[col] >= 0.f) ? 1u : 0u;
             }
           }
           fmask |= 1u << c;
           fval |= sign << c;
           const uint32_t diff = code ^ (ec & 15u);
-          const int bit = BITS * c, w = bit >> 5, sh = bit & 31;
+          const int bit = BW * c, w = bit >> 5, sh = bit & 31;
 #pragma unroll
-          for (int q = 0; q <= BITS; ++q) {
+          for (int q = 0; q <= BW; ++q) {
             if (q == w) wb[q] ^= diff << sh;
-            if (q == w + 1 && sh + BITS > 32) wb[q] ^= diff >> (32 - sh);
+            if (q == w + 1 && sh + BW > 32) wb[q] ^= diff >> (32 - sh);
           }
         }
         __syncwarp();
@@ -396,25 +423,25 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
 #pragma unroll 1
       for (int c = 0; c < 32; ++c) {
         const int col = col0 + c;
-        const float z = live ? exact_chain_s(a.x, a.x_dtype, a.x_pitch, a.Pi, n, col, nrm) : 0.f;
-        const uint32_t code = count_bounds<BITS>(bnd_s, z);
+        const float z = live ? exact_chain_s(a.x, a.x_dtype, a.x_pitch, a.Pi, n, MIXED ? perm_s[col] : col, nrm) : 0.f;
+        const uint32_t code = count_bounds<BW>(bnd_c, z);
         if (IP) fval |= (((z - cent_s[code]) * sgn_s[col] >= 0.f) ? 1u : 0u) << c;
-        const int bit = BITS * c, w = bit >> 5, sh = bit & 31;
+        const int bit = BW * c, w = bit >> 5, sh = bit & 31;
 #pragma unroll
-        for (int q = 0; q <= BITS; ++q) {
+        for (int q = 0; q <= BW; ++q) {
           if (q == w) wb[q] |= code << sh;
-          if (q == w + 1 && sh + BITS > 32) wb[q] |= code >> (32 - sh);
+          if (q == w + 1 && sh + BW > 32) wb[q] |= code >> (32 - sh);
         }
       }
       fmask = 0xFFFFFFFFu;
     }
     if (live) {
-      uint32_t* dst = out_codes + row * row_words + blk * BITS;
-      if (BITS == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(wb[0], wb[1], wb[2], wb[BITS - 1]);
-      else if (BITS == 2) *reinterpret_cast<uint2*>(dst) = make_uint2(wb[0], wb[1]);
+      uint32_t* dst = out_codes + row * row_words + word_off;
+      if (!MIXED && BW == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(wb[0], wb[1], wb[2], wb[BW - 1]);
+      else if (!MIXED && BW == 2) *reinterpret_cast<uint2*>(dst) = make_uint2(wb[0], wb[1]);
       else {
 #pragma unroll
-        for (int w = 0; w < BITS; ++w) dst[w] = wb[w];
+        for (int w = 0; w < BW; ++w) dst[w] = wb[w];
       }
       if (IP) {
         // unflagged coordinates: sign = residual >= 0 exclusive-or S < 0 (a zero residual is always flagged)
@@ -430,6 +457,10 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
       if (lane == 0) s.qcount[warp] = 0;
       __syncwarp();
     }
+  };
+  auto epilogue = [&](int64_t tile, int buf, float nrm, bool use_tmem) {
+    if (MIXED && cls_blk) epilogue_t(std::integral_constant<int, (MIXED ? BITS1 : BITS)>{}, tile, buf, nrm, use_tmem);
+    else epilogue_t(std::integral_constant<int, BITS>{}, tile, buf, nrm, use_tmem);
   };
 
   // ---- pipeline over this CTA's tiles ------------------------------------------------------------------
@@ -507,7 +538,13 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
 bool compress_umma_ok(const CompressArgs& a) {
   const uintptr_t al = reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.codes) |
                        (a.mode == MODE_IP ? reinterpret_cast<uintptr_t>(a.signs) : 0);
-  return a.d == kRD && a.mode != MODE_MIXED && a.packed && a.n_vec >= 1024 && a.n_vec < (int64_t(1) << 31) &&
+  if (a.mode == MODE_MIXED) {   // bf16 input, the common width pairs; row of 4-byte words (36 B at 32x3 + 96x2)
+    const bool pair = (a.bits0 == 3 && a.bits1 == 2) || (a.bits0 == 4 && a.bits1 == 3) || (a.bits0 == 4 && a.bits1 == 2);
+    if (!pair || a.x_dtype != QKV_BF16) return false;
+    return a.d == kRD && a.packed && a.n_vec >= 1024 && a.n_vec < (int64_t(1) << 31) && (a.x_pitch & 7) == 0 &&
+           ((reinterpret_cast<uintptr_t>(a.x) & 15u) | (reinterpret_cast<uintptr_t>(a.codes) & 3u)) == 0;
+  }
+  return a.d == kRD && a.packed && a.n_vec >= 1024 && a.n_vec < (int64_t(1) << 31) &&
          (a.x_pitch & 7) == 0 && (al & 15u) == 0;
 }
 
@@ -528,7 +565,23 @@ static int launch_compress_umma_t(const CompressArgs& a, cudaStream_t st) {
   return a.x_dtype == QKV_BF16 ? launch_compress_umma_n<BITS, IP, 1>(a, st) : launch_compress_umma_n<BITS, IP, 3>(a, st);
 }
 
+template <int B0, int B1>
+static int launch_compress_umma_mixed(const CompressArgs& a, cudaStream_t st) {
+  constexpr size_t smem = umma_smem_bytes<1>();
+  if (cudaFuncSetAttribute(compress_umma_kernel<B0, false, 1, B1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem)) != cudaSuccess)
+    return QKV_ELAUNCH;
+  const int64_t tiles = (a.n_vec + kUTile - 1) / kUTile;
+  const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
+  compress_umma_kernel<B0, false, 1, B1><<<grid, kUThreads, smem, st>>>(a);
+  return check_launch();
+}
+
 int launch_compress_umma(const CompressArgs& a, cudaStream_t st) {
+  if (a.mode == MODE_MIXED) {
+    if (a.bits0 == 3) return launch_compress_umma_mixed<3, 2>(a, st);
+    return a.bits1 == 3 ? launch_compress_umma_mixed<4, 3>(a, st) : launch_compress_umma_mixed<4, 2>(a, st);
+  }
   const bool ip = a.mode == MODE_IP;
   switch (a.bits0) {
     case 1: return ip ? launch_compress_umma_t<1, true>(a, st) : launch_compress_umma_t<1, false>(a, st);

@@ -267,6 +267,32 @@ def test_mixed_precision(golden):
     assert m.shape == s.shape == (32, 128) and int(s.max()) <= 1 and ipq.effective_bits == pytest.approx(2.25)
 
 
+def test_mixed_precision_tensor_core_equals_cuda_core(golden, monkeypatch):
+    """bf16 batches with a multiple of 32 outlier channels compress on the tcgen05 kernel (the rows of
+    Pi staged in stream order); the packed bytes and norms must equal the CUDA-core kernel's.  Other
+    outlier counts are left to the CUDA-core kernel by the device-side test both kernels make."""
+    c = golden("constants")
+    Pi = t(c["Pi_d128_s42"]).to(DEV)
+    gen = torch.Generator().manual_seed(21)
+    x = torch.randn(40_000 + 13, 128, generator=gen)
+    x[:, torch.randperm(128, generator=gen)[:6]] *= 6
+    xd = x.to(torch.bfloat16).to(DEV)
+    for (b_out, b_reg) in ((3, 2), (4, 3), (4, 2)):
+        bo, br = t(c[f"bnd_d128_b{b_out}"]).to(DEV), t(c[f"bnd_d128_b{b_reg}"]).to(DEV)
+        for n_out in (32, 64, 0, 128, 20):
+            mask = torch.zeros(128, dtype=torch.uint8)
+            mask[torch.randperm(128, generator=gen)[:n_out]] = 1
+            fast = ops.compress_mixed(xd, Pi, mask.to(DEV), bo, b_out, br, b_reg, packed=True)
+            monkeypatch.setenv("QUASHKV_B200_CUDA_CORE_ROTATION", "1")
+            slow = ops.compress_mixed(xd, Pi, mask.to(DEV), bo, b_out, br, b_reg, packed=True)
+            monkeypatch.delenv("QUASHKV_B200_CUDA_CORE_ROTATION")
+            n_bad = int((fast[0] != slow[0]).sum())
+            assert n_bad == 0, f"bits {b_out}/{b_reg}, {n_out} outlier channels: {n_bad} packed bytes differ"
+            assert torch.equal(fast[1], slow[1])
+    from quashkv_b200 import _lib
+    assert _lib.lib().qkv_tensor_core_timeouts() == 0
+
+
 # ---------------------------------------------------------------------------------------------
 # engine: configuration 1 and the multi-block / causal / other-width cases
 # ---------------------------------------------------------------------------------------------
