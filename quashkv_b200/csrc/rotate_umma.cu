@@ -611,6 +611,7 @@ struct DecSmem {
   static constexpr int NBUF = NT == 2 ? 2 : 1;
   unsigned char* a[NBUF][NT];
   unsigned char* b[NT];
+  unsigned char* stage;     // [warps][32 rows][64 bytes]: output transposition, 16 columns at a time
   uint64_t* mbar;           // [2]
   uint32_t* tmem_slot;
   int* dead;
@@ -618,7 +619,7 @@ struct DecSmem {
 
 template <int NT>
 constexpr size_t dec_smem_bytes() {
-  return 1024 + static_cast<size_t>(DecSmem<NT>::NBUF * NT + NT) * kUPlaneBytes + 2 * 8 + 16;
+  return 1024 + static_cast<size_t>(DecSmem<NT>::NBUF * NT + NT) * kUPlaneBytes + kUWarps * 2048 + 2 * 8 + 16;
 }
 
 template <int NT>
@@ -628,6 +629,7 @@ __device__ __forceinline__ DecSmem<NT> carve_dec(unsigned char* raw) {
   for (int bf = 0; bf < DecSmem<NT>::NBUF; ++bf)
     for (int t = 0; t < NT; ++t) { s.a[bf][t] = p; p += kUPlaneBytes; }
   for (int t = 0; t < NT; ++t) { s.b[t] = p; p += kUPlaneBytes; }
+  s.stage = p; p += kUWarps * 2048;
   s.mbar = reinterpret_cast<uint64_t*>(p); p += 16;
   s.tmem_slot = reinterpret_cast<uint32_t*>(p);
   s.dead = reinterpret_cast<int*>(p + 4);
@@ -645,6 +647,8 @@ template <int BITS, bool SIGNS, int NT>
 __global__ void __launch_bounds__(kUThreads, 1) decompress_umma_kernel(DecompressArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ float cent_s[16], qs_s[kRD];
+  __shared__ uint2 split_s[32];             // bf16 terms (h | m << 16, l) of the 2^(BITS+1) possible values
+  __shared__ uint32_t smask_s[4];           // bit c of word w: S[32 w + c] < 0
   const DecSmem<NT> s = carve_dec<NT>(smem_raw);
   constexpr int NBUF = DecSmem<NT>::NBUF;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -663,7 +667,24 @@ __global__ void __launch_bounds__(kUThreads, 1) decompress_umma_kernel(Decompres
     for (int t = 0; t < NT; ++t) *reinterpret_cast<__nv_bfloat16*>(s.b[t] + off) = t3[t];
   }
   if (tid < 16) cent_s[tid] = tid < (1 << BITS) ? a.cents0[tid] : 0.f;
-  if (tid < kRD) qs_s[tid] = SIGNS ? a.qjl_scale * a.S[tid] : 0.f;
+  bool pm1 = true;
+  if (tid < kRD) {
+    const float sv = SIGNS ? a.S[tid] : 1.f;
+    qs_s[tid] = SIGNS ? a.qjl_scale * sv : 0.f;
+    pm1 = fabsf(sv) == 1.f;
+    const uint32_t neg = __ballot_sync(QKV_FULL_MASK, sv < 0.f);
+    if (lane == 0) smask_s[warp] = neg;
+  }
+  const bool table_ok = __syncthreads_and(pm1) != 0;     // S = +-1 everywhere: the value table applies
+  if (tid < 32) {
+    const uint32_t code = tid & ((1u << BITS) - 1u);
+    float x = a.cents0[code < (1u << BITS) ? code : 0];
+    if (SIGNS) x += (tid >> BITS) & 1u ? a.qjl_scale : -a.qjl_scale;
+    __nv_bfloat16 h, m, l;
+    split3(x, h, m, l);
+    split_s[tid] = make_uint2(pack_bf16(h, m), static_cast<uint32_t>(__bfloat16_as_ushort(l)));
+  }
+  const uint32_t smask = SIGNS ? smask_s[blk] : 0u;
   if (tid == 0) {
     umma::mbar_init(&s.mbar[0], 1);
     umma::mbar_init(&s.mbar[1], 1);
@@ -677,16 +698,59 @@ __global__ void __launch_bounds__(kUThreads, 1) decompress_umma_kernel(Decompres
   const uint32_t tmem_base = *s.tmem_slot;
   const int64_t n_tiles = (a.n_vec + kUTile - 1) / kUTile;
 
-  // Decode this thread's 32 coordinates of row trow into the NT operand planes of A[bf].
+  // Decode this thread's 32 coordinates of row trow into the NT operand planes of A[bf].  With S = +-1 (what
+  // the quantiser generates) a coordinate's value is one of 2^(BITS+1) numbers, c[code] +- qjl_scale, chosen by
+  // the code and by sign bit xor (S < 0); their exact bf16 terms sit in a shared-memory table, so a
+  // coordinate costs a field extraction, one 8-byte look-up and its share of three PRMTs.
+  // Packed words (and the norm) of this thread's part of a row, fetched one tile ahead of their use.
+  uint32_t nw[BITS + 1], nsw = 0;
+  float nnorm = 0.f;
+  auto fetch = [&](int64_t tile) {
+    const int64_t n = tile * kUTile + trow;
+    const bool live = tile < n_tiles && n < a.n_vec;
+    const int64_t row = live ? map_row(a.rows, n) : 0;
+#pragma unroll
+    for (int q = 0; q < BITS; ++q) nw[q] = live ? __ldg(codes + row * row_words + blk * BITS + q) : 0u;
+    nw[BITS] = 0u;
+    if (SIGNS) nsw = live ? __ldg(signs + row * (kRD / 32) + blk) : 0u;
+    nnorm = live ? __ldg(a.norms + row) : 0.f;
+  };
   auto decode_tile = [&](int64_t tile, int bf) {
     const int64_t n = tile * kUTile + trow;
     const bool live = n < a.n_vec;
-    const int64_t row = live ? map_row(a.rows, n) : 0;
-    uint32_t w[BITS + 1], sw = 0;
+    uint32_t w[BITS + 1];
 #pragma unroll
-    for (int q = 0; q < BITS; ++q) w[q] = live ? __ldg(codes + row * row_words + blk * BITS + q) : 0u;
-    w[BITS] = 0u;
-    if (SIGNS) sw = live ? __ldg(signs + row * (kRD / 32) + blk) : 0u;
+    for (int q = 0; q <= BITS; ++q) w[q] = nw[q];
+    const uint32_t sw = nsw;
+    if (table_ok) {
+      const uint32_t sx = sw ^ smask;                 // bit c: add (1) or subtract (0) qjl_scale
+#pragma unroll
+      for (int c8 = 0; c8 < 4; ++c8) {
+        uint32_t packed[3][4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          uint2 e[2];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int c = 8 * c8 + 2 * p + h;
+            const int bit = BITS * c, wi = bit >> 5, sh = bit & 31;
+            uint32_t idx = w[wi] >> sh;
+            if (sh + BITS > 32) idx |= w[wi + 1] << (32 - sh);
+            idx &= (1u << BITS) - 1u;
+            if (SIGNS) idx |= (c >= BITS ? (sx >> (c - BITS)) : (sx << (BITS - c))) & (1u << BITS);
+            e[h] = split_s[idx];
+          }
+          packed[0][p] = __byte_perm(e[0].x, e[1].x, 0x5410);
+          packed[1][p] = __byte_perm(e[0].x, e[1].x, 0x7632);
+          packed[2][p] = __byte_perm(e[0].y, e[1].y, 0x5410);
+        }
+        const uint32_t off = umma::sw128_offset(trow, 32 * blk + 8 * c8, 128);
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+          *reinterpret_cast<uint4*>(s.a[bf][t] + off) = make_uint4(packed[t][0], packed[t][1], packed[t][2], packed[t][3]);
+      }
+      return;
+    }
 #pragma unroll
     for (int c8 = 0; c8 < 4; ++c8) {
       uint32_t packed[NT][4];
@@ -747,11 +811,10 @@ __global__ void __launch_bounds__(kUThreads, 1) decompress_umma_kernel(Decompres
   };
 
   // Scale this thread's 32 outputs of row trow by the norm and store them.
-  auto epilogue = [&](int64_t tile, int acc_buf, bool use_tmem) {
+  auto epilogue = [&](int64_t tile, int acc_buf, float nrm, bool use_tmem) {
     const int64_t n = tile * kUTile + trow;
     const bool live = n < a.n_vec;
     const int64_t row = live ? map_row(a.rows, n) : 0;
-    const float nrm = live ? __ldg(a.norms + row) : 0.f;
     uint32_t v[32];
     if (use_tmem) {
       umma::tmem_ld32(tmem_base + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + acc_buf * 128 + 32 * blk, v);
@@ -765,14 +828,34 @@ __global__ void __launch_bounds__(kUThreads, 1) decompress_umma_kernel(Decompres
       }
       for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(decompress_chain(vrow, a.Pi, 32 * blk + c));
     }
-    if (!live) return;
     if (a.out_dtype == QKV_F32) {
-      float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + n * a.out_pitch + 32 * blk);
+      // A thread holds 32 consecutive outputs of ONE row; stored as they are, a warp instruction would touch 32
+      // rows with 16 bytes each.  Sixteen columns at a time go through a 2 KB per-warp buffer (16-byte chunk q
+      // of row r at position q ^ ((r >> 1) & 3): conflict-free both ways) and come back as 8 rows x 64
+      // contiguous bytes per instruction.
+      unsigned char* st = s.stage + warp * 2048;
+      const int64_t n0 = tile * kUTile + 32 * (warp & 3);
 #pragma unroll
-      for (int q = 0; q < 8; ++q)
-        dst[q] = make_float4(__uint_as_float(v[4 * q]) * nrm, __uint_as_float(v[4 * q + 1]) * nrm,
-                             __uint_as_float(v[4 * q + 2]) * nrm, __uint_as_float(v[4 * q + 3]) * nrm);
-    } else {
+      for (int hf = 0; hf < 2; ++hf) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int c = 16 * hf + 4 * q;
+          *reinterpret_cast<float4*>(st + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) =
+              make_float4(__uint_as_float(v[c]) * nrm, __uint_as_float(v[c + 1]) * nrm,
+                          __uint_as_float(v[c + 2]) * nrm, __uint_as_float(v[c + 3]) * nrm);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int r = 8 * j + (lane >> 2), q = lane & 3;
+          const float4 o = *reinterpret_cast<const float4*>(st + r * 64 + ((q ^ ((r >> 1) & 3)) << 4));
+          if (n0 + r < a.n_vec)
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + (n0 + r) * a.out_pitch + 32 * blk + 16 * hf +
+                                       4 * q) = o;
+        }
+        __syncwarp();
+      }
+    } else if (live) {
 #pragma unroll
       for (int c = 0; c < 32; ++c)
         store_float(a.out, a.out_dtype, n * a.out_pitch + 32 * blk + c, __uint_as_float(v[c]) * nrm);
@@ -786,6 +869,8 @@ __global__ void __launch_bounds__(kUThreads, 1) decompress_umma_kernel(Decompres
   int64_t prev_tile = -1;
   int i = 0;
   bool prev_ok = true;
+  float norm_cur = 0.f, norm_prev = 0.f;
+  fetch(blockIdx.x);
   for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++i) {
     const int bf = i % NBUF, acc_buf = i & 1;
     auto wait_prev = [&]() {
@@ -800,6 +885,9 @@ __global__ void __launch_bounds__(kUThreads, 1) decompress_umma_kernel(Decompres
     };
     if (NBUF == 1) wait_prev();
     decode_tile(tile, bf);
+    norm_prev = norm_cur;
+    norm_cur = nnorm;
+    fetch(tile + gridDim.x);              // the next tile's words travel while this one is multiplied and stored
     umma::fence_smem_to_async();
     umma::fence_before_sync();
     __syncthreads();                      // A(i) written; epilogue(i-2) has left accumulator acc_buf
@@ -808,7 +896,7 @@ __global__ void __launch_bounds__(kUThreads, 1) decompress_umma_kernel(Decompres
       issue_mmas(bf, acc_buf);
     }
     if (NBUF == 2) wait_prev();
-    if (prev_tile >= 0) epilogue(prev_tile, acc_buf ^ 1, prev_ok);
+    if (prev_tile >= 0) epilogue(prev_tile, acc_buf ^ 1, norm_prev, prev_ok);
     prev_tile = tile;
   }
   if (prev_tile >= 0) {
@@ -819,7 +907,7 @@ __global__ void __launch_bounds__(kUThreads, 1) decompress_umma_kernel(Decompres
       if (!ok) { *s.dead = 1; atomicAdd(&g_umma_timeouts, 1u); }
     }
     umma::fence_after_sync();
-    epilogue(prev_tile, acc_buf, ok);
+    epilogue(prev_tile, acc_buf, norm_cur, ok);
   }
   umma::fence_before_sync();
   __syncthreads();
