@@ -372,9 +372,20 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
       const uint32_t mine = __brev(fm);
       uint32_t cols = __reduce_or_sync(QKV_FULL_MASK, mine);      // columns flagged in any lane
       while (cols) {
-        const int c = __ffs(cols) - 1;
-        cols &= cols - 1;
-        const float raw = __uint_as_float(umma::tmem_ld1(taddr + c));
+        // up to four flagged columns per round: their reads from tensor memory overlap
+        int cc[4]; uint32_t ta[4], rv[4];
+        int n_c = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          cc[j] = cols ? __ffs(cols) - 1 : 0;
+          if (cols) { ++n_c; cols &= cols - 1; }
+          ta[j] = taddr + cc[j];
+        }
+        umma::tmem_ld1x4(ta, rv);
+#pragma unroll 1
+        for (int j = 0; j < n_c; ++j) {
+        const int c = j == 0 ? cc[0] : (j == 1 ? cc[1] : (j == 2 ? cc[2] : cc[3]));
+        const float raw = __uint_as_float(j == 0 ? rv[0] : (j == 1 ? rv[1] : (j == 2 ? rv[2] : rv[3])));
         if ((mine >> c) & 1u) {
           const int col = col0 + c;
           const float y = raw * iv;
@@ -418,6 +429,7 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
           }
         }
         __syncwarp();
+        }
       }
     } else {
 #pragma unroll 1
@@ -491,7 +503,9 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
         issue_mmas(buf, buf);
       }
       const float norm_prev = prev_tile >= 0 ? row_norm(buf ^ 1) : 1.f;   // squares(i-1) were left before the barrier
-      part_squares(buf);
+      // the fp64 sums of half the warps go before the epilogue and of the other half after it, so that the
+      // sixteen warps do not queue for the fp64 pipe at the same moment
+      if (blk < 2) part_squares(buf);
       const int64_t next = tile + gridDim.x;
       if (prev_tile >= 0) {
         const bool ok = wait_acc(buf ^ 1);
@@ -500,6 +514,7 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
       } else if (next < n_tiles) {
         load_tile(next, buf ^ 1);
       }
+      if (blk >= 2) part_squares(buf);
       prev_tile = tile;
     }
   } else {

@@ -125,5 +125,18 @@ __device__ __forceinline__ uint32_t tmem_ld1(uint32_t taddr) {
   return v;
 }
 
+// Four columns at four addresses, one wait: the loads travel together.
+__device__ __forceinline__ void tmem_ld1x4(const uint32_t (&taddr)[4], uint32_t (&v)[4]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%4];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x1.b32 {%1}, [%5];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x1.b32 {%2}, [%6];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x1.b32 {%3}, [%7];\n\t"
+      "tcgen05.wait::ld.sync.aligned;\n"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+      : "r"(taddr[0]), "r"(taddr[1]), "r"(taddr[2]), "r"(taddr[3])
+      : "memory");
+}
+
 }  // namespace umma
 }  // namespace qkv
