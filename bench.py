@@ -185,6 +185,9 @@ def extras(device):
         out[f"compress_mse_{bits}bit_Mvec_s"] = n / sec / 1e6
         sec = timed(lambda: q.decompress_packed(codes, norms))
         out[f"decompress_mse_{bits}bit_Mvec_s"] = n / sec / 1e6
+        if bits == 3:
+            sec = timed(lambda: q.decompress_packed(codes, norms, out_dtype=torch.bfloat16))
+            out["decompress_mse_3bit_bf16_out_Mvec_s"] = n / sec / 1e6
     ipq = qk.InnerProductQuantizer(D, 3, seed=42)
     out["compress_ip_3bit_Mvec_s"] = n / timed(lambda: ipq.compress_packed(x)) / 1e6
     mp = qk.MixedPrecisionMSEQuantizer(D, 3, 2, 32, seed=42)

@@ -870,6 +870,30 @@ __global__ void __launch_bounds__(kUThreads, 1) decompress_umma_kernel(Decompres
         }
         __syncwarp();
       }
+    } else if (a.out_dtype == QKV_BF16) {
+      // same transposition with 2-byte outputs: the thread's 32 values are 64 bytes, one pass
+      unsigned char* st = s.stage + warp * 2048;
+      const int64_t n0 = tile * kUTile + 32 * (warp & 3);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 2 * e]) * nrm,
+                                                          __uint_as_float(v[8 * q + 2 * e + 1]) * nrm);
+          pk[e] = *reinterpret_cast<const uint32_t*>(&b2);
+        }
+        *reinterpret_cast<uint4*>(st + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int r = 8 * j + (lane >> 2), q = lane & 3;
+        const uint4 o = *reinterpret_cast<const uint4*>(st + r * 64 + ((q ^ ((r >> 1) & 3)) << 4));
+        if (n0 + r < a.n_vec)
+          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.out) + (n0 + r) * a.out_pitch + 32 * blk + 8 * q) = o;
+      }
+      __syncwarp();
     } else if (live) {
 #pragma unroll
       for (int c = 0; c < 32; ++c)
