@@ -29,7 +29,7 @@ struct ScanArgs {
   int64_t id_base;
   float* list_scores; int64_t* list_ids;    // [M][n_slices*k]
   float* dense;                             // [M][N] when DENSE
-  const int* flags;                         // when set: only queries with a non-zero flag are scanned
+  const int* qlist;                         // when set: scan queries qlist[0 .. qlist[M]) only, lists in that order
 };
 
 struct ScanPlan { int n_slices; int64_t slice_len; int n_qtiles; size_t qk_bytes, ls_bytes, li_bytes; };
@@ -94,17 +94,15 @@ __global__ void __launch_bounds__(kScanThreads) index_scan_kernel(ScanArgs a) {
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int slice = blockIdx.x, q0 = blockIdx.y * kMQ;
-  if (a.flags) {                            // CTA-uniform: nothing to do unless one of its queries is flagged
-    bool any = false;
-    for (int q = 0; q < kMQ; ++q) any = any || (q0 + q < a.M && a.flags[q0 + q] != 0);
-    if (!any) return;
-  }
+  const int n_q = a.qlist ? a.qlist[a.M] : a.M;      // queries to scan (a compacted list, or all of them)
+  if (q0 >= n_q) return;                             // CTA-uniform
 
   for (int idx = threadIdx.x; idx < d * kMQ; idx += blockDim.x) {
     const int j = idx / kMQ, q = idx % kMQ;
-    const bool ok = q0 + q < a.M;
-    reinterpret_cast<float*>(qa)[idx] = ok ? a.qk[static_cast<int64_t>(q0 + q) * 2 * d + j] : 0.f;
-    reinterpret_cast<float*>(wa)[idx] = ok ? a.qk[static_cast<int64_t>(q0 + q) * 2 * d + d + j] : 0.f;
+    const bool ok = q0 + q < n_q;
+    const int64_t qi = ok ? (a.qlist ? a.qlist[q0 + q] : q0 + q) : 0;
+    reinterpret_cast<float*>(qa)[idx] = ok ? a.qk[qi * 2 * d + j] : 0.f;
+    reinterpret_cast<float*>(wa)[idx] = ok ? a.qk[qi * 2 * d + d + j] : 0.f;
   }
   if (threadIdx.x < 16) kc_s[threadIdx.x] = threadIdx.x < (1 << WK) ? a.cent[threadIdx.x] : 0.f;
   if (threadIdx.x < kMQ) { cnt[threadIdx.x] = 0; thr[threadIdx.x] = -INFINITY; }
@@ -189,7 +187,7 @@ __global__ void __launch_bounds__(kScanThreads) index_scan_kernel(ScanArgs a) {
   if (DENSE) return;
 
   for (int q = warp; q < kMQ; q += kScanThreads / 32) {
-    if (q0 + q >= a.M) continue;
+    if (q0 + q >= n_q) continue;
     const int c = cnt[q];
     prune_warp(buf_s + q * kCap, buf_i + q * kCap, c, a.k, tmp_s + warp * QKV_INDEX_MAX_K,
                tmp_i + warp * QKV_INDEX_MAX_K, lane);
@@ -205,12 +203,13 @@ __global__ void __launch_bounds__(kScanThreads) index_scan_kernel(ScanArgs a) {
 // One warp per query: the r-th output is the best candidate that ranks after output r-1.
 __global__ void topk_merge_kernel(const float* __restrict__ in_s, const int64_t* __restrict__ in_i, int M,
                                   int64_t n_cand, int k_out, float* __restrict__ out_s,
-                                  int64_t* __restrict__ out_i, const int* __restrict__ flags) {
+                                  int64_t* __restrict__ out_i, const int* __restrict__ qlist) {
   const int lane = threadIdx.x & 31;
-  const int m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (m >= M || (flags && flags[m] == 0)) return;
-  const float* s = in_s + static_cast<int64_t>(m) * n_cand;
-  const int64_t* ids = in_i + static_cast<int64_t>(m) * n_cand;
+  const int mc = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);      // position in the input lists
+  if (mc >= (qlist ? qlist[M] : M)) return;
+  const int m = qlist ? qlist[mc] : mc;                                     // query whose result this is
+  const float* s = in_s + static_cast<int64_t>(mc) * n_cand;
+  const int64_t* ids = in_i + static_cast<int64_t>(mc) * n_cand;
   float prev_s = INFINITY; int64_t prev_i = -1; bool have_prev = false;
   for (int r = 0; r < k_out; ++r) {
     float best = -INFINITY; int64_t best_i = -1; bool have = false;
@@ -275,9 +274,38 @@ static int check_scan(const float* queries, int M, int d, const uint8_t* c, cons
   return QKV_OK;
 }
 
+// Flagged queries in ascending order at list[0 ..), their number at list[M] (one CTA, block-wide scan).
+__global__ void compact_flags_kernel(const int* __restrict__ flags, int M, int* __restrict__ list) {
+  __shared__ int warp_tot[32];
+  __shared__ int base_s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) base_s = 0;
+  __syncthreads();
+  for (int m0 = 0; m0 < M; m0 += blockDim.x) {
+    const int m = m0 + threadIdx.x;
+    const bool f = m < M && flags[m] != 0;
+    const unsigned bal = __ballot_sync(QKV_FULL_MASK, f);
+    if (lane == 0) warp_tot[warp] = __popc(bal);
+    __syncthreads();
+    int before = base_s;
+    for (int w = 0; w < warp; ++w) before += warp_tot[w];
+    if (f) list[before + __popc(bal & ((1u << lane) - 1u))] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int t = 0;
+      for (int w = 0; w < (blockDim.x >> 5); ++w) t += warp_tot[w];
+      base_s += t;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) list[M] = base_s;
+}
+
+static size_t flagged_qlist_bytes(int M) { return (static_cast<size_t>(M + 1) * sizeof(int) + 255) / 256 * 256; }
+
 size_t index_flagged_list_bytes(int64_t N, int M, int k) {
   const ScanPlan p = make_scan_plan(N, M, 128, k);
-  return p.ls_bytes + p.li_bytes;
+  return p.ls_bytes + (p.li_bytes + 255) / 256 * 256 + flagged_qlist_bytes(M);
 }
 
 int launch_scan_flagged(const float* qk, int M, int k, const uint8_t* codes, const uint8_t* signs,
@@ -288,14 +316,20 @@ int launch_scan_flagged(const float* qk, int M, int k, const uint8_t* codes, con
   a.qk = qk; a.M = M; a.d = 128; a.k = k;
   a.codes = reinterpret_cast<const uint32_t*>(codes); a.signs = reinterpret_cast<const uint32_t*>(signs);
   a.norms = norms; a.N = N; a.slice_len = p.slice_len; a.n_slices = p.n_slices; a.cent = cent;
-  a.id_base = id_base; a.flags = flags;
-  a.list_scores = reinterpret_cast<float*>(lists);
-  a.list_ids = reinterpret_cast<int64_t*>(reinterpret_cast<unsigned char*>(lists) + p.ls_bytes);
+  a.id_base = id_base;
+  unsigned char* lp = reinterpret_cast<unsigned char*>(lists);
+  a.list_scores = reinterpret_cast<float*>(lp);
+  a.list_ids = reinterpret_cast<int64_t*>(lp + p.ls_bytes);
+  int* qlist = reinterpret_cast<int*>(lp + p.ls_bytes + (p.li_bytes + 255) / 256 * 256);
+  a.qlist = qlist;
+  // The flagged queries are gathered into a dense list first, so that F of them cost ceil(F / 16) query tiles
+  // of the scan instead of up to F; the grid covers the worst case and CTAs beyond the list return at once.
+  compact_flags_kernel<<<1, 1024, 0, st>>>(flags, M, qlist);
   const int rc = launch_scan<false>(a, 2, dim3(p.n_slices, p.n_qtiles), st);
   if (rc) return rc;
   const int warps = 4;
   topk_merge_kernel<<<(M + warps - 1) / warps, warps * 32, 0, st>>>(
-      a.list_scores, a.list_ids, M, static_cast<int64_t>(p.n_slices) * k, k, out_scores, out_ids, flags);
+      a.list_scores, a.list_ids, M, static_cast<int64_t>(p.n_slices) * k, k, out_scores, out_ids, qlist);
   return check_launch();
 }
 
