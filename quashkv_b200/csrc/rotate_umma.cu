@@ -36,31 +36,34 @@ constexpr int kUWarps = kUThreads / 32;
 constexpr uint32_t kUPlaneBytes = 128 * 128 * 2;  // one bf16 operand tile (two 64-wide K blocks)
 constexpr uint32_t kUTmemCols = 256;
 
-// Bucket table of this kernel: 16384 buckets of width 1/8192 over [-1, 1).  The low nibble of an entry is
+// Bucket table of this kernel: LUTN buckets of width 2 / LUTN over [-1, 1) (32768 where shared memory allows:
+// bf16 input, uniform width; else 16384).  The low nibble of an entry is
 // the code of the bucket; bit 7 flags a bucket whose coordinates need a second look, of kind
 // 0x40 = decision boundary number (entry & 15) lies in or within the recheck margin of the bucket
 //        (code = that number, +1 if y is above it),
 // 0x20 = a centroid does (the sign bit needs the residual test),
 // 0x60 = anything else (edge buckets, two features in one bucket): generic path.
-__device__ __forceinline__ int bucket_fine(float v, float scale) {
-  return __float_as_int(fmaf(v, scale, 8192.f + 8388608.f)) & (kLutSize - 1);
+template <int LUTN>
+__device__ __forceinline__ int bucket_fine(float v, float scale) {          // scale = (LUTN / 2) / norm
+  return __float_as_int(fmaf(v, scale, static_cast<float>(LUTN / 2) + 8388608.f)) & (LUTN - 1);
 }
 
-template <int BITS, bool IP>
+template <int BITS, bool IP, int LUTN>
 __device__ __forceinline__ void build_fine_lut(uint8_t* lut, const float* bnd, const float* cent) {
   constexpr int NB = (1 << BITS) - 1;
-  for (int k = threadIdx.x; k < kLutSize; k += blockDim.x) {
-    const float lo = (static_cast<float>(k) - 8192.5f) * (1.f / 8192.f);
-    const float hi = (static_cast<float>(k) - 8191.5f) * (1.f / 8192.f);
+  constexpr float kHalf = static_cast<float>(LUTN / 2), kInv = 1.f / kHalf;
+  for (int k = threadIdx.x; k < LUTN; k += blockDim.x) {
+    const float lo = (static_cast<float>(k) - kHalf - 0.5f) * kInv;
+    const float hi = (static_cast<float>(k) - kHalf + 0.5f) * kInv;
     const float margin = kRecheckEps + 2e-6f;
     int n_b = 0, which = 0, n_c = 0;
     for (int b = 0; b < NB; ++b)
       if (bnd[b] >= lo - margin && bnd[b] <= hi + margin) { ++n_b; which = b; }
     if (IP)
       for (int c = 0; c <= NB; ++c) n_c += (cent[c] >= lo - margin && cent[c] <= hi + margin) ? 1 : 0;
-    const float mid = (static_cast<float>(k) - 8192.f) * (1.f / 8192.f);
+    const float mid = (static_cast<float>(k) - kHalf) * kInv;
     uint32_t v = count_bounds<BITS>(bnd, mid);
-    if (k == 0 || k == kLutSize - 1 || n_b > 1 || n_c > 1 || (n_b && n_c)) v |= 0xE0u;
+    if (k == 0 || k == LUTN - 1 || n_b > 1 || n_c > 1 || (n_b && n_c)) v |= 0xE0u;
     else if (n_b) v = static_cast<uint32_t>(which) | 0xC0u;
     else if (n_c) v |= 0xA0u;
     lut[k] = static_cast<uint8_t>(v);
@@ -122,7 +125,8 @@ template <int BITS, bool IP, int NT, int BITS1 = 0>
 __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArgs a) {
   constexpr bool MIXED = BITS1 != 0;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ int8_t lut_s[MIXED ? 2 : 1][kLutSize];
+  constexpr int LUTN = (NT == 1 && !MIXED) ? 2 * kLutSize : kLutSize;
+  __shared__ int8_t lut_s[MIXED ? 2 : 1][LUTN];
   __shared__ float bnd_s[2][16], cent_s[16], sgn_s[kRD];
   __shared__ uint8_t perm_s[kRD];
   const UmmaSmem s = carve_umma<NT>(smem_raw);
@@ -187,8 +191,9 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
     *s.dead = 0;
   }
   __syncthreads();
-  build_fine_lut<BITS, IP>(reinterpret_cast<uint8_t*>(lut_s[0]), bnd_s[0], cent_s);
-  if (MIXED) build_fine_lut<(MIXED ? BITS1 : 1), false>(reinterpret_cast<uint8_t*>(lut_s[MIXED ? 1 : 0]), bnd_s[1], cent_s);
+  build_fine_lut<BITS, IP, LUTN>(reinterpret_cast<uint8_t*>(lut_s[0]), bnd_s[0], cent_s);
+  if (MIXED)
+    build_fine_lut<(MIXED ? BITS1 : 1), false, LUTN>(reinterpret_cast<uint8_t*>(lut_s[MIXED ? 1 : 0]), bnd_s[1], cent_s);
   if (warp == 0) umma::tmem_alloc(s.tmem_slot, kUTmemCols);
   umma::fence_smem_to_async();
   umma::fence_before_sync();
@@ -347,7 +352,7 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
     const int64_t n = tile * kUTile + trow;
     const bool live = n < a.n_vec;
     const int64_t row = live ? map_row(a.rows, n) : 0;
-    const float iv = 1.f / nrm, scale = iv * 8192.f;
+    const float iv = 1.f / nrm, scale = iv * static_cast<float>(LUTN / 2);
     const int col0 = 32 * blk;
     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + buf * 128 + col0;
     uint32_t fmask = 0, fval = 0, R = 0;
@@ -361,7 +366,7 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
         const float raw = __uint_as_float(v[c]);
-        const int e = lut_c[bucket_fine(raw, scale)];             // sign-extended: negative when flagged
+        const int e = lut_c[bucket_fine<LUTN>(raw, scale)];             // sign-extended: negative when flagged
         fm = __funnelshift_l(static_cast<uint32_t>(e), fm, 1);
         const uint32_t code = static_cast<uint32_t>(e) & 15u;
         const int bit = BW * c, w = bit >> 5, sh = bit & 31;
@@ -389,7 +394,7 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
         if ((mine >> c) & 1u) {
           const int col = col0 + c;
           const float y = raw * iv;
-          const uint32_t ec = static_cast<uint8_t>(lut_c[bucket_fine(raw, scale)]);
+          const uint32_t ec = static_cast<uint8_t>(lut_c[bucket_fine<LUTN>(raw, scale)]);
           uint32_t code = ec & 15u, sign = 0;
           bool near = false;
           if ((ec & 0x60u) == 0x60u) {                 // edge bucket or two features: generic classification
