@@ -267,6 +267,55 @@ def test_mixed_precision(golden):
     assert m.shape == s.shape == (32, 128) and int(s.max()) <= 1 and ipq.effective_bits == pytest.approx(2.25)
 
 
+def test_tcgen05_rotation_edge_shapes(golden, monkeypatch):
+    """The tcgen05 rotation kernels on the inputs the other tests do not reach: fp16 input (split on
+    the fly), a ragged last tile, rows read and written through the (segment, offset) mapping of the
+    cache planes, keys decompressed with their sign term, bf16 output.  Reference: the CUDA-core
+    kernels (env switch), which the other tests pin to the oracle."""
+    c = golden("constants")
+    Pi, S = t(c["Pi_d128_s42"]).to(DEV), t(c["S_d128_s42"]).to(DEV)
+    bnd, cent = t(c["bnd_d128_b2"]).to(DEV), t(c["cent_d128_b2"]).to(DEV)
+    gen = torch.Generator().manual_seed(5)
+    x = torch.randn(3 * 1000 + 77, 128, generator=gen)
+
+    def both(fn):
+        fast = fn()
+        monkeypatch.setenv("QUASHKV_B200_CUDA_CORE_ROTATION", "1")
+        slow = fn()
+        monkeypatch.delenv("QUASHKV_B200_CUDA_CORE_ROTATION")
+        return fast, slow
+
+    xh = x.to(torch.float16).to(DEV)
+    f, s_ = both(lambda: ops.compress_ip(xh, Pi, bnd, cent, S, 2, packed=True))
+    assert all(torch.equal(a, b) for a, b in zip(f, s_)), "fp16 input"
+    mse, qjl, nrm = f
+    for dt, tol in ((torch.float32, 2e-6), (torch.bfloat16, 3e-4)):
+        a, b = both(lambda: ops.decompress(mse, nrm, Pi, cent, 2, signs=qjl, S=S, qjl_scale=0.0123, packed=True,
+                                           d=128, out_dtype=dt))
+        assert rel_l2(a, b) < tol, f"IP decompress {dt}: {rel_l2(a, b)}"
+    # engine planes: 3 segments of capacity 1280, 1000 live rows each, written in place at offset 100
+    K = torch.randn(1, 3, 1000, 128, generator=gen).to(torch.bfloat16).to(DEV)
+    V = torch.randn(1, 3, 1000, 128, generator=gen).to(torch.bfloat16).to(DEV)
+    vb, vc = t(c["bnd_d128_b3"]).to(DEV), t(c["cent_d128_b3"]).to(DEV)
+
+    def planes():
+        p = {"k_codes": torch.zeros(3, 1280, 32, dtype=torch.uint8, device=DEV),
+             "k_signs": torch.zeros(3, 1280, 16, dtype=torch.uint8, device=DEV),
+             "k_norms": torch.zeros(3, 1280, device=DEV),
+             "v_codes": torch.zeros(3, 1280, 48, dtype=torch.uint8, device=DEV),
+             "v_norms": torch.zeros(3, 1280, device=DEV)}
+        ops.append_kv(K, V, Pi, bnd, cent, S, 2, vb, 3, p["k_codes"], p["k_signs"], p["k_norms"], p["v_codes"],
+                      p["v_norms"], 100)
+        return p
+    pf, ps = both(planes)
+    for name in pf:
+        assert torch.equal(pf[name], ps[name]), name
+    a, b = both(lambda: ops.decompress_rows(pf["v_codes"], pf["v_norms"], Pi, vc, 3, 128, 3, 1000, 1280, 100))
+    assert a.shape == (3000, 128) and rel_l2(a, b) < 2e-6
+    from quashkv_b200 import _lib
+    assert _lib.lib().qkv_tensor_core_timeouts() == 0
+
+
 def test_mixed_precision_tensor_core_equals_cuda_core(golden, monkeypatch):
     """bf16 batches with a multiple of 32 outlier channels compress on the tcgen05 kernel (the rows of
     Pi staged in stream order); the packed bytes and norms must equal the CUDA-core kernel's.  Other
