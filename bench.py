@@ -193,6 +193,8 @@ def extras(device):
     mp = qk.MixedPrecisionMSEQuantizer(D, 3, 2, 32, seed=42)
     mp.calibrate(x[:4096].float())
     out["compress_mixed_2p5bit_Mvec_s"] = n / timed(lambda: mp.compress(x, packed=True)) / 1e6
+    mcodes, mnorms = mp.compress(x, packed=True)
+    out["decompress_mixed_2p5bit_Mvec_s"] = n / timed(lambda: mp.decompress(mcodes, mnorms, packed=True)) / 1e6
     del x
     g = torch.Generator(device=device).manual_seed(6)
     n_db, m = 1_000_000, 1024

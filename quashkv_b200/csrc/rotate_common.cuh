@@ -32,6 +32,7 @@ struct DecompressArgs {
   const uint8_t* is_outlier;
   const float* S; float qjl_scale;
   void* out; int out_dtype; int64_t out_pitch;
+  int skip_block_aligned;              // mixed, CUDA-core kernel: return if the outlier count is a multiple of 32
 };
 
 

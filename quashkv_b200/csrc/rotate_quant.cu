@@ -257,6 +257,7 @@ __global__ void __launch_bounds__(kThreads, 2) decompress_kernel(DecompressArgs 
   build_slots(s, mixed ? a.is_outlier : nullptr, d);
   __syncthreads();
   const int n_out = mixed ? count_outliers(s, d) : 0;
+  if (a.skip_block_aligned && (n_out & 31) == 0) return;      // uniform over the grid: the tcgen05 kernel did it
 
   float* stage = s.stage + static_cast<size_t>(warp) * d * kVPW;
   const int row_bytes_uniform = packed_row_bytes(d, a.bits0);
@@ -483,6 +484,12 @@ extern "C" int qkv_decompress_mixed(const uint8_t* codes, int packed, const floa
   a.n_vec = n_vec; a.d = d; a.Pi = Pi; a.mode = MODE_MIXED;
   a.cents0 = cents_out; a.bits0 = bits_out; a.cents1 = cents_reg; a.bits1 = bits_reg;
   a.is_outlier = is_outlier; a.out = out; a.out_dtype = out_dtype; a.out_pitch = out_pitch;
+  if (decompress_umma_ok(a) && !cuda_core_only() && !no_tcgen05()) {
+    // the tcgen05 kernel takes outlier counts that are multiples of 32 (a device-side test), the CUDA-core
+    // kernel behind it the others
+    if ((rc = launch_decompress_umma(a, static_cast<cudaStream_t>(stream)))) return rc;
+    a.skip_block_aligned = 1;
+  }
   return launch_by_nt(a, d, n_vec, static_cast<cudaStream_t>(stream), decompress_kernel<1>,
                       decompress_kernel<2>, decompress_kernel<3>, decompress_kernel<4>);
 }

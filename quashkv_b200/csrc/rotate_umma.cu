@@ -663,30 +663,67 @@ static __device__ __noinline__ float decompress_chain(const float* vrow, const f
   return z;
 }
 
-template <int BITS, bool SIGNS, int NT>
+// BITS1 != 0: mixed precision (no sign term).  The K dimension runs in STREAM order (outlier channels first):
+// A column k' is stream position k' and B row k' is Pi[perm[k']], so each thread's 32 coordinates belong to
+// one table; needs the outlier count to be a multiple of 32, otherwise the CTA returns and the CUDA-core
+// kernel launched behind it does the work (same device-side test, inverted).
+template <int BITS, bool SIGNS, int NT, int BITS1 = 0>
 __global__ void __launch_bounds__(kUThreads, 1) decompress_umma_kernel(DecompressArgs a) {
+  constexpr bool MIXED = BITS1 != 0;
+  constexpr int BMAX = BITS > BITS1 ? BITS : BITS1;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ float cent_s[16], qs_s[kRD];
-  __shared__ uint2 split_s[32];             // bf16 terms (h | m << 16, l) of the 2^(BITS+1) possible values
-  __shared__ uint32_t smask_s[4];           // bit c of word w: S[32 w + c] < 0
+  __shared__ float cent_s[2][16], qs_s[kRD];
+  __shared__ uint2 split_s[2][32];          // per table: bf16 terms (h | m << 16, l) of the possible values
+  __shared__ uint32_t smask_s[4];           // bit c of word w: S[32 w + c] < 0 (mixed: channel is an outlier)
+  __shared__ uint8_t perm_s[kRD];
   const DecSmem<NT> s = carve_dec<NT>(smem_raw);
   constexpr int NBUF = DecSmem<NT>::NBUF;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int trow = 32 * (warp & 3) + lane, blk = warp >> 2;
-  constexpr int row_words = 4 * BITS;
   const uint32_t* codes = reinterpret_cast<const uint32_t*>(a.codes);
   const uint32_t* signs = reinterpret_cast<const uint32_t*>(a.signs);
 
-  // ---- one-time setup: Pi^T planes (B[n = output j][k = input i] = Pi[i][j]), tables, barriers, TMEM -----
+  int n_out = MIXED ? 0 : kRD;                      // K positions below n_out use table 0
+  if (MIXED) {
+    bool o = false;
+    if (tid < kRD) {
+      o = a.is_outlier[tid] != 0;
+      const uint32_t m = __ballot_sync(QKV_FULL_MASK, o);
+      if (lane == 0) smask_s[warp] = m;
+    }
+    __syncthreads();
+    int before = 0;
+    for (int w = 0; w < 4; ++w) {
+      const int c = __popc(smask_s[w]);
+      n_out += c;
+      if (w < warp) before += c;
+    }
+    if (n_out & 31) return;                         // every thread of every CTA: left to the CUDA-core kernel
+    if (tid < kRD) {
+      before += __popc(smask_s[warp] & ((1u << lane) - 1u));
+      perm_s[o ? before : n_out + (tid - before)] = static_cast<uint8_t>(tid);
+    }
+    __syncthreads();
+  }
+  const int m_out = n_out >> 5;
+  const int row_words = MIXED ? m_out * BITS + (4 - m_out) * BITS1 : 4 * BITS;
+  const int cls = blk >= m_out ? 1 : 0;             // table of this thread's 32 K positions
+  const int word_off = cls ? m_out * BITS + (blk - m_out) * BITS1 : blk * BITS;
+  const int bits_c = cls ? BITS1 : BITS;
+
+  // ---- one-time setup: Pi^T planes (B[n = output j][k] = Pi[channel of k][j]), tables, barriers, TMEM -----
   for (int idx = tid; idx < kRD * kRD; idx += kUThreads) {
     const int i = idx >> 7, j = idx & 127;
     __nv_bfloat16 t3[3];
-    split3(a.Pi[idx], t3[0], t3[1], t3[2]);
+    split3(a.Pi[(MIXED ? perm_s[i] : i) * kRD + j], t3[0], t3[1], t3[2]);
     const uint32_t off = umma::sw128_offset(j, i, 128);
 #pragma unroll
     for (int t = 0; t < NT; ++t) *reinterpret_cast<__nv_bfloat16*>(s.b[t] + off) = t3[t];
   }
-  if (tid < 16) cent_s[tid] = tid < (1 << BITS) ? a.cents0[tid] : 0.f;
+  if (tid < 16) {
+    cent_s[0][tid] = tid < (1 << BITS) ? a.cents0[tid] : 0.f;
+    cent_s[1][tid] = (MIXED && tid < (1 << BITS1)) ? a.cents1[tid] : 0.f;
+  }
   bool pm1 = true;
   if (tid < kRD) {
     const float sv = SIGNS ? a.S[tid] : 1.f;
@@ -696,13 +733,15 @@ __global__ void __launch_bounds__(kUThreads, 1) decompress_umma_kernel(Decompres
     if (lane == 0) smask_s[warp] = neg;
   }
   const bool table_ok = __syncthreads_and(pm1) != 0;     // S = +-1 everywhere: the value table applies
-  if (tid < 32) {
-    const uint32_t code = tid & ((1u << BITS) - 1u);
-    float x = a.cents0[code < (1u << BITS) ? code : 0];
-    if (SIGNS) x += (tid >> BITS) & 1u ? a.qjl_scale : -a.qjl_scale;
+  if (tid < 64) {
+    const int tb = tid >> 5, e = tid & 31;
+    const int bw = tb ? (MIXED ? BITS1 : BITS) : BITS;
+    const uint32_t code = e & ((1u << bw) - 1u);
+    float x = (tb ? (MIXED ? a.cents1 : a.cents0) : a.cents0)[code];
+    if (SIGNS) x += (e >> BITS) & 1u ? a.qjl_scale : -a.qjl_scale;
     __nv_bfloat16 h, m, l;
     split3(x, h, m, l);
-    split_s[tid] = make_uint2(pack_bf16(h, m), static_cast<uint32_t>(__bfloat16_as_ushort(l)));
+    split_s[tb][e] = make_uint2(pack_bf16(h, m), static_cast<uint32_t>(__bfloat16_as_ushort(l)));
   }
   const uint32_t smask = SIGNS ? smask_s[blk] : 0u;
   if (tid == 0) {
@@ -723,52 +762,62 @@ __global__ void __launch_bounds__(kUThreads, 1) decompress_umma_kernel(Decompres
   // the code and by sign bit xor (S < 0); their exact bf16 terms sit in a shared-memory table, so a
   // coordinate costs a field extraction, one 8-byte look-up and its share of three PRMTs.
   // Packed words (and the norm) of this thread's part of a row, fetched one tile ahead of their use.
-  uint32_t nw[BITS + 1], nsw = 0;
+  uint32_t nw[BMAX + 1], nsw = 0;
   float nnorm = 0.f;
   auto fetch = [&](int64_t tile) {
     const int64_t n = tile * kUTile + trow;
     const bool live = tile < n_tiles && n < a.n_vec;
     const int64_t row = live ? map_row(a.rows, n) : 0;
 #pragma unroll
-    for (int q = 0; q < BITS; ++q) nw[q] = live ? __ldg(codes + row * row_words + blk * BITS + q) : 0u;
-    nw[BITS] = 0u;
+    for (int q = 0; q < BMAX; ++q) nw[q] = (live && q < bits_c) ? __ldg(codes + row * row_words + word_off + q) : 0u;
+    nw[BMAX] = 0u;
     if (SIGNS) nsw = live ? __ldg(signs + row * (kRD / 32) + blk) : 0u;
     nnorm = live ? __ldg(a.norms + row) : 0.f;
+  };
+  auto decode_table = [&](auto bits_tag, int bf) {    // table-driven decode at the bit width of this thread's table
+    constexpr int BW = decltype(bits_tag)::value;
+    const uint2* tab = split_s[cls];
+    const uint32_t sx = nsw ^ smask;                  // bit c: add (1) or subtract (0) qjl_scale
+#pragma unroll
+    for (int c8 = 0; c8 < 4; ++c8) {
+      uint32_t packed[3][4];
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        uint2 e[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int c = 8 * c8 + 2 * p + h;
+          const int bit = BW * c, wi = bit >> 5, sh = bit & 31;
+          uint32_t idx = nw[wi] >> sh;
+          if (sh + BW > 32) idx |= nw[wi + 1] << (32 - sh);
+          idx &= (1u << BW) - 1u;
+          if (SIGNS) idx |= (c >= BW ? (sx >> (c - BW)) : (sx << (BW - c))) & (1u << BW);
+          e[h] = tab[idx];
+        }
+        packed[0][p] = __byte_perm(e[0].x, e[1].x, 0x5410);
+        packed[1][p] = __byte_perm(e[0].x, e[1].x, 0x7632);
+        packed[2][p] = __byte_perm(e[0].y, e[1].y, 0x5410);
+      }
+      const uint32_t off = umma::sw128_offset(trow, 32 * blk + 8 * c8, 128);
+#pragma unroll
+      for (int t = 0; t < NT; ++t)
+        *reinterpret_cast<uint4*>(s.a[bf][t] + off) = make_uint4(packed[t][0], packed[t][1], packed[t][2], packed[t][3]);
+    }
   };
   auto decode_tile = [&](int64_t tile, int bf) {
     const int64_t n = tile * kUTile + trow;
     const bool live = n < a.n_vec;
+    if (MIXED) {
+      if (cls) decode_table(std::integral_constant<int, (MIXED ? BITS1 : BITS)>{}, bf);
+      else decode_table(std::integral_constant<int, BITS>{}, bf);
+      return;
+    }
     uint32_t w[BITS + 1];
 #pragma unroll
     for (int q = 0; q <= BITS; ++q) w[q] = nw[q];
     const uint32_t sw = nsw;
     if (table_ok) {
-      const uint32_t sx = sw ^ smask;                 // bit c: add (1) or subtract (0) qjl_scale
-#pragma unroll
-      for (int c8 = 0; c8 < 4; ++c8) {
-        uint32_t packed[3][4];
-#pragma unroll
-        for (int p = 0; p < 4; ++p) {
-          uint2 e[2];
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int c = 8 * c8 + 2 * p + h;
-            const int bit = BITS * c, wi = bit >> 5, sh = bit & 31;
-            uint32_t idx = w[wi] >> sh;
-            if (sh + BITS > 32) idx |= w[wi + 1] << (32 - sh);
-            idx &= (1u << BITS) - 1u;
-            if (SIGNS) idx |= (c >= BITS ? (sx >> (c - BITS)) : (sx << (BITS - c))) & (1u << BITS);
-            e[h] = split_s[idx];
-          }
-          packed[0][p] = __byte_perm(e[0].x, e[1].x, 0x5410);
-          packed[1][p] = __byte_perm(e[0].x, e[1].x, 0x7632);
-          packed[2][p] = __byte_perm(e[0].y, e[1].y, 0x5410);
-        }
-        const uint32_t off = umma::sw128_offset(trow, 32 * blk + 8 * c8, 128);
-#pragma unroll
-        for (int t = 0; t < NT; ++t)
-          *reinterpret_cast<uint4*>(s.a[bf][t] + off) = make_uint4(packed[t][0], packed[t][1], packed[t][2], packed[t][3]);
-      }
+      decode_table(std::integral_constant<int, BITS>{}, bf);
       return;
     }
 #pragma unroll
@@ -784,7 +833,7 @@ __global__ void __launch_bounds__(kUThreads, 1) decompress_umma_kernel(Decompres
           uint32_t code = w[wi] >> sh;
           if (sh + BITS > 32) code |= w[wi + 1] << (32 - sh);
           code &= (1u << BITS) - 1u;
-          float x = cent_s[code];
+          float x = cent_s[0][code];
           if (SIGNS) {
             const float q = qs_s[32 * blk + c];
             x += ((sw >> c) & 1u) ? q : -q;
@@ -840,11 +889,13 @@ __global__ void __launch_bounds__(kUThreads, 1) decompress_umma_kernel(Decompres
       umma::tmem_ld32(tmem_base + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + acc_buf * 128 + 32 * blk, v);
     } else if (live) {                                   // tensor core timed out: fp32 chain from the packed row
       float vrow[kRD];
-      for (int i = 0; i < kRD; ++i) {
-        const uint32_t code = read_field(a.codes + row * (row_words * 4), i * BITS, BITS, row_words * 4);
-        float x = cent_s[code];
+      for (int i = 0; i < kRD; ++i) {                    // i = stream position; channel = perm[i] when mixed
+        const int ci = i >= n_out ? 1 : 0;
+        const int bit = ci ? n_out * BITS + (i - n_out) * BITS1 : i * BITS;
+        const uint32_t code = read_field(a.codes + row * (row_words * 4), bit, ci ? BITS1 : BITS, row_words * 4);
+        float x = cent_s[ci][code];
         if (SIGNS) x += ((signs[row * (kRD / 32) + (i >> 5)] >> (i & 31)) & 1u) ? qs_s[i] : -qs_s[i];
-        vrow[i] = x;
+        vrow[MIXED ? perm_s[i] : i] = x;
       }
       for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(decompress_chain(vrow, a.Pi, 32 * blk + c));
     }
@@ -961,7 +1012,12 @@ __global__ void __launch_bounds__(kUThreads, 1) decompress_umma_kernel(Decompres
 bool decompress_umma_ok(const DecompressArgs& a) {
   const uintptr_t al = reinterpret_cast<uintptr_t>(a.codes) | reinterpret_cast<uintptr_t>(a.out) |
                        (a.signs ? reinterpret_cast<uintptr_t>(a.signs) : 0);
-  return a.d == kRD && a.mode != MODE_MIXED && a.packed && a.n_vec >= 1024 && (a.out_pitch & 7) == 0 &&
+  if (a.mode == MODE_MIXED) {   // the common width pairs; rows are whole 4-byte words (36 B at 32 x 3 + 96 x 2 bits)
+    const bool pair = (a.bits0 == 3 && a.bits1 == 2) || (a.bits0 == 4 && a.bits1 == 3) || (a.bits0 == 4 && a.bits1 == 2);
+    return pair && a.d == kRD && a.packed && a.n_vec >= 1024 && (a.out_pitch & 7) == 0 &&
+           ((reinterpret_cast<uintptr_t>(a.out) & 15u) | (reinterpret_cast<uintptr_t>(a.codes) & 3u)) == 0;
+  }
+  return a.d == kRD && a.packed && a.n_vec >= 1024 && (a.out_pitch & 7) == 0 &&
          (al & 15u) == 0;
 }
 
@@ -984,7 +1040,25 @@ static int launch_decompress_umma_b(const DecompressArgs& a, cudaStream_t st) {
   return exact ? launch_decompress_umma_t<BITS, false, 3>(a, st) : launch_decompress_umma_t<BITS, false, 2>(a, st);
 }
 
+template <int B0, int B1, int NT>
+static int launch_decompress_umma_mixed(const DecompressArgs& a, cudaStream_t st) {
+  constexpr size_t smem = dec_smem_bytes<NT>();
+  if (cudaFuncSetAttribute(decompress_umma_kernel<B0, false, NT, B1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem)) != cudaSuccess)
+    return QKV_ELAUNCH;
+  const int64_t tiles = (a.n_vec + kUTile - 1) / kUTile;
+  const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
+  decompress_umma_kernel<B0, false, NT, B1><<<grid, kUThreads, smem, st>>>(a);
+  return check_launch();
+}
+
 int launch_decompress_umma(const DecompressArgs& a, cudaStream_t st) {
+  if (a.mode == MODE_MIXED) {
+    const bool exact = a.out_dtype == QKV_F32;
+    if (a.bits0 == 3) return exact ? launch_decompress_umma_mixed<3, 2, 3>(a, st) : launch_decompress_umma_mixed<3, 2, 2>(a, st);
+    if (a.bits1 == 3) return exact ? launch_decompress_umma_mixed<4, 3, 3>(a, st) : launch_decompress_umma_mixed<4, 3, 2>(a, st);
+    return exact ? launch_decompress_umma_mixed<4, 2, 3>(a, st) : launch_decompress_umma_mixed<4, 2, 2>(a, st);
+  }
   switch (a.bits0) {
     case 1: return launch_decompress_umma_b<1>(a, st);
     case 2: return launch_decompress_umma_b<2>(a, st);

@@ -338,6 +338,12 @@ def test_mixed_precision_tensor_core_equals_cuda_core(golden, monkeypatch):
             n_bad = int((fast[0] != slow[0]).sum())
             assert n_bad == 0, f"bits {b_out}/{b_reg}, {n_out} outlier channels: {n_bad} packed bytes differ"
             assert torch.equal(fast[1], slow[1])
+            co, cr = t(c[f"cent_d128_b{b_out}"]).to(DEV), t(c[f"cent_d128_b{b_reg}"]).to(DEV)
+            rec_fast = ops.decompress_mixed(fast[0], fast[1], Pi, mask.to(DEV), co, b_out, cr, b_reg, packed=True, d=128)
+            monkeypatch.setenv("QUASHKV_B200_CUDA_CORE_ROTATION", "1")
+            rec_slow = ops.decompress_mixed(fast[0], fast[1], Pi, mask.to(DEV), co, b_out, cr, b_reg, packed=True, d=128)
+            monkeypatch.delenv("QUASHKV_B200_CUDA_CORE_ROTATION")
+            assert rel_l2(rec_fast, rec_slow) < 2e-6, f"mixed decompress {b_out}/{b_reg}, {n_out}: {rel_l2(rec_fast, rec_slow)}"
     from quashkv_b200 import _lib
     assert _lib.lib().qkv_tensor_core_timeouts() == 0
 
