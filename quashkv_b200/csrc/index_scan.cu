@@ -200,20 +200,13 @@ __global__ void __launch_bounds__(kScanThreads) index_scan_kernel(ScanArgs a) {
   }
 }
 
-// One warp per query: the r-th output is the best candidate that ranks after output r-1.
-__global__ void topk_merge_kernel(const float* __restrict__ in_s, const int64_t* __restrict__ in_i, int M,
-                                  int64_t n_cand, int k_out, float* __restrict__ out_s,
-                                  int64_t* __restrict__ out_i, const int* __restrict__ qlist) {
-  const int lane = threadIdx.x & 31;
-  const int mc = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);      // position in the input lists
-  if (mc >= (qlist ? qlist[M] : M)) return;
-  const int m = qlist ? qlist[mc] : mc;                                     // query whose result this is
-  const float* s = in_s + static_cast<int64_t>(mc) * n_cand;
-  const int64_t* ids = in_i + static_cast<int64_t>(mc) * n_cand;
+// Warp-wide: the k best of n candidates, in rank order, to (os, oi); the r-th output is the best candidate
+// that ranks after output r-1.  Missing results are (-inf, -1).
+__device__ void warp_topk(const float* s, const int64_t* ids, int64_t n, int k, float* os, int64_t* oi, int lane) {
   float prev_s = INFINITY; int64_t prev_i = -1; bool have_prev = false;
-  for (int r = 0; r < k_out; ++r) {
+  for (int r = 0; r < k; ++r) {
     float best = -INFINITY; int64_t best_i = -1; bool have = false;
-    for (int64_t p = lane; p < n_cand; p += 32) {
+    for (int64_t p = lane; p < n; p += 32) {
       const float v = s[p]; const int64_t id = ids[p];
       if (id < 0) continue;
       if (have_prev && !ranks_before(prev_s, prev_i, v, id)) continue;
@@ -226,18 +219,58 @@ __global__ void topk_merge_kernel(const float* __restrict__ in_s, const int64_t*
       const int h2 = __shfl_xor_sync(QKV_FULL_MASK, static_cast<int>(have), o);
       if (h2 && (!have || ranks_before(v2, i2, best, best_i))) { best = v2; best_i = i2; have = true; }
     }
-    if (lane == 0) {
-      out_s[static_cast<int64_t>(m) * k_out + r] = have ? best : -INFINITY;
-      out_i[static_cast<int64_t>(m) * k_out + r] = have ? best_i : -1;
-    }
+    if (lane == 0) { os[r] = have ? best : -INFINITY; oi[r] = have ? best_i : -1; }
     if (!have) {
-      for (int r2 = r + 1 + lane; r2 < k_out; r2 += 32) {
-        out_s[static_cast<int64_t>(m) * k_out + r2] = -INFINITY;
-        out_i[static_cast<int64_t>(m) * k_out + r2] = -1;
-      }
+      for (int r2 = r + 1 + lane; r2 < k; r2 += 32) { os[r2] = -INFINITY; oi[r2] = -1; }
       break;
     }
     prev_s = best; prev_i = best_i; have_prev = true;
+  }
+}
+
+// One warp per query.
+__global__ void topk_merge_kernel(const float* __restrict__ in_s, const int64_t* __restrict__ in_i, int M,
+                                  int64_t n_cand, int k_out, float* __restrict__ out_s,
+                                  int64_t* __restrict__ out_i, const int* __restrict__ qlist) {
+  const int lane = threadIdx.x & 31;
+  const int mc = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);      // position in the input lists
+  if (mc >= (qlist ? qlist[M] : M)) return;
+  const int m = qlist ? qlist[mc] : mc;                                     // query whose result this is
+  warp_topk(in_s + static_cast<int64_t>(mc) * n_cand, in_i + static_cast<int64_t>(mc) * n_cand, n_cand, k_out,
+            out_s + static_cast<int64_t>(m) * k_out, out_i + static_cast<int64_t>(m) * k_out, lane);
+}
+
+// Long candidate lists (few queries, many slices): one CTA of eight warps per query.  Every warp reduces an
+// eighth of the list to its k best in shared memory, then the first warp merges those 8 k.
+constexpr int kWideWarps = 8;
+__global__ void __launch_bounds__(kWideWarps * 32)
+topk_merge_wide_kernel(const float* __restrict__ in_s, const int64_t* __restrict__ in_i, int M, int64_t n_cand,
+                       int k_out, float* __restrict__ out_s, int64_t* __restrict__ out_i,
+                       const int* __restrict__ qlist) {
+  __shared__ float part_s[kWideWarps * QKV_INDEX_MAX_K];
+  __shared__ int64_t part_i[kWideWarps * QKV_INDEX_MAX_K];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int mc = blockIdx.x;
+  if (mc >= (qlist ? qlist[M] : M)) return;                                 // CTA-uniform
+  const int m = qlist ? qlist[mc] : mc;
+  const int64_t chunk = (n_cand + kWideWarps - 1) / kWideWarps;
+  const int64_t lo = warp * chunk, hi = lo + chunk < n_cand ? lo + chunk : n_cand;
+  warp_topk(in_s + static_cast<int64_t>(mc) * n_cand + lo, in_i + static_cast<int64_t>(mc) * n_cand + lo,
+            hi > lo ? hi - lo : 0, k_out, part_s + warp * k_out, part_i + warp * k_out, lane);
+  __syncthreads();
+  if (warp == 0)
+    warp_topk(part_s, part_i, kWideWarps * k_out, k_out, out_s + static_cast<int64_t>(m) * k_out,
+              out_i + static_cast<int64_t>(m) * k_out, lane);
+}
+
+static void launch_topk_merge(const float* in_s, const int64_t* in_i, int M, int64_t n_cand, int k_out,
+                              float* out_s, int64_t* out_i, const int* qlist, cudaStream_t st) {
+  if (n_cand >= 2048 && k_out <= QKV_INDEX_MAX_K) {
+    topk_merge_wide_kernel<<<M, kWideWarps * 32, 0, st>>>(in_s, in_i, M, n_cand, k_out, out_s, out_i, qlist);
+  } else {
+    const int warps = 4;
+    topk_merge_kernel<<<(M + warps - 1) / warps, warps * 32, 0, st>>>(in_s, in_i, M, n_cand, k_out, out_s, out_i,
+                                                                       qlist);
   }
 }
 
@@ -327,9 +360,8 @@ int launch_scan_flagged(const float* qk, int M, int k, const uint8_t* codes, con
   compact_flags_kernel<<<1, 1024, 0, st>>>(flags, M, qlist);
   const int rc = launch_scan<false>(a, 2, dim3(p.n_slices, p.n_qtiles), st);
   if (rc) return rc;
-  const int warps = 4;
-  topk_merge_kernel<<<(M + warps - 1) / warps, warps * 32, 0, st>>>(
-      a.list_scores, a.list_ids, M, static_cast<int64_t>(p.n_slices) * k, k, out_scores, out_ids, qlist);
+  launch_topk_merge(a.list_scores, a.list_ids, M, static_cast<int64_t>(p.n_slices) * k, k, out_scores, out_ids, qlist,
+                    st);
   return check_launch();
 }
 
@@ -405,8 +437,7 @@ extern "C" int qkv_topk_merge(const float* in_scores, const int64_t* in_ids, int
                               int k_out, float* out_scores, int64_t* out_ids, void* stream) {
   if (!in_scores || !in_ids || !out_scores || !out_ids) return QKV_ENULL;
   if (M < 1 || n_cand < 1 || k_out < 1) return QKV_EDIM;
-  const int warps = 4;
-  topk_merge_kernel<<<(M + warps - 1) / warps, warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      in_scores, in_ids, M, n_cand, k_out, out_scores, out_ids, nullptr);
+  launch_topk_merge(in_scores, in_ids, M, n_cand, k_out, out_scores, out_ids, nullptr,
+                    static_cast<cudaStream_t>(stream));
   return check_launch();
 }
