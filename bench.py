@@ -26,6 +26,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -138,6 +139,39 @@ def time_cpu(steps, warmup):
     return sample_bytes / sec / 1e9, sec, threads
 
 
+def cpu_extras():
+    """The oracle port of the secondary paths on the host cores, on bounded samples (a few seconds in all):
+    the CPU figures that stand beside the `extra` block of the GPU arm."""
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from oracle import quashkv_oracle as orc
+    out = {}
+    g = torch.Generator().manual_seed(3)
+    n = 1 << 16
+    x = torch.randn(n, D, generator=g).to(torch.bfloat16)
+    Pi, Sg = orc.rotation_matrix(D, 42), orc.sign_vector(D, 42)
+    for bits in (2, 3):
+        cent, bnd = orc.lloyd_max_tables(D, bits)
+        t0 = time.perf_counter()
+        codes, norms = orc.compress_mse(x, Pi, bnd)
+        orc.pack_bits(codes, bits)
+        out[f"compress_mse_{bits}bit_Mvec_s"] = n / (time.perf_counter() - t0) / 1e6
+        t0 = time.perf_counter()
+        orc.decompress_mse(codes, norms, Pi, cent)
+        out[f"decompress_mse_{bits}bit_Mvec_s"] = n / (time.perf_counter() - t0) / 1e6
+    cent2, bnd2 = orc.lloyd_max_tables(D, 2)
+    n_db, m = 100_000, 16
+    db = torch.randn(n_db, D, generator=g)
+    mse, sg, nrm = orc.compress_ip(db, Pi, bnd2, cent2, Sg)
+    qs = torch.randn(m, D, generator=g)
+    qjl = math.sqrt(math.pi / 2.0) / D
+    t0 = time.perf_counter()
+    orc.index_search(qs, mse, sg, nrm, Pi, cent2, Sg, qjl, 10)
+    sec = time.perf_counter() - t0
+    out["index_search_1M_x1024_queries_s"] = m / (sec * (1_000_000 / n_db))     # scaled to the 1M-row shard
+    out["sample"] = "65,536 vectors (compress / decompress incl. packing); 100,000 rows x 16 queries scaled to 1M rows"
+    return out
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -153,6 +187,7 @@ def run_reference(args):
                    "kv_len": S, "head_dim": D, "key_bits": KEY_BITS, "value_bits": VAL_BITS, "sample": sample},
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "extra": {} if args.no_extras else cpu_extras(),
     }))
 
 
