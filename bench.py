@@ -231,6 +231,15 @@ def extras(device):
     mcodes, mnorms = mp.compress(x, packed=True)
     out["decompress_mixed_2p5bit_Mvec_s"] = n / timed(lambda: mp.decompress(mcodes, mnorms, packed=True)) / 1e6
     del x
+    # causal prefill attention over the packed cache: 2 x 8 KV heads x 4096 tokens, 32 query heads, all rows
+    eng = qk.QuashKVEngine(D, 3, 3, seed=42, pack_storage=True)
+    gk = torch.Generator(device=device).manual_seed(11)
+    Kp = torch.randn(2, 8, 4096, D, device=device, generator=gk).to(torch.bfloat16)
+    Vp = torch.randn(2, 8, 4096, D, device=device, generator=gk).to(torch.bfloat16)
+    Qp = torch.randn(2, 32, 4096, D, device=device, generator=gk).to(torch.bfloat16)
+    eng.append(Kp, Vp)
+    out["prefill_causal_4096_ms"] = timed(lambda: eng.attention(Qp, causal=True), reps=2) * 1e3
+    del eng, Kp, Vp, Qp
     g = torch.Generator(device=device).manual_seed(6)
     n_db, m = 1_000_000, 1024
     db = torch.randn(n_db, D, device=device, generator=g)

@@ -427,7 +427,7 @@ extern "C" int qkv_attention(const void* q, int q_dtype, qkv_cache_t cache,
       ((reinterpret_cast<uintptr_t>(cache.k_norms) | reinterpret_cast<uintptr_t>(cache.v_norms)) & 15u) == 0;
   const bool use_mma = mma_path_ok(d, key_bits, val_bits, Hq / Hkv, q_len) && chunks_ok && !force_generic;
   int rc = launch_rotate(q, q_dtype, p.rows, d, Pi, S, qjl_scale, scale, qk, key_centroids, val_centroids,
-                         use_mma ? tables : nullptr, B * Hkv, st);
+                         use_mma ? tables : nullptr, B * Hkv * (((Hq / Hkv) * q_len + 7) / 8), st);
   if (rc) return rc;
 
   AttnArgs a{};

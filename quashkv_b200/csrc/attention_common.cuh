@@ -29,7 +29,7 @@ constexpr size_t kAttnHeaderBytes = 256;   // workspace header: look-up tables o
 
 struct AttnPlan {
   int n_splits; int64_t split_len; int n_qtiles; int64_t rows;
-  size_t hdr_bytes;     // look-up tables (first 256 bytes) + one arrival counter per (batch, kv head)
+  size_t hdr_bytes;     // look-up tables (first 256 bytes) + the arrival counters of the tensor-core path
   size_t qk_bytes, part_bytes;
 };
 
@@ -64,7 +64,8 @@ inline AttnPlan make_plan(int B, int Hq, int Hkv, int q_len, int64_t kv_len, int
   p.split_len = len;
   p.n_splits = static_cast<int>((kv_len + len - 1) / len);
   if (p.n_splits < 1) p.n_splits = 1;
-  p.hdr_bytes = (kAttnHeaderBytes + static_cast<size_t>(B) * Hkv * sizeof(unsigned) + 255) / 256 * 256;
+  // arrival counters: one per (batch, kv head, tile of eight query rows) of the tensor-core path
+  p.hdr_bytes = (kAttnHeaderBytes + static_cast<size_t>(B) * Hkv * ((nq + 7) / 8) * sizeof(unsigned) + 255) / 256 * 256;
   p.qk_bytes = static_cast<size_t>(p.rows) * 2 * d * sizeof(float);
   p.qk_bytes = (p.qk_bytes + 255) / 256 * 256;
   p.part_bytes = static_cast<size_t>(p.rows) * p.n_splits * (d + 2) * sizeof(float);

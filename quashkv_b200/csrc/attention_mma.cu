@@ -59,13 +59,17 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
   const int gid = lane >> 2, tig = lane & 3;
   const int split = blockIdx.x, seg = blockIdx.z;
   const int b = seg / a.Hkv, hkv = seg % a.Hkv;
-  const int nq = a.G * a.q_len;
+  // Query rows of a (batch, kv head) are numbered g * q_len + position; a CTA takes eight of them
+  // (blockIdx.y), so decode (one tile) and prefill (many) run through the same code.
+  const int r0 = 8 * blockIdx.y;
+  const int nq_all = a.G * a.q_len;
+  const int nq = nq_all - r0 < 8 ? nq_all - r0 : 8;
 
   for (int idx = threadIdx.x; idx < 8 * 2 * D; idx += blockDim.x) {
     const int r = idx / (2 * D), e = idx % (2 * D);
     float v = 0.f;
     if (r < nq) {
-      const int g = r / a.q_len, qi = r % a.q_len;
+      const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
       const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
       v = a.qk[qrow * 2 * D + e];
     }
@@ -119,7 +123,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
     const int r = 2 * tig + e;
-    lim[e] = (r < nq) ? (a.causal ? static_cast<int>(a.kv_len - a.q_len + r % a.q_len) : 0x7fffffff) : -1;
+    lim[e] = (r < nq) ? (a.causal ? static_cast<int>(a.kv_len - a.q_len + (r0 + r) % a.q_len) : 0x7fffffff) : -1;
   }
 
   const int64_t seg_row0 = static_cast<int64_t>(seg) * a.cache.capacity;
@@ -133,6 +137,12 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
   const int64_t t_begin = split * a.split_len;
   int64_t t_end = t_begin + a.split_len;
   if (t_end > a.kv_len) t_end = a.kv_len;
+  if (a.causal) {                      // tokens past the last position any row of this tile may see are skipped
+    int last = 0;
+    for (int r = 0; r < nq; ++r) last = max(last, (r0 + r) % a.q_len);
+    const int64_t visible = a.kv_len - a.q_len + last + 1;
+    if (t_end > visible) t_end = visible;
+  }
   const int n_valid = static_cast<int>(t_end - t_begin);        // tokens of this split
   // positions relative to the split start, as 32-bit values
   int lim_rel[2];
@@ -378,7 +388,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
         v += f * red[w][r][e];
       }
     }
-    const int g = r / a.q_len, qi = r % a.q_len;
+    const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
     const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
     a.part[(qrow * a.n_splits + split) * (D + 2) + e] = v;
   }
@@ -387,7 +397,8 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
   __shared__ bool last_split;
   __threadfence();                                   // this CTA's partials are visible device-wide
   __syncthreads();
-  if (threadIdx.x == 0) last_split = atomicAdd(a.arrivals + seg, 1u) == static_cast<unsigned>(a.n_splits - 1);
+  if (threadIdx.x == 0)
+    last_split = atomicAdd(a.arrivals + seg * gridDim.y + blockIdx.y, 1u) == static_cast<unsigned>(a.n_splits - 1);
   __syncthreads();
   if (!last_split) return;
   __threadfence();                                   // ... and so are everyone else's, now
@@ -395,7 +406,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
   float* wgt = vec + 8 * D;                          // [8][kMaxSplits] weights of the splits
   float* invl = wgt + 8 * kMaxSplits;                // [8]
   for (int r = warp; r < nq; r += kMmaWarps) {       // a warp per query row
-    const int g = r / a.q_len, qi = r % a.q_len;
+    const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
     const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
     const float* pp = a.part + qrow * a.n_splits * (D + 2);
     float M = -INFINITY;
@@ -416,7 +427,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
   __syncthreads();
   for (int idx = threadIdx.x; idx < nq * D; idx += blockDim.x) {
     const int r = idx / D, j = idx % D;
-    const int g = r / a.q_len, qi = r % a.q_len;
+    const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
     const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
     const float* pp = a.part + qrow * a.n_splits * (D + 2);
     float v = 0.f;
@@ -436,7 +447,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
       for (int r = 0; r < 8; ++r) o[r] = fmaf(vec[r * D + j], mval, o[r]);
     }
     for (int r = 0; r < nq; ++r) {
-      const int g = r / a.q_len, qi = r % a.q_len;
+      const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
       const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
       a.out[qrow * D + i] = o[r];
     }
@@ -444,11 +455,12 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
 }
 
 bool mma_path_ok(int d, int key_bits, int val_bits, int group, int q_len) {
-  return d == 128 && key_bits == 3 && val_bits == 3 && group * q_len <= 8;
+  (void)group; (void)q_len;            // any number of query rows: tiles of eight
+  return d == 128 && key_bits == 3 && val_bits == 3;
 }
 
 int launch_attend_mma(const AttnArgs& a, cudaStream_t st) {
-  const dim3 grid(a.n_splits, 1, a.B * a.Hkv);
+  const dim3 grid(a.n_splits, (a.G * a.q_len + 7) / 8, a.B * a.Hkv);
   attend_decode_mma_kernel<<<grid, kMmaWarps * 32, 0, st>>>(a);
   return check_launch();
 }

@@ -465,11 +465,13 @@ def test_decode_gqa_bf16_vs_oracle(golden, S, appends):
     assert err < BF16_TOL and err < FP32_TOL
 
 
-@pytest.mark.parametrize("G,q_len,causal", [(4, 1, False), (8, 1, False), (4, 2, True), (1, 8, True), (2, 3, False)])
+@pytest.mark.parametrize("G,q_len,causal", [(4, 1, False), (8, 1, False), (4, 2, True), (1, 8, True), (2, 3, False),
+                                            (4, 37, True), (2, 16, False), (1, 200, True), (3, 5, True)])
 def test_tensor_core_decode_path_vs_generic_and_oracle(G, q_len, causal, monkeypatch):
-    """head_dim 128 with 3/3 bits and at most 8 query rows per KV head takes the tensor-core kernel;
-    it must agree with the oracle and with the generic kernel on the same cache (ragged length, so
-    the last tile and the last split are partial)."""
+    """head_dim 128 with 3/3 bits takes the tensor-core kernel, eight query rows of a KV head per CTA
+    (one tile for decode, many for prefill, a last partial tile, tiles that straddle two query
+    heads); it must agree with the oracle and with the generic kernel on the same cache (ragged
+    length, so the last tile and the last split are partial; causal rows see different lengths)."""
     B, Hkv, S, D = 2, 3, 1000 + 13, 128
     K, V = _outlier_kv(B, Hkv, S, D, 5, torch.float32)
     eng = qk.QuashKVEngine(D, 3, 3, seed=42, pack_storage=True)
