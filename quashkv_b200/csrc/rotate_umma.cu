@@ -507,18 +507,17 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
         umma::fence_after_sync();
         issue_mmas(buf, buf);
       }
+      // The MMAs of tile i-1 were issued a whole iteration ago: their barrier is normally complete, so the
+      // copy of tile i+1 into the buffer they read starts right away and travels during everything below.
+      const int64_t next = tile + gridDim.x;
+      bool ok = true;
+      if (prev_tile >= 0) ok = wait_acc(buf ^ 1);
+      if (next < n_tiles) load_tile(next, buf ^ 1);
       const float norm_prev = prev_tile >= 0 ? row_norm(buf ^ 1) : 1.f;   // squares(i-1) were left before the barrier
       // the fp64 sums of half the warps go before the epilogue and of the other half after it, so that the
       // sixteen warps do not queue for the fp64 pipe at the same moment
       if (blk < 2) part_squares(buf);
-      const int64_t next = tile + gridDim.x;
-      if (prev_tile >= 0) {
-        const bool ok = wait_acc(buf ^ 1);
-        if (next < n_tiles) load_tile(next, buf ^ 1);     // A(i-1) has been consumed
-        epilogue(prev_tile, buf ^ 1, norm_prev, ok);
-      } else if (next < n_tiles) {
-        load_tile(next, buf ^ 1);
-      }
+      if (prev_tile >= 0) epilogue(prev_tile, buf ^ 1, norm_prev, ok);
       if (blk >= 2) part_squares(buf);
       prev_tile = tile;
     }
