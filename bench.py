@@ -240,6 +240,27 @@ def extras(device):
     eng.append(Kp, Vp)
     out["prefill_causal_4096_ms"] = timed(lambda: eng.attention(Qp, causal=True), reps=2) * 1e3
     del eng, Kp, Vp, Qp
+    # decode attention through a block table: the headline shape (32 sequences x 8 KV heads x 32768 tokens, 32
+    # query heads) as 16-token pages handed out in random order, then the same pool with ragged lengths
+    from quashkv_b200.integrations.vllm_backend import QuashKVPagedCache
+    n_seq, per_seq = 32, 32768 // 16
+    pool = QuashKVPagedCache(n_seq * per_seq, 8, D, device=device)
+    gp = torch.Generator(device=device).manual_seed(12)
+    for name, plane in pool.planes.items():
+        if plane.dtype == torch.uint8:
+            plane.copy_(torch.randint(0, 256, plane.shape, device=device, dtype=torch.uint8, generator=gp))
+        else:
+            plane.copy_(torch.rand(plane.shape, device=device, generator=gp) + 0.5)
+    table = torch.randperm(n_seq * per_seq, device=device, generator=gp).to(torch.int32).reshape(n_seq, per_seq)
+    Qd = torch.randn(n_seq, 32, 1, D, device=device, generator=gp).to(torch.bfloat16)
+    row_bytes = 8 * (32 + 16 + 48 + 8)          # packed bytes of one token over the 8 KV heads
+    full = torch.full((n_seq,), 32768, dtype=torch.int32, device=device)
+    sec = timed(lambda: pool.attention_with_tables(Qd, table, full, 32768), reps=20)
+    out["paged_decode_32x32768_GB_s"] = n_seq * 32768 * row_bytes / sec / 1e9
+    ragged = torch.randint(1024, 32769, (n_seq,), device=device, generator=gp).to(torch.int32)
+    sec = timed(lambda: pool.attention_with_tables(Qd, table, ragged, 32768), reps=20)
+    out["paged_decode_ragged_1k_32k_GB_s"] = int(ragged.sum()) * row_bytes / sec / 1e9
+    del pool, table, Qd
     g = torch.Generator(device=device).manual_seed(6)
     n_db, m = 1_000_000, 1024
     db = torch.randn(n_db, D, device=device, generator=g)

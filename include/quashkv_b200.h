@@ -190,6 +190,48 @@ int qkv_attention_static_scratch(const void* q, int q_dtype, qkv_cache_t cache,
                                  const float* S, float qjl_scale, float scale, int causal,
                                  float* out, void* stream);
 
+/* ---- attention over a paged (block-table) cache -------------------------------------------------
+ * The storage shape a serving engine's block allocator hands out: the reference keeps one page of
+ * `block_size` tokens per entry (integrations/vllm_backend.py:73-79, QuashKVPageConfig.block_size
+ * = 16; :82-195 QuashKVPageManager) but attends over its engine's contiguous blocks; here the
+ * pages are the storage and every batch entry has its own length.
+ *
+ * Pool planes, `block_size` rows per (block, kv head):
+ *   k_codes [num_blocks, Hkv, block_size, d*(key_bits-1)/8]   k_signs [.., d/8]   k_norms [..] fp32
+ *   v_codes [num_blocks, Hkv, block_size, d*val_bits/8]       v_norms [..] fp32
+ *   block_table (B, max_blocks) int32: token t of batch entry b is row t % block_size of block
+ *               block_table[b][t / block_size]; entries past an entry's length are not read
+ *   seq_lens    (B) int32: tokens of each entry (0 gives a zero output row); values above
+ *               max_kv_len are clamped to it
+ * max_kv_len sizes the split plan and the workspace (qkv_attention_workspace_bytes with kv_len =
+ * max_kv_len); with `causal`, query row i of entry b sits at position seq_lens[b] - q_len + i.
+ * Everything else as qkv_attention.  block_size a multiple of 16 keeps d = 128, 3/3-bit caches on
+ * the tensor-core kernel. */
+typedef struct {
+  const uint8_t* k_codes;
+  const uint8_t* k_signs;
+  const float* k_norms;
+  const uint8_t* v_codes;
+  const float* v_norms;
+  const int32_t* block_table;
+  const int32_t* seq_lens;
+  int max_blocks;
+  int block_size;
+} qkv_paged_cache_t;
+
+int qkv_attention_paged(const void* q, int q_dtype, qkv_paged_cache_t pool,
+                        int B, int Hq, int Hkv, int q_len, int64_t max_kv_len, int d,
+                        int key_bits, int val_bits,
+                        const float* Pi, const float* key_centroids, const float* val_centroids,
+                        const float* S, float qjl_scale, float scale, int causal,
+                        float* out, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Row scatter for appends into a paged pool: row i of src (n_rows rows of row_bytes bytes, a
+ * multiple of 4) is written to row slots[i] of dst; a negative slot drops the row.  Stands where the
+ * reference appends a block to its list (engine.py:145-172). */
+int qkv_scatter_rows(const void* src, void* dst, const int64_t* slots, int64_t n_rows, int row_bytes,
+                     void* stream);
+
 /* ---- index scan ------------------------------------------------------------------------------
  * Replaces QuashIndex.search (reference nn_search/index.py:121-163):
  * score[m,n] = norm_n * (q_rot_m . c[code_n] + qjl_scale * sum(|q_rot_m| * S * (2*sign_n-1))),

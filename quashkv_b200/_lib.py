@@ -29,6 +29,13 @@ class Cache(C.Structure):
                 ("v_norms", _vp), ("capacity", _i64)]
 
 
+class PagedCache(C.Structure):
+    """qkv_paged_cache_t: the five packed planes of a [blocks, kv heads, block_size, ...] pool, the
+    (B, max_blocks) int32 block table and the (B) int32 token counts."""
+    _fields_ = [("k_codes", _vp), ("k_signs", _vp), ("k_norms", _vp), ("v_codes", _vp), ("v_norms", _vp),
+                ("block_table", _vp), ("seq_lens", _vp), ("max_blocks", _i), ("block_size", _i)]
+
+
 # symbol -> (restype, argtypes); every symbol include/quashkv_b200.h declares is listed here
 SIGNATURES = {
     "qkv_abi_version": (_i, []),
@@ -46,6 +53,9 @@ SIGNATURES = {
                            _vp, _vp, _sz, _vp]),
     "qkv_attention_static_scratch": (_i, [_vp, _i, Cache, _i, _i, _i, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp,
                                           _f, _f, _i, _vp, _vp]),
+    "qkv_attention_paged": (_i, [_vp, _i, PagedCache, _i, _i, _i, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _f, _f,
+                                 _i, _vp, _vp, _sz, _vp]),
+    "qkv_scatter_rows": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "qkv_index_workspace_bytes": (_sz, [_i64, _i, _i, _i]),
     "qkv_index_scan_topk": (_i, [_vp, _i, _i, _vp, _vp, _vp, _i64, _i, _vp, _vp, _vp, _f, _i, _i64, _vp, _vp,
                                  _vp, _sz, _vp]),

@@ -110,6 +110,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attend_split_kernel(AttnArgs 
   const int seg = blockIdx.z;                 // b * Hkv + hkv
   const int b = seg / a.Hkv, hkv = seg % a.Hkv;
   const int nq = a.G * a.q_len;
+  // a paged cache has its own token count per batch entry; a.kv_len is then only their upper bound
+  const bool paged = a.block_table != nullptr;
+  int64_t kv_len = a.kv_len;
+  if (paged) kv_len = min(static_cast<int64_t>(max(a.seq_lens[b], 0)), a.kv_len);
 
   // ---- stage the query tile: qa[slot*33 + c] = (q0, q1, q2, q3) of coordinate slot*32+c ----
   int64_t qrow[kQT];
@@ -120,7 +124,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attend_split_kernel(AttnArgs 
     if (r < nq) {
       const int g = r / a.q_len, qi = r % a.q_len;
       qrow[q] = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
-      limit[q] = a.causal ? static_cast<int>(a.kv_len - a.q_len + qi) : static_cast<int>(a.kv_len - 1);
+      limit[q] = a.causal ? static_cast<int>(kv_len - a.q_len + qi) : static_cast<int>(kv_len - 1);
     } else {
       qrow[q] = -1;
       limit[q] = -1;
@@ -146,10 +150,12 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attend_split_kernel(AttnArgs 
 
   const int64_t t_begin = split * a.split_len;
   int64_t t_end = t_begin + a.split_len;
-  if (t_end > a.kv_len) t_end = a.kv_len;
+  if (t_end > kv_len) t_end = kv_len;
 
   const int words_k = (d >> 5) * WK, words_v = (d >> 5) * WV, words_s = d >> 5;
-  const int64_t seg_row0 = static_cast<int64_t>(seg) * a.cache.capacity;
+  // contiguous cache: first row of this (batch, kv head); paged cache: this head's rows inside block 0
+  const int64_t seg_row0 = paged ? static_cast<int64_t>(hkv) * a.block_size : static_cast<int64_t>(seg) * a.cache.capacity;
+  const int32_t* bt = paged ? a.block_table + static_cast<int64_t>(b) * a.max_blocks : nullptr;
   const uint32_t* kcode = reinterpret_cast<const uint32_t*>(a.cache.k_codes) + seg_row0 * words_k;
   const uint32_t* ksign = reinterpret_cast<const uint32_t*>(a.cache.k_signs) + seg_row0 * words_s;
   const uint32_t* vcode = reinterpret_cast<const uint32_t*>(a.cache.v_codes) + seg_row0 * words_v;
@@ -167,8 +173,13 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attend_split_kernel(AttnArgs 
 
   for (int64_t t0 = t_begin + static_cast<int64_t>(warp) * tps; t0 < t_end;
        t0 += static_cast<int64_t>(kAttnWarps) * tps) {
-    const int64_t tok = t0 + ts;
-    const bool live = tok < t_end && slot_live;
+    const int64_t pos = t0 + ts;               // token position; `tok` is its row relative to seg_row0
+    int64_t tok = pos;
+    if (paged && pos < t_end) {
+      const unsigned up = static_cast<unsigned>(pos), bs = static_cast<unsigned>(a.block_size);
+      tok = static_cast<int64_t>(__ldg(bt + up / bs)) * a.Hkv * a.block_size + up % bs;
+    }
+    const bool live = pos < t_end && slot_live;
     uint32_t kw[WK], vw[WV], sw = 0;
     float kn = 0.f, vn = 0.f;
 #pragma unroll
@@ -176,7 +187,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attend_split_kernel(AttnArgs 
 #pragma unroll
     for (int i = 0; i < WV; ++i) vw[i] = live ? __ldg(vcode + tok * words_v + slot * WV + i) : 0u;
     if (live) sw = __ldg(ksign + tok * words_s + slot);
-    if (tok < t_end) {                       // every lane of a token, so the softmax stays warp-uniform
+    if (pos < t_end) {                       // every lane of a token, so the softmax stays warp-uniform
       kn = __ldg(knorm + tok);
       vn = __ldg(vnorm + tok);
     }
@@ -204,7 +215,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attend_split_kernel(AttnArgs 
     bool grew = false;
 #pragma unroll
     for (int q = 0; q < kQT; ++q) {
-      const bool vis = tok < t_end && tok <= limit[q];
+      const bool vis = pos < t_end && pos <= limit[q];
       sc[q] = vis ? kn * s[q] : -INFINITY;
       mx[q] = sc[q];
     }
@@ -392,22 +403,34 @@ extern "C" size_t qkv_attention_workspace_bytes(int B, int Hq, int Hkv, int q_le
   return p.hdr_bytes + p.qk_bytes + p.part_bytes;
 }
 
-extern "C" int qkv_attention(const void* q, int q_dtype, qkv_cache_t cache,
-                             int B, int Hq, int Hkv, int q_len, int64_t kv_len, int d,
-                             int key_bits, int val_bits,
-                             const float* Pi, const float* key_centroids, const float* val_centroids,
-                             const float* S, float qjl_scale, float scale, int causal,
-                             float* out, void* workspace, size_t workspace_bytes, void* stream) {
+namespace {
+struct PagedInfo {
+  const int32_t* block_table; const int32_t* seq_lens;
+  int max_blocks, block_size;
+};
+
+int attention_run(const void* q, int q_dtype, qkv_cache_t cache, const PagedInfo* paged,
+                  int B, int Hq, int Hkv, int q_len, int64_t kv_len, int d,
+                  int key_bits, int val_bits,
+                  const float* Pi, const float* key_centroids, const float* val_centroids,
+                  const float* S, float qjl_scale, float scale, int causal,
+                  float* out, void* workspace, size_t workspace_bytes, void* stream) {
   if (!q || !cache.k_codes || !cache.k_signs || !cache.k_norms || !cache.v_codes || !cache.v_norms ||
       !Pi || !key_centroids || !val_centroids || !S || !out || !workspace)
     return QKV_ENULL;
   if (q_dtype != QKV_F32 && q_dtype != QKV_BF16 && q_dtype != QKV_F16) return QKV_EDTYPE;
   if (d < 32 || d > kMaxD || (d & 31)) return QKV_EDIM;
-  if (B < 1 || Hq < 1 || Hkv < 1 || q_len < 1 || kv_len < 1 || kv_len > cache.capacity ||
+  if (B < 1 || Hq < 1 || Hkv < 1 || q_len < 1 || kv_len < 1 || (!paged && kv_len > cache.capacity) ||
       kv_len > 0x7fffffff || Hq % Hkv != 0)
     return QKV_EDIM;
   if (key_bits < 2 || key_bits > 4 || val_bits < 1 || val_bits > 4) return QKV_EBITS;
   if (causal && q_len > kv_len) return QKV_EARG;
+  if (paged) {
+    if (!paged->block_table || !paged->seq_lens) return QKV_ENULL;
+    if (paged->block_size < 1 || paged->max_blocks < 1 ||
+        static_cast<int64_t>(paged->max_blocks) * paged->block_size < kv_len)
+      return QKV_EARG;
+  }
   const uintptr_t al = reinterpret_cast<uintptr_t>(cache.k_codes) | reinterpret_cast<uintptr_t>(cache.k_signs) |
                        reinterpret_cast<uintptr_t>(cache.v_codes) | reinterpret_cast<uintptr_t>(workspace);
   if (al & 15u) return QKV_EALIGN;
@@ -423,7 +446,8 @@ extern "C" int qkv_attention(const void* q, int q_dtype, qkv_cache_t cache,
   const char* env = getenv("QUASHKV_B200_GENERIC_ATTENTION");
   const bool force_generic = env && env[0] == '1';
   // the tensor-core path copies 16-byte chunks of every plane, norms included
-  const bool chunks_ok = cache.capacity % 4 == 0 &&
+  // (a paged tile of 16 tokens must also lie inside one block)
+  const bool chunks_ok = (paged ? paged->block_size % 16 == 0 : cache.capacity % 4 == 0) &&
       ((reinterpret_cast<uintptr_t>(cache.k_norms) | reinterpret_cast<uintptr_t>(cache.v_norms)) & 15u) == 0;
   const bool use_mma = mma_path_ok(d, key_bits, val_bits, Hq / Hkv, q_len) && chunks_ok && !force_generic;
   int rc = launch_rotate(q, q_dtype, p.rows, d, Pi, S, qjl_scale, scale, qk, key_centroids, val_centroids,
@@ -434,6 +458,10 @@ extern "C" int qkv_attention(const void* q, int q_dtype, qkv_cache_t cache,
   a.cache = cache; a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.G = Hq / Hkv; a.q_len = q_len; a.d = d;
   a.causal = causal; a.kv_len = kv_len; a.qk = qk; a.kcent = key_centroids; a.vcent = val_centroids;
   a.part = part; a.n_splits = p.n_splits; a.split_len = p.split_len;
+  if (paged) {
+    a.block_table = paged->block_table; a.seq_lens = paged->seq_lens;
+    a.max_blocks = paged->max_blocks; a.block_size = paged->block_size;
+  }
   if (use_mma) {          // one launch: the last split of every (batch, kv head) merges and un-rotates
     a.tables = tables;
     a.arrivals = reinterpret_cast<unsigned*>(ws + kAttnHeaderBytes);
@@ -447,6 +475,34 @@ extern "C" int qkv_attention(const void* q, int q_dtype, qkv_cache_t cache,
   merge_splits_kernel<<<static_cast<unsigned>((p.rows + kRowsPerCta - 1) / kRowsPerCta), 128, 0, st>>>(
       part, p.rows, p.n_splits, d, Pi, out);
   return check_launch();
+}
+}  // namespace
+
+extern "C" int qkv_attention(const void* q, int q_dtype, qkv_cache_t cache,
+                             int B, int Hq, int Hkv, int q_len, int64_t kv_len, int d,
+                             int key_bits, int val_bits,
+                             const float* Pi, const float* key_centroids, const float* val_centroids,
+                             const float* S, float qjl_scale, float scale, int causal,
+                             float* out, void* workspace, size_t workspace_bytes, void* stream) {
+  return attention_run(q, q_dtype, cache, nullptr, B, Hq, Hkv, q_len, kv_len, d, key_bits, val_bits, Pi,
+                       key_centroids, val_centroids, S, qjl_scale, scale, causal, out, workspace, workspace_bytes,
+                       stream);
+}
+
+extern "C" int qkv_attention_paged(const void* q, int q_dtype, qkv_paged_cache_t pool,
+                                   int B, int Hq, int Hkv, int q_len, int64_t max_kv_len, int d,
+                                   int key_bits, int val_bits,
+                                   const float* Pi, const float* key_centroids, const float* val_centroids,
+                                   const float* S, float qjl_scale, float scale, int causal,
+                                   float* out, void* workspace, size_t workspace_bytes, void* stream) {
+  qkv_cache_t planes{};
+  planes.k_codes = pool.k_codes; planes.k_signs = pool.k_signs; planes.k_norms = pool.k_norms;
+  planes.v_codes = pool.v_codes; planes.v_norms = pool.v_norms;
+  planes.capacity = 0;
+  const PagedInfo info{pool.block_table, pool.seq_lens, pool.max_blocks, pool.block_size};
+  return attention_run(q, q_dtype, planes, &info, B, Hq, Hkv, q_len, max_kv_len, d, key_bits, val_bits, Pi,
+                       key_centroids, val_centroids, S, qjl_scale, scale, causal, out, workspace, workspace_bytes,
+                       stream);
 }
 
 // ---- attention without a caller-provided workspace ------------------------------------------------

@@ -23,6 +23,11 @@ struct AttnArgs {
   const float* Pi;          // tensor-core path: the last split of a head merges and un-rotates
   float* out;
   int n_splits; int64_t split_len;
+  // Paged cache (block_table != nullptr): the planes are a pool of blocks of block_size rows per kv head,
+  // row (block * Hkv + hkv) * block_size + offset; token t of batch entry b lives in block
+  // block_table[b * max_blocks + t / block_size] and the entry has seq_lens[b] tokens (kv_len bounds them).
+  const int32_t* block_table; const int32_t* seq_lens;
+  int max_blocks, block_size;
 };
 
 constexpr size_t kAttnHeaderBytes = 256;   // workspace header: look-up tables of the tensor-core path

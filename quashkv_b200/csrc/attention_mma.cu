@@ -44,6 +44,7 @@ struct MmaPtrs {
   const uint8_t* kcode; const uint8_t* ksign; const uint8_t* vcode; const float* knorm; const float* vnorm;
 };
 
+template <bool PAGED>
 __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(AttnArgs a) {
   constexpr int D = 128;
   __shared__ float q_s[8][2 * D];                    // [query row][q_rot*scale | sign weights]
@@ -62,6 +63,9 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
   // Query rows of a (batch, kv head) are numbered g * q_len + position; a CTA takes eight of them
   // (blockIdx.y), so decode (one tile) and prefill (many) run through the same code.
   const int r0 = 8 * blockIdx.y;
+  // a paged cache has its own token count per batch entry; a.kv_len is then only their upper bound
+  int64_t kv_len = a.kv_len;
+  if (PAGED) kv_len = min(static_cast<int64_t>(max(a.seq_lens[b], 0)), a.kv_len);
   const int nq_all = a.G * a.q_len;
   const int nq = nq_all - r0 < 8 ? nq_all - r0 : 8;
 
@@ -123,10 +127,11 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
     const int r = 2 * tig + e;
-    lim[e] = (r < nq) ? (a.causal ? static_cast<int>(a.kv_len - a.q_len + (r0 + r) % a.q_len) : 0x7fffffff) : -1;
+    lim[e] = (r < nq) ? (a.causal ? static_cast<int>(kv_len - a.q_len + (r0 + r) % a.q_len) : 0x7fffffff) : -1;
   }
 
-  const int64_t seg_row0 = static_cast<int64_t>(seg) * a.cache.capacity;
+  // contiguous cache: first row of this (batch, kv head); paged cache: this head's rows inside block 0
+  const int64_t seg_row0 = PAGED ? static_cast<int64_t>(hkv) * a.block_size : static_cast<int64_t>(seg) * a.cache.capacity;
   MmaPtrs p;
   p.kcode = a.cache.k_codes + seg_row0 * 32;
   p.ksign = a.cache.k_signs + seg_row0 * 16;
@@ -136,11 +141,11 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
 
   const int64_t t_begin = split * a.split_len;
   int64_t t_end = t_begin + a.split_len;
-  if (t_end > a.kv_len) t_end = a.kv_len;
+  if (t_end > kv_len) t_end = kv_len;
   if (a.causal) {                      // tokens past the last position any row of this tile may see are skipped
     int last = 0;
     for (int r = 0; r < nq; ++r) last = max(last, (r0 + r) % a.q_len);
-    const int64_t visible = a.kv_len - a.q_len + last + 1;
+    const int64_t visible = kv_len - a.q_len + last + 1;
     if (t_end > visible) t_end = visible;
   }
   const int n_valid = static_cast<int>(t_end - t_begin);        // tokens of this split
@@ -165,41 +170,59 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
   const int first_rel = warp * kTile;
   const int n_it = first_rel < n_valid ? (n_valid - first_rel + kStep - 1) / kStep : 0;
   unsigned char* ring = pool + warp * (kStages * kStageBytes);
-  const unsigned char* src0[4];      // chunk source at tile 0
+  // Chunk sources: src0 is the chunk's address in tile 0 (paged: in the first tile of block 0) and stride the
+  // bytes between this warp's consecutive tiles (paged: the bytes of one row, a tile's first row being looked
+  // up in the block table).
+  const unsigned char* src0[4];
   int dst_off[4], tok_off[4], stride[4];
+  const int64_t t_src = PAGED ? 0 : t_first;
+  constexpr int kRowStep = PAGED ? 1 : kStep;
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const int c = lane + 32 * k;
     if (c < 32) {            // key codes: two chunks per token row
-      tok_off[k] = c >> 1; stride[k] = kStep * 32; dst_off[k] = c * 16;
-      src0[k] = p.kcode + (t_first + (c >> 1)) * 32 + (c & 1) * 16;
+      tok_off[k] = c >> 1; stride[k] = kRowStep * 32; dst_off[k] = c * 16;
+      src0[k] = p.kcode + (t_src + (c >> 1)) * 32 + (c & 1) * 16;
     } else if (c < 48) {     // sign bits: one chunk per token
       const int r = c - 32;
-      tok_off[k] = r; stride[k] = kStep * 16; dst_off[k] = kOffKs + r * 16;
-      src0[k] = p.ksign + (t_first + r) * 16;
+      tok_off[k] = r; stride[k] = kRowStep * 16; dst_off[k] = kOffKs + r * 16;
+      src0[k] = p.ksign + (t_src + r) * 16;
     } else if (c < 96) {     // value codes: three chunks per token
       const int i = c - 48;
-      tok_off[k] = i / 3; stride[k] = kStep * 48; dst_off[k] = kOffV + i * 16;
-      src0[k] = p.vcode + (t_first + i / 3) * 48 + (i % 3) * 16;
+      tok_off[k] = i / 3; stride[k] = kRowStep * 48; dst_off[k] = kOffV + i * 16;
+      src0[k] = p.vcode + (t_src + i / 3) * 48 + (i % 3) * 16;
     } else {                 // norms: four tokens per chunk (c < 104 holds data)
       const int j = (c - 96) & 3, which = (c - 96) >> 2;
-      tok_off[k] = 4 * j; stride[k] = kStep * 4;
+      tok_off[k] = 4 * j; stride[k] = kRowStep * 4;
       dst_off[k] = (which ? kOffVn : kOffKn) + j * 16;
-      src0[k] = reinterpret_cast<const unsigned char*>((which ? p.vnorm : p.knorm) + t_first + 4 * j);
+      src0[k] = reinterpret_cast<const unsigned char*>((which ? p.vnorm : p.knorm) + t_src + 4 * j);
     }
   }
-  auto issue = [&](int it) {
+  // paged: the block of the tile that the next issue() copies, read one call ahead of its use
+  const int32_t* bt = PAGED ? a.block_table + static_cast<int64_t>(b) * a.max_blocks : nullptr;
+  auto block_of = [&](int it) -> int {
+    const unsigned t = static_cast<unsigned>(t_first) + static_cast<unsigned>(it) * kStep;   // kv_len < 2^31
+    return it < n_it ? __ldg(bt + t / static_cast<unsigned>(a.block_size)) : 0;
+  };
+  int blk_next = PAGED ? block_of(0) : 0;
+  auto issue = [&](int it) {                                // called with it = 0, 1, 2, ... in order
     if (it < n_it) {
       const int rel = first_rel + it * kStep;
       unsigned char* stage = ring + (it % kStages) * kStageBytes;
+      int64_t step = it;                                    // multiplies stride[k]
+      if (PAGED) {                                          // first row of the tile inside the pool, less this head's offset
+        const unsigned t = static_cast<unsigned>(t_first) + static_cast<unsigned>(it) * kStep;
+        step = static_cast<int64_t>(blk_next) * a.Hkv * a.block_size + t % static_cast<unsigned>(a.block_size);
+      }
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         if (k < 3 || lane < 8) {
           const bool ok = rel + tok_off[k] < n_valid;      // rows past the split are zero-filled, not read
-          cp_async16(stage + dst_off[k], ok ? src0[k] + static_cast<int64_t>(it) * stride[k] : src0[k], ok ? 16 : 0);
+          cp_async16(stage + dst_off[k], ok ? src0[k] + step * stride[k] : src0[k], ok ? 16 : 0);
         }
       }
     }
+    if (PAGED) blk_next = block_of(it + 1);
     cp_async_commit();                                      // one group per tile slot, even when empty
   };
   auto fetch = [&](TileRegs& T, int it) {                  // this lane's fragment slice of a staged tile
@@ -461,7 +484,10 @@ bool mma_path_ok(int d, int key_bits, int val_bits, int group, int q_len) {
 
 int launch_attend_mma(const AttnArgs& a, cudaStream_t st) {
   const dim3 grid(a.n_splits, (a.G * a.q_len + 7) / 8, a.B * a.Hkv);
-  attend_decode_mma_kernel<<<grid, kMmaWarps * 32, 0, st>>>(a);
+  if (a.block_table)
+    attend_decode_mma_kernel<true><<<grid, kMmaWarps * 32, 0, st>>>(a);
+  else
+    attend_decode_mma_kernel<false><<<grid, kMmaWarps * 32, 0, st>>>(a);
   return check_launch();
 }
 

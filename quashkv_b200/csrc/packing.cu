@@ -35,6 +35,19 @@ __global__ void unpack_kernel(const uint8_t* __restrict__ packed, uint8_t* __res
   }
 }
 
+// Row i of `src` goes to row slots[i] of `dst`, rows of `words` 32-bit words; a negative slot drops the row.
+__global__ void scatter_rows_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst,
+                                    const int64_t* __restrict__ slots, int64_t n_rows, int words) {
+  const int64_t total = n_rows * words;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / words;
+    const int w = static_cast<int>(i - r * words);
+    const int64_t slot = __ldg(slots + r);
+    if (slot >= 0) dst[slot * words + w] = src[i];
+  }
+}
+
 static int grid_for(int64_t total) {
   const int64_t blocks = (total + 255) / 256;
   const int64_t cap = static_cast<int64_t>(kNumSMs) * 16;
@@ -81,5 +94,17 @@ extern "C" int qkv_unpack(const uint8_t* packed, uint8_t* codes, int64_t n_rows,
   const int row_bytes = packed_row_bytes(d, bits);
   unpack_kernel<<<grid_for(n_rows * d), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       packed, codes, n_rows, d, bits, row_bytes);
+  return check_launch();
+}
+
+extern "C" int qkv_scatter_rows(const void* src, void* dst, const int64_t* slots, int64_t n_rows, int row_bytes,
+                                void* stream) {
+  if (n_rows < 0 || row_bytes < 4 || (row_bytes & 3)) return QKV_EDIM;
+  if (n_rows == 0) return QKV_OK;
+  if (!src || !dst || !slots) return QKV_ENULL;
+  if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 3u) return QKV_EALIGN;
+  const int words = row_bytes / 4;
+  scatter_rows_kernel<<<grid_for(n_rows * words), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), slots, n_rows, words);
   return check_launch();
 }

@@ -271,6 +271,50 @@ def _(q, k_codes, k_signs, k_norms, v_codes, v_norms, kv_len, n_kv_heads, key_bi
     return q.new_empty(q.shape, dtype=torch.float32)
 
 
+@torch.library.custom_op("quashkv_b200::attention_paged", mutates_args=(), device_types="cuda")
+def _attention_paged(q: torch.Tensor, k_codes: torch.Tensor, k_signs: torch.Tensor, k_norms: torch.Tensor,
+                     v_codes: torch.Tensor, v_norms: torch.Tensor, block_table: torch.Tensor,
+                     seq_lens: torch.Tensor, max_kv_len: int, key_bits: int, val_bits: int, Pi: torch.Tensor,
+                     key_centroids: torch.Tensor, val_centroids: torch.Tensor, S: torch.Tensor,
+                     qjl_scale: float, scale: float, causal: bool) -> torch.Tensor:
+    """q (B,Hq,Q,d); pool planes [blocks, Hkv, block_size, bytes] packed; block_table (B, max_blocks) int32;
+    seq_lens (B) int32; max_kv_len an upper bound of seq_lens known on the host.  Returns (B,Hq,Q,d) fp32."""
+    B, Hq, Q, d = q.shape
+    if q.dtype not in _DT:
+        q = q.float()
+    qc = q.detach().contiguous()
+    n_kv_heads, block_size = k_norms.shape[1], k_norms.shape[2]
+    out = torch.empty((B, Hq, Q, d), dtype=torch.float32, device=q.device)
+    L = _lib.lib()
+    ws_bytes = L.qkv_attention_workspace_bytes(B, Hq, n_kv_heads, Q, max_kv_len, d)
+    ws = torch.empty((max(ws_bytes, 16),), dtype=torch.uint8, device=q.device)
+    pool = _lib.PagedCache(k_codes.data_ptr(), k_signs.data_ptr(), k_norms.data_ptr(), v_codes.data_ptr(),
+                           v_norms.data_ptr(), block_table.data_ptr(), seq_lens.data_ptr(),
+                           block_table.shape[1], block_size)
+    with torch.cuda.device(q.device):
+        _lib.check(L.qkv_attention_paged(
+            _p(qc), _DT[qc.dtype], pool, B, Hq, n_kv_heads, Q, max_kv_len, d, key_bits, val_bits,
+            _p(_f32(Pi)), _p(_f32(key_centroids)), _p(_f32(val_centroids)), _p(_f32(S)),
+            float(qjl_scale), float(scale), int(causal), _p(out), _p(ws), ws_bytes, _stream(q)), "attention_paged")
+    return out
+
+
+@_attention_paged.register_fake
+def _(q, k_codes, k_signs, k_norms, v_codes, v_norms, block_table, seq_lens, max_kv_len, key_bits, val_bits, Pi,
+      key_centroids, val_centroids, S, qjl_scale, scale, causal):
+    return q.new_empty(q.shape, dtype=torch.float32)
+
+
+@torch.library.custom_op("quashkv_b200::scatter_rows", mutates_args=("dst",), device_types="cuda")
+def _scatter_rows(src: torch.Tensor, dst: torch.Tensor, slots: torch.Tensor) -> None:
+    """Row i of src (n, ...) goes to row slots[i] of dst (rows, ...); rows are whole trailing slices."""
+    n = slots.numel()
+    row_bytes = (src.numel() // max(n, 1)) * src.element_size()
+    with torch.cuda.device(src.device):
+        _lib.check(_lib.lib().qkv_scatter_rows(_p(src), _p(dst), _p(slots), n, row_bytes, _stream(src)),
+                   "scatter_rows")
+
+
 @torch.library.custom_op("quashkv_b200::index_scan_topk", mutates_args=(), device_types="cuda")
 def _index_scan_topk(queries: torch.Tensor, db_codes: torch.Tensor, db_signs: torch.Tensor,
                      db_norms: torch.Tensor, n_vectors: int, bits: int, Pi: torch.Tensor,
@@ -411,6 +455,8 @@ def decompress_mixed(codes, norms, Pi, is_outlier, cents_out, bits_out, cents_re
 append_kv = _append_kv
 compress_ip_into = _compress_ip_into
 attention = _attention
+attention_paged = _attention_paged
+scatter_rows = _scatter_rows
 index_scan_topk = _index_scan_topk
 index_scores = _index_scores
 topk_merge = _topk_merge

@@ -786,3 +786,112 @@ def test_c_abi_direct_call_and_status_codes(golden):
     assert L.qkv_index_scan_topk(vp(x), 2, 64, vp(codes), vp(codes), vp(norms), 10, 3, vp(Pi), vp(bnd), vp(bnd), 0.1,
                                  200, 0, vp(x), vp(x), vp(x), 1 << 20, stream) == -8   # k above the limit
     torch.cuda.synchronize()
+
+
+# ---------------------------------------------------------------------------------------------
+# paged (block-table) cache
+# ---------------------------------------------------------------------------------------------
+def _paged_case(D, kbits, vbits, block_size, lens, Hkv=2, seed=7):
+    """Fills a page pool by interleaved appends of unequal chunks (so that pages of different sequences
+    interleave and one sequence's freed pages are reused) and returns the pool with every sequence's K/V."""
+    from quashkv_b200.integrations.vllm_backend import QuashKVPageConfig, QuashKVPagedCache
+    g = torch.Generator().manual_seed(seed)
+    cfg = QuashKVPageConfig(key_bits=kbits, value_bits=vbits, block_size=block_size)
+    pool = QuashKVPagedCache(4 + sum(-(-n // block_size) for n in lens), Hkv, D, cfg, device=DEV)
+    pool.append(["gone"], torch.randn(1, Hkv, 3 * block_size, D, generator=g).to(DEV),
+                torch.randn(1, Hkv, 3 * block_size, D, generator=g).to(DEV))
+    K = [torch.randn(1, Hkv, n, D, generator=g) for n in lens]
+    V = [torch.randn(1, Hkv, n, D, generator=g) for n in lens]
+    done = [0] * len(lens)
+    chunk = [23, 1, 40, 5, 64, 2]
+    step = 0
+    while any(d < n for d, n in zip(done, lens)):
+        for i, n in enumerate(lens):
+            c = min(chunk[(step + i) % len(chunk)], n - done[i])
+            if c > 0:
+                pool.append([i], K[i][:, :, done[i]:done[i] + c].to(DEV), V[i][:, :, done[i]:done[i] + c].to(DEV))
+                done[i] += c
+        if step == 1:
+            pool.free("gone")          # its pages go back to the pool and are handed out again
+        step += 1
+    return pool, K, V
+
+
+@pytest.mark.parametrize("D,kbits,vbits,block_size,q_len,causal,generic", [
+    (128, 3, 3, 16, 1, False, False),      # tensor-core kernel, one page per tile
+    (128, 3, 3, 32, 3, True, False),       # tensor-core kernel, two tiles per page, causal rows
+    (128, 3, 3, 16, 1, False, True),       # generic kernel on the same pool
+    (128, 3, 3, 8, 2, True, False),        # pages smaller than a tile: generic kernel
+    (64, 4, 2, 16, 1, False, False),       # other widths and head size: generic kernel
+])
+def test_paged_cache_matches_contiguous_engine_and_oracle(D, kbits, vbits, block_size, q_len, causal, generic,
+                                                          monkeypatch):
+    if generic:
+        monkeypatch.setenv("QUASHKV_B200_GENERIC_ATTENTION", "1")
+    lens = [700, 37, 130, 16, 3]
+    Hkv, G = 2, 4
+    pool, K, V = _paged_case(D, kbits, vbits, block_size, lens, Hkv)
+    ids = list(range(len(lens))) + ["never appended"]
+    Q = torch.randn(len(ids), Hkv * G, q_len, D, generator=torch.Generator().manual_seed(5))
+    out = pool.attention(ids, Q.to(DEV), causal=causal)
+    assert out.shape == Q.shape
+    assert torch.count_nonzero(out[-1]) == 0                     # a sequence without tokens gives zeros
+    table, seq_lens, longest = pool.block_table(ids)
+    assert longest == max(lens) and seq_lens.tolist() == lens + [0]
+    kq, vq = pool.engine.key_quantizer, pool.engine.value_quantizer
+    Pi, Sg = kq.mse_quantizer.Pi.cpu(), kq.S.cpu()
+    kc, kb = kq.mse_quantizer.codebook.centroids.cpu(), kq.mse_quantizer.codebook.boundaries.cpu()
+    vc, vb = vq.codebook.centroids.cpu(), vq.codebook.boundaries.cpu()
+    worst_eng = worst_orc = 0.0
+    for i, n in enumerate(lens):
+        # the same tokens through the contiguous engine: identical packed rows, attention equal up to the split plan
+        eng = qk.QuashKVEngine(D, kbits, vbits, seed=42, pack_storage=True)
+        eng.append(K[i].to(DEV), V[i].to(DEV))
+        rows = (table[i, torch.arange(n, device=DEV) // block_size].long()[None, :] * Hkv
+                + torch.arange(Hkv, device=DEV)[:, None]) * block_size + torch.arange(n, device=DEV)[None, :] % block_size
+        for name, plane in pool.planes.items():
+            flat = plane.reshape(plane.shape[0] * Hkv * block_size, -1)
+            assert torch.equal(flat[rows.reshape(-1)].reshape(Hkv, n, -1),
+                               eng._planes[name][:, :n].reshape(Hkv, n, -1)), f"pool rows of {name}, sequence {i}"
+        if causal and q_len > n:
+            continue                   # fewer tokens than query rows: the contiguous entry point refuses that
+        want_eng = eng.attention(Q[i:i + 1].to(DEV), causal=causal)
+        worst_eng = max(worst_eng, rel_l2(out[i:i + 1], want_eng))
+        mse, sg, kn = orc.compress_ip(K[i], Pi, kb, kc, Sg)
+        vi, vn = orc.compress_mse(V[i], Pi, vb)
+        planes = (mse, sg, kn, vi, vn, Pi, kc, vc, Sg, kq.qjl_scale)
+        want = torch.empty(1, Hkv * G, q_len, D)
+        for g in range(G):             # query head h reads KV head h // G; causal rows keep their own positions
+            want[:, g::G] = orc.attention(Q[i:i + 1, g::G], *planes, causal=causal, total_tokens=n)
+        worst_orc = max(worst_orc, rel_l2(out[i:i + 1], want))
+    print(f"[parity] paged d={D} block={block_size} q_len={q_len} causal={causal}: vs contiguous engine "
+          f"{worst_eng:.3e}, vs oracle {worst_orc:.3e}")
+    # same kernel on both sides (tensor-core or generic): equal up to the split plan; a pool whose pages are
+    # smaller than a tile runs the generic fp32 kernel against the engine's fp16 tensor-core operands
+    same_kernel = not (D == 128 and (kbits, vbits) == (3, 3) and block_size % 16 != 0)
+    assert worst_eng < (1e-5 if same_kernel else FP32_TOL) and worst_orc < FP32_TOL
+    assert _lib.lib().qkv_tensor_core_timeouts() == 0
+
+
+def test_paged_decode_steps_and_pool_exhaustion():
+    """Batched one-token appends (the decode loop) land in the right pages; running out of pages raises."""
+    from quashkv_b200.integrations.vllm_backend import QuashKVPageConfig, QuashKVPagedCache
+    D, Hkv = 128, 2
+    pool = QuashKVPagedCache(6, Hkv, D, QuashKVPageConfig(), device=DEV)
+    g = torch.Generator().manual_seed(3)
+    K = torch.randn(2, Hkv, 40, D, generator=g)
+    V = torch.randn(2, Hkv, 40, D, generator=g)
+    pool.append(["a", "b"], K[:, :, :14].to(DEV), V[:, :, :14].to(DEV))
+    for s in range(14, 40):
+        pool.append(["a", "b"], K[:, :, s:s + 1].to(DEV), V[:, :, s:s + 1].to(DEV))
+    assert pool.seq_len("a") == 40 and pool.free_blocks == 0 and len(pool.blocks_of("b")) == 3
+    Q = torch.randn(2, Hkv * 4, 1, D, generator=g)
+    out = pool.attention(["a", "b"], Q.to(DEV))
+    eng = qk.QuashKVEngine(D, 3, 3, seed=42, pack_storage=True)
+    eng.append(K.to(DEV), V.to(DEV))
+    assert rel_l2(out, eng.attention(Q.to(DEV))) < 1e-5
+    with pytest.raises(RuntimeError, match="pool exhausted"):
+        pool.append(["a"], K[:1, :, :9].to(DEV), V[:1, :, :9].to(DEV))
+    pool.free("b")
+    pool.append(["a"], K[:1, :, :9].to(DEV), V[:1, :, :9].to(DEV))
+    assert pool.seq_len("a") == 49 and pool.free_blocks == 2

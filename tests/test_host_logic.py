@@ -129,3 +129,40 @@ def test_argument_validation_needs_no_gpu():
     assert L.qkv_attention_workspace_bytes(32, 32, 8, 1, 32768, 128) > 0
     assert L.qkv_index_workspace_bytes(1000, 4, 64, 10) > 0
     assert L.qkv_mixed_row_bytes(128, 32, 3, 2) == 36
+
+
+def test_page_pool_bookkeeping_without_gpu():
+    """Page allocation, block tables and the reference-shaped page manager need no GPU; the data path
+    refuses CPU tensors."""
+    from quashkv_b200.integrations.vllm_backend import (QuashKVModelManager, QuashKVPageConfig, QuashKVPagedCache,
+                                                        QuashKVPageManager, register_quashkv_backend)
+    cfg = QuashKVPageConfig()
+    assert (cfg.key_bits, cfg.value_bits, cfg.block_size, cfg.seed) == (3, 3, 16, 42)   # reference defaults
+    pool = QuashKVPagedCache(5, 2, 64, cfg, device="cpu")
+    assert pool.planes["k_codes"].shape == (5, 2, 16, 16) and pool.planes["v_norms"].shape == (5, 2, 16)
+    pool._grow("a", 17)
+    pool._lens["a"] = 17
+    pool._grow("b", 1)
+    pool._lens["b"] = 1
+    pool._grow("a", 15)                      # 32 tokens still fit two pages
+    pool._lens["a"] = 32
+    assert pool.blocks_of("a") == [0, 1] and pool.blocks_of("b") == [2] and pool.free_blocks == 2
+    table, lens, longest = pool.block_table(["b", "a", "unknown"])
+    assert table.dtype == torch.int32 and table.tolist() == [[2, 0], [0, 1], [0, 0]]
+    assert lens.tolist() == [1, 32, 0] and longest == 32
+    with pytest.raises(RuntimeError, match="pool exhausted"):
+        pool._grow("b", 16 * 3)
+    pool.free("a")
+    assert pool.free_blocks == 4 and pool.seq_len("a") == 0
+    pool._grow("c", 1)
+    assert pool.blocks_of("c") == [0]        # freed pages are handed out again, lowest first
+    with pytest.raises(RuntimeError, match="no CPU implementation"):
+        pool.append(["d"], torch.randn(1, 2, 3, 64), torch.randn(1, 2, 3, 64))
+
+    mgr = QuashKVPageManager(2, 64, cfg, torch.device("cpu"), layer_idx=3)
+    with pytest.raises(ValueError, match="No compressed KV blocks stored yet"):
+        mgr.attention(torch.randn(1, 2, 1, 64))
+    model = QuashKVModelManager(3, 2, 64, device="cpu")
+    assert model.stats()["tokens_per_layer"] == [0, 0, 0] and model.stats()["config"]["block_size"] == 16
+    with pytest.raises((ImportError, NotImplementedError)):
+        register_quashkv_backend()
