@@ -89,6 +89,45 @@ class QuashIndex:
         self._n_vectors = need
         self._unpacked = None
 
+    # ---- persistence ----------------------------------------------------------------------------
+    # The reference keeps the index in memory only and rebuilds its tensors on every add
+    # (nn_search/index.py:100-104); here the three packed planes are the native form, so they are also the
+    # file form: one torch archive with the planes cut to n_vectors rows and the constructor arguments.
+    FILE_FORMAT = 1
+
+    def save(self, path) -> None:
+        """Write the packed planes and the constructor arguments; the rotation, codebook and sign vector are
+        regenerated from (dim, bits, seed) on load, as the constructor does."""
+        if self._n_vectors:
+            codes, signs, norms = (t.cpu() for t in self._views())
+        else:
+            codes = signs = norms = None
+        torch.save({"format": self.FILE_FORMAT, "dim": self.dim, "bits": self.bits, "seed": self.seed,
+                    "pack_storage": self.pack_storage, "n_vectors": self._n_vectors,
+                    "codes": codes, "signs": signs, "norms": norms}, path)
+
+    @classmethod
+    def load(cls, path, device="cuda") -> "QuashIndex":
+        """Rebuild an index from ``save``'s file on ``device``; more vectors can be added afterwards."""
+        blob = torch.load(path, map_location="cpu", weights_only=True)
+        if not isinstance(blob, dict) or blob.get("format") != cls.FILE_FORMAT:
+            raise ValueError(f"{path}: not a QuashIndex file of format {cls.FILE_FORMAT}")
+        index = cls(blob["dim"], blob["bits"], blob["seed"], device=device, pack_storage=blob["pack_storage"])
+        n = blob["n_vectors"]
+        if n:
+            pk = ops.packed_row_bytes(index.dim, index.bits - 1)
+            ps = ops.packed_row_bytes(index.dim, 1)
+            if (tuple(blob["codes"].shape) != (n, pk) or tuple(blob["signs"].shape) != (n, ps)
+                    or tuple(blob["norms"].shape) != (n,)):
+                raise ValueError(f"{path}: plane shapes do not match {n} vectors of dim {index.dim} at "
+                                 f"{index.bits} bits")
+            index._reserve(n, index.device)
+            index._codes[:n] = blob["codes"].to(index.device)
+            index._signs[:n] = blob["signs"].to(index.device)
+            index._norm_plane[:n] = blob["norms"].to(index.device)
+            index._n_vectors = n
+        return index
+
     # ---- search ---------------------------------------------------------------------------------
     def search(self, queries: torch.Tensor, k: int = 10, id_base: int = 0):
         """(M, dim) queries -> (scores (M,k) descending, indices (M,k) int64)."""

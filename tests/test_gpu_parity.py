@@ -895,3 +895,34 @@ def test_paged_decode_steps_and_pool_exhaustion():
     pool.free("b")
     pool.append(["a"], K[:1, :, :9].to(DEV), V[:1, :, :9].to(DEV))
     assert pool.seq_len("a") == 49 and pool.free_blocks == 2
+
+
+def test_index_save_load_and_incremental_add(tmp_path):
+    """An index written to a file and read back searches identically, keeps growing, and a build by many small
+    adds equals a build by one add (rows are compressed in place at their offsets)."""
+    g = torch.Generator().manual_seed(21)
+    db = torch.randn(5000, 128, generator=g)
+    qs = torch.randn(33, 128, generator=g).to(DEV)
+    one = qk.QuashIndex(128, 3, seed=42, pack_storage=True)
+    one.add(db.to(DEV))
+    many = qk.QuashIndex(128, 3, seed=42, pack_storage=True)
+    for lo, hi in ((0, 1), (1, 64), (64, 65), (65, 3000), (3000, 5000)):
+        many.add(db[lo:hi].to(DEV))
+    for a, b in zip(one._views(), many._views()):
+        assert torch.equal(a, b)
+    path = tmp_path / "index.pt"
+    many.save(path)
+    back = qk.QuashIndex.load(path, device=DEV)
+    assert len(back) == 5000 and back.bits == 3 and back.pack_storage
+    s0, i0 = one.search(qs, 10)
+    s1, i1 = back.search(qs, 10)
+    assert torch.equal(i0, i1) and torch.equal(s0, s1)
+    extra = torch.randn(700, 128, generator=g)
+    back.add(extra.to(DEV))
+    one.add(extra.to(DEV))
+    s0, i0 = one.search(qs, 10)
+    s1, i1 = back.search(qs, 10)
+    assert len(back) == 5700 and torch.equal(i0, i1) and torch.equal(s0, s1)
+    empty = qk.QuashIndex(64, 4, seed=7)
+    empty.save(tmp_path / "empty.pt")
+    assert len(qk.QuashIndex.load(tmp_path / "empty.pt", device=DEV)) == 0

@@ -166,3 +166,18 @@ def test_page_pool_bookkeeping_without_gpu():
     assert model.stats()["tokens_per_layer"] == [0, 0, 0] and model.stats()["config"]["block_size"] == 16
     with pytest.raises((ImportError, NotImplementedError)):
         register_quashkv_backend()
+
+
+def test_index_file_checks_without_gpu(tmp_path):
+    """An empty index round-trips on CPU; foreign or inconsistent files are refused."""
+    qk.QuashIndex(64, 4, seed=7).save(tmp_path / "empty.pt")
+    back = qk.QuashIndex.load(tmp_path / "empty.pt", device="cpu")
+    assert (back.dim, back.bits, back.seed, len(back)) == (64, 4, 7, 0)
+    torch.save({"something": 1}, tmp_path / "foreign.pt")
+    with pytest.raises(ValueError, match="not a QuashIndex file"):
+        qk.QuashIndex.load(tmp_path / "foreign.pt", device="cpu")
+    torch.save({"format": 1, "dim": 64, "bits": 3, "seed": 1, "pack_storage": True, "n_vectors": 4,
+                "codes": torch.zeros(4, 3, dtype=torch.uint8), "signs": torch.zeros(4, 8, dtype=torch.uint8),
+                "norms": torch.zeros(4)}, tmp_path / "bad.pt")
+    with pytest.raises(ValueError, match="plane shapes do not match"):
+        qk.QuashIndex.load(tmp_path / "bad.pt", device="cpu")
