@@ -305,13 +305,19 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
       if (!(tokB < n_valid && tokB <= lim_rel[0])) sc[2] = -INFINITY;
       if (!(tokB < n_valid && tokB <= lim_rel[1])) sc[3] = -INFINITY;
     }
+    // m is a reference exponent, not the exact running maximum: it is raised (to the exact maximum of the tile,
+    // over the eight token lanes of a query column) only when a score of this tile exceeds it by more than
+    // kSlack, so that most tiles need one vote instead of three shuffle rounds.  Weights stay below 2^kSlack,
+    // far inside fp16 once multiplied by a value norm, and the merge of the splits only needs l and the
+    // accumulators to be relative to the m that is written out.
+    constexpr float kSlack = 4.f;
     float mx[2] = {fmaxf(sc[0], sc[2]), fmaxf(sc[1], sc[3])};
+    if (__any_sync(QKV_FULL_MASK, mx[0] > m[0] + kSlack || mx[1] > m[1] + kSlack)) {
 #pragma unroll
-    for (int o = 4; o < 32; o <<= 1) {
-      mx[0] = fmaxf(mx[0], __shfl_xor_sync(QKV_FULL_MASK, mx[0], o));
-      mx[1] = fmaxf(mx[1], __shfl_xor_sync(QKV_FULL_MASK, mx[1], o));
-    }
-    if (__any_sync(QKV_FULL_MASK, mx[0] > m[0] || mx[1] > m[1])) {
+      for (int o = 4; o < 32; o <<= 1) {
+        mx[0] = fmaxf(mx[0], __shfl_xor_sync(QKV_FULL_MASK, mx[0], o));
+        mx[1] = fmaxf(mx[1], __shfl_xor_sync(QKV_FULL_MASK, mx[1], o));
+      }
       float al[2];
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
