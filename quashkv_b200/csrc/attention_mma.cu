@@ -69,7 +69,21 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
   const int nq_all = a.G * a.q_len;
   const int nq = nq_all - r0 < 8 ? nq_all - r0 : 8;
 
-  for (int idx = threadIdx.x; idx < 8 * 2 * D; idx += blockDim.x) {
+  const int64_t t_begin = split * a.split_len;
+  int64_t t_end = t_begin + a.split_len;
+  if (t_end > kv_len) t_end = kv_len;
+  if (a.causal) {                      // tokens past the last position any row of this tile may see are skipped
+    int last = 0;
+    for (int r = 0; r < nq; ++r) last = max(last, (r0 + r) % a.q_len);
+    const int64_t visible = kv_len - a.q_len + last + 1;
+    if (t_end > visible) t_end = visible;
+  }
+  const int n_valid = static_cast<int>(t_end - t_begin);        // tokens of this split
+  // A split without tokens (past the end of a short sequence of a paged batch, or above the diagonal of a
+  // causal prefill) skips the operand set-up and goes straight to its neutral partial result.
+  const bool has_work = n_valid > 0;
+
+  for (int idx = threadIdx.x; has_work && idx < 8 * 2 * D; idx += blockDim.x) {
     const int r = idx / (2 * D), e = idx % (2 * D);
     float v = 0.f;
     if (r < nq) {
@@ -80,7 +94,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
     q_s[r][e] = v;
   }
   __syncthreads();
-  if (threadIdx.x < 8) {
+  if (has_work && threadIdx.x < 8) {
     float t = 0.f;
     for (int j = 0; j < D; ++j) t += q_s[threadIdx.x][D + j];
     wsum[threadIdx.x] = t * kLog2e;
@@ -92,7 +106,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
   // base = 32 tig + 16 word, o = 8*(grp&1) + (grp>>1): the order in which the PRMT decode below
   // produces them.  Sign k-step s covers 32 tig + {2s, 2s+16 | 2s+1, 2s+17}.
   const float inv_sk = __uint_as_float(a.tables[6]), inv_sv = __uint_as_float(a.tables[7]);
-  {                                 // the operands depend on the lane only: each warp builds two k-steps
+  if (has_work) {                   // the operands depend on the lane only: each warp builds two k-steps
     const float qf = kLog2e * inv_sk;
     const float* q = q_s[gid];
     const float* w = q_s[gid] + D;
@@ -139,16 +153,6 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
   p.knorm = a.cache.k_norms + seg_row0;
   p.vnorm = a.cache.v_norms + seg_row0;
 
-  const int64_t t_begin = split * a.split_len;
-  int64_t t_end = t_begin + a.split_len;
-  if (t_end > kv_len) t_end = kv_len;
-  if (a.causal) {                      // tokens past the last position any row of this tile may see are skipped
-    int last = 0;
-    for (int r = 0; r < nq; ++r) last = max(last, (r0 + r) % a.q_len);
-    const int64_t visible = kv_len - a.q_len + last + 1;
-    if (t_end > visible) t_end = visible;
-  }
-  const int n_valid = static_cast<int>(t_end - t_begin);        // tokens of this split
   // positions relative to the split start, as 32-bit values
   int lim_rel[2];
 #pragma unroll
