@@ -148,8 +148,13 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attend_split_kernel(AttnArgs 
   }
   __syncthreads();
 
-  const int64_t t_begin = split * a.split_len;
-  int64_t t_end = t_begin + a.split_len;
+  int64_t split_len = a.split_len;
+  if (paged) {                         // a paged batch entry divides its own length over the splits
+    const int64_t per = ((kv_len + a.n_splits - 1) / a.n_splits + 127) / 128 * 128;
+    split_len = per < 128 ? 128 : per;
+  }
+  const int64_t t_begin = split * split_len;
+  int64_t t_end = t_begin + split_len;
   if (t_end > kv_len) t_end = kv_len;
 
   const int words_k = (d >> 5) * WK, words_v = (d >> 5) * WV, words_s = d >> 5;

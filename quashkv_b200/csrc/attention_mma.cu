@@ -69,8 +69,15 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
   const int nq_all = a.G * a.q_len;
   const int nq = nq_all - r0 < 8 ? nq_all - r0 : 8;
 
-  const int64_t t_begin = split * a.split_len;
-  int64_t t_end = t_begin + a.split_len;
+  // A paged batch entry divides its own length over the splits (whole 128-token chunks), so that a short
+  // sequence keeps every one of its CTAs busy for a short time instead of a few for a long time.
+  int64_t split_len = a.split_len;
+  if (PAGED) {
+    const int64_t per = ((kv_len + a.n_splits - 1) / a.n_splits + 127) / 128 * 128;
+    split_len = per < 128 ? 128 : per;
+  }
+  const int64_t t_begin = split * split_len;
+  int64_t t_end = t_begin + split_len;
   if (t_end > kv_len) t_end = kv_len;
   if (a.causal) {                      // tokens past the last position any row of this tile may see are skipped
     int last = 0;
