@@ -171,7 +171,10 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
   float O[8][4];
 #pragma unroll
   for (int i = 0; i < 8; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f;
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  // reference exponents start at a finite "nothing seen yet" value (any finite score raises them at once), so that
+  // the token loop needs no test for minus infinity; the value written out below turns it back into -inf
+  constexpr float kNone = -1e30f;
+  float m[2] = {kNone, kNone}, l[2] = {0.f, 0.f};
   const int odd16 = (gid & 1) * 16;
   const float ci0 = -wsum[2 * tig], ci1 = -wsum[2 * tig + 1];   // accumulator start: -sum of sign weights
 
@@ -225,11 +228,17 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
         const unsigned t = static_cast<unsigned>(t_first) + static_cast<unsigned>(it) * kStep;
         step = static_cast<int64_t>(blk_next) * a.Hkv * a.block_size + t % static_cast<unsigned>(a.block_size);
       }
+      if (rel + kTile <= n_valid) {                         // warp-uniform: the whole tile lies inside the split
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        if (k < 3 || lane < 8) {
-          const bool ok = rel + tok_off[k] < n_valid;      // rows past the split are zero-filled, not read
-          cp_async16(stage + dst_off[k], ok ? src0[k] + step * stride[k] : src0[k], ok ? 16 : 0);
+        for (int k = 0; k < 4; ++k)
+          if (k < 3 || lane < 8) cp_async16(stage + dst_off[k], src0[k] + step * stride[k], 16);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (k < 3 || lane < 8) {
+            const bool ok = rel + tok_off[k] < n_valid;    // rows past the split are zero-filled, not read
+            cp_async16(stage + dst_off[k], ok ? src0[k] + step * stride[k] : src0[k], ok ? 16 : 0);
+          }
         }
       }
     }
@@ -332,7 +341,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
       float al[2];
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        al[e] = (mx[e] > m[e]) ? ex2(m[e] - mx[e]) : 1.f;     // ex2(-inf) = 0 on the first tile
+        al[e] = (mx[e] > m[e]) ? ex2(m[e] - mx[e]) : 1.f;     // ex2(kNone - x) = 0 on the first tile
         m[e] = fmaxf(m[e], mx[e]);
         l[e] *= al[e];
       }
@@ -341,9 +350,8 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
         O[i][0] *= al[0]; O[i][1] *= al[1]; O[i][2] *= al[0]; O[i][3] *= al[1];
       }
     }
-    const float ms[2] = {m[0] == -INFINITY ? 0.f : m[0], m[1] == -INFINITY ? 0.f : m[1]};
-    const float p0 = ex2(sc[0] - ms[0]), p1 = ex2(sc[1] - ms[1]);
-    const float p2 = ex2(sc[2] - ms[0]), p3 = ex2(sc[3] - ms[1]);
+    const float p0 = ex2(sc[0] - m[0]), p1 = ex2(sc[1] - m[1]);   // masked scores are -inf: weight 0
+    const float p2 = ex2(sc[2] - m[0]), p3 = ex2(sc[3] - m[1]);
     l[0] += p0 + p2;
     l[1] += p1 + p3;
     // weights times value norm, transposed into the B layout (tokens as K, query = gid as N)
@@ -403,7 +411,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
   for (int e = 0; e < 2; ++e) {
     float* dst = red[warp][2 * tig + e];
     if (gid == 0) {
-      dst[0] = m[e] * kLn2;       // natural-log units, as the merge kernel expects (-inf stays -inf)
+      dst[0] = m[e] == kNone ? -INFINITY : m[e] * kLn2;   // natural-log units, as the merge expects; -inf = no token
       dst[1] = l[e];
     }
 #pragma unroll
