@@ -41,7 +41,7 @@ def same(a, b, what):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="checkout of the reference project (the directory that holds quashkv/)")
     args = ap.parse_args()
     sys.path.insert(0, args.ref)
     sys.dont_write_bytecode = True
