@@ -186,6 +186,45 @@ class QuashKVEngine:
                              self._total_tokens, Hkv, self.key_bits, self.value_bits, Pi, k_cents, v_cents,
                              Sgn, kq.qjl_scale, float(scale), bool(causal))
 
+    def attention_from_host(self, queries_host: torch.Tensor, out_host: torch.Tensor,
+                            scale: Optional[float] = None, causal: bool = False) -> torch.cuda.Event:
+        """Attention for a query that lives in pinned host memory, with the result written to a pinned host
+        buffer: ``out_host`` (batch, q_heads, q_len, head_dim) fp32 holds the output once the returned event
+        has completed.  The two transfers run on side streams with two device buffers in rotation, so that
+        back-to-back calls (decode steps of different requests, layers of a pipeline) overlap their copies
+        with each other's kernels; ``queries_host`` must stay unchanged until the event completes.  The
+        reference has no counterpart: its tensors are wherever the caller put them."""
+        if not (queries_host.is_pinned() and out_host.is_pinned()):
+            raise ValueError("attention_from_host expects pinned host tensors")
+        if out_host.dtype != torch.float32 or out_host.shape != queries_host.shape:
+            raise ValueError("out_host must be fp32 with the shape of the queries")
+        dev = self._planes["k_norms"].device if self._planes is not None else None
+        if dev is None:
+            raise ValueError("No compressed KV blocks in cache. Call append() first.")
+        io = getattr(self, "_host_io", None)
+        if io is None or io["device"] != dev:
+            io = self._host_io = {"device": dev, "h2d": torch.cuda.Stream(dev), "d2h": torch.cuda.Stream(dev),
+                                  "slots": [{"q": None, "free": None} for _ in range(2)], "n": 0}
+        slot = io["slots"][io["n"] % 2]
+        io["n"] += 1
+        compute = torch.cuda.current_stream(dev)
+        if slot["q"] is None or slot["q"].shape != queries_host.shape or slot["q"].dtype != queries_host.dtype:
+            slot["q"] = torch.empty(queries_host.shape, dtype=queries_host.dtype, device=dev)
+            slot["free"] = None
+        with torch.cuda.stream(io["h2d"]):
+            if slot["free"] is not None:
+                io["h2d"].wait_event(slot["free"])          # the kernels that read this buffer two calls ago
+            slot["q"].copy_(queries_host, non_blocking=True)
+            arrived = io["h2d"].record_event()
+        compute.wait_event(arrived)
+        out = self.attention(slot["q"], scale=scale, causal=causal)
+        slot["free"] = compute.record_event()
+        with torch.cuda.stream(io["d2h"]):
+            io["d2h"].wait_event(slot["free"])
+            out_host.copy_(out, non_blocking=True)
+            out.record_stream(io["d2h"])                    # the allocator must not reuse it before the copy ran
+            return io["d2h"].record_event()
+
     # ---- decompression of the whole cache (used by the HF-style cache) ----------------------------
     def decompress_all(self, with_signs: bool = False, out_dtype=torch.float32):
         """(keys, values) of shape (batch, heads, total_tokens, head_dim).  Keys use the code

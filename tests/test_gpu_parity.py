@@ -927,3 +927,20 @@ def test_index_save_load_and_incremental_add(tmp_path):
     empty = qk.QuashIndex(64, 4, seed=7)
     empty.save(tmp_path / "empty.pt")
     assert len(qk.QuashIndex.load(tmp_path / "empty.pt", device=DEV)) == 0
+
+
+def test_attention_from_host_overlapped_calls_match_device_calls():
+    """Back-to-back host-to-host calls (copies on side streams, device buffers in rotation) return what the
+    device-resident call returns for each query."""
+    B, Hkv, G, S, D = 2, 2, 4, 3000, 128
+    g = torch.Generator().manual_seed(17)
+    eng = qk.QuashKVEngine(D, 3, 3, seed=42, pack_storage=True)
+    eng.append(torch.randn(B, Hkv, S, D, generator=g).to(DEV), torch.randn(B, Hkv, S, D, generator=g).to(DEV))
+    qs = [torch.randn(B, Hkv * G, 1, D, generator=g).to(torch.bfloat16).pin_memory() for _ in range(7)]
+    outs = [torch.empty(B, Hkv * G, 1, D, dtype=torch.float32).pin_memory() for _ in range(7)]
+    events = [eng.attention_from_host(q, o) for q, o in zip(qs, outs)]
+    for q, o, ev in zip(qs, outs, events):
+        ev.synchronize()
+        assert torch.equal(o, eng.attention(q.to(DEV)).cpu())
+    with pytest.raises(ValueError, match="pinned"):
+        eng.attention_from_host(torch.randn(B, Hkv * G, 1, D), outs[0])
