@@ -30,6 +30,9 @@ __global__ void __launch_bounds__(128) rotate_queries_kernel(const void* __restr
                                                              const float* __restrict__ kcent,
                                                              const float* __restrict__ vcent,
                                                              uint32_t* __restrict__ tables, int n_counters) {
+  // The attention kernel that follows may be launched as a programmatic dependent: let it start right away (it
+  // waits for this grid's completion before it reads the rotated queries, the tables or the counters).
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   if (tables != nullptr && blockIdx.x == gridDim.x - 1) {   // one extra CTA: look-up tables of the
     unsigned* arrivals = reinterpret_cast<unsigned*>(reinterpret_cast<unsigned char*>(tables) + kAttnHeaderBytes);
     for (int i = threadIdx.x; i < n_counters; i += blockDim.x) arrivals[i] = 0u;   // tensor-core path,

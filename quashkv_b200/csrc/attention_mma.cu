@@ -90,67 +90,6 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
   // causal prefill) skips the operand set-up and goes straight to its neutral partial result.
   const bool has_work = n_valid > 0;
 
-  for (int idx = threadIdx.x; has_work && idx < 8 * 2 * D; idx += blockDim.x) {
-    const int r = idx / (2 * D), e = idx % (2 * D);
-    float v = 0.f;
-    if (r < nq) {
-      const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
-      const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
-      v = a.qk[qrow * 2 * D + e];
-    }
-    q_s[r][e] = v;
-  }
-  __syncthreads();
-  if (has_work && threadIdx.x < 8) {
-    float t = 0.f;
-    for (int j = 0; j < D; ++j) t += q_s[threadIdx.x][D + j];
-    wsum[threadIdx.x] = t * kLog2e;
-  }
-  __syncthreads();
-
-  // ---- register-resident B operands for query column n = gid ---------------------------------
-  // Key-code k-step s = 4*word + grp covers this lane's coordinates base + {o, o+2 | o+4, o+6},
-  // base = 32 tig + 16 word, o = 8*(grp&1) + (grp>>1): the order in which the PRMT decode below
-  // produces them.  Sign k-step s covers 32 tig + {2s, 2s+16 | 2s+1, 2s+17}.
-  const float inv_sk = __uint_as_float(a.tables[6]), inv_sv = __uint_as_float(a.tables[7]);
-  if (has_work) {                   // the operands depend on the lane only: each warp builds two k-steps
-    const float qf = kLog2e * inv_sk;
-    const float* q = q_s[gid];
-    const float* w = q_s[gid] + D;
-#pragma unroll
-    for (int s = warp; s < 8; s += kMmaWarps) {
-      const int word = s >> 2, grp = s & 3;
-      const int c0 = 32 * tig + 16 * word + grp;        // k-step s: coordinates c0 + {0, 4 | 8, 12}
-      float v[4], r[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        v[e] = q[c0 + 4 * e] * qf;
-        r[e] = v[e] - __half2float(__float2half_rn(v[e]));
-      }
-      bop[s][lane] = make_uint2(pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
-      bop[8 + s][lane] = make_uint2(pack_half2(r[0], r[1]), pack_half2(r[2], r[3]));
-      uint32_t wq[2];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {           // pairs t = 2s, 2s+1 of this lane's 32 coordinates
-        const int t = 2 * s + h, j = 32 * tig + sign_coord(t);
-        const float f = 2.f * kLog2e / sign_v1(sign_pos(t));
-        wq[h] = pack_half2(w[j] * f, w[j + 16] * f);
-      }
-      bop[16 + s][lane] = make_uint2(wq[0], wq[1]);
-    }
-  }
-  __syncthreads();
-  // ---- PRMT look-up tables: low and high bytes of the fp16 centroids ---------------------------
-  const uint32_t kt_a = a.tables[0], kt_b = a.tables[1];     // fp16 key centroids 0,1 | 2,3
-  const uint32_t vt_lo[2] = {a.tables[2], a.tables[3]}, vt_hi[2] = {a.tables[4], a.tables[5]};
-  // causal limits of this lane's two query columns (2 tig, 2 tig + 1)
-  int lim[2];
-#pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    const int r = 2 * tig + e;
-    lim[e] = (r < nq) ? (a.causal ? static_cast<int>(kv_len - a.q_len + (r0 + r) % a.q_len) : 0x7fffffff) : -1;
-  }
-
   // contiguous cache: first row of this (batch, kv head); paged cache: this head's rows inside block 0
   const int64_t seg_row0 = PAGED ? static_cast<int64_t>(hkv) * a.block_size : static_cast<int64_t>(seg) * a.cache.capacity;
   MmaPtrs p;
@@ -159,24 +98,6 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
   p.vcode = a.cache.v_codes + seg_row0 * 48;
   p.knorm = a.cache.k_norms + seg_row0;
   p.vnorm = a.cache.v_norms + seg_row0;
-
-  // positions relative to the split start, as 32-bit values
-  int lim_rel[2];
-#pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    const int64_t d = static_cast<int64_t>(lim[e]) - t_begin;
-    lim_rel[e] = lim[e] == 0x7fffffff ? 0x7fffffff : (d < -1 ? -1 : static_cast<int>(d));
-  }
-
-  float O[8][4];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f;
-  // reference exponents start at a finite "nothing seen yet" value (any finite score raises them at once), so that
-  // the token loop needs no test for minus infinity; the value written out below turns it back into -inf
-  constexpr float kNone = -1e30f;
-  float m[2] = {kNone, kNone}, l[2] = {0.f, 0.f};
-  const int odd16 = (gid & 1) * 16;
-  const float ci0 = -wsum[2 * tig], ci1 = -wsum[2 * tig + 1];   // accumulator start: -sum of sign weights
 
   // ---- cp.async ring: each lane copies up to four 16-byte chunks of a tile (104 chunks) ----------
   const int64_t t_first = t_begin + static_cast<int64_t>(warp) * kTile;
@@ -245,6 +166,96 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
     if (PAGED) blk_next = block_of(it + 1);
     cp_async_commit();                                      // one group per tile slot, even when empty
   };
+#pragma unroll
+  for (int i = 0; i < kStages - 1; ++i) issue(i);
+
+  // Everything above read only the cache planes and the block table, which no kernel of this call writes: when
+  // the launch allows it (programmatic dependent launch), this grid starts while the query-rotation kernel is
+  // still running and its first tiles are already on their way.  From here on the rotated queries, the look-up
+  // tables and the zeroed arrival counters are needed: wait for that kernel to have completed.
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+
+
+  for (int idx = threadIdx.x; has_work && idx < 8 * 2 * D; idx += blockDim.x) {
+    const int r = idx / (2 * D), e = idx % (2 * D);
+    float v = 0.f;
+    if (r < nq) {
+      const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
+      const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
+      v = a.qk[qrow * 2 * D + e];
+    }
+    q_s[r][e] = v;
+  }
+  __syncthreads();
+  if (has_work && threadIdx.x < 8) {
+    float t = 0.f;
+    for (int j = 0; j < D; ++j) t += q_s[threadIdx.x][D + j];
+    wsum[threadIdx.x] = t * kLog2e;
+  }
+  __syncthreads();
+
+  // ---- register-resident B operands for query column n = gid ---------------------------------
+  // Key-code k-step s = 4*word + grp covers this lane's coordinates base + {o, o+2 | o+4, o+6},
+  // base = 32 tig + 16 word, o = 8*(grp&1) + (grp>>1): the order in which the PRMT decode below
+  // produces them.  Sign k-step s covers 32 tig + {2s, 2s+16 | 2s+1, 2s+17}.
+  const float inv_sk = __uint_as_float(a.tables[6]), inv_sv = __uint_as_float(a.tables[7]);
+  if (has_work) {                   // the operands depend on the lane only: each warp builds two k-steps
+    const float qf = kLog2e * inv_sk;
+    const float* q = q_s[gid];
+    const float* w = q_s[gid] + D;
+#pragma unroll
+    for (int s = warp; s < 8; s += kMmaWarps) {
+      const int word = s >> 2, grp = s & 3;
+      const int c0 = 32 * tig + 16 * word + grp;        // k-step s: coordinates c0 + {0, 4 | 8, 12}
+      float v[4], r[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        v[e] = q[c0 + 4 * e] * qf;
+        r[e] = v[e] - __half2float(__float2half_rn(v[e]));
+      }
+      bop[s][lane] = make_uint2(pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
+      bop[8 + s][lane] = make_uint2(pack_half2(r[0], r[1]), pack_half2(r[2], r[3]));
+      uint32_t wq[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {           // pairs t = 2s, 2s+1 of this lane's 32 coordinates
+        const int t = 2 * s + h, j = 32 * tig + sign_coord(t);
+        const float f = 2.f * kLog2e / sign_v1(sign_pos(t));
+        wq[h] = pack_half2(w[j] * f, w[j + 16] * f);
+      }
+      bop[16 + s][lane] = make_uint2(wq[0], wq[1]);
+    }
+  }
+  __syncthreads();
+  // ---- PRMT look-up tables: low and high bytes of the fp16 centroids ---------------------------
+  const uint32_t kt_a = a.tables[0], kt_b = a.tables[1];     // fp16 key centroids 0,1 | 2,3
+  const uint32_t vt_lo[2] = {a.tables[2], a.tables[3]}, vt_hi[2] = {a.tables[4], a.tables[5]};
+  // causal limits of this lane's two query columns (2 tig, 2 tig + 1)
+  int lim[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int r = 2 * tig + e;
+    lim[e] = (r < nq) ? (a.causal ? static_cast<int>(kv_len - a.q_len + (r0 + r) % a.q_len) : 0x7fffffff) : -1;
+  }
+
+
+  // positions relative to the split start, as 32-bit values
+  int lim_rel[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int64_t d = static_cast<int64_t>(lim[e]) - t_begin;
+    lim_rel[e] = lim[e] == 0x7fffffff ? 0x7fffffff : (d < -1 ? -1 : static_cast<int>(d));
+  }
+
+  float O[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f;
+  // reference exponents start at a finite "nothing seen yet" value (any finite score raises them at once), so that
+  // the token loop needs no test for minus infinity; the value written out below turns it back into -inf
+  constexpr float kNone = -1e30f;
+  float m[2] = {kNone, kNone}, l[2] = {0.f, 0.f};
+  const int odd16 = (gid & 1) * 16;
+  const float ci0 = -wsum[2 * tig], ci1 = -wsum[2 * tig + 1];   // accumulator start: -sum of sign weights
+
   auto fetch = [&](TileRegs& T, int it) {                  // this lane's fragment slice of a staged tile
     const unsigned char* stage = ring + (it % kStages) * kStageBytes;
 #pragma unroll
@@ -386,8 +397,6 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
     }
   };
 
-#pragma unroll
-  for (int i = 0; i < kStages - 1; ++i) issue(i);
   for (int it = 0; it < n_it; ++it) {
     issue(it + kStages - 1);              // refills the slot that tile it-1 used
     cp_async_wait<kStages - 1>();         // this lane's chunks of tile `it` have landed
@@ -509,10 +518,22 @@ bool mma_path_ok(int d, int key_bits, int val_bits, int group, int q_len) {
 
 int launch_attend_mma(const AttnArgs& a, cudaStream_t st) {
   const dim3 grid(a.n_splits, (a.G * a.q_len + 7) / 8, a.B * a.Hkv);
-  if (a.block_table)
-    attend_decode_mma_kernel<true><<<grid, kMmaWarps * 32, 0, st>>>(a);
-  else
-    attend_decode_mma_kernel<false><<<grid, kMmaWarps * 32, 0, st>>>(a);
+  // Programmatic dependent launch: the grid may start while the kernel before it in the stream (the query
+  // rotation, which releases its dependents at once) is still running; the kernel waits for that kernel's
+  // completion before it reads anything that kernel writes.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kMmaWarps * 32);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t err = a.block_table ? cudaLaunchKernelEx(&cfg, attend_decode_mma_kernel<true>, a)
+                                        : cudaLaunchKernelEx(&cfg, attend_decode_mma_kernel<false>, a);
+  if (err != cudaSuccess) return QKV_ELAUNCH;
   return check_launch();
 }
 
