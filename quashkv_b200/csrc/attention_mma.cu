@@ -187,10 +187,15 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
     q_s[r][e] = v;
   }
   __syncthreads();
-  if (has_work && threadIdx.x < 8) {
-    float t = 0.f;
-    for (int j = 0; j < D; ++j) t += q_s[threadIdx.x][D + j];
-    wsum[threadIdx.x] = t * kLog2e;
+  if (has_work) {                   // a warp sums the sign weights of two query rows
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float* w = q_s[2 * warp + h] + D;
+      float t = (w[lane] + w[lane + 32]) + (w[lane + 64] + w[lane + 96]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(QKV_FULL_MASK, t, o);
+      if (lane == 0) wsum[2 * warp + h] = t * kLog2e;
+    }
   }
   __syncthreads();
 
