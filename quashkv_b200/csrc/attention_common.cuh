@@ -30,6 +30,20 @@ struct AttnArgs {
   int max_blocks, block_size;
 };
 
+// Tensor-core path: the KV range is cut into splits of UNEQUAL length, in 128-token chunks, the longest first:
+// split k gets a share proportional to 1 + kSkew (1 - 2k/(n-1)).  Splits are dispatched longest first (the split
+// index is the slowest grid dimension), so CTAs that share an SM end at different times instead of all running
+// their set-up and reduction phases together, and the last CTAs to start are the shortest.
+constexpr float kSplitSkew = 0.4f;
+__host__ __device__ inline int64_t split_begin_chunk(int k, int n, int64_t chunks) {
+  if (k <= 0) return 0;
+  if (k >= n) return chunks;
+  const float kf = static_cast<float>(k);
+  const float f = (kf + kSplitSkew * (kf - kf * (kf - 1.f) / static_cast<float>(n - 1))) / static_cast<float>(n);
+  const int64_t c = static_cast<int64_t>(f * static_cast<float>(chunks) + 0.5f);
+  return c < 0 ? 0 : (c > chunks ? chunks : c);
+}
+
 constexpr size_t kAttnHeaderBytes = 256;   // workspace header: look-up tables of the tensor-core path
 
 struct AttnPlan {

@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gid = lane >> 2, tig = lane & 3;
-  const int split = blockIdx.x, seg = blockIdx.z;
+  const int split = blockIdx.z, seg = blockIdx.x;     // splits are the slowest dimension: longest first
   const int b = seg / a.Hkv, hkv = seg % a.Hkv;
   // Query rows of a (batch, kv head) are numbered g * q_len + position; a CTA takes eight of them
   // (blockIdx.y), so decode (one tile) and prefill (many) run through the same code.
@@ -69,15 +69,11 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
   const int nq_all = a.G * a.q_len;
   const int nq = nq_all - r0 < 8 ? nq_all - r0 : 8;
 
-  // A paged batch entry divides its own length over the splits (whole 128-token chunks), so that a short
-  // sequence keeps every one of its CTAs busy for a short time instead of a few for a long time.
-  int64_t split_len = a.split_len;
-  if (PAGED) {
-    const int64_t per = ((kv_len + a.n_splits - 1) / a.n_splits + 127) / 128 * 128;
-    split_len = per < 128 ? 128 : per;
-  }
-  const int64_t t_begin = split * split_len;
-  int64_t t_end = t_begin + split_len;
+  // Every (batch entry's) length is divided over the splits in whole 128-token chunks, unequal shares, longest
+  // first; a short sequence of a paged batch so keeps all its CTAs busy for a short time.
+  const int64_t chunks = (kv_len + 127) / 128;
+  const int64_t t_begin = 128 * split_begin_chunk(split, a.n_splits, chunks);
+  int64_t t_end = 128 * split_begin_chunk(split + 1, a.n_splits, chunks);
   if (t_end > kv_len) t_end = kv_len;
   if (a.causal) {                      // tokens past the last position any row of this tile may see are skipped
     int last = 0;
@@ -522,7 +518,7 @@ bool mma_path_ok(int d, int key_bits, int val_bits, int group, int q_len) {
 }
 
 int launch_attend_mma(const AttnArgs& a, cudaStream_t st) {
-  const dim3 grid(a.n_splits, (a.G * a.q_len + 7) / 8, a.B * a.Hkv);
+  const dim3 grid(a.B * a.Hkv, (a.G * a.q_len + 7) / 8, a.n_splits);
   // Programmatic dependent launch: the grid may start while the kernel before it in the stream (the query
   // rotation, which releases its dependents at once) is still running; the kernel waits for that kernel's
   // completion before it reads anything that kernel writes.
