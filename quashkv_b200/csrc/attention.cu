@@ -472,6 +472,8 @@ int attention_run(const void* q, int q_dtype, qkv_cache_t cache, const PagedInfo
   }
   if (use_mma) {          // one launch: the last split of every (batch, kv head) merges and un-rotates
     a.tables = tables;
+    const int64_t grid_ctas = static_cast<int64_t>(B) * Hkv * (((Hq / Hkv) * q_len + 7) / 8) * p.n_splits;
+    a.skew = grid_ctas >= 2 * 4 * kNumSMs ? kSplitSkew : 0.f;
     a.arrivals = reinterpret_cast<unsigned*>(ws + kAttnHeaderBytes);
     a.Pi = Pi;
     a.out = out;

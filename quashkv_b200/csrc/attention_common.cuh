@@ -28,18 +28,21 @@ struct AttnArgs {
   // block_table[b * max_blocks + t / block_size] and the entry has seq_lens[b] tokens (kv_len bounds them).
   const int32_t* block_table; const int32_t* seq_lens;
   int max_blocks, block_size;
+  float skew;               // tensor-core path: how unequal the splits are (split_begin_chunk)
 };
 
 // Tensor-core path: the KV range is cut into splits of UNEQUAL length, in 128-token chunks, the longest first:
 // split k gets a share proportional to 1 + kSkew (1 - 2k/(n-1)).  Splits are dispatched longest first (the split
 // index is the slowest grid dimension), so CTAs that share an SM end at different times instead of all running
-// their set-up and reduction phases together, and the last CTAs to start are the shortest.
-constexpr float kSplitSkew = 0.4f;
-__host__ __device__ inline int64_t split_begin_chunk(int k, int n, int64_t chunks) {
+// their set-up and reduction phases together, and the last CTAs to start are the shortest.  The skew is only
+// used when the grid is at least two waves of resident CTAs: with fewer CTAs everything runs at once and the
+// longest split would set the time (measured on the benchmark shape: 0 -> 1.89, 0.4 -> 1.93, 0.8 -> 1.96 TB/s).
+constexpr float kSplitSkew = 0.8f;
+__host__ __device__ inline int64_t split_begin_chunk(int k, int n, int64_t chunks, float skew) {
   if (k <= 0) return 0;
   if (k >= n) return chunks;
   const float kf = static_cast<float>(k);
-  const float f = (kf + kSplitSkew * (kf - kf * (kf - 1.f) / static_cast<float>(n - 1))) / static_cast<float>(n);
+  const float f = (kf + skew * (kf - kf * (kf - 1.f) / static_cast<float>(n - 1))) / static_cast<float>(n);
   const int64_t c = static_cast<int64_t>(f * static_cast<float>(chunks) + 0.5f);
   return c < 0 ? 0 : (c > chunks ? chunks : c);
 }

@@ -72,8 +72,8 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 4) attend_decode_mma_kernel(At
   // Every (batch entry's) length is divided over the splits in whole 128-token chunks, unequal shares, longest
   // first; a short sequence of a paged batch so keeps all its CTAs busy for a short time.
   const int64_t chunks = (kv_len + 127) / 128;
-  const int64_t t_begin = 128 * split_begin_chunk(split, a.n_splits, chunks);
-  int64_t t_end = 128 * split_begin_chunk(split + 1, a.n_splits, chunks);
+  const int64_t t_begin = 128 * split_begin_chunk(split, a.n_splits, chunks, a.skew);
+  int64_t t_end = 128 * split_begin_chunk(split + 1, a.n_splits, chunks, a.skew);
   if (t_end > kv_len) t_end = kv_len;
   if (a.causal) {                      // tokens past the last position any row of this tile may see are skipped
     int last = 0;
