@@ -380,10 +380,10 @@ def run_ours(args):
                      "note": "per-GPU packed bytes / whole attention call (query rotation + split scan + merge)"},
     }
     # dram__bytes_read + write of one attend_decode_mma_kernel launch from the ncu capture summarised
-    # in profiles/attend_decode_mma_decode_batch8.md (223.1 MB at batch 8, traffic grows with the
+    # in profiles/attend_decode_mma_decode_batch8.md (223.2 MB at batch 8, traffic grows with the
     # token-heads processed: x4 at the benchmark's batch 32)
     if B == 32:
-        line["roofline"]["traffic"] = 4 * 223.06e6
+        line["roofline"]["traffic"] = 4 * 223.2e6
     if B != 32:
         line["config"]["workload"] = WORKLOAD + f"_REDUCED_batch{B}"
     if world == 1 and not args.no_cpu:
