@@ -944,3 +944,34 @@ def test_attention_from_host_overlapped_calls_match_device_calls():
         assert torch.equal(o, eng.attention(q.to(DEV)).cpu())
     with pytest.raises(ValueError, match="pinned"):
         eng.attention_from_host(torch.randn(B, Hkv * G, 1, D), outs[0])
+
+
+def test_paged_and_contiguous_large_grid_unequal_splits():
+    """A grid of more than two waves of CTAs takes the unequal-split plan (longest first); the paged and the
+    contiguous cache must still agree with each other and with the oracle (one sequence checked on CPU)."""
+    from quashkv_b200.integrations.vllm_backend import QuashKVPagedCache
+    n_seq, Hkv, G, S, D = 32, 8, 4, 8192, 128
+    g = torch.Generator(device=DEV).manual_seed(23)
+    K = torch.randn(n_seq, Hkv, S, D, device=DEV, generator=g).to(torch.bfloat16)
+    V = torch.randn(n_seq, Hkv, S, D, device=DEV, generator=g).to(torch.bfloat16)
+    Q = torch.randn(n_seq, Hkv * G, 1, D, device=DEV, generator=g).to(torch.bfloat16)
+    eng = qk.QuashKVEngine(D, 3, 3, seed=42, device=DEV, pack_storage=True)
+    eng.append(K, V)
+    pool = QuashKVPagedCache(n_seq * S // 16, Hkv, D, device=DEV)
+    ids = list(range(n_seq))
+    for lo in range(0, S, 1024):                       # interleaves the sequences' pages
+        pool.append(ids, K[:, :, lo:lo + 1024], V[:, :, lo:lo + 1024])
+    out_c = eng.attention(Q)
+    out_p = pool.attention(ids, Q)
+    kq, vq = eng.key_quantizer, eng.value_quantizer
+    Pi, Sg = kq.mse_quantizer.Pi.cpu(), kq.S.cpu()
+    kc, kb = kq.mse_quantizer.codebook.centroids.cpu(), kq.mse_quantizer.codebook.boundaries.cpu()
+    k0, v0 = K[:1].float().cpu(), V[:1].float().cpu()
+    mse, sg, kn = orc.compress_ip(k0, Pi, kb, kc, Sg)
+    vi, vn = orc.compress_mse(v0, Pi, vq.codebook.boundaries.cpu())
+    want = orc.attention_gqa(Q[:1].float().cpu(), mse, sg, kn, vi, vn, Pi, kc, vq.codebook.centroids.cpu(), Sg,
+                             kq.qjl_scale, n_kv_heads=Hkv)
+    e_pc, e_c, e_p = rel_l2(out_p, out_c), rel_l2(out_c[:1], want), rel_l2(out_p[:1], want)
+    print(f"[parity] large grid: paged vs contiguous {e_pc:.3e}, contiguous vs oracle {e_c:.3e}, paged vs oracle {e_p:.3e}")
+    assert e_pc < 2e-4 and e_c < BF16_TOL and e_p < BF16_TOL and e_c < FP32_TOL and e_p < FP32_TOL
+    assert _lib.lib().qkv_tensor_core_timeouts() == 0
