@@ -106,6 +106,19 @@ int qkv_compress_mixed(const void* x, int x_dtype, int64_t x_pitch, int64_t n_ve
                        const float* bounds_reg, int bits_reg,
                        uint8_t* codes_out, int packed, float* norms_out,
                        qkv_rows_t rows, void* stream);
+/* Mixed-precision codes plus the sign bit of the rotated residual on every channel: the two-stage
+ * quantiser with per-channel bit allocation.  Replaces MixedPrecisionIPQuantizer.compress (reference
+ * mixed_precision.py:270-322).  Codes as qkv_compress_mixed (tables at the callers' bits - 1); the
+ * residual is taken against the centroid of the channel's own table (cents_out / cents_reg) and the
+ * sign is (residual * S >= 0).  signs_out: unpacked d bytes of 0/1 per row, or packed ceil(d/8) bytes
+ * per row in channel order. */
+int qkv_compress_mixed_ip(const void* x, int x_dtype, int64_t x_pitch, int64_t n_vec, int d,
+                          const float* Pi, const uint8_t* is_outlier,
+                          const float* bounds_out, const float* cents_out, int bits_out,
+                          const float* bounds_reg, const float* cents_reg, int bits_reg,
+                          const float* S,
+                          uint8_t* codes_out, uint8_t* signs_out, int packed, float* norms_out,
+                          qkv_rows_t rows, void* stream);
 /* Bytes per packed mixed row for n_out outlier channels among d. */
 int64_t qkv_mixed_row_bytes(int d, int n_out, int bits_out, int bits_reg);
 
@@ -232,6 +245,59 @@ int qkv_attention_paged(const void* q, int q_dtype, qkv_paged_cache_t pool,
 int qkv_scatter_rows(const void* src, void* dst, const int64_t* slots, int64_t n_rows, int row_bytes,
                      void* stream);
 
+/* ---- tile records: the cache layout of the fast decode path -----------------------------------------
+ * For head_dim 128 with 3-bit keys (2-bit codes + sign bit) and 3-bit values the cache can be kept as
+ * RECORDS of 16 consecutive tokens of one (batch, kv head): QKV_TILE_BYTES = 16 * 104 bytes, the same
+ * bytes per token as the five planes of qkv_cache_t, arranged in the order in which the tensor-core
+ * kernel consumes them (key codes and sign bits as the reference packs them, reference
+ * packing.py:22-94, regrouped by lane; value codes as a sign bit and a 2-bit magnitude index with the two
+ * tokens of a multiply-accumulate pair side by side; norms last).  One record is one bulk copy for the
+ * kernel.  The re-arrangement is an exact integer permutation: qkv_untile_rows returns the reference's
+ * packed rows byte for byte.  The value half of the format presumes a value table with
+ * centroid[7 - i] = -centroid[i] (Lloyd-Max tables of a symmetric density).
+ *
+ * qkv_tile_rows files n_rows tokens, given as dense row-major planes (what qkv_compress_ip /
+ * qkv_compress_mse write with packed = 1: k_codes 32 B, k_signs 16 B, v_codes 48 B per row), into
+ * records.  Token i goes to token slot  slots[i]  when slots != NULL (negative = drop), else to slot
+ * (i / map.seg_len) * map.seg_stride + map.seg_off + i % map.seg_len; slot s is token s % 16 of record
+ * s / 16.  For a contiguous cache of `capacity` tokens per segment: seg_len = new tokens per segment,
+ * seg_stride = capacity, seg_off = tokens already stored.  Stands where the reference appends a block to
+ * its list (engine.py:145-172).  Tokens own whole bytes of a record, so any set of distinct slots may
+ * be written by one call or by concurrent calls.  records must be 16-byte aligned. */
+#define QKV_TILE_TOKENS 16
+#define QKV_TILE_BYTES 1664
+int qkv_tile_rows(const uint8_t* k_codes, const uint8_t* k_signs, const float* k_norms,
+                  const uint8_t* v_codes, const float* v_norms, int64_t n_rows,
+                  uint8_t* records, qkv_rows_t map, const int64_t* slots, void* stream);
+/* Inverse: token slots -> dense row-major planes (n_rows rows each). */
+int qkv_untile_rows(const uint8_t* records, qkv_rows_t map, const int64_t* slots, int64_t n_rows,
+                    uint8_t* k_codes, uint8_t* k_signs, float* k_norms, uint8_t* v_codes, float* v_norms,
+                    void* stream);
+
+/* qkv_attention / qkv_attention_paged over a cache of tile records (d = 128, key_bits = val_bits = 3).
+ *   contiguous (block_table == NULL): records [B*Hkv, capacity / 16, QKV_TILE_BYTES], capacity a
+ *     multiple of 16, tokens 0..kv_len-1 of each segment attended;
+ *   paged (block_table != NULL): records [num_blocks, Hkv, block_size / 16, QKV_TILE_BYTES], block_size a
+ *     multiple of 16, block_table / seq_lens / max_blocks as in qkv_paged_cache_t, kv_len the host-known
+ *     upper bound of seq_lens.
+ * Tokens of the last record beyond the length are ignored whatever they hold.  Workspace as
+ * qkv_attention_workspace_bytes.  Replaces QuashKVEngine.attention (reference engine.py:204-299). */
+typedef struct {
+  const uint8_t* records;
+  int64_t capacity;
+  const int32_t* block_table;
+  const int32_t* seq_lens;
+  int max_blocks;
+  int block_size;
+} qkv_tiled_cache_t;
+
+int qkv_attention_tiled(const void* q, int q_dtype, qkv_tiled_cache_t cache,
+                        int B, int Hq, int Hkv, int q_len, int64_t kv_len, int d,
+                        int key_bits, int val_bits,
+                        const float* Pi, const float* key_centroids, const float* val_centroids,
+                        const float* S, float qjl_scale, float scale, int causal,
+                        float* out, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- index scan ------------------------------------------------------------------------------
  * Replaces QuashIndex.search (reference nn_search/index.py:121-163):
  * score[m,n] = norm_n * (q_rot_m . c[code_n] + qjl_scale * sum(|q_rot_m| * S * (2*sign_n-1))),
@@ -261,9 +327,10 @@ int qkv_index_scores(const float* queries, int M, int d,
 int qkv_topk_merge(const float* in_scores, const int64_t* in_ids, int M, int64_t n_cand,
                    int k_out, float* out_scores, int64_t* out_ids, void* stream);
 
-/* Diagnostics, no reference counterpart: how many bounded waits on the tcgen05 tensor core ran out
- * on the current device since the library was loaded (a CTA that meets one finishes its work with
- * the fp32 CUDA-core arithmetic, so results stay correct).  0 in a healthy run.  Synchronises the
+/* Diagnostics, no reference counterpart: how many bounded waits ran out on the current device since the
+ * library was loaded: waits on the tcgen05 tensor core (a CTA that meets one finishes its work with the
+ * fp32 CUDA-core arithmetic, so results stay correct) and waits on a record copy of
+ * qkv_attention_tiled (that call's output is then not valid).  0 in a healthy run.  Synchronises the
  * device. */
 int64_t qkv_tensor_core_timeouts(void);
 

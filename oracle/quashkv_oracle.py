@@ -176,6 +176,25 @@ def compress_mixed(x, Pi, mask, bounds_outlier, bounds_regular):
     return codes, norms
 
 
+def compress_mixed_ip(x, Pi, mask, bounds_outlier, cents_outlier, bounds_regular, cents_regular, S):
+    """Mixed-precision codes plus the sign bit of the rotated residual on every channel
+    (quashkv/mixed_precision.py:270-322): codes as compress_mixed, residual against the centroid
+    of the channel's own codebook, sign = (residual * S >= 0)."""
+    x_rot, norms = _unit_rotated(x.float(), Pi)
+    if mask is None:
+        codes = codes_from_boundaries(x_rot, bounds_regular)
+        hat = cents_regular[codes.long()]
+    else:
+        codes = torch.empty_like(x_rot, dtype=torch.uint8)
+        codes[..., mask] = codes_from_boundaries(x_rot[..., mask], bounds_outlier)
+        codes[..., ~mask] = codes_from_boundaries(x_rot[..., ~mask], bounds_regular)
+        hat = torch.empty(*codes.shape, dtype=torch.float32)
+        hat[..., mask] = cents_outlier[codes[..., mask].long()]
+        hat[..., ~mask] = cents_regular[codes[..., ~mask].long()]
+    signs = (((x_rot - hat) * S) >= 0).to(torch.uint8)
+    return codes, signs, norms
+
+
 def decompress_mixed(codes, norms, Pi, mask, cents_outlier, cents_regular):
     """quashkv/mixed_precision.py:160-187."""
     if mask is None:

@@ -36,6 +36,14 @@ class PagedCache(C.Structure):
                 ("block_table", _vp), ("seq_lens", _vp), ("max_blocks", _i), ("block_size", _i)]
 
 
+class TiledCache(C.Structure):
+    """qkv_tiled_cache_t: 16-token tile records, contiguous per (batch, kv head) or paged through a block table."""
+    _fields_ = [("records", _vp), ("capacity", _i64), ("block_table", _vp), ("seq_lens", _vp),
+                ("max_blocks", _i), ("block_size", _i)]
+
+
+TILE_TOKENS, TILE_BYTES = 16, 1664
+
 # symbol -> (restype, argtypes); every symbol include/quashkv_b200.h declares is listed here
 SIGNATURES = {
     "qkv_abi_version": (_i, []),
@@ -45,6 +53,8 @@ SIGNATURES = {
     "qkv_compress_mse": (_i, [_vp, _i, _i64, _i64, _i, _vp, _vp, _i, _vp, _i, _vp, Rows, _vp]),
     "qkv_compress_ip": (_i, [_vp, _i, _i64, _i64, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, Rows, _vp]),
     "qkv_compress_mixed": (_i, [_vp, _i, _i64, _i64, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, Rows, _vp]),
+    "qkv_compress_mixed_ip": (_i, [_vp, _i, _i64, _i64, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i,
+                                   _vp, Rows, _vp]),
     "qkv_mixed_row_bytes": (_i64, [_i, _i, _i, _i]),
     "qkv_decompress": (_i, [_vp, _vp, _i, _vp, Rows, _i64, _i, _vp, _vp, _i, _vp, _f, _vp, _i, _i64, _vp]),
     "qkv_decompress_mixed": (_i, [_vp, _i, _vp, Rows, _i64, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i64, _vp]),
@@ -54,6 +64,10 @@ SIGNATURES = {
     "qkv_attention_static_scratch": (_i, [_vp, _i, Cache, _i, _i, _i, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp,
                                           _f, _f, _i, _vp, _vp]),
     "qkv_attention_paged": (_i, [_vp, _i, PagedCache, _i, _i, _i, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _f, _f,
+                                 _i, _vp, _vp, _sz, _vp]),
+    "qkv_tile_rows": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, Rows, _vp, _vp]),
+    "qkv_untile_rows": (_i, [_vp, Rows, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "qkv_attention_tiled": (_i, [_vp, _i, TiledCache, _i, _i, _i, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _f, _f,
                                  _i, _vp, _vp, _sz, _vp]),
     "qkv_scatter_rows": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "qkv_index_workspace_bytes": (_sz, [_i64, _i, _i, _i]),

@@ -417,14 +417,15 @@ struct PagedInfo {
   int max_blocks, block_size;
 };
 
-int attention_run(const void* q, int q_dtype, qkv_cache_t cache, const PagedInfo* paged,
+int attention_run(const void* q, int q_dtype, qkv_cache_t cache, const uint8_t* records, const PagedInfo* paged,
                   int B, int Hq, int Hkv, int q_len, int64_t kv_len, int d,
                   int key_bits, int val_bits,
                   const float* Pi, const float* key_centroids, const float* val_centroids,
                   const float* S, float qjl_scale, float scale, int causal,
                   float* out, void* workspace, size_t workspace_bytes, void* stream) {
-  if (!q || !cache.k_codes || !cache.k_signs || !cache.k_norms || !cache.v_codes || !cache.v_norms ||
-      !Pi || !key_centroids || !val_centroids || !S || !out || !workspace)
+  const bool tiled = records != nullptr;
+  if (!q || !Pi || !key_centroids || !val_centroids || !S || !out || !workspace) return QKV_ENULL;
+  if (!tiled && (!cache.k_codes || !cache.k_signs || !cache.k_norms || !cache.v_codes || !cache.v_norms))
     return QKV_ENULL;
   if (q_dtype != QKV_F32 && q_dtype != QKV_BF16 && q_dtype != QKV_F16) return QKV_EDTYPE;
   if (d < 32 || d > kMaxD || (d & 31)) return QKV_EDIM;
@@ -440,8 +441,13 @@ int attention_run(const void* q, int q_dtype, qkv_cache_t cache, const PagedInfo
       return QKV_EARG;
   }
   const uintptr_t al = reinterpret_cast<uintptr_t>(cache.k_codes) | reinterpret_cast<uintptr_t>(cache.k_signs) |
-                       reinterpret_cast<uintptr_t>(cache.v_codes) | reinterpret_cast<uintptr_t>(workspace);
+                       reinterpret_cast<uintptr_t>(cache.v_codes) | reinterpret_cast<uintptr_t>(workspace) |
+                       reinterpret_cast<uintptr_t>(records);
   if (al & 15u) return QKV_EALIGN;
+  if (tiled) {           // records exist for head_dim 128 at 3/3 bits only, in whole 16-token tiles
+    if (!tiled_path_ok(d, key_bits, val_bits)) return QKV_EBITS;
+    if (paged ? (paged->block_size & 15) != 0 : (cache.capacity & 15) != 0) return QKV_EARG;
+  }
   const AttnPlan p = make_plan(B, Hq, Hkv, q_len, kv_len, d);
   if (workspace_bytes < p.hdr_bytes + p.qk_bytes + p.part_bytes) return QKV_EWORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -457,7 +463,7 @@ int attention_run(const void* q, int q_dtype, qkv_cache_t cache, const PagedInfo
   // (a paged tile of 16 tokens must also lie inside one block)
   const bool chunks_ok = (paged ? paged->block_size % 16 == 0 : cache.capacity % 4 == 0) &&
       ((reinterpret_cast<uintptr_t>(cache.k_norms) | reinterpret_cast<uintptr_t>(cache.v_norms)) & 15u) == 0;
-  const bool use_mma = mma_path_ok(d, key_bits, val_bits, Hq / Hkv, q_len) && chunks_ok && !force_generic;
+  const bool use_mma = tiled || (mma_path_ok(d, key_bits, val_bits, Hq / Hkv, q_len) && chunks_ok && !force_generic);
   int rc = launch_rotate(q, q_dtype, p.rows, d, Pi, S, qjl_scale, scale, qk, key_centroids, val_centroids,
                          use_mma ? tables : nullptr, B * Hkv * (((Hq / Hkv) * q_len + 7) / 8), st);
   if (rc) return rc;
@@ -477,7 +483,8 @@ int attention_run(const void* q, int q_dtype, qkv_cache_t cache, const PagedInfo
     a.arrivals = reinterpret_cast<unsigned*>(ws + kAttnHeaderBytes);
     a.Pi = Pi;
     a.out = out;
-    return launch_attend_mma(a, st);
+    a.records = records;
+    return tiled ? launch_attend_tiled(a, st) : launch_attend_mma(a, st);
   } else {
     const dim3 grid(p.n_splits, p.n_qtiles, B * Hkv);
     pick(key_bits - 1, val_bits)<<<grid, kAttnWarps * 32, 0, st>>>(a);
@@ -494,7 +501,7 @@ extern "C" int qkv_attention(const void* q, int q_dtype, qkv_cache_t cache,
                              const float* Pi, const float* key_centroids, const float* val_centroids,
                              const float* S, float qjl_scale, float scale, int causal,
                              float* out, void* workspace, size_t workspace_bytes, void* stream) {
-  return attention_run(q, q_dtype, cache, nullptr, B, Hq, Hkv, q_len, kv_len, d, key_bits, val_bits, Pi,
+  return attention_run(q, q_dtype, cache, nullptr, nullptr, B, Hq, Hkv, q_len, kv_len, d, key_bits, val_bits, Pi,
                        key_centroids, val_centroids, S, qjl_scale, scale, causal, out, workspace, workspace_bytes,
                        stream);
 }
@@ -510,9 +517,24 @@ extern "C" int qkv_attention_paged(const void* q, int q_dtype, qkv_paged_cache_t
   planes.v_codes = pool.v_codes; planes.v_norms = pool.v_norms;
   planes.capacity = 0;
   const PagedInfo info{pool.block_table, pool.seq_lens, pool.max_blocks, pool.block_size};
-  return attention_run(q, q_dtype, planes, &info, B, Hq, Hkv, q_len, max_kv_len, d, key_bits, val_bits, Pi,
+  return attention_run(q, q_dtype, planes, nullptr, &info, B, Hq, Hkv, q_len, max_kv_len, d, key_bits, val_bits, Pi,
                        key_centroids, val_centroids, S, qjl_scale, scale, causal, out, workspace, workspace_bytes,
                        stream);
+}
+
+extern "C" int qkv_attention_tiled(const void* q, int q_dtype, qkv_tiled_cache_t cache,
+                                   int B, int Hq, int Hkv, int q_len, int64_t kv_len, int d,
+                                   int key_bits, int val_bits,
+                                   const float* Pi, const float* key_centroids, const float* val_centroids,
+                                   const float* S, float qjl_scale, float scale, int causal,
+                                   float* out, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!cache.records) return QKV_ENULL;
+  qkv_cache_t planes{};
+  planes.capacity = cache.capacity;
+  const PagedInfo info{cache.block_table, cache.seq_lens, cache.max_blocks, cache.block_size};
+  return attention_run(q, q_dtype, planes, cache.records, cache.block_table ? &info : nullptr, B, Hq, Hkv, q_len,
+                       kv_len, d, key_bits, val_bits, Pi, key_centroids, val_centroids, S, qjl_scale, scale, causal,
+                       out, workspace, workspace_bytes, stream);
 }
 
 // ---- attention without a caller-provided workspace ------------------------------------------------

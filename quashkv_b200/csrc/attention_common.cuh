@@ -29,6 +29,10 @@ struct AttnArgs {
   const int32_t* block_table; const int32_t* seq_lens;
   int max_blocks, block_size;
   float skew;               // tensor-core path: how unequal the splits are (split_begin_chunk)
+  // Tiled cache (records != nullptr): 16-token tile records (tile_format.cuh) instead of the five planes;
+  // contiguous: cache.capacity / 16 records per (batch, kv head); paged: block_size / 16 records per
+  // (block, kv head).
+  const uint8_t* records;
 };
 
 // Tensor-core path: the KV range is cut into splits of UNEQUAL length, in 128-token chunks, the longest first:
@@ -99,11 +103,17 @@ inline AttnPlan make_plan(int B, int Hq, int Hkv, int q_len, int64_t kv_len, int
 bool mma_path_ok(int d, int key_bits, int val_bits, int group, int q_len);
 int launch_attend_mma(const AttnArgs& a, cudaStream_t st);
 
+// Tensor-core path over tile records (attention_tiled.cu).
+bool tiled_path_ok(int d, int key_bits, int val_bits);
+int launch_attend_tiled(const AttnArgs& a, cudaStream_t st);
+unsigned int bulk_copy_timeouts();        // bounded waits on a record copy that ran out (device-wide counter)
+
 // Look-up tables of the tensor-core path, built by one CTA of 128 threads.  For each table the scale
 // s in [1,2) (512 candidates, 4 per thread) is chosen that makes the largest relative fp16 rounding
 // error of s*c_i smallest, so the systematic error of the fp16 operands drops well below 2^-12.
 // tables[0..1] key centroids as fp16 pairs, [2..3] value low bytes, [4..5] value high bytes,
-// [6] 1/key scale, [7] 1/value scale (floats).
+// [6] 1/key scale, [7] 1/value scale (floats), [8..9] the four value magnitudes (entries 4..7 of the
+// value table, the positive half of a symmetric table) as fp16 pairs for the sign-and-magnitude records.
 __device__ inline void prepare_tables_cta(const float* __restrict__ kcent, const float* __restrict__ vcent,
                                           uint32_t* __restrict__ tables) {
   __shared__ float cand_err[2][128];
@@ -148,6 +158,13 @@ __device__ inline void prepare_tables_cta(const float* __restrict__ kcent, const
     t[4 + (i >> 2)] |= (h >> 8) << (8 * (i & 3));
   }
   for (int i = 0; i < 6; ++i) tables[i] = t[i];
+  uint32_t mg[2] = {0, 0};
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t h = __half_as_ushort(__float2half_rn(vcent[4 + i] * sc[1]));
+    mg[i >> 1] |= h << (16 * (i & 1));
+  }
+  tables[8] = mg[0];
+  tables[9] = mg[1];
   tables[6] = __float_as_uint(1.f / sc[0]);
   tables[7] = __float_as_uint(1.f / sc[1]);
 }

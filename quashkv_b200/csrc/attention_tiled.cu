@@ -1,0 +1,505 @@
+// Decode / prefill attention over a cache of tile records (tile_format.cuh): head_dim 128, 3-bit keys
+// (2-bit codes + sign bit), 3-bit values, eight query rows of a KV head per CTA.
+// Semantics: QuashKVEngine.attention (reference engine.py:204-299).
+//
+// A warp owns 16-token tiles of its split.  One elected lane fetches a whole record (1664 bytes) with
+// ONE bulk copy into the warp's ring of four stages; an mbarrier per stage counts the bytes in, every
+// wait on it is bounded.  Each lane then reads its share with five vector loads, decodes it IN
+// REGISTERS into m16n8k16 fragments (tile_decode.cuh: one PRMT per pair of codes, one LOP3 per pair of
+// sign bits) and feeds mma.sync:
+//   scores   tokens = M, queries = N, coordinates = K: 8 MMAs on the key codes, 8 on the sign bits
+//   values   coordinates = M, tokens = K, queries = N: 8 MMAs, accumulated in the ROTATED domain
+// with an online softmax in between (log2 domain, lazily raised reference exponent).  Per split the
+// CTA writes (max, sum, accumulator); the last CTA of a (batch, kv head) to finish merges the splits
+// and applies Pi once, which equals un-rotating every value (engine.py:284-287) because the rotation
+// is linear.
+//
+// With at most four query rows per KV head (decode with up to four query heads per KV head) the
+// columns 4..7 of the score MMAs carry the fp16 rounding residual of the queries, so the scores see
+// the query at twice fp16 precision at no extra MMA.
+#include <math.h>
+#include <stdlib.h>
+
+#include "attention_common.cuh"
+#include "mma_decode.cuh"
+#include "tile_decode.cuh"
+#include "umma.cuh"
+
+namespace qkv {
+
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kRing = 5;                    // ring slots per warp: four records in flight while one is worked on
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ unsigned int g_bulk_timeouts = 0;   // bounded waits on a bulk copy that ran out
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(umma::smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+
+// global -> shared bulk copy of this GPU's own memory; completion is counted on `bar` in bytes
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                   umma::smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(umma::smem_u32(bar))
+               : "memory");
+}
+
+struct TileRegs {
+  uint4 kc;       // key codes: token g words 0, 1; token g + 8 words 0, 1
+  uint4 vm;       // value magnitudes, words m = 0..3
+  uint2 ks;       // key sign words of tokens g, g + 8
+  uint2 vs;       // value sign words of token pairs (2t, 2t+1), (2t+8, 2t+9)
+  float4 nrm;     // key norms of tokens g, g + 8; value norms of tokens g, g + 8
+};
+
+template <bool PAGED, bool LO4, int SEL>
+__global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a) {
+  constexpr int D = 128;
+  constexpr int kTile = tile::kTokens;
+  __shared__ float q_s[8][2 * D];                    // [query row][q_rot*scale | sign weights]
+  // the per-warp record rings of the token loop and the end-of-kernel reduction share storage
+  constexpr int kRingBytes = kWarps * kRing * tile::kBytes;
+  constexpr int kRedBytes = kWarps * 8 * (D + 2) * 4;
+  __shared__ __align__(128) unsigned char pool[kRingBytes > kRedBytes ? kRingBytes : kRedBytes];
+  float (*red)[8][D + 2] = reinterpret_cast<float (*)[8][D + 2]>(pool);   // [warp][query][max, sum, acc]
+  __shared__ __align__(8) uint64_t bars[kWarps][kRing];
+  __shared__ float wsum[8];                          // sum of the sign weights per query column
+  __shared__ uint2 bop[16][32];                      // B operands per k-step and lane: 8 key-code steps, 8 sign steps
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int split = blockIdx.z, seg = blockIdx.x;     // splits are the slowest dimension: longest first
+  const int b = seg / a.Hkv, hkv = seg % a.Hkv;
+  // Query rows of a (batch, kv head) are numbered g * q_len + position; a CTA takes eight of them
+  // (blockIdx.y), so decode (one tile) and prefill (many) run through the same code.
+  const int r0 = 8 * blockIdx.y;
+  int64_t kv_len = a.kv_len;
+  if (PAGED) kv_len = min(static_cast<int64_t>(max(a.seq_lens[b], 0)), a.kv_len);
+  const int nq_all = a.G * a.q_len;
+  const int nq = nq_all - r0 < 8 ? nq_all - r0 : 8;
+
+  // Every (batch entry's) length is divided over the splits in whole 128-token chunks, unequal shares,
+  // longest first (split_begin_chunk).
+  const int64_t chunks = (kv_len + 127) / 128;
+  const int64_t t_begin = 128 * split_begin_chunk(split, a.n_splits, chunks, a.skew);
+  int64_t t_end = 128 * split_begin_chunk(split + 1, a.n_splits, chunks, a.skew);
+  if (t_end > kv_len) t_end = kv_len;
+  if (a.causal) {                      // tokens past the last position any row of this tile may see are skipped
+    int last = 0;
+    for (int r = 0; r < nq; ++r) last = max(last, (r0 + r) % a.q_len);
+    const int64_t visible = kv_len - a.q_len + last + 1;
+    if (t_end > visible) t_end = visible;
+  }
+  const int n_valid = static_cast<int>(t_end - t_begin);        // tokens of this split
+  const bool has_work = n_valid > 0;
+
+  // ---- record ring: lane 0 of a warp issues one bulk copy per tile --------------------------------------
+  constexpr int kStep = kWarps * kTile;                          // tokens between a warp's tiles
+  const int first_rel = warp * kTile;
+  const int n_it = first_rel < n_valid ? (n_valid - first_rel + kStep - 1) / kStep : 0;
+  unsigned char* ring = pool + warp * (kRing * tile::kBytes);
+  uint64_t* bar = bars[warp];
+  const int64_t tile_first = (t_begin >> 4) + warp;              // this warp's first tile of the sequence
+  // contiguous cache: records of this (batch, kv head); paged: the pool, indexed through the block table
+  const int tiles_per_block = PAGED ? a.block_size >> 4 : 1;
+  const uint8_t* rec0 = PAGED ? a.records
+                              : a.records + (static_cast<int64_t>(seg) * (a.cache.capacity >> 4) + tile_first) * tile::kBytes;
+  const int32_t* bt = PAGED ? a.block_table + static_cast<int64_t>(b) * a.max_blocks : nullptr;
+  auto block_of = [&](int it) -> int {
+    const unsigned tl = static_cast<unsigned>(tile_first) + static_cast<unsigned>(it) * kWarps;
+    return it < n_it ? __ldg(bt + tl / static_cast<unsigned>(tiles_per_block)) : 0;
+  };
+  int blk_next = PAGED ? block_of(0) : 0;             // block of the tile the next issue() fetches
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < kRing; ++s) umma::mbar_init(bar + s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncwarp();
+  auto issue = [&](int it) {                          // called with it = 0, 1, 2, ... in order
+    if (it < n_it && lane == 0) {
+      const uint8_t* src;
+      if (PAGED) {
+        const unsigned tl = static_cast<unsigned>(tile_first) + static_cast<unsigned>(it) * kWarps;
+        src = rec0 + ((static_cast<int64_t>(blk_next) * a.Hkv + hkv) * tiles_per_block +
+                      tl % static_cast<unsigned>(tiles_per_block)) * tile::kBytes;
+      } else {
+        src = rec0 + static_cast<int64_t>(it) * (kWarps * tile::kBytes);
+      }
+      uint64_t* bs = bar + (it % kRing);
+      mbar_expect_tx(bs, tile::kBytes);
+      bulk_load(ring + (it % kRing) * tile::kBytes, src, tile::kBytes, bs);
+    }
+    if (PAGED) blk_next = block_of(it + 1);
+  };
+#pragma unroll
+  for (int i = 0; i < kRing; ++i) issue(i);
+
+  // Everything above read only the records and the block table, which no kernel of this call writes: when
+  // the launch allows it (programmatic dependent launch), this grid starts while the query-rotation kernel is
+  // still running and its first records are already on their way.  From here on the rotated queries, the
+  // look-up tables and the zeroed arrival counters are needed: wait for that kernel to have completed.
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+
+  // In LO4 mode query column n >= 4 is the residual of column n - 4.
+  for (int idx = threadIdx.x; has_work && idx < 8 * 2 * D; idx += blockDim.x) {
+    const int r = idx / (2 * D), e = idx % (2 * D);
+    const int rq = LO4 ? (r & 3) : r;
+    float v = 0.f;
+    if (rq < nq) {
+      const int g = (r0 + rq) / a.q_len, qi = (r0 + rq) % a.q_len;
+      const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
+      v = a.qk[qrow * 2 * D + e];
+    }
+    q_s[r][e] = v;
+  }
+  __syncthreads();
+  if (has_work) {                   // a warp sums the sign weights of two query columns
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int col = 2 * warp + h;
+      const float* w = q_s[col] + D;
+      float t = (w[lane] + w[lane + 32]) + (w[lane + 64] + w[lane + 96]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(QKV_FULL_MASK, t, o);
+      if (lane == 0) wsum[col] = (LO4 && col >= 4) ? 0.f : t * kLog2e;
+    }
+  }
+  __syncthreads();
+
+  // ---- B operands for query column n = gid ---------------------------------------------------------
+  // Key-code k-step s = 4*word + f covers this lane's coordinates 32 tig + 16 word + {f, 4+f | 8+f, 12+f}
+  // (the order in which tile::key_fragment produces them).  Sign k-step s covers 32 tig + {2s, 2s+16 | 2s+1, 2s+17}
+  // through sign_coord / sign_pos.
+  const float inv_sk = __uint_as_float(a.tables[6]), inv_sv = __uint_as_float(a.tables[7]);
+  if (has_work) {                   // the operands depend on the lane only: each warp builds two k-steps
+    const float qf = kLog2e * inv_sk;
+    const float* q = q_s[gid];
+    const float* w = q_s[gid] + D;
+    const bool resid = LO4 && gid >= 4;
+#pragma unroll
+    for (int s = warp; s < 8; s += kWarps) {
+      const int word = s >> 2, f = s & 3;
+      const int c0 = 32 * tig + 16 * word + f;
+      float v[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        v[e] = q[c0 + 4 * e] * qf;
+        if (resid) v[e] -= __half2float(__float2half_rn(v[e]));
+      }
+      bop[s][lane] = make_uint2(pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
+      uint32_t wq[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {           // pairs t = 2s, 2s+1 of this lane's 32 coordinates
+        const int t = 2 * s + h, j = 32 * tig + sign_coord(t);
+        const float fs = resid ? 0.f : 2.f * kLog2e / sign_v1(sign_pos(t));
+        wq[h] = pack_half2(w[j] * fs, w[j + 16] * fs);
+      }
+      bop[8 + s][lane] = make_uint2(wq[0], wq[1]);
+    }
+  }
+  __syncthreads();
+  const uint32_t kt_a = a.tables[0], kt_b = a.tables[1];     // fp16 key centroids 0,1 | 2,3
+  const uint32_t vt_a = a.tables[8], vt_b = a.tables[9];     // fp16 value magnitudes 0,1 | 2,3
+  // causal limits of this lane's two query columns (2 tig, 2 tig + 1), relative to the split start
+  int lim_rel[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int col = 2 * tig + e;
+    const int r = LO4 ? (col & 3) : col;
+    int lim = (r < nq) ? (a.causal ? static_cast<int>(kv_len - a.q_len + (r0 + r) % a.q_len) : 0x7fffffff) : -1;
+    const int64_t dlt = static_cast<int64_t>(lim) - t_begin;
+    lim_rel[e] = lim == 0x7fffffff ? 0x7fffffff : (dlt < -1 ? -1 : static_cast<int>(dlt));
+  }
+
+  float O[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f;
+  // reference exponents start at a finite "nothing seen yet" value (any finite score raises them at once), so that
+  // the token loop needs no test for minus infinity; the value written out below turns it back into -inf
+  constexpr float kNone = -1e30f;
+  float m[2] = {kNone, kNone}, l[2] = {0.f, 0.f};
+  const float ci0 = -wsum[2 * tig], ci1 = -wsum[2 * tig + 1];   // accumulator start: -sum of sign weights
+
+  auto process = [&](const TileRegs& cur, int it) {
+    const int rel = first_rel + it * kStep;
+    const bool masked = a.causal || rel + kTile > n_valid;      // warp-uniform
+    // ---- scores: 8 MMAs on key codes, 8 on sign bits --------------------------------------------
+    float c[4] = {ci0, ci1, ci0, ci1};
+    {
+      uint32_t af[4];
+      uint2 bq;
+#define QKV_KEY_STEP(W0, W1, WORD, F)                                   \
+  tile::key_fragment<F, SEL>(W0, W1, kt_a, kt_b, af);                        \
+  bq = bop[(WORD) * 4 + (F)][lane];                                     \
+  mma16816(c, af, bq.x, bq.y);
+      QKV_KEY_STEP(cur.kc.x, cur.kc.z, 0, 0) QKV_KEY_STEP(cur.kc.x, cur.kc.z, 0, 1)
+      QKV_KEY_STEP(cur.kc.x, cur.kc.z, 0, 2) QKV_KEY_STEP(cur.kc.x, cur.kc.z, 0, 3)
+      QKV_KEY_STEP(cur.kc.y, cur.kc.w, 1, 0) QKV_KEY_STEP(cur.kc.y, cur.kc.w, 1, 1)
+      QKV_KEY_STEP(cur.kc.y, cur.kc.w, 1, 2) QKV_KEY_STEP(cur.kc.y, cur.kc.w, 1, 3)
+#undef QKV_KEY_STEP
+    }
+    {
+      const uint32_t cp0[4] = {cur.ks.x, cur.ks.x << 7, cur.ks.x >> 1, cur.ks.x << 13};
+      const uint32_t cp1[4] = {cur.ks.y, cur.ks.y << 7, cur.ks.y >> 1, cur.ks.y << 13};
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        uint32_t af[4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int t = 2 * s + h;
+          const int cpy = t < 7 ? 0 : (t < 14 ? 1 : t - 12);
+          const uint32_t mask = 0x00010001u << sign_pos(t);
+          af[2 * h] = cp0[cpy] & mask;
+          af[2 * h + 1] = cp1[cpy] & mask;
+        }
+        const uint2 bw = bop[8 + s][lane];
+        mma16816(c, af, bw.x, bw.y);
+      }
+    }
+    if (LO4) {                      // column n + 4 holds the residual part of column n: add the two
+#pragma unroll
+      for (int e = 0; e < 4; ++e) c[e] += __shfl_xor_sync(QKV_FULL_MASK, c[e], 2);
+    }
+
+    // ---- online softmax on the accumulator fragment (log2 domain) ------------------------------
+    float sc[4] = {c[0] * cur.nrm.x, c[1] * cur.nrm.x, c[2] * cur.nrm.y, c[3] * cur.nrm.y};
+    float vn0 = cur.nrm.z, vn1 = cur.nrm.w;
+    if (masked) {
+      const int tokA = rel + gid, tokB = tokA + 8;
+      if (!(tokA < n_valid && tokA <= lim_rel[0])) sc[0] = -INFINITY;
+      if (!(tokA < n_valid && tokA <= lim_rel[1])) sc[1] = -INFINITY;
+      if (!(tokB < n_valid && tokB <= lim_rel[0])) sc[2] = -INFINITY;
+      if (!(tokB < n_valid && tokB <= lim_rel[1])) sc[3] = -INFINITY;
+      if (tokA >= n_valid) vn0 = 0.f;         // rows past the end of the sequence hold no data
+      if (tokB >= n_valid) vn1 = 0.f;
+    }
+    // m is a reference exponent, not the exact running maximum: it is raised (to the exact maximum of the tile,
+    // over the eight token lanes of a query column) only when a score of this tile exceeds it by more than
+    // kSlack, so that most tiles need one vote instead of three shuffle rounds.  Weights stay below 2^kSlack,
+    // far inside fp16 once multiplied by a value norm, and the merge of the splits only needs l and the
+    // accumulators to be relative to the m that is written out.
+    constexpr float kSlack = 4.f;
+    float mx[2] = {fmaxf(sc[0], sc[2]), fmaxf(sc[1], sc[3])};
+    if (__any_sync(QKV_FULL_MASK, mx[0] > m[0] + kSlack || mx[1] > m[1] + kSlack)) {
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) {
+        mx[0] = fmaxf(mx[0], __shfl_xor_sync(QKV_FULL_MASK, mx[0], o));
+        mx[1] = fmaxf(mx[1], __shfl_xor_sync(QKV_FULL_MASK, mx[1], o));
+      }
+      float al[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        al[e] = (mx[e] > m[e]) ? ex2(m[e] - mx[e]) : 1.f;     // ex2(kNone - x) = 0 on the first tile
+        m[e] = fmaxf(m[e], mx[e]);
+        l[e] *= al[e];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        O[i][0] *= al[0]; O[i][1] *= al[1]; O[i][2] *= al[0]; O[i][3] *= al[1];
+      }
+    }
+    const float p0 = ex2(sc[0] - m[0]), p1 = ex2(sc[1] - m[1]);   // masked scores are -inf: weight 0
+    const float p2 = ex2(sc[2] - m[0]), p3 = ex2(sc[3] - m[1]);
+    l[0] += p0 + p2;
+    l[1] += p1 + p3;
+    // weights times value norm, transposed into the B layout (tokens as K, query = gid as N)
+    const uint32_t pb0 = movmatrix_trans(pack_half2(p0 * vn0, p1 * vn0));
+    const uint32_t pb1 = movmatrix_trans(pack_half2(p2 * vn1, p3 * vn1));
+
+    // ---- values: magnitude look-up, sign flip, 8 MMAs ---------------------------------------------
+    {
+      uint32_t af[4];
+#define QKV_VAL_STEP(WORD, M, HALF)                                                  \
+  tile::value_fragment<M, HALF, SEL>(WORD, cur.vs.x, cur.vs.y, vt_a, vt_b, af);           \
+  mma16816(O[2 * (M) + (HALF)], af, pb0, pb1);
+      QKV_VAL_STEP(cur.vm.x, 0, 0) QKV_VAL_STEP(cur.vm.x, 0, 1)
+      QKV_VAL_STEP(cur.vm.y, 1, 0) QKV_VAL_STEP(cur.vm.y, 1, 1)
+      QKV_VAL_STEP(cur.vm.z, 2, 0) QKV_VAL_STEP(cur.vm.z, 2, 1)
+      QKV_VAL_STEP(cur.vm.w, 3, 0) QKV_VAL_STEP(cur.vm.w, 3, 1)
+#undef QKV_VAL_STEP
+    }
+  };
+
+  int it_failed = -1;
+  for (int it = 0; it < n_it; ++it) {
+    const int slot = it % kRing;
+    if (!__all_sync(QKV_FULL_MASK, umma::mbar_wait(bar + slot, (it / kRing) & 1))) { it_failed = it; break; }
+    const unsigned char* stage = ring + slot * tile::kBytes;
+    TileRegs cur;
+    cur.kc = *reinterpret_cast<const uint4*>(stage + tile::kOffKeyCodes + 16 * lane);
+    cur.vm = *reinterpret_cast<const uint4*>(stage + tile::kOffValMags + 16 * lane);
+    cur.ks = *reinterpret_cast<const uint2*>(stage + tile::kOffKeySigns + 8 * lane);
+    cur.vs = *reinterpret_cast<const uint2*>(stage + tile::kOffValSigns + 8 * lane);
+    cur.nrm = *reinterpret_cast<const float4*>(stage + tile::kOffNorms + 16 * gid);
+    process(cur, it);
+    // The slot is refilled only now.  A warp issues its instructions in order and an instruction issues only
+    // once its source registers hold their values, so at this point every lane's loads from the slot have
+    // returned (process() consumed all of them): the copy cannot overwrite bytes that are still to be read.
+    // Issuing it straight after the loads, before their values are used, lost that guarantee: with records
+    // coming from L2 and the load queue of the SM full, a copy was seen to land before a queued load.
+    __syncwarp();
+    issue(it + kRing);
+  }
+  if (it_failed >= 0) {
+    // A copy never arrived (not seen in practice; a hardware fault would look like this).  Count it, give the
+    // copies that are still in flight a last bounded chance to land, so that nothing writes this CTA's shared
+    // memory once it is reused below, and go on: the result of this split is then meaningless, and the
+    // counter behind qkv_tensor_core_timeouts() tells the caller so.
+    if (lane == 0) atomicAdd(&g_bulk_timeouts, 1u);
+    for (int it = it_failed + 1; it < n_it && it < it_failed + kRing; ++it)
+      umma::mbar_wait(bar + it % kRing, (it / kRing) & 1);
+  }
+  __syncthreads();                        // the reduction buffer below reuses the ring storage
+
+  // ---- per-warp results to shared memory: column sums over the token lanes, then all warps ------
+#pragma unroll
+  for (int o = 4; o < 32; o <<= 1) {
+    l[0] += __shfl_xor_sync(QKV_FULL_MASK, l[0], o);
+    l[1] += __shfl_xor_sync(QKV_FULL_MASK, l[1], o);
+  }
+  constexpr float kLn2 = 0.6931471805599453f;
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    float* dst = red[warp][2 * tig + e];
+    if (gid == 0) {
+      dst[0] = m[e] == kNone ? -INFINITY : m[e] * kLn2;   // natural-log units, as the merge expects; -inf = no token
+      dst[1] = l[e];
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {   // M-tile i holds coordinates 16 gid + 2 i, +1
+      dst[2 + 16 * gid + 2 * i] = O[i][e] * inv_sv;
+      dst[2 + 16 * gid + 2 * i + 1] = O[i][2 + e] * inv_sv;
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < nq * (D + 2); idx += blockDim.x) {
+    const int r = idx / (D + 2), e = idx % (D + 2);
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) M = fmaxf(M, red[w][r][0]);
+    float v = 0.f;
+    if (e == 0) {
+      v = M;
+    } else {
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const float f = (red[w][r][0] == -INFINITY) ? 0.f : expf(red[w][r][0] - M);
+        v += f * red[w][r][e];
+      }
+    }
+    const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
+    const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
+    a.part[(qrow * a.n_splits + split) * (D + 2) + e] = v;
+  }
+
+  // ---- the CTA that finishes a (batch, kv head) last merges its splits and applies Pi ----------------
+  __shared__ bool last_split;
+  __threadfence();                                   // this CTA's partials are visible device-wide
+  __syncthreads();
+  if (threadIdx.x == 0)
+    last_split = atomicAdd(a.arrivals + seg * gridDim.y + blockIdx.y, 1u) == static_cast<unsigned>(a.n_splits - 1);
+  __syncthreads();
+  if (!last_split) return;
+  __threadfence();                                   // ... and so are everyone else's, now
+  float* vec = reinterpret_cast<float*>(pool);       // [8][D] merged, normalised accumulators
+  float* wgt = vec + 8 * D;                          // [8][kMaxSplits] weights of the splits
+  float* invl = wgt + 8 * kMaxSplits;                // [8]
+  for (int r = warp; r < nq; r += kWarps) {          // a warp per query row
+    const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
+    const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
+    const float* pp = a.part + qrow * a.n_splits * (D + 2);
+    float M = -INFINITY;
+    for (int sp = lane; sp < a.n_splits; sp += 32) M = fmaxf(M, __ldcg(pp + sp * (D + 2)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(QKV_FULL_MASK, M, o));
+    float L = 0.f;
+    for (int sp = lane; sp < a.n_splits; sp += 32) {
+      const float mm = __ldcg(pp + sp * (D + 2));
+      const float f = (mm == -INFINITY) ? 0.f : expf(mm - M);
+      wgt[r * kMaxSplits + sp] = f;
+      L += f * __ldcg(pp + sp * (D + 2) + 1);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(QKV_FULL_MASK, L, o);
+    if (lane == 0) invl[r] = 1.f / fmaxf(L, 1e-30f);
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < nq * D; idx += blockDim.x) {
+    const int r = idx / D, j = idx % D;
+    const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
+    const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
+    const float* pp = a.part + qrow * a.n_splits * (D + 2);
+    float v = 0.f;
+    for (int sp = 0; sp < a.n_splits; ++sp) v += wgt[r * kMaxSplits + sp] * __ldcg(pp + sp * (D + 2) + 2 + j);
+    vec[r * D + j] = v * invl[r];
+  }
+  __syncthreads();
+  {
+    const int i = threadIdx.x;                       // output coordinate (blockDim.x == D)
+    float o[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) o[r] = 0.f;
+#pragma unroll 8
+    for (int j = 0; j < D; ++j) {
+      const float mval = __ldg(a.Pi + j * D + i);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) o[r] = fmaf(vec[r * D + j], mval, o[r]);
+    }
+    for (int r = 0; r < nq; ++r) {
+      const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
+      const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
+      a.out[qrow * D + i] = o[r];
+    }
+  }
+}
+
+}  // namespace
+
+unsigned int bulk_copy_timeouts() {
+  unsigned int v = 0;
+  cudaMemcpyFromSymbol(&v, g_bulk_timeouts, sizeof(v));
+  return v;
+}
+
+
+bool tiled_path_ok(int d, int key_bits, int val_bits) { return d == 128 && key_bits == 3 && val_bits == 3; }
+
+int launch_attend_tiled(const AttnArgs& a_in, cudaStream_t st) {
+  const dim3 grid(a_in.B * a_in.Hkv, (a_in.G * a_in.q_len + 7) / 8, a_in.n_splits);
+  // Programmatic dependent launch: the grid may start while the kernel before it in the stream (the query
+  // rotation, which releases its dependents at once) is still running; the kernel waits for that kernel's
+  // completion before it reads anything that kernel writes.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kWarps * 32);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const bool lo4 = a_in.G * a_in.q_len <= 4;      // spare query columns carry the fp16 residual of the queries
+  const AttnArgs& a = a_in;
+  cudaError_t err;
+  const char* es = getenv("QUASHKV_B200_TILED_SEL");
+  const int sel = es ? atoi(es) : 1;
+  if (a.block_table)
+    err = lo4 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<true, true, 1>, a)
+              : cudaLaunchKernelEx(&cfg, attend_tiled_kernel<true, false, 1>, a);
+  else if (sel == 0)
+    err = lo4 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, true, 0>, a)
+              : cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, false, 0>, a);
+  else
+    err = lo4 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, true, 1>, a)
+              : cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, false, 1>, a);
+  if (err != cudaSuccess) return QKV_ELAUNCH;
+  return check_launch();
+}
+
+}  // namespace qkv

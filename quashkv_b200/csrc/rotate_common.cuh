@@ -13,13 +13,17 @@ struct CompressArgs {
   int mode;
   const float* bounds0; int bits0;     // uniform / outlier table
   const float* bounds1; int bits1;     // regular table (mixed)
-  const float* centroids;              // IP: centroids of table 0
-  const float* S;                      // IP
+  const float* centroids;              // sign stage: centroids of table 0
+  const float* centroids1;             // sign stage of the mixed mode: centroids of table 1
+  const float* S;                      // sign stage (IP mode, or mixed mode with signs != nullptr)
   const uint8_t* is_outlier;           // mixed
   uint8_t* codes; uint8_t* signs; int packed; float* norms;
   qkv_rows_t rows;
   int skip_block_aligned;              // mixed, CUDA-core kernel: return if the outlier count is a multiple of 32
                                        // (the tcgen05 kernel launched before it took that case)
+  int test_drop_mma;                   // test hook of the tcgen05 kernel: CTA 0 issues nothing for its second
+                                       // tile, so the bounded wait on that accumulator runs out (nothing is left
+                                       // in flight) and the CTA finishes with the fp32 chain
 };
 
 struct DecompressArgs {

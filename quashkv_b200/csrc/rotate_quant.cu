@@ -20,7 +20,7 @@ constexpr int kThreads = kWarps * 32;
 //   mat   [d][DP]            fp32   (DP = 32*NT)
 //   stage [kWarps][d*kVPW]   fp32   per-warp: vector values, later permuted codes
 //   tab   [2][16]            fp32   boundaries or centroids of table 0 / 1
-//   cent  [16], sgn [128]    fp32
+//   cent  [2][16], sgn [128] fp32   centroids of table 0 / 1 (sign stage)
 //   slot  [128] int16, outl [128] uint8
 struct Smem {
   float* mat; float* stage; float* tab; float* cent; float* sgn; int16_t* slot; uint8_t* outl;
@@ -32,7 +32,7 @@ __device__ __forceinline__ Smem carve(unsigned char* raw, int d, int DP) {
   s.stage = s.mat + static_cast<size_t>(d) * DP;
   s.tab = s.stage + static_cast<size_t>(kWarps) * d * kVPW;
   s.cent = s.tab + 32;
-  s.sgn = s.cent + 16;
+  s.sgn = s.cent + 32;
   s.slot = reinterpret_cast<int16_t*>(s.sgn + kMaxD);
   s.outl = reinterpret_cast<uint8_t*>(s.slot + kMaxD);
   return s;
@@ -40,7 +40,7 @@ __device__ __forceinline__ Smem carve(unsigned char* raw, int d, int DP) {
 
 static size_t smem_bytes(int d, int NT) {
   const size_t DP = 32 * NT;
-  return (static_cast<size_t>(d) * DP + static_cast<size_t>(kWarps) * d * kVPW + 32 + 16 + kMaxD) * 4 +
+  return (static_cast<size_t>(d) * DP + static_cast<size_t>(kWarps) * d * kVPW + 32 + 32 + kMaxD) * 4 +
          kMaxD * 2 + kMaxD;
 }
 
@@ -101,12 +101,16 @@ __global__ void __launch_bounds__(kThreads, 2) compress_kernel(CompressArgs a) {
     s.mat[idx] = (i < d) ? a.Pi[i * d + j] : 0.f;
   }
   const int nb0 = (1 << a.bits0) - 1, nb1 = (a.mode == MODE_MIXED) ? (1 << a.bits1) - 1 : 0;
+  // sign stage: the two-stage key quantiser, or the mixed mode when a sign plane is asked for
+  const bool with_signs = a.mode == MODE_IP || (a.mode == MODE_MIXED && a.signs != nullptr);
   if (threadIdx.x < 16) {
     s.tab[threadIdx.x] = (threadIdx.x < nb0) ? a.bounds0[threadIdx.x] : 0.f;
     s.tab[16 + threadIdx.x] = (threadIdx.x < nb1) ? a.bounds1[threadIdx.x] : 0.f;
-    s.cent[threadIdx.x] = (a.mode == MODE_IP && threadIdx.x < (1 << a.bits0)) ? a.centroids[threadIdx.x] : 0.f;
+    s.cent[threadIdx.x] = (with_signs && threadIdx.x < (1 << a.bits0)) ? a.centroids[threadIdx.x] : 0.f;
+    s.cent[16 + threadIdx.x] =
+        (with_signs && a.mode == MODE_MIXED && threadIdx.x < (1 << a.bits1)) ? a.centroids1[threadIdx.x] : 0.f;
   }
-  for (int i = threadIdx.x; i < d; i += blockDim.x) s.sgn[i] = (a.mode == MODE_IP) ? a.S[i] : 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) s.sgn[i] = with_signs ? a.S[i] : 0.f;
   build_slots(s, a.mode == MODE_MIXED ? a.is_outlier : nullptr, d);
   __syncthreads();
   const int n_out = (a.mode == MODE_MIXED) ? count_outliers(s, d) : 0;
@@ -175,7 +179,7 @@ __global__ void __launch_bounds__(kThreads, 2) compress_kernel(CompressArgs a) {
         for (int b = 0; b < nb_of[t]; ++b) c += (y > s.tab[tab_of[t] + b]) ? 1u : 0u;
         code[t] = (i < d) ? c : 0u;
         sbit[t] = 0;
-        if (a.mode == MODE_IP && i < d) sbit[t] = ((y - s.cent[c]) * s.sgn[i] >= 0.f) ? 1u : 0u;
+        if (with_signs && i < d) sbit[t] = ((y - s.cent[tab_of[t] + c]) * s.sgn[i] >= 0.f) ? 1u : 0u;
       }
       if (lane == 0) a.norms[row] = nrm[v];
       if (!a.packed) {
@@ -185,7 +189,7 @@ __global__ void __launch_bounds__(kThreads, 2) compress_kernel(CompressArgs a) {
           const int i = lane + 32 * t;
           if (i < d) {
             crow[i] = static_cast<uint8_t>(code[t]);
-            if (a.mode == MODE_IP) a.signs[row * d + i] = static_cast<uint8_t>(sbit[t]);
+            if (with_signs) a.signs[row * d + i] = static_cast<uint8_t>(sbit[t]);
           }
         }
       } else if (a.mode != MODE_MIXED) {
@@ -229,6 +233,16 @@ __global__ void __launch_bounds__(kThreads, 2) compress_kernel(CompressArgs a) {
           const uint32_t c = (k < d - n_out) ? cstage[n_out + k] : 0u;
           const uint32_t w = pack32(c, a.bits1, lane);
           store_packed_words(w, a.bits1, crow, seg0_bytes + 4 * g * a.bits1, row_bytes_mixed, lane);
+        }
+        if (with_signs) {             // one bit per channel, in channel order
+          uint8_t* srow = a.signs + row * sign_bytes;
+#pragma unroll
+          for (int t = 0; t < NT; ++t) {
+            if (32 * t < d) {
+              const uint32_t w = __ballot_sync(QKV_FULL_MASK, sbit[t]);
+              store_packed_words(w, 1, srow, 4 * t, sign_bytes, lane);
+            }
+          }
         }
       }
     }
@@ -368,6 +382,9 @@ static bool no_tcgen05() {
 
 static int run_compress(const CompressArgs& a, cudaStream_t st) {
   if (a.n_vec == 0) return QKV_OK;
+  if (a.mode == MODE_MIXED && a.signs)       // the sign stage of the mixed mode exists in the CUDA-core kernel only
+    return launch_by_nt(a, a.d, a.n_vec, st, compress_kernel<1>, compress_kernel<2>, compress_kernel<3>,
+                        compress_kernel<4>);
   if (compress_umma_ok(a) && !cuda_core_only() && !no_tcgen05()) {
     const int rc = launch_compress_umma(a, st);
     if (rc || a.mode != MODE_MIXED) return rc;
@@ -440,6 +457,29 @@ extern "C" int qkv_compress_mixed(const void* x, int x_dtype, int64_t x_pitch, i
   return run_compress(a, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int qkv_compress_mixed_ip(const void* x, int x_dtype, int64_t x_pitch, int64_t n_vec, int d,
+                                     const float* Pi, const uint8_t* is_outlier,
+                                     const float* bounds_out, const float* cents_out, int bits_out,
+                                     const float* bounds_reg, const float* cents_reg, int bits_reg,
+                                     const float* S,
+                                     uint8_t* codes_out, uint8_t* signs_out, int packed, float* norms_out,
+                                     qkv_rows_t rows, void* stream) {
+  int rc = check_common(x, x_dtype, n_vec, d, Pi);
+  if (rc) return rc;
+  if (!is_outlier || !bounds_out || !bounds_reg || !cents_out || !cents_reg || !S ||
+      ((!codes_out || !signs_out || !norms_out) && n_vec != 0))
+    return QKV_ENULL;
+  if (bits_out < 1 || bits_out > 4 || bits_reg < 1 || bits_reg > 4) return QKV_EBITS;
+  if ((rc = check_rows(rows))) return rc;
+  CompressArgs a{};
+  a.x = x; a.x_dtype = x_dtype; a.x_pitch = x_pitch; a.n_vec = n_vec; a.d = d; a.Pi = Pi;
+  a.mode = MODE_MIXED; a.bounds0 = bounds_out; a.bits0 = bits_out; a.bounds1 = bounds_reg; a.bits1 = bits_reg;
+  a.centroids = cents_out; a.centroids1 = cents_reg; a.S = S;
+  a.is_outlier = is_outlier;
+  a.codes = codes_out; a.signs = signs_out; a.packed = packed; a.norms = norms_out; a.rows = rows;
+  return run_compress(a, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int64_t qkv_mixed_row_bytes(int d, int n_out, int bits_out, int bits_reg) {
   if (d < 1 || n_out < 0 || n_out > d) return QKV_EDIM;
   return packed_row_bytes(n_out, bits_out) + packed_row_bytes(d - n_out, bits_reg);
@@ -494,8 +534,9 @@ extern "C" int qkv_decompress_mixed(const uint8_t* codes, int packed, const floa
                       decompress_kernel<2>, decompress_kernel<3>, decompress_kernel<4>);
 }
 
-namespace qkv { unsigned int index_umma_timeouts(); }
+namespace qkv { unsigned int index_umma_timeouts(); unsigned int bulk_copy_timeouts(); }
 
 extern "C" int64_t qkv_tensor_core_timeouts(void) {
-  return static_cast<int64_t>(umma_timeouts()) + static_cast<int64_t>(index_umma_timeouts());
+  return static_cast<int64_t>(umma_timeouts()) + static_cast<int64_t>(index_umma_timeouts()) +
+         static_cast<int64_t>(bulk_copy_timeouts());
 }

@@ -20,6 +20,7 @@ head h // group); the reference requires equal counts.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -51,7 +52,14 @@ class QuashKVEngine:
         self.pack_storage = pack_storage
         self.key_quantizer = InnerProductQuantizer(d=head_dim, total_bits=key_bits, seed=seed, device=device)
         self.value_quantizer = MSEQuantizer(d=head_dim, bits=value_bits, seed=seed, device=device)
-        self._planes = None          # dict of the five planes
+        # Storage: 16-token tile records when the tensor-core decode kernel covers the configuration (head_dim
+        # 128, 3-bit keys and values, a value table with c[7-i] = -c[i]), else the five row-major planes.
+        # QUASHKV_B200_ROW_STORAGE=1 keeps the row-major planes everywhere (for A/B checks).
+        vc = self.value_quantizer.codebook.centroids
+        self._tiled = ops.tiled_layout_ok(head_dim, key_bits, value_bits) and \
+            bool((vc + vc.flip(0)).abs().max() <= 1e-6 * vc.abs().max()) and \
+            os.environ.get("QUASHKV_B200_ROW_STORAGE") != "1"
+        self._planes = None          # dict: {"records"} or the five planes
         self._shape = None           # (batch, heads)
         self._capacity = 0
         self._total_tokens = 0
@@ -72,8 +80,10 @@ class QuashKVEngine:
                 ops.packed_row_bytes(d, self.value_bits))
 
     def _allocate(self, segments: int, capacity: int, device) -> dict:
-        pk, ps, pv = self._row_bytes()
         u8 = dict(dtype=torch.uint8, device=device)
+        if self._tiled:          # 16-token tile records, the layout the tensor-core decode kernel streams
+            return {"records": torch.zeros((segments, capacity // ops.TILE_TOKENS, ops.TILE_BYTES), **u8)}
+        pk, ps, pv = self._row_bytes()
         f32 = dict(dtype=torch.float32, device=device)
         return {
             "k_codes": torch.zeros((segments, capacity, pk), **u8),
@@ -84,19 +94,48 @@ class QuashKVEngine:
         }
 
     def reserve(self, batch: int, heads: int, capacity: int, device=None) -> None:
-        """Pre-size the planes (optional; ``append`` grows them as needed)."""
+        """Pre-size the storage (optional; ``append`` grows it as needed)."""
         device = torch.device(device) if device is not None else self.device
-        capacity = -(-capacity // 64) * 64      # whole 64-row groups keep every plane row 16-byte aligned
+        capacity = -(-capacity // 64) * 64      # whole 64-row groups: 16-byte aligned plane rows, whole tiles
         if self._planes is None:
             self._shape = (batch, heads)
             self._planes = self._allocate(batch * heads, capacity, device)
             self._capacity = capacity
         elif capacity > self._capacity:
-            grown = self._allocate(self._shape[0] * self._shape[1], capacity, self._planes["k_norms"].device)
+            grown = self._allocate(self._shape[0] * self._shape[1], capacity, self._device())
+            used = -(-self._total_tokens // ops.TILE_TOKENS) if self._tiled else self._total_tokens
             for name, plane in self._planes.items():
-                grown[name][:, :self._total_tokens] = plane[:, :self._total_tokens]
+                grown[name][:, :used] = plane[:, :used]
             self._planes, self._capacity = grown, capacity
             self._block_cache = None
+
+    def _device(self):
+        return next(iter(self._planes.values())).device
+
+    def _write(self, keys: torch.Tensor, values: torch.Tensor, seg0: int, offset: int) -> None:
+        """Compress (b, H, S, d) keys / values into segments seg0.. at token offset ``offset``."""
+        kq, vq = self.key_quantizer, self.value_quantizer
+        Pi, k_bounds, k_cents, Sgn = kq._on(keys.device)
+        _, v_bounds, _ = vq._on(keys.device)
+        b, H, S, _ = keys.shape
+        p = self._planes
+        if not self._tiled:
+            sl = slice(seg0, seg0 + b * H)
+            ops.append_kv(keys, values, Pi, k_bounds, k_cents, Sgn, kq.mse_bits, v_bounds, self.value_bits,
+                          p["k_codes"][sl], p["k_signs"][sl], p["k_norms"][sl], p["v_codes"][sl], p["v_norms"][sl],
+                          offset)
+            return
+        # tiled storage: the compress kernels write the reference's packed rows into a dense staging area, an
+        # exact integer kernel files every token into its record
+        pk, ps, pv = self._row_bytes()
+        n = b * H * S
+        u8 = dict(dtype=torch.uint8, device=keys.device)
+        st = (torch.empty((b * H, S, pk), **u8), torch.empty((b * H, S, ps), **u8),
+              torch.empty((b * H, S), dtype=torch.float32, device=keys.device),
+              torch.empty((b * H, S, pv), **u8), torch.empty((b * H, S), dtype=torch.float32, device=keys.device))
+        ops.append_kv(keys, values, Pi, k_bounds, k_cents, Sgn, kq.mse_bits, v_bounds, self.value_bits, *st, 0)
+        assert st[2].numel() == n
+        ops.tile_rows(*st, p["records"][seg0:seg0 + b * H], S, self._capacity, offset, None)
 
     def append(self, keys: torch.Tensor, values: torch.Tensor) -> None:
         """Compress (batch, heads, seq, head_dim) keys and values and add them to the cache."""
@@ -104,6 +143,9 @@ class QuashKVEngine:
         B, H, S, D = keys.shape
         if D != self.head_dim or values.shape != keys.shape:
             raise ValueError(f"Expected keys and values of shape (B, H, S, {self.head_dim})")
+        if self._planes is not None and self._total_tokens == 0 and \
+                ((B, H) != self._shape or self._device() != keys.device):
+            self._planes = None          # an emptied cache takes any shape next, like the reference's clear()
         if self._planes is None:
             self.reserve(B, H, max(64, S), keys.device)
         elif (B, H) != self._shape:
@@ -111,17 +153,15 @@ class QuashKVEngine:
         need = self._total_tokens + S
         if need > self._capacity:
             self.reserve(B, H, max(need, 2 * self._capacity))
-        kq, vq = self.key_quantizer, self.value_quantizer
-        Pi, k_bounds, k_cents, Sgn = kq._on(keys.device)
-        _, v_bounds, _ = vq._on(keys.device)
-        p = self._planes
-        ops.append_kv(keys, values, Pi, k_bounds, k_cents, Sgn, kq.mse_bits, v_bounds, self.value_bits,
-                      p["k_codes"], p["k_signs"], p["k_norms"], p["v_codes"], p["v_norms"], self._total_tokens)
+        if S > 0:
+            self._write(keys, values, 0, self._total_tokens)
         self._block_lens.append(S)
         self._total_tokens = need
         self._block_cache = None
 
     def clear(self) -> None:
+        """Empty the cache (reference engine.py:174-177).  The storage is kept for the next sequence of the
+        same (batch, heads); ``append`` re-allocates when the next one differs."""
         self._total_tokens = 0
         self._block_lens = []
         self._block_cache = None
@@ -134,14 +174,27 @@ class QuashKVEngine:
     def num_blocks(self) -> int:
         return len(self._block_lens)
 
+    def row_planes(self, start: int = 0, stop: Optional[int] = None) -> dict:
+        """The five packed planes ``[batch*heads, stop - start, ...]`` in the reference's row layout
+        (packing.py:22-94): views of the storage, or exact untiled copies when the storage is tile records."""
+        stop = self._total_tokens if stop is None else stop
+        n = max(stop - start, 0)
+        p = self._planes
+        if not self._tiled:
+            return {name: plane[:, start:stop] for name, plane in p.items()}
+        segs = self._shape[0] * self._shape[1]
+        kc, ks, kn, vc, vn = ops.untile_rows(p["records"], segs * n, max(n, 1), self._capacity, start, None)
+        return {"k_codes": kc.reshape(segs, n, -1), "k_signs": ks.reshape(segs, n, -1), "k_norms": kn.reshape(segs, n),
+                "v_codes": vc.reshape(segs, n, -1), "v_norms": vn.reshape(segs, n)}
+
     @property
     def _cache(self) -> list:
         """Per-append blocks, (B, H, seq, ...) tensors like the reference keeps."""
         if self._block_cache is None:
             blocks, off = [], 0
             B, H = self._shape if self._shape else (0, 0)
+            p = self.row_planes() if self._block_lens else {}
             for n in self._block_lens:
-                p = self._planes
                 view = lambda t: t[:, off:off + n].reshape(B, H, n, *t.shape[2:])  # noqa: E731
                 mse, sgn, val = view(p["k_codes"]), view(p["k_signs"]), view(p["v_codes"])
                 if not self.pack_storage:
@@ -182,6 +235,9 @@ class QuashKVEngine:
         Pi, _, k_cents, Sgn = kq._on(queries.device)
         _, _, v_cents = vq._on(queries.device)
         p = self._planes
+        if self._tiled:
+            return ops.attention_tiled(queries, p["records"], self._capacity, self._total_tokens, Hkv, None, None, 0,
+                                       Pi, k_cents, v_cents, Sgn, kq.qjl_scale, float(scale), bool(causal))
         return ops.attention(queries, p["k_codes"], p["k_signs"], p["k_norms"], p["v_codes"], p["v_norms"],
                              self._total_tokens, Hkv, self.key_bits, self.value_bits, Pi, k_cents, v_cents,
                              Sgn, kq.qjl_scale, float(scale), bool(causal))
@@ -198,7 +254,7 @@ class QuashKVEngine:
             raise ValueError("attention_from_host expects pinned host tensors")
         if out_host.dtype != torch.float32 or out_host.shape != queries_host.shape:
             raise ValueError("out_host must be fp32 with the shape of the queries")
-        dev = self._planes["k_norms"].device if self._planes is not None else None
+        dev = self._device() if self._planes is not None else None
         if dev is None:
             raise ValueError("No compressed KV blocks in cache. Call append() first.")
         io = getattr(self, "_host_io", None)
@@ -230,16 +286,18 @@ class QuashKVEngine:
         """(keys, values) of shape (batch, heads, total_tokens, head_dim).  Keys use the code
         centroids only unless ``with_signs`` adds the sign term."""
         B, H = self._shape
-        n, d, p = self._total_tokens, self.head_dim, self._planes
+        n, d = self._total_tokens, self.head_dim
+        p = self.row_planes()
+        stride = p["k_norms"].stride(0)          # rows between segments: n for untiled copies, the capacity for views
         kq, vq = self.key_quantizer, self.value_quantizer
-        dev = p["k_norms"].device
+        dev = self._device()
         Pi, _, k_cents, Sgn = kq._on(dev)
         _, _, v_cents = vq._on(dev)
         keys = ops.decompress_rows(p["k_codes"], p["k_norms"], Pi, k_cents, kq.mse_bits, d, B * H, n,
-                                   self._capacity, 0, signs=p["k_signs"] if with_signs else None,
+                                   stride, 0, signs=p["k_signs"] if with_signs else None,
                                    S=Sgn if with_signs else None, qjl_scale=kq.qjl_scale, out_dtype=out_dtype)
         vals = ops.decompress_rows(p["v_codes"], p["v_norms"], Pi, v_cents, self.value_bits, d, B * H, n,
-                                   self._capacity, 0, out_dtype=out_dtype)
+                                   stride, 0, out_dtype=out_dtype)
         return keys.reshape(B, H, n, d), vals.reshape(B, H, n, d)
 
     # ---- statistics (formulas of reference engine.py:305-337) -------------------------------------

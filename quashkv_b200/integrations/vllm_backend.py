@@ -148,10 +148,11 @@ def register_quashkv_backend() -> None:
 class QuashKVPagedCache:
     """A pool of compressed KV pages shared by many sequences of one attention layer.
 
-    Pool planes are ``[num_blocks, num_kv_heads, block_size, row bytes]`` (codes, sign bits) and
-    ``[num_blocks, num_kv_heads, block_size]`` (norms); a sequence owns a list of pages and a token
-    count.  ``block_size`` a multiple of 16 keeps head size 128 at 3/3 bits on the tensor-core
-    attention kernel.
+    A sequence owns a list of pages and a token count.  For head size 128 at 3/3 bits with ``block_size`` a
+    multiple of 16 the pool is ``records [num_blocks, num_kv_heads, block_size / 16, 1664]``: 16-token tile
+    records, the layout the tensor-core attention kernel streams (a 16-token page is exactly one record per
+    head).  Otherwise the pool is the five row-major planes ``[num_blocks, num_kv_heads, block_size, row
+    bytes]`` (codes, sign bits) and ``[num_blocks, num_kv_heads, block_size]`` (norms) of the generic kernel.
     """
 
     def __init__(self, num_blocks: int, num_kv_heads: int, head_size: int,
@@ -171,11 +172,16 @@ class QuashKVPagedCache:
         shape = (num_blocks, num_kv_heads, self.block_size)
         u8 = dict(dtype=torch.uint8, device=self.device)
         f32 = dict(dtype=torch.float32, device=self.device)
-        self.planes = {
-            "k_codes": torch.zeros((*shape, pk), **u8), "k_signs": torch.zeros((*shape, ps), **u8),
-            "k_norms": torch.zeros(shape, **f32),
-            "v_codes": torch.zeros((*shape, pv), **u8), "v_norms": torch.zeros(shape, **f32),
-        }
+        self.tiled = self.engine._tiled and self.block_size % ops.TILE_TOKENS == 0
+        if self.tiled:
+            self.planes = {"records": torch.zeros((num_blocks, num_kv_heads, self.block_size // ops.TILE_TOKENS,
+                                                   ops.TILE_BYTES), **u8)}
+        else:
+            self.planes = {
+                "k_codes": torch.zeros((*shape, pk), **u8), "k_signs": torch.zeros((*shape, ps), **u8),
+                "k_norms": torch.zeros(shape, **f32),
+                "v_codes": torch.zeros((*shape, pv), **u8), "v_norms": torch.zeros(shape, **f32),
+            }
         self._free = list(range(num_blocks - 1, -1, -1))      # pop() hands out block 0 first
         self._blocks: dict = {}                                # sequence id -> list of block ids
         self._lens: dict = {}                                  # sequence id -> tokens stored
@@ -246,9 +252,29 @@ class QuashKVPagedCache:
         codes, signs, k_norms = ops.compress_ip(keys, Pi, k_bounds, k_cents, Sgn, kq.mse_bits, packed=True)
         v_codes, v_norms = ops.compress_mse(values, Pi, v_bounds, self.config.value_bits, packed=True)
         p = self.planes
+        if self.tiled:
+            flat = lambda t: t.reshape(n * H * T, -1).contiguous()      # noqa: E731
+            ops.tile_rows(flat(codes), flat(signs), k_norms.reshape(-1).contiguous(), flat(v_codes),
+                          v_norms.reshape(-1).contiguous(), p["records"], 1, 0, 0, slots_d)
+            return
         for src, name in ((codes, "k_codes"), (signs, "k_signs"), (k_norms, "k_norms"),
                           (v_codes, "v_codes"), (v_norms, "v_norms")):
             ops.scatter_rows(src.contiguous(), p[name], slots_d)
+
+    def rows_of(self, seq_id) -> dict:
+        """The stored tokens of one sequence as the five packed planes ``[num_kv_heads, tokens, ...]`` in the
+        reference's row layout (exact copies; for inspection and tests)."""
+        n, H, bs = self._lens.get(seq_id, 0), self.num_kv_heads, self.block_size
+        pos = torch.arange(n, device=self.device)
+        blk = torch.tensor(self._blocks.get(seq_id, []), dtype=torch.int64, device=self.device)[pos // bs]
+        slots = ((blk[None, :] * H + torch.arange(H, device=self.device)[:, None]) * bs + (pos % bs)[None, :]).reshape(-1)
+        names = ("k_codes", "k_signs", "k_norms", "v_codes", "v_norms")
+        if self.tiled:
+            rows = ops.untile_rows(self.planes["records"], H * n, 1, 0, 0, slots.contiguous())
+        else:
+            rows = [self.planes[name].reshape(self.num_blocks * H * bs, -1)[slots] for name in names]
+        return {name: r.reshape(H, n, -1) if r.dim() == 2 and name.endswith(("codes", "signs")) else r.reshape(H, n)
+                for name, r in zip(names, rows)}
 
     def attention_with_tables(self, queries: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor,
                               max_kv_len: int, scale: Optional[float] = None, causal: bool = False) -> torch.Tensor:
@@ -267,6 +293,10 @@ class QuashKVPagedCache:
         Pi, _, k_cents, Sgn = kq._on(queries.device)
         _, _, v_cents = vq._on(queries.device)
         p = self.planes
+        if self.tiled:
+            return ops.attention_tiled(queries, p["records"], 0, int(max_kv_len), self.num_kv_heads,
+                                       block_table.contiguous(), seq_lens.contiguous(), self.block_size, Pi,
+                                       k_cents, v_cents, Sgn, kq.qjl_scale, float(scale), bool(causal))
         return ops.attention_paged(queries, p["k_codes"], p["k_signs"], p["k_norms"], p["v_codes"], p["v_norms"],
                                    block_table.contiguous(), seq_lens.contiguous(), int(max_kv_len),
                                    self.config.key_bits, self.config.value_bits, Pi, k_cents, v_cents, Sgn,

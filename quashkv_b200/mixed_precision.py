@@ -32,6 +32,8 @@ class MixedPrecisionMSEQuantizer:
         self.regular_codebook = LloydMaxCodebook(d, regular_bits).to(self.device)
         self._outlier_indices: Optional[torch.Tensor] = None
         self._outlier_mask: Optional[torch.Tensor] = None
+        self._mask_u8 = torch.zeros(d, dtype=torch.uint8, device=self.device)   # what the kernels read
+        self._n_marked = 0
         self._consts = _DeviceConstants()
 
     @property
@@ -57,6 +59,9 @@ class MixedPrecisionMSEQuantizer:
         mask = torch.zeros(self.d, dtype=torch.bool, device=self.device)
         mask[self._outlier_indices] = True
         self._outlier_mask = mask
+        self._mask_u8 = mask.to(torch.uint8)
+        self._n_marked = int(torch.unique(self._outlier_indices).numel())    # host-side count, once per calibration
+        self._consts.clear()
 
     def rotate(self, x):
         return x @ self.Pi.to(x.device).T
@@ -65,11 +70,8 @@ class MixedPrecisionMSEQuantizer:
         return x_rot @ self.Pi.to(x_rot.device)
 
     def _tables(self, device):
-        c = self._consts
-        mask = self._outlier_mask
-        if mask is None:   # uncalibrated: regular codebook on every channel
-            mask = torch.zeros(self.d, dtype=torch.bool, device=self.device)
-        return (c.get("Pi", self.Pi, device), c.get("m", mask, device),
+        c = self._consts       # uncalibrated: the all-zero mask puts the regular codebook on every channel
+        return (c.get("Pi", self.Pi, device), c.get("m", self._mask_u8, device),
                 c.get("ob", self.outlier_codebook.boundaries, device),
                 c.get("rb", self.regular_codebook.boundaries, device),
                 c.get("oc", self.outlier_codebook.centroids, device),
@@ -79,7 +81,8 @@ class MixedPrecisionMSEQuantizer:
         """(..., d) -> (codes uint8, norms).  ``packed=True`` returns the packed mixed row
         (outlier channels at outlier_bits, then regular channels at regular_bits)."""
         Pi, mask, ob, rb, _, _ = self._tables(x.device)
-        return ops.compress_mixed(x, Pi, mask, ob, self.outlier_bits, rb, self.regular_bits, packed)
+        return ops.compress_mixed(x, Pi, mask, ob, self.outlier_bits, rb, self.regular_bits, packed,
+                                  n_out=self._n_marked)
 
     def decompress(self, indices: torch.Tensor, norms: torch.Tensor, packed: bool = False) -> torch.Tensor:
         Pi, mask, _, _, oc, rc = self._tables(indices.device)
@@ -94,14 +97,15 @@ class MixedPrecisionMSEQuantizer:
         if self._outlier_mask is not None:
             self._outlier_mask = self._outlier_mask.to(self.device)
             self._outlier_indices = self._outlier_indices.to(self.device)
+        self._mask_u8 = self._mask_u8.to(self.device)
+        self._consts.clear()
         return self
 
 
 class MixedPrecisionIPQuantizer:
-    """Mixed-precision codes at (bits - 1) plus one sign bit of the residual on every channel.
-
-    The code stage runs in the mixed compress kernel; the residual sign is a short
-    element-wise epilogue in torch (this variant is not on the measured hot path)."""
+    """Mixed-precision codes at (bits - 1) plus one sign bit of the rotated residual on every channel
+    (reference mixed_precision.py:200-322).  Both stages run in one kernel: the residual is taken against
+    the centroid of the channel's own codebook while the rotated coordinate is still in a register."""
 
     def __init__(self, d: int, outlier_bits: int = 3, regular_bits: int = 2, n_outliers: int = 32,
                  seed: int = DEFAULT_SEED, device="cpu"):
@@ -114,6 +118,7 @@ class MixedPrecisionIPQuantizer:
                                                         seed, device)
         self.S = _random_signs(d, seed, self.device)
         self.qjl_scale = QJL_COEFF / d
+        self._consts = _DeviceConstants()
 
     @property
     def effective_bits(self) -> float:
@@ -130,16 +135,15 @@ class MixedPrecisionIPQuantizer:
         self.mse_quantizer.set_outlier_channels(indices)
 
     def compress(self, x: torch.Tensor):
+        """(..., d) -> (codes uint8 (..., d), signs uint8 in {0,1} (..., d), norms (...))."""
         mq = self.mse_quantizer
-        codes, norms = mq.compress(x)
-        Pi, mask, _, _, oc, rc = mq._tables(x.device)
-        x_rot = (x.float() / norms.unsqueeze(-1)) @ Pi.T
-        hat = torch.where(mask, oc[codes.long().clamp(max=oc.numel() - 1)], rc[codes.long().clamp(max=rc.numel() - 1)])
-        signs = (((x_rot - hat) * self.S.to(x.device)) >= 0).to(torch.uint8)
-        return codes, signs, norms
+        Pi, mask, ob, rb, oc, rc = mq._tables(x.device)
+        S = self._consts.get("S", self.S, x.device)
+        return ops.compress_mixed_ip(x, Pi, mask, ob, oc, mq.outlier_bits, rb, rc, mq.regular_bits, S)
 
     def to(self, device):
         self.device = torch.device(device)
         self.mse_quantizer.to(device)
         self.S = self.S.to(device)
+        self._consts.clear()
         return self

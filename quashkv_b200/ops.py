@@ -18,7 +18,7 @@ from typing import Optional
 import torch
 
 from . import _lib
-from ._lib import Cache, Rows
+from ._lib import Cache, Rows, TILE_BYTES, TILE_TOKENS, TiledCache
 
 _DT = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _lib.F16}
 
@@ -43,6 +43,27 @@ def _f32(t: torch.Tensor) -> torch.Tensor:
     return t.detach().to(torch.float32).contiguous()
 
 
+class _Keep:
+    """Device pointers of converted arguments, with the converted tensors held until the C call has
+    returned: a pointer taken from a temporary would otherwise outlive its storage, and the next allocation
+    on the stream could hand that storage out again before the kernel has read it."""
+
+    def __init__(self):
+        self.held = []
+
+    def f32(self, t: Optional[torch.Tensor]):
+        if t is None:
+            return None
+        t = _f32(t)
+        self.held.append(t)
+        return _p(t)
+
+    def u8(self, t: torch.Tensor):
+        t = t.detach().to(torch.uint8).contiguous()
+        self.held.append(t)
+        return _p(t)
+
+
 def _flat(x: torch.Tensor):
     d = x.shape[-1]
     if x.dtype not in _DT:
@@ -63,6 +84,7 @@ def _pack(codes: torch.Tensor, bits: int) -> torch.Tensor:
     d = codes.shape[-1]
     flat = codes.reshape(-1, d).contiguous()
     out = torch.empty((flat.shape[0], packed_row_bytes(d, bits)), dtype=torch.uint8, device=codes.device)
+    A = _Keep()
     with torch.cuda.device(codes.device):
         _lib.check(_lib.lib().qkv_pack(_p(flat), _p(out), flat.shape[0], d, bits, _stream(codes)), "pack")
     return out.reshape(*codes.shape[:-1], out.shape[1])
@@ -81,6 +103,7 @@ def _unpack(packed: torch.Tensor, bits: int, d: int) -> torch.Tensor:
         raise ValueError(f"packed rows of {flat.shape[1]} bytes cannot hold {d} fields of {bits} bits")
     flat = flat[:, :need].contiguous()
     out = torch.empty((flat.shape[0], d), dtype=torch.uint8, device=packed.device)
+    A = _Keep()
     with torch.cuda.device(packed.device):
         _lib.check(_lib.lib().qkv_unpack(_p(flat), _p(out), flat.shape[0], d, bits, _stream(packed)), "unpack")
     return out.reshape(*packed.shape[:-1], d)
@@ -99,9 +122,10 @@ def _compress_mse(x: torch.Tensor, Pi: torch.Tensor, boundaries: torch.Tensor, b
     width = packed_row_bytes(d, bits) if packed else d
     codes = torch.empty((n, width), dtype=torch.uint8, device=x.device)
     norms = torch.empty((n,), dtype=torch.float32, device=x.device)
+    A = _Keep()
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib().qkv_compress_mse(
-            _p(flat), _DT[flat.dtype], d, n, d, _p(_f32(Pi)), _p(_f32(boundaries)), bits,
+            _p(flat), _DT[flat.dtype], d, n, d, A.f32(Pi), A.f32(boundaries), bits,
             _p(codes), int(packed), _p(norms), _dense(n), _stream(x)), "compress_mse")
     return codes.reshape(*x.shape[:-1], width), norms.reshape(x.shape[:-1])
 
@@ -124,10 +148,11 @@ def _compress_ip(x: torch.Tensor, Pi: torch.Tensor, boundaries: torch.Tensor, ce
     codes = torch.empty((n, cw), dtype=torch.uint8, device=x.device)
     signs = torch.empty((n, sw), dtype=torch.uint8, device=x.device)
     norms = torch.empty((n,), dtype=torch.float32, device=x.device)
+    A = _Keep()
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib().qkv_compress_ip(
-            _p(flat), _DT[flat.dtype], d, n, d, _p(_f32(Pi)), _p(_f32(boundaries)), _p(_f32(centroids)),
-            mse_bits, _p(_f32(S)), _p(codes), _p(signs), int(packed), _p(norms), _dense(n), _stream(x)),
+            _p(flat), _DT[flat.dtype], d, n, d, A.f32(Pi), A.f32(boundaries), A.f32(centroids),
+            mse_bits, A.f32(S), _p(codes), _p(signs), int(packed), _p(norms), _dense(n), _stream(x)),
             "compress_ip")
     lead = x.shape[:-1]
     return codes.reshape(*lead, cw), signs.reshape(*lead, sw), norms.reshape(lead)
@@ -158,13 +183,14 @@ def _append_kv(keys: torch.Tensor, values: torch.Tensor, Pi: torch.Tensor,
     cap = k_norms.shape[-1]
     rows = Rows(s_new, cap, offset)
     Pi32 = _f32(Pi)
+    A = _Keep()
     with torch.cuda.device(keys.device):
         L = _lib.lib()
         _lib.check(L.qkv_compress_ip(
-            _p(kf), _DT[kf.dtype], d, kf.shape[0], d, _p(Pi32), _p(_f32(k_bounds)), _p(_f32(k_cents)), mse_bits,
-            _p(_f32(S)), _p(k_codes), _p(k_signs), 1, _p(k_norms), rows, _stream(keys)), "append keys")
+            _p(kf), _DT[kf.dtype], d, kf.shape[0], d, _p(Pi32), A.f32(k_bounds), A.f32(k_cents), mse_bits,
+            A.f32(S), _p(k_codes), _p(k_signs), 1, _p(k_norms), rows, _stream(keys)), "append keys")
         _lib.check(L.qkv_compress_mse(
-            _p(vf), _DT[vf.dtype], d, vf.shape[0], d, _p(Pi32), _p(_f32(v_bounds)), val_bits,
+            _p(vf), _DT[vf.dtype], d, vf.shape[0], d, _p(Pi32), A.f32(v_bounds), val_bits,
             _p(v_codes), 1, _p(v_norms), rows, _stream(keys)), "append values")
 
 
@@ -176,30 +202,67 @@ def _compress_ip_into(x: torch.Tensor, Pi: torch.Tensor, boundaries: torch.Tenso
     """Compress (N,d) vectors into packed planes [capacity, bytes] at rows offset..offset+N."""
     flat, d = _flat(x)
     n = flat.shape[0]
+    A = _Keep()
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib().qkv_compress_ip(
-            _p(flat), _DT[flat.dtype], d, n, d, _p(_f32(Pi)), _p(_f32(boundaries)), _p(_f32(centroids)),
-            mse_bits, _p(_f32(S)), _p(codes), _p(signs), 1, _p(norms), Rows(max(n, 1), 0, offset),
+            _p(flat), _DT[flat.dtype], d, n, d, A.f32(Pi), A.f32(boundaries), A.f32(centroids),
+            mse_bits, A.f32(S), _p(codes), _p(signs), 1, _p(norms), Rows(max(n, 1), 0, offset),
             _stream(x)), "compress_ip_into")
 
 
 @torch.library.custom_op("quashkv_b200::compress_mixed", mutates_args=(), device_types="cuda")
 def _compress_mixed(x: torch.Tensor, Pi: torch.Tensor, is_outlier: torch.Tensor,
                     bounds_out: torch.Tensor, bits_out: int, bounds_reg: torch.Tensor, bits_reg: int,
-                    packed: bool) -> tuple[torch.Tensor, torch.Tensor]:
+                    packed: bool, n_out: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """``n_out`` = number of marked channels of ``is_outlier`` (known on the host, so that the packed row width
+    needs no device read)."""
     flat, d = _flat(x)
     n = flat.shape[0]
-    mask = is_outlier.to(torch.uint8).contiguous()
-    n_out = int(mask.sum().item()) if packed else 0
     width = int(_lib.lib().qkv_mixed_row_bytes(d, n_out, bits_out, bits_reg)) if packed else d
     codes = torch.empty((n, width), dtype=torch.uint8, device=x.device)
     norms = torch.empty((n,), dtype=torch.float32, device=x.device)
+    A = _Keep()
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib().qkv_compress_mixed(
-            _p(flat), _DT[flat.dtype], d, n, d, _p(_f32(Pi)), _p(mask), _p(_f32(bounds_out)), bits_out,
-            _p(_f32(bounds_reg)), bits_reg, _p(codes), int(packed), _p(norms), _dense(n), _stream(x)),
+            _p(flat), _DT[flat.dtype], d, n, d, A.f32(Pi), A.u8(is_outlier), A.f32(bounds_out), bits_out,
+            A.f32(bounds_reg), bits_reg, _p(codes), int(packed), _p(norms), _dense(n), _stream(x)),
             "compress_mixed")
     return codes.reshape(*x.shape[:-1], width), norms.reshape(x.shape[:-1])
+
+
+@_compress_mixed.register_fake
+def _(x, Pi, is_outlier, bounds_out, bits_out, bounds_reg, bits_reg, packed, n_out):
+    d = x.shape[-1]
+    width = (n_out * bits_out + 7) // 8 + ((d - n_out) * bits_reg + 7) // 8 if packed else d
+    return (x.new_empty((*x.shape[:-1], width), dtype=torch.uint8),
+            x.new_empty(x.shape[:-1], dtype=torch.float32))
+
+
+@torch.library.custom_op("quashkv_b200::compress_mixed_ip", mutates_args=(), device_types="cuda")
+def _compress_mixed_ip(x: torch.Tensor, Pi: torch.Tensor, is_outlier: torch.Tensor,
+                       bounds_out: torch.Tensor, cents_out: torch.Tensor, bits_out: int,
+                       bounds_reg: torch.Tensor, cents_reg: torch.Tensor, bits_reg: int,
+                       S: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Mixed-precision codes and residual sign bits, one uint8 per coordinate each, and the norms."""
+    flat, d = _flat(x)
+    n = flat.shape[0]
+    codes = torch.empty((n, d), dtype=torch.uint8, device=x.device)
+    signs = torch.empty((n, d), dtype=torch.uint8, device=x.device)
+    norms = torch.empty((n,), dtype=torch.float32, device=x.device)
+    A = _Keep()
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().qkv_compress_mixed_ip(
+            _p(flat), _DT[flat.dtype], d, n, d, A.f32(Pi), A.u8(is_outlier), A.f32(bounds_out), A.f32(cents_out),
+            bits_out, A.f32(bounds_reg), A.f32(cents_reg), bits_reg, A.f32(S), _p(codes), _p(signs), 0, _p(norms),
+            _dense(n), _stream(x)), "compress_mixed_ip")
+    lead = x.shape[:-1]
+    return codes.reshape(*lead, d), signs.reshape(*lead, d), norms.reshape(lead)
+
+
+@_compress_mixed_ip.register_fake
+def _(x, Pi, is_outlier, bounds_out, cents_out, bits_out, bounds_reg, cents_reg, bits_reg, S):
+    return (x.new_empty(x.shape, dtype=torch.uint8), x.new_empty(x.shape, dtype=torch.uint8),
+            x.new_empty(x.shape[:-1], dtype=torch.float32))
 
 
 @torch.library.custom_op("quashkv_b200::decompress", mutates_args=(), device_types="cuda")
@@ -210,10 +273,11 @@ def _decompress(codes: torch.Tensor, signs: Optional[torch.Tensor], norms: torch
     """Rows of the code/norm planes are addressed with (seg_len, seg_stride, seg_off); the
     output is dense (n_vec, d)."""
     out = torch.empty((n_vec, d), dtype=out_dtype, device=codes.device)
+    A = _Keep()
     with torch.cuda.device(codes.device):
         _lib.check(_lib.lib().qkv_decompress(
             _p(codes), _p(signs), int(packed), _p(norms), Rows(seg_len, seg_stride, seg_off), n_vec, d,
-            _p(_f32(Pi)), _p(_f32(centroids)), bits, _p(None if S is None else _f32(S)), float(qjl_scale),
+            A.f32(Pi), A.f32(centroids), bits, A.f32(S), float(qjl_scale),
             _p(out), _DT[out_dtype], d, _stream(codes)), "decompress")
     return out
 
@@ -231,12 +295,18 @@ def _decompress_mixed(codes: torch.Tensor, norms: torch.Tensor, Pi: torch.Tensor
     flat = codes.reshape(-1, codes.shape[-1]).contiguous()
     n = flat.shape[0]
     out = torch.empty((n, d), dtype=torch.float32, device=codes.device)
+    A = _Keep()
     with torch.cuda.device(codes.device):
         _lib.check(_lib.lib().qkv_decompress_mixed(
-            _p(flat), int(packed), _p(_f32(norms).reshape(-1)), _dense(n), n, d, _p(_f32(Pi)),
-            _p(is_outlier.to(torch.uint8).contiguous()), _p(_f32(cents_out)), bits_out,
-            _p(_f32(cents_reg)), bits_reg, _p(out), _lib.F32, d, _stream(codes)), "decompress_mixed")
+            _p(flat), int(packed), A.f32(norms.reshape(-1)), _dense(n), n, d, A.f32(Pi),
+            A.u8(is_outlier), A.f32(cents_out), bits_out,
+            A.f32(cents_reg), bits_reg, _p(out), _lib.F32, d, _stream(codes)), "decompress_mixed")
     return out.reshape(*codes.shape[:-1], d)
+
+
+@_decompress_mixed.register_fake
+def _(codes, norms, Pi, is_outlier, cents_out, bits_out, cents_reg, bits_reg, packed, d):
+    return codes.new_empty((*codes.shape[:-1], d), dtype=torch.float32)
 
 
 @torch.library.custom_op("quashkv_b200::attention", mutates_args=(), device_types="cuda")
@@ -257,10 +327,11 @@ def _attention(q: torch.Tensor, k_codes: torch.Tensor, k_signs: torch.Tensor, k_
     ws = torch.empty((max(ws_bytes, 16),), dtype=torch.uint8, device=q.device)
     cache = Cache(k_codes.data_ptr(), k_signs.data_ptr(), k_norms.data_ptr(), v_codes.data_ptr(),
                   v_norms.data_ptr(), cap)
+    A = _Keep()
     with torch.cuda.device(q.device):
         _lib.check(L.qkv_attention(
             _p(qc), _DT[qc.dtype], cache, B, Hq, n_kv_heads, Q, kv_len, d, key_bits, val_bits,
-            _p(_f32(Pi)), _p(_f32(key_centroids)), _p(_f32(val_centroids)), _p(_f32(S)),
+            A.f32(Pi), A.f32(key_centroids), A.f32(val_centroids), A.f32(S),
             float(qjl_scale), float(scale), int(causal), _p(out), _p(ws), ws_bytes, _stream(q)), "attention")
     return out
 
@@ -291,10 +362,11 @@ def _attention_paged(q: torch.Tensor, k_codes: torch.Tensor, k_signs: torch.Tens
     pool = _lib.PagedCache(k_codes.data_ptr(), k_signs.data_ptr(), k_norms.data_ptr(), v_codes.data_ptr(),
                            v_norms.data_ptr(), block_table.data_ptr(), seq_lens.data_ptr(),
                            block_table.shape[1], block_size)
+    A = _Keep()
     with torch.cuda.device(q.device):
         _lib.check(L.qkv_attention_paged(
             _p(qc), _DT[qc.dtype], pool, B, Hq, n_kv_heads, Q, max_kv_len, d, key_bits, val_bits,
-            _p(_f32(Pi)), _p(_f32(key_centroids)), _p(_f32(val_centroids)), _p(_f32(S)),
+            A.f32(Pi), A.f32(key_centroids), A.f32(val_centroids), A.f32(S),
             float(qjl_scale), float(scale), int(causal), _p(out), _p(ws), ws_bytes, _stream(q)), "attention_paged")
     return out
 
@@ -310,9 +382,92 @@ def _scatter_rows(src: torch.Tensor, dst: torch.Tensor, slots: torch.Tensor) -> 
     """Row i of src (n, ...) goes to row slots[i] of dst (rows, ...); rows are whole trailing slices."""
     n = slots.numel()
     row_bytes = (src.numel() // max(n, 1)) * src.element_size()
+    A = _Keep()
     with torch.cuda.device(src.device):
         _lib.check(_lib.lib().qkv_scatter_rows(_p(src), _p(dst), _p(slots), n, row_bytes, _stream(src)),
                    "scatter_rows")
+
+
+# ---- tile records (the cache layout of the tensor-core decode kernel) ---------------------------------
+
+def tiled_layout_ok(d: int, key_bits: int, val_bits: int) -> bool:
+    """Tile records exist for head_dim 128 with 3-bit keys and 3-bit values."""
+    return d == 128 and key_bits == 3 and val_bits == 3
+
+
+@torch.library.custom_op("quashkv_b200::tile_rows", mutates_args=("records",), device_types="cuda")
+def _tile_rows(k_codes: torch.Tensor, k_signs: torch.Tensor, k_norms: torch.Tensor, v_codes: torch.Tensor,
+               v_norms: torch.Tensor, records: torch.Tensor, seg_len: int, seg_stride: int, seg_off: int,
+               slots: Optional[torch.Tensor]) -> None:
+    """File dense packed rows (n, 32 / 16 / 48 bytes, fp32 norms) into 16-token tile records.  Row i goes to
+    token slot slots[i], or (i // seg_len) * seg_stride + seg_off + i % seg_len when slots is None."""
+    n = k_norms.numel()
+    A = _Keep()
+    with torch.cuda.device(records.device):
+        _lib.check(_lib.lib().qkv_tile_rows(
+            _p(k_codes), _p(k_signs), _p(k_norms), _p(v_codes), _p(v_norms), n, _p(records),
+            Rows(max(seg_len, 1), seg_stride, seg_off), _p(slots), _stream(records)), "tile_rows")
+
+
+@torch.library.custom_op("quashkv_b200::untile_rows", mutates_args=(), device_types="cuda")
+def _untile_rows(records: torch.Tensor, n_rows: int, seg_len: int, seg_stride: int, seg_off: int,
+                 slots: Optional[torch.Tensor]) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """The reference's packed rows of n_rows token slots of a tiled cache: (k_codes (n,32), k_signs (n,16),
+    k_norms (n), v_codes (n,48), v_norms (n))."""
+    dev = records.device
+    kc = torch.empty((n_rows, 32), dtype=torch.uint8, device=dev)
+    ks = torch.empty((n_rows, 16), dtype=torch.uint8, device=dev)
+    kn = torch.empty((n_rows,), dtype=torch.float32, device=dev)
+    vc = torch.empty((n_rows, 48), dtype=torch.uint8, device=dev)
+    vn = torch.empty((n_rows,), dtype=torch.float32, device=dev)
+    A = _Keep()
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().qkv_untile_rows(
+            _p(records), Rows(max(seg_len, 1), seg_stride, seg_off), _p(slots), n_rows, _p(kc), _p(ks), _p(kn),
+            _p(vc), _p(vn), _stream(records)), "untile_rows")
+    return kc, ks, kn, vc, vn
+
+
+@_untile_rows.register_fake
+def _(records, n_rows, seg_len, seg_stride, seg_off, slots):
+    u8 = lambda w: records.new_empty((n_rows, w), dtype=torch.uint8)      # noqa: E731
+    f32 = lambda: records.new_empty((n_rows,), dtype=torch.float32)       # noqa: E731
+    return u8(32), u8(16), f32(), u8(48), f32()
+
+
+@torch.library.custom_op("quashkv_b200::attention_tiled", mutates_args=(), device_types="cuda")
+def _attention_tiled(q: torch.Tensor, records: torch.Tensor, capacity: int, kv_len: int, n_kv_heads: int,
+                     block_table: Optional[torch.Tensor], seq_lens: Optional[torch.Tensor], block_size: int,
+                     Pi: torch.Tensor, key_centroids: torch.Tensor, val_centroids: torch.Tensor, S: torch.Tensor,
+                     qjl_scale: float, scale: float, causal: bool) -> torch.Tensor:
+    """q (B,Hq,Q,128); records [B*Hkv, capacity/16, 1664] (contiguous) or [blocks, Hkv, block_size/16, 1664] with a
+    (B, max_blocks) int32 block table and (B) int32 lengths (paged; kv_len is then their host-known upper
+    bound).  Returns (B,Hq,Q,128) fp32.  Pi, centroids and S must be contiguous fp32."""
+    B, Hq, Q, d = q.shape
+    if q.dtype not in _DT:
+        q = q.float()
+    qc = q.detach().contiguous()
+    out = torch.empty((B, Hq, Q, d), dtype=torch.float32, device=q.device)
+    L = _lib.lib()
+    ws_bytes = L.qkv_attention_workspace_bytes(B, Hq, n_kv_heads, Q, kv_len, d)
+    ws = torch.empty((max(ws_bytes, 16),), dtype=torch.uint8, device=q.device)
+    paged = block_table is not None
+    cache = TiledCache(records.data_ptr(), capacity, block_table.data_ptr() if paged else None,
+                       seq_lens.data_ptr() if paged else None, block_table.shape[1] if paged else 0, block_size)
+    Pi32, kc32, vc32, S32 = _f32(Pi), _f32(key_centroids), _f32(val_centroids), _f32(S)   # held until the call returns
+    A = _Keep()
+    with torch.cuda.device(q.device):
+        _lib.check(L.qkv_attention_tiled(
+            _p(qc), _DT[qc.dtype], cache, B, Hq, n_kv_heads, Q, kv_len, d, 3, 3, _p(Pi32), _p(kc32), _p(vc32),
+            _p(S32), float(qjl_scale), float(scale), int(causal), _p(out), _p(ws), ws_bytes, _stream(q)),
+            "attention_tiled")
+    return out
+
+
+@_attention_tiled.register_fake
+def _(q, records, capacity, kv_len, n_kv_heads, block_table, seq_lens, block_size, Pi, key_centroids,
+      val_centroids, S, qjl_scale, scale, causal):
+    return q.new_empty(q.shape, dtype=torch.float32)
 
 
 @torch.library.custom_op("quashkv_b200::index_scan_topk", mutates_args=(), device_types="cuda")
@@ -327,10 +482,11 @@ def _index_scan_topk(queries: torch.Tensor, db_codes: torch.Tensor, db_signs: to
     L = _lib.lib()
     ws_bytes = L.qkv_index_workspace_bytes(n_vectors, M, d, k)
     ws = torch.empty((max(ws_bytes, 16),), dtype=torch.uint8, device=qf.device)
+    A = _Keep()
     with torch.cuda.device(qf.device):
         _lib.check(L.qkv_index_scan_topk(
-            _p(qf), M, d, _p(db_codes), _p(db_signs), _p(db_norms), n_vectors, bits, _p(_f32(Pi)),
-            _p(_f32(centroids)), _p(_f32(S)), float(qjl_scale), k, id_base, _p(scores), _p(ids),
+            _p(qf), M, d, _p(db_codes), _p(db_signs), _p(db_norms), n_vectors, bits, A.f32(Pi),
+            A.f32(centroids), A.f32(S), float(qjl_scale), k, id_base, _p(scores), _p(ids),
             _p(ws), ws_bytes, _stream(qf)), "index_scan_topk")
     return scores, ids
 
@@ -351,12 +507,18 @@ def _index_scores(queries: torch.Tensor, db_codes: torch.Tensor, db_signs: torch
     L = _lib.lib()
     ws_bytes = L.qkv_index_workspace_bytes(n_vectors, M, d, 1)
     ws = torch.empty((max(ws_bytes, 16),), dtype=torch.uint8, device=qf.device)
+    A = _Keep()
     with torch.cuda.device(qf.device):
         _lib.check(L.qkv_index_scores(
-            _p(qf), M, d, _p(db_codes), _p(db_signs), _p(db_norms), n_vectors, bits, _p(_f32(Pi)),
-            _p(_f32(centroids)), _p(_f32(S)), float(qjl_scale), _p(out), _p(ws), ws_bytes, _stream(qf)),
+            _p(qf), M, d, _p(db_codes), _p(db_signs), _p(db_norms), n_vectors, bits, A.f32(Pi),
+            A.f32(centroids), A.f32(S), float(qjl_scale), _p(out), _p(ws), ws_bytes, _stream(qf)),
             "index_scores")
     return out
+
+
+@_index_scores.register_fake
+def _(queries, db_codes, db_signs, db_norms, n_vectors, bits, Pi, centroids, S, qjl_scale):
+    return queries.new_empty((queries.shape[0], n_vectors), dtype=torch.float32)
 
 
 @torch.library.custom_op("quashkv_b200::topk_merge", mutates_args=(), device_types="cuda")
@@ -366,6 +528,7 @@ def _topk_merge(scores: torch.Tensor, ids: torch.Tensor, k: int) -> tuple[torch.
     M, n_cand = s.shape
     out_s = torch.empty((M, k), dtype=torch.float32, device=s.device)
     out_i = torch.empty((M, k), dtype=torch.int64, device=s.device)
+    A = _Keep()
     with torch.cuda.device(s.device):
         _lib.check(_lib.lib().qkv_topk_merge(_p(s), _p(i), M, n_cand, k, _p(out_s), _p(out_i), _stream(s)),
                    "topk_merge")
@@ -417,9 +580,17 @@ def compress_ip(x, Pi, boundaries, centroids, S, mse_bits, packed=False):
     return _compress_ip(x, Pi, boundaries, centroids, S, mse_bits, packed)
 
 
-def compress_mixed(x, Pi, is_outlier, bounds_out, bits_out, bounds_reg, bits_reg, packed=False):
+def compress_mixed(x, Pi, is_outlier, bounds_out, bits_out, bounds_reg, bits_reg, packed=False, n_out=None):
+    """``n_out``: how many channels ``is_outlier`` marks; counted here (one device read) when not given."""
     _need_cuda(x, "compress_mixed")
-    return _compress_mixed(x, Pi, is_outlier, bounds_out, bits_out, bounds_reg, bits_reg, packed)
+    if n_out is None:
+        n_out = int(is_outlier.sum().item()) if packed else 0
+    return _compress_mixed(x, Pi, is_outlier, bounds_out, bits_out, bounds_reg, bits_reg, packed, int(n_out))
+
+
+def compress_mixed_ip(x, Pi, is_outlier, bounds_out, cents_out, bits_out, bounds_reg, cents_reg, bits_reg, S):
+    _need_cuda(x, "compress_mixed_ip")
+    return _compress_mixed_ip(x, Pi, is_outlier, bounds_out, cents_out, bits_out, bounds_reg, cents_reg, bits_reg, S)
 
 
 def decompress(codes, norms, Pi, centroids, bits, *, signs=None, S=None, qjl_scale=0.0, packed=False,
@@ -457,6 +628,9 @@ compress_ip_into = _compress_ip_into
 attention = _attention
 attention_paged = _attention_paged
 scatter_rows = _scatter_rows
+tile_rows = _tile_rows
+untile_rows = _untile_rows
+attention_tiled = _attention_tiled
 index_scan_topk = _index_scan_topk
 index_scores = _index_scores
 topk_merge = _topk_merge

@@ -21,7 +21,8 @@ def _random_orthogonal(d: int, seed: int, device) -> torch.Tensor:
     gen = torch.Generator(device="cpu").manual_seed(seed)
     gauss = torch.randn(d, d, generator=gen, dtype=torch.float32)
     q, r = torch.linalg.qr(gauss)
-    return (q * torch.sign(torch.diag(r)).unsqueeze(0)).to(device)
+    # the QR factor comes back column-major; the kernels read Pi row-major, so make it so once, here
+    return (q * torch.sign(torch.diag(r)).unsqueeze(0)).contiguous().to(device)
 
 
 def _random_signs(d: int, seed: int, device) -> torch.Tensor:
@@ -32,18 +33,24 @@ def _random_signs(d: int, seed: int, device) -> torch.Tensor:
 
 class _DeviceConstants:
     """Copies of small constant tensors per device, so an object built with the default
-    ``device="cpu"`` can still serve CUDA inputs."""
+    ``device="cpu"`` can still serve CUDA inputs.  A copy is tied to the very tensor object it was made
+    from (held here, so its address cannot be recycled) and to that tensor's version counter: replacing or
+    modifying the source tensor makes the next ``get`` copy again."""
 
     def __init__(self):
         self._copies = {}
 
     def get(self, name: str, tensor: torch.Tensor, device: torch.device) -> torch.Tensor:
-        if tensor.device == device:
+        if tensor.device == device and tensor.is_contiguous():
             return tensor
-        key = (name, device, tensor.data_ptr())
-        if key not in self._copies:
-            self._copies[key] = tensor.to(device)
-        return self._copies[key]
+        ent = self._copies.get((name, device))
+        if ent is None or ent[0] is not tensor or ent[1] != tensor._version:
+            ent = (tensor, tensor._version, tensor.to(device).contiguous())
+            self._copies[(name, device)] = ent
+        return ent[2]
+
+    def clear(self) -> None:
+        self._copies.clear()
 
 
 class MSEQuantizer:

@@ -34,6 +34,9 @@ def fused_quantized_attention(queries: torch.Tensor, blocks: list, Pi: torch.Ten
                               key_centroids: torch.Tensor, val_centroids: torch.Tensor, S: torch.Tensor,
                               qjl_scale: float, scale: Optional[float] = None, causal: bool = False,
                               total_kv_tokens: int = 0) -> torch.Tensor:
+    """With ``causal``, query row i sits at position ``total_kv_tokens - Q + i`` and sees keys at positions up to
+    its own (reference attention.py:119-123).  ``total_kv_tokens = 0`` (the default, for which the reference masks
+    every key and returns NaN) is read as "the number of tokens in ``blocks``"."""
     B, H, Q, D = queries.shape
     if scale is None:
         scale = 1.0 / math.sqrt(D)
@@ -47,5 +50,26 @@ def fused_quantized_attention(queries: torch.Tensor, blocks: list, Pi: torch.Ten
     v_codes = ops.pack(cat("val_indices"), vb).reshape(seg, kv, -1)
     k_norms = cat("key_norms").float().reshape(seg, kv).contiguous()
     v_norms = cat("val_norms").float().reshape(seg, kv).contiguous()
-    return ops.attention(queries, k_codes, k_signs, k_norms, v_codes, v_norms, kv, Hkv, kb + 1, vb, Pi,
-                         key_centroids, val_centroids, S, float(qjl_scale), float(scale), bool(causal))
+
+    def run(q, n_keys, is_causal):
+        return ops.attention(q, k_codes, k_signs, k_norms, v_codes, v_norms, n_keys, Hkv, kb + 1, vb, Pi,
+                             key_centroids, val_centroids, S, float(qjl_scale), float(scale), is_causal)
+
+    total = int(total_kv_tokens) if total_kv_tokens else kv
+    if not causal or total == kv:
+        return run(queries, kv, bool(causal))
+    if total < kv:
+        # the queries sit before the end of the blocks: keys at positions >= total are hidden from all of them
+        if total < Q:
+            raise ValueError(f"causal attention: total_kv_tokens = {total} puts query rows before position 0")
+        return run(queries, total, True)
+    # the queries sit past the end of the blocks: the last rows see every key, the first
+    # Q - (total - kv) rows are the causal tail of the stored keys
+    n_causal = Q - (total - kv)
+    if n_causal <= 0:
+        return run(queries, kv, False)
+    if n_causal > kv:
+        raise ValueError(f"causal attention: total_kv_tokens = {total} puts query rows before position 0")
+    head = run(queries[:, :, :n_causal], kv, True)
+    tail = run(queries[:, :, n_causal:], kv, False)
+    return torch.cat([head, tail], dim=2)

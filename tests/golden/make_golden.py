@@ -238,8 +238,26 @@ def main():
     rec = mp.decompress(idx, nrm)
     same(orc.decompress_mixed(idx, nrm, mp.Pi, mp._outlier_mask, mp.outlier_codebook.centroids,
                               mp.regular_codebook.centroids), rec, "mixed decompress")
+    # two-stage variant: codes at (bits - 1) per channel group plus one residual sign bit on every channel
+    mip = ref.MixedPrecisionIPQuantizer(d, 3, 2, 32, seed=42)
+    u_codes, u_signs, u_norms = mip.compress(x[:64])              # uncalibrated: regular codebook everywhere
+    mq = mip.mse_quantizer
+    o_codes, o_signs, o_norms = orc.compress_mixed_ip(x[:64], mq.Pi, None, mq.outlier_codebook.boundaries,
+                                                      mq.outlier_codebook.centroids, mq.regular_codebook.boundaries,
+                                                      mq.regular_codebook.centroids, mip.S)
+    same(o_codes, u_codes, "mixed ip uncalibrated codes"), same(o_signs, u_signs, "mixed ip uncalibrated signs")
+    mip.calibrate(x[:1024])
+    ip_codes, ip_signs, ip_norms = mip.compress(x[1024:])
+    o_codes, o_signs, o_norms = orc.compress_mixed_ip(x[1024:], mq.Pi, mq._outlier_mask,
+                                                      mq.outlier_codebook.boundaries, mq.outlier_codebook.centroids,
+                                                      mq.regular_codebook.boundaries, mq.regular_codebook.centroids,
+                                                      mip.S)
+    same(o_codes, ip_codes, "mixed ip codes"), same(o_signs, ip_signs, "mixed ip signs")
+    same(o_norms, ip_norms, "mixed ip norms")
     np.savez_compressed(os.path.join(HERE, "mixed.npz"), x=npy(x), channels=npy(ch), codes=npy(idx),
-                        norms=npy(nrm), rec=npy(rec), codes_uncal=npy(i_un))
+                        norms=npy(nrm), rec=npy(rec), codes_uncal=npy(i_un),
+                        ip_channels=npy(mq._outlier_indices), ip_codes=npy(ip_codes), ip_signs=npy(ip_signs),
+                        ip_norms=npy(ip_norms), ip_codes_uncal=npy(u_codes), ip_signs_uncal=npy(u_signs))
 
     # ---- index search ------------------------------------------------------------------
     ix = {}

@@ -21,7 +21,7 @@ from quashkv_b200.triton_kernels import (CompressedBlock, fused_compress_ip, fus
                                          fused_decompress_ip, fused_decompress_mse,
                                          fused_quantized_attention)
 from oracle import quashkv_oracle as orc
-from helpers import code_ties, rel_l2, t, ulp_diff
+from helpers import code_ties, rel_l2, t, tile_records_reference, ulp_diff
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -261,10 +261,38 @@ def test_mixed_precision(golden):
     layout = torch.cat([orc.pack_bits(cc[:, mask], 3), orc.pack_bits(cc[:, ~mask], 2)], dim=1)
     assert torch.equal(pk.cpu(), layout)
     assert torch.equal(mp.decompress(pk, norms, packed=True), mp.decompress(codes, norms))
+    # two-stage variant against the reference class: codes at (bits - 1) per channel group, one residual sign
+    # bit on every channel (taken against the centroid of the channel's own codebook)
     ipq = qk.MixedPrecisionIPQuantizer(128, 3, 2, 32, seed=42)
-    ipq.set_outlier_channels(mp._outlier_indices)
-    m, s, n = ipq.compress(xs[:32].to(DEV))
-    assert m.shape == s.shape == (32, 128) and int(s.max()) <= 1 and ipq.effective_bits == pytest.approx(2.25)
+    pin_rotation(ipq, Pi)
+    S = t(c["S_d128_s42"])
+    assert torch.equal(ipq.S.cpu(), S) and ipq.effective_bits == pytest.approx(2.25)
+    cent1, cent2, bnd1 = t(c["cent_d128_b1"]), t(c["cent_d128_b2"]), t(c["bnd_d128_b1"])
+    m, s, n = ipq.compress(x[:64].to(DEV))                      # uncalibrated: 1-bit codes everywhere
+    assert m.shape == s.shape == (64, 128) and int(s.max()) <= 1
+    assert_codes(x[:64], Pi, bnd1, m, t(g["ip_codes_uncal"]), "mixed ip uncalibrated codes")
+    agree = m.cpu() == t(g["ip_codes_uncal"])
+    n_bad, n_all, dist = code_ties(x[:64], Pi, None, torch.where(agree, s.cpu(), t(g["ip_signs_uncal"])),
+                                   t(g["ip_signs_uncal"]), kind="sign", centroids=cent1,
+                                   codes_for_resid=t(g["ip_codes_uncal"]))
+    assert n_bad <= 2 and dist < TIE_TOL
+    ipq.calibrate(x[:1024].to(DEV))
+    assert ipq.mse_quantizer._outlier_indices.cpu().tolist() == g["ip_channels"].tolist()
+    m, s, n = ipq.compress(xs.to(DEV))
+    want_m, want_s = t(g["ip_codes"]), t(g["ip_signs"])
+    imask = ipq.mse_quantizer._outlier_mask.cpu()
+    assert_codes(xs, Pi, t(c["bnd_d128_b2"]), torch.where(imask, m.cpu(), want_m), want_m, "mixed ip outlier ch")
+    assert_codes(xs, Pi, bnd1, torch.where(~imask, m.cpu(), want_m), want_m, "mixed ip regular ch")
+    assert ulp_diff(n, t(g["ip_norms"])) <= 2
+    # sign bits where the codes agree; a differing sign must have a residual within rounding of zero
+    hat = torch.where(imask, cent2[want_m.long().clamp(max=3)], cent1[want_m.long().clamp(max=1)])
+    x64 = xs.double()
+    rot = (x64 / x64.norm(dim=-1, keepdim=True).clamp(min=1e-8)) @ Pi.double().T
+    bad = (s.cpu() != want_s) & (m.cpu() == want_m)
+    n_bad = int(bad.sum())
+    dist = float((rot - hat.double())[bad].abs().max()) if n_bad else 0.0
+    print(f"[ties] mixed ip sign bits: {n_bad} of {bad.numel()}, max |residual| {dist:.3e}")
+    assert n_bad <= 4 and dist < TIE_TOL
 
 
 def test_tcgen05_rotation_edge_shapes(golden, monkeypatch):
@@ -428,6 +456,28 @@ def test_engine_cases_multiblock_causal_widths(golden):
         assert eng.total_tokens == 0 and eng.num_blocks == 0
 
 
+def test_fused_attention_entry_point_honours_total_kv_tokens():
+    """Causal rows of the functional entry point sit at total_kv_tokens - Q + i (reference
+    triton_kernels/attention.py:119-123): equal to, below and above the number of stored tokens."""
+    B, H, S, Qn, D = 1, 2, 50, 6, 64
+    gq = torch.Generator().manual_seed(12)
+    K, V, Q = (torch.randn(B, H, n, D, generator=gq) for n in (S, S, Qn))
+    eng = qk.QuashKVEngine(D, 3, 3, seed=42)
+    kq, vq = eng.key_quantizer, eng.value_quantizer
+    Pi, Sg, kc, vc = kq.mse_quantizer.Pi, kq.S, kq.mse_quantizer.codebook.centroids, vq.codebook.centroids
+    mse, sg, kn = orc.compress_ip(K, Pi, kq.mse_quantizer.codebook.boundaries, kc, Sg)
+    vi, vn = orc.compress_mse(V, Pi, vq.codebook.boundaries)
+    block = CompressedBlock(mse.to(DEV), sg.to(DEV), kn.to(DEV), vi.to(DEV), vn.to(DEV), S)
+    args = [x.to(DEV) for x in (Pi, kc, vc, Sg)]
+    for total in (0, S, S - 7, S + 2, S + 40):
+        got = fused_quantized_attention(Q.to(DEV), [block], *args, kq.qjl_scale, causal=True, total_kv_tokens=total)
+        want = orc.attention(Q, mse, sg, kn, vi, vn, Pi, kc, vc, Sg, kq.qjl_scale, causal=True,
+                             total_tokens=total if total else S)
+        assert rel_l2(got, want) < 1e-5, total
+    with pytest.raises(ValueError, match="before position 0"):
+        fused_quantized_attention(Q.to(DEV), [block], *args, kq.qjl_scale, causal=True, total_kv_tokens=3)
+
+
 def _outlier_kv(B, H, S, D, seed, dtype):
     gk = torch.Generator().manual_seed(seed)
     K = torch.randn(B, H, S, D, generator=gk)
@@ -468,18 +518,28 @@ def test_decode_gqa_bf16_vs_oracle(golden, S, appends):
 @pytest.mark.parametrize("G,q_len,causal", [(4, 1, False), (8, 1, False), (4, 2, True), (1, 8, True), (2, 3, False),
                                             (4, 37, True), (2, 16, False), (1, 200, True), (3, 5, True)])
 def test_tensor_core_decode_path_vs_generic_and_oracle(G, q_len, causal, monkeypatch):
-    """head_dim 128 with 3/3 bits takes the tensor-core kernel, eight query rows of a KV head per CTA
-    (one tile for decode, many for prefill, a last partial tile, tiles that straddle two query
-    heads); it must agree with the oracle and with the generic kernel on the same cache (ragged
-    length, so the last tile and the last split are partial; causal rows see different lengths)."""
+    """head_dim 128 with 3/3 bits takes the tensor-core kernel over tile records, eight query rows of a KV head
+    per CTA (one tile for decode, many for prefill, a last partial tile, tiles that straddle two query
+    heads); it must agree with the oracle, with the tensor-core kernel over row-major planes and with the
+    generic kernel on the same tokens (ragged length, so the last tile and the last split are partial;
+    causal rows see different lengths)."""
     B, Hkv, S, D = 2, 3, 1000 + 13, 128
     K, V = _outlier_kv(B, Hkv, S, D, 5, torch.float32)
     eng = qk.QuashKVEngine(D, 3, 3, seed=42, pack_storage=True)
+    assert eng._tiled
     eng.append(K.to(DEV), V.to(DEV))
     Q = torch.randn(B, Hkv * G, q_len, D, generator=torch.Generator().manual_seed(9))
     fast = eng.attention(Q.to(DEV), causal=causal)
+    monkeypatch.setenv("QUASHKV_B200_ROW_STORAGE", "1")
+    rows = qk.QuashKVEngine(D, 3, 3, seed=42, pack_storage=True)
+    monkeypatch.delenv("QUASHKV_B200_ROW_STORAGE")
+    assert not rows._tiled
+    rows.append(K.to(DEV), V.to(DEV))
+    for name, plane in eng.row_planes().items():          # the records hold exactly the rows of the planes
+        assert torch.equal(plane, rows.row_planes()[name].reshape(plane.shape)), name
+    mid = rows.attention(Q.to(DEV), causal=causal)
     monkeypatch.setenv("QUASHKV_B200_GENERIC_ATTENTION", "1")
-    slow = eng.attention(Q.to(DEV), causal=causal)
+    slow = rows.attention(Q.to(DEV), causal=causal)
     monkeypatch.delenv("QUASHKV_B200_GENERIC_ATTENTION")
     kq, vq = eng.key_quantizer, eng.value_quantizer
     Pi, Sg, kc = kq.mse_quantizer.Pi, kq.S, kq.mse_quantizer.codebook.centroids
@@ -490,9 +550,48 @@ def test_tensor_core_decode_path_vs_generic_and_oracle(G, q_len, causal, monkeyp
     want = torch.empty(B, Hkv * G, q_len, D)
     for g in range(G):
         want[:, g::G] = orc.attention(Q[:, g::G], *planes, causal=causal, total_tokens=S)
-    e_fast, e_slow = rel_l2(fast, want), rel_l2(slow, want)
-    print(f"[parity] G={G} q_len={q_len} causal={causal}: tensor-core rel-L2 {e_fast:.3e}, generic {e_slow:.3e}")
-    assert e_slow < 1e-5 and e_fast < FP32_TOL
+    e_fast, e_mid, e_slow = rel_l2(fast, want), rel_l2(mid, want), rel_l2(slow, want)
+    print(f"[parity] G={G} q_len={q_len} causal={causal}: tile records rel-L2 {e_fast:.3e}, row-major tensor-core "
+          f"{e_mid:.3e}, generic {e_slow:.3e}")
+    assert e_slow < 1e-5 and e_mid < FP32_TOL and e_fast < FP32_TOL
+    assert _lib.lib().qkv_tensor_core_timeouts() == 0
+
+
+def test_tile_records_match_the_format_definition_and_round_trip():
+    """qkv_tile_rows against a numpy statement of the record format, then qkv_untile_rows back to the very
+    bytes; scattered slots (a paged pool's shape), dropped rows, and single tokens added to existing records."""
+    g = torch.Generator().manual_seed(31)
+    n = 16 * 37
+    kc = torch.randint(0, 256, (n, 32), dtype=torch.uint8, generator=g)
+    ks = torch.randint(0, 256, (n, 16), dtype=torch.uint8, generator=g)
+    vc = torch.randint(0, 256, (n, 48), dtype=torch.uint8, generator=g)
+    kn, vn = torch.rand(n, generator=g) + 0.5, torch.rand(n, generator=g) + 0.5
+    want = tile_records_reference(kc.numpy(), ks.numpy(), kn.numpy(), vc.numpy(), vn.numpy())
+    dev = [x.to(DEV) for x in (kc, ks, kn, vc, vn)]
+    rec = torch.full((37, ops.TILE_BYTES), 0xEE, dtype=torch.uint8, device=DEV)
+    ops.tile_rows(*dev, rec, n, 0, 0, None)
+    assert np.array_equal(rec.cpu().numpy(), want), "records differ from the format definition"
+    back = ops.untile_rows(rec, n, n, 0, 0, None)
+    for a, b in zip(back, (kc, ks, kn, vc, vn)):
+        assert torch.equal(a.cpu(), b)
+    # token by token, in a random order, into a second set of records: every token owns its own bytes
+    rec2 = torch.zeros_like(rec)
+    order = torch.randperm(n, generator=g)
+    for lo in range(0, n, 97):
+        idx = order[lo:lo + 97]
+        ops.tile_rows(*[x[idx.to(DEV)].contiguous() for x in dev], rec2, 1, 0, 0, idx.to(DEV))
+    assert torch.equal(rec2, rec)
+    # a negative slot drops its row; segment mapping (two segments of capacity 320, appended at offset 7)
+    rec3 = torch.zeros((2 * 20, ops.TILE_BYTES), dtype=torch.uint8, device=DEV)
+    ops.tile_rows(*[x[:200].contiguous() for x in dev], rec3, 100, 320, 7, None)
+    got = ops.untile_rows(rec3, 200, 100, 320, 7, None)
+    for a, b in zip(got, (kc, ks, kn, vc, vn)):
+        assert torch.equal(a.cpu(), b[:200])
+    slots = torch.tensor([5, -1, 6], dtype=torch.int64, device=DEV)
+    rec4 = torch.zeros((1, ops.TILE_BYTES), dtype=torch.uint8, device=DEV)
+    ops.tile_rows(*[x[:3].contiguous() for x in dev], rec4, 1, 0, 0, slots)
+    got = ops.untile_rows(rec4, 2, 1, 0, 0, torch.tensor([5, 6], dtype=torch.int64, device=DEV))
+    assert torch.equal(got[3].cpu(), vc[[0, 2]]) and torch.equal(got[0].cpu(), kc[[0, 2]])
 
 
 def test_prefill_causal_long_vs_oracle():
@@ -526,14 +625,7 @@ def test_full_size_decode_sampled_heads():
         K, V = _outlier_kv(1, Hkv, S, D, 2 + 31 * b, torch.bfloat16)
         if b in (0, 17, 31):
             keep[b] = (K, V)
-        rows = _lib.Rows(S, eng._capacity, 0)
-        kq, vq = eng.key_quantizer, eng.value_quantizer
-        Pi, kb, kc, Sg = kq._on(torch.device(DEV, 0))
-        _, vb, _ = vq._on(torch.device(DEV, 0))
-        p = eng._planes
-        sl = slice(b * Hkv, (b + 1) * Hkv)
-        ops.append_kv(K.to(DEV), V.to(DEV), Pi, kb, kc, Sg, 2, vb, 3, p["k_codes"][sl], p["k_signs"][sl],
-                      p["k_norms"][sl], p["v_codes"][sl], p["v_norms"][sl], 0)
+        eng._write(K.to(DEV), V.to(DEV), b * Hkv, 0)
     eng._block_lens, eng._total_tokens = [S], S
     assert eng.actual_memory_bytes() == 872415232
     Q = torch.randn(B, Hkv * G, 1, D, generator=torch.Generator().manual_seed(1000)).to(torch.bfloat16)
@@ -746,11 +838,25 @@ def test_hf_cache_update_matches_reference(golden):
     assert torch.equal(k_again, fk) and torch.equal(v_again, fv)
     assert cache.compression_stats()["tokens_per_layer"] == [0, 10]
     # the fused route over the same cache agrees with attention over the returned tensors
-    q = torch.randn(2, 8, 1, 64, device=DEV)
-    fused = cache.attention(q, 1)
-    assert fused.shape == (2, 8, 1, 64) and torch.isfinite(fused).all()
+    q = torch.randn(2, 8, 1, 64, generator=torch.Generator().manual_seed(4))
+    fused = cache.attention(q.to(DEV), 1)
+    eng = cache.engines[1]
+    kq, vq = eng.key_quantizer, eng.value_quantizer
+    Pi, Sg = kq.mse_quantizer.Pi.cpu(), kq.S.cpu()
+    kc, kb = kq.mse_quantizer.codebook.centroids.cpu(), kq.mse_quantizer.codebook.boundaries.cpu()
+    K, V = torch.cat([t(g["k1"]), t(g["k2"])], dim=2), torch.cat([t(g["v1"]), t(g["v2"])], dim=2)
+    mse, sg, kn = orc.compress_ip(K, Pi, kb, kc, Sg)
+    vi, vn = orc.compress_mse(V, Pi, vq.codebook.boundaries.cpu())
+    want = orc.attention_gqa(q, mse, sg, kn, vi, vn, Pi, kc, vq.codebook.centroids.cpu(), Sg, kq.qjl_scale,
+                             n_kv_heads=4)
+    err = rel_l2(fused, want)
+    print(f"[parity] HF-style cache, fused decode route vs oracle: rel-L2 {err:.3e}")
+    assert fused.shape == (2, 8, 1, 64) and err < FP32_TOL
     cache.reset()
     assert cache.get_seq_length(1) == 0
+    # an emptied cache takes another batch size next (reference engine.py:174-177 simply drops its blocks)
+    fk, fv = cache.update(k1[:1], v1[:1], 1)
+    assert fk.shape == (1, 4, 9, 64) and cache.get_seq_length(1) == 9
 
 
 # ---------------------------------------------------------------------------------------------
@@ -817,16 +923,19 @@ def _paged_case(D, kbits, vbits, block_size, lens, Hkv=2, seed=7):
     return pool, K, V
 
 
-@pytest.mark.parametrize("D,kbits,vbits,block_size,q_len,causal,generic", [
-    (128, 3, 3, 16, 1, False, False),      # tensor-core kernel, one page per tile
-    (128, 3, 3, 32, 3, True, False),       # tensor-core kernel, two tiles per page, causal rows
-    (128, 3, 3, 16, 1, False, True),       # generic kernel on the same pool
-    (128, 3, 3, 8, 2, True, False),        # pages smaller than a tile: generic kernel
-    (64, 4, 2, 16, 1, False, False),       # other widths and head size: generic kernel
+@pytest.mark.parametrize("D,kbits,vbits,block_size,q_len,causal,mode", [
+    (128, 3, 3, 16, 1, False, "records"),    # tensor-core kernel over tile records, one record per page
+    (128, 3, 3, 32, 3, True, "records"),     # two records per page, causal rows
+    (128, 3, 3, 16, 1, False, "rows"),       # row-major pool: tensor-core kernel over planes
+    (128, 3, 3, 32, 2, True, "generic"),     # row-major pool, generic kernel
+    (128, 3, 3, 8, 2, True, "records"),      # pages smaller than a tile: row-major pool, generic kernel
+    (64, 4, 2, 16, 1, False, "records"),     # other widths and head size: generic kernel
 ])
-def test_paged_cache_matches_contiguous_engine_and_oracle(D, kbits, vbits, block_size, q_len, causal, generic,
+def test_paged_cache_matches_contiguous_engine_and_oracle(D, kbits, vbits, block_size, q_len, causal, mode,
                                                           monkeypatch):
-    if generic:
+    if mode != "records":            # row-major pool and engine
+        monkeypatch.setenv("QUASHKV_B200_ROW_STORAGE", "1")
+    if mode == "generic":
         monkeypatch.setenv("QUASHKV_B200_GENERIC_ATTENTION", "1")
     lens = [700, 37, 130, 16, 3]
     Hkv, G = 2, 4
@@ -849,10 +958,10 @@ def test_paged_cache_matches_contiguous_engine_and_oracle(D, kbits, vbits, block
         eng.append(K[i].to(DEV), V[i].to(DEV))
         rows = (table[i, torch.arange(n, device=DEV) // block_size].long()[None, :] * Hkv
                 + torch.arange(Hkv, device=DEV)[:, None]) * block_size + torch.arange(n, device=DEV)[None, :] % block_size
-        for name, plane in pool.planes.items():
-            flat = plane.reshape(plane.shape[0] * Hkv * block_size, -1)
-            assert torch.equal(flat[rows.reshape(-1)].reshape(Hkv, n, -1),
-                               eng._planes[name][:, :n].reshape(Hkv, n, -1)), f"pool rows of {name}, sequence {i}"
+        eng_rows = eng.row_planes()
+        for name, plane in pool.rows_of(i).items():
+            assert torch.equal(plane.reshape(Hkv, n, -1), eng_rows[name].reshape(Hkv, n, -1)), \
+                f"pool rows of {name}, sequence {i}"
         if causal and q_len > n:
             continue                   # fewer tokens than query rows: the contiguous entry point refuses that
         want_eng = eng.attention(Q[i:i + 1].to(DEV), causal=causal)

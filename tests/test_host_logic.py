@@ -181,3 +181,72 @@ def test_index_file_checks_without_gpu(tmp_path):
                 "norms": torch.zeros(4)}, tmp_path / "bad.pt")
     with pytest.raises(ValueError, match="plane shapes do not match"):
         qk.QuashIndex.load(tmp_path / "bad.pt", device="cpu")
+
+
+def test_tile_record_format_decodes_to_the_expected_fragments(tmp_path):
+    """The record layout, the tiling arithmetic and the register-level decode share one header; a small host
+    program walks all 32 lanes of a random record and checks every fragment element (no GPU)."""
+    import shutil
+    import subprocess
+    gxx = shutil.which("g++")
+    if gxx is None:
+        pytest.skip("no host C++ compiler")
+    here = os.path.dirname(os.path.abspath(__file__))
+    exe = tmp_path / "tile_format_check"
+    subprocess.run([gxx, "-O1", "-std=c++17", "-o", str(exe), os.path.join(here, "tile_format_check.cpp")], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0 and "tile emulation OK" in out.stdout, out.stdout + out.stderr
+
+
+def test_tile_entry_points_refuse_bad_arguments_without_launching():
+    L = _lib.lib()
+    one, rec = ctypes.c_void_p(16), ctypes.c_void_p(256)
+    rows = _lib.Rows(1, 0, 0)
+    assert L.qkv_tile_rows(one, one, one, one, one, 0, rec, rows, None, None) == 0        # nothing to do
+    assert L.qkv_tile_rows(None, one, one, one, one, 4, rec, rows, None, None) == -1
+    assert L.qkv_tile_rows(one, one, one, one, one, 4, ctypes.c_void_p(24), rows, None, None) == -5   # records unaligned
+    assert L.qkv_untile_rows(rec, _lib.Rows(0, 0, 0), None, 4, one, one, one, one, one, None) == -8
+    cache = _lib.TiledCache(256, 64, None, None, 0, 0)
+    args = (one, 0, cache, 1, 4, 1, 1, 64)
+    tail = (one, one, one, one, 0.1, 0.1, 0, one, rec, 1 << 20, None)
+    assert L.qkv_attention_tiled(*args, 64, 3, 3, *tail) == -3          # records exist for head_dim 128 at 3/3 bits only
+    assert L.qkv_attention_tiled(*args, 128, 4, 3, *tail) == -3
+    odd = _lib.TiledCache(256, 72, None, None, 0, 0)
+    assert L.qkv_attention_tiled(one, 0, odd, 1, 4, 1, 1, 64, 128, 3, 3, *tail) == -8   # capacity not whole tiles
+    assert L.qkv_attention_tiled(one, 0, _lib.TiledCache(None, 64, None, None, 0, 0), 1, 4, 1, 1, 64, 128, 3, 3, *tail) == -1
+
+
+def test_engine_storage_choice_and_reset_shapes_without_gpu(monkeypatch):
+    """Tile records are chosen for head_dim 128 at 3/3 bits, row-major planes otherwise or on request; clear()
+    keeps nothing that pins the next sequence to the old (batch, heads)."""
+    assert qk.QuashKVEngine(128, 3, 3)._tiled and not qk.QuashKVEngine(64, 3, 3)._tiled
+    assert not qk.QuashKVEngine(128, 4, 3)._tiled and not qk.QuashKVEngine(128, 3, 2)._tiled
+    monkeypatch.setenv("QUASHKV_B200_ROW_STORAGE", "1")
+    assert not qk.QuashKVEngine(128, 3, 3)._tiled
+    monkeypatch.delenv("QUASHKV_B200_ROW_STORAGE")
+    eng = qk.QuashKVEngine(128, 3, 3)
+    eng.reserve(2, 3, 100, "cpu")
+    assert eng._planes["records"].shape == (6, 8, 1664) and eng._capacity == 128
+    eng.reserve(2, 3, 300, "cpu")
+    assert eng._planes["records"].shape == (6, 20, 1664)
+
+
+def test_device_constants_follow_replaced_and_modified_tensors():
+    """The per-device copies of a quantizer's constants are tied to the source tensor object and its version:
+    a replaced or modified mask / rotation is copied again, never served stale."""
+    from quashkv_b200.quantizer import _DeviceConstants
+    c = _DeviceConstants()
+    meta = torch.device("meta")
+    a = torch.zeros(4)
+    first = c.get("m", a, meta)
+    assert c.get("m", a, meta) is first
+    a.add_(1)                                   # modified in place: version changes
+    second = c.get("m", a, meta)
+    assert second is not first
+    b = torch.zeros(4)                          # another tensor under the same name
+    assert c.get("m", b, meta) is not second
+    assert len(c._copies) == 1
+    q = qk.MixedPrecisionMSEQuantizer(64, 3, 2, 8)
+    q.set_outlier_channels(torch.tensor([1, 5, 9]))
+    assert q._n_marked == 3 and q._mask_u8.tolist().count(1) == 3 and not q._consts._copies
+    assert qk.MSEQuantizer(64, 3).Pi.is_contiguous()

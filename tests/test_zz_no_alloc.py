@@ -16,19 +16,34 @@ import pytest
 import torch
 
 import quashkv_b200 as qk
-from quashkv_b200 import _lib
+from quashkv_b200 import _lib, ops
 from helpers import rel_l2
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def _call(L, eng, q, causal=False):
+def _planes(eng):
+    """The cache as the five row-major packed planes the entry point reads, over the whole capacity (exact
+    copies when the engine stores tile records)."""
+    return eng.row_planes(0, eng._capacity)
+
+
+def _workspace_entry_point(eng, p, q, causal=False):
+    """The ordinary entry point (qkv_attention, workspace from the caller) on the same planes."""
+    kq, vq = eng.key_quantizer, eng.value_quantizer
+    Pi, _, kc, S = kq._on(q.device)
+    _, _, vc = vq._on(q.device)
+    return ops.attention(q, p["k_codes"], p["k_signs"], p["k_norms"], p["v_codes"], p["v_norms"], eng.total_tokens,
+                         eng._shape[1], eng.key_bits, eng.value_bits, Pi, kc, vc, S, kq.qjl_scale,
+                         1.0 / q.shape[-1] ** 0.5, causal)
+
+
+def _call(L, eng, p, q, causal=False):
     kq, vq = eng.key_quantizer, eng.value_quantizer
     dev = q.device
-    Pi, _, kc, S = (t.contiguous() for t in kq._on(dev))   # the QR factor may be column-major
+    Pi, _, kc, S = kq._on(dev)
     _, _, vc = vq._on(dev)
-    p = eng._planes
     B, Hq, Q, D = q.shape
     cache = _lib.Cache(p["k_codes"].data_ptr(), p["k_signs"].data_ptr(), p["k_norms"].data_ptr(),
                        p["v_codes"].data_ptr(), p["v_norms"].data_ptr(), eng._capacity)
@@ -48,10 +63,12 @@ def test_static_scratch_attention_matches_workspace_entry_point(D, bits):
     g = torch.Generator().manual_seed(21)
     eng = qk.QuashKVEngine(D, bits, bits, seed=42, pack_storage=True)
     eng.append(torch.randn(2, 2, 777, D, generator=g).to(DEV), torch.randn(2, 2, 777, D, generator=g).to(DEV))
+    p = _planes(eng)
     for trial in range(2):      # two calls in a row share the scratch array
         q = torch.randn(2, 8, 1, D, generator=g).to(DEV)
-        want = eng.attention(q)
-        rc, got = _call(L, eng, q)
+        want = _workspace_entry_point(eng, p, q)
+        assert rel_l2(want, eng.attention(q)) < 1e-3       # ... which agrees with the engine's own route
+        rc, got = _call(L, eng, p, q)
         torch.cuda.synchronize()
         assert rc == 0, _lib.lib().qkv_strerror(rc)
         assert torch.isfinite(got).all()
@@ -59,8 +76,9 @@ def test_static_scratch_attention_matches_workspace_entry_point(D, bits):
     # a longer cache between calls changes the split layout inside the same array
     eng.append(torch.randn(2, 2, 5000, D, generator=g).to(DEV), torch.randn(2, 2, 5000, D, generator=g).to(DEV))
     q = torch.randn(2, 8, 2, D, generator=g).to(DEV)
-    rc, got = _call(L, eng, q, causal=True)
-    assert rc == 0 and rel_l2(got, eng.attention(q, causal=True)) < 1e-6
+    p = _planes(eng)
+    rc, got = _call(L, eng, p, q, causal=True)
+    assert rc == 0 and rel_l2(got, _workspace_entry_point(eng, p, q, causal=True)) < 1e-6
 
 
 def test_static_scratch_refuses_shapes_beyond_the_array():
