@@ -4,7 +4,7 @@
 //
 // A warp owns 16-token tiles of its split.  One elected lane fetches a whole record (1664 bytes) with
 // ONE bulk copy into the warp's ring of four stages; an mbarrier per stage counts the bytes in, every
-// wait on it is bounded.  Each lane then reads its share with five vector loads, decodes it IN
+// wait on it is bounded.  Each lane then reads its share with four vector loads, decodes it IN
 // REGISTERS into m16n8k16 fragments (tile_decode.cuh: one PRMT per pair of codes, one LOP3 per pair of
 // sign bits) and feeds mma.sync:
 //   scores   tokens = M, queries = N, coordinates = K: 8 MMAs on the key codes, 8 on the sign bits
@@ -51,13 +51,12 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
 struct TileRegs {
   uint4 kc;       // key codes: token g words 0, 1; token g + 8 words 0, 1
   uint4 vm;       // value magnitudes, words m = 0..3
-  uint2 ks;       // key sign words of tokens g, g + 8
-  uint2 vs;       // value sign words of token pairs (2t, 2t+1), (2t+8, 2t+9)
+  uint4 sg;       // key sign words of tokens g, g + 8; value sign words of token pairs (2t, 2t+1), (2t+8, 2t+9)
   float4 nrm;     // key norms of tokens g, g + 8; value norms of tokens g, g + 8
 };
 
-template <bool PAGED, bool LO4, int SEL>
-__global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a) {
+template <bool PAGED, bool LO4, int MINB>
+__global__ void __launch_bounds__(kWarps * 32, MINB) attend_tiled_kernel(AttnArgs a) {
   constexpr int D = 128;
   constexpr int kTile = tile::kTokens;
   __shared__ float q_s[8][2 * D];                    // [query row][q_rot*scale | sign weights]
@@ -68,7 +67,7 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
   float (*red)[8][D + 2] = reinterpret_cast<float (*)[8][D + 2]>(pool);   // [warp][query][max, sum, acc]
   __shared__ __align__(8) uint64_t bars[kWarps][kRing];
   __shared__ float wsum[8];                          // sum of the sign weights per query column
-  __shared__ uint2 bop[16][32];                      // B operands per k-step and lane: 8 key-code steps, 8 sign steps
+  __shared__ uint4 bop[8][32];                       // B operands of two k-steps per lane: 8 key-code steps, then 8 sign steps
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gid = lane >> 2, tig = lane & 3;
@@ -120,7 +119,7 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncwarp();
-  auto issue = [&](int it) {                          // called with it = 0, 1, 2, ... in order
+  auto issue = [&](int it, int slot) {                // called with it = 0, 1, 2, ... in order; slot = it % kRing
     if (it < n_it && lane == 0) {
       const uint8_t* src;
       if (PAGED) {
@@ -130,14 +129,14 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
       } else {
         src = rec0 + static_cast<int64_t>(it) * (kWarps * tile::kBytes);
       }
-      uint64_t* bs = bar + (it % kRing);
+      uint64_t* bs = bar + slot;
       mbar_expect_tx(bs, tile::kBytes);
-      bulk_load(ring + (it % kRing) * tile::kBytes, src, tile::kBytes, bs);
+      bulk_load(ring + slot * tile::kBytes, src, tile::kBytes, bs);
     }
     if (PAGED) blk_next = block_of(it + 1);
   };
 #pragma unroll
-  for (int i = 0; i < kRing; ++i) issue(i);
+  for (int i = 0; i < kRing; ++i) issue(i, i);
 
   // Everything above read only the records and the block table, which no kernel of this call writes: when
   // the launch allows it (programmatic dependent launch), this grid starts while the query-rotation kernel is
@@ -191,7 +190,7 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
         v[e] = q[c0 + 4 * e] * qf;
         if (resid) v[e] -= __half2float(__float2half_rn(v[e]));
       }
-      bop[s][lane] = make_uint2(pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
+      reinterpret_cast<uint2*>(&bop[s >> 1][lane])[s & 1] = make_uint2(pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
       uint32_t wq[2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {           // pairs t = 2s, 2s+1 of this lane's 32 coordinates
@@ -199,7 +198,7 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
         const float fs = resid ? 0.f : 2.f * kLog2e / sign_v1(sign_pos(t));
         wq[h] = pack_half2(w[j] * fs, w[j + 16] * fs);
       }
-      bop[8 + s][lane] = make_uint2(wq[0], wq[1]);
+      reinterpret_cast<uint2*>(&bop[4 + (s >> 1)][lane])[s & 1] = make_uint2(wq[0], wq[1]);
     }
   }
   __syncthreads();
@@ -225,40 +224,43 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
   float m[2] = {kNone, kNone}, l[2] = {0.f, 0.f};
   const float ci0 = -wsum[2 * tig], ci1 = -wsum[2 * tig + 1];   // accumulator start: -sum of sign weights
 
-  auto process = [&](const TileRegs& cur, int it) {
-    const int rel = first_rel + it * kStep;
+  auto process = [&](const TileRegs& cur, int rel) {
     const bool masked = a.causal || rel + kTile > n_valid;      // warp-uniform
     // ---- scores: 8 MMAs on key codes, 8 on sign bits --------------------------------------------
     float c[4] = {ci0, ci1, ci0, ci1};
     {
       uint32_t af[4];
-      uint2 bq;
-#define QKV_KEY_STEP(W0, W1, WORD, F)                                   \
-  tile::key_fragment<F, SEL>(W0, W1, kt_a, kt_b, af);                        \
-  bq = bop[(WORD) * 4 + (F)][lane];                                     \
-  mma16816(c, af, bq.x, bq.y);
-      QKV_KEY_STEP(cur.kc.x, cur.kc.z, 0, 0) QKV_KEY_STEP(cur.kc.x, cur.kc.z, 0, 1)
-      QKV_KEY_STEP(cur.kc.x, cur.kc.z, 0, 2) QKV_KEY_STEP(cur.kc.x, cur.kc.z, 0, 3)
-      QKV_KEY_STEP(cur.kc.y, cur.kc.w, 1, 0) QKV_KEY_STEP(cur.kc.y, cur.kc.w, 1, 1)
-      QKV_KEY_STEP(cur.kc.y, cur.kc.w, 1, 2) QKV_KEY_STEP(cur.kc.y, cur.kc.w, 1, 3)
-#undef QKV_KEY_STEP
+      uint4 bq;
+#define QKV_KEY_STEPS(W0, W1, WORD, F)                                  \
+  bq = bop[(WORD) * 2 + (F) / 2][lane];                                 \
+  tile::key_fragment<F>(W0, W1, kt_a, kt_b, af);                        \
+  mma16816(c, af, bq.x, bq.y);                                          \
+  tile::key_fragment<F + 1>(W0, W1, kt_a, kt_b, af);                    \
+  mma16816(c, af, bq.z, bq.w);
+      QKV_KEY_STEPS(cur.kc.x, cur.kc.z, 0, 0) QKV_KEY_STEPS(cur.kc.x, cur.kc.z, 0, 2)
+      QKV_KEY_STEPS(cur.kc.y, cur.kc.w, 1, 0) QKV_KEY_STEPS(cur.kc.y, cur.kc.w, 1, 2)
+#undef QKV_KEY_STEPS
     }
     {
-      const uint32_t cp0[4] = {cur.ks.x, cur.ks.x << 7, cur.ks.x >> 1, cur.ks.x << 13};
-      const uint32_t cp1[4] = {cur.ks.y, cur.ks.y << 7, cur.ks.y >> 1, cur.ks.y << 13};
+      const uint32_t cp0[4] = {cur.sg.x, cur.sg.x << 7, cur.sg.x >> 1, cur.sg.x << 13};
+      const uint32_t cp1[4] = {cur.sg.y, cur.sg.y << 7, cur.sg.y >> 1, cur.sg.y << 13};
 #pragma unroll
-      for (int s = 0; s < 8; ++s) {
-        uint32_t af[4];
+      for (int s2 = 0; s2 < 4; ++s2) {
+        const uint4 bw = bop[4 + s2][lane];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int t = 2 * s + h;
-          const int cpy = t < 7 ? 0 : (t < 14 ? 1 : t - 12);
-          const uint32_t mask = 0x00010001u << sign_pos(t);
-          af[2 * h] = cp0[cpy] & mask;
-          af[2 * h + 1] = cp1[cpy] & mask;
+        for (int u = 0; u < 2; ++u) {
+          const int s = 2 * s2 + u;
+          uint32_t af[4];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int t = 2 * s + h;
+            const int cpy = t < 7 ? 0 : (t < 14 ? 1 : t - 12);
+            const uint32_t mask = 0x00010001u << sign_pos(t);
+            af[2 * h] = cp0[cpy] & mask;
+            af[2 * h + 1] = cp1[cpy] & mask;
+          }
+          mma16816(c, af, u ? bw.z : bw.x, u ? bw.w : bw.y);
         }
-        const uint2 bw = bop[8 + s][lane];
-        mma16816(c, af, bw.x, bw.y);
       }
     }
     if (LO4) {                      // column n + 4 holds the residual part of column n: add the two
@@ -267,25 +269,31 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
     }
 
     // ---- online softmax on the accumulator fragment (log2 domain) ------------------------------
-    float sc[4] = {c[0] * cur.nrm.x, c[1] * cur.nrm.x, c[2] * cur.nrm.y, c[3] * cur.nrm.y};
+    // t = score - m, in one multiply-add per entry.  m is a reference exponent, not the exact running maximum:
+    // it is raised (to the exact maximum of the tile, over the eight token lanes of a query column) only when a
+    // score of this tile exceeds it by more than kSlack, so that most tiles need one vote instead of three
+    // shuffle rounds.  Weights stay below 2^kSlack, far inside fp16 once multiplied by a value norm, and the
+    // merge of the splits only needs l and the accumulators to be relative to the m that is written out.
+    constexpr float kSlack = 4.f;
+    const float kn0 = cur.nrm.x, kn1 = cur.nrm.y;
     float vn0 = cur.nrm.z, vn1 = cur.nrm.w;
+    float t[4] = {fmaf(c[0], kn0, -m[0]), fmaf(c[1], kn0, -m[1]), fmaf(c[2], kn1, -m[0]), fmaf(c[3], kn1, -m[1])};
     if (masked) {
       const int tokA = rel + gid, tokB = tokA + 8;
-      if (!(tokA < n_valid && tokA <= lim_rel[0])) sc[0] = -INFINITY;
-      if (!(tokA < n_valid && tokA <= lim_rel[1])) sc[1] = -INFINITY;
-      if (!(tokB < n_valid && tokB <= lim_rel[0])) sc[2] = -INFINITY;
-      if (!(tokB < n_valid && tokB <= lim_rel[1])) sc[3] = -INFINITY;
+      if (!(tokA < n_valid && tokA <= lim_rel[0])) t[0] = -INFINITY;
+      if (!(tokA < n_valid && tokA <= lim_rel[1])) t[1] = -INFINITY;
+      if (!(tokB < n_valid && tokB <= lim_rel[0])) t[2] = -INFINITY;
+      if (!(tokB < n_valid && tokB <= lim_rel[1])) t[3] = -INFINITY;
       if (tokA >= n_valid) vn0 = 0.f;         // rows past the end of the sequence hold no data
       if (tokB >= n_valid) vn1 = 0.f;
     }
-    // m is a reference exponent, not the exact running maximum: it is raised (to the exact maximum of the tile,
-    // over the eight token lanes of a query column) only when a score of this tile exceeds it by more than
-    // kSlack, so that most tiles need one vote instead of three shuffle rounds.  Weights stay below 2^kSlack,
-    // far inside fp16 once multiplied by a value norm, and the merge of the splits only needs l and the
-    // accumulators to be relative to the m that is written out.
-    constexpr float kSlack = 4.f;
-    float mx[2] = {fmaxf(sc[0], sc[2]), fmaxf(sc[1], sc[3])};
-    if (__any_sync(QKV_FULL_MASK, mx[0] > m[0] + kSlack || mx[1] > m[1] + kSlack)) {
+    if (__any_sync(QKV_FULL_MASK, fmaxf(fmaxf(t[0], t[2]), fmaxf(t[1], t[3])) > kSlack)) {
+      // (rare after the first tiles) exact scores again: against the start value of m, t has lost them
+      float sc[4] = {c[0] * kn0, c[1] * kn0, c[2] * kn1, c[3] * kn1};
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (t[e] == -INFINITY) sc[e] = -INFINITY;
+      float mx[2] = {fmaxf(sc[0], sc[2]), fmaxf(sc[1], sc[3])};
 #pragma unroll
       for (int o = 4; o < 32; o <<= 1) {
         mx[0] = fmaxf(mx[0], __shfl_xor_sync(QKV_FULL_MASK, mx[0], o));
@@ -302,9 +310,9 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
       for (int i = 0; i < 8; ++i) {
         O[i][0] *= al[0]; O[i][1] *= al[1]; O[i][2] *= al[0]; O[i][3] *= al[1];
       }
+      t[0] = sc[0] - m[0]; t[1] = sc[1] - m[1]; t[2] = sc[2] - m[0]; t[3] = sc[3] - m[1];
     }
-    const float p0 = ex2(sc[0] - m[0]), p1 = ex2(sc[1] - m[1]);   // masked scores are -inf: weight 0
-    const float p2 = ex2(sc[2] - m[0]), p3 = ex2(sc[3] - m[1]);
+    const float p0 = ex2(t[0]), p1 = ex2(t[1]), p2 = ex2(t[2]), p3 = ex2(t[3]);   // masked entries: weight 0
     l[0] += p0 + p2;
     l[1] += p1 + p3;
     // weights times value norm, transposed into the B layout (tokens as K, query = gid as N)
@@ -315,7 +323,7 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
     {
       uint32_t af[4];
 #define QKV_VAL_STEP(WORD, M, HALF)                                                  \
-  tile::value_fragment<M, HALF, SEL>(WORD, cur.vs.x, cur.vs.y, vt_a, vt_b, af);           \
+  tile::value_fragment<M, HALF>(WORD, cur.sg.z, cur.sg.w, vt_a, vt_b, af);           \
   mma16816(O[2 * (M) + (HALF)], af, pb0, pb1);
       QKV_VAL_STEP(cur.vm.x, 0, 0) QKV_VAL_STEP(cur.vm.x, 0, 1)
       QKV_VAL_STEP(cur.vm.y, 1, 0) QKV_VAL_STEP(cur.vm.y, 1, 1)
@@ -326,24 +334,25 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
   };
 
   int it_failed = -1;
-  for (int it = 0; it < n_it; ++it) {
-    const int slot = it % kRing;
-    if (!__all_sync(QKV_FULL_MASK, umma::mbar_wait(bar + slot, (it / kRing) & 1))) { it_failed = it; break; }
+  int slot = 0;
+  uint32_t parity = 0;
+  for (int it = 0, rel = first_rel; it < n_it; ++it, rel += kStep) {
+    if (!__all_sync(QKV_FULL_MASK, umma::mbar_wait(bar + slot, parity))) { it_failed = it; break; }
     const unsigned char* stage = ring + slot * tile::kBytes;
     TileRegs cur;
     cur.kc = *reinterpret_cast<const uint4*>(stage + tile::kOffKeyCodes + 16 * lane);
     cur.vm = *reinterpret_cast<const uint4*>(stage + tile::kOffValMags + 16 * lane);
-    cur.ks = *reinterpret_cast<const uint2*>(stage + tile::kOffKeySigns + 8 * lane);
-    cur.vs = *reinterpret_cast<const uint2*>(stage + tile::kOffValSigns + 8 * lane);
+    cur.sg = *reinterpret_cast<const uint4*>(stage + tile::kOffSigns + 16 * lane);
     cur.nrm = *reinterpret_cast<const float4*>(stage + tile::kOffNorms + 16 * gid);
-    process(cur, it);
+    process(cur, rel);
     // The slot is refilled only now.  A warp issues its instructions in order and an instruction issues only
     // once its source registers hold their values, so at this point every lane's loads from the slot have
     // returned (process() consumed all of them): the copy cannot overwrite bytes that are still to be read.
     // Issuing it straight after the loads, before their values are used, lost that guarantee: with records
     // coming from L2 and the load queue of the SM full, a copy was seen to land before a queued load.
     __syncwarp();
-    issue(it + kRing);
+    issue(it + kRing, slot);
+    if (++slot == kRing) { slot = 0; parity ^= 1u; }
   }
   if (it_failed >= 0) {
     // A copy never arrived (not seen in practice; a hardware fault would look like this).  Count it, give the
@@ -487,17 +496,17 @@ int launch_attend_tiled(const AttnArgs& a_in, cudaStream_t st) {
   const bool lo4 = a_in.G * a_in.q_len <= 4;      // spare query columns carry the fp16 residual of the queries
   const AttnArgs& a = a_in;
   cudaError_t err;
-  const char* es = getenv("QUASHKV_B200_TILED_SEL");
-  const int sel = es ? atoi(es) : 1;
+  const char* es = getenv("QUASHKV_B200_TILED_MINB");
+  const int minb = es ? atoi(es) : 4;
   if (a.block_table)
-    err = lo4 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<true, true, 1>, a)
-              : cudaLaunchKernelEx(&cfg, attend_tiled_kernel<true, false, 1>, a);
-  else if (sel == 0)
-    err = lo4 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, true, 0>, a)
-              : cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, false, 0>, a);
+    err = lo4 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<true, true, 4>, a)
+              : cudaLaunchKernelEx(&cfg, attend_tiled_kernel<true, false, 4>, a);
+  else if (minb == 3)
+    err = lo4 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, true, 3>, a)
+              : cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, false, 3>, a);
   else
-    err = lo4 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, true, 1>, a)
-              : cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, false, 1>, a);
+    err = lo4 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, true, 4>, a)
+              : cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, false, 4>, a);
   if (err != cudaSuccess) return QKV_ELAUNCH;
   return check_launch();
 }

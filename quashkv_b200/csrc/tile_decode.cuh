@@ -29,47 +29,25 @@ QKV_HD uint32_t prmt_hd(uint32_t a, uint32_t b, uint32_t sel) {
 #endif
 }
 
-QKV_HD uint32_t mulhi_hd(uint32_t a, uint32_t b) {
-#if defined(__CUDA_ARCH__)
-  return __umulhi(a, b);
-#else
-  return static_cast<uint32_t>((static_cast<uint64_t>(a) * b) >> 32);
-#endif
-}
-
 // Four 2-bit codes, one per byte of `w` at bits 2 f .. 2 f + 1, become two PRMT selectors: the table of
 // four fp16 values sits in two registers as (lo, hi) byte pairs, so selector byte 0x10 + 0x22 * code
-// picks a whole fp16.  `lo` selects for the codes of bytes 0 and 1, `hi` for bytes 2 and 3 (PRMT reads
-// the low 16 bits of a selector).  The right shifts are multiplications whose high word is kept, which
-// run on the multiply pipe instead of the logic pipe that the look-ups themselves occupy.
-template <int F, int SEL = 1>
+// picks a whole fp16: one multiply-add builds four selector bytes.  `lo` selects for the codes of bytes
+// 0 and 1, `hi` for bytes 2 and 3 (PRMT reads the low 16 bits of a selector).  (Right shifts written
+// as high-word multiplications, to move them off the logic pipe, measured 10 % slower.)
+template <int F>
 QKV_HD void selectors(uint32_t w, uint32_t& lo, uint32_t& hi) {
-  if (SEL == 0) {                 // plain form: shift, mask, replicate; the second selector by a 16-bit shift
-    const uint32_t y = (w >> (2 * F)) & 0x03030303u;
-    lo = y * 0x22u + 0x10101010u;
-    hi = lo >> 16;
-  } else if (F == 0) {
-    const uint32_t y = w & 0x03030303u;
-    lo = y * 0x22u + 0x10101010u;
-    hi = mulhi_hd(y, 0x22u << 16) + 0x1010u;
-  } else if (F == 3) {
-    const uint32_t y = w & 0xC0C0C0C0u;
-    lo = mulhi_hd(y, 0x22u << 26) + 0x10101010u;
-    hi = mulhi_hd(y, 0x22u << 10) + 0x1010u;
-  } else {
-    const uint32_t y = (w >> (2 * F)) & 0x03030303u;
-    lo = y * 0x22u + 0x10101010u;
-    hi = mulhi_hd(y, 0x22u << 16) + 0x1010u;
-  }
+  const uint32_t y = (F == 0 ? w : w >> (2 * F)) & 0x03030303u;
+  lo = y * 0x22u + 0x10101010u;
+  hi = lo >> 16;
 }
 
 // Key codes of one k-step.  w0 / w1: the same code word of the tokens in rows g and g + 8.  Step
 // (word, F) covers the lane's coordinates 16 word + {F, 4 + F | 8 + F, 12 + F} (k columns 2t, 2t+1 | 2t+8, 2t+9).
-template <int F, int SEL = 1>
+template <int F>
 QKV_HD void key_fragment(uint32_t w0, uint32_t w1, uint32_t tab_a, uint32_t tab_b, uint32_t (&af)[4]) {
   uint32_t l0, h0, l1, h1;
-  selectors<F, SEL>(w0, l0, h0);
-  selectors<F, SEL>(w1, l1, h1);
+  selectors<F>(w0, l0, h0);
+  selectors<F>(w1, l1, h1);
   af[0] = prmt_hd(tab_a, tab_b, l0);
   af[1] = prmt_hd(tab_a, tab_b, l1);
   af[2] = prmt_hd(tab_a, tab_b, h0);
@@ -79,14 +57,14 @@ QKV_HD void key_fragment(uint32_t w0, uint32_t w1, uint32_t tab_a, uint32_t tab_
 // Values of one M tile i = 2 m + HALF (coordinates 16 g + 2 i, + 1 as rows g, g + 8): magnitude word m,
 // fields 2 HALF (row g) and 2 HALF + 1 (row g + 8); sign words s0 (tokens 2t, 2t+1) and s1 (2t+8, 2t+9),
 // bit p = 4 m + field in each half.
-template <int M, int HALF, int SEL = 1>
+template <int M, int HALF>
 QKV_HD void value_fragment(uint32_t mag_word, uint32_t s0, uint32_t s1, uint32_t tab_a, uint32_t tab_b,
                            uint32_t (&af)[4]) {
   constexpr int F0 = 2 * HALF, F1 = 2 * HALF + 1;
   constexpr int P0 = 4 * M + F0, P1 = 4 * M + F1;
   uint32_t l0, h0, l1, h1;
-  selectors<F0, SEL>(mag_word, l0, h0);
-  selectors<F1, SEL>(mag_word, l1, h1);
+  selectors<F0>(mag_word, l0, h0);
+  selectors<F1>(mag_word, l1, h1);
   af[0] = prmt_hd(tab_a, tab_b, l0) ^ ((s0 << (15 - P0)) & 0x80008000u);
   af[1] = prmt_hd(tab_a, tab_b, l1) ^ ((s0 << (15 - P1)) & 0x80008000u);
   af[2] = prmt_hd(tab_a, tab_b, h0) ^ ((s1 << (15 - P0)) & 0x80008000u);

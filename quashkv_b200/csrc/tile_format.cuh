@@ -5,17 +5,18 @@
 // paged pool — in 1664 bytes, the same 104 bytes per token as the five row-major planes
 // (reference packing.py:22-94 rows of 32 + 16 + 48 bytes and two fp32 norms).  The bytes are arranged
 // in the order in which the lanes of a warp consume them as m16n8k16 fragments, so that a lane
-// fetches its share with five vector loads and the whole record arrives with one bulk copy.
+// fetches its share with four vector loads and the whole record arrives with one bulk copy.
 //
 // Lane L = 4 g + t (g = 0..7, t = 0..3):
 //   [   0,  512)  key codes     16 B per lane: tokens g and g+8, coordinates 32 t .. 32 t + 31 each
 //                               (bytes 8 t .. 8 t + 7 of the token's 32-byte 2-bit row, unchanged)
 //   [ 512, 1024)  value mags    16 B per lane: words m = 0..3; byte b of a word belongs to token
 //                               2 t + (b & 1) + 8 (b >> 1); its 2-bit field f to coordinate 16 g + 4 m + f
-//   [1024, 1280)  key signs      8 B per lane: tokens g and g+8, coordinates 32 t .. 32 t + 31
-//                               (bytes 4 t .. 4 t + 3 of the token's 16-byte sign row, unchanged)
-//   [1280, 1536)  value signs    8 B per lane: word h = 0, 1; its low half belongs to token 2 t + 8 h,
-//                               its high half to token 2 t + 1 + 8 h; bit p to coordinate 16 g + p
+//   [1024, 1536)  sign bits     16 B per lane:
+//                   key signs   8 B: tokens g and g+8, coordinates 32 t .. 32 t + 31 (bytes 4 t .. 4 t + 3
+//                               of the token's 16-byte sign row, unchanged)
+//                   value signs 8 B: word h = 0, 1; its low half belongs to token 2 t + 8 h, its high half
+//                               to token 2 t + 1 + 8 h; bit p to coordinate 16 g + p
 //   [1536, 1664)  norms         16 B per g: key norm of tokens g, g+8, value norm of tokens g, g+8
 //
 // Values are stored as sign and magnitude instead of the reference's 3-bit code u (0..7, ascending
@@ -41,20 +42,20 @@ namespace tile {
 
 constexpr int kTokens = 16;
 constexpr int kBytes = 1664;
-constexpr int kOffKeyCodes = 0, kOffValMags = 512, kOffKeySigns = 1024, kOffValSigns = 1280, kOffNorms = 1536;
+constexpr int kOffKeyCodes = 0, kOffValMags = 512, kOffSigns = 1024, kOffNorms = 1536;
 constexpr int kKeyRowBytes = 32, kSignRowBytes = 16, kValRowBytes = 48;
 
 // ---- where a token's bytes live ----------------------------------------------------------------------
 // key codes: 4-byte piece j (0..7) of token k's 32-byte row
 QKV_HD int key_code_offset(int k, int j) { return kOffKeyCodes + 16 * (4 * (k & 7) + (j >> 1)) + 8 * (k >> 3) + 4 * (j & 1); }
 // key signs: 4-byte piece t (0..3) of token k's 16-byte row
-QKV_HD int key_sign_offset(int k, int t) { return kOffKeySigns + 8 * (4 * (k & 7) + t) + 4 * (k >> 3); }
+QKV_HD int key_sign_offset(int k, int t) { return kOffSigns + 16 * (4 * (k & 7) + t) + 4 * (k >> 3); }
 // value magnitudes: byte of token k in word m of coordinate group g (coordinates 16 g + 4 m .. + 3)
 QKV_HD int val_mag_offset(int k, int g, int m) {
   return kOffValMags + 16 * (4 * g + ((k & 7) >> 1)) + 4 * m + (k & 1) + 2 * (k >> 3);
 }
 // value signs: 16-bit piece of token k for coordinate group g (bit p = coordinate 16 g + p)
-QKV_HD int val_sign_offset(int k, int g) { return kOffValSigns + 8 * (4 * g + ((k & 7) >> 1)) + 4 * (k >> 3) + 2 * (k & 1); }
+QKV_HD int val_sign_offset(int k, int g) { return kOffSigns + 16 * (4 * g + ((k & 7) >> 1)) + 8 + 4 * (k >> 3) + 2 * (k & 1); }
 QKV_HD int key_norm_offset(int k) { return kOffNorms + 16 * (k & 7) + 4 * (k >> 3); }
 QKV_HD int val_norm_offset(int k) { return kOffNorms + 16 * (k & 7) + 8 + 4 * (k >> 3); }
 

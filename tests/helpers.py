@@ -47,9 +47,8 @@ def tile_records_reference(k_codes, k_signs, k_norms, v_codes, v_norms):
 
     Lane L = 4 g + t.  [0,512) key codes: 16 B per lane = bytes 8t..8t+7 of tokens g and g+8.  [512,1024) value
     magnitudes: 16 B per lane = words m = 0..3, byte b of a word for token 2t + (b&1) + 8 (b>>1), 2-bit field f
-    for coordinate 16 g + 4 m + f.  [1024,1280) key signs: 8 B per lane = bytes 4t..4t+3 of tokens g, g+8.
-    [1280,1536) value signs: 8 B per lane = 16-bit pieces of tokens 2t, 2t+1, 2t+8, 2t+9, bit p for coordinate
-    16 g + p.  [1536,1664) per g: key norms of tokens g, g+8, value norms of tokens g, g+8.  A 3-bit value
+    for coordinate 16 g + 4 m + f.  [1024,1536) sign bits: 16 B per lane = bytes 4t..4t+3 of the key sign rows of
+    tokens g, g+8, then the 16-bit value-sign pieces of tokens 2t, 2t+1, 2t+8, 2t+9, bit p for coordinate 16 g + p.  [1536,1664) per g: key norms of tokens g, g+8, value norms of tokens g, g+8.  A 3-bit value
     code u is stored as negative = (u < 4) and magnitude index u - 4 (u >= 4) or 3 - u."""
     k_codes, k_signs, v_codes = (np.asarray(a, dtype=np.uint8) for a in (k_codes, k_signs, v_codes))
     k_norms, v_norms = np.asarray(k_norms, dtype=np.float32), np.asarray(v_norms, dtype=np.float32)
@@ -71,15 +70,15 @@ def tile_records_reference(k_codes, k_signs, k_norms, v_codes, v_norms):
             L = 4 * g + t_
             rec[:, 16 * L:16 * L + 8] = kc[:, g, 8 * t_:8 * t_ + 8]
             rec[:, 16 * L + 8:16 * L + 16] = kc[:, g + 8, 8 * t_:8 * t_ + 8]
-            rec[:, 1024 + 8 * L:1024 + 8 * L + 4] = ks[:, g, 4 * t_:4 * t_ + 4]
-            rec[:, 1024 + 8 * L + 4:1024 + 8 * L + 8] = ks[:, g + 8, 4 * t_:4 * t_ + 4]
+            rec[:, 1024 + 16 * L:1024 + 16 * L + 4] = ks[:, g, 4 * t_:4 * t_ + 4]
+            rec[:, 1024 + 16 * L + 4:1024 + 16 * L + 8] = ks[:, g + 8, 4 * t_:4 * t_ + 4]
             for b in range(4):
                 tok = 2 * t_ + (b & 1) + 8 * (b >> 1)
                 for m in range(4):
                     byte = sum(mag[:, tok, 16 * g + 4 * m + f] << (2 * f) for f in range(4))
                     rec[:, 512 + 16 * L + 4 * m + b] = byte.astype(np.uint8)
                 piece = sum(neg[:, tok, 16 * g + p_] << p_ for p_ in range(16)).astype(np.uint16)
-                off = 1280 + 8 * L + 4 * (b >> 1) + 2 * (b & 1)
+                off = 1024 + 16 * L + 8 + 4 * (b >> 1) + 2 * (b & 1)
                 rec[:, off] = (piece & 0xFF).astype(np.uint8)
                 rec[:, off + 1] = (piece >> 8).astype(np.uint8)
         nrm = np.stack([kn[:, g], kn[:, g + 8], vn[:, g], vn[:, g + 8]], axis=1).astype(np.float32)

@@ -59,11 +59,11 @@ int main() {
   int bad = 0;
   for (int lane = 0; lane < 32; ++lane) {
     const int g = lane >> 2, t = lane & 3;
-    uint32_t kc[4], vm[4], ks[2], vs[2];
+    uint32_t kc[4], vm[4], sg[4];
     memcpy(kc, &rec[tile::kOffKeyCodes + 16 * lane], 16);
     memcpy(vm, &rec[tile::kOffValMags + 16 * lane], 16);
-    memcpy(ks, &rec[tile::kOffKeySigns + 8 * lane], 8);
-    memcpy(vs, &rec[tile::kOffValSigns + 8 * lane], 8);
+    memcpy(sg, &rec[tile::kOffSigns + 16 * lane], 16);
+    const uint32_t ks[2] = {sg[0], sg[1]}, vs[2] = {sg[2], sg[3]};
     for (int h = 0; h < 2; ++h)
       for (int c = 0; c < 32; ++c)
         if (((ks[h] >> c) & 1u) != static_cast<uint32_t>(ksign[g + 8 * h][32 * t + c])) bad++;
