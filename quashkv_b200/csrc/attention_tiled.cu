@@ -30,7 +30,9 @@ namespace qkv {
 namespace {
 
 constexpr int kWarps = 4;
-constexpr int kRing = 5;                    // ring slots per warp: four records in flight while one is worked on
+// Ring slots per warp: four records in flight while one is worked on.  (Five or six resident CTAs per SM with
+// shorter rings, 94 / 80 registers, measured 4 % / 8 % slower than four.)
+constexpr int kRing = 5;
 constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ unsigned int g_bulk_timeouts = 0;   // bounded waits on a bulk copy that ran out
@@ -55,8 +57,8 @@ struct TileRegs {
   float4 nrm;     // key norms of tokens g, g + 8; value norms of tokens g, g + 8
 };
 
-template <bool PAGED, bool LO4, int MINB>
-__global__ void __launch_bounds__(kWarps * 32, MINB) attend_tiled_kernel(AttnArgs a) {
+template <bool PAGED, bool LO4>
+__global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a) {
   constexpr int D = 128;
   constexpr int kTile = tile::kTokens;
   __shared__ float q_s[8][2 * D];                    // [query row][q_rot*scale | sign weights]
@@ -418,34 +420,58 @@ __global__ void __launch_bounds__(kWarps * 32, MINB) attend_tiled_kernel(AttnArg
   float* vec = reinterpret_cast<float*>(pool);       // [8][D] merged, normalised accumulators
   float* wgt = vec + 8 * D;                          // [8][kMaxSplits] weights of the splits
   float* invl = wgt + 8 * kMaxSplits;                // [8]
-  for (int r = warp; r < nq; r += kWarps) {          // a warp per query row
+  // This tail runs once per (batch, kv head) at the very end of the call, so it is written for latency: every
+  // round of loads is issued before the first result is used.
+  for (int r = warp; r < nq; r += kWarps) {          // a warp per query row; a lane takes splits lane, lane + 32
     const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
     const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
     const float* pp = a.part + qrow * a.n_splits * (D + 2);
-    float M = -INFINITY;
-    for (int sp = lane; sp < a.n_splits; sp += 32) M = fmaxf(M, __ldcg(pp + sp * (D + 2)));
+    float mm[2], ll[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int sp = lane + 32 * h;
+      const bool live = sp < a.n_splits;
+      mm[h] = live ? __ldcg(pp + sp * (D + 2)) : -INFINITY;
+      ll[h] = live ? __ldcg(pp + sp * (D + 2) + 1) : 0.f;
+    }
+    float M = fmaxf(mm[0], mm[1]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(QKV_FULL_MASK, M, o));
     float L = 0.f;
-    for (int sp = lane; sp < a.n_splits; sp += 32) {
-      const float mm = __ldcg(pp + sp * (D + 2));
-      const float f = (mm == -INFINITY) ? 0.f : expf(mm - M);
-      wgt[r * kMaxSplits + sp] = f;
-      L += f * __ldcg(pp + sp * (D + 2) + 1);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int sp = lane + 32 * h;
+      const float f = (mm[h] == -INFINITY) ? 0.f : expf(mm[h] - M);
+      if (sp < a.n_splits) wgt[r * kMaxSplits + sp] = f;
+      L += f * ll[h];
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(QKV_FULL_MASK, L, o);
     if (lane == 0) invl[r] = 1.f / fmaxf(L, 1e-30f);
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < nq * D; idx += blockDim.x) {
-    const int r = idx / D, j = idx % D;
+  for (int idx = threadIdx.x; idx < nq * (D / 2); idx += blockDim.x) {     // a thread per pair of coordinates
+    const int r = idx / (D / 2), j = 2 * (idx % (D / 2));
     const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
     const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
-    const float* pp = a.part + qrow * a.n_splits * (D + 2);
-    float v = 0.f;
-    for (int sp = 0; sp < a.n_splits; ++sp) v += wgt[r * kMaxSplits + sp] * __ldcg(pp + sp * (D + 2) + 2 + j);
-    vec[r * D + j] = v * invl[r];
+    const float* pp = a.part + qrow * a.n_splits * (D + 2) + 2 + j;       // 8-byte aligned: rows of 130 floats
+    const float* w = wgt + r * kMaxSplits;
+    float2 acc = make_float2(0.f, 0.f);
+    int sp = 0;
+    for (; sp + 8 <= a.n_splits; sp += 8) {
+      float2 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldcg(reinterpret_cast<const float2*>(pp + (sp + u) * (D + 2)));
+#pragma unroll
+      for (int u = 0; u < 8; ++u) { acc.x = fmaf(w[sp + u], v[u].x, acc.x); acc.y = fmaf(w[sp + u], v[u].y, acc.y); }
+    }
+    for (; sp < a.n_splits; ++sp) {
+      const float2 v = __ldcg(reinterpret_cast<const float2*>(pp + sp * (D + 2)));
+      acc.x = fmaf(w[sp], v.x, acc.x);
+      acc.y = fmaf(w[sp], v.y, acc.y);
+    }
+    vec[r * D + j] = acc.x * invl[r];
+    vec[r * D + j + 1] = acc.y * invl[r];
   }
   __syncthreads();
   {
@@ -453,7 +479,7 @@ __global__ void __launch_bounds__(kWarps * 32, MINB) attend_tiled_kernel(AttnArg
     float o[8];
 #pragma unroll
     for (int r = 0; r < 8; ++r) o[r] = 0.f;
-#pragma unroll 8
+#pragma unroll 32
     for (int j = 0; j < D; ++j) {
       const float mval = __ldg(a.Pi + j * D + i);
 #pragma unroll
@@ -496,17 +522,12 @@ int launch_attend_tiled(const AttnArgs& a_in, cudaStream_t st) {
   const bool lo4 = a_in.G * a_in.q_len <= 4;      // spare query columns carry the fp16 residual of the queries
   const AttnArgs& a = a_in;
   cudaError_t err;
-  const char* es = getenv("QUASHKV_B200_TILED_MINB");
-  const int minb = es ? atoi(es) : 4;
   if (a.block_table)
-    err = lo4 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<true, true, 4>, a)
-              : cudaLaunchKernelEx(&cfg, attend_tiled_kernel<true, false, 4>, a);
-  else if (minb == 3)
-    err = lo4 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, true, 3>, a)
-              : cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, false, 3>, a);
+    err = lo4 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<true, true>, a)
+              : cudaLaunchKernelEx(&cfg, attend_tiled_kernel<true, false>, a);
   else
-    err = lo4 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, true, 4>, a)
-              : cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, false, 4>, a);
+    err = lo4 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, true>, a)
+              : cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, false>, a);
   if (err != cudaSuccess) return QKV_ELAUNCH;
   return check_launch();
 }

