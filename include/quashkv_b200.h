@@ -250,8 +250,9 @@ int qkv_scatter_rows(const void* src, void* dst, const int64_t* slots, int64_t n
  * RECORDS of 16 consecutive tokens of one (batch, kv head): QKV_TILE_BYTES = 16 * 104 bytes, the same
  * bytes per token as the five planes of qkv_cache_t, arranged in the order in which the tensor-core
  * kernel consumes them (key codes and sign bits as the reference packs them, reference
- * packing.py:22-94, regrouped by lane; value codes as a sign bit and a 2-bit magnitude index with the two
- * tokens of a multiply-accumulate pair side by side; norms last).  One record is one bulk copy for the
+ * packing.py:22-94, regrouped by lane; value codes as 6-bit fields that hold the two tokens of a
+ * multiply-accumulate pair, each as a sign bit and a 2-bit magnitude index, so that a field is the
+ * index of a table of ready operand pairs; norms last).  One record is one bulk copy for the
  * kernel.  The re-arrangement is an exact integer permutation: qkv_untile_rows returns the reference's
  * packed rows byte for byte.  The value half of the format presumes a value table with
  * centroid[7 - i] = -centroid[i] (Lloyd-Max tables of a symmetric density).
@@ -262,7 +263,8 @@ int qkv_scatter_rows(const void* src, void* dst, const int64_t* slots, int64_t n
  * (i / map.seg_len) * map.seg_stride + map.seg_off + i % map.seg_len; slot s is token s % 16 of record
  * s / 16.  For a contiguous cache of `capacity` tokens per segment: seg_len = new tokens per segment,
  * seg_stride = capacity, seg_off = tokens already stored.  Stands where the reference appends a block to
- * its list (engine.py:145-172).  Tokens own whole bytes of a record, so any set of distinct slots may
+ * its list (engine.py:145-172).  A token's bits are written with plain stores where it owns whole bytes
+ * and with atomic AND / OR where it shares a word with its neighbour, so any set of distinct slots may
  * be written by one call or by concurrent calls.  records must be 16-byte aligned. */
 #define QKV_TILE_TOKENS 16
 #define QKV_TILE_BYTES 1664

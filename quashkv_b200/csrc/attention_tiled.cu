@@ -4,9 +4,10 @@
 //
 // A warp owns 16-token tiles of its split.  One elected lane fetches a whole record (1664 bytes) with
 // ONE bulk copy into the warp's ring of four stages; an mbarrier per stage counts the bytes in, every
-// wait on it is bounded.  Each lane then reads its share with four vector loads, decodes it IN
-// REGISTERS into m16n8k16 fragments (tile_decode.cuh: one PRMT per pair of codes, one LOP3 per pair of
-// sign bits) and feeds mma.sync:
+// wait on it is bounded.  Each lane then reads its share with five vector loads, decodes it into m16n8k16
+// fragments (tile_decode.cuh: key codes with one PRMT per pair of codes, sign bits with one LOP3 per pair,
+// both in registers; values with one look-up per pair of tokens in a 64-entry table of ready fp16 pairs in
+// shared memory, laid out so that every lane reads its own bank) and feeds mma.sync:
 //   scores   tokens = M, queries = N, coordinates = K: 8 MMAs on the key codes, 8 on the sign bits
 //   values   coordinates = M, tokens = K, queries = N: 8 MMAs, accumulated in the ROTATED domain
 // with an online softmax in between (log2 domain, lazily raised reference exponent).  Per split the
@@ -30,9 +31,9 @@ namespace qkv {
 namespace {
 
 constexpr int kWarps = 4;
-// Ring slots per warp: four records in flight while one is worked on.  (Five or six resident CTAs per SM with
-// shorter rings, 94 / 80 registers, measured 4 % / 8 % slower than four.)
-constexpr int kRing = 5;
+// Ring slots per warp: three records in flight while one is worked on.  (Five or six resident CTAs per SM,
+// 94 / 80 registers, measured 4 % / 8 % slower than four.)
+constexpr int kRing = 4;
 constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ unsigned int g_bulk_timeouts = 0;   // bounded waits on a bulk copy that ran out
@@ -52,8 +53,9 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
 
 struct TileRegs {
   uint4 kc;       // key codes: token g words 0, 1; token g + 8 words 0, 1
-  uint4 vm;       // value magnitudes, words m = 0..3
-  uint4 sg;       // key sign words of tokens g, g + 8; value sign words of token pairs (2t, 2t+1), (2t+8, 2t+9)
+  uint2 ks;       // key sign words of tokens g, g + 8
+  uint4 va;       // values: the three words of token pair (2t, 2t+1), then the first word of pair (2t+8, 2t+9)
+  uint2 vb;       // values: the other two words of pair (2t+8, 2t+9)
   float4 nrm;     // key norms of tokens g, g + 8; value norms of tokens g, g + 8
 };
 
@@ -70,6 +72,7 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
   __shared__ __align__(8) uint64_t bars[kWarps][kRing];
   __shared__ float wsum[8];                          // sum of the sign weights per query column
   __shared__ uint4 bop[8][32];                       // B operands of two k-steps per lane: 8 key-code steps, then 8 sign steps
+  __shared__ uint32_t vtab[64][32];                  // value table: entry (6-bit field) x lane, an fp16 pair each
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gid = lane >> 2, tig = lane & 3;
@@ -205,7 +208,21 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
   }
   __syncthreads();
   const uint32_t kt_a = a.tables[0], kt_b = a.tables[1];     // fp16 key centroids 0,1 | 2,3
-  const uint32_t vt_a = a.tables[8], vt_b = a.tables[9];     // fp16 value magnitudes 0,1 | 2,3
+  if (has_work) {
+    // value table: entry e holds the fp16 values of two stored codes (neg << 2 | mag), the first token's in the
+    // low half; every entry is repeated for the 32 lanes (entry e of lane L at word 32 e + L), so that a warp's
+    // look-ups never meet in a bank
+    const uint32_t mg0 = a.tables[8], mg1 = a.tables[9];        // fp16 value magnitudes 0,1 | 2,3
+    auto value_bits = [&](int v) { return ((((v & 2) ? mg1 : mg0) >> (16 * (v & 1))) & 0xFFFFu) | ((v & 4) ? 0x8000u : 0u); };
+#pragma unroll
+    for (int k = 0; k < 64 / kWarps; ++k) {
+      const int e = warp + kWarps * k;
+      vtab[e][lane] = value_bits(e & 7) | (value_bits(e >> 3) << 16);
+    }
+  }
+  __syncthreads();
+  const unsigned char* vt_base = reinterpret_cast<const unsigned char*>(&vtab[0][0]);
+  const uint32_t lane4 = 4u * lane;
   // causal limits of this lane's two query columns (2 tig, 2 tig + 1), relative to the split start
   int lim_rel[2];
 #pragma unroll
@@ -244,8 +261,8 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
 #undef QKV_KEY_STEPS
     }
     {
-      const uint32_t cp0[4] = {cur.sg.x, cur.sg.x << 7, cur.sg.x >> 1, cur.sg.x << 13};
-      const uint32_t cp1[4] = {cur.sg.y, cur.sg.y << 7, cur.sg.y >> 1, cur.sg.y << 13};
+      const uint32_t cp0[4] = {cur.ks.x, cur.ks.x << 7, cur.ks.x >> 1, cur.ks.x << 13};
+      const uint32_t cp1[4] = {cur.ks.y, cur.ks.y << 7, cur.ks.y >> 1, cur.ks.y << 13};
 #pragma unroll
       for (int s2 = 0; s2 < 4; ++s2) {
         const uint4 bw = bop[4 + s2][lane];
@@ -321,16 +338,18 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
     const uint32_t pb0 = movmatrix_trans(pack_half2(p0 * vn0, p1 * vn0));
     const uint32_t pb1 = movmatrix_trans(pack_half2(p2 * vn1, p3 * vn1));
 
-    // ---- values: magnitude look-up, sign flip, 8 MMAs ---------------------------------------------
+    // ---- values: one table look-up per pair of tokens, 8 MMAs ---------------------------------------
     {
       uint32_t af[4];
-#define QKV_VAL_STEP(WORD, M, HALF)                                                  \
-  tile::value_fragment<M, HALF>(WORD, cur.sg.z, cur.sg.w, vt_a, vt_b, af);           \
-  mma16816(O[2 * (M) + (HALF)], af, pb0, pb1);
-      QKV_VAL_STEP(cur.vm.x, 0, 0) QKV_VAL_STEP(cur.vm.x, 0, 1)
-      QKV_VAL_STEP(cur.vm.y, 1, 0) QKV_VAL_STEP(cur.vm.y, 1, 1)
-      QKV_VAL_STEP(cur.vm.z, 2, 0) QKV_VAL_STEP(cur.vm.z, 2, 1)
-      QKV_VAL_STEP(cur.vm.w, 3, 0) QKV_VAL_STEP(cur.vm.w, 3, 1)
+      auto vt = [&](uint32_t off) { return *reinterpret_cast<const uint32_t*>(vt_base + off); };
+#define QKV_VAL_STEP(I)                                                                                   \
+  af[0] = vt(tile::value_table_offset<2 * (I)>(cur.va.x, cur.va.y, cur.va.z, lane4));                     \
+  af[1] = vt(tile::value_table_offset<2 * (I) + 1>(cur.va.x, cur.va.y, cur.va.z, lane4));                 \
+  af[2] = vt(tile::value_table_offset<2 * (I)>(cur.va.w, cur.vb.x, cur.vb.y, lane4));                     \
+  af[3] = vt(tile::value_table_offset<2 * (I) + 1>(cur.va.w, cur.vb.x, cur.vb.y, lane4));                 \
+  mma16816(O[I], af, pb0, pb1);
+      QKV_VAL_STEP(0) QKV_VAL_STEP(1) QKV_VAL_STEP(2) QKV_VAL_STEP(3)
+      QKV_VAL_STEP(4) QKV_VAL_STEP(5) QKV_VAL_STEP(6) QKV_VAL_STEP(7)
 #undef QKV_VAL_STEP
     }
   };
@@ -343,8 +362,9 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
     const unsigned char* stage = ring + slot * tile::kBytes;
     TileRegs cur;
     cur.kc = *reinterpret_cast<const uint4*>(stage + tile::kOffKeyCodes + 16 * lane);
-    cur.vm = *reinterpret_cast<const uint4*>(stage + tile::kOffValMags + 16 * lane);
-    cur.sg = *reinterpret_cast<const uint4*>(stage + tile::kOffSigns + 16 * lane);
+    cur.ks = *reinterpret_cast<const uint2*>(stage + tile::kOffKeySigns + 8 * lane);
+    cur.va = *reinterpret_cast<const uint4*>(stage + tile::kOffVal16 + 16 * lane);
+    cur.vb = *reinterpret_cast<const uint2*>(stage + tile::kOffVal8 + 8 * lane);
     cur.nrm = *reinterpret_cast<const float4*>(stage + tile::kOffNorms + 16 * gid);
     process(cur, rel);
     // The slot is refilled only now.  A warp issues its instructions in order and an instruction issues only

@@ -54,21 +54,27 @@ QKV_HD void key_fragment(uint32_t w0, uint32_t w1, uint32_t tab_a, uint32_t tab_
   af[3] = prmt_hd(tab_a, tab_b, h1);
 }
 
-// Values of one M tile i = 2 m + HALF (coordinates 16 g + 2 i, + 1 as rows g, g + 8): magnitude word m,
-// fields 2 HALF (row g) and 2 HALF + 1 (row g + 8); sign words s0 (tokens 2t, 2t+1) and s1 (2t+8, 2t+9),
-// bit p = 4 m + field in each half.
-template <int M, int HALF>
-QKV_HD void value_fragment(uint32_t mag_word, uint32_t s0, uint32_t s1, uint32_t tab_a, uint32_t tab_b,
-                           uint32_t (&af)[4]) {
-  constexpr int F0 = 2 * HALF, F1 = 2 * HALF + 1;
-  constexpr int P0 = 4 * M + F0, P1 = 4 * M + F1;
-  uint32_t l0, h0, l1, h1;
-  selectors<F0>(mag_word, l0, h0);
-  selectors<F1>(mag_word, l1, h1);
-  af[0] = prmt_hd(tab_a, tab_b, l0) ^ ((s0 << (15 - P0)) & 0x80008000u);
-  af[1] = prmt_hd(tab_a, tab_b, l1) ^ ((s0 << (15 - P1)) & 0x80008000u);
-  af[2] = prmt_hd(tab_a, tab_b, h0) ^ ((s1 << (15 - P0)) & 0x80008000u);
-  af[3] = prmt_hd(tab_a, tab_b, h1) ^ ((s1 << (15 - P1)) & 0x80008000u);
+// Byte offset, inside a 64-entry value table whose entry e of lane L sits at 128 e + 4 L (every lane reads its
+// own bank), of field F (0..15) of a 96-bit group w[0..2]: two instructions, a (funnel) shift that brings the
+// field to bits 7..12 and one logic operation that masks it and merges the lane's offset.
+template <int F>
+QKV_HD uint32_t value_table_offset(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t lane4) {
+  constexpr int bit = 6 * F, word = bit >> 5, sh = bit & 31;
+  const uint32_t lo = word == 0 ? w0 : (word == 1 ? w1 : w2);
+  const uint32_t hi = word == 0 ? w1 : w2;               // only read when the field straddles two words
+  uint32_t t;
+  if (sh + 6 > 32) {
+#if defined(__CUDA_ARCH__)
+    t = __funnelshift_r(lo, hi, sh - 7);
+#else
+    t = static_cast<uint32_t>(((static_cast<uint64_t>(hi) << 32) | lo) >> (sh - 7));
+#endif
+  } else if (sh >= 7) {
+    t = lo >> (sh - 7);
+  } else {
+    t = lo << (7 - sh);
+  }
+  return (t & (0x3Fu << 7)) | lane4;
 }
 
 }  // namespace tile

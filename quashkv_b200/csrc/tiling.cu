@@ -7,8 +7,9 @@
 // decompression and the byte-level parity checks read a tiled cache.
 //
 // Eight threads per token: thread j moves 4 bytes of the key-code row, (j < 4) 4 bytes of the sign
-// row, (j = 4, 5) a norm, and re-codes the 16 value coordinates 16 j .. 16 j + 15 (6 bytes of the
-// 3-bit row) as four magnitude bytes and 16 sign bits.
+// row, (j = 4, 5) a norm, and files the 16 value coordinates 16 j .. 16 j + 15 (6 bytes of the
+// 3-bit row) into the token's half of sixteen 6-bit fields.  Those fields are shared with the other
+// token of the pair, so the token's bits are cleared and set with atomic AND / OR on the three words.
 #include "common.cuh"
 #include "tile_format.cuh"
 
@@ -45,11 +46,15 @@ __global__ void __launch_bounds__(256) tile_rows_kernel(RowPlanes src, int64_t n
   const uint16_t* vrow = reinterpret_cast<const uint16_t*>(src.v_codes + i * tile::kValRowBytes + 6 * j);
   const uint64_t codes48 = static_cast<uint64_t>(vrow[0]) | (static_cast<uint64_t>(vrow[1]) << 16) |
                            (static_cast<uint64_t>(vrow[2]) << 32);
-  uint32_t mags, negs;
-  tile::split_codes16(codes48, mags, negs);
+  uint32_t bits[3], mask[3];
+  tile::spread_codes16(codes48, tile::val_half_shift(k), bits, mask);
+  const int lane = tile::val_lane(k, j), grp = tile::val_group(k);
 #pragma unroll
-  for (int m = 0; m < 4; ++m) rec[tile::val_mag_offset(k, j, m)] = static_cast<uint8_t>(mags >> (8 * m));
-  *reinterpret_cast<uint16_t*>(rec + tile::val_sign_offset(k, j)) = static_cast<uint16_t>(negs);
+  for (int w = 0; w < 3; ++w) {
+    uint32_t* word = reinterpret_cast<uint32_t*>(rec + tile::val_word_offset(lane, 3 * grp + w));
+    atomicAnd(word, ~mask[w]);
+    atomicOr(word, bits[w]);
+  }
 }
 
 __global__ void __launch_bounds__(256) untile_rows_kernel(const uint8_t* __restrict__ records, qkv_rows_t map,
@@ -70,11 +75,11 @@ __global__ void __launch_bounds__(256) untile_rows_kernel(const uint8_t* __restr
         *reinterpret_cast<const uint32_t*>(rec + tile::key_sign_offset(k, j));
   if (j == 4) dst.k_norms[i] = *reinterpret_cast<const float*>(rec + tile::key_norm_offset(k));
   if (j == 5) dst.v_norms[i] = *reinterpret_cast<const float*>(rec + tile::val_norm_offset(k));
-  uint32_t mags = 0;
+  uint32_t w[3];
+  const int lane = tile::val_lane(k, j), grp = tile::val_group(k);
 #pragma unroll
-  for (int m = 0; m < 4; ++m) mags |= static_cast<uint32_t>(rec[tile::val_mag_offset(k, j, m)]) << (8 * m);
-  const uint32_t negs = *reinterpret_cast<const uint16_t*>(rec + tile::val_sign_offset(k, j));
-  const uint64_t codes48 = tile::join_codes16(mags, negs);
+  for (int q = 0; q < 3; ++q) w[q] = *reinterpret_cast<const uint32_t*>(rec + tile::val_word_offset(lane, 3 * grp + q));
+  const uint64_t codes48 = tile::gather_codes16(w, tile::val_half_shift(k));
   uint16_t* vrow = reinterpret_cast<uint16_t*>(dst.v_codes + i * tile::kValRowBytes + 6 * j);
   vrow[0] = static_cast<uint16_t>(codes48);
   vrow[1] = static_cast<uint16_t>(codes48 >> 16);

@@ -27,6 +27,7 @@ int main() {
     }
   std::vector<uint8_t> rec(tile::kBytes, 0);
   std::vector<int> cover(tile::kBytes, 0);
+  std::vector<uint32_t> vbits(tile::kBytes / 4, 0);          // value bits claimed so far, per word
   for (int k = 0; k < 16; ++k)
     for (int j = 0; j < 8; ++j) {                               // the steps of the tiling kernel's thread j
       memcpy(&rec[tile::key_code_offset(k, j)], &krow[k][4 * j], 4);
@@ -37,33 +38,38 @@ int main() {
       }
       uint64_t c48 = 0;
       memcpy(&c48, &vrow[k][6 * j], 6);
-      uint32_t mags, negs;
-      tile::split_codes16(c48, mags, negs);
-      if (tile::join_codes16(mags, negs) != c48) { printf("join_codes16 is not the inverse\n"); return 1; }
-      for (int m = 0; m < 4; ++m) {
-        rec[tile::val_mag_offset(k, j, m)] = static_cast<uint8_t>(mags >> (8 * m));
-        cover[tile::val_mag_offset(k, j, m)]++;
+      uint32_t bits[3], mask[3];
+      tile::spread_codes16(c48, tile::val_half_shift(k), bits, mask);
+      const int vl = tile::val_lane(k, j), grp = tile::val_group(k);
+      uint32_t back[3];
+      for (int w = 0; w < 3; ++w) {                             // the atomic AND / OR of the tiling kernel
+        uint32_t word;
+        memcpy(&word, &rec[tile::val_word_offset(vl, 3 * grp + w)], 4);
+        if (word & mask[w]) { printf("two tokens claim the same value bits\n"); return 1; }
+        word = (word & ~mask[w]) | bits[w];
+        memcpy(&rec[tile::val_word_offset(vl, 3 * grp + w)], &word, 4);
+        vbits[tile::val_word_offset(vl, 3 * grp + w) / 4] |= mask[w];
+        back[w] = word;
       }
-      const uint16_t ng = static_cast<uint16_t>(negs);
-      memcpy(&rec[tile::val_sign_offset(k, j)], &ng, 2);
-      for (int b = 0; b < 2; ++b) cover[tile::val_sign_offset(k, j) + b]++;
+      if (tile::gather_codes16(back, tile::val_half_shift(k)) != c48) { printf("gather_codes16 is not the inverse\n"); return 1; }
       if (j == 0)
         for (int b = 0; b < 4; ++b) { cover[tile::key_norm_offset(k) + b]++; cover[tile::val_norm_offset(k) + b]++; }
     }
-  for (int i = 0; i < tile::kBytes; ++i)
-    if (cover[i] != 1) { printf("byte %d of the record is written %d times\n", i, cover[i]); return 1; }
+  for (int i = 0; i < tile::kBytes; ++i) {
+    const bool value_part = i >= tile::kOffVal16 && i < tile::kOffNorms;
+    if (value_part ? vbits[i / 4] != 0xFFFFFFFFu : cover[i] != 1) { printf("byte %d of the record is not written exactly once\n", i); return 1; }
+  }
 
   // tables of recognisable bit patterns: key entry i -> 0x1000 + i, value magnitude m -> 0x2000 + m
   const uint32_t kt_a = 0x1000u | (0x1001u << 16), kt_b = 0x1002u | (0x1003u << 16);
-  const uint32_t vt_a = 0x2000u | (0x2001u << 16), vt_b = 0x2002u | (0x2003u << 16);
   int bad = 0;
   for (int lane = 0; lane < 32; ++lane) {
     const int g = lane >> 2, t = lane & 3;
-    uint32_t kc[4], vm[4], sg[4];
+    uint32_t kc[4], ks[2], va[4], vb[2];
     memcpy(kc, &rec[tile::kOffKeyCodes + 16 * lane], 16);
-    memcpy(vm, &rec[tile::kOffValMags + 16 * lane], 16);
-    memcpy(sg, &rec[tile::kOffSigns + 16 * lane], 16);
-    const uint32_t ks[2] = {sg[0], sg[1]}, vs[2] = {sg[2], sg[3]};
+    memcpy(ks, &rec[tile::kOffKeySigns + 8 * lane], 8);
+    memcpy(va, &rec[tile::kOffVal16 + 16 * lane], 16);
+    memcpy(vb, &rec[tile::kOffVal8 + 8 * lane], 8);
     for (int h = 0; h < 2; ++h)
       for (int c = 0; c < 32; ++c)
         if (((ks[h] >> c) & 1u) != static_cast<uint32_t>(ksign[g + 8 * h][32 * t + c])) bad++;
@@ -77,18 +83,18 @@ int main() {
     uint32_t af[4];
 #define K(W, F) tile::key_fragment<F>(kc[W], kc[2 + W], kt_a, kt_b, af); check_key(W, F, af);
     K(0, 0) K(0, 1) K(0, 2) K(0, 3) K(1, 0) K(1, 1) K(1, 2) K(1, 3)
-    auto val = [&](int k, int c) {
-      const uint32_t u = vcode[k][c];
-      return (0x2000u + tile::code_to_mag(u)) | (tile::code_to_neg(u) << 15);
+    // value look-ups: the table offset of field F must be 128 * (stored(token a) | stored(token b) << 3) + 4 * lane
+    auto want_off = [&](int ka, int kb, int c) {
+      return 128u * (tile::code_to_stored(vcode[ka][c]) | (tile::code_to_stored(vcode[kb][c]) << 3)) + 4u * lane;
     };
-    auto check_val = [&](int i, const uint32_t (&a)[4]) {     // M tile i: rows g, g+8 = coordinates 16g+2i, +1
-      const int c0 = 16 * g + 2 * i, c1 = c0 + 1;
-      if (a[0] != (val(2 * t, c0) | (val(2 * t + 1, c0) << 16)) || a[1] != (val(2 * t, c1) | (val(2 * t + 1, c1) << 16)) ||
-          a[2] != (val(2 * t + 8, c0) | (val(2 * t + 9, c0) << 16)) || a[3] != (val(2 * t + 8, c1) | (val(2 * t + 9, c1) << 16)))
-        bad++;
-    };
-#define V(M, H) tile::value_fragment<M, H>(vm[M], vs[0], vs[1], vt_a, vt_b, af); check_val(2 * M + H, af);
-    V(0, 0) V(0, 1) V(1, 0) V(1, 1) V(2, 0) V(2, 1) V(3, 0) V(3, 1)
+    uint32_t got[2][16];
+#define OFF(F) got[0][F] = tile::value_table_offset<F>(va[0], va[1], va[2], 4u * lane); \
+               got[1][F] = tile::value_table_offset<F>(va[3], vb[0], vb[1], 4u * lane);
+    OFF(0) OFF(1) OFF(2) OFF(3) OFF(4) OFF(5) OFF(6) OFF(7) OFF(8) OFF(9) OFF(10) OFF(11) OFF(12) OFF(13) OFF(14) OFF(15)
+    for (int f = 0; f < 16; ++f) {      // field f = coordinate 16 g + f; M tile i uses fields 2 i (row g) and 2 i + 1 (row g + 8)
+      if (got[0][f] != want_off(2 * t, 2 * t + 1, 16 * g + f)) bad++;
+      if (got[1][f] != want_off(2 * t + 8, 2 * t + 9, 16 * g + f)) bad++;
+    }
   }
   if (bad) { printf("FAILED: %d fragment mismatches\n", bad); return 1; }
   printf("tile emulation OK\n");
