@@ -298,7 +298,92 @@ def config5(device, n_db=10_000_000, m=10_000, k=10, rows=None):
     return index, qs, out
 
 
-def extras(device, hbm_gbs, tf_sustained):
+def config4(device, with_cpu=True, new_tokens=256):
+    """QuashKVCache inside a random-init Llama-architecture decoder (22 layers, hidden 2048, 32 query / 4 KV heads,
+    head_dim 64, MLP 5632, vocab 32000, weights N(0, 0.02) from seed 4, bf16): a 1024-token prompt of random ids
+    (seed 5), batch 8, 256 greedy tokens.  The compressed cache is attached as a transformers Cache whose
+    attention runs on the packed cache (no decompression in the loop); tokens/s at 2 / 3 / 4 bits beside an
+    uncompressed DynamicCache, and the cosine of every layer's attention output at the first decode step."""
+    from transformers import DynamicCache, LlamaConfig, LlamaForCausalLM
+    from quashkv_b200.integrations.hf_cache import QuashKVCache, QuashKVCacheConfig, make_hf_cache
+    cfg = LlamaConfig(num_hidden_layers=22, hidden_size=2048, num_attention_heads=32, num_key_value_heads=4,
+                      head_dim=64, intermediate_size=5632, vocab_size=32000, max_position_embeddings=2048,
+                      eos_token_id=None, bos_token_id=None, pad_token_id=None)
+    torch.manual_seed(4)
+    with torch.device(device):
+        model = LlamaForCausalLM(cfg)
+    model = model.to(torch.bfloat16).eval()
+    prompt = torch.randint(0, 32000, (8, 1024), generator=torch.Generator().manual_seed(5)).to(device)
+    layers = [m for m in model.modules() if hasattr(m, "layer_idx") and hasattr(m, "q_proj")]
+
+    @torch.no_grad()
+    def generate(cache, capture=None):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = model(input_ids=prompt, past_key_values=cache, use_cache=True)
+        nxt = out.logits[:, -1].argmax(-1, keepdim=True)
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        hooks = []
+        if capture is not None:             # attention outputs of the first decode step
+            hooks = [m.register_forward_hook(lambda mod, a, o, i=i: capture.__setitem__(i, o[0].float())) for i, m in enumerate(layers)]
+        for step in range(new_tokens):
+            out = model(input_ids=nxt, past_key_values=cache, use_cache=True)
+            nxt = out.logits[:, -1].argmax(-1, keepdim=True)
+            if step == 0:
+                for h in hooks:
+                    h.remove()
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        return {"decode_tokens_s": prompt.shape[0] * new_tokens / (t2 - t1), "prefill_s": t1 - t0}
+
+    out = {"model": "llama-architecture 22 x 2048, 32/4 heads, head_dim 64, random init (seed 4), bf16",
+           "batch": 8, "prompt_tokens": 1024, "new_tokens": new_tokens}
+    generate(DynamicCache(config=cfg))                       # warm-up of the model's kernels
+    ref_attn = {}
+    out["dynamic_cache"] = generate(DynamicCache(config=cfg), capture=ref_attn)
+    for bits in (2, 3, 4):
+        qc = QuashKVCache(cfg.num_hidden_layers, 64, QuashKVCacheConfig(key_bits=bits, value_bits=bits, seed=42), device=device)
+        cache = make_hf_cache(qc, fused=True)
+        previous = cache.attach(model)
+        got = {}
+        try:
+            res = generate(cache, capture=got)
+        finally:
+            cache.detach(model, previous)
+        cos = [float(torch.nn.functional.cosine_similarity(got[i].flatten(1), ref_attn[i].flatten(1), dim=1).mean())
+               for i in range(len(layers))]
+        res["attention_output_cosine_first_layer"] = cos[0]
+        res["attention_output_cosine_mean"] = sum(cos) / len(cos)
+        res["attention_output_cosine_min"] = min(cos)
+        res["compression_ratio"] = qc.compression_stats()["overall_compression_ratio"]
+        out[f"quashkv_{bits}bit"] = res
+        del qc, cache
+    if with_cpu:
+        # The reference's loop on the host cores: per generated token and layer it decompresses the whole history
+        # (keys and values) and attends over it.  One layer at the final length, scaled to 22 layers.
+        from oracle import quashkv_oracle as orc
+        torch.set_num_threads(os.cpu_count() or 1)
+        Pi = orc.rotation_matrix(64, 42)
+        cent, bnd = orc.lloyd_max_tables(64, 3)
+        g = torch.Generator().manual_seed(5)
+        codes, norms = orc.compress_mse(torch.randn(8, 4, 1280, 64, generator=g), Pi, bnd)
+        q = torch.randn(8, 32, 1, 64, generator=g)
+        t0 = time.perf_counter()
+        for _ in range(3):
+            k = orc.decompress_mse(codes, norms, Pi, cent)
+            v = orc.decompress_mse(codes, norms, Pi, cent)
+            torch.nn.functional.scaled_dot_product_attention(q, k.repeat_interleave(8, 1), v.repeat_interleave(8, 1))
+        per_layer = (time.perf_counter() - t0) / 3
+        out["cpu_reference_loop"] = {"decode_tokens_s": 8 / (22 * per_layer), "cores": os.cpu_count() or 1,
+                                     "sample": "cache work of one layer at 1280 tokens (decompress K and V, attend), "
+                                               "x 22 layers per token; the model's own matmuls not counted"}
+    del model
+    torch.cuda.empty_cache()
+    return out
+
+
+def extras(device, hbm_gbs, tf_sustained, with_cpu=True):
     """Secondary throughputs (not part of the timed headline): compress / decompress on the bulk prefill shape,
     causal prefill, the paged cache, and the index scan."""
     import quashkv_b200 as qk
@@ -369,6 +454,9 @@ def extras(device, hbm_gbs, tf_sustained):
     small._capacity = small._n_vectors = 1_000_000
     sec = timed(lambda: small.search(qs[:1024], 10), reps=2)
     out["index_search_1M_x1024_queries_s"] = 1024 / sec
+    del index, small, qs
+    torch.cuda.empty_cache()
+    out["config4_llama_generation"] = config4(device, with_cpu=with_cpu)
     return out
 
 
@@ -598,7 +686,7 @@ def run_ours(args):
                                 "sample": CPU_SAMPLE + ", mean of 3 passes"}
     if world == 1 and not args.no_extras:
         del eng
-        extra.update(extras(device, hbm_gbs, tf_sustained))
+        extra.update(extras(device, hbm_gbs, tf_sustained, with_cpu=not args.no_cpu))
         if not args.no_cpu:
             extra["cpu"] = cpu_extras()
     if extra:

@@ -103,3 +103,107 @@ class QuashKVCache:
             "total_compressed_bits": compressed,
             "overall_compression_ratio": original / compressed if compressed > 0 else 0,
         }
+
+
+# ---------------------------------------------------------------------------------------------------
+# The cache as a `transformers.Cache`, with the fused decode route
+# ---------------------------------------------------------------------------------------------------
+# The reference's generation loop (benchmarks/generation_demo.py:222-344) decompresses every layer's whole
+# history for every generated token and rebuilds a DynamicCache from it (hf_cache.py:96-152): its attention never
+# reads the compressed form.  Here the model's attention layers call the packed-cache attention kernel
+# directly: `update` only appends the new tokens, and an attention function registered with transformers'
+# attention interface reads the layer's engine.  Nothing is decompressed in the decode loop.
+
+FUSED_ATTENTION_NAME = "quashkv_fused"
+
+
+def _hf():
+    try:
+        from transformers import AttentionInterface
+        from transformers.cache_utils import Cache, CacheLayerMixin
+        return Cache, CacheLayerMixin, AttentionInterface
+    except ImportError as e:            # transformers is optional for the rest of the package
+        raise ImportError("the HuggingFace cache interface needs the `transformers` package") from e
+
+
+def quashkv_fused_attention(module, query, key, value, attention_mask=None, dropout=0.0, scaling=None, **kwargs):
+    """Attention function for transformers' attention interface: the layer's keys and values have already been
+    appended to its engine by `QuashKVHFCache.update`; `key` / `value` (the new tokens only) and the mask are not
+    read.  Rows of a multi-token call are causal among themselves (prefill); a single-token call sees the whole
+    cache (decode).  Padding masks are not supported: every sequence of the batch has the cache's length."""
+    cache = getattr(module, "quashkv_cache", None)
+    if cache is None:
+        raise RuntimeError("quashkv_fused attention: no QuashKVHFCache attached to this layer (call cache.attach(model))")
+    engine = cache.engines[module.layer_idx]
+    out = engine.attention(query, scale=scaling, causal=query.shape[2] > 1)          # (B, Hq, Q, D) fp32
+    return out.to(query.dtype).transpose(1, 2).contiguous(), None
+
+
+def make_hf_cache(quash_cache: "QuashKVCache", fused: bool = True):
+    """A `transformers.Cache` over the engines of ``quash_cache``.
+
+    fused=True   `update` appends the new tokens and hands them straight back; attention must then run through
+                 `quashkv_fused_attention` (see `attach`), which reads the packed cache.
+    fused=False  `update` returns the whole history decompressed, keys from the code centroids only, as the
+                 reference's cache does (hf_cache.py:96-152); any attention implementation works on it."""
+    Cache, CacheLayerMixin, AttentionInterface = _hf()
+
+    class _Layer(CacheLayerMixin):
+        is_compileable = False
+        is_sliding = False
+
+        def __init__(self, engine):
+            super().__init__()
+            self.engine = engine
+
+        def lazy_initialization(self, key_states, value_states):
+            self.is_initialized = True
+
+        def update(self, key_states, value_states, *args, **kwargs):
+            self.is_initialized = True
+            self.engine.append(key_states, value_states)
+            if fused:
+                return key_states, value_states
+            keys, values = self.engine.decompress_all(with_signs=False)
+            return keys.to(key_states.dtype), values.to(value_states.dtype)
+
+        def get_seq_length(self) -> int:
+            return self.engine.total_tokens
+
+        def get_mask_sizes(self, query_length: int):
+            return self.engine.total_tokens + query_length, 0
+
+        def get_max_cache_shape(self) -> int:
+            return -1
+
+        def reset(self) -> None:
+            self.engine.clear()
+
+    class QuashKVHFCache(Cache):
+        def __init__(self):
+            super().__init__(layers=[_Layer(e) for e in quash_cache.engines])
+            self.engines = quash_cache.engines
+            self.fused = fused
+
+        def attach(self, model):
+            """Point every attention layer of ``model`` at this cache and, for the fused route, switch the model to
+            the packed-cache attention function.  Returns the model's previous attention implementation."""
+            previous = model.config._attn_implementation
+            if fused:
+                from transformers import AttentionMaskInterface
+                from transformers.masking_utils import sdpa_mask
+                AttentionInterface.register(FUSED_ATTENTION_NAME, quashkv_fused_attention)
+                AttentionMaskInterface.register(FUSED_ATTENTION_NAME, sdpa_mask)
+                model.config._attn_implementation = FUSED_ATTENTION_NAME
+            for module in model.modules():
+                if hasattr(module, "layer_idx") and hasattr(module, "q_proj"):
+                    module.quashkv_cache = self
+            return previous
+
+        def detach(self, model, previous: str) -> None:
+            model.config._attn_implementation = previous
+            for module in model.modules():
+                if getattr(module, "quashkv_cache", None) is self:
+                    del module.quashkv_cache
+
+    return QuashKVHFCache()

@@ -860,6 +860,51 @@ def test_hf_cache_update_matches_reference(golden):
     assert fk.shape == (1, 4, 9, 64) and cache.get_seq_length(1) == 9
 
 
+def test_hf_fused_attention_hook_head_dim_64_vs_oracle():
+    """The attention function that transformers calls on the fused route, at the generation benchmark's head shape
+    (32 query heads on 4 KV heads, head_dim 64): prefill rows are causal among themselves, a decode row sees the
+    whole cache; both against the oracle.  The Cache object reports lengths the way transformers asks for them."""
+    pytest.importorskip("transformers")
+    from quashkv_b200.integrations.hf_cache import make_hf_cache, quashkv_fused_attention
+    B, Hq, Hkv, D, S = 2, 32, 4, 64, 70
+    g = torch.Generator().manual_seed(8)
+    K, V = torch.randn(B, Hkv, S + 1, D, generator=g), torch.randn(B, Hkv, S + 1, D, generator=g)
+    Q = torch.randn(B, Hq, S + 1, D, generator=g)
+    qc = QuashKVCache(num_layers=3, head_dim=D, device=DEV)
+    cache = make_hf_cache(qc, fused=True)
+
+    class Layer:                        # what the attention function reads of an attention module
+        layer_idx = 2
+        quashkv_cache = cache
+
+    eng = qc.engines[2]
+    kq, vq = eng.key_quantizer, eng.value_quantizer
+    Pi, Sg = kq.mse_quantizer.Pi.cpu(), kq.S.cpu()
+    kc, kb = kq.mse_quantizer.codebook.centroids.cpu(), kq.mse_quantizer.codebook.boundaries.cpu()
+    mse, sg, kn = orc.compress_ip(K, Pi, kb, kc, Sg)
+    vi, vn = orc.compress_mse(V, Pi, vq.codebook.boundaries.cpu())
+    vc = vq.codebook.centroids.cpu()
+
+    def want(q, n, causal):
+        out = torch.empty(B, Hq, q.shape[2], D)
+        for j in range(Hq // Hkv):      # query head h reads KV head h // G
+            out[:, j::Hq // Hkv] = orc.attention(q[:, j::Hq // Hkv], mse[:, :, :n], sg[:, :, :n], kn[:, :, :n], vi[:, :, :n],
+                                                  vn[:, :, :n], Pi, kc, vc, Sg, kq.qjl_scale, causal=causal, total_tokens=n)
+        return out.transpose(1, 2)
+
+    k_new, v_new = cache.update(K[:, :, :S].to(DEV), V[:, :, :S].to(DEV), 2)         # prefill: S tokens
+    assert k_new.shape == (B, Hkv, S, D) and cache.get_seq_length(2) == S and cache.get_seq_length(0) == 0
+    assert cache.get_mask_sizes(1, 2) == (S + 1, 0)
+    got, weights = quashkv_fused_attention(Layer, Q[:, :, :S].to(DEV), k_new, v_new, None, scaling=D ** -0.5)
+    assert weights is None and got.shape == (B, S, Hq, D)
+    e_prefill = rel_l2(got, want(Q[:, :, :S], S, True))
+    cache.update(K[:, :, S:].to(DEV), V[:, :, S:].to(DEV), 2)                          # one decode step
+    got, _ = quashkv_fused_attention(Layer, Q[:, :, S:].to(DEV), None, None, None, scaling=D ** -0.5)
+    e_decode = rel_l2(got, want(Q[:, :, S:], S + 1, False))
+    print(f"[parity] fused HF attention hook, head_dim 64: prefill rel-L2 {e_prefill:.3e}, decode {e_decode:.3e}")
+    assert e_prefill < FP32_TOL and e_decode < FP32_TOL
+
+
 # ---------------------------------------------------------------------------------------------
 # the C ABI called directly, and its argument checks
 # ---------------------------------------------------------------------------------------------

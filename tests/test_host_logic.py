@@ -250,3 +250,61 @@ def test_device_constants_follow_replaced_and_modified_tensors():
     q.set_outlier_channels(torch.tensor([1, 5, 9]))
     assert q._n_marked == 3 and q._mask_u8.tolist().count(1) == 3 and not q._consts._copies
     assert qk.MSEQuantizer(64, 3).Pi.is_contiguous()
+
+
+def test_hf_cache_plumbing_with_a_stand_in_engine():
+    """The transformers Cache over the engines and the attention function that reads them, on CPU with a stand-in
+    engine that stores K / V and attends exactly: a tiny Llama must give the logits it gives with a DynamicCache,
+    on the fused route (update appends only, attention reads the engine) and on the decompress-everything route."""
+    transformers = pytest.importorskip("transformers")
+    from quashkv_b200.integrations.hf_cache import QuashKVCache, make_hf_cache
+
+    class StandIn:
+        def __init__(self):
+            self.K = self.V = None
+
+        @property
+        def total_tokens(self):
+            return 0 if self.K is None else self.K.shape[2]
+
+        def append(self, k, v):
+            self.K = k.float() if self.K is None else torch.cat([self.K, k.float()], 2)
+            self.V = v.float() if self.V is None else torch.cat([self.V, v.float()], 2)
+
+        def clear(self):
+            self.K = self.V = None
+
+        def decompress_all(self, with_signs=False):
+            return self.K, self.V
+
+        def attention(self, q, scale=None, causal=False):
+            G = q.shape[1] // self.K.shape[1]
+            K, V = self.K.repeat_interleave(G, 1), self.V.repeat_interleave(G, 1)
+            s = (q.float() @ K.transpose(-1, -2)) * scale
+            if causal:
+                n, Q = K.shape[2], q.shape[2]
+                pos = torch.arange(Q) + n - Q
+                s = s.masked_fill(torch.arange(n)[None, :] > pos[:, None], float("-inf"))
+            return torch.softmax(s, -1) @ V
+
+    torch.manual_seed(0)
+    cfg = transformers.LlamaConfig(num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2,
+                                   head_dim=16, intermediate_size=128, vocab_size=100)
+    model = transformers.LlamaForCausalLM(cfg).eval()
+    ids = torch.randint(0, 100, (2, 7))
+    with torch.no_grad():
+        ref = model(input_ids=ids, use_cache=True)
+        nxt = ref.logits[:, -1].argmax(-1, keepdim=True)
+        ref2 = model(input_ids=nxt, past_key_values=ref.past_key_values, use_cache=True)
+        for fused in (True, False):
+            qc = QuashKVCache(2, 16)
+            qc.engines = [StandIn(), StandIn()]
+            cache = make_hf_cache(qc, fused=fused)
+            previous = cache.attach(model)
+            assert model.config._attn_implementation == ("quashkv_fused" if fused else previous)
+            o1 = model(input_ids=ids, past_key_values=cache, use_cache=True)
+            o2 = model(input_ids=nxt, past_key_values=cache, use_cache=True)
+            cache.detach(model, previous)
+            assert model.config._attn_implementation == previous
+            assert torch.allclose(o1.logits, ref.logits, atol=1e-5) and torch.allclose(o2.logits, ref2.logits, atol=1e-5)
+            assert cache.get_seq_length() == 8
