@@ -29,7 +29,8 @@ __global__ void __launch_bounds__(128) rotate_queries_kernel(const void* __restr
                                                              float scale, float* __restrict__ qk,
                                                              const float* __restrict__ kcent,
                                                              const float* __restrict__ vcent,
-                                                             uint32_t* __restrict__ tables, int n_counters) {
+                                                             uint32_t* __restrict__ tables, int n_counters,
+                                                             int rows_per_cta, PlaneImage* __restrict__ planes) {
   // The attention kernel that follows may be launched as a programmatic dependent: let it start right away (it
   // waits for this grid's completion before it reads the rotated queries, the tables or the counters).
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
@@ -41,10 +42,11 @@ __global__ void __launch_bounds__(128) rotate_queries_kernel(const void* __restr
   }
   __shared__ __align__(16) float x_s[kRowsPerCta][kMaxD];
   const int i = threadIdx.x;
-  const int64_t row0 = static_cast<int64_t>(blockIdx.x) * kRowsPerCta;
+  const int64_t row0 = static_cast<int64_t>(blockIdx.x) * rows_per_cta;
+  const int64_t row_end = row0 + rows_per_cta < rows ? row0 + rows_per_cta : rows;
   for (int idx = threadIdx.x; idx < kRowsPerCta * kMaxD; idx += blockDim.x) {
     const int r = idx / kMaxD, j = idx % kMaxD;
-    x_s[r][j] = (row0 + r < rows && j < d) ? load_float(q, q_dtype, (row0 + r) * d + j) : 0.f;
+    x_s[r][j] = (row0 + r < row_end && j < d) ? load_float(q, q_dtype, (row0 + r) * d + j) : 0.f;
   }
   __syncthreads();
   if (i >= d) return;
@@ -76,10 +78,93 @@ __global__ void __launch_bounds__(128) rotate_queries_kernel(const void* __restr
   const float sg = S[i];
 #pragma unroll
   for (int r = 0; r < kRowsPerCta; ++r) {
-    if (row0 + r < rows) {
+    if (row0 + r < row_end) {
       qk[(row0 + r) * 2 * d + i] = acc[r] * scale;
       qk[(row0 + r) * 2 * d + d + i] = (qjl_scale * scale) * (fabsf(acc[r]) * sg);
     }
+  }
+  if (planes == nullptr) return;
+
+  // ---- bit-plane operands of this (batch, kv head): rows row0 .. row_end are its query rows (d == 128) ----
+  // Element (plane, coordinate j) of a token is a bit worth 2^p in its operand byte: p = 2 (j & 3) + plane for
+  // the code planes (plane 0 / 1: low / high bit of the 2-bit key code, coordinates four to a byte), p = j & 7
+  // for the sign plane.  With the key table written as c(u) = g0 + g1 (u & 1) + g2 (u >> 1) the bit weighs
+  // log2e g1 q_j, log2e g2 q_j, or 2 log2e w_j for a sign bit (in the score before the key norm, log2 domain).
+  // The B operand holds y = weight * s / 2^p, s per query row bringing the largest |y| to 127, in radix 128 as
+  // t1 + t2 / 128 + t3 / 128^2 + t4 / 128^3 (signed bytes): columns n and n + 4 of the first accumulator chain
+  // take t1, t2 of row n, those of the second chain t3, t4.  Lane L = 4 n' + t of k-step s holds, in byte i of
+  // register r, the element that the attention kernel cuts out of the lane's word with 0x01010101 << (2 f + r):
+  // code word s >> 2, f = s & 3, coordinate 32 t + 16 (s >> 2) + 4 i + f for s < 8; sign word, f = s - 8,
+  // coordinate 32 t + 8 i + 2 f + r for s >= 8.
+  constexpr float kL2e = 1.4426950408889634f;
+  __shared__ float red_s[4][kRowsPerCta][3];
+  __shared__ float scale_s[kRowsPerCta];
+  const float g0 = kcent[0], g1 = kcent[1] - kcent[0], g2 = kcent[2] - kcent[0];
+  __syncthreads();                                  // everyone is done with the inputs in x_s
+  float (*qs)[kMaxD] = x_s;                         // rotated, scaled queries; sign weights go to w_s
+  __shared__ float w_s[kRowsPerCta][kMaxD];
+  {
+    const float e0 = 1.f / static_cast<float>(1 << (2 * (i & 3))), e2 = 1.f / static_cast<float>(1 << (i & 7));
+    const int lane = i & 31, warp = i >> 5;
+#pragma unroll
+    for (int r = 0; r < kRowsPerCta; ++r) {
+      const bool live = row0 + r < row_end;
+      const float qv = live ? acc[r] * scale : 0.f;
+      const float wv = live ? (qjl_scale * scale) * (fabsf(acc[r]) * sg) : 0.f;
+      qs[r][i] = qv;
+      w_s[r][i] = wv;
+      float mx = fmaxf(fmaxf(fabsf(qv * g1) * e0, fabsf(qv * g2) * (0.5f * e0)), 2.f * fabsf(wv) * e2);
+      float sq = qv, sw = wv;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        mx = fmaxf(mx, __shfl_xor_sync(QKV_FULL_MASK, mx, o));
+        sq += __shfl_xor_sync(QKV_FULL_MASK, sq, o);
+        sw += __shfl_xor_sync(QKV_FULL_MASK, sw, o);
+      }
+      if (lane == 0) { red_s[warp][r][0] = mx; red_s[warp][r][1] = sq; red_s[warp][r][2] = sw; }
+    }
+  }
+  __syncthreads();
+  PlaneImage* img = planes + blockIdx.x;
+  if (i < kRowsPerCta) {
+    float mx = 0.f, sq = 0.f, sw = 0.f;
+    for (int w = 0; w < 4; ++w) { mx = fmaxf(mx, red_s[w][i][0]); sq += red_s[w][i][1]; sw += red_s[w][i][2]; }
+    mx *= kL2e;
+    scale_s[i] = mx > 0.f ? 127.f / mx : 0.f;
+    img->inv[i] = mx * (1.f / 127.f);
+    img->cst[i] = kL2e * (g0 * sq - sw);
+  }
+  __syncthreads();
+  for (int item = i; item < 12 * 32; item += 128) {
+    const int s = item >> 5, L = item & 31, t = L & 3, n = (L >> 2) & 3, hi = L >> 4;
+    const float sc = scale_s[n];
+    uint32_t ra[2] = {0u, 0u}, rb[2] = {0u, 0u};
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        int p; float x;
+        if (s < 8) {
+          p = 2 * (s & 3) + r;
+          x = kL2e * (r ? g2 : g1) * qs[n][32 * t + 16 * (s >> 2) + 4 * b + (s & 3)];
+        } else {
+          p = 2 * (s - 8) + r;
+          x = 2.f * kL2e * w_s[n][32 * t + 8 * b + p];
+        }
+        const float y = x * sc * (1.f / static_cast<float>(1 << p));
+        const float t1 = fminf(fmaxf(rintf(y), -127.f), 127.f);
+        const float r1 = (y - t1) * 128.f;
+        const float t2 = fminf(fmaxf(rintf(r1), -127.f), 127.f);
+        const float r2 = (r1 - t2) * 128.f;
+        const float t3 = fminf(fmaxf(rintf(r2), -127.f), 127.f);
+        const float r3 = (r2 - t3) * 128.f;
+        const float t4 = fminf(fmaxf(rintf(r3), -127.f), 127.f);
+        const int ba = static_cast<int>(hi ? t2 : t1), bb = static_cast<int>(hi ? t4 : t3);
+        ra[r] |= (static_cast<uint32_t>(ba) & 0xFFu) << (8 * b);
+        rb[r] |= (static_cast<uint32_t>(bb) & 0xFFu) << (8 * b);
+      }
+    }
+    img->bop[s][L] = make_uint4(ra[0], ra[1], rb[0], rb[1]);
   }
 }
 
@@ -361,12 +446,15 @@ __global__ void __launch_bounds__(128) merge_splits_kernel(const float* __restri
 }
 
 // Host-side launcher shared with the index scan.
+// rows_per_cta (1..4): query rows per CTA; with `planes` it is the number of query rows of a (batch, kv head),
+// so that CTA k builds plane image k.
 static int launch_rotate(const void* q, int q_dtype, int64_t rows, int d, const float* Pi, const float* S,
                          float qjl_scale, float scale, float* qk, const float* kcent, const float* vcent,
-                         uint32_t* tables, int n_counters, cudaStream_t st) {
-  const unsigned ctas = static_cast<unsigned>((rows + kRowsPerCta - 1) / kRowsPerCta) + (tables ? 1u : 0u);
+                         uint32_t* tables, int n_counters, cudaStream_t st, int rows_per_cta = kRowsPerCta,
+                         PlaneImage* planes = nullptr) {
+  const unsigned ctas = static_cast<unsigned>((rows + rows_per_cta - 1) / rows_per_cta) + (tables ? 1u : 0u);
   rotate_queries_kernel<<<ctas, 128, 0, st>>>(q, q_dtype, rows, d, Pi, S, qjl_scale, scale, qk, kcent, vcent,
-                                              tables, n_counters);
+                                              tables, n_counters, rows_per_cta, planes);
   return check_launch();
 }
 
@@ -464,8 +552,12 @@ int attention_run(const void* q, int q_dtype, qkv_cache_t cache, const uint8_t* 
   const bool chunks_ok = (paged ? paged->block_size % 16 == 0 : cache.capacity % 4 == 0) &&
       ((reinterpret_cast<uintptr_t>(cache.k_norms) | reinterpret_cast<uintptr_t>(cache.v_norms)) & 15u) == 0;
   const bool use_mma = tiled || (mma_path_ok(d, key_bits, val_bits, Hq / Hkv, q_len) && chunks_ok && !force_generic);
+  // tile records with up to four query rows per KV head: scores from bit planes, operands built by the rotation
+  const bool from_planes = tiled && tiled_scores_from_planes(Hq / Hkv, q_len);
+  PlaneImage* planes = from_planes ? reinterpret_cast<PlaneImage*>(ws + p.img_off) : nullptr;
   int rc = launch_rotate(q, q_dtype, p.rows, d, Pi, S, qjl_scale, scale, qk, key_centroids, val_centroids,
-                         use_mma ? tables : nullptr, B * Hkv * (((Hq / Hkv) * q_len + 7) / 8), st);
+                         use_mma ? tables : nullptr, B * Hkv * (((Hq / Hkv) * q_len + 7) / 8), st,
+                         from_planes ? (Hq / Hkv) * q_len : kRowsPerCta, planes);
   if (rc) return rc;
 
   AttnArgs a{};
@@ -484,6 +576,7 @@ int attention_run(const void* q, int q_dtype, qkv_cache_t cache, const uint8_t* 
     a.Pi = Pi;
     a.out = out;
     a.records = records;
+    a.planes = planes;
     return tiled ? launch_attend_tiled(a, st) : launch_attend_mma(a, st);
   } else {
     const dim3 grid(p.n_splits, p.n_qtiles, B * Hkv);

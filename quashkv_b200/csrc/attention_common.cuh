@@ -12,6 +12,15 @@ constexpr int kQT = 4;          // query rows per CTA
 constexpr int kAttnWarps = 4;
 constexpr int kMaxSplits = 64;
 
+// Bit-plane scores of the tiled path (up to four query rows per KV head): what a CTA needs of its (batch, kv head)
+// besides the records, built once by the query-rotation kernel and fetched with one bulk copy.
+struct PlaneImage {
+  uint4 bop[12][32];    // B operands per k-step and lane: both accumulator chains
+  float inv[4];         // score units per unit of the first term, per query row
+  float cst[4];         // the score of a token whose bits are all clear, per query row
+};
+static_assert(sizeof(PlaneImage) % 16 == 0, "fetched with a bulk copy");
+
 struct AttnArgs {
   qkv_cache_t cache;
   int B, Hq, Hkv, G, q_len, d, causal;
@@ -34,6 +43,7 @@ struct AttnArgs {
   // contiguous: cache.capacity / 16 records per (batch, kv head); paged: block_size / 16 records per
   // (block, kv head).
   const uint8_t* records;
+  const PlaneImage* planes; // tiled path, bit-plane scores: one image per (batch, kv head), else nullptr
 };
 
 // Tensor-core path: the KV range is cut into splits of UNEQUAL length, in 128-token chunks, the longest first:
@@ -56,7 +66,8 @@ constexpr size_t kAttnHeaderBytes = 256;   // workspace header: look-up tables o
 
 struct AttnPlan {
   int n_splits; int64_t split_len; int n_qtiles; int64_t rows;
-  size_t hdr_bytes;     // look-up tables (first 256 bytes) + the arrival counters of the tensor-core path
+  size_t hdr_bytes;     // look-up tables (first 256 bytes), the arrival counters of the tensor-core path, plane images
+  size_t img_off;       // offset of the plane images (one per batch entry and kv head) inside the header
   size_t qk_bytes, part_bytes;
 };
 
@@ -108,7 +119,9 @@ inline AttnPlan make_plan(int B, int Hq, int Hkv, int q_len, int64_t kv_len, int
   p.n_splits = static_cast<int>((kv_len + len - 1) / len);
   if (p.n_splits < 1) p.n_splits = 1;
   // arrival counters: one per (batch, kv head, tile of eight query rows) of the tensor-core path
-  p.hdr_bytes = (kAttnHeaderBytes + static_cast<size_t>(B) * Hkv * ((nq + 7) / 8) * sizeof(unsigned) + 255) / 256 * 256;
+  p.img_off = (kAttnHeaderBytes + static_cast<size_t>(B) * Hkv * ((nq + 7) / 8) * sizeof(unsigned) + 255) / 256 * 256;
+  p.hdr_bytes = p.img_off;
+  if (d == 128 && nq <= 4) p.hdr_bytes = (p.img_off + static_cast<size_t>(B) * Hkv * sizeof(PlaneImage) + 255) / 256 * 256;
   p.qk_bytes = static_cast<size_t>(p.rows) * 2 * d * sizeof(float);
   p.qk_bytes = (p.qk_bytes + 255) / 256 * 256;
   p.part_bytes = static_cast<size_t>(p.rows) * p.n_splits * (d + 2) * sizeof(float);
@@ -122,6 +135,7 @@ int launch_attend_mma(const AttnArgs& a, cudaStream_t st);
 
 // Tensor-core path over tile records (attention_tiled.cu).
 bool tiled_path_ok(int d, int key_bits, int val_bits);
+bool tiled_scores_from_planes(int group, int q_len);      // up to four query rows per KV head (and not switched off)
 int launch_attend_tiled(const AttnArgs& a, cudaStream_t st);
 unsigned int bulk_copy_timeouts();        // bounded waits on a record copy that ran out (device-wide counter)
 
@@ -130,7 +144,9 @@ unsigned int bulk_copy_timeouts();        // bounded waits on a record copy that
 // error of s*c_i smallest, so the systematic error of the fp16 operands drops well below 2^-12.
 // tables[0..1] key centroids as fp16 pairs, [2..3] value low bytes, [4..5] value high bytes,
 // [6] 1/key scale, [7] 1/value scale (floats), [8..9] the four value magnitudes (entries 4..7 of the
-// value table, the positive half of a symmetric table) as fp16 pairs for the sign-and-magnitude records.
+// value table, the positive half of a symmetric table) as fp16 pairs for the sign-and-magnitude records,
+// [10] contract flags (bit 0: the value table is not symmetric, bit 1: the key table is not affine in the two
+// bits of its code), [11..13] g0, g1, g2 of the key table written as c(u) = g0 + g1 (u & 1) + g2 (u >> 1).
 __device__ inline void prepare_tables_cta(const float* __restrict__ kcent, const float* __restrict__ vcent,
                                           uint32_t* __restrict__ tables) {
   __shared__ float cand_err[2][128];
@@ -184,6 +200,15 @@ __device__ inline void prepare_tables_cta(const float* __restrict__ kcent, const
   tables[9] = mg[1];
   tables[6] = __float_as_uint(1.f / sc[0]);
   tables[7] = __float_as_uint(1.f / sc[1]);
+  float kmax = 0.f, vmax = 0.f, vasym = 0.f;
+  for (int i = 0; i < 4; ++i) kmax = fmaxf(kmax, fabsf(kcent[i]));
+  for (int i = 0; i < 8; ++i) vmax = fmaxf(vmax, fabsf(vcent[i]));
+  for (int i = 0; i < 4; ++i) vasym = fmaxf(vasym, fabsf(vcent[i] + vcent[7 - i]));
+  const float kbend = fabsf((kcent[3] - kcent[2]) - (kcent[1] - kcent[0]));
+  tables[10] = (vasym > 1e-5f * vmax ? 1u : 0u) | (kbend > 1e-5f * kmax ? 2u : 0u);
+  tables[11] = __float_as_uint(kcent[0]);
+  tables[12] = __float_as_uint(kcent[1] - kcent[0]);
+  tables[13] = __float_as_uint(kcent[2] - kcent[0]);
 }
 
 }  // namespace qkv

@@ -15,9 +15,18 @@
 // and applies Pi once, which equals un-rotating every value (engine.py:284-287) because the rotation
 // is linear.
 //
-// With at most four query rows per KV head (decode with up to four query heads per KV head) the
-// columns 4..7 of the score MMAs carry the fp16 rounding residual of the queries, so the scores see
-// the query at twice fp16 precision at no extra MMA.
+// With at most four query rows per KV head (decode with up to four query heads per KV head) the scores
+// are computed on the INTEGER tensor cores from bit planes (MODE 2).  A 4-level key table that is affine in
+// the two bits of its code, c(u) = g0 + g1 b0 + g2 b1 (true of every table with c0 + c3 = c1 + c2, so of
+// every symmetric one), turns the score into a constant plus a weighted sum over single bits: of the two code
+// bits and of the sign bit of every coordinate.  `word & (0x01010101 << p)` IS an unsigned 8-bit A operand
+// (four elements, each 0 or 2^p) of mma.m16n8k32.u8.s8, so a register of four operand elements costs one
+// logic instruction and no shift, against three instructions per TWO elements of the fp16 path; the query
+// side carries weight / 2^p as four signed 8-bit terms (radix 128, a common scale per query), two per
+// accumulator chain in the column pairs (n, n + 4), which is exact integer arithmetic to 2^-21 of the largest
+// weight.  The accumulators start at the bit pattern of 1.5 * 2^23, so the integer sums read back as floats
+// with one subtraction.  (The fp16 form of the same idea, MODE 1, puts the fp16 rounding residual of the
+// queries into columns 4..7; it is kept for comparison, QUASHKV_B200_SCORES=fp16.)
 #include <math.h>
 #include <stdlib.h>
 
@@ -32,7 +41,7 @@ namespace {
 
 constexpr int kWarps = 4;
 // Ring slots per warp: three records in flight while one is worked on.  (Five or six resident CTAs per SM,
-// 94 / 80 registers, measured 4 % / 8 % slower than four.)
+// 96 / 80 registers, measured 6 % / 10 % slower than four at their best split counts.)
 constexpr int kRing = 4;
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -59,24 +68,46 @@ struct TileRegs {
   float4 nrm;     // key norms of tokens g, g + 8; value norms of tokens g, g + 8
 };
 
-template <bool PAGED, bool LO4>
+// u8 x s8 -> s32, m16n8k32
+__device__ __forceinline__ void imma16832(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// MODE 0: up to eight query rows, fp16 scores.  MODE 1: up to four rows, fp16 scores with the residual of the
+// queries in columns 4..7.  MODE 2: up to four rows, scores from bit planes on the integer tensor cores.
+template <bool PAGED, int MODE>
 __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a) {
+  constexpr bool LO4 = MODE != 0;                    // query columns n and n + 4 belong to the same query row
+  constexpr bool PLANES = MODE == 2;
   constexpr int D = 128;
   constexpr int kTile = tile::kTokens;
-  __shared__ float q_s[8][2 * D];                    // [query row][q_rot*scale | sign weights]
   // the per-warp record rings of the token loop and the end-of-kernel reduction share storage
   constexpr int kRingBytes = kWarps * kRing * tile::kBytes;
   constexpr int kRedBytes = kWarps * 8 * (D + 2) * 4;
   __shared__ __align__(128) unsigned char pool[kRingBytes > kRedBytes ? kRingBytes : kRedBytes];
   float (*red)[8][D + 2] = reinterpret_cast<float (*)[8][D + 2]>(pool);   // [warp][query][max, sum, acc]
   __shared__ __align__(8) uint64_t bars[kWarps][kRing];
-  __shared__ float wsum[8];                          // sum of the sign weights per query column
-  __shared__ uint4 bop[8][32];                       // B operands of two k-steps per lane: 8 key-code steps, then 8 sign steps
+  __shared__ float wsum[8];                          // fp16 scores: sum of the sign weights per query column
+  // B operands per lane.  fp16 scores: two k-steps per entry, 8 key-code steps, then 8 sign steps.  Bit planes:
+  // the image that the rotation kernel built for this (batch, kv head): one k-step per entry (both accumulator
+  // chains), 8 steps on the code words, then 4 on the sign words, followed by the constants of the query rows.
+  __shared__ __align__(16) unsigned char opbuf[PLANES ? sizeof(PlaneImage) : 8 * 32 * sizeof(uint4)];
+  uint4 (*bop)[32] = reinterpret_cast<uint4 (*)[32]>(opbuf);
+  __shared__ __align__(8) uint64_t img_bar;
   __shared__ uint32_t vtab[64][32];                  // value table: entry (6-bit field) x lane, an fp16 pair each
+  // [query row][q_rot*scale | sign weights]: only read while the B operands are built, before the value table
+  // (same size) is written over it
+  float (*q_s)[2 * D] = reinterpret_cast<float (*)[2 * D]>(&vtab[0][0]);
+  static_assert(sizeof(vtab) == 8 * 2 * D * sizeof(float), "the queries are staged in the value table's storage");
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gid = lane >> 2, tig = lane & 3;
-  const int split = blockIdx.z, seg = blockIdx.x;     // splits are the slowest dimension: longest first
+  // Splits are the slowest grid dimension: longest first.  (The splits of a head in consecutive CTAs, so that the
+  // CTAs sharing an SM differ in length, measured 5-15 % slower.)
+  const int split = blockIdx.z, seg = blockIdx.x;
   const int b = seg / a.Hkv, hkv = seg % a.Hkv;
   // Query rows of a (batch, kv head) are numbered g * q_len + position; a CTA takes eight of them
   // (blockIdx.y), so decode (one tile) and prefill (many) run through the same code.
@@ -121,6 +152,7 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < kRing; ++s) umma::mbar_init(bar + s, 1);
+    if (PLANES && warp == 0) umma::mbar_init(&img_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncwarp();
@@ -149,61 +181,71 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
   // look-up tables and the zeroed arrival counters are needed: wait for that kernel to have completed.
   asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
-  // In LO4 mode query column n >= 4 is the residual of column n - 4.
-  for (int idx = threadIdx.x; has_work && idx < 8 * 2 * D; idx += blockDim.x) {
-    const int r = idx / (2 * D), e = idx % (2 * D);
-    const int rq = LO4 ? (r & 3) : r;
-    float v = 0.f;
-    if (rq < nq) {
-      const int g = (r0 + rq) / a.q_len, qi = (r0 + rq) % a.q_len;
-      const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
-      v = a.qk[qrow * 2 * D + e];
+  if (PLANES) {
+    // bit planes: everything the scores need of the queries is the image of this (batch, kv head)
+    if (has_work && threadIdx.x == 0) {
+      mbar_expect_tx(&img_bar, sizeof(PlaneImage));
+      bulk_load(opbuf, a.planes + seg, sizeof(PlaneImage), &img_bar);
     }
-    q_s[r][e] = v;
-  }
-  __syncthreads();
-  if (has_work) {                   // a warp sums the sign weights of two query columns
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int col = 2 * warp + h;
-      const float* w = q_s[col] + D;
-      float t = (w[lane] + w[lane + 32]) + (w[lane + 64] + w[lane + 96]);
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(QKV_FULL_MASK, t, o);
-      if (lane == 0) wsum[col] = (LO4 && col >= 4) ? 0.f : t * kLog2e;
+  } else {
+    // In LO4 mode query column n >= 4 is the residual of column n - 4.
+    for (int idx = threadIdx.x; has_work && idx < 8 * 2 * D; idx += blockDim.x) {
+      const int r = idx / (2 * D), e = idx % (2 * D);
+      const int rq = LO4 ? (r & 3) : r;
+      float v = 0.f;
+      if (rq < nq) {
+        const int g = (r0 + rq) / a.q_len, qi = (r0 + rq) % a.q_len;
+        const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
+        v = a.qk[qrow * 2 * D + e];
+      }
+      q_s[r][e] = v;
     }
+    __syncthreads();
   }
-  __syncthreads();
-
-  // ---- B operands for query column n = gid ---------------------------------------------------------
-  // Key-code k-step s = 4*word + f covers this lane's coordinates 32 tig + 16 word + {f, 4+f | 8+f, 12+f}
-  // (the order in which tile::key_fragment produces them).  Sign k-step s covers 32 tig + {2s, 2s+16 | 2s+1, 2s+17}
-  // through sign_coord / sign_pos.
   const float inv_sk = __uint_as_float(a.tables[6]), inv_sv = __uint_as_float(a.tables[7]);
-  if (has_work) {                   // the operands depend on the lane only: each warp builds two k-steps
-    const float qf = kLog2e * inv_sk;
-    const float* q = q_s[gid];
-    const float* w = q_s[gid] + D;
-    const bool resid = LO4 && gid >= 4;
+  if (!PLANES) {
+    if (has_work) {                   // a warp sums the sign weights of two query columns
 #pragma unroll
-    for (int s = warp; s < 8; s += kWarps) {
-      const int word = s >> 2, f = s & 3;
-      const int c0 = 32 * tig + 16 * word + f;
-      float v[4];
+      for (int h = 0; h < 2; ++h) {
+        const int col = 2 * warp + h;
+        const float* w = q_s[col] + D;
+        float t = (w[lane] + w[lane + 32]) + (w[lane + 64] + w[lane + 96]);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        v[e] = q[c0 + 4 * e] * qf;
-        if (resid) v[e] -= __half2float(__float2half_rn(v[e]));
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(QKV_FULL_MASK, t, o);
+        if (lane == 0) wsum[col] = (LO4 && col >= 4) ? 0.f : t * kLog2e;
       }
-      reinterpret_cast<uint2*>(&bop[s >> 1][lane])[s & 1] = make_uint2(pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
-      uint32_t wq[2];
+    }
+    __syncthreads();
+
+    // ---- B operands for query column n = gid ---------------------------------------------------------
+    // Key-code k-step s = 4*word + f covers this lane's coordinates 32 tig + 16 word + {f, 4+f | 8+f, 12+f}
+    // (the order in which tile::key_fragment produces them).  Sign k-step s covers 32 tig + {2s, 2s+16 | 2s+1, 2s+17}
+    // through sign_coord / sign_pos.
+    if (has_work) {                   // the operands depend on the lane only: each warp builds two k-steps
+      const float qf = kLog2e * inv_sk;
+      const float* q = q_s[gid];
+      const float* w = q_s[gid] + D;
+      const bool resid = LO4 && gid >= 4;
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {           // pairs t = 2s, 2s+1 of this lane's 32 coordinates
-        const int t = 2 * s + h, j = 32 * tig + sign_coord(t);
-        const float fs = resid ? 0.f : 2.f * kLog2e / sign_v1(sign_pos(t));
-        wq[h] = pack_half2(w[j] * fs, w[j + 16] * fs);
+      for (int s = warp; s < 8; s += kWarps) {
+        const int word = s >> 2, f = s & 3;
+        const int c0 = 32 * tig + 16 * word + f;
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          v[e] = q[c0 + 4 * e] * qf;
+          if (resid) v[e] -= __half2float(__float2half_rn(v[e]));
+        }
+        reinterpret_cast<uint2*>(&bop[s >> 1][lane])[s & 1] = make_uint2(pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
+        uint32_t wq[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {           // pairs t = 2s, 2s+1 of this lane's 32 coordinates
+          const int t = 2 * s + h, j = 32 * tig + sign_coord(t);
+          const float fs = resid ? 0.f : 2.f * kLog2e / sign_v1(sign_pos(t));
+          wq[h] = pack_half2(w[j] * fs, w[j + 16] * fs);
+        }
+        reinterpret_cast<uint2*>(&bop[4 + (s >> 1)][lane])[s & 1] = make_uint2(wq[0], wq[1]);
       }
-      reinterpret_cast<uint2*>(&bop[4 + (s >> 1)][lane])[s & 1] = make_uint2(wq[0], wq[1]);
     }
   }
   __syncthreads();
@@ -241,12 +283,64 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
   // the token loop needs no test for minus infinity; the value written out below turns it back into -inf
   constexpr float kNone = -1e30f;
   float m[2] = {kNone, kNone}, l[2] = {0.f, 0.f};
-  const float ci0 = -wsum[2 * tig], ci1 = -wsum[2 * tig + 1];   // accumulator start: -sum of sign weights
+  // fp16 scores: the accumulators start at -sum of the sign weights.  Bit planes: columns 2 tig, 2 tig + 1 hold
+  // terms (t1, t3) of queries 2 tig + e for tig < 2, terms (t2, t4) of queries 2 (tig - 2) + e otherwise; kA, kB
+  // turn the two integer sums into score units and ci is the constant of the query (counted once, by tig < 2).
+  float ci0 = 0.f, ci1 = 0.f, kA[2] = {0.f, 0.f}, kB[2] = {0.f, 0.f};
+  bool img_failed = false;
+  if (PLANES) {
+    if (has_work) {
+      // the image copy was issued before the value table was built: it has normally landed by now
+      img_failed = !__all_sync(QKV_FULL_MASK, umma::mbar_wait(&img_bar, 0));
+      const PlaneImage* img = reinterpret_cast<const PlaneImage*>(opbuf);
+      const int hi = tig >> 1;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float u = img->inv[(2 * tig + e) & 3];
+        kA[e] = hi ? u * (1.f / 128.f) : u;
+        kB[e] = hi ? u * (1.f / 2097152.f) : u * (1.f / 16384.f);
+      }
+      ci0 = hi ? 0.f : img->cst[(2 * tig) & 3];
+      ci1 = hi ? 0.f : img->cst[(2 * tig + 1) & 3];
+    }
+  } else {
+    ci0 = -wsum[2 * tig];
+    ci1 = -wsum[2 * tig + 1];
+  }
 
   auto process = [&](const TileRegs& cur, int rel) {
     const bool masked = a.causal || rel + kTile > n_valid;      // warp-uniform
+    float c[4];
+    if constexpr (PLANES) {
+      // ---- scores from bit planes: 12 k-steps of 32 single-bit elements, two integer accumulator chains ----
+      constexpr int kMagic = 0x4B400000;                         // bit pattern of 1.5 * 2^23
+      int ia[4] = {kMagic, kMagic, kMagic, kMagic}, ib[4] = {kMagic, kMagic, kMagic, kMagic};
+      uint32_t af[4];
+      uint4 bq;
+#define QKV_PLANE_STEP(S, W0, W1, P)                                    \
+  bq = bop[S][lane];                                                    \
+  af[0] = (W0) & (0x01010101u << (P));                                  \
+  af[1] = (W1) & (0x01010101u << (P));                                  \
+  af[2] = (W0) & (0x01010101u << ((P) + 1));                            \
+  af[3] = (W1) & (0x01010101u << ((P) + 1));                            \
+  imma16832(ia, af, bq.x, bq.y);                                        \
+  imma16832(ib, af, bq.z, bq.w);
+      QKV_PLANE_STEP(0, cur.kc.x, cur.kc.z, 0) QKV_PLANE_STEP(1, cur.kc.x, cur.kc.z, 2)
+      QKV_PLANE_STEP(2, cur.kc.x, cur.kc.z, 4) QKV_PLANE_STEP(3, cur.kc.x, cur.kc.z, 6)
+      QKV_PLANE_STEP(4, cur.kc.y, cur.kc.w, 0) QKV_PLANE_STEP(5, cur.kc.y, cur.kc.w, 2)
+      QKV_PLANE_STEP(6, cur.kc.y, cur.kc.w, 4) QKV_PLANE_STEP(7, cur.kc.y, cur.kc.w, 6)
+      QKV_PLANE_STEP(8, cur.ks.x, cur.ks.y, 0) QKV_PLANE_STEP(9, cur.ks.x, cur.ks.y, 2)
+      QKV_PLANE_STEP(10, cur.ks.x, cur.ks.y, 4) QKV_PLANE_STEP(11, cur.ks.x, cur.ks.y, 6)
+#undef QKV_PLANE_STEP
+      constexpr float kMagicF = 12582912.f;                      // the sums are below 2^22 in magnitude: exact
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float fa = __int_as_float(ia[e]) - kMagicF, fb = __int_as_float(ib[e]) - kMagicF;
+        c[e] = fmaf(fa, kA[e & 1], fmaf(fb, kB[e & 1], (e & 1) ? ci1 : ci0));
+      }
+    } else {
     // ---- scores: 8 MMAs on key codes, 8 on sign bits --------------------------------------------
-    float c[4] = {ci0, ci1, ci0, ci1};
+    c[0] = ci0; c[1] = ci1; c[2] = ci0; c[3] = ci1;
     {
       uint32_t af[4];
       uint4 bq;
@@ -282,7 +376,8 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
         }
       }
     }
-    if (LO4) {                      // column n + 4 holds the residual part of column n: add the two
+    }
+    if (LO4) {                      // column n + 4 holds the other part of column n: add the two
 #pragma unroll
       for (int e = 0; e < 4; ++e) c[e] += __shfl_xor_sync(QKV_FULL_MASK, c[e], 2);
     }
@@ -385,6 +480,7 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
     for (int it = it_failed + 1; it < n_it && it < it_failed + kRing; ++it)
       umma::mbar_wait(bar + it % kRing, (it / kRing) & 1);
   }
+  if (img_failed && lane == 0) atomicAdd(&g_bulk_timeouts, 1u);   // same for the operand image (its storage is not reused)
   __syncthreads();                        // the reduction buffer below reuses the ring storage
 
   // ---- per-warp results to shared memory: column sums over the token lanes, then all warps ------
@@ -505,10 +601,13 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
 #pragma unroll
       for (int r = 0; r < 8; ++r) o[r] = fmaf(vec[r * D + j], mval, o[r]);
     }
+    // A table that breaks what the record format (symmetric value table) or the bit planes (key table affine in
+    // its code bits) presume would give wrong numbers silently: give NaN instead.
+    const bool broken = (a.tables[10] & (PLANES ? 3u : 1u)) != 0u;
     for (int r = 0; r < nq; ++r) {
       const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
       const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
-      a.out[qrow * D + i] = o[r];
+      a.out[qrow * D + i] = broken ? __int_as_float(0x7fc00000) : o[r];
     }
   }
 }
@@ -523,6 +622,13 @@ unsigned int bulk_copy_timeouts() {
 
 
 bool tiled_path_ok(int d, int key_bits, int val_bits) { return d == 128 && key_bits == 3 && val_bits == 3; }
+
+// QUASHKV_B200_SCORES=fp16 keeps the fp16 scores everywhere (for comparison).
+bool tiled_scores_from_planes(int group, int q_len) {
+  if (group * q_len > 4) return false;
+  const char* e = getenv("QUASHKV_B200_SCORES");
+  return !(e && e[0] == 'f');
+}
 
 int launch_attend_tiled(const AttnArgs& a_in, cudaStream_t st) {
   const dim3 grid(a_in.B * a_in.Hkv, (a_in.G * a_in.q_len + 7) / 8, a_in.n_splits);
@@ -539,15 +645,19 @@ int launch_attend_tiled(const AttnArgs& a_in, cudaStream_t st) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const bool lo4 = a_in.G * a_in.q_len <= 4;      // spare query columns carry the fp16 residual of the queries
+  // up to four query rows: scores from bit planes on the integer tensor cores, when the caller had the
+  // rotation kernel build the operand images; else the fp16 form
+  const int mode = a_in.G * a_in.q_len <= 4 ? (a_in.planes ? 2 : 1) : 0;
   const AttnArgs& a = a_in;
   cudaError_t err;
   if (a.block_table)
-    err = lo4 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<true, true>, a)
-              : cudaLaunchKernelEx(&cfg, attend_tiled_kernel<true, false>, a);
+    err = mode == 2 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<true, 2>, a)
+        : mode == 1 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<true, 1>, a)
+                    : cudaLaunchKernelEx(&cfg, attend_tiled_kernel<true, 0>, a);
   else
-    err = lo4 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, true>, a)
-              : cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, false>, a);
+    err = mode == 2 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, 2>, a)
+        : mode == 1 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, 1>, a)
+                    : cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, 0>, a);
   if (err != cudaSuccess) return QKV_ELAUNCH;
   return check_launch();
 }

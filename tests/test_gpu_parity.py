@@ -517,13 +517,15 @@ def test_decode_gqa_bf16_vs_oracle(golden, S, appends):
 
 
 @pytest.mark.parametrize("G,q_len,causal", [(4, 1, False), (8, 1, False), (4, 2, True), (1, 8, True), (2, 3, False),
-                                            (4, 37, True), (2, 16, False), (1, 200, True), (3, 5, True)])
+                                            (4, 37, True), (2, 16, False), (1, 200, True), (3, 5, True),
+                                            (1, 1, False), (3, 1, False), (2, 2, True), (1, 4, True)])
 def test_tensor_core_decode_path_vs_generic_and_oracle(G, q_len, causal, monkeypatch):
     """head_dim 128 with 3/3 bits takes the tensor-core kernel over tile records, eight query rows of a KV head
     per CTA (one tile for decode, many for prefill, a last partial tile, tiles that straddle two query
     heads); it must agree with the oracle, with the tensor-core kernel over row-major planes and with the
     generic kernel on the same tokens (ragged length, so the last tile and the last split are partial;
-    causal rows see different lengths)."""
+    causal rows see different lengths).  With at most four query rows per KV head the scores come from bit
+    planes on the integer tensor cores; the fp16 form of the same kernel is run beside it."""
     B, Hkv, S, D = 2, 3, 1000 + 13, 128
     K, V = _outlier_kv(B, Hkv, S, D, 5, torch.float32)
     eng = qk.QuashKVEngine(D, 3, 3, seed=42, pack_storage=True)
@@ -531,6 +533,9 @@ def test_tensor_core_decode_path_vs_generic_and_oracle(G, q_len, causal, monkeyp
     eng.append(K.to(DEV), V.to(DEV))
     Q = torch.randn(B, Hkv * G, q_len, D, generator=torch.Generator().manual_seed(9))
     fast = eng.attention(Q.to(DEV), causal=causal)
+    monkeypatch.setenv("QUASHKV_B200_SCORES", "fp16")
+    fast16 = eng.attention(Q.to(DEV), causal=causal)
+    monkeypatch.delenv("QUASHKV_B200_SCORES")
     monkeypatch.setenv("QUASHKV_B200_ROW_STORAGE", "1")
     rows = qk.QuashKVEngine(D, 3, 3, seed=42, pack_storage=True)
     monkeypatch.delenv("QUASHKV_B200_ROW_STORAGE")
@@ -552,9 +557,12 @@ def test_tensor_core_decode_path_vs_generic_and_oracle(G, q_len, causal, monkeyp
     for g in range(G):
         want[:, g::G] = orc.attention(Q[:, g::G], *planes, causal=causal, total_tokens=S)
     e_fast, e_mid, e_slow = rel_l2(fast, want), rel_l2(mid, want), rel_l2(slow, want)
-    print(f"[parity] G={G} q_len={q_len} causal={causal}: tile records rel-L2 {e_fast:.3e}, row-major tensor-core "
-          f"{e_mid:.3e}, generic {e_slow:.3e}")
-    assert e_slow < 1e-5 and e_mid < FP32_TOL and e_fast < FP32_TOL
+    e_fast16 = rel_l2(fast16, want)
+    print(f"[parity] G={G} q_len={q_len} causal={causal}: tile records rel-L2 {e_fast:.3e} (fp16 scores "
+          f"{e_fast16:.3e}), row-major tensor-core {e_mid:.3e}, generic {e_slow:.3e}")
+    assert e_slow < 1e-5 and e_mid < FP32_TOL and e_fast < FP32_TOL and e_fast16 < FP32_TOL
+    if G * q_len > 4:
+        assert torch.equal(fast, fast16)              # one kernel: the switch only exists for four rows or fewer
     assert _lib.lib().qkv_tensor_core_timeouts() == TIMEOUTS[0]
 
 
