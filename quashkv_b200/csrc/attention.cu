@@ -29,8 +29,7 @@ __global__ void __launch_bounds__(128) rotate_queries_kernel(const void* __restr
                                                              float scale, float* __restrict__ qk,
                                                              const float* __restrict__ kcent,
                                                              const float* __restrict__ vcent,
-                                                             uint32_t* __restrict__ tables, int n_counters,
-                                                             int rows_per_cta, PlaneImage* __restrict__ planes) {
+                                                             uint32_t* __restrict__ tables, int n_counters) {
   // The attention kernel that follows may be launched as a programmatic dependent: let it start right away (it
   // waits for this grid's completion before it reads the rotated queries, the tables or the counters).
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
@@ -42,11 +41,10 @@ __global__ void __launch_bounds__(128) rotate_queries_kernel(const void* __restr
   }
   __shared__ __align__(16) float x_s[kRowsPerCta][kMaxD];
   const int i = threadIdx.x;
-  const int64_t row0 = static_cast<int64_t>(blockIdx.x) * rows_per_cta;
-  const int64_t row_end = row0 + rows_per_cta < rows ? row0 + rows_per_cta : rows;
+  const int64_t row0 = static_cast<int64_t>(blockIdx.x) * kRowsPerCta;
   for (int idx = threadIdx.x; idx < kRowsPerCta * kMaxD; idx += blockDim.x) {
     const int r = idx / kMaxD, j = idx % kMaxD;
-    x_s[r][j] = (row0 + r < row_end && j < d) ? load_float(q, q_dtype, (row0 + r) * d + j) : 0.f;
+    x_s[r][j] = (row0 + r < rows && j < d) ? load_float(q, q_dtype, (row0 + r) * d + j) : 0.f;
   }
   __syncthreads();
   if (i >= d) return;
@@ -78,77 +76,115 @@ __global__ void __launch_bounds__(128) rotate_queries_kernel(const void* __restr
   const float sg = S[i];
 #pragma unroll
   for (int r = 0; r < kRowsPerCta; ++r) {
-    if (row0 + r < row_end) {
+    if (row0 + r < rows) {
       qk[(row0 + r) * 2 * d + i] = acc[r] * scale;
       qk[(row0 + r) * 2 * d + d + i] = (qjl_scale * scale) * (fabsf(acc[r]) * sg);
     }
   }
-  if (planes == nullptr) return;
+}
 
-  // ---- bit-plane operands of this (batch, kv head): rows row0 .. row_end are its query rows (d == 128) ----
-  // Element (plane, coordinate j) of a token is a bit worth 2^p in its operand byte: p = 2 (j & 3) + plane for
-  // the code planes (plane 0 / 1: low / high bit of the 2-bit key code, coordinates four to a byte), p = j & 7
-  // for the sign plane.  With the key table written as c(u) = g0 + g1 (u & 1) + g2 (u >> 1) the bit weighs
-  // log2e g1 q_j, log2e g2 q_j, or 2 log2e w_j for a sign bit (in the score before the key norm, log2 domain).
-  // The B operand holds y = weight * s / 2^p, s per query row bringing the largest |y| to 127, in radix 128 as
-  // t1 + t2 / 128 + t3 / 128^2 + t4 / 128^3 (signed bytes): columns n and n + 4 of the first accumulator chain
-  // take t1, t2 of row n, those of the second chain t3, t4.  Lane L = 4 n' + t of k-step s holds, in byte i of
-  // register r, the element that the attention kernel cuts out of the lane's word with 0x01010101 << (2 f + r):
-  // code word s >> 2, f = s & 3, coordinate 32 t + 16 (s >> 2) + 4 i + f for s < 8; sign word, f = s - 8,
-  // coordinate 32 t + 8 i + 2 f + r for s >= 8.
+
+// Query rotation for the tiled attention with scores from bit planes (head_dim 128, up to four query rows per
+// KV head): CTA k rotates the rows of (batch, kv head) k, 128 threads per row, and builds plane image k; one
+// extra CTA prepares the look-up tables and zeroes the arrival counters.
+//
+// Element (plane, coordinate j) of a token is a bit worth 2^p in its operand byte: p = 2 (j & 3) + plane for
+// the code planes (plane 0 / 1: low / high bit of the 2-bit key code, coordinates four to a byte), p = j & 7
+// for the sign plane.  With the key table written as c(u) = g0 + g1 (u & 1) + g2 (u >> 1) the bit weighs
+// log2e g1 q_j, log2e g2 q_j, or 2 log2e w_j for a sign bit (in the score before the key norm, log2 domain).
+// The B operand holds y = weight * s / 2^p, s per query row bringing the largest |y| to 127, in radix 128 as
+// t1 + t2 / 128 + t3 / 128^2 + t4 / 128^3 (signed bytes): columns n and n + 4 of the first accumulator chain
+// take t1, t2 of row n, those of the second chain t3, t4.  Lane L = 4 n' + t of k-step s holds, in byte b of
+// register r, the element that the attention kernel cuts out of the lane's word with 0x01010101 << (2 f + r):
+// code word s >> 2, f = s & 3, coordinate 32 t + 16 (s >> 2) + 4 b + f for s < 8; sign word, f = s - 8,
+// coordinate 32 t + 8 b + 2 f + r for s >= 8.
+__global__ void __launch_bounds__(512) rotate_planes_kernel(const void* __restrict__ q, int q_dtype, int64_t rows,
+                                                            const float* __restrict__ Pi, const float* __restrict__ S,
+                                                            float qjl_scale, float scale, float* __restrict__ qk,
+                                                            const float* __restrict__ kcent,
+                                                            const float* __restrict__ vcent,
+                                                            uint32_t* __restrict__ tables, int n_counters,
+                                                            int rows_per_cta, PlaneImage* __restrict__ planes) {
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  if (blockIdx.x == gridDim.x - 1) {
+    unsigned* arrivals = reinterpret_cast<unsigned*>(reinterpret_cast<unsigned char*>(tables) + kAttnHeaderBytes);
+    for (int i = threadIdx.x; i < n_counters; i += blockDim.x) arrivals[i] = 0u;
+    prepare_tables_cta(kcent, vcent, tables);
+    return;
+  }
+  constexpr int D = 128;
   constexpr float kL2e = 1.4426950408889634f;
-  __shared__ float red_s[4][kRowsPerCta][3];
+  __shared__ __align__(16) float x_s[kRowsPerCta][D];
+  __shared__ float q_s[kRowsPerCta][D], w_s[kRowsPerCta][D];
+  __shared__ float red_s[kRowsPerCta][4][3];
   __shared__ float scale_s[kRowsPerCta];
+  const int r = threadIdx.x >> 7, i = threadIdx.x & 127, lane = threadIdx.x & 31, wr = (threadIdx.x >> 5) & 3;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * rows_per_cta + r;
+  const bool live = r < rows_per_cta && row < rows;
+  x_s[r][i] = live ? load_float(q, q_dtype, row * D + i) : 0.f;
   const float g0 = kcent[0], g1 = kcent[1] - kcent[0], g2 = kcent[2] - kcent[0];
-  __syncthreads();                                  // everyone is done with the inputs in x_s
-  float (*qs)[kMaxD] = x_s;                         // rotated, scaled queries; sign weights go to w_s
-  __shared__ float w_s[kRowsPerCta][kMaxD];
+  const float sg = S[i];
+  __syncthreads();
+  float acc = 0.f;
+  {
+    const float4* p4 = reinterpret_cast<const float4*>(Pi + static_cast<int64_t>(i) * D);
+#pragma unroll 16
+    for (int j4 = 0; j4 < D / 4; ++j4) {
+      const float4 m = __ldg(p4 + j4);
+      const float4 x = *reinterpret_cast<const float4*>(&x_s[r][4 * j4]);
+      acc = fmaf(x.x, m.x, acc);
+      acc = fmaf(x.y, m.y, acc);
+      acc = fmaf(x.z, m.z, acc);
+      acc = fmaf(x.w, m.w, acc);
+    }
+  }
+  const float qv = live ? acc * scale : 0.f;
+  const float wv = live ? (qjl_scale * scale) * (fabsf(acc) * sg) : 0.f;
+  if (live) {
+    qk[row * 2 * D + i] = qv;
+    qk[row * 2 * D + D + i] = wv;
+  }
+  q_s[r][i] = qv;
+  w_s[r][i] = wv;
   {
     const float e0 = 1.f / static_cast<float>(1 << (2 * (i & 3))), e2 = 1.f / static_cast<float>(1 << (i & 7));
-    const int lane = i & 31, warp = i >> 5;
+    float mx = fmaxf(fmaxf(fabsf(qv * g1) * e0, fabsf(qv * g2) * (0.5f * e0)), 2.f * fabsf(wv) * e2);
+    float sq = qv, sw = wv;
 #pragma unroll
-    for (int r = 0; r < kRowsPerCta; ++r) {
-      const bool live = row0 + r < row_end;
-      const float qv = live ? acc[r] * scale : 0.f;
-      const float wv = live ? (qjl_scale * scale) * (fabsf(acc[r]) * sg) : 0.f;
-      qs[r][i] = qv;
-      w_s[r][i] = wv;
-      float mx = fmaxf(fmaxf(fabsf(qv * g1) * e0, fabsf(qv * g2) * (0.5f * e0)), 2.f * fabsf(wv) * e2);
-      float sq = qv, sw = wv;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        mx = fmaxf(mx, __shfl_xor_sync(QKV_FULL_MASK, mx, o));
-        sq += __shfl_xor_sync(QKV_FULL_MASK, sq, o);
-        sw += __shfl_xor_sync(QKV_FULL_MASK, sw, o);
-      }
-      if (lane == 0) { red_s[warp][r][0] = mx; red_s[warp][r][1] = sq; red_s[warp][r][2] = sw; }
+    for (int o = 16; o > 0; o >>= 1) {
+      mx = fmaxf(mx, __shfl_xor_sync(QKV_FULL_MASK, mx, o));
+      sq += __shfl_xor_sync(QKV_FULL_MASK, sq, o);
+      sw += __shfl_xor_sync(QKV_FULL_MASK, sw, o);
     }
+    if (lane == 0) { red_s[r][wr][0] = mx; red_s[r][wr][1] = sq; red_s[r][wr][2] = sw; }
   }
   __syncthreads();
   PlaneImage* img = planes + blockIdx.x;
-  if (i < kRowsPerCta) {
+  if (threadIdx.x < kRowsPerCta) {
+    const int n = threadIdx.x;
     float mx = 0.f, sq = 0.f, sw = 0.f;
-    for (int w = 0; w < 4; ++w) { mx = fmaxf(mx, red_s[w][i][0]); sq += red_s[w][i][1]; sw += red_s[w][i][2]; }
+    for (int w = 0; w < 4; ++w) { mx = fmaxf(mx, red_s[n][w][0]); sq += red_s[n][w][1]; sw += red_s[n][w][2]; }
     mx *= kL2e;
-    scale_s[i] = mx > 0.f ? 127.f / mx : 0.f;
-    img->inv[i] = mx * (1.f / 127.f);
-    img->cst[i] = kL2e * (g0 * sq - sw);
+    scale_s[n] = mx > 0.f ? 127.f / mx : 0.f;
+    img->inv[n] = mx * (1.f / 127.f);
+    img->cst[n] = kL2e * (g0 * sq - sw);
   }
   __syncthreads();
-  for (int item = i; item < 12 * 32; item += 128) {
+  if (threadIdx.x < 12 * 32) {
+    const int item = threadIdx.x;
     const int s = item >> 5, L = item & 31, t = L & 3, n = (L >> 2) & 3, hi = L >> 4;
     const float sc = scale_s[n];
     uint32_t ra[2] = {0u, 0u}, rb[2] = {0u, 0u};
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
+    for (int rr = 0; rr < 2; ++rr) {
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
         int p; float x;
         if (s < 8) {
-          p = 2 * (s & 3) + r;
-          x = kL2e * (r ? g2 : g1) * qs[n][32 * t + 16 * (s >> 2) + 4 * b + (s & 3)];
+          p = 2 * (s & 3) + rr;
+          x = kL2e * (rr ? g2 : g1) * q_s[n][32 * t + 16 * (s >> 2) + 4 * b + (s & 3)];
         } else {
-          p = 2 * (s - 8) + r;
+          p = 2 * (s - 8) + rr;
           x = 2.f * kL2e * w_s[n][32 * t + 8 * b + p];
         }
         const float y = x * sc * (1.f / static_cast<float>(1 << p));
@@ -160,8 +196,8 @@ __global__ void __launch_bounds__(128) rotate_queries_kernel(const void* __restr
         const float r3 = (r2 - t3) * 128.f;
         const float t4 = fminf(fmaxf(rintf(r3), -127.f), 127.f);
         const int ba = static_cast<int>(hi ? t2 : t1), bb = static_cast<int>(hi ? t4 : t3);
-        ra[r] |= (static_cast<uint32_t>(ba) & 0xFFu) << (8 * b);
-        rb[r] |= (static_cast<uint32_t>(bb) & 0xFFu) << (8 * b);
+        ra[rr] |= (static_cast<uint32_t>(ba) & 0xFFu) << (8 * b);
+        rb[rr] |= (static_cast<uint32_t>(bb) & 0xFFu) << (8 * b);
       }
     }
     img->bop[s][L] = make_uint4(ra[0], ra[1], rb[0], rb[1]);
@@ -446,15 +482,12 @@ __global__ void __launch_bounds__(128) merge_splits_kernel(const float* __restri
 }
 
 // Host-side launcher shared with the index scan.
-// rows_per_cta (1..4): query rows per CTA; with `planes` it is the number of query rows of a (batch, kv head),
-// so that CTA k builds plane image k.
 static int launch_rotate(const void* q, int q_dtype, int64_t rows, int d, const float* Pi, const float* S,
                          float qjl_scale, float scale, float* qk, const float* kcent, const float* vcent,
-                         uint32_t* tables, int n_counters, cudaStream_t st, int rows_per_cta = kRowsPerCta,
-                         PlaneImage* planes = nullptr) {
-  const unsigned ctas = static_cast<unsigned>((rows + rows_per_cta - 1) / rows_per_cta) + (tables ? 1u : 0u);
+                         uint32_t* tables, int n_counters, cudaStream_t st) {
+  const unsigned ctas = static_cast<unsigned>((rows + kRowsPerCta - 1) / kRowsPerCta) + (tables ? 1u : 0u);
   rotate_queries_kernel<<<ctas, 128, 0, st>>>(q, q_dtype, rows, d, Pi, S, qjl_scale, scale, qk, kcent, vcent,
-                                              tables, n_counters, rows_per_cta, planes);
+                                              tables, n_counters);
   return check_launch();
 }
 
@@ -555,9 +588,16 @@ int attention_run(const void* q, int q_dtype, qkv_cache_t cache, const uint8_t* 
   // tile records with up to four query rows per KV head: scores from bit planes, operands built by the rotation
   const bool from_planes = tiled && tiled_scores_from_planes(Hq / Hkv, q_len);
   PlaneImage* planes = from_planes ? reinterpret_cast<PlaneImage*>(ws + p.img_off) : nullptr;
-  int rc = launch_rotate(q, q_dtype, p.rows, d, Pi, S, qjl_scale, scale, qk, key_centroids, val_centroids,
-                         use_mma ? tables : nullptr, B * Hkv * (((Hq / Hkv) * q_len + 7) / 8), st,
-                         from_planes ? (Hq / Hkv) * q_len : kRowsPerCta, planes);
+  int rc;
+  if (from_planes) {
+    rotate_planes_kernel<<<static_cast<unsigned>(B * Hkv + 1), 512, 0, st>>>(
+        q, q_dtype, p.rows, Pi, S, qjl_scale, scale, qk, key_centroids, val_centroids, tables, B * Hkv,
+        (Hq / Hkv) * q_len, planes);
+    rc = check_launch();
+  } else {
+    rc = launch_rotate(q, q_dtype, p.rows, d, Pi, S, qjl_scale, scale, qk, key_centroids, val_centroids,
+                       use_mma ? tables : nullptr, B * Hkv * (((Hq / Hkv) * q_len + 7) / 8), st);
+  }
   if (rc) return rc;
 
   AttnArgs a{};

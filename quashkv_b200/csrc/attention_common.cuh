@@ -151,8 +151,8 @@ __device__ inline void prepare_tables_cta(const float* __restrict__ kcent, const
                                           uint32_t* __restrict__ tables) {
   __shared__ float cand_err[2][128];
   __shared__ float cand_s[2][128];
-  const int tid = threadIdx.x;
-  for (int tb = 0; tb < 2; ++tb) {
+  const int tid = threadIdx.x;              // 128 threads search; a larger CTA's other threads only keep the barrier
+  for (int tb = 0; tb < 2 && tid < 128; ++tb) {
     const float* cent = tb ? vcent : kcent;
     const int n = tb ? 8 : 4;
     float c[8];

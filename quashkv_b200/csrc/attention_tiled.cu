@@ -449,27 +449,42 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
     }
   };
 
+  // The loop over this warp's tiles is unrolled over the ring, so that stage addresses and barrier addresses are
+  // constants of each copy of the body.
   int it_failed = -1;
-  int slot = 0;
-  uint32_t parity = 0;
-  for (int it = 0, rel = first_rel; it < n_it; ++it, rel += kStep) {
-    if (!__all_sync(QKV_FULL_MASK, umma::mbar_wait(bar + slot, parity))) { it_failed = it; break; }
-    const unsigned char* stage = ring + slot * tile::kBytes;
-    TileRegs cur;
-    cur.kc = *reinterpret_cast<const uint4*>(stage + tile::kOffKeyCodes + 16 * lane);
-    cur.ks = *reinterpret_cast<const uint2*>(stage + tile::kOffKeySigns + 8 * lane);
-    cur.va = *reinterpret_cast<const uint4*>(stage + tile::kOffVal16 + 16 * lane);
-    cur.vb = *reinterpret_cast<const uint2*>(stage + tile::kOffVal8 + 8 * lane);
-    cur.nrm = *reinterpret_cast<const float4*>(stage + tile::kOffNorms + 16 * gid);
-    process(cur, rel);
-    // The slot is refilled only now.  A warp issues its instructions in order and an instruction issues only
-    // once its source registers hold their values, so at this point every lane's loads from the slot have
-    // returned (process() consumed all of them): the copy cannot overwrite bytes that are still to be read.
-    // Issuing it straight after the loads, before their values are used, lost that guarantee: with records
-    // coming from L2 and the load queue of the SM full, a copy was seen to land before a queued load.
-    __syncwarp();
-    issue(it + kRing, slot);
-    if (++slot == kRing) { slot = 0; parity ^= 1u; }
+  {
+    int it = 0, rel = first_rel;
+    uint32_t parity = 0;
+    while (it < n_it && it_failed < 0) {
+#pragma unroll
+      for (int slot = 0; slot < kRing; ++slot) {
+        if (it < n_it && it_failed < 0) {
+          if (__all_sync(QKV_FULL_MASK, umma::mbar_wait(bar + slot, parity))) {
+            const unsigned char* stage = ring + slot * tile::kBytes;
+            TileRegs cur;
+            cur.kc = *reinterpret_cast<const uint4*>(stage + tile::kOffKeyCodes + 16 * lane);
+            cur.ks = *reinterpret_cast<const uint2*>(stage + tile::kOffKeySigns + 8 * lane);
+            cur.va = *reinterpret_cast<const uint4*>(stage + tile::kOffVal16 + 16 * lane);
+            cur.vb = *reinterpret_cast<const uint2*>(stage + tile::kOffVal8 + 8 * lane);
+            cur.nrm = *reinterpret_cast<const float4*>(stage + tile::kOffNorms + 16 * gid);
+            process(cur, rel);
+            // The slot is refilled only now.  A warp issues its instructions in order and an instruction issues
+            // only once its source registers hold their values, so at this point every lane's loads from the
+            // slot have returned (process() consumed all of them): the copy cannot overwrite bytes that are still
+            // to be read.  Issuing it straight after the loads, before their values are used, lost that
+            // guarantee: with records coming from L2 and the load queue of the SM full, a copy was seen to land
+            // before a queued load.
+            __syncwarp();
+            issue(it + kRing, slot);
+            ++it;
+            rel += kStep;
+          } else {
+            it_failed = it;
+          }
+        }
+      }
+      parity ^= 1u;
+    }
   }
   if (it_failed >= 0) {
     // A copy never arrived (not seen in practice; a hardware fault would look like this).  Count it, give the
