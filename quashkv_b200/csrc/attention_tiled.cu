@@ -551,6 +551,7 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
   float* vec = reinterpret_cast<float*>(pool);       // [8][D] merged, normalised accumulators
   float* wgt = vec + 8 * D;                          // [8][kMaxSplits] weights of the splits
   float* invl = wgt + 8 * kMaxSplits;                // [8]
+  static_assert((8 * D + 8 * kMaxSplits + 8 + kWarps * 8 * D) * 4 <= sizeof(pool), "merge buffers fit the ring storage");
   // This tail runs once per (batch, kv head) at the very end of the call, so it is written for latency: every
   // round of loads is issued before the first result is used.
   for (int r = warp; r < nq; r += kWarps) {          // a warp per query row; a lane takes splits lane, lane + 32
@@ -588,41 +589,56 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
     const float* pp = a.part + qrow * a.n_splits * (D + 2) + 2 + j;       // 8-byte aligned: rows of 130 floats
     const float* w = wgt + r * kMaxSplits;
     float2 acc = make_float2(0.f, 0.f);
-    int sp = 0;
-    for (; sp + 8 <= a.n_splits; sp += 8) {
-      float2 v[8];
+    for (int sp = 0; sp < a.n_splits; sp += 16) {                         // sixteen splits per round of loads
+      float2 v[16];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = __ldcg(reinterpret_cast<const float2*>(pp + (sp + u) * (D + 2)));
+      for (int u = 0; u < 16; ++u)
+        v[u] = sp + u < a.n_splits ? __ldcg(reinterpret_cast<const float2*>(pp + (sp + u) * (D + 2))) : make_float2(0.f, 0.f);
 #pragma unroll
-      for (int u = 0; u < 8; ++u) { acc.x = fmaf(w[sp + u], v[u].x, acc.x); acc.y = fmaf(w[sp + u], v[u].y, acc.y); }
-    }
-    for (; sp < a.n_splits; ++sp) {
-      const float2 v = __ldcg(reinterpret_cast<const float2*>(pp + sp * (D + 2)));
-      acc.x = fmaf(w[sp], v.x, acc.x);
-      acc.y = fmaf(w[sp], v.y, acc.y);
+      for (int u = 0; u < 16; ++u) {
+        const float wu = sp + u < a.n_splits ? w[sp + u] : 0.f;
+        acc.x = fmaf(wu, v[u].x, acc.x);
+        acc.y = fmaf(wu, v[u].y, acc.y);
+      }
     }
     vec[r * D + j] = acc.x * invl[r];
     vec[r * D + j + 1] = acc.y * invl[r];
   }
   __syncthreads();
   {
-    const int i = threadIdx.x;                       // output coordinate (blockDim.x == D)
-    float o[8];
+    // out = vec @ Pi.  Warp w takes rows 32 w .. 32 w + 31 of Pi, a lane four output coordinates, so that the 32
+    // loads of a thread are independent (two rounds of 16); the four partial sums meet in shared memory.
+    float4 o[8];
 #pragma unroll
-    for (int r = 0; r < 8; ++r) o[r] = 0.f;
-#pragma unroll 32
-    for (int j = 0; j < D; ++j) {
-      const float mval = __ldg(a.Pi + j * D + i);
+    for (int r = 0; r < 8; ++r) o[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4* prow = reinterpret_cast<const float4*>(a.Pi + static_cast<int64_t>(32 * warp) * D) + lane;
+#pragma unroll 16
+    for (int jj = 0; jj < 32; ++jj) {
+      const float4 mval = __ldg(prow + jj * (D / 4));
 #pragma unroll
-      for (int r = 0; r < 8; ++r) o[r] = fmaf(vec[r * D + j], mval, o[r]);
+      for (int r = 0; r < 8; ++r) {
+        const float x = vec[r * D + 32 * warp + jj];
+        o[r].x = fmaf(x, mval.x, o[r].x);
+        o[r].y = fmaf(x, mval.y, o[r].y);
+        o[r].z = fmaf(x, mval.z, o[r].z);
+        o[r].w = fmaf(x, mval.w, o[r].w);
+      }
     }
+    float* psum = invl + 8;                            // [kWarps][8][D] partial sums, behind vec, wgt and invl
+#pragma unroll
+    for (int r = 0; r < 8; ++r) *reinterpret_cast<float4*>(psum + (warp * 8 + r) * D + 4 * lane) = o[r];
+    __syncthreads();
+    const int i = threadIdx.x;                       // output coordinate (blockDim.x == D)
     // A table that breaks what the record format (symmetric value table) or the bit planes (key table affine in
     // its code bits) presume would give wrong numbers silently: give NaN instead.
     const bool broken = (a.tables[10] & (PLANES ? 3u : 1u)) != 0u;
     for (int r = 0; r < nq; ++r) {
       const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
       const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
-      a.out[qrow * D + i] = broken ? __int_as_float(0x7fc00000) : o[r];
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) v += psum[(w * 8 + r) * D + i];
+      a.out[qrow * D + i] = broken ? __int_as_float(0x7fc00000) : v;
     }
   }
 }
