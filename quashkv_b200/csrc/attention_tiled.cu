@@ -300,8 +300,8 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
         kA[e] = hi ? u * (1.f / 128.f) : u;
         kB[e] = hi ? u * (1.f / 2097152.f) : u * (1.f / 16384.f);
       }
-      ci0 = hi ? 0.f : img->cst[(2 * tig) & 3];
-      ci1 = hi ? 0.f : img->cst[(2 * tig + 1) & 3];
+      ci0 = (hi ? 0.f : img->cst[(2 * tig) & 3]) - 12582912.f * kB[0];
+      ci1 = (hi ? 0.f : img->cst[(2 * tig + 1) & 3]) - 12582912.f * kB[1];
     }
   } else {
     ci0 = -wsum[2 * tig];
@@ -332,11 +332,14 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
       QKV_PLANE_STEP(8, cur.ks.x, cur.ks.y, 0) QKV_PLANE_STEP(9, cur.ks.x, cur.ks.y, 2)
       QKV_PLANE_STEP(10, cur.ks.x, cur.ks.y, 4) QKV_PLANE_STEP(11, cur.ks.x, cur.ks.y, 6)
 #undef QKV_PLANE_STEP
-      constexpr float kMagicF = 12582912.f;                      // the sums are below 2^22 in magnitude: exact
+      // The sums are below 2^22 in magnitude, so the first chain comes out exactly with one subtraction.  The
+      // second chain weighs 2^-14 of the first: its offset is taken out with the constant (ci holds
+      // -1.5 * 2^23 * kB), the rounding of that product being 2^-38 of the largest weight.
+      constexpr float kMagicF = 12582912.f;
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float fa = __int_as_float(ia[e]) - kMagicF, fb = __int_as_float(ib[e]) - kMagicF;
-        c[e] = fmaf(fa, kA[e & 1], fmaf(fb, kB[e & 1], (e & 1) ? ci1 : ci0));
+        const float fa = __int_as_float(ia[e]) - kMagicF;
+        c[e] = fmaf(fa, kA[e & 1], fmaf(__int_as_float(ib[e]), kB[e & 1], (e & 1) ? ci1 : ci0));
       }
     } else {
     // ---- scores: 8 MMAs on key codes, 8 on sign bits --------------------------------------------
