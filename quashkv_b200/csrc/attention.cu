@@ -119,33 +119,58 @@ __global__ void __launch_bounds__(512) rotate_planes_kernel(const void* __restri
   __shared__ float red_s[kRowsPerCta][4][3];
   __shared__ float scale_s[kRowsPerCta];
   const int r = threadIdx.x >> 7, i = threadIdx.x & 127, lane = threadIdx.x & 31, wr = (threadIdx.x >> 5) & 3;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * rows_per_cta + r;
-  const bool live = r < rows_per_cta && row < rows;
-  x_s[r][i] = live ? load_float(q, q_dtype, row * D + i) : 0.f;
-  const float g0 = kcent[0], g1 = kcent[1] - kcent[0], g2 = kcent[2] - kcent[0];
-  const float sg = S[i];
-  __syncthreads();
-  float acc = 0.f;
+  const int warp = threadIdx.x >> 5;
+  const int64_t row0 = static_cast<int64_t>(blockIdx.x) * rows_per_cta;
   {
-    const float4* p4 = reinterpret_cast<const float4*>(Pi + static_cast<int64_t>(i) * D);
-#pragma unroll 16
-    for (int j4 = 0; j4 < D / 4; ++j4) {
-      const float4 m = __ldg(p4 + j4);
-      const float4 x = *reinterpret_cast<const float4*>(&x_s[r][4 * j4]);
-      acc = fmaf(x.x, m.x, acc);
-      acc = fmaf(x.y, m.y, acc);
-      acc = fmaf(x.z, m.z, acc);
-      acc = fmaf(x.w, m.w, acc);
+    const int64_t row = row0 + r;
+    x_s[r][i] = (r < rows_per_cta && row < rows) ? load_float(q, q_dtype, row * D + i) : 0.f;
+  }
+  const float g0 = kcent[0], g1 = kcent[1] - kcent[0], g2 = kcent[2] - kcent[0];
+  // Rotation: warp w takes rows 8 w .. 8 w + 7 of Pi, a lane four columns of each (one coalesced 16-byte load per
+  // row, all eight in flight at once), against the four query rows: 32 partial sums per lane, which a butterfly
+  // of 31 exchanges reduces so that lane L ends with the total of Pi row 8 w + (L >> 2) and query row L & 3.
+  float4 m[8];
+#pragma unroll
+  for (int o = 0; o < 8; ++o)
+    m[o] = __ldg(reinterpret_cast<const float4*>(Pi + static_cast<int64_t>(8 * warp + o) * D) + lane);
+  __syncthreads();
+  float v[32];
+  {
+    float4 x[kRowsPerCta];
+#pragma unroll
+    for (int rr = 0; rr < kRowsPerCta; ++rr) x[rr] = *reinterpret_cast<const float4*>(&x_s[rr][4 * lane]);
+#pragma unroll
+    for (int o = 0; o < 8; ++o)
+#pragma unroll
+      for (int rr = 0; rr < kRowsPerCta; ++rr)
+        v[4 * o + rr] = fmaf(m[o].x, x[rr].x, fmaf(m[o].y, x[rr].y, fmaf(m[o].z, x[rr].z, m[o].w * x[rr].w)));
+  }
+#pragma unroll
+  for (int s = 16, n = 32; s >= 1; s >>= 1, n >>= 1) {
+    const bool upper = (lane & s) != 0;
+#pragma unroll
+    for (int k = 0; k < n / 2; ++k) {
+      const float send = upper ? v[k] : v[k + n / 2];
+      const float keep = upper ? v[k + n / 2] : v[k];
+      v[k] = keep + __shfl_xor_sync(QKV_FULL_MASK, send, s);
     }
   }
-  const float qv = live ? acc * scale : 0.f;
-  const float wv = live ? (qjl_scale * scale) * (fabsf(acc) * sg) : 0.f;
-  if (live) {
-    qk[row * 2 * D + i] = qv;
-    qk[row * 2 * D + D + i] = wv;
+  {
+    const int io = 8 * warp + (lane >> 2), ro = lane & 3;            // this lane's output: coordinate, query row
+    const int64_t row = row0 + ro;
+    const bool live = ro < rows_per_cta && row < rows;
+    const float acc = v[0];
+    const float qo = live ? acc * scale : 0.f;
+    const float wo = live ? (qjl_scale * scale) * (fabsf(acc) * S[io]) : 0.f;
+    if (live) {
+      qk[row * 2 * D + io] = qo;
+      qk[row * 2 * D + D + io] = wo;
+    }
+    q_s[ro][io] = qo;
+    w_s[ro][io] = wo;
   }
-  q_s[r][i] = qv;
-  w_s[r][i] = wv;
+  __syncthreads();
+  const float qv = q_s[r][i], wv = w_s[r][i];
   {
     const float e0 = 1.f / static_cast<float>(1 << (2 * (i & 3))), e2 = 1.f / static_cast<float>(1 << (i & 7));
     float mx = fmaxf(fmaxf(fabsf(qv * g1) * e0, fabsf(qv * g2) * (0.5f * e0)), 2.f * fabsf(wv) * e2);

@@ -149,8 +149,8 @@ unsigned int bulk_copy_timeouts();        // bounded waits on a record copy that
 // bits of its code), [11..13] g0, g1, g2 of the key table written as c(u) = g0 + g1 (u & 1) + g2 (u >> 1).
 __device__ inline void prepare_tables_cta(const float* __restrict__ kcent, const float* __restrict__ vcent,
                                           uint32_t* __restrict__ tables) {
-  __shared__ float cand_err[2][128];
-  __shared__ float cand_s[2][128];
+  __shared__ float cand_err[2][4];
+  __shared__ float cand_s[2][4];
   const int tid = threadIdx.x;              // 128 threads search; a larger CTA's other threads only keep the barrier
   for (int tb = 0; tb < 2 && tid < 128; ++tb) {
     const float* cent = tb ? vcent : kcent;
@@ -168,15 +168,20 @@ __device__ inline void prepare_tables_cta(const float* __restrict__ kcent, const
       }
       if (err < best_err) { best_err = err; best_s = s; }
     }
-    cand_err[tb][tid] = best_err;
-    cand_s[tb][tid] = best_s;
+    // smallest error, then smallest scale: over the warp by exchange, over the four warps by thread 0
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float e2 = __shfl_xor_sync(0xffffffffu, best_err, o), s2 = __shfl_xor_sync(0xffffffffu, best_s, o);
+      if (e2 < best_err || (e2 == best_err && s2 < best_s)) { best_err = e2; best_s = s2; }
+    }
+    if ((tid & 31) == 0) { cand_err[tb][tid >> 5] = best_err; cand_s[tb][tid >> 5] = best_s; }
   }
   __syncthreads();
   if (tid != 0) return;
   float sc[2];
   for (int tb = 0; tb < 2; ++tb) {
     float e = 1e30f, s = 1.f;
-    for (int i = 0; i < 128; ++i)
+    for (int i = 0; i < 4; ++i)
       if (cand_err[tb][i] < e || (cand_err[tb][i] == e && cand_s[tb][i] < s)) { e = cand_err[tb][i]; s = cand_s[tb][i]; }
     sc[tb] = s;
   }
