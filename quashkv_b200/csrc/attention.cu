@@ -20,9 +20,37 @@
 
 namespace qkv {
 
-// q_rot = q @ Pi^T for 4 query rows per CTA.  Thread i owns output coordinate i and streams row i of Pi
-// with 16-byte loads (independent loads, no barriers), every element feeding 4 rows.
+// q_rot = q @ Pi^T for 4 query rows per CTA.  A warp takes eight rows of Pi at a time, a lane four columns of
+// each (coalesced 16-byte loads, all eight in flight), against the four query rows; the 32 partial sums of a
+// lane are reduced over the warp by a butterfly of 31 exchanges, after which lane L holds the total of Pi row
+// (L >> 2) of the eight and query row L & 3.
 constexpr int kRowsPerCta = 4;
+
+// Rows i0 .. i0 + 7 of Pi (d columns, d a multiple of 4, at most 128) against four vectors held as the lane's
+// four columns each: on return v[0] of lane L is <Pi[i0 + (L >> 2)], vector L & 3>.
+__device__ __forceinline__ void rotate_eight_rows(const float* __restrict__ Pi, int d, int i0, int lane,
+                                                  const float4 (&x)[kRowsPerCta], float (&v)[32]) {
+  float4 m[8];
+#pragma unroll
+  for (int o = 0; o < 8; ++o)
+    m[o] = (i0 + o < d && 4 * lane < d) ? __ldg(reinterpret_cast<const float4*>(Pi + static_cast<int64_t>(i0 + o) * d) + lane)
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int o = 0; o < 8; ++o)
+#pragma unroll
+    for (int r = 0; r < kRowsPerCta; ++r)
+      v[4 * o + r] = fmaf(m[o].x, x[r].x, fmaf(m[o].y, x[r].y, fmaf(m[o].z, x[r].z, m[o].w * x[r].w)));
+#pragma unroll
+  for (int s = 16, n = 32; s >= 1; s >>= 1, n >>= 1) {
+    const bool upper = (lane & s) != 0;
+#pragma unroll
+    for (int k = 0; k < n / 2; ++k) {
+      const float send = upper ? v[k] : v[k + n / 2];
+      const float keep = upper ? v[k + n / 2] : v[k];
+      v[k] = keep + __shfl_xor_sync(QKV_FULL_MASK, send, s);
+    }
+  }
+}
 __global__ void __launch_bounds__(128) rotate_queries_kernel(const void* __restrict__ q, int q_dtype, int64_t rows,
                                                              int d, const float* __restrict__ Pi,
                                                              const float* __restrict__ S, float qjl_scale,
@@ -47,38 +75,17 @@ __global__ void __launch_bounds__(128) rotate_queries_kernel(const void* __restr
     x_s[r][j] = (row0 + r < rows && j < d) ? load_float(q, q_dtype, (row0 + r) * d + j) : 0.f;
   }
   __syncthreads();
-  if (i >= d) return;
-  float acc[kRowsPerCta];
+  const int lane = i & 31, warp = i >> 5;
+  float4 x[kRowsPerCta];
 #pragma unroll
-  for (int r = 0; r < kRowsPerCta; ++r) acc[r] = 0.f;
-  const float* prow = Pi + static_cast<int64_t>(i) * d;
-  if ((d & 3) == 0) {
-    const float4* p4 = reinterpret_cast<const float4*>(prow);
-#pragma unroll 8
-    for (int j4 = 0; j4 < d / 4; ++j4) {
-      const float4 m = __ldg(p4 + j4);
-#pragma unroll
-      for (int r = 0; r < kRowsPerCta; ++r) {
-        const float4 x = *reinterpret_cast<const float4*>(&x_s[r][4 * j4]);
-        acc[r] = fmaf(x.x, m.x, acc[r]);
-        acc[r] = fmaf(x.y, m.y, acc[r]);
-        acc[r] = fmaf(x.z, m.z, acc[r]);
-        acc[r] = fmaf(x.w, m.w, acc[r]);
-      }
-    }
-  } else {
-    for (int j = 0; j < d; ++j) {
-      const float m = __ldg(prow + j);
-#pragma unroll
-      for (int r = 0; r < kRowsPerCta; ++r) acc[r] = fmaf(x_s[r][j], m, acc[r]);
-    }
-  }
-  const float sg = S[i];
-#pragma unroll
-  for (int r = 0; r < kRowsPerCta; ++r) {
-    if (row0 + r < rows) {
-      qk[(row0 + r) * 2 * d + i] = acc[r] * scale;
-      qk[(row0 + r) * 2 * d + d + i] = (qjl_scale * scale) * (fabsf(acc[r]) * sg);
+  for (int r = 0; r < kRowsPerCta; ++r) x[r] = *reinterpret_cast<const float4*>(&x_s[r][4 * lane]);   // zero beyond d
+  for (int i0 = 8 * warp; i0 < d; i0 += 32) {
+    float v[32];
+    rotate_eight_rows(Pi, d, i0, lane, x, v);
+    const int io = i0 + (lane >> 2), ro = lane & 3;
+    if (io < d && row0 + ro < rows) {
+      qk[(row0 + ro) * 2 * d + io] = v[0] * scale;
+      qk[(row0 + ro) * 2 * d + d + io] = (qjl_scale * scale) * (fabsf(v[0]) * S[io]);
     }
   }
 }
@@ -126,34 +133,14 @@ __global__ void __launch_bounds__(512) rotate_planes_kernel(const void* __restri
     x_s[r][i] = (r < rows_per_cta && row < rows) ? load_float(q, q_dtype, row * D + i) : 0.f;
   }
   const float g0 = kcent[0], g1 = kcent[1] - kcent[0], g2 = kcent[2] - kcent[0];
-  // Rotation: warp w takes rows 8 w .. 8 w + 7 of Pi, a lane four columns of each (one coalesced 16-byte load per
-  // row, all eight in flight at once), against the four query rows: 32 partial sums per lane, which a butterfly
-  // of 31 exchanges reduces so that lane L ends with the total of Pi row 8 w + (L >> 2) and query row L & 3.
-  float4 m[8];
-#pragma unroll
-  for (int o = 0; o < 8; ++o)
-    m[o] = __ldg(reinterpret_cast<const float4*>(Pi + static_cast<int64_t>(8 * warp + o) * D) + lane);
+  // Rotation: warp w takes rows 8 w .. 8 w + 7 of Pi (rotate_eight_rows).
   __syncthreads();
   float v[32];
   {
     float4 x[kRowsPerCta];
 #pragma unroll
     for (int rr = 0; rr < kRowsPerCta; ++rr) x[rr] = *reinterpret_cast<const float4*>(&x_s[rr][4 * lane]);
-#pragma unroll
-    for (int o = 0; o < 8; ++o)
-#pragma unroll
-      for (int rr = 0; rr < kRowsPerCta; ++rr)
-        v[4 * o + rr] = fmaf(m[o].x, x[rr].x, fmaf(m[o].y, x[rr].y, fmaf(m[o].z, x[rr].z, m[o].w * x[rr].w)));
-  }
-#pragma unroll
-  for (int s = 16, n = 32; s >= 1; s >>= 1, n >>= 1) {
-    const bool upper = (lane & s) != 0;
-#pragma unroll
-    for (int k = 0; k < n / 2; ++k) {
-      const float send = upper ? v[k] : v[k + n / 2];
-      const float keep = upper ? v[k + n / 2] : v[k];
-      v[k] = keep + __shfl_xor_sync(QKV_FULL_MASK, send, s);
-    }
+    rotate_eight_rows(Pi, D, 8 * warp, lane, x, v);
   }
   {
     const int io = 8 * warp + (lane >> 2), ro = lane & 3;            // this lane's output: coordinate, query row
