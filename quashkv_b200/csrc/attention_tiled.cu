@@ -521,25 +521,36 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
       dst[2 + 16 * gid + 2 * i + 1] = O[i][2 + e] * inv_sv;
     }
   }
+  // weights of the four warps' results per query row, and where the row's partials go: once per row, not per entry
+  __shared__ float fw_s[kWarps][8], mrow_s[8];
+  __shared__ int64_t qrow_s[8];
   __syncthreads();
-  for (int idx = threadIdx.x; idx < nq * (D + 2); idx += blockDim.x) {
-    const int r = idx / (D + 2), e = idx % (D + 2);
+  if (threadIdx.x < 8 * kWarps) {
+    const int w = threadIdx.x >> 3, r = threadIdx.x & 7;
     float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kWarps; ++w) M = fmaxf(M, red[w][r][0]);
-    float v = 0.f;
-    if (e == 0) {
-      v = M;
-    } else {
-#pragma unroll
-      for (int w = 0; w < kWarps; ++w) {
-        const float f = (red[w][r][0] == -INFINITY) ? 0.f : expf(red[w][r][0] - M);
-        v += f * red[w][r][e];
-      }
+    for (int u = 0; u < kWarps; ++u) M = fmaxf(M, red[u][r][0]);
+    fw_s[w][r] = (red[w][r][0] == -INFINITY) ? 0.f : expf(red[w][r][0] - M);
+    if (w == 0) {
+      mrow_s[r] = M;
+      const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
+      qrow_s[r] = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
     }
-    const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
-    const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
-    a.part[(qrow * a.n_splits + split) * (D + 2) + e] = v;
+  }
+  __syncthreads();
+  for (int r = 0; r < nq; ++r) {                     // a thread per coordinate; threads 0, 1 also write max and sum
+    float* dst = a.part + (qrow_s[r] * a.n_splits + split) * (D + 2);
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) v = fmaf(fw_s[w][r], red[w][r][2 + threadIdx.x], v);
+    dst[2 + threadIdx.x] = v;
+    if (threadIdx.x == 0) dst[0] = mrow_s[r];
+    if (threadIdx.x == 1) {
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) sum = fmaf(fw_s[w][r], red[w][r][1], sum);
+      dst[1] = sum;
+    }
   }
 
   // ---- the CTA that finishes a (batch, kv head) last merges its splits and applies Pi ----------------
@@ -558,9 +569,7 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
   // This tail runs once per (batch, kv head) at the very end of the call, so it is written for latency: every
   // round of loads is issued before the first result is used.
   for (int r = warp; r < nq; r += kWarps) {          // a warp per query row; a lane takes splits lane, lane + 32
-    const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
-    const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
-    const float* pp = a.part + qrow * a.n_splits * (D + 2);
+    const float* pp = a.part + qrow_s[r] * a.n_splits * (D + 2);
     float mm[2], ll[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -587,9 +596,7 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
   __syncthreads();
   for (int idx = threadIdx.x; idx < nq * (D / 2); idx += blockDim.x) {     // a thread per pair of coordinates
     const int r = idx / (D / 2), j = 2 * (idx % (D / 2));
-    const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
-    const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
-    const float* pp = a.part + qrow * a.n_splits * (D + 2) + 2 + j;       // 8-byte aligned: rows of 130 floats
+    const float* pp = a.part + qrow_s[r] * a.n_splits * (D + 2) + 2 + j;  // 8-byte aligned: rows of 130 floats
     const float* w = wgt + r * kMaxSplits;
     float2 acc = make_float2(0.f, 0.f);
     for (int sp = 0; sp < a.n_splits; sp += 16) {                         // sixteen splits per round of loads
@@ -636,12 +643,10 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
     // its code bits) presume would give wrong numbers silently: give NaN instead.
     const bool broken = (a.tables[10] & (PLANES ? 3u : 1u)) != 0u;
     for (int r = 0; r < nq; ++r) {
-      const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
-      const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
       float v = 0.f;
 #pragma unroll
       for (int w = 0; w < kWarps; ++w) v += psum[(w * 8 + r) * D + i];
-      a.out[qrow * D + i] = broken ? __int_as_float(0x7fc00000) : v;
+      a.out[qrow_s[r] * D + i] = broken ? __int_as_float(0x7fc00000) : v;
     }
   }
 }
