@@ -283,7 +283,11 @@ int qkv_untile_rows(const uint8_t* records, qkv_rows_t map, const int64_t* slots
  *     multiple of 16, block_table / seq_lens / max_blocks as in qkv_paged_cache_t, kv_len the host-known
  *     upper bound of seq_lens.
  * Tokens of the last record beyond the length are ignored whatever they hold.  Workspace as
- * qkv_attention_workspace_bytes.  Replaces QuashKVEngine.attention (reference engine.py:204-299). */
+ * qkv_attention_workspace_bytes.  Replaces QuashKVEngine.attention (reference engine.py:204-299).
+ * The records and their kernel presume what the reference's Lloyd-Max tables satisfy: a symmetric value table
+ * (c[7 - i] == -c[i]) and, with up to four query rows per KV head, a key table that is affine in the two bits
+ * of its code (c[0] + c[3] == c[1] + c[2]).  A call with other tables writes NaN to `out`; keep such caches as
+ * row-major planes and use qkv_attention. */
 typedef struct {
   const uint8_t* records;
   int64_t capacity;

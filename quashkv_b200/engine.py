@@ -53,11 +53,12 @@ class QuashKVEngine:
         self.key_quantizer = InnerProductQuantizer(d=head_dim, total_bits=key_bits, seed=seed, device=device)
         self.value_quantizer = MSEQuantizer(d=head_dim, bits=value_bits, seed=seed, device=device)
         # Storage: 16-token tile records when the tensor-core decode kernel covers the configuration (head_dim
-        # 128, 3-bit keys and values, a value table with c[7-i] = -c[i]), else the five row-major planes.
-        # QUASHKV_B200_ROW_STORAGE=1 keeps the row-major planes everywhere (for A/B checks).
-        vc = self.value_quantizer.codebook.centroids
+        # 128, 3-bit keys and values, a value table with c[7-i] = -c[i], a key table with c0 + c3 = c1 + c2), else
+        # the five row-major planes.  QUASHKV_B200_ROW_STORAGE=1 keeps the row-major planes everywhere (for A/B
+        # checks).
         self._tiled = ops.tiled_layout_ok(head_dim, key_bits, value_bits) and \
-            bool((vc + vc.flip(0)).abs().max() <= 1e-6 * vc.abs().max()) and \
+            ops.tiled_tables_ok(self.key_quantizer.mse_quantizer.codebook.centroids,
+                                self.value_quantizer.codebook.centroids) and \
             os.environ.get("QUASHKV_B200_ROW_STORAGE") != "1"
         self._planes = None          # dict: {"records"} or the five planes
         self._shape = None           # (batch, heads)

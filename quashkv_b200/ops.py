@@ -395,6 +395,17 @@ def tiled_layout_ok(d: int, key_bits: int, val_bits: int) -> bool:
     return d == 128 and key_bits == 3 and val_bits == 3
 
 
+def tiled_tables_ok(key_centroids: torch.Tensor, value_centroids: torch.Tensor) -> bool:
+    """What the tile records and their decode kernel presume of the tables (the kernel writes NaN otherwise):
+    a symmetric 8-entry value table and a 4-entry key table that is affine in the two bits of its code."""
+    kc, vc = key_centroids.detach().float().cpu(), value_centroids.detach().float().cpu()
+    if kc.numel() != 4 or vc.numel() != 8:
+        return False
+    sym = float((vc + vc.flip(0)).abs().max()) <= 1e-6 * float(vc.abs().max())
+    aff = abs(float((kc[3] - kc[2]) - (kc[1] - kc[0]))) <= 1e-6 * float(kc.abs().max())
+    return sym and aff
+
+
 @torch.library.custom_op("quashkv_b200::tile_rows", mutates_args=("records",), device_types="cuda")
 def _tile_rows(k_codes: torch.Tensor, k_signs: torch.Tensor, k_norms: torch.Tensor, v_codes: torch.Tensor,
                v_norms: torch.Tensor, records: torch.Tensor, seg_len: int, seg_stride: int, seg_off: int,

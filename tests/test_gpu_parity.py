@@ -566,6 +566,31 @@ def test_tensor_core_decode_path_vs_generic_and_oracle(G, q_len, causal, monkeyp
     assert _lib.lib().qkv_tensor_core_timeouts() == TIMEOUTS[0]
 
 
+def test_tiled_attention_refuses_tables_the_records_do_not_cover():
+    """The tile-record kernel presumes a symmetric value table and, for up to four query rows per KV head, a key
+    table that is affine in its two code bits.  With other tables it must not return plausible numbers: the
+    output is NaN.  (Eight query rows per KV head run on fp16 scores, which take any key table.)"""
+    from quashkv_b200 import ops
+    B, Hkv, S, D = 1, 2, 160, 128
+    K, V = _outlier_kv(B, Hkv, S, D, 3, torch.float32)
+    eng = qk.QuashKVEngine(D, 3, 3, seed=42, pack_storage=True)
+    eng.append(K.to(DEV), V.to(DEV))
+    kq, vq = eng.key_quantizer, eng.value_quantizer
+    kc, vc = kq.mse_quantizer.codebook.centroids.to(DEV), vq.codebook.centroids.to(DEV)
+
+    def run(G, kcent, vcent):
+        Q = torch.randn(B, Hkv * G, 1, D, generator=torch.Generator().manual_seed(3)).to(DEV)
+        return ops._attention_tiled(Q, eng._planes["records"], eng._capacity, S, Hkv, None, None, 0,
+                                    kq.mse_quantizer.Pi.to(DEV), kcent, vcent, kq.S.to(DEV), kq.qjl_scale,
+                                    D ** -0.5, False)
+    bent = kc.clone(); bent[3] *= 1.05
+    skew = vc.clone(); skew[7] *= 1.05
+    assert torch.isfinite(run(4, kc, vc)).all() and torch.isfinite(run(8, kc, vc)).all()
+    assert torch.isnan(run(4, bent, vc)).all()            # bit planes need the affine key table
+    assert torch.isfinite(run(8, bent, vc)).all()         # fp16 scores do not
+    assert torch.isnan(run(4, kc, skew)).all() and torch.isnan(run(8, kc, skew)).all()
+
+
 def test_tile_records_match_the_format_definition_and_round_trip():
     """qkv_tile_rows against a numpy statement of the record format, then qkv_untile_rows back to the very
     bytes; scattered slots (a paged pool's shape), dropped rows, and single tokens added to existing records."""

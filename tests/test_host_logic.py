@@ -224,6 +224,15 @@ def test_engine_storage_choice_and_reset_shapes_without_gpu(monkeypatch):
     monkeypatch.setenv("QUASHKV_B200_ROW_STORAGE", "1")
     assert not qk.QuashKVEngine(128, 3, 3)._tiled
     monkeypatch.delenv("QUASHKV_B200_ROW_STORAGE")
+    # what the records presume of the tables: symmetric values, keys affine in the two bits of their code
+    from quashkv_b200 import ops
+    ref = qk.QuashKVEngine(128, 3, 3)
+    kc, vc = ref.key_quantizer.mse_quantizer.codebook.centroids, ref.value_quantizer.codebook.centroids
+    assert ops.tiled_tables_ok(kc, vc)
+    bent = kc.clone(); bent[3] *= 1.01
+    skew = vc.clone(); skew[0] *= 1.01
+    assert not ops.tiled_tables_ok(bent, vc) and not ops.tiled_tables_ok(kc, skew)
+    assert not ops.tiled_tables_ok(kc[:2], vc)
     eng = qk.QuashKVEngine(128, 3, 3)
     eng.reserve(2, 3, 100, "cpu")
     assert eng._planes["records"].shape == (6, 8, 1664) and eng._capacity == 128
