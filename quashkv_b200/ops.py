@@ -32,15 +32,32 @@ def packed_row_bytes(d: int, bits: int) -> int:
 
 
 def _p(t: Optional[torch.Tensor]):
-    return None if t is None else C.c_void_p(t.data_ptr())
+    """Device pointer of a tensor for the C call.  A host pointer must never reach a kernel: anything that is
+    not a CUDA tensor is refused here."""
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError(f"quashkv_b200: expected a CUDA tensor, got one on {t.device}")
+    return C.c_void_p(t.data_ptr())
+
+
+def _same_device(device: torch.device, *tensors: Optional[torch.Tensor]) -> None:
+    """Data tensors (codes, norms, records, tables of indices) are not moved for the caller: they have to be on
+    the device the call runs on."""
+    for t in tensors:
+        if t is not None and t.device != device:
+            raise ValueError(f"quashkv_b200: tensors of one call on different devices ({t.device} and {device})")
 
 
 def _stream(t: torch.Tensor):
     return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
 
 
-def _f32(t: torch.Tensor) -> torch.Tensor:
-    return t.detach().to(torch.float32).contiguous()
+def _f32(t: torch.Tensor, device: Optional[torch.device] = None) -> torch.Tensor:
+    """fp32, contiguous, and on `device` when one is given (small constants such as Pi, tables and S follow the
+    data; the quantizer classes keep per-device copies, the functional entry points convert per call)."""
+    t = t.detach()
+    return t.to(device=t.device if device is None else device, dtype=torch.float32).contiguous()
 
 
 class _Keep:
@@ -48,18 +65,19 @@ class _Keep:
     returned: a pointer taken from a temporary would otherwise outlive its storage, and the next allocation
     on the stream could hand that storage out again before the kernel has read it."""
 
-    def __init__(self):
+    def __init__(self, device: torch.device):
         self.held = []
+        self.device = device
 
     def f32(self, t: Optional[torch.Tensor]):
         if t is None:
             return None
-        t = _f32(t)
+        t = _f32(t, self.device)
         self.held.append(t)
         return _p(t)
 
     def u8(self, t: torch.Tensor):
-        t = t.detach().to(torch.uint8).contiguous()
+        t = t.detach().to(device=self.device, dtype=torch.uint8).contiguous()
         self.held.append(t)
         return _p(t)
 
@@ -84,7 +102,7 @@ def _pack(codes: torch.Tensor, bits: int) -> torch.Tensor:
     d = codes.shape[-1]
     flat = codes.reshape(-1, d).contiguous()
     out = torch.empty((flat.shape[0], packed_row_bytes(d, bits)), dtype=torch.uint8, device=codes.device)
-    A = _Keep()
+    A = _Keep(codes.device)
     with torch.cuda.device(codes.device):
         _lib.check(_lib.lib().qkv_pack(_p(flat), _p(out), flat.shape[0], d, bits, _stream(codes)), "pack")
     return out.reshape(*codes.shape[:-1], out.shape[1])
@@ -103,7 +121,7 @@ def _unpack(packed: torch.Tensor, bits: int, d: int) -> torch.Tensor:
         raise ValueError(f"packed rows of {flat.shape[1]} bytes cannot hold {d} fields of {bits} bits")
     flat = flat[:, :need].contiguous()
     out = torch.empty((flat.shape[0], d), dtype=torch.uint8, device=packed.device)
-    A = _Keep()
+    A = _Keep(packed.device)
     with torch.cuda.device(packed.device):
         _lib.check(_lib.lib().qkv_unpack(_p(flat), _p(out), flat.shape[0], d, bits, _stream(packed)), "unpack")
     return out.reshape(*packed.shape[:-1], d)
@@ -122,7 +140,7 @@ def _compress_mse(x: torch.Tensor, Pi: torch.Tensor, boundaries: torch.Tensor, b
     width = packed_row_bytes(d, bits) if packed else d
     codes = torch.empty((n, width), dtype=torch.uint8, device=x.device)
     norms = torch.empty((n,), dtype=torch.float32, device=x.device)
-    A = _Keep()
+    A = _Keep(x.device)
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib().qkv_compress_mse(
             _p(flat), _DT[flat.dtype], d, n, d, A.f32(Pi), A.f32(boundaries), bits,
@@ -148,7 +166,7 @@ def _compress_ip(x: torch.Tensor, Pi: torch.Tensor, boundaries: torch.Tensor, ce
     codes = torch.empty((n, cw), dtype=torch.uint8, device=x.device)
     signs = torch.empty((n, sw), dtype=torch.uint8, device=x.device)
     norms = torch.empty((n,), dtype=torch.float32, device=x.device)
-    A = _Keep()
+    A = _Keep(x.device)
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib().qkv_compress_ip(
             _p(flat), _DT[flat.dtype], d, n, d, A.f32(Pi), A.f32(boundaries), A.f32(centroids),
@@ -182,8 +200,9 @@ def _append_kv(keys: torch.Tensor, values: torch.Tensor, Pi: torch.Tensor,
     s_new = keys.shape[-2]
     cap = k_norms.shape[-1]
     rows = Rows(s_new, cap, offset)
-    Pi32 = _f32(Pi)
-    A = _Keep()
+    _same_device(keys.device, values, k_codes, k_signs, k_norms, v_codes, v_norms)
+    Pi32 = _f32(Pi, keys.device)
+    A = _Keep(keys.device)
     with torch.cuda.device(keys.device):
         L = _lib.lib()
         _lib.check(L.qkv_compress_ip(
@@ -202,7 +221,7 @@ def _compress_ip_into(x: torch.Tensor, Pi: torch.Tensor, boundaries: torch.Tenso
     """Compress (N,d) vectors into packed planes [capacity, bytes] at rows offset..offset+N."""
     flat, d = _flat(x)
     n = flat.shape[0]
-    A = _Keep()
+    A = _Keep(x.device)
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib().qkv_compress_ip(
             _p(flat), _DT[flat.dtype], d, n, d, A.f32(Pi), A.f32(boundaries), A.f32(centroids),
@@ -221,7 +240,7 @@ def _compress_mixed(x: torch.Tensor, Pi: torch.Tensor, is_outlier: torch.Tensor,
     width = int(_lib.lib().qkv_mixed_row_bytes(d, n_out, bits_out, bits_reg)) if packed else d
     codes = torch.empty((n, width), dtype=torch.uint8, device=x.device)
     norms = torch.empty((n,), dtype=torch.float32, device=x.device)
-    A = _Keep()
+    A = _Keep(x.device)
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib().qkv_compress_mixed(
             _p(flat), _DT[flat.dtype], d, n, d, A.f32(Pi), A.u8(is_outlier), A.f32(bounds_out), bits_out,
@@ -249,7 +268,7 @@ def _compress_mixed_ip(x: torch.Tensor, Pi: torch.Tensor, is_outlier: torch.Tens
     codes = torch.empty((n, d), dtype=torch.uint8, device=x.device)
     signs = torch.empty((n, d), dtype=torch.uint8, device=x.device)
     norms = torch.empty((n,), dtype=torch.float32, device=x.device)
-    A = _Keep()
+    A = _Keep(x.device)
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib().qkv_compress_mixed_ip(
             _p(flat), _DT[flat.dtype], d, n, d, A.f32(Pi), A.u8(is_outlier), A.f32(bounds_out), A.f32(cents_out),
@@ -273,7 +292,8 @@ def _decompress(codes: torch.Tensor, signs: Optional[torch.Tensor], norms: torch
     """Rows of the code/norm planes are addressed with (seg_len, seg_stride, seg_off); the
     output is dense (n_vec, d)."""
     out = torch.empty((n_vec, d), dtype=out_dtype, device=codes.device)
-    A = _Keep()
+    _same_device(codes.device, codes, signs, norms)
+    A = _Keep(codes.device)
     with torch.cuda.device(codes.device):
         _lib.check(_lib.lib().qkv_decompress(
             _p(codes), _p(signs), int(packed), _p(norms), Rows(seg_len, seg_stride, seg_off), n_vec, d,
@@ -295,7 +315,8 @@ def _decompress_mixed(codes: torch.Tensor, norms: torch.Tensor, Pi: torch.Tensor
     flat = codes.reshape(-1, codes.shape[-1]).contiguous()
     n = flat.shape[0]
     out = torch.empty((n, d), dtype=torch.float32, device=codes.device)
-    A = _Keep()
+    _same_device(codes.device, codes, norms)
+    A = _Keep(codes.device)
     with torch.cuda.device(codes.device):
         _lib.check(_lib.lib().qkv_decompress_mixed(
             _p(flat), int(packed), A.f32(norms.reshape(-1)), _dense(n), n, d, A.f32(Pi),
@@ -325,9 +346,11 @@ def _attention(q: torch.Tensor, k_codes: torch.Tensor, k_signs: torch.Tensor, k_
     L = _lib.lib()
     ws_bytes = L.qkv_attention_workspace_bytes(B, Hq, n_kv_heads, Q, kv_len, d)
     ws = torch.empty((max(ws_bytes, 16),), dtype=torch.uint8, device=q.device)
+    _same_device(q.device, k_codes, k_signs, k_norms, v_codes, v_norms)
+    _p(k_codes)                                        # refuses anything that is not device memory
     cache = Cache(k_codes.data_ptr(), k_signs.data_ptr(), k_norms.data_ptr(), v_codes.data_ptr(),
                   v_norms.data_ptr(), cap)
-    A = _Keep()
+    A = _Keep(q.device)
     with torch.cuda.device(q.device):
         _lib.check(L.qkv_attention(
             _p(qc), _DT[qc.dtype], cache, B, Hq, n_kv_heads, Q, kv_len, d, key_bits, val_bits,
@@ -359,10 +382,12 @@ def _attention_paged(q: torch.Tensor, k_codes: torch.Tensor, k_signs: torch.Tens
     L = _lib.lib()
     ws_bytes = L.qkv_attention_workspace_bytes(B, Hq, n_kv_heads, Q, max_kv_len, d)
     ws = torch.empty((max(ws_bytes, 16),), dtype=torch.uint8, device=q.device)
+    _same_device(q.device, k_codes, k_signs, k_norms, v_codes, v_norms, block_table, seq_lens)
+    _p(k_codes)
     pool = _lib.PagedCache(k_codes.data_ptr(), k_signs.data_ptr(), k_norms.data_ptr(), v_codes.data_ptr(),
                            v_norms.data_ptr(), block_table.data_ptr(), seq_lens.data_ptr(),
                            block_table.shape[1], block_size)
-    A = _Keep()
+    A = _Keep(q.device)
     with torch.cuda.device(q.device):
         _lib.check(L.qkv_attention_paged(
             _p(qc), _DT[qc.dtype], pool, B, Hq, n_kv_heads, Q, max_kv_len, d, key_bits, val_bits,
@@ -382,7 +407,8 @@ def _scatter_rows(src: torch.Tensor, dst: torch.Tensor, slots: torch.Tensor) -> 
     """Row i of src (n, ...) goes to row slots[i] of dst (rows, ...); rows are whole trailing slices."""
     n = slots.numel()
     row_bytes = (src.numel() // max(n, 1)) * src.element_size()
-    A = _Keep()
+    _same_device(src.device, src, dst, slots)
+    A = _Keep(src.device)
     with torch.cuda.device(src.device):
         _lib.check(_lib.lib().qkv_scatter_rows(_p(src), _p(dst), _p(slots), n, row_bytes, _stream(src)),
                    "scatter_rows")
@@ -413,7 +439,8 @@ def _tile_rows(k_codes: torch.Tensor, k_signs: torch.Tensor, k_norms: torch.Tens
     """File dense packed rows (n, 32 / 16 / 48 bytes, fp32 norms) into 16-token tile records.  Row i goes to
     token slot slots[i], or (i // seg_len) * seg_stride + seg_off + i % seg_len when slots is None."""
     n = k_norms.numel()
-    A = _Keep()
+    _same_device(records.device, records, k_codes, k_signs, k_norms, v_codes, v_norms, slots)
+    A = _Keep(records.device)
     with torch.cuda.device(records.device):
         _lib.check(_lib.lib().qkv_tile_rows(
             _p(k_codes), _p(k_signs), _p(k_norms), _p(v_codes), _p(v_norms), n, _p(records),
@@ -431,7 +458,8 @@ def _untile_rows(records: torch.Tensor, n_rows: int, seg_len: int, seg_stride: i
     kn = torch.empty((n_rows,), dtype=torch.float32, device=dev)
     vc = torch.empty((n_rows, 48), dtype=torch.uint8, device=dev)
     vn = torch.empty((n_rows,), dtype=torch.float32, device=dev)
-    A = _Keep()
+    _same_device(dev, records, slots)
+    A = _Keep(dev)
     with torch.cuda.device(dev):
         _lib.check(_lib.lib().qkv_untile_rows(
             _p(records), Rows(max(seg_len, 1), seg_stride, seg_off), _p(slots), n_rows, _p(kc), _p(ks), _p(kn),
@@ -463,10 +491,12 @@ def _attention_tiled(q: torch.Tensor, records: torch.Tensor, capacity: int, kv_l
     ws_bytes = L.qkv_attention_workspace_bytes(B, Hq, n_kv_heads, Q, kv_len, d)
     ws = torch.empty((max(ws_bytes, 16),), dtype=torch.uint8, device=q.device)
     paged = block_table is not None
+    _same_device(q.device, records, block_table, seq_lens)
+    _p(records)
     cache = TiledCache(records.data_ptr(), capacity, block_table.data_ptr() if paged else None,
                        seq_lens.data_ptr() if paged else None, block_table.shape[1] if paged else 0, block_size)
-    Pi32, kc32, vc32, S32 = _f32(Pi), _f32(key_centroids), _f32(val_centroids), _f32(S)   # held until the call returns
-    A = _Keep()
+    Pi32, kc32, vc32, S32 = (_f32(t, q.device) for t in (Pi, key_centroids, val_centroids, S))   # held until the call returns
+    A = _Keep(q.device)
     with torch.cuda.device(q.device):
         _lib.check(L.qkv_attention_tiled(
             _p(qc), _DT[qc.dtype], cache, B, Hq, n_kv_heads, Q, kv_len, d, 3, 3, _p(Pi32), _p(kc32), _p(vc32),
@@ -498,6 +528,8 @@ class TiledAttentionCall:
         if q.dtype not in _DT:
             q = q.float()
         qc = q if q.is_contiguous() else q.contiguous()
+        if qc.device != self.device or records.device != self.device:
+            raise ValueError(f"quashkv_b200: queries on {qc.device}, records on {records.device}, constants on {self.device}")
         out = torch.empty((B, Hq, Q, d), dtype=torch.float32, device=q.device)
         need = self.lib.qkv_attention_workspace_bytes(B, Hq, n_kv_heads, Q, kv_len, d)
         if self.ws is None or self.ws.numel() < need:
@@ -529,7 +561,8 @@ def _index_scan_topk(queries: torch.Tensor, db_codes: torch.Tensor, db_signs: to
     L = _lib.lib()
     ws_bytes = L.qkv_index_workspace_bytes(n_vectors, M, d, k)
     ws = torch.empty((max(ws_bytes, 16),), dtype=torch.uint8, device=qf.device)
-    A = _Keep()
+    _same_device(qf.device, qf, db_codes, db_signs, db_norms)
+    A = _Keep(qf.device)
     with torch.cuda.device(qf.device):
         _lib.check(L.qkv_index_scan_topk(
             _p(qf), M, d, _p(db_codes), _p(db_signs), _p(db_norms), n_vectors, bits, A.f32(Pi),
@@ -554,7 +587,8 @@ def _index_scores(queries: torch.Tensor, db_codes: torch.Tensor, db_signs: torch
     L = _lib.lib()
     ws_bytes = L.qkv_index_workspace_bytes(n_vectors, M, d, 1)
     ws = torch.empty((max(ws_bytes, 16),), dtype=torch.uint8, device=qf.device)
-    A = _Keep()
+    _same_device(qf.device, qf, db_codes, db_signs, db_norms)
+    A = _Keep(qf.device)
     with torch.cuda.device(qf.device):
         _lib.check(L.qkv_index_scores(
             _p(qf), M, d, _p(db_codes), _p(db_signs), _p(db_norms), n_vectors, bits, A.f32(Pi),
@@ -575,7 +609,8 @@ def _topk_merge(scores: torch.Tensor, ids: torch.Tensor, k: int) -> tuple[torch.
     M, n_cand = s.shape
     out_s = torch.empty((M, k), dtype=torch.float32, device=s.device)
     out_i = torch.empty((M, k), dtype=torch.int64, device=s.device)
-    A = _Keep()
+    _same_device(s.device, s, i)
+    A = _Keep(s.device)
     with torch.cuda.device(s.device):
         _lib.check(_lib.lib().qkv_topk_merge(_p(s), _p(i), M, n_cand, k, _p(out_s), _p(out_i), _stream(s)),
                    "topk_merge")

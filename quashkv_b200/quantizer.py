@@ -19,7 +19,7 @@ def _random_orthogonal(d: int, seed: int, device) -> torch.Tensor:
     """Q of the QR factorisation of a seeded Gaussian matrix, columns signed by diag(R)
     (reference quantizer.py:32-44)."""
     gen = torch.Generator(device="cpu").manual_seed(seed)
-    gauss = torch.randn(d, d, generator=gen, dtype=torch.float32)
+    gauss = torch.randn(d, d, generator=gen, dtype=torch.float32, device="cpu")
     q, r = torch.linalg.qr(gauss)
     # the QR factor comes back column-major; the kernels read Pi row-major, so make it so once, here
     return (q * torch.sign(torch.diag(r)).unsqueeze(0)).contiguous().to(device)

@@ -566,6 +566,30 @@ def test_tensor_core_decode_path_vs_generic_and_oracle(G, q_len, causal, monkeyp
     assert _lib.lib().qkv_tensor_core_timeouts() == TIMEOUTS[0]
 
 
+def test_functional_entry_points_take_constants_from_any_device(golden):
+    """The reference's functional kernels (`fused_compress_mse(x, Pi, boundaries)` ...) are called with the tables
+    of a quantizer built on the default device.  Here the data decide the device: constants on the CPU are copied
+    over (never read through a host pointer), data tensors on the wrong device are refused."""
+    from quashkv_b200 import ops
+    from quashkv_b200.triton_kernels import fused_compress_mse, fused_compress_ip
+    q = qk.MSEQuantizer(d=64, bits=3, seed=42)                       # tables on the CPU
+    assert not q.Pi.is_cuda and not q.codebook.boundaries.is_cuda
+    x = torch.randn(2, 4, 16, 64, generator=torch.Generator().manual_seed(0)).to(DEV)
+    idx, norms = fused_compress_mse(x, q.Pi, q.codebook.boundaries)
+    idx2, norms2 = q.compress(x)
+    assert torch.equal(idx, idx2) and torch.equal(norms, norms2)
+    ipq = qk.InnerProductQuantizer(d=64, total_bits=3, seed=42)
+    mq = ipq.mse_quantizer
+    a = fused_compress_ip(x, mq.Pi, mq.codebook.boundaries, ipq.S, mq.codebook.centroids)
+    b = ipq.compress(x)
+    assert all(torch.equal(u, v) for u, v in zip(a, b))
+    with pytest.raises(ValueError):
+        ops.decompress(idx, norms.cpu(), q.Pi, q.codebook.centroids, 3)     # data on two devices: refused
+    back = ops.decompress(idx, norms, q.Pi, q.codebook.centroids, 3)       # constants from the CPU: fine
+    assert torch.equal(back, q.decompress(idx, norms))
+    torch.cuda.synchronize()
+
+
 def test_tiled_attention_refuses_tables_the_records_do_not_cover():
     """The tile-record kernel presumes a symmetric value table and, for up to four query rows per KV head, a key
     table that is affine in its two code bits.  With other tables it must not return plausible numbers: the

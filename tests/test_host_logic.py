@@ -240,6 +240,23 @@ def test_engine_storage_choice_and_reset_shapes_without_gpu(monkeypatch):
     assert eng._planes["records"].shape == (6, 20, 1664)
 
 
+def test_no_host_pointer_reaches_the_library():
+    """The pointer helper refuses anything that is not device memory, and data tensors of one call have to share
+    a device: a constant built on the CPU (a quantizer made with the default device) must never be handed to a
+    kernel as if it were a device address."""
+    from quashkv_b200 import ops
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        ops._p(torch.zeros(4))
+    assert ops._p(None) is None
+    with pytest.raises(ValueError, match="different devices"):
+        ops._same_device(torch.device("cpu"), torch.zeros(1), None, torch.zeros(1, device="meta"))
+    ops._same_device(torch.device("cpu"), torch.zeros(1), None)
+    keep = ops._Keep(torch.device("meta"))
+    with pytest.raises(ValueError, match="CUDA tensor"):        # converted to the call's device first, then refused
+        keep.f32(torch.zeros(3))
+    assert keep.held[0].device.type == "meta"
+
+
 def test_device_constants_follow_replaced_and_modified_tensors():
     """The per-device copies of a quantizer's constants are tied to the source tensor object and its version:
     a replaced or modified mask / rotation is copied again, never served stale."""
