@@ -78,10 +78,14 @@ __device__ __forceinline__ void imma16832(int (&c)[4], const uint32_t (&a)[4], u
 
 // MODE 0: up to eight query rows, fp16 scores.  MODE 1: up to four rows, fp16 scores with the residual of the
 // queries in columns 4..7.  MODE 2: up to four rows, scores from bit planes on the integer tensor cores.
+// MODE 3: up to sixteen query rows as two groups of eight columns (prefill): every decoded key and value
+// fragment feeds two MMAs, so the decode work and the cache traffic per query row halve; fp16 scores.
 template <bool PAGED, int MODE>
-__global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a) {
-  constexpr bool LO4 = MODE != 0;                    // query columns n and n + 4 belong to the same query row
+__global__ void __launch_bounds__(kWarps * 32, MODE == 3 ? 3 : 4) attend_tiled_kernel(AttnArgs a) {
+  constexpr bool LO4 = MODE == 1 || MODE == 2;       // query columns n and n + 4 belong to the same query row
   constexpr bool PLANES = MODE == 2;
+  constexpr int NG = MODE == 3 ? 2 : 1;              // groups of eight query columns
+  constexpr int kRows = 8 * NG;                      // query rows per CTA
   constexpr int D = 128;
   constexpr int kTile = tile::kTokens;
   // the per-warp record rings of the token loop and the end-of-kernel reduction share storage
@@ -90,11 +94,11 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
   __shared__ __align__(128) unsigned char pool[kRingBytes > kRedBytes ? kRingBytes : kRedBytes];
   float (*red)[8][D + 2] = reinterpret_cast<float (*)[8][D + 2]>(pool);   // [warp][query][max, sum, acc]
   __shared__ __align__(8) uint64_t bars[kWarps][kRing];
-  __shared__ float wsum[8];                          // fp16 scores: sum of the sign weights per query column
+  __shared__ float wsum[kRows];                      // fp16 scores: sum of the sign weights per query column
   // B operands per lane.  fp16 scores: two k-steps per entry, 8 key-code steps, then 8 sign steps.  Bit planes:
   // the image that the rotation kernel built for this (batch, kv head): one k-step per entry (both accumulator
   // chains), 8 steps on the code words, then 4 on the sign words, followed by the constants of the query rows.
-  __shared__ __align__(16) unsigned char opbuf[PLANES ? sizeof(PlaneImage) : 8 * 32 * sizeof(uint4)];
+  __shared__ __align__(16) unsigned char opbuf[PLANES ? sizeof(PlaneImage) : NG * 8 * 32 * sizeof(uint4)];   // [group][k-steps / 2][lane]
   uint4 (*bop)[32] = reinterpret_cast<uint4 (*)[32]>(opbuf);
   __shared__ __align__(8) uint64_t img_bar;
   __shared__ uint32_t vtab[64][32];                  // value table: entry (6-bit field) x lane, an fp16 pair each
@@ -109,13 +113,13 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
   // CTAs sharing an SM differ in length, measured 5-15 % slower.)
   const int split = blockIdx.z, seg = blockIdx.x;
   const int b = seg / a.Hkv, hkv = seg % a.Hkv;
-  // Query rows of a (batch, kv head) are numbered g * q_len + position; a CTA takes eight of them
+  // Query rows of a (batch, kv head) are numbered g * q_len + position; a CTA takes eight (sixteen) of them
   // (blockIdx.y), so decode (one tile) and prefill (many) run through the same code.
-  const int r0 = 8 * blockIdx.y;
+  const int r0 = kRows * blockIdx.y;
   int64_t kv_len = a.kv_len;
   if (PAGED) kv_len = min(static_cast<int64_t>(max(a.seq_lens[b], 0)), a.kv_len);
   const int nq_all = a.G * a.q_len;
-  const int nq = nq_all - r0 < 8 ? nq_all - r0 : 8;
+  const int nq = nq_all - r0 < kRows ? nq_all - r0 : kRows;
 
   // Every (batch entry's) length is divided over the splits in whole 128-token chunks, unequal shares,
   // longest first (split_begin_chunk).
@@ -124,8 +128,9 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
   int64_t t_end = 128 * split_begin_chunk(split + 1, a.n_splits, chunks, a.skew);
   if (t_end > kv_len) t_end = kv_len;
   if (a.causal) {                      // tokens past the last position any row of this tile may see are skipped
-    int last = 0;
-    for (int r = 0; r < nq; ++r) last = max(last, (r0 + r) % a.q_len);
+    // rows r0 .. r0 + nq - 1 are consecutive positions of one query head unless they run past its end
+    const int p_first = r0 % a.q_len;
+    const int last = p_first + nq - 1 >= a.q_len ? a.q_len - 1 : p_first + nq - 1;
     const int64_t visible = kv_len - a.q_len + last + 1;
     if (t_end > visible) t_end = visible;
   }
@@ -187,65 +192,68 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
       mbar_expect_tx(&img_bar, sizeof(PlaneImage));
       bulk_load(opbuf, a.planes + seg, sizeof(PlaneImage), &img_bar);
     }
-  } else {
-    // In LO4 mode query column n >= 4 is the residual of column n - 4.
-    for (int idx = threadIdx.x; has_work && idx < 8 * 2 * D; idx += blockDim.x) {
-      const int r = idx / (2 * D), e = idx % (2 * D);
-      const int rq = LO4 ? (r & 3) : r;
-      float v = 0.f;
-      if (rq < nq) {
-        const int g = (r0 + rq) / a.q_len, qi = (r0 + rq) % a.q_len;
-        const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
-        v = a.qk[qrow * 2 * D + e];
-      }
-      q_s[r][e] = v;
-    }
-    __syncthreads();
   }
   const float inv_sk = __uint_as_float(a.tables[6]), inv_sv = __uint_as_float(a.tables[7]);
   if (!PLANES) {
-    if (has_work) {                   // a warp sums the sign weights of two query columns
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int col = 2 * warp + h;
-        const float* w = q_s[col] + D;
-        float t = (w[lane] + w[lane + 32]) + (w[lane + 64] + w[lane + 96]);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(QKV_FULL_MASK, t, o);
-        if (lane == 0) wsum[col] = (LO4 && col >= 4) ? 0.f : t * kLog2e;
+#pragma unroll 1
+    for (int grp = 0; grp < NG; ++grp) {              // eight query rows at a time through the staging area
+      // In LO4 mode query column n >= 4 is the residual of column n - 4.
+      for (int idx = threadIdx.x; has_work && idx < 8 * 2 * D; idx += blockDim.x) {
+        const int r = idx / (2 * D), e = idx % (2 * D);
+        const int rq = 8 * grp + (LO4 ? (r & 3) : r);
+        float v = 0.f;
+        if (rq < nq) {
+          const int g = (r0 + rq) / a.q_len, qi = (r0 + rq) % a.q_len;
+          const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
+          v = a.qk[qrow * 2 * D + e];
+        }
+        q_s[r][e] = v;
       }
-    }
-    __syncthreads();
+      __syncthreads();
+      if (has_work) {                   // a warp sums the sign weights of two query columns
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int col = 2 * warp + h;
+          const float* w = q_s[col] + D;
+          float t = (w[lane] + w[lane + 32]) + (w[lane + 64] + w[lane + 96]);
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(QKV_FULL_MASK, t, o);
+          if (lane == 0) wsum[8 * grp + col] = (LO4 && col >= 4) ? 0.f : t * kLog2e;
+        }
+      }
 
-    // ---- B operands for query column n = gid ---------------------------------------------------------
-    // Key-code k-step s = 4*word + f covers this lane's coordinates 32 tig + 16 word + {f, 4+f | 8+f, 12+f}
-    // (the order in which tile::key_fragment produces them).  Sign k-step s covers 32 tig + {2s, 2s+16 | 2s+1, 2s+17}
-    // through sign_coord / sign_pos.
-    if (has_work) {                   // the operands depend on the lane only: each warp builds two k-steps
-      const float qf = kLog2e * inv_sk;
-      const float* q = q_s[gid];
-      const float* w = q_s[gid] + D;
-      const bool resid = LO4 && gid >= 4;
+      // ---- B operands for query column n = gid ---------------------------------------------------------
+      // Key-code k-step s = 4*word + f covers this lane's coordinates 32 tig + 16 word + {f, 4+f | 8+f, 12+f}
+      // (the order in which tile::key_fragment produces them).  Sign k-step s covers 32 tig + {2s, 2s+16 | 2s+1,
+      // 2s+17} through sign_coord / sign_pos.
+      if (has_work) {                   // the operands depend on the lane only: each warp builds two k-steps
+        const float qf = kLog2e * inv_sk;
+        const float* q = q_s[gid];
+        const float* w = q_s[gid] + D;
+        const bool resid = LO4 && gid >= 4;
+        uint4 (*bg)[32] = bop + 8 * grp;
 #pragma unroll
-      for (int s = warp; s < 8; s += kWarps) {
-        const int word = s >> 2, f = s & 3;
-        const int c0 = 32 * tig + 16 * word + f;
-        float v[4];
+        for (int s = warp; s < 8; s += kWarps) {
+          const int word = s >> 2, f = s & 3;
+          const int c0 = 32 * tig + 16 * word + f;
+          float v[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          v[e] = q[c0 + 4 * e] * qf;
-          if (resid) v[e] -= __half2float(__float2half_rn(v[e]));
+          for (int e = 0; e < 4; ++e) {
+            v[e] = q[c0 + 4 * e] * qf;
+            if (resid) v[e] -= __half2float(__float2half_rn(v[e]));
+          }
+          reinterpret_cast<uint2*>(&bg[s >> 1][lane])[s & 1] = make_uint2(pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
+          uint32_t wq[2];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {           // pairs t = 2s, 2s+1 of this lane's 32 coordinates
+            const int t = 2 * s + h, j = 32 * tig + sign_coord(t);
+            const float fs = resid ? 0.f : 2.f * kLog2e / sign_v1(sign_pos(t));
+            wq[h] = pack_half2(w[j] * fs, w[j + 16] * fs);
+          }
+          reinterpret_cast<uint2*>(&bg[4 + (s >> 1)][lane])[s & 1] = make_uint2(wq[0], wq[1]);
         }
-        reinterpret_cast<uint2*>(&bop[s >> 1][lane])[s & 1] = make_uint2(pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
-        uint32_t wq[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {           // pairs t = 2s, 2s+1 of this lane's 32 coordinates
-          const int t = 2 * s + h, j = 32 * tig + sign_coord(t);
-          const float fs = resid ? 0.f : 2.f * kLog2e / sign_v1(sign_pos(t));
-          wq[h] = pack_half2(w[j] * fs, w[j + 16] * fs);
-        }
-        reinterpret_cast<uint2*>(&bop[4 + (s >> 1)][lane])[s & 1] = make_uint2(wq[0], wq[1]);
       }
+      __syncthreads();                  // the staging area is free for the next group (or for the value table)
     }
   }
   __syncthreads();
@@ -265,28 +273,37 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
   __syncthreads();
   const unsigned char* vt_base = reinterpret_cast<const unsigned char*>(&vtab[0][0]);
   const uint32_t lane4 = 4u * lane;
-  // causal limits of this lane's two query columns (2 tig, 2 tig + 1), relative to the split start
-  int lim_rel[2];
+  // causal limits of this lane's query columns (2 tig, 2 tig + 1 of every group), relative to the split start
+  int lim_rel[NG][2];
 #pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    const int col = 2 * tig + e;
-    const int r = LO4 ? (col & 3) : col;
-    int lim = (r < nq) ? (a.causal ? static_cast<int>(kv_len - a.q_len + (r0 + r) % a.q_len) : 0x7fffffff) : -1;
-    const int64_t dlt = static_cast<int64_t>(lim) - t_begin;
-    lim_rel[e] = lim == 0x7fffffff ? 0x7fffffff : (dlt < -1 ? -1 : static_cast<int>(dlt));
+  for (int grp = 0; grp < NG; ++grp) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int col = 2 * tig + e;
+      const int r = 8 * grp + (LO4 ? (col & 3) : col);
+      int lim = (r < nq) ? (a.causal ? static_cast<int>(kv_len - a.q_len + (r0 + r) % a.q_len) : 0x7fffffff) : -1;
+      const int64_t dlt = static_cast<int64_t>(lim) - t_begin;
+      lim_rel[grp][e] = lim == 0x7fffffff ? 0x7fffffff : (dlt < -1 ? -1 : static_cast<int>(dlt));
+    }
   }
 
-  float O[8][4];
+  float O[NG][8][4];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f;
+  for (int grp = 0; grp < NG; ++grp)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) O[grp][i][0] = O[grp][i][1] = O[grp][i][2] = O[grp][i][3] = 0.f;
   // reference exponents start at a finite "nothing seen yet" value (any finite score raises them at once), so that
   // the token loop needs no test for minus infinity; the value written out below turns it back into -inf
   constexpr float kNone = -1e30f;
-  float m[2] = {kNone, kNone}, l[2] = {0.f, 0.f};
+  float m[NG][2], l[NG][2];
+#pragma unroll
+  for (int grp = 0; grp < NG; ++grp) { m[grp][0] = m[grp][1] = kNone; l[grp][0] = l[grp][1] = 0.f; }
   // fp16 scores: the accumulators start at -sum of the sign weights.  Bit planes: columns 2 tig, 2 tig + 1 hold
   // terms (t1, t3) of queries 2 tig + e for tig < 2, terms (t2, t4) of queries 2 (tig - 2) + e otherwise; kA, kB
   // turn the two integer sums into score units and ci is the constant of the query (counted once, by tig < 2).
-  float ci0 = 0.f, ci1 = 0.f, kA[2] = {0.f, 0.f}, kB[2] = {0.f, 0.f};
+  float ci[NG][2], kA[2] = {0.f, 0.f}, kB[2] = {0.f, 0.f};
+#pragma unroll
+  for (int grp = 0; grp < NG; ++grp) ci[grp][0] = ci[grp][1] = 0.f;
   bool img_failed = false;
   if (PLANES) {
     if (has_work) {
@@ -300,17 +317,20 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
         kA[e] = hi ? u * (1.f / 128.f) : u;
         kB[e] = hi ? u * (1.f / 2097152.f) : u * (1.f / 16384.f);
       }
-      ci0 = (hi ? 0.f : img->cst[(2 * tig) & 3]) - 12582912.f * kB[0];
-      ci1 = (hi ? 0.f : img->cst[(2 * tig + 1) & 3]) - 12582912.f * kB[1];
+      ci[0][0] = (hi ? 0.f : img->cst[(2 * tig) & 3]) - 12582912.f * kB[0];
+      ci[0][1] = (hi ? 0.f : img->cst[(2 * tig + 1) & 3]) - 12582912.f * kB[1];
     }
   } else {
-    ci0 = -wsum[2 * tig];
-    ci1 = -wsum[2 * tig + 1];
+#pragma unroll
+    for (int grp = 0; grp < NG; ++grp) {
+      ci[grp][0] = -wsum[8 * grp + 2 * tig];
+      ci[grp][1] = -wsum[8 * grp + 2 * tig + 1];
+    }
   }
 
   auto process = [&](const TileRegs& cur, int rel) {
     const bool masked = a.causal || rel + kTile > n_valid;      // warp-uniform
-    float c[4];
+    float c[NG][4];
     if constexpr (PLANES) {
       // ---- scores from bit planes: 12 k-steps of 32 single-bit elements, two integer accumulator chains ----
       constexpr int kMagic = 0x4B400000;                         // bit pattern of 1.5 * 2^23
@@ -339,50 +359,57 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float fa = __int_as_float(ia[e]) - kMagicF;
-        c[e] = fmaf(fa, kA[e & 1], fmaf(__int_as_float(ib[e]), kB[e & 1], (e & 1) ? ci1 : ci0));
+        c[0][e] = fmaf(fa, kA[e & 1], fmaf(__int_as_float(ib[e]), kB[e & 1], ci[0][e & 1]));
       }
     } else {
-    // ---- scores: 8 MMAs on key codes, 8 on sign bits --------------------------------------------
-    c[0] = ci0; c[1] = ci1; c[2] = ci0; c[3] = ci1;
-    {
-      uint32_t af[4];
-      uint4 bq;
-#define QKV_KEY_STEPS(W0, W1, WORD, F)                                  \
-  bq = bop[(WORD) * 2 + (F) / 2][lane];                                 \
-  tile::key_fragment<F>(W0, W1, kt_a, kt_b, af);                        \
-  mma16816(c, af, bq.x, bq.y);                                          \
-  tile::key_fragment<F + 1>(W0, W1, kt_a, kt_b, af);                    \
-  mma16816(c, af, bq.z, bq.w);
-      QKV_KEY_STEPS(cur.kc.x, cur.kc.z, 0, 0) QKV_KEY_STEPS(cur.kc.x, cur.kc.z, 0, 2)
-      QKV_KEY_STEPS(cur.kc.y, cur.kc.w, 1, 0) QKV_KEY_STEPS(cur.kc.y, cur.kc.w, 1, 2)
+      // ---- scores: 8 MMAs on key codes, 8 on sign bits, per group of eight query columns ----------------
+#pragma unroll
+      for (int grp = 0; grp < NG; ++grp) {
+        c[grp][0] = ci[grp][0]; c[grp][1] = ci[grp][1]; c[grp][2] = ci[grp][0]; c[grp][3] = ci[grp][1];
+      }
+      {
+        uint32_t af[4];
+        uint4 bq[NG];
+#define QKV_KEY_STEPS(W0, W1, WORD, F)                                                      \
+  _Pragma("unroll") for (int grp = 0; grp < NG; ++grp) bq[grp] = bop[8 * grp + (WORD) * 2 + (F) / 2][lane];   \
+  tile::key_fragment<F>(W0, W1, kt_a, kt_b, af);                                            \
+  _Pragma("unroll") for (int grp = 0; grp < NG; ++grp) mma16816(c[grp], af, bq[grp].x, bq[grp].y);            \
+  tile::key_fragment<F + 1>(W0, W1, kt_a, kt_b, af);                                        \
+  _Pragma("unroll") for (int grp = 0; grp < NG; ++grp) mma16816(c[grp], af, bq[grp].z, bq[grp].w);
+        QKV_KEY_STEPS(cur.kc.x, cur.kc.z, 0, 0) QKV_KEY_STEPS(cur.kc.x, cur.kc.z, 0, 2)
+        QKV_KEY_STEPS(cur.kc.y, cur.kc.w, 1, 0) QKV_KEY_STEPS(cur.kc.y, cur.kc.w, 1, 2)
 #undef QKV_KEY_STEPS
-    }
-    {
-      const uint32_t cp0[4] = {cur.ks.x, cur.ks.x << 7, cur.ks.x >> 1, cur.ks.x << 13};
-      const uint32_t cp1[4] = {cur.ks.y, cur.ks.y << 7, cur.ks.y >> 1, cur.ks.y << 13};
+      }
+      {
+        const uint32_t cp0[4] = {cur.ks.x, cur.ks.x << 7, cur.ks.x >> 1, cur.ks.x << 13};
+        const uint32_t cp1[4] = {cur.ks.y, cur.ks.y << 7, cur.ks.y >> 1, cur.ks.y << 13};
 #pragma unroll
-      for (int s2 = 0; s2 < 4; ++s2) {
-        const uint4 bw = bop[4 + s2][lane];
+        for (int s2 = 0; s2 < 4; ++s2) {
+          uint4 bw[NG];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int s = 2 * s2 + u;
-          uint32_t af[4];
+          for (int grp = 0; grp < NG; ++grp) bw[grp] = bop[8 * grp + 4 + s2][lane];
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int t = 2 * s + h;
-            const int cpy = t < 7 ? 0 : (t < 14 ? 1 : t - 12);
-            const uint32_t mask = 0x00010001u << sign_pos(t);
-            af[2 * h] = cp0[cpy] & mask;
-            af[2 * h + 1] = cp1[cpy] & mask;
+          for (int u = 0; u < 2; ++u) {
+            const int s = 2 * s2 + u;
+            uint32_t af[4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int t = 2 * s + h;
+              const int cpy = t < 7 ? 0 : (t < 14 ? 1 : t - 12);
+              const uint32_t mask = 0x00010001u << sign_pos(t);
+              af[2 * h] = cp0[cpy] & mask;
+              af[2 * h + 1] = cp1[cpy] & mask;
+            }
+#pragma unroll
+            for (int grp = 0; grp < NG; ++grp)
+              mma16816(c[grp], af, u ? bw[grp].z : bw[grp].x, u ? bw[grp].w : bw[grp].y);
           }
-          mma16816(c, af, u ? bw.z : bw.x, u ? bw.w : bw.y);
         }
       }
     }
-    }
     if (LO4) {                      // column n + 4 holds the other part of column n: add the two
 #pragma unroll
-      for (int e = 0; e < 4; ++e) c[e] += __shfl_xor_sync(QKV_FULL_MASK, c[e], 2);
+      for (int e = 0; e < 4; ++e) c[0][e] += __shfl_xor_sync(QKV_FULL_MASK, c[0][e], 2);
     }
 
     // ---- online softmax on the accumulator fragment (log2 domain) ------------------------------
@@ -394,49 +421,55 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
     constexpr float kSlack = 4.f;
     const float kn0 = cur.nrm.x, kn1 = cur.nrm.y;
     float vn0 = cur.nrm.z, vn1 = cur.nrm.w;
-    float t[4] = {fmaf(c[0], kn0, -m[0]), fmaf(c[1], kn0, -m[1]), fmaf(c[2], kn1, -m[0]), fmaf(c[3], kn1, -m[1])};
+    const int tokA = rel + gid, tokB = tokA + 8;
     if (masked) {
-      const int tokA = rel + gid, tokB = tokA + 8;
-      if (!(tokA < n_valid && tokA <= lim_rel[0])) t[0] = -INFINITY;
-      if (!(tokA < n_valid && tokA <= lim_rel[1])) t[1] = -INFINITY;
-      if (!(tokB < n_valid && tokB <= lim_rel[0])) t[2] = -INFINITY;
-      if (!(tokB < n_valid && tokB <= lim_rel[1])) t[3] = -INFINITY;
       if (tokA >= n_valid) vn0 = 0.f;         // rows past the end of the sequence hold no data
       if (tokB >= n_valid) vn1 = 0.f;
     }
-    if (__any_sync(QKV_FULL_MASK, fmaxf(fmaxf(t[0], t[2]), fmaxf(t[1], t[3])) > kSlack)) {
-      // (rare after the first tiles) exact scores again: against the start value of m, t has lost them
-      float sc[4] = {c[0] * kn0, c[1] * kn0, c[2] * kn1, c[3] * kn1};
+    uint32_t pb[NG][2];             // weights times value norm, in the B layout (tokens as K, query = gid as N)
 #pragma unroll
-      for (int e = 0; e < 4; ++e)
-        if (t[e] == -INFINITY) sc[e] = -INFINITY;
-      float mx[2] = {fmaxf(sc[0], sc[2]), fmaxf(sc[1], sc[3])};
-#pragma unroll
-      for (int o = 4; o < 32; o <<= 1) {
-        mx[0] = fmaxf(mx[0], __shfl_xor_sync(QKV_FULL_MASK, mx[0], o));
-        mx[1] = fmaxf(mx[1], __shfl_xor_sync(QKV_FULL_MASK, mx[1], o));
+    for (int grp = 0; grp < NG; ++grp) {
+      float t[4] = {fmaf(c[grp][0], kn0, -m[grp][0]), fmaf(c[grp][1], kn0, -m[grp][1]),
+                    fmaf(c[grp][2], kn1, -m[grp][0]), fmaf(c[grp][3], kn1, -m[grp][1])};
+      if (masked) {
+        if (!(tokA < n_valid && tokA <= lim_rel[grp][0])) t[0] = -INFINITY;
+        if (!(tokA < n_valid && tokA <= lim_rel[grp][1])) t[1] = -INFINITY;
+        if (!(tokB < n_valid && tokB <= lim_rel[grp][0])) t[2] = -INFINITY;
+        if (!(tokB < n_valid && tokB <= lim_rel[grp][1])) t[3] = -INFINITY;
       }
-      float al[2];
+      if (__any_sync(QKV_FULL_MASK, fmaxf(fmaxf(t[0], t[2]), fmaxf(t[1], t[3])) > kSlack)) {
+        // (rare after the first tiles) exact scores again: against the start value of m, t has lost them
+        float sc[4] = {c[grp][0] * kn0, c[grp][1] * kn0, c[grp][2] * kn1, c[grp][3] * kn1};
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        al[e] = (mx[e] > m[e]) ? ex2(m[e] - mx[e]) : 1.f;     // ex2(kNone - x) = 0 on the first tile
-        m[e] = fmaxf(m[e], mx[e]);
-        l[e] *= al[e];
-      }
+        for (int e = 0; e < 4; ++e)
+          if (t[e] == -INFINITY) sc[e] = -INFINITY;
+        float mx[2] = {fmaxf(sc[0], sc[2]), fmaxf(sc[1], sc[3])};
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        O[i][0] *= al[0]; O[i][1] *= al[1]; O[i][2] *= al[0]; O[i][3] *= al[1];
+        for (int o = 4; o < 32; o <<= 1) {
+          mx[0] = fmaxf(mx[0], __shfl_xor_sync(QKV_FULL_MASK, mx[0], o));
+          mx[1] = fmaxf(mx[1], __shfl_xor_sync(QKV_FULL_MASK, mx[1], o));
+        }
+        float al[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          al[e] = (mx[e] > m[grp][e]) ? ex2(m[grp][e] - mx[e]) : 1.f;     // ex2(kNone - x) = 0 on the first tile
+          m[grp][e] = fmaxf(m[grp][e], mx[e]);
+          l[grp][e] *= al[e];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          O[grp][i][0] *= al[0]; O[grp][i][1] *= al[1]; O[grp][i][2] *= al[0]; O[grp][i][3] *= al[1];
+        }
+        t[0] = sc[0] - m[grp][0]; t[1] = sc[1] - m[grp][1]; t[2] = sc[2] - m[grp][0]; t[3] = sc[3] - m[grp][1];
       }
-      t[0] = sc[0] - m[0]; t[1] = sc[1] - m[1]; t[2] = sc[2] - m[0]; t[3] = sc[3] - m[1];
+      const float p0 = ex2(t[0]), p1 = ex2(t[1]), p2 = ex2(t[2]), p3 = ex2(t[3]);   // masked entries: weight 0
+      l[grp][0] += p0 + p2;
+      l[grp][1] += p1 + p3;
+      pb[grp][0] = movmatrix_trans(pack_half2(p0 * vn0, p1 * vn0));
+      pb[grp][1] = movmatrix_trans(pack_half2(p2 * vn1, p3 * vn1));
     }
-    const float p0 = ex2(t[0]), p1 = ex2(t[1]), p2 = ex2(t[2]), p3 = ex2(t[3]);   // masked entries: weight 0
-    l[0] += p0 + p2;
-    l[1] += p1 + p3;
-    // weights times value norm, transposed into the B layout (tokens as K, query = gid as N)
-    const uint32_t pb0 = movmatrix_trans(pack_half2(p0 * vn0, p1 * vn0));
-    const uint32_t pb1 = movmatrix_trans(pack_half2(p2 * vn1, p3 * vn1));
 
-    // ---- values: one table look-up per pair of tokens, 8 MMAs ---------------------------------------
+    // ---- values: one table look-up per pair of tokens, 8 MMAs per group --------------------------------
     {
       uint32_t af[4];
       auto vt = [&](uint32_t off) { return *reinterpret_cast<const uint32_t*>(vt_base + off); };
@@ -445,7 +478,7 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
   af[1] = vt(tile::value_table_offset<2 * (I) + 1>(cur.va.x, cur.va.y, cur.va.z, lane4));                 \
   af[2] = vt(tile::value_table_offset<2 * (I)>(cur.va.w, cur.vb.x, cur.vb.y, lane4));                     \
   af[3] = vt(tile::value_table_offset<2 * (I) + 1>(cur.va.w, cur.vb.x, cur.vb.y, lane4));                 \
-  mma16816(O[I], af, pb0, pb1);
+  _Pragma("unroll") for (int grp = 0; grp < NG; ++grp) mma16816(O[grp][I], af, pb[grp][0], pb[grp][1]);
       QKV_VAL_STEP(0) QKV_VAL_STEP(1) QKV_VAL_STEP(2) QKV_VAL_STEP(3)
       QKV_VAL_STEP(4) QKV_VAL_STEP(5) QKV_VAL_STEP(6) QKV_VAL_STEP(7)
 #undef QKV_VAL_STEP
@@ -501,57 +534,121 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
   if (img_failed && lane == 0) atomicAdd(&g_bulk_timeouts, 1u);   // same for the operand image (its storage is not reused)
   __syncthreads();                        // the reduction buffer below reuses the ring storage
 
-  // ---- per-warp results to shared memory: column sums over the token lanes, then all warps ------
+  // out rows = vec @ Pi for up to eight rows `vec[r][D]` in shared memory.  Warp w takes rows 32 w .. 32 w + 31 of
+  // Pi, a lane four output coordinates, so that the 32 loads of a thread are independent (two rounds of 16); the
+  // four warps' partial sums meet in `psum` ([kWarps][8][D], shared memory that nobody else is reading).
+  // A table that breaks what the record format (symmetric value table) or the bit planes (key table affine in
+  // its code bits) presume would give wrong numbers silently: NaN instead.
+  const bool broken = (a.tables[10] & (PLANES ? 3u : 1u)) != 0u;
+  auto unrotate = [&](const float* vec, float* psum, int n_rows, const int64_t* qrow) {
+    float4 o[8];
 #pragma unroll
-  for (int o = 4; o < 32; o <<= 1) {
-    l[0] += __shfl_xor_sync(QKV_FULL_MASK, l[0], o);
-    l[1] += __shfl_xor_sync(QKV_FULL_MASK, l[1], o);
-  }
+    for (int r = 0; r < 8; ++r) o[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4* prow = reinterpret_cast<const float4*>(a.Pi + static_cast<int64_t>(32 * warp) * D) + lane;
+#pragma unroll 16
+    for (int jj = 0; jj < 32; ++jj) {
+      const float4 mval = __ldg(prow + jj * (D / 4));
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float x = vec[r * D + 32 * warp + jj];
+        o[r].x = fmaf(x, mval.x, o[r].x);
+        o[r].y = fmaf(x, mval.y, o[r].y);
+        o[r].z = fmaf(x, mval.z, o[r].z);
+        o[r].w = fmaf(x, mval.w, o[r].w);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r) *reinterpret_cast<float4*>(psum + (warp * 8 + r) * D + 4 * lane) = o[r];
+    __syncthreads();
+    const int i = threadIdx.x;                       // output coordinate (blockDim.x == D)
+    for (int r = 0; r < n_rows; ++r) {
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) v += psum[(w * 8 + r) * D + i];
+      a.out[qrow[r] * D + i] = broken ? __int_as_float(0x7fc00000) : v;
+    }
+  };
+  // With a single split there is nothing to merge: the rows go from the reduction buffer straight through the
+  // un-rotation, without the round trip through the partials in global memory, the fence and the arrival counter.
+  const bool single = a.n_splits == 1;
+  float* vec1 = reinterpret_cast<float*>(pool + kRedBytes);     // [8][D] behind the reduction buffer
+  static_assert(kRedBytes + 8 * D * 4 <= sizeof(pool) && kWarps * 8 * D * 4 <= kRedBytes, "single-split buffers fit");
+
+  // ---- per-warp results to shared memory: column sums over the token lanes, then all warps; a group of eight
+  // query columns at a time through the same buffer ------------------------------------------------------------
   constexpr float kLn2 = 0.6931471805599453f;
-#pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    float* dst = red[warp][2 * tig + e];
-    if (gid == 0) {
-      dst[0] = m[e] == kNone ? -INFINITY : m[e] * kLn2;   // natural-log units, as the merge expects; -inf = no token
-      dst[1] = l[e];
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {   // M-tile i holds coordinates 16 gid + 2 i, +1
-      dst[2 + 16 * gid + 2 * i] = O[i][e] * inv_sv;
-      dst[2 + 16 * gid + 2 * i + 1] = O[i][2 + e] * inv_sv;
-    }
-  }
   // weights of the four warps' results per query row, and where the row's partials go: once per row, not per entry
   __shared__ float fw_s[kWarps][8], mrow_s[8];
-  __shared__ int64_t qrow_s[8];
-  __syncthreads();
-  if (threadIdx.x < 8 * kWarps) {
-    const int w = threadIdx.x >> 3, r = threadIdx.x & 7;
-    float M = -INFINITY;
+  __shared__ int64_t qrow_s[kRows];
+  if (threadIdx.x < kRows) {
+    const int r = threadIdx.x;
+    const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
+    qrow_s[r] = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
+  }
 #pragma unroll
-    for (int u = 0; u < kWarps; ++u) M = fmaxf(M, red[u][r][0]);
-    fw_s[w][r] = (red[w][r][0] == -INFINITY) ? 0.f : expf(red[w][r][0] - M);
-    if (w == 0) {
-      mrow_s[r] = M;
-      const int g = (r0 + r) / a.q_len, qi = (r0 + r) % a.q_len;
-      qrow_s[r] = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
+  for (int grp = 0; grp < NG; ++grp) {
+    if (grp > 0) __syncthreads();                     // the previous group's rows have been read
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+      l[grp][0] += __shfl_xor_sync(QKV_FULL_MASK, l[grp][0], o);
+      l[grp][1] += __shfl_xor_sync(QKV_FULL_MASK, l[grp][1], o);
+    }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      float* dst = red[warp][2 * tig + e];
+      if (gid == 0) {
+        dst[0] = m[grp][e] == kNone ? -INFINITY : m[grp][e] * kLn2;   // natural-log units, as the merge expects; -inf = no token
+        dst[1] = l[grp][e];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {   // M-tile i holds coordinates 16 gid + 2 i, +1
+        dst[2 + 16 * gid + 2 * i] = O[grp][i][e] * inv_sv;
+        dst[2 + 16 * gid + 2 * i + 1] = O[grp][i][2 + e] * inv_sv;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < 8 * kWarps) {
+      const int w = threadIdx.x >> 3, r = threadIdx.x & 7;
+      float M = -INFINITY;
+#pragma unroll
+      for (int u = 0; u < kWarps; ++u) M = fmaxf(M, red[u][r][0]);
+      fw_s[w][r] = (red[w][r][0] == -INFINITY) ? 0.f : expf(red[w][r][0] - M);
+      if (w == 0) mrow_s[r] = M;
+    }
+    __syncthreads();
+    const int nqg = nq - 8 * grp < 8 ? nq - 8 * grp : 8;
+    if (single) {
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {                  // a thread per coordinate
+        float v = 0.f, sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+          v = fmaf(fw_s[w][r], red[w][r][2 + threadIdx.x], v);
+          sum = fmaf(fw_s[w][r], red[w][r][1], sum);
+        }
+        vec1[r * D + threadIdx.x] = r < nqg ? v / fmaxf(sum, 1e-30f) : 0.f;
+      }
+      __syncthreads();                               // rows complete; the reduction buffer is free for the sums
+      unrotate(vec1, reinterpret_cast<float*>(pool), nqg, qrow_s + 8 * grp);
+      continue;
+    }
+    for (int r = 0; r < nqg; ++r) {                  // a thread per coordinate; threads 0, 1 also write max and sum
+      float* dst = a.part + (qrow_s[8 * grp + r] * a.n_splits + split) * (D + 2);
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) v = fmaf(fw_s[w][r], red[w][r][2 + threadIdx.x], v);
+      dst[2 + threadIdx.x] = v;
+      if (threadIdx.x == 0) dst[0] = mrow_s[r];
+      if (threadIdx.x == 1) {
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) sum = fmaf(fw_s[w][r], red[w][r][1], sum);
+        dst[1] = sum;
+      }
     }
   }
-  __syncthreads();
-  for (int r = 0; r < nq; ++r) {                     // a thread per coordinate; threads 0, 1 also write max and sum
-    float* dst = a.part + (qrow_s[r] * a.n_splits + split) * (D + 2);
-    float v = 0.f;
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) v = fmaf(fw_s[w][r], red[w][r][2 + threadIdx.x], v);
-    dst[2 + threadIdx.x] = v;
-    if (threadIdx.x == 0) dst[0] = mrow_s[r];
-    if (threadIdx.x == 1) {
-      float sum = 0.f;
-#pragma unroll
-      for (int w = 0; w < kWarps; ++w) sum = fmaf(fw_s[w][r], red[w][r][1], sum);
-      dst[1] = sum;
-    }
-  }
+
+  if (single) return;
 
   // ---- the CTA that finishes a (batch, kv head) last merges its splits and applies Pi ----------------
   __shared__ bool last_split;
@@ -566,10 +663,13 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
   float* wgt = vec + 8 * D;                          // [8][kMaxSplits] weights of the splits
   float* invl = wgt + 8 * kMaxSplits;                // [8]
   static_assert((8 * D + 8 * kMaxSplits + 8 + kWarps * 8 * D) * 4 <= sizeof(pool), "merge buffers fit the ring storage");
+  for (int grp = 0; grp < NG; ++grp) {               // eight query rows at a time through the merge buffers
+  const int nqg = nq - 8 * grp < 8 ? nq - 8 * grp : 8;
+  if (grp > 0) __syncthreads();
   // This tail runs once per (batch, kv head) at the very end of the call, so it is written for latency: every
   // round of loads is issued before the first result is used.
-  for (int r = warp; r < nq; r += kWarps) {          // a warp per query row; a lane takes splits lane, lane + 32
-    const float* pp = a.part + qrow_s[r] * a.n_splits * (D + 2);
+  for (int r = warp; r < nqg; r += kWarps) {          // a warp per query row; a lane takes splits lane, lane + 32
+    const float* pp = a.part + qrow_s[8 * grp + r] * a.n_splits * (D + 2);
     float mm[2], ll[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -594,9 +694,9 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
     if (lane == 0) invl[r] = 1.f / fmaxf(L, 1e-30f);
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < nq * (D / 2); idx += blockDim.x) {     // a thread per pair of coordinates
+  for (int idx = threadIdx.x; idx < nqg * (D / 2); idx += blockDim.x) {     // a thread per pair of coordinates
     const int r = idx / (D / 2), j = 2 * (idx % (D / 2));
-    const float* pp = a.part + qrow_s[r] * a.n_splits * (D + 2) + 2 + j;  // 8-byte aligned: rows of 130 floats
+    const float* pp = a.part + qrow_s[8 * grp + r] * a.n_splits * (D + 2) + 2 + j;  // 8-byte aligned: rows of 130 floats
     const float* w = wgt + r * kMaxSplits;
     float2 acc = make_float2(0.f, 0.f);
     for (int sp = 0; sp < a.n_splits; sp += 16) {                         // sixteen splits per round of loads
@@ -615,39 +715,7 @@ __global__ void __launch_bounds__(kWarps * 32, 4) attend_tiled_kernel(AttnArgs a
     vec[r * D + j + 1] = acc.y * invl[r];
   }
   __syncthreads();
-  {
-    // out = vec @ Pi.  Warp w takes rows 32 w .. 32 w + 31 of Pi, a lane four output coordinates, so that the 32
-    // loads of a thread are independent (two rounds of 16); the four partial sums meet in shared memory.
-    float4 o[8];
-#pragma unroll
-    for (int r = 0; r < 8; ++r) o[r] = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4* prow = reinterpret_cast<const float4*>(a.Pi + static_cast<int64_t>(32 * warp) * D) + lane;
-#pragma unroll 16
-    for (int jj = 0; jj < 32; ++jj) {
-      const float4 mval = __ldg(prow + jj * (D / 4));
-#pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const float x = vec[r * D + 32 * warp + jj];
-        o[r].x = fmaf(x, mval.x, o[r].x);
-        o[r].y = fmaf(x, mval.y, o[r].y);
-        o[r].z = fmaf(x, mval.z, o[r].z);
-        o[r].w = fmaf(x, mval.w, o[r].w);
-      }
-    }
-    float* psum = invl + 8;                            // [kWarps][8][D] partial sums, behind vec, wgt and invl
-#pragma unroll
-    for (int r = 0; r < 8; ++r) *reinterpret_cast<float4*>(psum + (warp * 8 + r) * D + 4 * lane) = o[r];
-    __syncthreads();
-    const int i = threadIdx.x;                       // output coordinate (blockDim.x == D)
-    // A table that breaks what the record format (symmetric value table) or the bit planes (key table affine in
-    // its code bits) presume would give wrong numbers silently: give NaN instead.
-    const bool broken = (a.tables[10] & (PLANES ? 3u : 1u)) != 0u;
-    for (int r = 0; r < nq; ++r) {
-      float v = 0.f;
-#pragma unroll
-      for (int w = 0; w < kWarps; ++w) v += psum[(w * 8 + r) * D + i];
-      a.out[qrow_s[r] * D + i] = broken ? __int_as_float(0x7fc00000) : v;
-    }
+  unrotate(vec, invl + 8, nqg, qrow_s + 8 * grp);   // partial sums behind vec, wgt and invl
   }
 }
 
@@ -669,8 +737,21 @@ bool tiled_scores_from_planes(int group, int q_len) {
   return !(e && e[0] == 'f');
 }
 
+// QUASHKV_B200_PREFILL_ROWS=8 keeps eight query rows per CTA for longer query blocks too (for comparison).
+static bool sixteen_rows(int nq_all) {
+  if (nq_all <= 8) return false;
+  const char* e = getenv("QUASHKV_B200_PREFILL_ROWS");
+  return !(e && e[0] == '8');
+}
+
 int launch_attend_tiled(const AttnArgs& a_in, cudaStream_t st) {
-  const dim3 grid(a_in.B * a_in.Hkv, (a_in.G * a_in.q_len + 7) / 8, a_in.n_splits);
+  const int nq_all = a_in.G * a_in.q_len;
+  // up to four query rows: scores from bit planes on the integer tensor cores, when the caller had the rotation
+  // kernel build the operand images, else the fp16 form; five to eight rows: one group of eight columns; more:
+  // sixteen rows per CTA
+  const int mode = nq_all <= 4 ? (a_in.planes ? 2 : 1) : (sixteen_rows(nq_all) ? 3 : 0);
+  const int rows = mode == 3 ? 16 : 8;
+  const dim3 grid(a_in.B * a_in.Hkv, (nq_all + rows - 1) / rows, a_in.n_splits);
   // Programmatic dependent launch: the grid may start while the kernel before it in the stream (the query
   // rotation, which releases its dependents at once) is still running; the kernel waits for that kernel's
   // completion before it reads anything that kernel writes.
@@ -684,17 +765,16 @@ int launch_attend_tiled(const AttnArgs& a_in, cudaStream_t st) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  // up to four query rows: scores from bit planes on the integer tensor cores, when the caller had the
-  // rotation kernel build the operand images; else the fp16 form
-  const int mode = a_in.G * a_in.q_len <= 4 ? (a_in.planes ? 2 : 1) : 0;
   const AttnArgs& a = a_in;
   cudaError_t err;
   if (a.block_table)
-    err = mode == 2 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<true, 2>, a)
+    err = mode == 3 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<true, 3>, a)
+        : mode == 2 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<true, 2>, a)
         : mode == 1 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<true, 1>, a)
                     : cudaLaunchKernelEx(&cfg, attend_tiled_kernel<true, 0>, a);
   else
-    err = mode == 2 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, 2>, a)
+    err = mode == 3 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, 3>, a)
+        : mode == 2 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, 2>, a)
         : mode == 1 ? cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, 1>, a)
                     : cudaLaunchKernelEx(&cfg, attend_tiled_kernel<false, 0>, a);
   if (err != cudaSuccess) return QKV_ELAUNCH;
