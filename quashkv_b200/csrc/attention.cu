@@ -17,6 +17,7 @@
 #include <stdlib.h>
 
 #include "attention_common.cuh"
+#include "mma_decode.cuh"
 
 namespace qkv {
 
@@ -213,6 +214,94 @@ __global__ void __launch_bounds__(512) rotate_planes_kernel(const void* __restri
       }
     }
     img->bop[s][L] = make_uint4(ra[0], ra[1], rb[0], rb[1]);
+  }
+}
+
+// Query rotation for the tiled attention with fp16 scores (head_dim 128): CTA k rotates one group of eight
+// query rows of a (batch, kv head) (rows n0 .. n0 + 7 of the head's G * q_len rows; with `lo4` four rows, columns
+// 4..7 carrying the fp16 rounding residual of columns 0..3) and builds its GroupImage: the B operands in the
+// order the scan's MMAs consume them.  Key-code k-step s = 4 * word + f covers a lane's coordinates
+// 32 t + 16 word + {f, 4 + f | 8 + f, 12 + f}; sign k-step s covers 32 t + {2s, 2s + 16 | 2s + 1, 2s + 17}
+// through sign_coord / sign_pos (mma_decode.cuh).  One extra CTA prepares the look-up tables and the counters.
+__global__ void __launch_bounds__(128) rotate_groups_kernel(const void* __restrict__ q, int q_dtype,
+                                                            const float* __restrict__ Pi, const float* __restrict__ S,
+                                                            float qjl_scale, float scale,
+                                                            const float* __restrict__ kcent,
+                                                            const float* __restrict__ vcent,
+                                                            uint32_t* __restrict__ tables, int n_counters,
+                                                            int nq_all, int groups_per_seg, int lo4,
+                                                            GroupImage* __restrict__ groups) {
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  if (blockIdx.x == gridDim.x - 1) {
+    unsigned* arrivals = reinterpret_cast<unsigned*>(reinterpret_cast<unsigned char*>(tables) + kAttnHeaderBytes);
+    for (int i = threadIdx.x; i < n_counters; i += blockDim.x) arrivals[i] = 0u;
+    prepare_tables_cta(kcent, vcent, tables);
+    return;
+  }
+  constexpr int D = 128;
+  constexpr float kL2e = 1.4426950408889634f;
+  __shared__ __align__(16) float x_s[8][D];
+  __shared__ float q_s[8][D], w_s[8][D];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, tig = lane & 3;
+  const int seg = blockIdx.x / groups_per_seg, grp = blockIdx.x % groups_per_seg;
+  const int n0 = 8 * grp;
+  const int64_t row0 = static_cast<int64_t>(seg) * nq_all + n0;       // the head's rows are consecutive query rows
+  for (int idx = threadIdx.x; idx < 8 * D; idx += blockDim.x) {
+    const int r = idx >> 7, j = idx & 127;
+    const int rq = lo4 ? (r & 3) : r;
+    x_s[r][j] = (n0 + rq < nq_all) ? load_float(q, q_dtype, (row0 + rq) * D + j) : 0.f;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    float4 x[kRowsPerCta];
+#pragma unroll
+    for (int r = 0; r < kRowsPerCta; ++r) x[r] = *reinterpret_cast<const float4*>(&x_s[4 * half + r][4 * lane]);
+    for (int i0 = 8 * warp; i0 < D; i0 += 32) {
+      float v[32];
+      rotate_eight_rows(Pi, D, i0, lane, x, v);
+      const int io = i0 + (lane >> 2), ro = 4 * half + (lane & 3);
+      q_s[ro][io] = v[0] * scale;
+      w_s[ro][io] = (qjl_scale * scale) * (fabsf(v[0]) * S[io]);
+    }
+  }
+  __syncthreads();
+  const float inv_sk = 1.f / best_fp16_scale_cta(kcent, 4);      // the scale the table CTA gives the key table
+  GroupImage* img = groups + blockIdx.x;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {           // a warp sums the sign weights of two query columns
+    const int col = 2 * warp + h;
+    const float* w = w_s[col];
+    float t = (w[lane] + w[lane + 32]) + (w[lane + 64] + w[lane + 96]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(QKV_FULL_MASK, t, o);
+    if (lane == 0) img->wsum[col] = (lo4 && col >= 4) ? 0.f : t * kL2e;
+  }
+  {
+    const float qf = kL2e * inv_sk;
+    const float* qv = q_s[gid];
+    const float* w = w_s[gid];
+    const bool resid = lo4 && gid >= 4;
+#pragma unroll
+    for (int s = warp; s < 8; s += 4) {
+      const int word = s >> 2, f = s & 3;
+      const int c0 = 32 * tig + 16 * word + f;
+      float v[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        v[e] = qv[c0 + 4 * e] * qf;
+        if (resid) v[e] -= __half2float(__float2half_rn(v[e]));
+      }
+      reinterpret_cast<uint2*>(&img->bop[s >> 1][lane])[s & 1] = make_uint2(pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
+      uint32_t wq[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {           // pairs t = 2s, 2s+1 of this lane's 32 coordinates
+        const int t = 2 * s + h, j = 32 * tig + sign_coord(t);
+        const float fs = resid ? 0.f : 2.f * kL2e / sign_v1(sign_pos(t));
+        wq[h] = pack_half2(w[j] * fs, w[j + 16] * fs);
+      }
+      reinterpret_cast<uint2*>(&img->bop[4 + (s >> 1)][lane])[s & 1] = make_uint2(wq[0], wq[1]);
+    }
   }
 }
 
@@ -600,8 +689,16 @@ int attention_run(const void* q, int q_dtype, qkv_cache_t cache, const uint8_t* 
   // tile records with up to four query rows per KV head: scores from bit planes, operands built by the rotation
   const bool from_planes = tiled && tiled_scores_from_planes(Hq / Hkv, q_len);
   PlaneImage* planes = from_planes ? reinterpret_cast<PlaneImage*>(ws + p.img_off) : nullptr;
+  // ... otherwise fp16 scores from operand images per group of eight query rows, built by the rotation as well
+  GroupImage* groups = (tiled && !from_planes) ? reinterpret_cast<GroupImage*>(ws + p.img_off) : nullptr;
   int rc;
-  if (from_planes) {
+  if (groups) {
+    const int nq_all = (Hq / Hkv) * q_len, gps = (nq_all + 7) / 8;
+    rotate_groups_kernel<<<static_cast<unsigned>(B * Hkv * gps + 1), 128, 0, st>>>(
+        q, q_dtype, Pi, S, qjl_scale, scale, key_centroids, val_centroids, tables, B * Hkv * gps, nq_all, gps,
+        nq_all <= 4 ? 1 : 0, groups);
+    rc = check_launch();
+  } else if (from_planes) {
     rotate_planes_kernel<<<static_cast<unsigned>(B * Hkv + 1), 512, 0, st>>>(
         q, q_dtype, p.rows, Pi, S, qjl_scale, scale, qk, key_centroids, val_centroids, tables, B * Hkv,
         (Hq / Hkv) * q_len, planes);
@@ -629,6 +726,7 @@ int attention_run(const void* q, int q_dtype, qkv_cache_t cache, const uint8_t* 
     a.out = out;
     a.records = records;
     a.planes = planes;
+    a.groups = groups;
     return tiled ? launch_attend_tiled(a, st) : launch_attend_mma(a, st);
   } else {
     const dim3 grid(p.n_splits, p.n_qtiles, B * Hkv);

@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cuda_fp16.h>
+#include <stddef.h>
 #include <stdlib.h>
 
 #include "common.cuh"
@@ -20,6 +21,14 @@ struct PlaneImage {
   float cst[4];         // the score of a token whose bits are all clear, per query row
 };
 static_assert(sizeof(PlaneImage) % 16 == 0, "fetched with a bulk copy");
+
+// fp16 scores of the tiled path: the B operands of one group of eight query rows of a (batch, kv head), built once
+// by the query-rotation kernel (the CTAs of the scan fetch them with bulk copies instead of rebuilding them).
+struct GroupImage {
+  uint4 bop[8][32];     // per lane: two k-steps per entry, 8 key-code steps, then 8 sign steps
+  float wsum[8];        // log2e * sum of the sign weights per query column (0 for the residual columns)
+};
+static_assert(sizeof(GroupImage) % 16 == 0 && offsetof(GroupImage, wsum) % 16 == 0, "fetched with bulk copies");
 
 struct AttnArgs {
   qkv_cache_t cache;
@@ -44,6 +53,7 @@ struct AttnArgs {
   // (block, kv head).
   const uint8_t* records;
   const PlaneImage* planes; // tiled path, bit-plane scores: one image per (batch, kv head), else nullptr
+  const GroupImage* groups; // tiled path, fp16 scores: one image per (batch, kv head, group of eight query rows)
 };
 
 // Tensor-core path: the KV range is cut into splits of UNEQUAL length, in 128-token chunks, the longest first:
@@ -121,7 +131,11 @@ inline AttnPlan make_plan(int B, int Hq, int Hkv, int q_len, int64_t kv_len, int
   // arrival counters: one per (batch, kv head, tile of eight query rows) of the tensor-core path
   p.img_off = (kAttnHeaderBytes + static_cast<size_t>(B) * Hkv * ((nq + 7) / 8) * sizeof(unsigned) + 255) / 256 * 256;
   p.hdr_bytes = p.img_off;
-  if (d == 128 && nq <= 4) p.hdr_bytes = (p.img_off + static_cast<size_t>(B) * Hkv * sizeof(PlaneImage) + 255) / 256 * 256;
+  if (d == 128) {       // operand images of the tiled path: bit planes (up to four rows) or fp16 groups of eight rows
+    const size_t planes = nq <= 4 ? static_cast<size_t>(B) * Hkv * sizeof(PlaneImage) : 0;
+    const size_t groups = static_cast<size_t>(B) * Hkv * ((nq + 7) / 8) * sizeof(GroupImage);
+    p.hdr_bytes = (p.img_off + (planes > groups ? planes : groups) + 255) / 256 * 256;
+  }
   p.qk_bytes = static_cast<size_t>(p.rows) * 2 * d * sizeof(float);
   p.qk_bytes = (p.qk_bytes + 255) / 256 * 256;
   p.part_bytes = static_cast<size_t>(p.rows) * p.n_splits * (d + 2) * sizeof(float);
@@ -147,14 +161,14 @@ unsigned int bulk_copy_timeouts();        // bounded waits on a record copy that
 // value table, the positive half of a symmetric table) as fp16 pairs for the sign-and-magnitude records,
 // [10] contract flags (bit 0: the value table is not symmetric, bit 1: the key table is not affine in the two
 // bits of its code), [11..13] g0, g1, g2 of the key table written as c(u) = g0 + g1 (u & 1) + g2 (u >> 1).
-__device__ inline void prepare_tables_cta(const float* __restrict__ kcent, const float* __restrict__ vcent,
-                                          uint32_t* __restrict__ tables) {
-  __shared__ float cand_err[2][4];
-  __shared__ float cand_s[2][4];
-  const int tid = threadIdx.x;              // 128 threads search; a larger CTA's other threads only keep the barrier
-  for (int tb = 0; tb < 2 && tid < 128; ++tb) {
-    const float* cent = tb ? vcent : kcent;
-    const int n = tb ? 8 : 4;
+// The scale in [1, 2) of a table of n <= 8 values: a CTA-wide call (first 128 threads search four candidates each,
+// everyone passes the barriers), every thread gets the result.  Deterministic: smallest error, then smallest scale.
+__device__ inline float best_fp16_scale_cta(const float* __restrict__ cent, int n) {
+  __shared__ float cand_err[4];
+  __shared__ float cand_s[4];
+  __shared__ float chosen;
+  const int tid = threadIdx.x;
+  if (tid < 128) {
     float c[8];
     for (int i = 0; i < 8; ++i) c[i] = i < n ? cent[i] : 0.f;
     float best_err = 1e30f, best_s = 1.f;
@@ -168,23 +182,33 @@ __device__ inline void prepare_tables_cta(const float* __restrict__ kcent, const
       }
       if (err < best_err) { best_err = err; best_s = s; }
     }
-    // smallest error, then smallest scale: over the warp by exchange, over the four warps by thread 0
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float e2 = __shfl_xor_sync(0xffffffffu, best_err, o), s2 = __shfl_xor_sync(0xffffffffu, best_s, o);
       if (e2 < best_err || (e2 == best_err && s2 < best_s)) { best_err = e2; best_s = s2; }
     }
-    if ((tid & 31) == 0) { cand_err[tb][tid >> 5] = best_err; cand_s[tb][tid >> 5] = best_s; }
+    if ((tid & 31) == 0) { cand_err[tid >> 5] = best_err; cand_s[tid >> 5] = best_s; }
   }
   __syncthreads();
-  if (tid != 0) return;
-  float sc[2];
-  for (int tb = 0; tb < 2; ++tb) {
+  if (tid == 0) {
     float e = 1e30f, s = 1.f;
     for (int i = 0; i < 4; ++i)
-      if (cand_err[tb][i] < e || (cand_err[tb][i] == e && cand_s[tb][i] < s)) { e = cand_err[tb][i]; s = cand_s[tb][i]; }
-    sc[tb] = s;
+      if (cand_err[i] < e || (cand_err[i] == e && cand_s[i] < s)) { e = cand_err[i]; s = cand_s[i]; }
+    chosen = s;
   }
+  __syncthreads();
+  const float r = chosen;
+  __syncthreads();                          // the scratch may be reused by the next call
+  return r;
+}
+
+__device__ inline void prepare_tables_cta(const float* __restrict__ kcent, const float* __restrict__ vcent,
+                                          uint32_t* __restrict__ tables) {
+  const int tid = threadIdx.x;
+  float sc[2];
+  sc[0] = best_fp16_scale_cta(kcent, 4);
+  sc[1] = best_fp16_scale_cta(vcent, 8);
+  if (tid != 0) return;
   uint32_t t[6] = {0, 0, 0, 0, 0, 0};
   for (int i = 0; i < 4; ++i) {   // whole fp16 values: entries 0,1 in word 0, entries 2,3 in word 1
     const uint32_t h = __half_as_ushort(__float2half_rn(kcent[i] * sc[0]));

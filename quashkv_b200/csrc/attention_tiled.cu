@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(kWarps * 32, MODE == 3 ? 3 : 4) attend_tiled_k
   __shared__ __align__(128) unsigned char pool[kRingBytes > kRedBytes ? kRingBytes : kRedBytes];
   float (*red)[8][D + 2] = reinterpret_cast<float (*)[8][D + 2]>(pool);   // [warp][query][max, sum, acc]
   __shared__ __align__(8) uint64_t bars[kWarps][kRing];
-  __shared__ float wsum[kRows];                      // fp16 scores: sum of the sign weights per query column
+  __shared__ __align__(16) float wsum[kRows];        // fp16 scores: sum of the sign weights per query column
   // B operands per lane.  fp16 scores: two k-steps per entry, 8 key-code steps, then 8 sign steps.  Bit planes:
   // the image that the rotation kernel built for this (batch, kv head): one k-step per entry (both accumulator
   // chains), 8 steps on the code words, then 4 on the sign words, followed by the constants of the query rows.
@@ -102,10 +102,6 @@ __global__ void __launch_bounds__(kWarps * 32, MODE == 3 ? 3 : 4) attend_tiled_k
   uint4 (*bop)[32] = reinterpret_cast<uint4 (*)[32]>(opbuf);
   __shared__ __align__(8) uint64_t img_bar;
   __shared__ uint32_t vtab[64][32];                  // value table: entry (6-bit field) x lane, an fp16 pair each
-  // [query row][q_rot*scale | sign weights]: only read while the B operands are built, before the value table
-  // (same size) is written over it
-  float (*q_s)[2 * D] = reinterpret_cast<float (*)[2 * D]>(&vtab[0][0]);
-  static_assert(sizeof(vtab) == 8 * 2 * D * sizeof(float), "the queries are staged in the value table's storage");
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gid = lane >> 2, tig = lane & 3;
@@ -157,7 +153,7 @@ __global__ void __launch_bounds__(kWarps * 32, MODE == 3 ? 3 : 4) attend_tiled_k
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < kRing; ++s) umma::mbar_init(bar + s, 1);
-    if (PLANES && warp == 0) umma::mbar_init(&img_bar, 1);
+    if (warp == 0) umma::mbar_init(&img_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncwarp();
@@ -186,77 +182,40 @@ __global__ void __launch_bounds__(kWarps * 32, MODE == 3 ? 3 : 4) attend_tiled_k
   // look-up tables and the zeroed arrival counters are needed: wait for that kernel to have completed.
   asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
+  // Everything the scores need of the queries was built by the rotation kernel: the bit-plane image of this
+  // (batch, kv head), or the fp16 operand images of this CTA's groups of eight query rows.  One thread fetches
+  // them with bulk copies; they land while the value table is built.
+  const int groups_per_seg = (nq_all + 7) / 8;
   if (PLANES) {
-    // bit planes: everything the scores need of the queries is the image of this (batch, kv head)
     if (has_work && threadIdx.x == 0) {
       mbar_expect_tx(&img_bar, sizeof(PlaneImage));
       bulk_load(opbuf, a.planes + seg, sizeof(PlaneImage), &img_bar);
     }
-  }
-  const float inv_sk = __uint_as_float(a.tables[6]), inv_sv = __uint_as_float(a.tables[7]);
-  if (!PLANES) {
-#pragma unroll 1
-    for (int grp = 0; grp < NG; ++grp) {              // eight query rows at a time through the staging area
-      // In LO4 mode query column n >= 4 is the residual of column n - 4.
-      for (int idx = threadIdx.x; has_work && idx < 8 * 2 * D; idx += blockDim.x) {
-        const int r = idx / (2 * D), e = idx % (2 * D);
-        const int rq = 8 * grp + (LO4 ? (r & 3) : r);
-        float v = 0.f;
-        if (rq < nq) {
-          const int g = (r0 + rq) / a.q_len, qi = (r0 + rq) % a.q_len;
-          const int64_t qrow = (static_cast<int64_t>(b) * a.Hq + hkv * a.G + g) * a.q_len + qi;
-          v = a.qk[qrow * 2 * D + e];
-        }
-        q_s[r][e] = v;
-      }
-      __syncthreads();
-      if (has_work) {                   // a warp sums the sign weights of two query columns
+  } else if (has_work) {
+    int n_live = 0;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int col = 2 * warp + h;
-          const float* w = q_s[col] + D;
-          float t = (w[lane] + w[lane + 32]) + (w[lane + 64] + w[lane + 96]);
+    for (int grp = 0; grp < NG; ++grp) n_live += (NG * static_cast<int>(blockIdx.y) + grp < groups_per_seg) ? 1 : 0;
+    if (threadIdx.x == 0) {
+      mbar_expect_tx(&img_bar, n_live * static_cast<uint32_t>(sizeof(GroupImage)));
 #pragma unroll
-          for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(QKV_FULL_MASK, t, o);
-          if (lane == 0) wsum[8 * grp + col] = (LO4 && col >= 4) ? 0.f : t * kLog2e;
+      for (int grp = 0; grp < NG; ++grp) {
+        const int gi = NG * static_cast<int>(blockIdx.y) + grp;
+        if (gi < groups_per_seg) {
+          const GroupImage* src = a.groups + static_cast<int64_t>(seg) * groups_per_seg + gi;
+          bulk_load(opbuf + grp * sizeof(src->bop), src->bop, sizeof(src->bop), &img_bar);
+          bulk_load(wsum + 8 * grp, src->wsum, sizeof(src->wsum), &img_bar);
         }
       }
-
-      // ---- B operands for query column n = gid ---------------------------------------------------------
-      // Key-code k-step s = 4*word + f covers this lane's coordinates 32 tig + 16 word + {f, 4+f | 8+f, 12+f}
-      // (the order in which tile::key_fragment produces them).  Sign k-step s covers 32 tig + {2s, 2s+16 | 2s+1,
-      // 2s+17} through sign_coord / sign_pos.
-      if (has_work) {                   // the operands depend on the lane only: each warp builds two k-steps
-        const float qf = kLog2e * inv_sk;
-        const float* q = q_s[gid];
-        const float* w = q_s[gid] + D;
-        const bool resid = LO4 && gid >= 4;
-        uint4 (*bg)[32] = bop + 8 * grp;
+    }
 #pragma unroll
-        for (int s = warp; s < 8; s += kWarps) {
-          const int word = s >> 2, f = s & 3;
-          const int c0 = 32 * tig + 16 * word + f;
-          float v[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            v[e] = q[c0 + 4 * e] * qf;
-            if (resid) v[e] -= __half2float(__float2half_rn(v[e]));
-          }
-          reinterpret_cast<uint2*>(&bg[s >> 1][lane])[s & 1] = make_uint2(pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
-          uint32_t wq[2];
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {           // pairs t = 2s, 2s+1 of this lane's 32 coordinates
-            const int t = 2 * s + h, j = 32 * tig + sign_coord(t);
-            const float fs = resid ? 0.f : 2.f * kLog2e / sign_v1(sign_pos(t));
-            wq[h] = pack_half2(w[j] * fs, w[j + 16] * fs);
-          }
-          reinterpret_cast<uint2*>(&bg[4 + (s >> 1)][lane])[s & 1] = make_uint2(wq[0], wq[1]);
-        }
+    for (int grp = 0; grp < NG; ++grp) {               // a group past the head's last row: neutral operands
+      if (NG * static_cast<int>(blockIdx.y) + grp >= groups_per_seg) {
+        for (int i = threadIdx.x; i < 8 * 32; i += blockDim.x) bop[8 * grp + (i >> 5)][i & 31] = make_uint4(0u, 0u, 0u, 0u);
+        if (threadIdx.x < 8) wsum[8 * grp + threadIdx.x] = 0.f;
       }
-      __syncthreads();                  // the staging area is free for the next group (or for the value table)
     }
   }
-  __syncthreads();
+  const float inv_sv = __uint_as_float(a.tables[7]);
   const uint32_t kt_a = a.tables[0], kt_b = a.tables[1];     // fp16 key centroids 0,1 | 2,3
   if (has_work) {
     // value table: entry e holds the fp16 values of two stored codes (neg << 2 | mag), the first token's in the
@@ -305,10 +264,10 @@ __global__ void __launch_bounds__(kWarps * 32, MODE == 3 ? 3 : 4) attend_tiled_k
 #pragma unroll
   for (int grp = 0; grp < NG; ++grp) ci[grp][0] = ci[grp][1] = 0.f;
   bool img_failed = false;
+  // the image copies were issued before the value table was built: they have normally landed by now
+  if (has_work) img_failed = !__all_sync(QKV_FULL_MASK, umma::mbar_wait(&img_bar, 0));
   if (PLANES) {
     if (has_work) {
-      // the image copy was issued before the value table was built: it has normally landed by now
-      img_failed = !__all_sync(QKV_FULL_MASK, umma::mbar_wait(&img_bar, 0));
       const PlaneImage* img = reinterpret_cast<const PlaneImage*>(opbuf);
       const int hi = tig >> 1;
 #pragma unroll
