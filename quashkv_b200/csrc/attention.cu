@@ -52,6 +52,26 @@ __device__ __forceinline__ void rotate_eight_rows(const float* __restrict__ Pi, 
     }
   }
 }
+// Four rows of Pi already in registers (`m`, this lane's four columns of rows i0 .. i0 + 3) against eight vectors:
+// on return v[0] of lane L is <Pi[i0 + (L >> 3)], vector L & 7>.
+__device__ __forceinline__ void rotate_four_rows_eight(const float4 (&m)[4], const float4 (&x)[8], float (&v)[32]) {
+#pragma unroll
+  for (int o = 0; o < 4; ++o)
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+      v[8 * o + r] = fmaf(m[o].x, x[r].x, fmaf(m[o].y, x[r].y, fmaf(m[o].z, x[r].z, m[o].w * x[r].w)));
+#pragma unroll
+  for (int s = 16, n = 32; s >= 1; s >>= 1, n >>= 1) {
+    const bool upper = (threadIdx.x & s) != 0;
+#pragma unroll
+    for (int k = 0; k < n / 2; ++k) {
+      const float send = upper ? v[k] : v[k + n / 2];
+      const float keep = upper ? v[k + n / 2] : v[k];
+      v[k] = keep + __shfl_xor_sync(QKV_FULL_MASK, send, s);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(128) rotate_queries_kernel(const void* __restrict__ q, int q_dtype, int64_t rows,
                                                              int d, const float* __restrict__ Pi,
                                                              const float* __restrict__ S, float qjl_scale,
@@ -217,19 +237,21 @@ __global__ void __launch_bounds__(512) rotate_planes_kernel(const void* __restri
   }
 }
 
-// Query rotation for the tiled attention with fp16 scores (head_dim 128): CTA k rotates one group of eight
-// query rows of a (batch, kv head) (rows n0 .. n0 + 7 of the head's G * q_len rows; with `lo4` four rows, columns
-// 4..7 carrying the fp16 rounding residual of columns 0..3) and builds its GroupImage: the B operands in the
-// order the scan's MMAs consume them.  Key-code k-step s = 4 * word + f covers a lane's coordinates
-// 32 t + 16 word + {f, 4 + f | 8 + f, 12 + f}; sign k-step s covers 32 t + {2s, 2s + 16 | 2s + 1, 2s + 17}
-// through sign_coord / sign_pos (mma_decode.cuh).  One extra CTA prepares the look-up tables and the counters.
+// Query rotation for the tiled attention with fp16 scores (head_dim 128).  A CTA rotates kGroupsPerCta
+// consecutive groups of eight query rows of a (batch, kv head) (rows n0 .. n0 + 7 of the head's G * q_len rows;
+// with `lo4` four rows, columns 4..7 carrying the fp16 rounding residual of columns 0..3), every four rows of Pi
+// being loaded once for all of them, and builds their GroupImages: the B operands in the order the scan's MMAs
+// consume them.  Key-code k-step s = 4 * word + f covers a lane's coordinates 32 t + 16 word + {f, 4 + f | 8 + f,
+// 12 + f}; sign k-step s covers 32 t + {2s, 2s + 16 | 2s + 1, 2s + 17} through sign_coord / sign_pos
+// (mma_decode.cuh).  One extra CTA prepares the look-up tables and the counters.
+constexpr int kGroupsPerCta = 2;
 __global__ void __launch_bounds__(128) rotate_groups_kernel(const void* __restrict__ q, int q_dtype,
                                                             const float* __restrict__ Pi, const float* __restrict__ S,
                                                             float qjl_scale, float scale,
                                                             const float* __restrict__ kcent,
                                                             const float* __restrict__ vcent,
                                                             uint32_t* __restrict__ tables, int n_counters,
-                                                            int nq_all, int groups_per_seg, int lo4,
+                                                            int nq_all, int groups_per_seg, int n_groups, int lo4,
                                                             GroupImage* __restrict__ groups) {
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   if (blockIdx.x == gridDim.x - 1) {
@@ -238,49 +260,59 @@ __global__ void __launch_bounds__(128) rotate_groups_kernel(const void* __restri
     prepare_tables_cta(kcent, vcent, tables);
     return;
   }
-  constexpr int D = 128;
+  constexpr int D = 128, NGC = kGroupsPerCta;
   constexpr float kL2e = 1.4426950408889634f;
-  __shared__ __align__(16) float x_s[8][D];
-  __shared__ float q_s[8][D], w_s[8][D];
+  __shared__ __align__(16) float x_s[NGC][8][D];
+  __shared__ float q_s[NGC][8][D], w_s[NGC][8][D];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, tig = lane & 3;
-  const int seg = blockIdx.x / groups_per_seg, grp = blockIdx.x % groups_per_seg;
-  const int n0 = 8 * grp;
-  const int64_t row0 = static_cast<int64_t>(seg) * nq_all + n0;       // the head's rows are consecutive query rows
-  for (int idx = threadIdx.x; idx < 8 * D; idx += blockDim.x) {
-    const int r = idx >> 7, j = idx & 127;
-    const int rq = lo4 ? (r & 3) : r;
-    x_s[r][j] = (n0 + rq < nq_all) ? load_float(q, q_dtype, (row0 + rq) * D + j) : 0.f;
+  const int g_first = NGC * blockIdx.x;
+  for (int idx = threadIdx.x; idx < NGC * 8 * D; idx += blockDim.x) {
+    const int gl = idx / (8 * D), r = (idx >> 7) & 7, j = idx & 127;
+    const int g_idx = g_first + gl;
+    float v = 0.f;
+    if (g_idx < n_groups) {
+      const int seg = g_idx / groups_per_seg, n0 = 8 * (g_idx % groups_per_seg);
+      const int rq = lo4 ? (r & 3) : r;
+      if (n0 + rq < nq_all)                              // the head's rows are consecutive query rows
+        v = load_float(q, q_dtype, (static_cast<int64_t>(seg) * nq_all + n0 + rq) * D + j);
+    }
+    x_s[gl][r][j] = v;
   }
-  __syncthreads();
+  const float inv_sk = 1.f / best_fp16_scale_cta(kcent, 4);      // the scale the table CTA gives the key table (syncs)
+  const float qf = kL2e * inv_sk;
+  for (int i0 = 4 * warp; i0 < D; i0 += 16) {          // a warp takes four rows of Pi at a time
+    float4 m[4];
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    float4 x[kRowsPerCta];
+    for (int o = 0; o < 4; ++o) m[o] = __ldg(reinterpret_cast<const float4*>(Pi + static_cast<int64_t>(i0 + o) * D) + lane);
 #pragma unroll
-    for (int r = 0; r < kRowsPerCta; ++r) x[r] = *reinterpret_cast<const float4*>(&x_s[4 * half + r][4 * lane]);
-    for (int i0 = 8 * warp; i0 < D; i0 += 32) {
+    for (int gl = 0; gl < NGC; ++gl) {
+      float4 x[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) x[r] = *reinterpret_cast<const float4*>(&x_s[gl][r][4 * lane]);
       float v[32];
-      rotate_eight_rows(Pi, D, i0, lane, x, v);
-      const int io = i0 + (lane >> 2), ro = 4 * half + (lane & 3);
-      q_s[ro][io] = v[0] * scale;
-      w_s[ro][io] = (qjl_scale * scale) * (fabsf(v[0]) * S[io]);
+      rotate_four_rows_eight(m, x, v);
+      const int io = i0 + (lane >> 3), ro = lane & 7;
+      q_s[gl][ro][io] = v[0] * scale;
+      w_s[gl][ro][io] = (qjl_scale * scale) * (fabsf(v[0]) * S[io]);
     }
   }
   __syncthreads();
-  const float inv_sk = 1.f / best_fp16_scale_cta(kcent, 4);      // the scale the table CTA gives the key table
-  GroupImage* img = groups + blockIdx.x;
+#pragma unroll 1
+  for (int gl = 0; gl < NGC; ++gl) {
+    const int g_idx = g_first + gl;
+    if (g_idx >= n_groups) break;
+    GroupImage* img = groups + g_idx;
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {           // a warp sums the sign weights of two query columns
-    const int col = 2 * warp + h;
-    const float* w = w_s[col];
-    float t = (w[lane] + w[lane + 32]) + (w[lane + 64] + w[lane + 96]);
+    for (int h = 0; h < 2; ++h) {           // a warp sums the sign weights of two query columns
+      const int col = 2 * warp + h;
+      const float* w = w_s[gl][col];
+      float t = (w[lane] + w[lane + 32]) + (w[lane + 64] + w[lane + 96]);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(QKV_FULL_MASK, t, o);
-    if (lane == 0) img->wsum[col] = (lo4 && col >= 4) ? 0.f : t * kL2e;
-  }
-  {
-    const float qf = kL2e * inv_sk;
-    const float* qv = q_s[gid];
-    const float* w = w_s[gid];
+      for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(QKV_FULL_MASK, t, o);
+      if (lane == 0) img->wsum[col] = (lo4 && col >= 4) ? 0.f : t * kL2e;
+    }
+    const float* qv = q_s[gl][gid];
+    const float* w = w_s[gl][gid];
     const bool resid = lo4 && gid >= 4;
 #pragma unroll
     for (int s = warp; s < 8; s += 4) {
@@ -694,8 +726,9 @@ int attention_run(const void* q, int q_dtype, qkv_cache_t cache, const uint8_t* 
   int rc;
   if (groups) {
     const int nq_all = (Hq / Hkv) * q_len, gps = (nq_all + 7) / 8;
-    rotate_groups_kernel<<<static_cast<unsigned>(B * Hkv * gps + 1), 128, 0, st>>>(
-        q, q_dtype, Pi, S, qjl_scale, scale, key_centroids, val_centroids, tables, B * Hkv * gps, nq_all, gps,
+    const int n_groups = B * Hkv * gps;
+    rotate_groups_kernel<<<static_cast<unsigned>((n_groups + kGroupsPerCta - 1) / kGroupsPerCta + 1), 128, 0, st>>>(
+        q, q_dtype, Pi, S, qjl_scale, scale, key_centroids, val_centroids, tables, n_groups, nq_all, gps, n_groups,
         nq_all <= 4 ? 1 : 0, groups);
     rc = check_launch();
   } else if (from_planes) {
