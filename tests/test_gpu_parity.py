@@ -536,6 +536,11 @@ def test_tensor_core_decode_path_vs_generic_and_oracle(G, q_len, causal, monkeyp
     monkeypatch.setenv("QUASHKV_B200_SCORES", "fp16")
     fast16 = eng.attention(Q.to(DEV), causal=causal)
     monkeypatch.delenv("QUASHKV_B200_SCORES")
+    if G * q_len > 8:            # sixteen query rows per CTA against eight: the same arithmetic per row
+        monkeypatch.setenv("QUASHKV_B200_PREFILL_ROWS", "8")
+        rows8 = eng.attention(Q.to(DEV), causal=causal)
+        monkeypatch.delenv("QUASHKV_B200_PREFILL_ROWS")
+        assert torch.equal(fast, rows8)
     monkeypatch.setenv("QUASHKV_B200_ROW_STORAGE", "1")
     rows = qk.QuashKVEngine(D, 3, 3, seed=42, pack_storage=True)
     monkeypatch.delenv("QUASHKV_B200_ROW_STORAGE")
