@@ -133,6 +133,10 @@ __global__ void __launch_bounds__(512) rotate_planes_kernel(const void* __restri
                                                             const float* __restrict__ vcent,
                                                             uint32_t* __restrict__ tables, int n_counters,
                                                             int rows_per_cta, PlaneImage* __restrict__ planes) {
+  // Launched as a programmatic dependent itself: when the kernel before it in the stream releases its dependents
+  // early (the scan of the previous decode step does), this grid is already resident when that kernel ends.
+  // Nothing is read or written before the wait.
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   if (blockIdx.x == gridDim.x - 1) {
     unsigned* arrivals = reinterpret_cast<unsigned*>(reinterpret_cast<unsigned char*>(tables) + kAttnHeaderBytes);
@@ -732,9 +736,18 @@ int attention_run(const void* q, int q_dtype, qkv_cache_t cache, const uint8_t* 
         nq_all <= 4 ? 1 : 0, groups);
     rc = check_launch();
   } else if (from_planes) {
-    rotate_planes_kernel<<<static_cast<unsigned>(B * Hkv + 1), 512, 0, st>>>(
-        q, q_dtype, p.rows, Pi, S, qjl_scale, scale, qk, key_centroids, val_centroids, tables, B * Hkv,
-        (Hq / Hkv) * q_len, planes);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(B * Hkv + 1));
+    cfg.blockDim = dim3(512);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, rotate_planes_kernel, q, q_dtype, p.rows, Pi, S, qjl_scale, scale, qk, key_centroids,
+                           val_centroids, tables, B * Hkv, (Hq / Hkv) * q_len, planes) != cudaSuccess)
+      return QKV_ELAUNCH;
     rc = check_launch();
   } else {
     rc = launch_rotate(q, q_dtype, p.rows, d, Pi, S, qjl_scale, scale, qk, key_centroids, val_centroids,

@@ -103,6 +103,9 @@ __global__ void __launch_bounds__(kWarps * 32, MODE == 3 ? 3 : 4) attend_tiled_k
   __shared__ __align__(8) uint64_t img_bar;
   __shared__ uint32_t vtab[64][32];                  // value table: entry (6-bit field) x lane, an fp16 pair each
 
+  // A kernel launched behind this one as a programmatic dependent (the rotation of the next decode step) may take
+  // free CTA slots from now on; it reads and writes nothing before this grid has completed.
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gid = lane >> 2, tig = lane & 3;
   // Splits are the slowest grid dimension: longest first.  (The splits of a head in consecutive CTAs, so that the
