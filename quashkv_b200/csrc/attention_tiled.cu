@@ -1,22 +1,23 @@
 // Decode / prefill attention over a cache of tile records (tile_format.cuh): head_dim 128, 3-bit keys
-// (2-bit codes + sign bit), 3-bit values, eight query rows of a KV head per CTA.
+// (2-bit codes + sign bit), 3-bit values, eight (prefill: sixteen) query rows of a KV head per CTA.
 // Semantics: QuashKVEngine.attention (reference engine.py:204-299).
 //
 // A warp owns 16-token tiles of its split.  One elected lane fetches a whole record (1664 bytes) with
 // ONE bulk copy into the warp's ring of four stages; an mbarrier per stage counts the bytes in, every
-// wait on it is bounded.  Each lane then reads its share with five vector loads, decodes it into m16n8k16
-// fragments (tile_decode.cuh: key codes with one PRMT per pair of codes, sign bits with one LOP3 per pair,
-// both in registers; values with one look-up per pair of tokens in a 64-entry table of ready fp16 pairs in
-// shared memory, laid out so that every lane reads its own bank) and feeds mma.sync:
-//   scores   tokens = M, queries = N, coordinates = K: 8 MMAs on the key codes, 8 on the sign bits
-//   values   coordinates = M, tokens = K, queries = N: 8 MMAs, accumulated in the ROTATED domain
+// wait on it is bounded.  Each lane then reads its share with five vector loads and feeds mma.sync:
+//   scores   tokens = M, queries = N, coordinates = K
+//   values   coordinates = M, tokens = K, queries = N, accumulated in the ROTATED domain; a value operand
+//            register is one look-up per pair of tokens in a 64-entry table of ready fp16 pairs in shared memory,
+//            laid out so that every lane reads its own bank: 8 MMAs per group of eight query columns
 // with an online softmax in between (log2 domain, lazily raised reference exponent).  Per split the
 // CTA writes (max, sum, accumulator); the last CTA of a (batch, kv head) to finish merges the splits
 // and applies Pi once, which equals un-rotating every value (engine.py:284-287) because the rotation
-// is linear.
+// is linear.  With a single split the rows go straight through the un-rotation.
+// Everything the scores need of the queries (B operands, constants) is built once per (batch, kv head) by the
+// query-rotation kernel (attention.cu) and fetched with bulk copies.
 //
-// With at most four query rows per KV head (decode with up to four query heads per KV head) the scores
-// are computed on the INTEGER tensor cores from bit planes (MODE 2).  A 4-level key table that is affine in
+// Scores, up to four query rows per KV head (decode with up to four query heads per KV head): on the INTEGER
+// tensor cores from bit planes (MODE 2).  A 4-level key table that is affine in
 // the two bits of its code, c(u) = g0 + g1 b0 + g2 b1 (true of every table with c0 + c3 = c1 + c2, so of
 // every symmetric one), turns the score into a constant plus a weighted sum over single bits: of the two code
 // bits and of the sign bit of every coordinate.  `word & (0x01010101 << p)` IS an unsigned 8-bit A operand
@@ -24,9 +25,14 @@
 // logic instruction and no shift, against three instructions per TWO elements of the fp16 path; the query
 // side carries weight / 2^p as four signed 8-bit terms (radix 128, a common scale per query), two per
 // accumulator chain in the column pairs (n, n + 4), which is exact integer arithmetic to 2^-21 of the largest
-// weight.  The accumulators start at the bit pattern of 1.5 * 2^23, so the integer sums read back as floats
-// with one subtraction.  (The fp16 form of the same idea, MODE 1, puts the fp16 rounding residual of the
-// queries into columns 4..7; it is kept for comparison, QUASHKV_B200_SCORES=fp16.)
+// weight: 24 MMAs per tile.  The accumulators start at the bit pattern of 1.5 * 2^23, so the integer sums read
+// back as floats with one subtraction.  (The fp16 form of the same idea, MODE 1, puts the fp16 rounding residual
+// of the queries into columns 4..7; it is kept for comparison, QUASHKV_B200_SCORES=fp16.)
+//
+// Scores, more rows (MODE 0: five to eight; MODE 3: sixteen as two groups of eight columns, for prefill): fp16
+// m16n8k16, key codes decoded in registers with one PRMT per pair of codes, sign bits with one LOP3 per pair
+// (tile_decode.cuh, mma_decode.cuh): 8 MMAs on the key codes and 8 on the sign bits per group; in MODE 3 every
+// decoded key and value fragment feeds both groups.
 #include <math.h>
 #include <stdlib.h>
 
