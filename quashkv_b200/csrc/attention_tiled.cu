@@ -154,11 +154,17 @@ __global__ void __launch_bounds__(kWarps * 32, MODE == 3 ? 3 : 4) attend_tiled_k
   const uint8_t* rec0 = PAGED ? a.records
                               : a.records + (static_cast<int64_t>(seg) * (a.cache.capacity >> 4) + tile_first) * tile::kBytes;
   const int32_t* bt = PAGED ? a.block_table + static_cast<int64_t>(b) * a.max_blocks : nullptr;
-  auto block_of = [&](int it) -> int {
-    const unsigned tl = static_cast<unsigned>(tile_first) + static_cast<unsigned>(it) * kWarps;
-    return it < n_it ? __ldg(bt + tl / static_cast<unsigned>(tiles_per_block)) : 0;
-  };
-  int blk_next = PAGED ? block_of(0) : 0;             // block of the tile the next issue() fetches
+  // Paged: position of the tile the next issue() fetches, as (entry of the block table, tile inside the block),
+  // advanced by kWarps tiles per issue without a division in the loop; the block id is read one issue ahead.
+  int pg_entry = 0, pg_off = 0, pg_step_q = 0, pg_step_r = 0, blk_next = 0;
+  if (PAGED) {
+    const unsigned tpb = static_cast<unsigned>(tiles_per_block);
+    pg_entry = static_cast<int>(static_cast<unsigned>(tile_first) / tpb);
+    pg_off = static_cast<int>(static_cast<unsigned>(tile_first) % tpb);
+    pg_step_q = static_cast<int>(kWarps / tpb);
+    pg_step_r = static_cast<int>(kWarps % tpb);
+    blk_next = n_it > 0 ? __ldg(bt + pg_entry) : 0;
+  }
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < kRing; ++s) umma::mbar_init(bar + s, 1);
@@ -170,9 +176,7 @@ __global__ void __launch_bounds__(kWarps * 32, MODE == 3 ? 3 : 4) attend_tiled_k
     if (it < n_it && lane == 0) {
       const uint8_t* src;
       if (PAGED) {
-        const unsigned tl = static_cast<unsigned>(tile_first) + static_cast<unsigned>(it) * kWarps;
-        src = rec0 + ((static_cast<int64_t>(blk_next) * a.Hkv + hkv) * tiles_per_block +
-                      tl % static_cast<unsigned>(tiles_per_block)) * tile::kBytes;
+        src = rec0 + ((static_cast<int64_t>(blk_next) * a.Hkv + hkv) * tiles_per_block + pg_off) * tile::kBytes;
       } else {
         src = rec0 + static_cast<int64_t>(it) * (kWarps * tile::kBytes);
       }
@@ -180,7 +184,12 @@ __global__ void __launch_bounds__(kWarps * 32, MODE == 3 ? 3 : 4) attend_tiled_k
       mbar_expect_tx(bs, tile::kBytes);
       bulk_load(ring + slot * tile::kBytes, src, tile::kBytes, bs);
     }
-    if (PAGED) blk_next = block_of(it + 1);
+    if (PAGED) {                                      // on to tile it + 1 of this warp
+      pg_entry += pg_step_q;
+      pg_off += pg_step_r;
+      if (pg_off >= tiles_per_block) { pg_off -= tiles_per_block; ++pg_entry; }
+      blk_next = it + 1 < n_it ? __ldg(bt + pg_entry) : 0;
+    }
   };
 #pragma unroll
   for (int i = 0; i < kRing; ++i) issue(i, i);
