@@ -245,7 +245,35 @@ class QuashKVPagedCache:
             blk = np.asarray(self._blocks[s], dtype=np.int64)[pos // bs]
             slots[i] = (blk[None, :] * H + np.arange(H)[:, None]) * bs + (pos % bs)[None, :]
             self._lens[s] = self._lens.get(s, 0) + T
-        slots_d = torch.from_numpy(slots.reshape(-1)).to(self.device)
+        self._store(keys, values, torch.from_numpy(slots.reshape(-1)).to(self.device))
+
+    def append_with_tables(self, keys: torch.Tensor, values: torch.Tensor, block_table: torch.Tensor,
+                           start_lens: torch.Tensor) -> None:
+        """The same store for a caller that owns the page allocation (a serving engine): ``block_table`` (n_seq,
+        max_blocks) int32 and ``start_lens`` (n_seq) int32 live on the device, the new tokens of sequence i go to
+        positions start_lens[i] .. start_lens[i] + new_tokens - 1 of its pages.  The slots are computed on the
+        device: no host loop and no host-to-device copy per decode step.  The pool's own bookkeeping
+        (``seq_len``, ``free``) is not involved."""
+        ops._need_cuda(keys, "QuashKVPagedCache.append_with_tables")
+        n, H, T, D = keys.shape
+        if H != self.num_kv_heads or D != self.head_size or values.shape != keys.shape or \
+                block_table.shape[0] != n or start_lens.numel() != n:
+            raise ValueError(f"Expected keys and values of shape (n_seq, {self.num_kv_heads}, T, {self.head_size}) with "
+                             "a block table and start lengths for n_seq sequences")
+        if T == 0:
+            return
+        bs = self.block_size
+        dev = keys.device
+        pos = start_lens.to(torch.int64).reshape(n, 1) + torch.arange(T, device=dev, dtype=torch.int64).reshape(1, T)
+        blk = torch.gather(block_table.to(torch.int64), 1, torch.div(pos, bs, rounding_mode="floor"))       # (n, T)
+        heads = torch.arange(H, device=dev, dtype=torch.int64).reshape(1, H, 1)
+        slots = (blk.reshape(n, 1, T) * H + heads) * bs + (pos % bs).reshape(n, 1, T)
+        self._store(keys, values, slots.reshape(-1).contiguous())
+
+    def _store(self, keys: torch.Tensor, values: torch.Tensor, slots_d: torch.Tensor) -> None:
+        """Compress (n_seq, heads, T, d) keys and values and file every token at its slot
+        ((block * heads + head) * block_size + offset)."""
+        n, H, T, D = keys.shape
         kq, vq = self.engine.key_quantizer, self.engine.value_quantizer
         Pi, k_bounds, k_cents, Sgn = kq._on(keys.device)
         _, v_bounds, _ = vq._on(keys.device)

@@ -1115,6 +1115,33 @@ def test_paged_decode_steps_and_pool_exhaustion():
     assert pool.seq_len("a") == 49 and pool.free_blocks == 2
 
 
+@pytest.mark.parametrize("D,bs", [(128, 16), (128, 32), (64, 16)])
+def test_paged_append_with_device_tables_matches_host_bookkeeping(D, bs):
+    """A serving engine that owns the page allocation hands over its device block table and start lengths:
+    the slots are computed on the device and the pool ends up byte-identical to the one filled through the
+    pool's own (host) bookkeeping; attention over the caller's tables gives the same output."""
+    from quashkv_b200.integrations.vllm_backend import QuashKVPageConfig, QuashKVPagedCache
+    Hkv, n = 2, 3
+    cfg = QuashKVPageConfig(block_size=bs)
+    host = QuashKVPagedCache(24, Hkv, D, cfg, device=DEV)
+    dev = QuashKVPagedCache(24, Hkv, D, cfg, device=DEV)
+    g = torch.Generator().manual_seed(11)
+    K = torch.randn(n, Hkv, 50, D, generator=g).to(DEV)
+    V = torch.randn(n, Hkv, 50, D, generator=g).to(DEV)
+    ids = ["a", "b", "c"]
+    steps = [(0, 21), (21, 22), (22, 23), (23, 50)]                     # a prefill, two decode steps, a longer block
+    for lo, hi in steps:
+        host.append(ids, K[:, :, lo:hi], V[:, :, lo:hi])
+        table, _, _ = host.block_table(ids)                            # the allocation a serving engine would hold
+        start = torch.full((n,), lo, dtype=torch.int32, device=DEV)
+        dev.append_with_tables(K[:, :, lo:hi], V[:, :, lo:hi], table, start)
+    for name in host.planes:
+        assert torch.equal(host.planes[name], dev.planes[name]), name
+    table, lens, mx = host.block_table(ids)
+    Q = torch.randn(n, Hkv * 4, 1, D, generator=g).to(DEV)
+    assert torch.equal(host.attention(ids, Q), dev.attention_with_tables(Q, table, lens, mx))
+
+
 def test_index_save_load_and_incremental_add(tmp_path):
     """An index written to a file and read back searches identically, keeps growing, and a build by many small
     adds equals a build by one add (rows are compressed in place at their offsets)."""
