@@ -263,6 +263,8 @@ class QuashKVEngine:
         dev = self._device() if self._planes is not None else None
         if dev is None:
             raise ValueError("No compressed KV blocks in cache. Call append() first.")
+        if self._tiled and os.environ.get("QUASHKV_B200_HOST_IO") != "torch":
+            return self._attention_from_host_lean(queries_host, out_host, dev, scale, causal)
         io = getattr(self, "_host_io", None)
         if io is None or io["device"] != dev:
             io = self._host_io = {"device": dev, "h2d": torch.cuda.Stream(dev), "d2h": torch.cuda.Stream(dev),
@@ -286,6 +288,66 @@ class QuashKVEngine:
             out_host.copy_(out, non_blocking=True)
             out.record_stream(io["d2h"])                    # the allocator must not reuse it before the copy ran
             return io["d2h"].record_event()
+
+    def _attention_from_host_lean(self, queries_host, out_host, dev, scale, causal) -> torch.cuda.Event:
+        """The same three-stream pipeline for a tiled cache with the host work cut down: device buffers for the
+        queries and the outputs are kept per slot, the copies and the ordering between the streams go through the
+        CUDA runtime directly (raw stream and event handles), and the attention call writes into the slot's
+        output buffer.  A decode step over one KV head of a sharded cache lasts about 55 us on the device; the
+        generic path spends more than that on the host."""
+        rt = ops.cudart()
+        io = getattr(self, "_host_io_lean", None)
+        if io is None or io["device"] != dev:
+            with torch.cuda.device(dev):
+                io = self._host_io_lean = {
+                    "device": dev, "h2d": torch.cuda.Stream(dev), "d2h": torch.cuda.Stream(dev), "n": 0,
+                    "slots": [{"q": None, "out": None, "arrived": torch.cuda.Event(), "computed": torch.cuda.Event(),
+                               "copied": torch.cuda.Event()} for _ in range(2)]}
+                for sl in io["slots"]:                    # an event has a handle once it has been recorded
+                    for name in ("arrived", "computed", "copied"):
+                        sl[name].record(io["h2d"])
+        slot = io["slots"][io["n"] % 2]
+        io["n"] += 1
+        if slot["q"] is None or slot["q"].shape != queries_host.shape or slot["q"].dtype != queries_host.dtype:
+            torch.cuda.synchronize(dev)                   # (re)allocation: nothing may still use the old buffers
+            slot["q"] = torch.empty(queries_host.shape, dtype=queries_host.dtype, device=dev)
+            slot["out"] = torch.empty(queries_host.shape, dtype=torch.float32, device=dev)
+        compute = torch.cuda.current_stream(dev).cuda_stream
+        h2d, d2h = io["h2d"].cuda_stream, io["d2h"].cuda_stream
+        arrived, computed, copied = (slot[k].cuda_event for k in ("arrived", "computed", "copied"))
+        kq, vq = self.key_quantizer, self.value_quantizer
+        Pi, _, k_cents, Sgn = kq._on(dev)
+        _, _, v_cents = vq._on(dev)
+        call = self._tiled_call
+        if call is None or call.device != dev or call.consts[0].data_ptr() != Pi.data_ptr():
+            call = self._tiled_call = ops.TiledAttentionCall(Pi, k_cents, v_cents, Sgn, kq.qjl_scale)
+        if scale is None:
+            scale = 1.0 / math.sqrt(self.head_dim)
+        B, Hq = queries_host.shape[0], queries_host.shape[1]
+        Hkv = self._shape[1]
+        if B != self._shape[0] or Hq % Hkv != 0 or queries_host.shape[-1] != self.head_dim:
+            raise ValueError(f"queries {tuple(queries_host.shape)} do not match a cache of {self._shape[0]} x {Hkv} heads")
+        ok = 0
+        # the slot's query buffer is free once the kernels of two calls ago have read it (computed), its output
+        # buffer once that call's copy back has read it (copied)
+        ok |= rt.cudaStreamWaitEvent(h2d, computed, 0)
+        ok |= rt.cudaMemcpyAsync(slot["q"].data_ptr(), queries_host.data_ptr(),
+                                 queries_host.numel() * queries_host.element_size(), 1, h2d)
+        ok |= rt.cudaEventRecord(arrived, h2d)
+        ok |= rt.cudaStreamWaitEvent(compute, arrived, 0)
+        ok |= rt.cudaStreamWaitEvent(compute, copied, 0)
+        with torch.cuda.device(dev):
+            call(slot["q"], self._planes["records"], self._capacity, self._total_tokens, Hkv, float(scale),
+                 bool(causal), out=slot["out"], stream=compute)
+        ok |= rt.cudaEventRecord(computed, compute)
+        ok |= rt.cudaStreamWaitEvent(d2h, computed, 0)
+        ok |= rt.cudaMemcpyAsync(out_host.data_ptr(), slot["out"].data_ptr(), out_host.numel() * 4, 2, d2h)
+        ok |= rt.cudaEventRecord(copied, d2h)
+        if ok != 0:
+            raise RuntimeError("quashkv_b200: a CUDA runtime call of the host-buffer path failed")
+        done = torch.cuda.Event()
+        done.record(io["d2h"])
+        return done
 
     # ---- decompression of the whole cache (used by the HF-style cache) ----------------------------
     def decompress_all(self, with_signs: bool = False, out_dtype=torch.float32):

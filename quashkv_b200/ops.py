@@ -505,6 +505,26 @@ def _attention_tiled(q: torch.Tensor, records: torch.Tensor, capacity: int, kv_l
     return out
 
 
+_CUDART = None
+
+
+def cudart():
+    """The CUDA runtime that torch has loaded, through ctypes: raw asynchronous copies and event calls for the
+    host-buffer path, where the stream context managers of torch cost more than the device work of a short
+    decode step."""
+    global _CUDART
+    if _CUDART is None:
+        rt = C.CDLL("libcudart.so.12")
+        rt.cudaMemcpyAsync.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]
+        rt.cudaMemcpyAsync.restype = C.c_int
+        rt.cudaEventRecord.argtypes = [C.c_void_p, C.c_void_p]
+        rt.cudaEventRecord.restype = C.c_int
+        rt.cudaStreamWaitEvent.argtypes = [C.c_void_p, C.c_void_p, C.c_uint]
+        rt.cudaStreamWaitEvent.restype = C.c_int
+        _CUDART = rt
+    return _CUDART
+
+
 class TiledAttentionCall:
     """The same C call as the ``attention_tiled`` op, prepared once for an engine's decode loop: constants are
     converted and kept, the workspace is kept between calls and grows when a longer cache needs more, and the
@@ -523,21 +543,27 @@ class TiledAttentionCall:
         self.fn = self.lib.qkv_attention_tiled
 
     def __call__(self, q: torch.Tensor, records: torch.Tensor, capacity: int, kv_len: int, n_kv_heads: int,
-                 scale: float, causal: bool) -> torch.Tensor:
+                 scale: float, causal: bool, out: Optional[torch.Tensor] = None,
+                 stream: Optional[int] = None) -> torch.Tensor:
+        """``out`` (fp32, contiguous, shape of q) is written when given; ``stream`` is a raw stream handle
+        (default: the current stream of q's device)."""
         B, Hq, Q, d = q.shape
         if q.dtype not in _DT:
             q = q.float()
         qc = q if q.is_contiguous() else q.contiguous()
         if qc.device != self.device or records.device != self.device:
             raise ValueError(f"quashkv_b200: queries on {qc.device}, records on {records.device}, constants on {self.device}")
-        out = torch.empty((B, Hq, Q, d), dtype=torch.float32, device=q.device)
+        if out is None:
+            out = torch.empty((B, Hq, Q, d), dtype=torch.float32, device=q.device)
+        elif out.dtype != torch.float32 or out.shape != q.shape or not out.is_contiguous() or out.device != self.device:
+            raise ValueError("quashkv_b200: out must be a contiguous fp32 tensor of the queries' shape on their device")
         need = self.lib.qkv_attention_workspace_bytes(B, Hq, n_kv_heads, Q, kv_len, d)
         if self.ws is None or self.ws.numel() < need:
             self.ws = torch.empty((max(need + need // 4, 1 << 16),), dtype=torch.uint8, device=q.device)
         cache = TiledCache(records.data_ptr(), capacity, None, None, 0, 0)
         rc = self.fn(qc.data_ptr(), _DT[qc.dtype], cache, B, Hq, n_kv_heads, Q, kv_len, d, 3, 3, *self.ptrs,
                      self.qjl_scale, scale, int(causal), out.data_ptr(), self.ws.data_ptr(), self.ws.numel(),
-                     torch.cuda.current_stream(q.device).cuda_stream)
+                     torch.cuda.current_stream(q.device).cuda_stream if stream is None else stream)
         if rc:
             _lib.check(rc, "attention_tiled")
         return out

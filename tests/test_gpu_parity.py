@@ -1173,10 +1173,14 @@ def test_index_save_load_and_incremental_add(tmp_path):
     assert len(qk.QuashIndex.load(tmp_path / "empty.pt", device=DEV)) == 0
 
 
-def test_attention_from_host_overlapped_calls_match_device_calls():
+@pytest.mark.parametrize("io,D", [("lean", 128), ("torch", 128), ("lean", 64)])
+def test_attention_from_host_overlapped_calls_match_device_calls(io, D, monkeypatch):
     """Back-to-back host-to-host calls (copies on side streams, device buffers in rotation) return what the
-    device-resident call returns for each query."""
-    B, Hkv, G, S, D = 2, 2, 4, 3000, 128
+    device-resident call returns for each query: through the lean path of a tiled cache (raw runtime calls, kept
+    buffers), through the generic path, and for an engine on row-major planes (head_dim 64)."""
+    if io == "torch":
+        monkeypatch.setenv("QUASHKV_B200_HOST_IO", "torch")
+    B, Hkv, G, S = 2, 2, 4, 3000
     g = torch.Generator().manual_seed(17)
     eng = qk.QuashKVEngine(D, 3, 3, seed=42, pack_storage=True)
     eng.append(torch.randn(B, Hkv, S, D, generator=g).to(DEV), torch.randn(B, Hkv, S, D, generator=g).to(DEV))
