@@ -67,6 +67,8 @@ class QuashKVEngine:
         self._block_lens: list[int] = []
         self._block_cache = None
         self._tiled_call = None      # prepared attention call of the decode loop (ops.TiledAttentionCall)
+        self._row_call = None        # ... over row-major planes (ops.RowAttentionCall)
+        self._append_call = None     # prepared compression of new tokens (ops.AppendCall)
 
     # ---- compression ------------------------------------------------------------------------
     def compress_keys(self, keys: torch.Tensor):
@@ -121,6 +123,18 @@ class QuashKVEngine:
         _, v_bounds, _ = vq._on(keys.device)
         b, H, S, _ = keys.shape
         p = self._planes
+        if seg0 == 0 and (b, H) == self._shape:
+            # the usual append over all segments: the prepared call (no op dispatcher, kept staging planes)
+            call = self._append_call
+            if call is None or call.device != keys.device or call.consts[0].data_ptr() != Pi.data_ptr():
+                call = self._append_call = ops.AppendCall(Pi, k_bounds, k_cents, Sgn, kq.mse_bits, v_bounds,
+                                                          self.value_bits)
+            with torch.cuda.device(keys.device):
+                if self._tiled:
+                    call.into_records(keys, values, p["records"], self._row_bytes(), self._capacity, offset)
+                else:
+                    call.into_planes(keys, values, p, offset)
+            return
         if not self._tiled:
             sl = slice(seg0, seg0 + b * H)
             ops.append_kv(keys, values, Pi, k_bounds, k_cents, Sgn, kq.mse_bits, v_bounds, self.value_bits,
@@ -244,9 +258,12 @@ class QuashKVEngine:
             with torch.cuda.device(queries.device):
                 return call(queries.detach(), p["records"], self._capacity, self._total_tokens, Hkv, float(scale),
                             bool(causal))
-        return ops.attention(queries, p["k_codes"], p["k_signs"], p["k_norms"], p["v_codes"], p["v_norms"],
-                             self._total_tokens, Hkv, self.key_bits, self.value_bits, Pi, k_cents, v_cents,
-                             Sgn, kq.qjl_scale, float(scale), bool(causal))
+        call = self._row_call
+        if call is None or call.device != queries.device or call.consts[0].data_ptr() != Pi.data_ptr():
+            call = self._row_call = ops.RowAttentionCall(Pi, k_cents, v_cents, Sgn, kq.qjl_scale, self.key_bits,
+                                                         self.value_bits)
+        with torch.cuda.device(queries.device):
+            return call(queries.detach(), p, self._total_tokens, Hkv, float(scale), bool(causal))
 
     def attention_from_host(self, queries_host: torch.Tensor, out_host: torch.Tensor,
                             scale: Optional[float] = None, causal: bool = False) -> torch.cuda.Event:

@@ -505,6 +505,108 @@ def _attention_tiled(q: torch.Tensor, records: torch.Tensor, capacity: int, kv_l
     return out
 
 
+class RowAttentionCall:
+    """The C call of the ``attention`` op (row-major packed planes), prepared once for an engine's decode loop:
+    constants converted once, the workspace kept and grown when needed, no op dispatcher.  A decode step over a
+    short cache is a few tens of microseconds of device work; the generic op spends more than that on the
+    host.  One instance serves one stream at a time (the workspace is shared by its calls)."""
+
+    def __init__(self, Pi, key_centroids, val_centroids, S, qjl_scale: float, key_bits: int, val_bits: int):
+        self.consts = tuple(_f32(t) for t in (Pi, key_centroids, val_centroids, S))
+        self.ptrs = tuple(_p(t) for t in self.consts)
+        self.qjl_scale, self.key_bits, self.val_bits = float(qjl_scale), int(key_bits), int(val_bits)
+        self.device = self.consts[0].device
+        self.ws = None
+        self.lib = _lib.lib()
+        self.fn = self.lib.qkv_attention
+
+    def __call__(self, q: torch.Tensor, planes: dict, kv_len: int, n_kv_heads: int, scale: float,
+                 causal: bool) -> torch.Tensor:
+        B, Hq, Q, d = q.shape
+        if q.dtype not in _DT:
+            q = q.float()
+        qc = q if q.is_contiguous() else q.contiguous()
+        kn = planes["k_norms"]
+        if qc.device != self.device or kn.device != self.device:
+            raise ValueError(f"quashkv_b200: queries on {qc.device}, planes on {kn.device}, constants on {self.device}")
+        out = torch.empty((B, Hq, Q, d), dtype=torch.float32, device=q.device)
+        need = self.lib.qkv_attention_workspace_bytes(B, Hq, n_kv_heads, Q, kv_len, d)
+        if self.ws is None or self.ws.numel() < need:
+            self.ws = torch.empty((max(need + need // 4, 1 << 16),), dtype=torch.uint8, device=q.device)
+        cache = Cache(planes["k_codes"].data_ptr(), planes["k_signs"].data_ptr(), kn.data_ptr(),
+                      planes["v_codes"].data_ptr(), planes["v_norms"].data_ptr(), kn.shape[-1])
+        rc = self.fn(qc.data_ptr(), _DT[qc.dtype], cache, B, Hq, n_kv_heads, Q, kv_len, d, self.key_bits,
+                     self.val_bits, *self.ptrs, self.qjl_scale, scale, int(causal), out.data_ptr(),
+                     self.ws.data_ptr(), self.ws.numel(), torch.cuda.current_stream(q.device).cuda_stream)
+        if rc:
+            _lib.check(rc, "attention")
+        return out
+
+
+class AppendCall:
+    """Compression of new keys and values into an engine's storage, prepared once: constants converted once,
+    the staging planes of a tiled cache kept between calls, the library called directly.  The generic ops cost
+    80-120 us of host time per one-token append (dispatcher, conversions, five allocations)."""
+
+    def __init__(self, Pi, k_bounds, k_cents, S, mse_bits: int, v_bounds, val_bits: int):
+        self.consts = tuple(_f32(t) for t in (Pi, k_bounds, k_cents, S, v_bounds))
+        self.Pi, self.kb, self.kc, self.S, self.vb = (_p(t) for t in self.consts)
+        self.mse_bits, self.val_bits = int(mse_bits), int(val_bits)
+        self.device = self.consts[0].device
+        self.lib = _lib.lib()
+        self.stage = None           # tiled: (k_codes, k_signs, k_norms, v_codes, v_norms) for up to stage_rows rows
+        self.stage_rows = 0
+        self.stage_stream = None    # the staging planes belong to the stream they were last used on
+
+    def _compress(self, keys, values, ptrs, rows: "Rows", stream) -> None:
+        kf, d = _flat(keys)
+        vf, _ = _flat(values)
+        if kf.device != self.device or vf.device != self.device:
+            raise ValueError(f"quashkv_b200: keys on {kf.device}, constants on {self.device}")
+        L = self.lib
+        rc = L.qkv_compress_ip(kf.data_ptr(), _DT[kf.dtype], d, kf.shape[0], d, self.Pi, self.kb, self.kc,
+                               self.mse_bits, self.S, ptrs[0], ptrs[1], 1, ptrs[2], rows, stream)
+        if rc:
+            _lib.check(rc, "append keys")
+        rc = L.qkv_compress_mse(vf.data_ptr(), _DT[vf.dtype], d, vf.shape[0], d, self.Pi, self.vb, self.val_bits,
+                                ptrs[3], 1, ptrs[4], rows, stream)
+        if rc:
+            _lib.check(rc, "append values")
+
+    def into_planes(self, keys: torch.Tensor, values: torch.Tensor, planes: dict, offset: int) -> None:
+        """(B,H,S,d) keys / values into row-major planes [B*H, capacity, ...] at rows offset..offset+S."""
+        kn = planes["k_norms"]
+        if kn.device != self.device:
+            raise ValueError(f"quashkv_b200: planes on {kn.device}, constants on {self.device}")
+        ptrs = tuple(C.c_void_p(planes[n].data_ptr()) for n in ("k_codes", "k_signs", "k_norms", "v_codes", "v_norms"))
+        self._compress(keys, values, ptrs, Rows(keys.shape[-2], kn.shape[-1], offset),
+                       C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+
+    def into_records(self, keys: torch.Tensor, values: torch.Tensor, records: torch.Tensor, row_bytes: tuple,
+                     capacity: int, offset: int) -> None:
+        """(B,H,S,d) keys / values into tile records [B*H, capacity/16, 1664] at tokens offset..offset+S."""
+        if records.device != self.device:
+            raise ValueError(f"quashkv_b200: records on {records.device}, constants on {self.device}")
+        b, H, S, _ = keys.shape
+        n = b * H * S
+        stream_handle = torch.cuda.current_stream(self.device).cuda_stream
+        if self.stage is None or self.stage_rows < n or self.stage_stream != stream_handle:
+            pk, ps, pv = row_bytes
+            u8 = dict(dtype=torch.uint8, device=self.device)
+            f32 = dict(dtype=torch.float32, device=self.device)
+            self.stage = (torch.empty((n, pk), **u8), torch.empty((n, ps), **u8), torch.empty((n,), **f32),
+                          torch.empty((n, pv), **u8), torch.empty((n,), **f32))
+            self.stage_rows = n
+            self.stage_stream = stream_handle
+        ptrs = tuple(C.c_void_p(t.data_ptr()) for t in self.stage)
+        stream = C.c_void_p(stream_handle)
+        self._compress(keys, values, ptrs, _dense(n), stream)
+        rc = self.lib.qkv_tile_rows(*ptrs, n, C.c_void_p(records.data_ptr()), Rows(max(S, 1), capacity, offset), None,
+                                    stream)
+        if rc:
+            _lib.check(rc, "tile_rows")
+
+
 _CUDART = None
 
 
