@@ -15,7 +15,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libquashkv_b200.so")
-SOURCES = ["rotate_quant.cu", "rotate_mma.cu", "rotate_umma.cu", "packing.cu", "attention.cu", "attention_mma.cu", "attention_tiled.cu", "tiling.cu", "index_scan.cu", "index_scan_mma.cu", "index_scan_umma.cu"]
+SOURCES = ["rotate_quant.cu", "rotate_mma.cu", "rotate_umma.cu", "decompress_umma.cu", "packing.cu", "attention.cu", "attention_mma.cu", "attention_tiled.cu", "tiling.cu", "index_scan.cu", "index_scan_mma.cu", "index_scan_umma.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",

@@ -1,0 +1,529 @@
+// Decompress at d = 128 with the un-rotation on the fifth-generation tensor cores (tcgen05).
+//
+// out = norm * (v @ Pi) with v_i = c[code_i] (+ qjl_scale * S_i * (2 sign_i - 1) for keys): a 128 x 128 x 128
+// contraction per tile of 128 vectors with A = the decoded rows, written by the threads into the 128-byte
+// swizzled K-major operand layout, and B = Pi^T, staged once per CTA.  One CTA of 512 threads per SM; ONE thread
+// issues the tcgen05.mma instructions (M = 128, N = 128, K = 16), the fp32 accumulator lives in tensor memory
+// (two accumulators alternate) and completion arrives on an mbarrier.
+//
+//   * Exact fp32 from fp16 MMAs.  Both operands are scaled by a power of two that puts their largest magnitude
+//     just below 2^14 and split into TWO fp16 terms, x = h + m with |m| <= ulp(h) / 2: 22 significand bits, and
+//     the scaling keeps m out of the subnormal range for every value that matters.  Four products (m*m, m*h,
+//     h*m, h*h, smallest first: 32 MMAs per tile) accumulate in fp32; the power of two leaves with the norm.
+//   * Decode by pairs.  With S = +-1 (what the quantiser generates) a pair of neighbouring coordinates takes one
+//     of 2^(2 bits [+ 2]) values, and the packed row holds the two codes side by side: the field (and the two
+//     sign bits) index a shared-memory table of READY operand words (h0 | h1, m0 | m1), repeated per lane so that
+//     every lane of a half warp reads its own banks.  A pair costs a shift, a mask (a shift and a merge more for
+//     the sign bits) and one 8-byte load; four pairs leave as one 16-byte store per plane.
+//   * Two A buffers: the threads decode tile t + 1 while the tensor core multiplies tile t.  The buffer of tile
+//     t - 1 is idle by then, and every warp owns the chunks of it that it wrote itself (32 rows x 64 bytes per
+//     plane): the epilogue uses exactly those chunks to transpose its outputs (a thread holds 32 consecutive
+//     outputs of ONE row; they come back as 8 rows x 64 contiguous bytes per store instruction), so no other
+//     staging memory and no CTA barrier is needed for it.
+//   * The packed words and the norm of a tile are fetched one tile ahead of their use.
+//
+// Every wait on the tensor core is bounded; if one runs out the CTA stops using the tensor core, counts the
+// event and derives its remaining tiles with the fp32 chain alone (slow, still correct).
+#include <cuda_fp16.h>
+
+#include <type_traits>
+
+#include "rotate_exact.cuh"
+#include "umma.cuh"
+
+namespace qkv {
+
+__device__ unsigned int g_dec_umma_timeouts = 0;
+
+namespace {
+
+constexpr int kDTile = 128;                       // vectors per tile = MMA M
+constexpr int kDThreads = 512;                    // four threads per vector: 32 coordinates each
+constexpr uint32_t kDPlaneBytes = 128 * 128 * 2;  // one fp16 operand tile (two 64-wide K blocks)
+constexpr uint32_t kDTmemCols = 256;
+constexpr uint32_t kDTableBytes = 32768;          // pair tables (mixed precision: two halves)
+constexpr int kDTopExp = 14;                      // operands are scaled to a largest magnitude in [2^13, 2^14)
+
+__host__ __device__ constexpr int ilog2(int v) { return v <= 1 ? 0 : 1 + ilog2(v >> 1); }
+
+// A pair table has one entry per (code, code [, sign, sign]) of two neighbouring coordinates and is repeated
+// `replicas` times, entry e of replica r at element e * replicas + r: with 16 replicas the 16 lanes of a half
+// warp (an 8-byte load is served per half warp) never meet in a bank whatever entries they read.
+template <int BW, bool SIGNS>
+__host__ __device__ constexpr int pair_entries() { return 1 << (2 * (BW + (SIGNS ? 1 : 0))); }
+template <int BW, bool SIGNS, bool MIXED>
+__host__ __device__ constexpr int pair_replicas() {
+  constexpr int cap = static_cast<int>((MIXED ? kDTableBytes / 2 : kDTableBytes) / 8) / pair_entries<BW, SIGNS>();
+  return cap >= 16 ? 16 : cap;
+}
+
+struct DecSmem {
+  unsigned char* a[2][2];   // A tiles [buffer][term h, m] (fp16, swizzled), 1024-byte aligned
+  unsigned char* b[2];      // Pi^T planes h, m
+  unsigned char* tab;       // pair tables
+  uint64_t* mbar;           // [2]
+  uint32_t* tmem_slot;
+  int* dead;
+};
+
+constexpr size_t dec_smem_bytes() { return 1024 + 6 * kDPlaneBytes + kDTableBytes + 2 * 8 + 16; }
+
+__device__ __forceinline__ DecSmem carve_dec(unsigned char* raw) {
+  DecSmem s;
+  unsigned char* p = raw + ((1024u - (umma::smem_u32(raw) & 1023u)) & 1023u);
+  for (int bf = 0; bf < 2; ++bf)
+    for (int t = 0; t < 2; ++t) { s.a[bf][t] = p; p += kDPlaneBytes; }
+  for (int t = 0; t < 2; ++t) { s.b[t] = p; p += kDPlaneBytes; }
+  s.tab = p; p += kDTableBytes;
+  s.mbar = reinterpret_cast<uint64_t*>(p); p += 16;
+  s.tmem_slot = reinterpret_cast<uint32_t*>(p);
+  s.dead = reinterpret_cast<int*>(p + 4);
+  return s;
+}
+
+// x = h + m to 22 bits, each term an fp16 (round to nearest at both steps; x - h is exact in fp32).
+__device__ __forceinline__ void split2h(float x, __half& h, __half& m) {
+  h = __float2half_rn(x);
+  m = __float2half_rn(x - __half2float(h));
+}
+
+__device__ __forceinline__ uint32_t pack_h(__half lo, __half hi) {
+  return static_cast<uint32_t>(__half_as_ushort(lo)) | (static_cast<uint32_t>(__half_as_ushort(hi)) << 16);
+}
+
+// Power of two that brings a largest magnitude of `mx` into [2^(kDTopExp-1), 2^kDTopExp); 0 for 0, inf, nan.
+__device__ __forceinline__ int scale_exponent(float mx) {
+  if (!(mx > 0.f) || !(mx < 3.0e38f)) return 0;
+  int e;
+  frexpf(mx, &e);                                   // mx = f * 2^e, f in [0.5, 1)
+  const int k = kDTopExp - e;
+  return k < -60 ? -60 : (k > 60 ? 60 : k);
+}
+
+// y = Pi^T-rotation of one decoded row by the fp32 chain (only used after a tensor-core timeout).
+__device__ __noinline__ float decompress_chain(const float* vrow, const float* Pi, int col) {
+  float z = 0.f;
+  for (int i = 0; i < kRD; ++i) z = fmaf(vrow[i], __ldg(Pi + i * kRD + col), z);
+  return z;
+}
+
+// BITS1 != 0: mixed precision (no sign term).  The K dimension runs in STREAM order (outlier channels first):
+// A column k' is stream position k' and B row k' is Pi[perm[k']], so each thread's 32 coordinates belong to
+// one table; needs the outlier count to be a multiple of 32, otherwise the CTA returns and the CUDA-core
+// kernel launched behind it does the work (same device-side test, inverted).
+template <int BITS, bool SIGNS, int BITS1 = 0>
+__global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(DecompressArgs a) {
+  constexpr bool MIXED = BITS1 != 0;
+  constexpr int BMAX = BITS > BITS1 ? BITS : BITS1;
+  constexpr int R0 = pair_replicas<BITS, SIGNS, MIXED>();
+  constexpr int R1 = pair_replicas<(MIXED ? BITS1 : BITS), SIGNS, MIXED>();
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ float cent_s[2][16], qs_s[kRD];
+  __shared__ uint32_t smask_s[4];           // bit c of word w: S[32 w + c] < 0 (mixed: channel is an outlier)
+  __shared__ uint32_t red_s[3];             // bit patterns of max |Pi|, max |centroid|, max |S|
+  __shared__ uint8_t perm_s[kRD];
+  const DecSmem s = carve_dec(smem_raw);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int trow = 32 * (warp & 3) + lane, blk = warp >> 2;
+  const uint32_t* codes = reinterpret_cast<const uint32_t*>(a.codes);
+  const uint32_t* signs = reinterpret_cast<const uint32_t*>(a.signs);
+
+  int n_out = MIXED ? 0 : kRD;                      // K positions below n_out use table 0
+  if (MIXED) {
+    bool o = false;
+    if (tid < kRD) {
+      o = a.is_outlier[tid] != 0;
+      const uint32_t m = __ballot_sync(QKV_FULL_MASK, o);
+      if (lane == 0) smask_s[warp] = m;
+    }
+    __syncthreads();
+    int before = 0;
+    for (int w = 0; w < 4; ++w) {
+      const int c = __popc(smask_s[w]);
+      n_out += c;
+      if (w < warp) before += c;
+    }
+    if (n_out & 31) return;                         // every thread of every CTA: left to the CUDA-core kernel
+    if (tid < kRD) {
+      before += __popc(smask_s[warp] & ((1u << lane) - 1u));
+      perm_s[o ? before : n_out + (tid - before)] = static_cast<uint8_t>(tid);
+    }
+    __syncthreads();
+  }
+  const int m_out = n_out >> 5;
+  const int row_words = MIXED ? m_out * BITS + (4 - m_out) * BITS1 : 4 * BITS;
+  const int cls = blk >= m_out ? 1 : 0;             // table of this thread's 32 K positions
+  const int word_off = cls ? m_out * BITS + (blk - m_out) * BITS1 : blk * BITS;
+  const int bits_c = cls ? BITS1 : BITS;
+
+  // ---- one-time setup: small tables, operand scales, Pi^T planes, pair tables, barriers, TMEM --------------
+  if (tid < 3) red_s[tid] = 0u;
+  if (tid < 16) {
+    cent_s[0][tid] = tid < (1 << BITS) ? a.cents0[tid] : 0.f;
+    cent_s[1][tid] = (MIXED && tid < (1 << BITS1)) ? a.cents1[tid] : 0.f;
+  }
+  bool pm1 = true;
+  float s_abs = 0.f;
+  if (tid < kRD) {
+    const float sv = SIGNS ? a.S[tid] : 1.f;
+    qs_s[tid] = SIGNS ? a.qjl_scale * sv : 0.f;
+    pm1 = fabsf(sv) == 1.f;
+    s_abs = SIGNS ? fabsf(sv) : 0.f;
+    const uint32_t neg = __ballot_sync(QKV_FULL_MASK, sv < 0.f);
+    if (lane == 0) smask_s[warp] = neg;
+  }
+  const bool table_ok = __syncthreads_and(pm1) != 0;     // S = +-1 everywhere: the pair table applies
+  {
+    float pi_abs = 0.f;
+    for (int idx = tid; idx < kRD * kRD; idx += kDThreads) pi_abs = fmaxf(pi_abs, fabsf(__ldg(a.Pi + idx)));
+    float c_abs = tid < 32 ? fabsf(cent_s[tid >> 4][tid & 15]) : 0.f;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      pi_abs = fmaxf(pi_abs, __shfl_xor_sync(QKV_FULL_MASK, pi_abs, o));
+      c_abs = fmaxf(c_abs, __shfl_xor_sync(QKV_FULL_MASK, c_abs, o));
+      s_abs = fmaxf(s_abs, __shfl_xor_sync(QKV_FULL_MASK, s_abs, o));
+    }
+    if (lane == 0) {                                // non-negative floats order like their bit patterns
+      atomicMax(&red_s[0], __float_as_uint(pi_abs));
+      if (warp == 0) atomicMax(&red_s[1], __float_as_uint(c_abs));
+      if (SIGNS && warp < 4) atomicMax(&red_s[2], __float_as_uint(s_abs));
+    }
+  }
+  __syncthreads();
+  const int kb = scale_exponent(__uint_as_float(red_s[0]));
+  const int ka = scale_exponent(__uint_as_float(red_s[1]) + fabsf(a.qjl_scale) * __uint_as_float(red_s[2]));
+  const float scale_a = ldexpf(1.f, ka), scale_b = ldexpf(1.f, kb), descale = ldexpf(1.f, -(ka + kb));
+
+  for (int idx = tid; idx < kRD * kRD; idx += kDThreads) {      // B[n = output j][k] = Pi[channel of k][j]
+    const int i = idx >> 7, j = idx & 127;
+    __half h, m;
+    split2h(a.Pi[(MIXED ? perm_s[i] : i) * kRD + j] * scale_b, h, m);
+    const uint32_t off = umma::sw128_offset(j, i, 128);
+    *reinterpret_cast<__half*>(s.b[0] + off) = h;
+    *reinterpret_cast<__half*>(s.b[1] + off) = m;
+  }
+  auto build_pairs = [&](auto bw_tag, auto rep_tag, uint2* tab, const float* cent) {
+    constexpr int BW = decltype(bw_tag)::value, R = decltype(rep_tag)::value;
+    constexpr int E = pair_entries<BW, SIGNS>();
+    constexpr uint32_t CM = (1u << BW) - 1u;
+    for (int idx = tid; idx < E * R; idx += kDThreads) {
+      const uint32_t e = static_cast<uint32_t>(idx / R);
+      float x0 = cent[e & CM], x1 = cent[(e >> BW) & CM];
+      if (SIGNS) {
+        x0 += (e >> (2 * BW)) & 1u ? a.qjl_scale : -a.qjl_scale;
+        x1 += (e >> (2 * BW + 1)) & 1u ? a.qjl_scale : -a.qjl_scale;
+      }
+      __half h0, m0, h1, m1;
+      split2h(x0 * scale_a, h0, m0);
+      split2h(x1 * scale_a, h1, m1);
+      tab[idx] = make_uint2(pack_h(h0, h1), pack_h(m0, m1));
+    }
+  };
+  uint2* const tab0 = reinterpret_cast<uint2*>(s.tab);
+  uint2* const tab1 = reinterpret_cast<uint2*>(s.tab + kDTableBytes / 2);
+  build_pairs(std::integral_constant<int, BITS>{}, std::integral_constant<int, R0>{}, tab0, cent_s[0]);
+  if (MIXED)
+    build_pairs(std::integral_constant<int, (MIXED ? BITS1 : BITS)>{}, std::integral_constant<int, R1>{}, tab1, cent_s[1]);
+  const unsigned char* const tabl = cls ? reinterpret_cast<const unsigned char*>(tab1 + (lane & (R1 - 1)))
+                                        : reinterpret_cast<const unsigned char*>(tab0 + (lane & (R0 - 1)));
+  const uint32_t smask = SIGNS ? smask_s[blk] : 0u;
+  if (tid == 0) {
+    umma::mbar_init(&s.mbar[0], 1);
+    umma::mbar_init(&s.mbar[1], 1);
+    *s.dead = 0;
+  }
+  if (warp == 0) umma::tmem_alloc(s.tmem_slot, kDTmemCols);
+  umma::fence_smem_to_async();
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  const uint32_t tmem_base = *s.tmem_slot;
+  const int64_t n_tiles = (a.n_vec + kDTile - 1) / kDTile;
+  const bool one_segment = a.rows.seg_len >= a.n_vec;           // rows are n + seg_off: no division
+  auto row_of = [&](int64_t n) -> int64_t { return one_segment ? n + a.rows.seg_off : map_row(a.rows, n); };
+
+  // Packed words (and the norm) of this thread's part of a row, fetched one tile ahead of their use.
+  uint32_t nw[BMAX + 1], nsw = 0;
+  float nnorm = 0.f;
+  auto fetch = [&](int64_t tile) {
+    const int64_t n = tile * kDTile + trow;
+    const bool live = tile < n_tiles && n < a.n_vec;
+    const int64_t row = live ? row_of(n) : 0;
+#pragma unroll
+    for (int q = 0; q < BMAX; ++q) nw[q] = (live && q < bits_c) ? __ldg(codes + row * row_words + word_off + q) : 0u;
+    nw[BMAX] = 0u;
+    if (SIGNS) nsw = live ? __ldg(signs + row * (kRD / 32) + blk) : 0u;
+    nnorm = live ? __ldg(a.norms + row) : 0.f;
+  };
+
+  // Offset of this thread's 16-byte chunk q (coordinates 8 q .. 8 q + 7 of its 32) of row `row` inside a plane.
+  auto chunk_off = [&](int row, int q) -> uint32_t {
+    return static_cast<uint32_t>((blk >> 1) * (128 * 128) + row * 128 + (((4 * (blk & 1) + q) ^ (row & 7)) << 4));
+  };
+
+  // Decode this thread's 32 coordinates of row trow into the two operand planes of A[bf] through the pair table.
+  auto decode_table = [&](auto bw_tag, auto rep_tag, int bf) {
+    constexpr int BW = decltype(bw_tag)::value, R = decltype(rep_tag)::value;
+    constexpr int L = 3 + ilog2(R);                   // an entry index becomes a byte offset by << L
+    constexpr uint32_t FM = ((1u << (2 * BW)) - 1u) << L, SM = 3u << (2 * BW + L);
+    const uint32_t sx = nsw ^ smask;                  // bit c: add (1) or subtract (0) qjl_scale
+#pragma unroll
+    for (int c8 = 0; c8 < 4; ++c8) {
+      uint2 e[4];
+#pragma unroll
+      for (int p4 = 0; p4 < 4; ++p4) {
+        const int p = 4 * c8 + p4, bit = 2 * BW * p, wi = bit >> 5, sh = bit & 31;
+        uint32_t off;
+        if (sh + 2 * BW > 32) off = __funnelshift_r(nw[wi], nw[wi + 1], sh - L);
+        else off = sh >= L ? nw[wi] >> (sh - L) : nw[wi] << (L - sh);
+        off &= FM;
+        if (SIGNS) {
+          const int ss = 2 * p - (2 * BW + L);        // the pair's two sign bits go right above the codes
+          off |= (ss >= 0 ? sx >> ss : sx << -ss) & SM;
+        }
+        e[p4] = *reinterpret_cast<const uint2*>(tabl + off);
+      }
+      const uint32_t o = chunk_off(trow, c8);
+      *reinterpret_cast<uint4*>(s.a[bf][0] + o) = make_uint4(e[0].x, e[1].x, e[2].x, e[3].x);
+      *reinterpret_cast<uint4*>(s.a[bf][1] + o) = make_uint4(e[0].y, e[1].y, e[2].y, e[3].y);
+    }
+  };
+  auto decode_tile = [&](int bf) {
+    if (MIXED) {
+      if (cls) decode_table(std::integral_constant<int, (MIXED ? BITS1 : BITS)>{}, std::integral_constant<int, R1>{}, bf);
+      else decode_table(std::integral_constant<int, BITS>{}, std::integral_constant<int, R0>{}, bf);
+      return;
+    }
+    if (table_ok) {
+      decode_table(std::integral_constant<int, BITS>{}, std::integral_constant<int, R0>{}, bf);
+      return;
+    }
+    // S with other magnitudes than 1: every coordinate by arithmetic
+#pragma unroll
+    for (int c8 = 0; c8 < 4; ++c8) {
+      uint32_t packed[2][4];
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        float v[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int c = 8 * c8 + 2 * p + h;
+          const int bit = BITS * c, wi = bit >> 5, sh = bit & 31;
+          uint32_t code = nw[wi] >> sh;
+          if (sh + BITS > 32) code |= nw[wi + 1] << (32 - sh);
+          code &= (1u << BITS) - 1u;
+          float x = cent_s[0][code];
+          if (SIGNS) {
+            const float q = qs_s[32 * blk + c];
+            x += ((nsw >> c) & 1u) ? q : -q;
+          }
+          v[h] = x * scale_a;
+        }
+        __half h0, m0, h1, m1;
+        split2h(v[0], h0, m0);
+        split2h(v[1], h1, m1);
+        packed[0][p] = pack_h(h0, h1);
+        packed[1][p] = pack_h(m0, m1);
+      }
+      const uint32_t o = chunk_off(trow, c8);
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+        *reinterpret_cast<uint4*>(s.a[bf][t] + o) = make_uint4(packed[t][0], packed[t][1], packed[t][2], packed[t][3]);
+    }
+  };
+
+  // One thread: four products, smallest first, then the completion arrival.
+  auto issue_mmas = [&](int bf, int acc_buf) {
+    constexpr uint32_t idesc = umma::instr_desc(umma::kFmtF16, 128, 128);
+    const uint32_t d = tmem_base + acc_buf * 128;
+    constexpr int pa[4] = {1, 0, 1, 0}, pb[4] = {1, 1, 0, 0};
+    bool acc = false;
+#pragma unroll
+    for (int pr = 0; pr < 4; ++pr) {
+      const uint32_t a_addr = umma::smem_u32(s.a[bf][pa[pr]]), b_addr = umma::smem_u32(s.b[pb[pr]]);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t off = (ks >> 2) * (128 * 128) + (ks & 3) * 32;
+        umma::mma_f16(d, umma::smem_desc_sw128(a_addr + off), umma::smem_desc_sw128(b_addr + off), idesc, acc);
+        acc = true;
+      }
+    }
+    umma::commit(&s.mbar[acc_buf]);
+  };
+
+  // Scale this thread's 32 outputs of row trow by the norm and store them; the transposition goes through this
+  // warp's own chunks of the idle A buffer `bf` (plane 0, and plane 1 for the second half of fp32 outputs).
+  auto epilogue = [&](int64_t tile, int acc_buf, int bf, float nrm, bool use_tmem) {
+    const int64_t n = tile * kDTile + trow;
+    const bool live = n < a.n_vec;
+    uint32_t v[32];
+    float f = nrm;
+    if (use_tmem) {
+      umma::tmem_ld32(tmem_base + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + acc_buf * 128 + 32 * blk, v);
+      f = nrm * descale;
+      if (!(fabsf(f) >= 1e-30f && fabsf(f) <= 1e30f)) {  // the product would lose bits: take the power of two first
+#pragma unroll
+        for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * descale);
+        f = nrm;
+      }
+    } else if (live) {                                   // tensor core timed out: fp32 chain from the packed row
+      const int64_t row = row_of(n);
+      float vrow[kRD];
+      for (int i = 0; i < kRD; ++i) {                    // i = stream position; channel = perm[i] when mixed
+        const int ci = i >= n_out ? 1 : 0;
+        const int bit = ci ? n_out * BITS + (i - n_out) * BITS1 : i * BITS;
+        const uint32_t code = read_field(a.codes + row * (row_words * 4), bit, ci ? BITS1 : BITS, row_words * 4);
+        float x = cent_s[ci][code];
+        if (SIGNS) x += ((signs[row * (kRD / 32) + (i >> 5)] >> (i & 31)) & 1u) ? qs_s[i] : -qs_s[i];
+        vrow[MIXED ? perm_s[i] : i] = x;
+      }
+      for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(decompress_chain(vrow, a.Pi, 32 * blk + c));
+    }
+    const int64_t n0 = tile * kDTile + 32 * (warp & 3);
+    const int rbase = 32 * (warp & 3);
+    // read side of the transposition: lane -> (row 8 j + rr, chunk q); the two rows of a quarter warp differ in
+    // bit 2, so its eight chunks sit in eight different 16-byte columns of the swizzled layout
+    const int rr = ((lane >> 3) & 3) | (((lane >> 2) & 1) << 2), rq = lane & 3;
+    if (a.out_dtype == QKV_F32) {
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        unsigned char* st = s.a[bf][hf];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int c = 16 * hf + 4 * q;
+          *reinterpret_cast<float4*>(st + chunk_off(trow, q)) =
+              make_float4(__uint_as_float(v[c]) * f, __uint_as_float(v[c + 1]) * f, __uint_as_float(v[c + 2]) * f,
+                          __uint_as_float(v[c + 3]) * f);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int r = 8 * j + rr;
+          const float4 o = *reinterpret_cast<const float4*>(st + chunk_off(rbase + r, rq));
+          if (n0 + r < a.n_vec)
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + (n0 + r) * a.out_pitch + 32 * blk + 16 * hf +
+                                       4 * rq) = o;
+        }
+      }
+      __syncwarp();
+    } else if (a.out_dtype == QKV_BF16) {
+      unsigned char* st = s.a[bf][0];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 2 * e]) * f,
+                                                          __uint_as_float(v[8 * q + 2 * e + 1]) * f);
+          pk[e] = *reinterpret_cast<const uint32_t*>(&b2);
+        }
+        *reinterpret_cast<uint4*>(st + chunk_off(trow, q)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int r = 8 * j + rr;
+        const uint4 o = *reinterpret_cast<const uint4*>(st + chunk_off(rbase + r, rq));
+        if (n0 + r < a.n_vec)
+          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.out) + (n0 + r) * a.out_pitch + 32 * blk + 8 * rq) = o;
+      }
+      __syncwarp();
+    } else if (live) {
+#pragma unroll
+      for (int c = 0; c < 32; ++c)
+        store_float(a.out, a.out_dtype, n * a.out_pitch + 32 * blk + c, __uint_as_float(v[c]) * f);
+    }
+  };
+
+  // ---- pipeline: decode(i); issue(i); wait(i-1); epilogue(i-1)   (decode overlaps the MMAs of tile i-1) -----
+  uint32_t phase[2] = {0u, 0u};
+  int64_t prev_tile = -1;
+  int i = 0;
+  float norm_cur = 0.f, norm_prev = 0.f;
+  fetch(blockIdx.x);
+  for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++i) {
+    const int bf = i & 1;                   // A buffer and accumulator of tile i
+    decode_tile(bf);
+    norm_prev = norm_cur;
+    norm_cur = nnorm;
+    fetch(tile + gridDim.x);                // the next tile's words travel while this one is multiplied and stored
+    umma::fence_smem_to_async();
+    umma::fence_before_sync();
+    __syncthreads();                        // A(i) written; epilogue(i-2) has left accumulator bf
+    if (tid == 0 && *s.dead == 0) {
+      umma::fence_after_sync();
+      issue_mmas(bf, bf);
+    }
+    if (prev_tile >= 0) {
+      bool ok = *s.dead == 0;
+      if (ok) {
+        ok = umma::mbar_wait(&s.mbar[bf ^ 1], phase[bf ^ 1]);
+        phase[bf ^ 1] ^= 1u;
+        if (!ok) { *s.dead = 1; atomicAdd(&g_dec_umma_timeouts, 1u); }
+      }
+      umma::fence_after_sync();
+      epilogue(prev_tile, bf ^ 1, bf ^ 1, norm_prev, ok);
+    }
+    prev_tile = tile;
+  }
+  if (prev_tile >= 0) {
+    const int bf = (i - 1) & 1;
+    bool ok = *s.dead == 0;
+    if (ok) {
+      ok = umma::mbar_wait(&s.mbar[bf], phase[bf]);
+      if (!ok) { *s.dead = 1; atomicAdd(&g_dec_umma_timeouts, 1u); }
+    }
+    umma::fence_after_sync();
+    epilogue(prev_tile, bf, bf, norm_cur, ok);
+  }
+  umma::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) umma::tmem_dealloc(tmem_base, kDTmemCols);
+}
+
+template <int BITS, bool SIGNS, int BITS1 = 0>
+int launch_t(const DecompressArgs& a, cudaStream_t st) {
+  constexpr size_t smem = dec_smem_bytes();
+  if (cudaFuncSetAttribute(decompress_umma_kernel<BITS, SIGNS, BITS1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem)) != cudaSuccess)
+    return QKV_ELAUNCH;
+  const int64_t tiles = (a.n_vec + kDTile - 1) / kDTile;
+  const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
+  decompress_umma_kernel<BITS, SIGNS, BITS1><<<grid, kDThreads, smem, st>>>(a);
+  return check_launch();
+}
+
+}  // namespace
+
+unsigned int decompress_umma_timeouts() {
+  unsigned int v = 0;
+  cudaMemcpyFromSymbol(&v, g_dec_umma_timeouts, sizeof(v));
+  return v;
+}
+
+bool decompress_umma_ok(const DecompressArgs& a) {
+  const uintptr_t al = reinterpret_cast<uintptr_t>(a.codes) | reinterpret_cast<uintptr_t>(a.out) |
+                       (a.signs ? reinterpret_cast<uintptr_t>(a.signs) : 0);
+  if (a.mode == MODE_MIXED) {   // the common width pairs; rows are whole 4-byte words (36 B at 32 x 3 + 96 x 2 bits)
+    const bool pair = (a.bits0 == 3 && a.bits1 == 2) || (a.bits0 == 4 && a.bits1 == 3) || (a.bits0 == 4 && a.bits1 == 2);
+    return pair && a.d == kRD && a.packed && a.n_vec >= 1024 && (a.out_pitch & 7) == 0 &&
+           ((reinterpret_cast<uintptr_t>(a.out) & 15u) | (reinterpret_cast<uintptr_t>(a.codes) & 3u)) == 0;
+  }
+  return a.d == kRD && a.packed && a.n_vec >= 1024 && (a.out_pitch & 7) == 0 && (al & 15u) == 0;
+}
+
+int launch_decompress_umma(const DecompressArgs& a, cudaStream_t st) {
+  if (a.mode == MODE_MIXED) {
+    if (a.bits0 == 3) return launch_t<3, false, 2>(a, st);
+    return a.bits1 == 3 ? launch_t<4, false, 3>(a, st) : launch_t<4, false, 2>(a, st);
+  }
+  const bool sg = a.signs != nullptr;
+  switch (a.bits0) {
+    case 1: return sg ? launch_t<1, true>(a, st) : launch_t<1, false>(a, st);
+    case 2: return sg ? launch_t<2, true>(a, st) : launch_t<2, false>(a, st);
+    case 3: return sg ? launch_t<3, true>(a, st) : launch_t<3, false>(a, st);
+    default: return sg ? launch_t<4, true>(a, st) : launch_t<4, false>(a, st);
+  }
+}
+
+}  // namespace qkv

@@ -44,7 +44,7 @@ struct DecompressArgs {
 bool compress_mma_ok(const CompressArgs& a);
 int launch_compress_mma(const CompressArgs& a, cudaStream_t st);
 bool decompress_mma_ok(const DecompressArgs& a);
-// tcgen05 rotation (rotate_umma.cu): d == 128, bf16 input, packed output.
+// tcgen05 rotation (rotate_umma.cu, decompress_umma.cu): d == 128, packed rows.
 bool compress_umma_ok(const CompressArgs& a);
 int launch_compress_umma(const CompressArgs& a, cudaStream_t st);
 bool decompress_umma_ok(const DecompressArgs& a);

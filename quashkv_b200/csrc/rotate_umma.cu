@@ -615,460 +615,13 @@ int launch_compress_umma(const CompressArgs& a_in, cudaStream_t st) {
   }
 }
 
+unsigned int decompress_umma_timeouts();           // decompress_umma.cu keeps its own counter
+
 unsigned int umma_timeouts() {
   unsigned int v = 0;
   cudaMemcpyFromSymbol(&v, g_umma_timeouts, sizeof(v));
-  return v;
+  return v + decompress_umma_timeouts();
 }
 
-
-// ---- decompress ------------------------------------------------------------------------------------------
-// out = norm * (v @ Pi) with v_i = c[code_i] (+ qjl_scale * S_i * (2 sign_i - 1)): the same 128 x 128 x 128
-// contraction with the roles swapped: A = the decoded rows, written by the threads into the
-// swizzled operand layout, B = Pi^T.  Both operands are split into NT bf16 terms:
-//   NT = 3 (fp32 output): exact split, six products, an fp32-faithful result; one A buffer;
-//   NT = 2 (bf16 output): four products, relative error ~1e-5, far below the bf16 rounding of
-//                         the output; two A buffers, so decoding tile t+1 overlaps the MMAs of tile t.
-// Four threads per row: each decodes 32 coordinates and later scales and stores 32 outputs.
-template <int NT>
-struct DecSmem {
-  static constexpr int NBUF = NT == 2 ? 2 : 1;
-  unsigned char* a[NBUF][NT];
-  unsigned char* b[NT];
-  unsigned char* stage;     // [warps][32 rows][64 bytes]: output transposition, 16 columns at a time
-  uint64_t* mbar;           // [2]
-  uint32_t* tmem_slot;
-  int* dead;
-};
-
-template <int NT>
-constexpr size_t dec_smem_bytes() {
-  return 1024 + static_cast<size_t>(DecSmem<NT>::NBUF * NT + NT) * kUPlaneBytes + kUWarps * 2048 + 2 * 8 + 16;
-}
-
-template <int NT>
-__device__ __forceinline__ DecSmem<NT> carve_dec(unsigned char* raw) {
-  DecSmem<NT> s;
-  unsigned char* p = raw + ((1024u - (umma::smem_u32(raw) & 1023u)) & 1023u);
-  for (int bf = 0; bf < DecSmem<NT>::NBUF; ++bf)
-    for (int t = 0; t < NT; ++t) { s.a[bf][t] = p; p += kUPlaneBytes; }
-  for (int t = 0; t < NT; ++t) { s.b[t] = p; p += kUPlaneBytes; }
-  s.stage = p; p += kUWarps * 2048;
-  s.mbar = reinterpret_cast<uint64_t*>(p); p += 16;
-  s.tmem_slot = reinterpret_cast<uint32_t*>(p);
-  s.dead = reinterpret_cast<int*>(p + 4);
-  return s;
-}
-
-// y = Pi^T-rotation of one decoded row by the fp32 chain (only used after a tensor-core timeout).
-static __device__ __noinline__ float decompress_chain(const float* vrow, const float* Pi, int col) {
-  float z = 0.f;
-  for (int i = 0; i < kRD; ++i) z = fmaf(vrow[i], __ldg(Pi + i * kRD + col), z);
-  return z;
-}
-
-// BITS1 != 0: mixed precision (no sign term).  The K dimension runs in STREAM order (outlier channels first):
-// A column k' is stream position k' and B row k' is Pi[perm[k']], so each thread's 32 coordinates belong to
-// one table; needs the outlier count to be a multiple of 32, otherwise the CTA returns and the CUDA-core
-// kernel launched behind it does the work (same device-side test, inverted).
-template <int BITS, bool SIGNS, int NT, int BITS1 = 0>
-__global__ void __launch_bounds__(kUThreads, 1) decompress_umma_kernel(DecompressArgs a) {
-  constexpr bool MIXED = BITS1 != 0;
-  constexpr int BMAX = BITS > BITS1 ? BITS : BITS1;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ float cent_s[2][16], qs_s[kRD];
-  __shared__ uint2 split_s[2][32];          // per table: bf16 terms (h | m << 16, l) of the possible values
-  __shared__ uint32_t smask_s[4];           // bit c of word w: S[32 w + c] < 0 (mixed: channel is an outlier)
-  __shared__ uint8_t perm_s[kRD];
-  const DecSmem<NT> s = carve_dec<NT>(smem_raw);
-  constexpr int NBUF = DecSmem<NT>::NBUF;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int trow = 32 * (warp & 3) + lane, blk = warp >> 2;
-  const uint32_t* codes = reinterpret_cast<const uint32_t*>(a.codes);
-  const uint32_t* signs = reinterpret_cast<const uint32_t*>(a.signs);
-
-  int n_out = MIXED ? 0 : kRD;                      // K positions below n_out use table 0
-  if (MIXED) {
-    bool o = false;
-    if (tid < kRD) {
-      o = a.is_outlier[tid] != 0;
-      const uint32_t m = __ballot_sync(QKV_FULL_MASK, o);
-      if (lane == 0) smask_s[warp] = m;
-    }
-    __syncthreads();
-    int before = 0;
-    for (int w = 0; w < 4; ++w) {
-      const int c = __popc(smask_s[w]);
-      n_out += c;
-      if (w < warp) before += c;
-    }
-    if (n_out & 31) return;                         // every thread of every CTA: left to the CUDA-core kernel
-    if (tid < kRD) {
-      before += __popc(smask_s[warp] & ((1u << lane) - 1u));
-      perm_s[o ? before : n_out + (tid - before)] = static_cast<uint8_t>(tid);
-    }
-    __syncthreads();
-  }
-  const int m_out = n_out >> 5;
-  const int row_words = MIXED ? m_out * BITS + (4 - m_out) * BITS1 : 4 * BITS;
-  const int cls = blk >= m_out ? 1 : 0;             // table of this thread's 32 K positions
-  const int word_off = cls ? m_out * BITS + (blk - m_out) * BITS1 : blk * BITS;
-  const int bits_c = cls ? BITS1 : BITS;
-
-  // ---- one-time setup: Pi^T planes (B[n = output j][k] = Pi[channel of k][j]), tables, barriers, TMEM -----
-  for (int idx = tid; idx < kRD * kRD; idx += kUThreads) {
-    const int i = idx >> 7, j = idx & 127;
-    __nv_bfloat16 t3[3];
-    split3(a.Pi[(MIXED ? perm_s[i] : i) * kRD + j], t3[0], t3[1], t3[2]);
-    const uint32_t off = umma::sw128_offset(j, i, 128);
-#pragma unroll
-    for (int t = 0; t < NT; ++t) *reinterpret_cast<__nv_bfloat16*>(s.b[t] + off) = t3[t];
-  }
-  if (tid < 16) {
-    cent_s[0][tid] = tid < (1 << BITS) ? a.cents0[tid] : 0.f;
-    cent_s[1][tid] = (MIXED && tid < (1 << BITS1)) ? a.cents1[tid] : 0.f;
-  }
-  bool pm1 = true;
-  if (tid < kRD) {
-    const float sv = SIGNS ? a.S[tid] : 1.f;
-    qs_s[tid] = SIGNS ? a.qjl_scale * sv : 0.f;
-    pm1 = fabsf(sv) == 1.f;
-    const uint32_t neg = __ballot_sync(QKV_FULL_MASK, sv < 0.f);
-    if (lane == 0) smask_s[warp] = neg;
-  }
-  const bool table_ok = __syncthreads_and(pm1) != 0;     // S = +-1 everywhere: the value table applies
-  if (tid < 64) {
-    const int tb = tid >> 5, e = tid & 31;
-    const int bw = tb ? (MIXED ? BITS1 : BITS) : BITS;
-    const uint32_t code = e & ((1u << bw) - 1u);
-    float x = (tb ? (MIXED ? a.cents1 : a.cents0) : a.cents0)[code];
-    if (SIGNS) x += (e >> BITS) & 1u ? a.qjl_scale : -a.qjl_scale;
-    __nv_bfloat16 h, m, l;
-    split3(x, h, m, l);
-    split_s[tb][e] = make_uint2(pack_bf16(h, m), static_cast<uint32_t>(__bfloat16_as_ushort(l)));
-  }
-  const uint32_t smask = SIGNS ? smask_s[blk] : 0u;
-  if (tid == 0) {
-    umma::mbar_init(&s.mbar[0], 1);
-    umma::mbar_init(&s.mbar[1], 1);
-    *s.dead = 0;
-  }
-  if (warp == 0) umma::tmem_alloc(s.tmem_slot, kUTmemCols);
-  umma::fence_smem_to_async();
-  umma::fence_before_sync();
-  __syncthreads();
-  umma::fence_after_sync();
-  const uint32_t tmem_base = *s.tmem_slot;
-  const int64_t n_tiles = (a.n_vec + kUTile - 1) / kUTile;
-
-  // Decode this thread's 32 coordinates of row trow into the NT operand planes of A[bf].  With S = +-1 (what
-  // the quantiser generates) a coordinate's value is one of 2^(BITS+1) numbers, c[code] +- qjl_scale, chosen by
-  // the code and by sign bit xor (S < 0); their exact bf16 terms sit in a shared-memory table, so a
-  // coordinate costs a field extraction, one 8-byte look-up and its share of three PRMTs.
-  // Packed words (and the norm) of this thread's part of a row, fetched one tile ahead of their use.
-  uint32_t nw[BMAX + 1], nsw = 0;
-  float nnorm = 0.f;
-  auto fetch = [&](int64_t tile) {
-    const int64_t n = tile * kUTile + trow;
-    const bool live = tile < n_tiles && n < a.n_vec;
-    const int64_t row = live ? map_row(a.rows, n) : 0;
-#pragma unroll
-    for (int q = 0; q < BMAX; ++q) nw[q] = (live && q < bits_c) ? __ldg(codes + row * row_words + word_off + q) : 0u;
-    nw[BMAX] = 0u;
-    if (SIGNS) nsw = live ? __ldg(signs + row * (kRD / 32) + blk) : 0u;
-    nnorm = live ? __ldg(a.norms + row) : 0.f;
-  };
-  auto decode_table = [&](auto bits_tag, int bf) {    // table-driven decode at the bit width of this thread's table
-    constexpr int BW = decltype(bits_tag)::value;
-    const uint2* tab = split_s[cls];
-    const uint32_t sx = nsw ^ smask;                  // bit c: add (1) or subtract (0) qjl_scale
-#pragma unroll
-    for (int c8 = 0; c8 < 4; ++c8) {
-      uint32_t packed[3][4];
-#pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        uint2 e[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int c = 8 * c8 + 2 * p + h;
-          const int bit = BW * c, wi = bit >> 5, sh = bit & 31;
-          uint32_t idx = nw[wi] >> sh;
-          if (sh + BW > 32) idx |= nw[wi + 1] << (32 - sh);
-          idx &= (1u << BW) - 1u;
-          if (SIGNS) idx |= (c >= BW ? (sx >> (c - BW)) : (sx << (BW - c))) & (1u << BW);
-          e[h] = tab[idx];
-        }
-        packed[0][p] = __byte_perm(e[0].x, e[1].x, 0x5410);
-        packed[1][p] = __byte_perm(e[0].x, e[1].x, 0x7632);
-        packed[2][p] = __byte_perm(e[0].y, e[1].y, 0x5410);
-      }
-      const uint32_t off = umma::sw128_offset(trow, 32 * blk + 8 * c8, 128);
-#pragma unroll
-      for (int t = 0; t < NT; ++t)
-        *reinterpret_cast<uint4*>(s.a[bf][t] + off) = make_uint4(packed[t][0], packed[t][1], packed[t][2], packed[t][3]);
-    }
-  };
-  auto decode_tile = [&](int64_t tile, int bf) {
-    const int64_t n = tile * kUTile + trow;
-    const bool live = n < a.n_vec;
-    if (MIXED) {
-      if (cls) decode_table(std::integral_constant<int, (MIXED ? BITS1 : BITS)>{}, bf);
-      else decode_table(std::integral_constant<int, BITS>{}, bf);
-      return;
-    }
-    uint32_t w[BITS + 1];
-#pragma unroll
-    for (int q = 0; q <= BITS; ++q) w[q] = nw[q];
-    const uint32_t sw = nsw;
-    if (table_ok) {
-      decode_table(std::integral_constant<int, BITS>{}, bf);
-      return;
-    }
-#pragma unroll
-    for (int c8 = 0; c8 < 4; ++c8) {
-      uint32_t packed[NT][4];
-#pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        float v[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int c = 8 * c8 + 2 * p + h;
-          const int bit = BITS * c, wi = bit >> 5, sh = bit & 31;
-          uint32_t code = w[wi] >> sh;
-          if (sh + BITS > 32) code |= w[wi + 1] << (32 - sh);
-          code &= (1u << BITS) - 1u;
-          float x = cent_s[0][code];
-          if (SIGNS) {
-            const float q = qs_s[32 * blk + c];
-            x += ((sw >> c) & 1u) ? q : -q;
-          }
-          v[h] = live ? x : 0.f;
-        }
-        const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[0], v[1]);
-        packed[0][p] = *reinterpret_cast<const uint32_t*>(&h2);
-        const float r0 = v[0] - __bfloat162float(h2.x), r1 = v[1] - __bfloat162float(h2.y);
-        const __nv_bfloat162 m2 = __floats2bfloat162_rn(r0, r1);
-        packed[1][p] = *reinterpret_cast<const uint32_t*>(&m2);
-        if (NT == 3) {
-          const __nv_bfloat162 l2 = __floats2bfloat162_rn(r0 - __bfloat162float(m2.x), r1 - __bfloat162float(m2.y));
-          packed[NT - 1][p] = *reinterpret_cast<const uint32_t*>(&l2);
-        }
-      }
-      const uint32_t off = umma::sw128_offset(trow, 32 * blk + 8 * c8, 128);
-#pragma unroll
-      for (int t = 0; t < NT; ++t)
-        *reinterpret_cast<uint4*>(s.a[bf][t] + off) = make_uint4(packed[t][0], packed[t][1], packed[t][2], packed[t][3]);
-    }
-  };
-
-  // Thread 0: products smallest first, then the completion arrival.
-  auto issue_mmas = [&](int bf, int acc_buf) {
-    constexpr uint32_t idesc = umma::instr_desc(umma::kFmtBF16, 128, 128);
-    const uint32_t d = tmem_base + acc_buf * 128;
-    constexpr int n_prod = NT == 2 ? 4 : 6;
-    constexpr int pa2[4] = {1, 0, 1, 0}, pb2[4] = {1, 1, 0, 0};
-    constexpr int pa3[6] = {1, 2, 0, 1, 0, 0}, pb3[6] = {1, 0, 2, 0, 1, 0};
-    bool acc = false;
-#pragma unroll
-    for (int pr = 0; pr < n_prod; ++pr) {
-      const int ta = NT == 2 ? pa2[pr] : pa3[pr], tb = NT == 2 ? pb2[pr] : pb3[pr];
-      const uint32_t a_addr = umma::smem_u32(s.a[bf][ta]), b_addr = umma::smem_u32(s.b[tb]);
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint32_t off = (ks >> 2) * (128 * 128) + (ks & 3) * 32;
-        umma::mma_f16(d, umma::smem_desc_sw128(a_addr + off), umma::smem_desc_sw128(b_addr + off), idesc, acc);
-        acc = true;
-      }
-    }
-    umma::commit(&s.mbar[acc_buf]);
-  };
-
-  // Scale this thread's 32 outputs of row trow by the norm and store them.
-  auto epilogue = [&](int64_t tile, int acc_buf, float nrm, bool use_tmem) {
-    const int64_t n = tile * kUTile + trow;
-    const bool live = n < a.n_vec;
-    const int64_t row = live ? map_row(a.rows, n) : 0;
-    uint32_t v[32];
-    if (use_tmem) {
-      umma::tmem_ld32(tmem_base + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + acc_buf * 128 + 32 * blk, v);
-    } else if (live) {                                   // tensor core timed out: fp32 chain from the packed row
-      float vrow[kRD];
-      for (int i = 0; i < kRD; ++i) {                    // i = stream position; channel = perm[i] when mixed
-        const int ci = i >= n_out ? 1 : 0;
-        const int bit = ci ? n_out * BITS + (i - n_out) * BITS1 : i * BITS;
-        const uint32_t code = read_field(a.codes + row * (row_words * 4), bit, ci ? BITS1 : BITS, row_words * 4);
-        float x = cent_s[ci][code];
-        if (SIGNS) x += ((signs[row * (kRD / 32) + (i >> 5)] >> (i & 31)) & 1u) ? qs_s[i] : -qs_s[i];
-        vrow[MIXED ? perm_s[i] : i] = x;
-      }
-      for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(decompress_chain(vrow, a.Pi, 32 * blk + c));
-    }
-    if (a.out_dtype == QKV_F32) {
-      // A thread holds 32 consecutive outputs of ONE row; stored as they are, a warp instruction would touch 32
-      // rows with 16 bytes each.  Sixteen columns at a time go through a 2 KB per-warp buffer (16-byte chunk q
-      // of row r at position q ^ ((r >> 1) & 3): conflict-free both ways) and come back as 8 rows x 64
-      // contiguous bytes per instruction.
-      unsigned char* st = s.stage + warp * 2048;
-      const int64_t n0 = tile * kUTile + 32 * (warp & 3);
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int c = 16 * hf + 4 * q;
-          *reinterpret_cast<float4*>(st + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) =
-              make_float4(__uint_as_float(v[c]) * nrm, __uint_as_float(v[c + 1]) * nrm,
-                          __uint_as_float(v[c + 2]) * nrm, __uint_as_float(v[c + 3]) * nrm);
-        }
-        __syncwarp();
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int r = 8 * j + (lane >> 2), q = lane & 3;
-          const float4 o = *reinterpret_cast<const float4*>(st + r * 64 + ((q ^ ((r >> 1) & 3)) << 4));
-          if (n0 + r < a.n_vec)
-            *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + (n0 + r) * a.out_pitch + 32 * blk + 16 * hf +
-                                       4 * q) = o;
-        }
-        __syncwarp();
-      }
-    } else if (a.out_dtype == QKV_BF16) {
-      // same transposition with 2-byte outputs: the thread's 32 values are 64 bytes, one pass
-      unsigned char* st = s.stage + warp * 2048;
-      const int64_t n0 = tile * kUTile + 32 * (warp & 3);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint32_t pk[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 2 * e]) * nrm,
-                                                          __uint_as_float(v[8 * q + 2 * e + 1]) * nrm);
-          pk[e] = *reinterpret_cast<const uint32_t*>(&b2);
-        }
-        *reinterpret_cast<uint4*>(st + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-      }
-      __syncwarp();
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int r = 8 * j + (lane >> 2), q = lane & 3;
-        const uint4 o = *reinterpret_cast<const uint4*>(st + r * 64 + ((q ^ ((r >> 1) & 3)) << 4));
-        if (n0 + r < a.n_vec)
-          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.out) + (n0 + r) * a.out_pitch + 32 * blk + 8 * q) = o;
-      }
-      __syncwarp();
-    } else if (live) {
-#pragma unroll
-      for (int c = 0; c < 32; ++c)
-        store_float(a.out, a.out_dtype, n * a.out_pitch + 32 * blk + c, __uint_as_float(v[c]) * nrm);
-    }
-  };
-
-  // ---- pipeline ---------------------------------------------------------------------------------------------
-  // two A buffers: decode(i); issue(i); wait(i-1); epilogue(i-1)     (decode overlaps the MMAs of tile i-1)
-  // one A buffer : wait(i-1); decode(i); issue(i); epilogue(i-1)     (the MMAs of tile i-1 still read A)
-  uint32_t phase[2] = {0u, 0u};
-  int64_t prev_tile = -1;
-  int i = 0;
-  bool prev_ok = true;
-  float norm_cur = 0.f, norm_prev = 0.f;
-  fetch(blockIdx.x);
-  for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++i) {
-    const int bf = i % NBUF, acc_buf = i & 1;
-    auto wait_prev = [&]() {
-      if (prev_tile < 0) return;
-      prev_ok = *s.dead == 0;
-      if (prev_ok) {
-        prev_ok = umma::mbar_wait(&s.mbar[acc_buf ^ 1], phase[acc_buf ^ 1]);
-        phase[acc_buf ^ 1] ^= 1u;
-        if (!prev_ok) { *s.dead = 1; atomicAdd(&g_umma_timeouts, 1u); }
-      }
-      umma::fence_after_sync();
-    };
-    if (NBUF == 1) wait_prev();
-    decode_tile(tile, bf);
-    norm_prev = norm_cur;
-    norm_cur = nnorm;
-    fetch(tile + gridDim.x);              // the next tile's words travel while this one is multiplied and stored
-    umma::fence_smem_to_async();
-    umma::fence_before_sync();
-    __syncthreads();                      // A(i) written; epilogue(i-2) has left accumulator acc_buf
-    if (tid == 0 && *s.dead == 0) {
-      umma::fence_after_sync();
-      issue_mmas(bf, acc_buf);
-    }
-    if (NBUF == 2) wait_prev();
-    if (prev_tile >= 0) epilogue(prev_tile, acc_buf ^ 1, norm_prev, prev_ok);
-    prev_tile = tile;
-  }
-  if (prev_tile >= 0) {
-    const int acc_buf = (i - 1) & 1;
-    bool ok = *s.dead == 0;
-    if (ok) {
-      ok = umma::mbar_wait(&s.mbar[acc_buf], phase[acc_buf]);
-      if (!ok) { *s.dead = 1; atomicAdd(&g_umma_timeouts, 1u); }
-    }
-    umma::fence_after_sync();
-    epilogue(prev_tile, acc_buf, norm_cur, ok);
-  }
-  umma::fence_before_sync();
-  __syncthreads();
-  if (warp == 0) umma::tmem_dealloc(tmem_base, kUTmemCols);
-}
-
-bool decompress_umma_ok(const DecompressArgs& a) {
-  const uintptr_t al = reinterpret_cast<uintptr_t>(a.codes) | reinterpret_cast<uintptr_t>(a.out) |
-                       (a.signs ? reinterpret_cast<uintptr_t>(a.signs) : 0);
-  if (a.mode == MODE_MIXED) {   // the common width pairs; rows are whole 4-byte words (36 B at 32 x 3 + 96 x 2 bits)
-    const bool pair = (a.bits0 == 3 && a.bits1 == 2) || (a.bits0 == 4 && a.bits1 == 3) || (a.bits0 == 4 && a.bits1 == 2);
-    return pair && a.d == kRD && a.packed && a.n_vec >= 1024 && (a.out_pitch & 7) == 0 &&
-           ((reinterpret_cast<uintptr_t>(a.out) & 15u) | (reinterpret_cast<uintptr_t>(a.codes) & 3u)) == 0;
-  }
-  return a.d == kRD && a.packed && a.n_vec >= 1024 && (a.out_pitch & 7) == 0 &&
-         (al & 15u) == 0;
-}
-
-template <int BITS, bool SIGNS, int NT>
-static int launch_decompress_umma_t(const DecompressArgs& a, cudaStream_t st) {
-  constexpr size_t smem = dec_smem_bytes<NT>();
-  if (cudaFuncSetAttribute(decompress_umma_kernel<BITS, SIGNS, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(smem)) != cudaSuccess)
-    return QKV_ELAUNCH;
-  const int64_t tiles = (a.n_vec + kUTile - 1) / kUTile;
-  const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
-  decompress_umma_kernel<BITS, SIGNS, NT><<<grid, kUThreads, smem, st>>>(a);
-  return check_launch();
-}
-
-template <int BITS>
-static int launch_decompress_umma_b(const DecompressArgs& a, cudaStream_t st) {
-  const bool exact = a.out_dtype == QKV_F32;
-  if (a.signs) return exact ? launch_decompress_umma_t<BITS, true, 3>(a, st) : launch_decompress_umma_t<BITS, true, 2>(a, st);
-  return exact ? launch_decompress_umma_t<BITS, false, 3>(a, st) : launch_decompress_umma_t<BITS, false, 2>(a, st);
-}
-
-template <int B0, int B1, int NT>
-static int launch_decompress_umma_mixed(const DecompressArgs& a, cudaStream_t st) {
-  constexpr size_t smem = dec_smem_bytes<NT>();
-  if (cudaFuncSetAttribute(decompress_umma_kernel<B0, false, NT, B1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(smem)) != cudaSuccess)
-    return QKV_ELAUNCH;
-  const int64_t tiles = (a.n_vec + kUTile - 1) / kUTile;
-  const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
-  decompress_umma_kernel<B0, false, NT, B1><<<grid, kUThreads, smem, st>>>(a);
-  return check_launch();
-}
-
-int launch_decompress_umma(const DecompressArgs& a, cudaStream_t st) {
-  if (a.mode == MODE_MIXED) {
-    const bool exact = a.out_dtype == QKV_F32;
-    if (a.bits0 == 3) return exact ? launch_decompress_umma_mixed<3, 2, 3>(a, st) : launch_decompress_umma_mixed<3, 2, 2>(a, st);
-    if (a.bits1 == 3) return exact ? launch_decompress_umma_mixed<4, 3, 3>(a, st) : launch_decompress_umma_mixed<4, 3, 2>(a, st);
-    return exact ? launch_decompress_umma_mixed<4, 2, 3>(a, st) : launch_decompress_umma_mixed<4, 2, 2>(a, st);
-  }
-  switch (a.bits0) {
-    case 1: return launch_decompress_umma_b<1>(a, st);
-    case 2: return launch_decompress_umma_b<2>(a, st);
-    case 3: return launch_decompress_umma_b<3>(a, st);
-    default: return launch_decompress_umma_b<4>(a, st);
-  }
-}
 
 }  // namespace qkv
