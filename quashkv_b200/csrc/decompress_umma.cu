@@ -38,10 +38,13 @@ __device__ unsigned int g_dec_umma_timeouts = 0;
 namespace {
 
 constexpr int kDTile = 128;                       // vectors per tile = MMA M
-constexpr int kDThreads = 512;                    // four threads per vector: 32 coordinates each
+constexpr int kDFirstWorker = 4;                  // warps 4 .. 11 decode and store; warp 0 issues the MMAs
+constexpr int kDWorkers = 256;                    // two worker threads per vector: 2 x 32 coordinates each
+constexpr int kDThreads = 32 * kDFirstWorker + kDWorkers;
 constexpr uint32_t kDPlaneBytes = 128 * 128 * 2;  // one fp16 operand tile (two 64-wide K blocks)
 constexpr uint32_t kDTmemCols = 256;
 constexpr uint32_t kDTableBytes = 32768;          // pair tables (mixed precision: two halves)
+constexpr int kDProducts = 3;                     // of m*m, m*h, h*m, h*h the last three: the first is below 2^-22
 constexpr int kDTopExp = 14;                      // operands are scaled to a largest magnitude in [2^13, 2^14)
 
 __host__ __device__ constexpr int ilog2(int v) { return v <= 1 ? 0 : 1 + ilog2(v >> 1); }
@@ -58,24 +61,23 @@ __host__ __device__ constexpr int pair_replicas() {
 }
 
 struct DecSmem {
-  unsigned char* a[2][2];   // A tiles [buffer][term h, m] (fp16, swizzled), 1024-byte aligned
-  unsigned char* b[2];      // Pi^T planes h, m
+  unsigned char* a;         // A tiles [buffer][term h, m] (fp16, swizzled), 1024-byte aligned, kDPlaneBytes each
+  unsigned char* b;         // Pi^T planes h, m
   unsigned char* tab;       // pair tables
-  uint64_t* mbar;           // [2]
+  uint64_t* mbar;           // [4]: accumulator 0 / 1 complete, A buffer 0 / 1 written
   uint32_t* tmem_slot;
   int* dead;
 };
 
-constexpr size_t dec_smem_bytes() { return 1024 + 6 * kDPlaneBytes + kDTableBytes + 2 * 8 + 16; }
+constexpr size_t dec_smem_bytes() { return 1024 + 6 * kDPlaneBytes + kDTableBytes + 4 * 8 + 16; }
 
 __device__ __forceinline__ DecSmem carve_dec(unsigned char* raw) {
   DecSmem s;
   unsigned char* p = raw + ((1024u - (umma::smem_u32(raw) & 1023u)) & 1023u);
-  for (int bf = 0; bf < 2; ++bf)
-    for (int t = 0; t < 2; ++t) { s.a[bf][t] = p; p += kDPlaneBytes; }
-  for (int t = 0; t < 2; ++t) { s.b[t] = p; p += kDPlaneBytes; }
+  s.a = p; p += 4 * kDPlaneBytes;
+  s.b = p; p += 2 * kDPlaneBytes;
   s.tab = p; p += kDTableBytes;
-  s.mbar = reinterpret_cast<uint64_t*>(p); p += 16;
+  s.mbar = reinterpret_cast<uint64_t*>(p); p += 32;
   s.tmem_slot = reinterpret_cast<uint32_t*>(p);
   s.dead = reinterpret_cast<int*>(p + 4);
   return s;
@@ -85,6 +87,11 @@ __device__ __forceinline__ DecSmem carve_dec(unsigned char* raw) {
 __device__ __forceinline__ void split2h(float x, __half& h, __half& m) {
   h = __float2half_rn(x);
   m = __float2half_rn(x - __half2float(h));
+}
+
+// One arrival (release at CTA scope) on a CTA-local barrier; the thread does not wait.
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_u32(bar)) : "memory");
 }
 
 __device__ __forceinline__ uint32_t pack_h(__half lo, __half hi) {
@@ -108,9 +115,18 @@ __device__ __noinline__ float decompress_chain(const float* vrow, const float* P
 }
 
 // BITS1 != 0: mixed precision (no sign term).  The K dimension runs in STREAM order (outlier channels first):
-// A column k' is stream position k' and B row k' is Pi[perm[k']], so each thread's 32 coordinates belong to
+// A column k' is stream position k' and B row k' is Pi[perm[k']], so each block of 32 coordinates belongs to
 // one table; needs the outlier count to be a multiple of 32, otherwise the CTA returns and the CUDA-core
 // kernel launched behind it does the work (same device-side test, inverted).
+//
+// Warps: 0 = the issuing warp (its first lane waits for "A(i) is written", issues the 32 MMAs of tile i and
+// commits them to the accumulator's barrier), 1-3 take part in the set-up only, 4-11 = workers.  Worker warp w
+// owns rows 32 (w & 3) .. + 31 (the tensor-memory lanes its warp may read) and columns 64 ((w - 4) >> 2) .. + 63
+// as two blocks of 32; a worker thread decodes and later stores 2 x 32 coordinates of ONE row.  Workers never wait
+// for each other inside the loop: they arrive on the "written" barrier and go on to the epilogue of the previous
+// tile, so the decode of some warps overlaps the stores of others.  (The thread that issues the MMAs is blocked
+// for about as long as they execute, the queue being short; as a worker it held the whole CTA back by that time
+// at the next barrier.)
 template <int BITS, bool SIGNS, int BITS1 = 0>
 __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(DecompressArgs a) {
   constexpr bool MIXED = BITS1 != 0;
@@ -124,7 +140,9 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
   __shared__ uint8_t perm_s[kRD];
   const DecSmem s = carve_dec(smem_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int trow = 32 * (warp & 3) + lane, blk = warp >> 2;
+  const bool worker = warp >= kDFirstWorker;
+  const int trow = 32 * (warp & 3) + lane;
+  const int blk0 = worker ? 2 * ((warp - kDFirstWorker) >> 2) : 0;     // first of this thread's two column blocks
   const uint32_t* codes = reinterpret_cast<const uint32_t*>(a.codes);
   const uint32_t* signs = reinterpret_cast<const uint32_t*>(a.signs);
 
@@ -152,9 +170,14 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
   }
   const int m_out = n_out >> 5;
   const int row_words = MIXED ? m_out * BITS + (4 - m_out) * BITS1 : 4 * BITS;
-  const int cls = blk >= m_out ? 1 : 0;             // table of this thread's 32 K positions
-  const int word_off = cls ? m_out * BITS + (blk - m_out) * BITS1 : blk * BITS;
-  const int bits_c = cls ? BITS1 : BITS;
+  int cls[2], word_off[2], bits_c[2];               // per column block: table, first packed word, bit width
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int blk = blk0 + u;
+    cls[u] = blk >= m_out ? 1 : 0;
+    word_off[u] = cls[u] ? m_out * BITS + (blk - m_out) * BITS1 : blk * BITS;
+    bits_c[u] = cls[u] ? BITS1 : BITS;
+  }
 
   // ---- one-time setup: small tables, operand scales, Pi^T planes, pair tables, barriers, TMEM --------------
   if (tid < 3) red_s[tid] = 0u;
@@ -199,8 +222,8 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
     __half h, m;
     split2h(a.Pi[(MIXED ? perm_s[i] : i) * kRD + j] * scale_b, h, m);
     const uint32_t off = umma::sw128_offset(j, i, 128);
-    *reinterpret_cast<__half*>(s.b[0] + off) = h;
-    *reinterpret_cast<__half*>(s.b[1] + off) = m;
+    *reinterpret_cast<__half*>(s.b + off) = h;
+    *reinterpret_cast<__half*>(s.b + kDPlaneBytes + off) = m;
   }
   auto build_pairs = [&](auto bw_tag, auto rep_tag, uint2* tab, const float* cent) {
     constexpr int BW = decltype(bw_tag)::value, R = decltype(rep_tag)::value;
@@ -224,12 +247,19 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
   build_pairs(std::integral_constant<int, BITS>{}, std::integral_constant<int, R0>{}, tab0, cent_s[0]);
   if (MIXED)
     build_pairs(std::integral_constant<int, (MIXED ? BITS1 : BITS)>{}, std::integral_constant<int, R1>{}, tab1, cent_s[1]);
-  const unsigned char* const tabl = cls ? reinterpret_cast<const unsigned char*>(tab1 + (lane & (R1 - 1)))
-                                        : reinterpret_cast<const unsigned char*>(tab0 + (lane & (R0 - 1)));
-  const uint32_t smask = SIGNS ? smask_s[blk] : 0u;
+  const unsigned char* tabl[2];
+  uint32_t smask[2];
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    tabl[u] = cls[u] ? reinterpret_cast<const unsigned char*>(tab1 + (lane & (R1 - 1)))
+                     : reinterpret_cast<const unsigned char*>(tab0 + (lane & (R0 - 1)));
+    smask[u] = SIGNS ? smask_s[blk0 + u] : 0u;
+  }
   if (tid == 0) {
-    umma::mbar_init(&s.mbar[0], 1);
+    umma::mbar_init(&s.mbar[0], 1);                  // accumulator 0 / 1 complete (one commit)
     umma::mbar_init(&s.mbar[1], 1);
+    umma::mbar_init(&s.mbar[2], kDWorkers);          // A buffer 0 / 1 written (every worker thread)
+    umma::mbar_init(&s.mbar[3], kDWorkers);
     *s.dead = 0;
   }
   if (warp == 0) umma::tmem_alloc(s.tmem_slot, kDTmemCols);
@@ -242,239 +272,271 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
   const bool one_segment = a.rows.seg_len >= a.n_vec;           // rows are n + seg_off: no division
   auto row_of = [&](int64_t n) -> int64_t { return one_segment ? n + a.rows.seg_off : map_row(a.rows, n); };
 
-  // Packed words (and the norm) of this thread's part of a row, fetched one tile ahead of their use.
-  uint32_t nw[BMAX + 1], nsw = 0;
-  float nnorm = 0.f;
-  auto fetch = [&](int64_t tile) {
-    const int64_t n = tile * kDTile + trow;
-    const bool live = tile < n_tiles && n < a.n_vec;
-    const int64_t row = live ? row_of(n) : 0;
-#pragma unroll
-    for (int q = 0; q < BMAX; ++q) nw[q] = (live && q < bits_c) ? __ldg(codes + row * row_words + word_off + q) : 0u;
-    nw[BMAX] = 0u;
-    if (SIGNS) nsw = live ? __ldg(signs + row * (kRD / 32) + blk) : 0u;
-    nnorm = live ? __ldg(a.norms + row) : 0.f;
-  };
-
-  // Offset of this thread's 16-byte chunk q (coordinates 8 q .. 8 q + 7 of its 32) of row `row` inside a plane.
-  auto chunk_off = [&](int row, int q) -> uint32_t {
-    return static_cast<uint32_t>((blk >> 1) * (128 * 128) + row * 128 + (((4 * (blk & 1) + q) ^ (row & 7)) << 4));
-  };
-
-  // Decode this thread's 32 coordinates of row trow into the two operand planes of A[bf] through the pair table.
-  auto decode_table = [&](auto bw_tag, auto rep_tag, int bf) {
-    constexpr int BW = decltype(bw_tag)::value, R = decltype(rep_tag)::value;
-    constexpr int L = 3 + ilog2(R);                   // an entry index becomes a byte offset by << L
-    constexpr uint32_t FM = ((1u << (2 * BW)) - 1u) << L, SM = 3u << (2 * BW + L);
-    const uint32_t sx = nsw ^ smask;                  // bit c: add (1) or subtract (0) qjl_scale
-#pragma unroll
-    for (int c8 = 0; c8 < 4; ++c8) {
-      uint2 e[4];
-#pragma unroll
-      for (int p4 = 0; p4 < 4; ++p4) {
-        const int p = 4 * c8 + p4, bit = 2 * BW * p, wi = bit >> 5, sh = bit & 31;
-        uint32_t off;
-        if (sh + 2 * BW > 32) off = __funnelshift_r(nw[wi], nw[wi + 1], sh - L);
-        else off = sh >= L ? nw[wi] >> (sh - L) : nw[wi] << (L - sh);
-        off &= FM;
-        if (SIGNS) {
-          const int ss = 2 * p - (2 * BW + L);        // the pair's two sign bits go right above the codes
-          off |= (ss >= 0 ? sx >> ss : sx << -ss) & SM;
+  // ---- warp 0: per tile, wait until every worker has written A(i), then four products, smallest first --------
+  if (warp == 0) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma::instr_desc(umma::kFmtF16, 128, 128);
+      // terms of A and of B per product: m*m (left out with three products), m*h, h*m, h*h
+      constexpr int pa[4] = {1, 1, 0, 0}, pb[4] = {1, 0, 1, 0};
+      uint32_t full_phase[2] = {0u, 0u};
+      int i = 0;
+      for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++i) {
+        const int bf = i & 1;
+        if (*reinterpret_cast<volatile int*>(s.dead)) break;
+        if (!umma::mbar_wait(&s.mbar[2 + bf], full_phase[bf])) {     // a worker gave up (or never came)
+          *reinterpret_cast<volatile int*>(s.dead) = 1;
+          atomicAdd(&g_dec_umma_timeouts, 1u);
+          break;
         }
-        e[p4] = *reinterpret_cast<const uint2*>(tabl + off);
-      }
-      const uint32_t o = chunk_off(trow, c8);
-      *reinterpret_cast<uint4*>(s.a[bf][0] + o) = make_uint4(e[0].x, e[1].x, e[2].x, e[3].x);
-      *reinterpret_cast<uint4*>(s.a[bf][1] + o) = make_uint4(e[0].y, e[1].y, e[2].y, e[3].y);
-    }
-  };
-  auto decode_tile = [&](int bf) {
-    if (MIXED) {
-      if (cls) decode_table(std::integral_constant<int, (MIXED ? BITS1 : BITS)>{}, std::integral_constant<int, R1>{}, bf);
-      else decode_table(std::integral_constant<int, BITS>{}, std::integral_constant<int, R0>{}, bf);
-      return;
-    }
-    if (table_ok) {
-      decode_table(std::integral_constant<int, BITS>{}, std::integral_constant<int, R0>{}, bf);
-      return;
-    }
-    // S with other magnitudes than 1: every coordinate by arithmetic
+        full_phase[bf] ^= 1u;
+        if (*reinterpret_cast<volatile int*>(s.dead)) break;
+        umma::fence_after_sync();
+        const uint32_t d = tmem_base + bf * 128;
+        bool acc = false;
 #pragma unroll
-    for (int c8 = 0; c8 < 4; ++c8) {
-      uint32_t packed[2][4];
+        for (int pr = 4 - kDProducts; pr < 4; ++pr) {
+          const uint32_t a_addr = umma::smem_u32(s.a) + (2 * bf + pa[pr]) * kDPlaneBytes;
+          const uint32_t b_addr = umma::smem_u32(s.b) + pb[pr] * kDPlaneBytes;
 #pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        float v[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int c = 8 * c8 + 2 * p + h;
-          const int bit = BITS * c, wi = bit >> 5, sh = bit & 31;
-          uint32_t code = nw[wi] >> sh;
-          if (sh + BITS > 32) code |= nw[wi + 1] << (32 - sh);
-          code &= (1u << BITS) - 1u;
-          float x = cent_s[0][code];
-          if (SIGNS) {
-            const float q = qs_s[32 * blk + c];
-            x += ((nsw >> c) & 1u) ? q : -q;
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t off = (ks >> 2) * (128 * 128) + (ks & 3) * 32;
+            umma::mma_f16(d, umma::smem_desc_sw128(a_addr + off), umma::smem_desc_sw128(b_addr + off), idesc, acc);
+            acc = true;
           }
-          v[h] = x * scale_a;
         }
-        __half h0, m0, h1, m1;
-        split2h(v[0], h0, m0);
-        split2h(v[1], h1, m1);
-        packed[0][p] = pack_h(h0, h1);
-        packed[1][p] = pack_h(m0, m1);
+        umma::commit(&s.mbar[bf]);
       }
-      const uint32_t o = chunk_off(trow, c8);
-#pragma unroll
-      for (int t = 0; t < 2; ++t)
-        *reinterpret_cast<uint4*>(s.a[bf][t] + o) = make_uint4(packed[t][0], packed[t][1], packed[t][2], packed[t][3]);
     }
-  };
+    __syncwarp();
+  }
 
-  // One thread: four products, smallest first, then the completion arrival.
-  auto issue_mmas = [&](int bf, int acc_buf) {
-    constexpr uint32_t idesc = umma::instr_desc(umma::kFmtF16, 128, 128);
-    const uint32_t d = tmem_base + acc_buf * 128;
-    constexpr int pa[4] = {1, 0, 1, 0}, pb[4] = {1, 1, 0, 0};
-    bool acc = false;
+  if (worker) {
+    // Packed words (and the norm) of this thread's part of a row, fetched one tile ahead of their use.
+    uint32_t nw[2][BMAX + 1], nsw[2] = {0u, 0u};
+    float nnorm = 0.f;
+    auto fetch = [&](int64_t tile) {
+      const int64_t n = tile * kDTile + trow;
+      const bool live = tile < n_tiles && n < a.n_vec;
+      const int64_t row = live ? row_of(n) : 0;
 #pragma unroll
-    for (int pr = 0; pr < 4; ++pr) {
-      const uint32_t a_addr = umma::smem_u32(s.a[bf][pa[pr]]), b_addr = umma::smem_u32(s.b[pb[pr]]);
+      for (int u = 0; u < 2; ++u) {
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint32_t off = (ks >> 2) * (128 * 128) + (ks & 3) * 32;
-        umma::mma_f16(d, umma::smem_desc_sw128(a_addr + off), umma::smem_desc_sw128(b_addr + off), idesc, acc);
-        acc = true;
+        for (int q = 0; q < BMAX; ++q)
+          nw[u][q] = (live && q < bits_c[u]) ? __ldg(codes + row * row_words + word_off[u] + q) : 0u;
+        nw[u][BMAX] = 0u;
+        if (SIGNS) nsw[u] = live ? __ldg(signs + row * (kRD / 32) + blk0 + u) : 0u;
       }
-    }
-    umma::commit(&s.mbar[acc_buf]);
-  };
+      nnorm = live ? __ldg(a.norms + row) : 0.f;
+    };
 
-  // Scale this thread's 32 outputs of row trow by the norm and store them; the transposition goes through this
-  // warp's own chunks of the idle A buffer `bf` (plane 0, and plane 1 for the second half of fp32 outputs).
-  auto epilogue = [&](int64_t tile, int acc_buf, int bf, float nrm, bool use_tmem) {
-    const int64_t n = tile * kDTile + trow;
-    const bool live = n < a.n_vec;
-    uint32_t v[32];
-    float f = nrm;
-    if (use_tmem) {
-      umma::tmem_ld32(tmem_base + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + acc_buf * 128 + 32 * blk, v);
-      f = nrm * descale;
-      if (!(fabsf(f) >= 1e-30f && fabsf(f) <= 1e30f)) {  // the product would lose bits: take the power of two first
+    // Offset of the 16-byte chunk q (coordinates 8 q .. 8 q + 7) of column block blk, row `row`, inside a plane.
+    auto chunk_off = [&](int blk, int row, int q) -> uint32_t {
+      return static_cast<uint32_t>((blk >> 1) * (128 * 128) + row * 128 + (((4 * (blk & 1) + q) ^ (row & 7)) << 4));
+    };
+
+    // Decode block u (32 coordinates of row trow) into the two operand planes of A[bf] through the pair table.
+    auto decode_table = [&](auto bw_tag, auto rep_tag, int u, int bf) {
+      constexpr int BW = decltype(bw_tag)::value, R = decltype(rep_tag)::value;
+      constexpr int L = 3 + ilog2(R);                   // an entry index becomes a byte offset by << L
+      constexpr uint32_t FM = ((1u << (2 * BW)) - 1u) << L, SM = 3u << (2 * BW + L);
+      const uint32_t sx = nsw[u] ^ smask[u];            // bit c: add (1) or subtract (0) qjl_scale
 #pragma unroll
-        for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * descale);
-        f = nrm;
+      for (int c8 = 0; c8 < 4; ++c8) {
+        uint2 e[4];
+#pragma unroll
+        for (int p4 = 0; p4 < 4; ++p4) {
+          const int p = 4 * c8 + p4, bit = 2 * BW * p, wi = bit >> 5, sh = bit & 31;
+          uint32_t off;
+          if (sh + 2 * BW > 32) off = __funnelshift_r(nw[u][wi], nw[u][wi + 1], sh - L);
+          else off = sh >= L ? nw[u][wi] >> (sh - L) : nw[u][wi] << (L - sh);
+          off &= FM;
+          if (SIGNS) {
+            const int ss = 2 * p - (2 * BW + L);        // the pair's two sign bits go right above the codes
+            off |= (ss >= 0 ? sx >> ss : sx << -ss) & SM;
+          }
+          e[p4] = *reinterpret_cast<const uint2*>(tabl[u] + off);
+        }
+        const uint32_t o = chunk_off(blk0 + u, trow, c8);
+        unsigned char* const ap = s.a + 2 * bf * kDPlaneBytes + o;
+        *reinterpret_cast<uint4*>(ap) = make_uint4(e[0].x, e[1].x, e[2].x, e[3].x);
+        *reinterpret_cast<uint4*>(ap + kDPlaneBytes) = make_uint4(e[0].y, e[1].y, e[2].y, e[3].y);
       }
-    } else if (live) {                                   // tensor core timed out: fp32 chain from the packed row
-      const int64_t row = row_of(n);
-      float vrow[kRD];
-      for (int i = 0; i < kRD; ++i) {                    // i = stream position; channel = perm[i] when mixed
-        const int ci = i >= n_out ? 1 : 0;
-        const int bit = ci ? n_out * BITS + (i - n_out) * BITS1 : i * BITS;
-        const uint32_t code = read_field(a.codes + row * (row_words * 4), bit, ci ? BITS1 : BITS, row_words * 4);
-        float x = cent_s[ci][code];
-        if (SIGNS) x += ((signs[row * (kRD / 32) + (i >> 5)] >> (i & 31)) & 1u) ? qs_s[i] : -qs_s[i];
-        vrow[MIXED ? perm_s[i] : i] = x;
+    };
+    auto decode_block = [&](int u, int bf) {
+      if (MIXED) {
+        if (cls[u]) decode_table(std::integral_constant<int, (MIXED ? BITS1 : BITS)>{}, std::integral_constant<int, R1>{}, u, bf);
+        else decode_table(std::integral_constant<int, BITS>{}, std::integral_constant<int, R0>{}, u, bf);
+        return;
       }
-      for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(decompress_chain(vrow, a.Pi, 32 * blk + c));
-    }
-    const int64_t n0 = tile * kDTile + 32 * (warp & 3);
+      if (table_ok) {
+        decode_table(std::integral_constant<int, BITS>{}, std::integral_constant<int, R0>{}, u, bf);
+        return;
+      }
+      // S with other magnitudes than 1: every coordinate by arithmetic
+#pragma unroll
+      for (int c8 = 0; c8 < 4; ++c8) {
+        uint32_t packed[2][4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          float v[2];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int c = 8 * c8 + 2 * p + h;
+            const int bit = BITS * c, wi = bit >> 5, sh = bit & 31;
+            uint32_t code = nw[u][wi] >> sh;
+            if (sh + BITS > 32) code |= nw[u][wi + 1] << (32 - sh);
+            code &= (1u << BITS) - 1u;
+            float x = cent_s[0][code];
+            if (SIGNS) {
+              const float q = qs_s[32 * (blk0 + u) + c];
+              x += ((nsw[u] >> c) & 1u) ? q : -q;
+            }
+            v[h] = x * scale_a;
+          }
+          __half h0, m0, h1, m1;
+          split2h(v[0], h0, m0);
+          split2h(v[1], h1, m1);
+          packed[0][p] = pack_h(h0, h1);
+          packed[1][p] = pack_h(m0, m1);
+        }
+        const uint32_t o = chunk_off(blk0 + u, trow, c8);
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+          *reinterpret_cast<uint4*>(s.a + (2 * bf + t) * kDPlaneBytes + o) =
+              make_uint4(packed[t][0], packed[t][1], packed[t][2], packed[t][3]);
+      }
+    };
+
+    // Scale this thread's 2 x 32 outputs of row trow by the norm and store them.  A thread holds consecutive outputs
+    // of ONE row; stored as they are, a warp instruction would touch 32 rows.  They are transposed through this
+    // warp's own part of the idle A buffer `ab` (rows 32 (w & 3) .., the 128-byte lines of its K half; 16-byte
+    // chunk c of row r at position c ^ (r & 7): conflict-free both ways) and leave as 4 rows x 128 contiguous
+    // bytes per store instruction: whole lines, a quarter of the store wavefronts of 8 rows x 64 bytes.
     const int rbase = 32 * (warp & 3);
-    // read side of the transposition: lane -> (row 8 j + rr, chunk q); the two rows of a quarter warp differ in
-    // bit 2, so its eight chunks sit in eight different 16-byte columns of the swizzled layout
-    const int rr = ((lane >> 3) & 3) | (((lane >> 2) & 1) << 2), rq = lane & 3;
-    if (a.out_dtype == QKV_F32) {
+    const int rr = lane >> 3, rc = lane & 7;           // read side: row 4 j + rr, chunk rc
+    auto line_off = [&](int row, int c) -> uint32_t {
+      return static_cast<uint32_t>((blk0 >> 1) * (128 * 128) + row * 128 + ((c ^ (row & 7)) << 4));
+    };
+    auto epilogue = [&](int64_t tile, int ab, float nrm, bool use_tmem) {
+      const int64_t n = tile * kDTile + trow;
+      const bool live = n < a.n_vec;
+      uint32_t v[64];
+      float f = nrm;
+      if (use_tmem) {
+        umma::tmem_ld64(tmem_base + (static_cast<uint32_t>(rbase) << 16) + ab * 128 + 32 * blk0, v);
+        f = nrm * descale;
+        if (!(fabsf(f) >= 1e-30f && fabsf(f) <= 1e30f)) {  // the product would lose bits: take the power of two first
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        unsigned char* st = s.a[bf][hf];
+          for (int c = 0; c < 64; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * descale);
+          f = nrm;
+        }
+      } else if (live) {                                   // tensor core timed out: fp32 chain from the packed row
+        const int64_t row = row_of(n);
+        float vrow[kRD];
+        for (int i = 0; i < kRD; ++i) {                    // i = stream position; channel = perm[i] when mixed
+          const int ci = i >= n_out ? 1 : 0;
+          const int bit = ci ? n_out * BITS + (i - n_out) * BITS1 : i * BITS;
+          const uint32_t code = read_field(a.codes + row * (row_words * 4), bit, ci ? BITS1 : BITS, row_words * 4);
+          float x = cent_s[ci][code];
+          if (SIGNS) x += ((signs[row * (kRD / 32) + (i >> 5)] >> (i & 31)) & 1u) ? qs_s[i] : -qs_s[i];
+          vrow[MIXED ? perm_s[i] : i] = x;
+        }
+        for (int c = 0; c < 64; ++c) v[c] = __float_as_uint(decompress_chain(vrow, a.Pi, 32 * blk0 + c));
+      }
+      const int64_t n0 = tile * kDTile + rbase;
+      unsigned char* const st = s.a + 2 * ab * kDPlaneBytes;
+      if (a.out_dtype == QKV_F32) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int c = 16 * hf + 4 * q;
-          *reinterpret_cast<float4*>(st + chunk_off(trow, q)) =
-              make_float4(__uint_as_float(v[c]) * f, __uint_as_float(v[c + 1]) * f, __uint_as_float(v[c + 2]) * f,
-                          __uint_as_float(v[c + 3]) * f);
+        for (int u = 0; u < 2; ++u) {                      // block u through plane u: 32 rows x 128 bytes
+          unsigned char* const pl = st + u * kDPlaneBytes;
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<float4*>(pl + line_off(trow, c)) =
+                make_float4(__uint_as_float(v[32 * u + 4 * c]) * f, __uint_as_float(v[32 * u + 4 * c + 1]) * f,
+                            __uint_as_float(v[32 * u + 4 * c + 2]) * f, __uint_as_float(v[32 * u + 4 * c + 3]) * f);
         }
         __syncwarp();
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int r = 8 * j + rr;
-          const float4 o = *reinterpret_cast<const float4*>(st + chunk_off(rbase + r, rq));
+        for (int u = 0; u < 2; ++u) {
+          const unsigned char* const pl = st + u * kDPlaneBytes;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int r = 4 * j + rr;
+            const float4 o = *reinterpret_cast<const float4*>(pl + line_off(rbase + r, rc));
+            if (n0 + r < a.n_vec)
+              *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + (n0 + r) * a.out_pitch + 32 * (blk0 + u) +
+                                         4 * rc) = o;
+          }
+        }
+        __syncwarp();
+      } else if (a.out_dtype == QKV_BF16) {                // both blocks are 128 bytes of a row: one plane
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint32_t pk[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[8 * c + 2 * e]) * f,
+                                                            __uint_as_float(v[8 * c + 2 * e + 1]) * f);
+            pk[e] = *reinterpret_cast<const uint32_t*>(&b2);
+          }
+          *reinterpret_cast<uint4*>(st + line_off(trow, c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int r = 4 * j + rr;
+          const uint4 o = *reinterpret_cast<const uint4*>(st + line_off(rbase + r, rc));
           if (n0 + r < a.n_vec)
-            *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + (n0 + r) * a.out_pitch + 32 * blk + 16 * hf +
-                                       4 * rq) = o;
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.out) + (n0 + r) * a.out_pitch + 32 * blk0 + 8 * rc) = o;
         }
+        __syncwarp();
+      } else if (live) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c)
+          store_float(a.out, a.out_dtype, n * a.out_pitch + 32 * blk0 + c, __uint_as_float(v[c]) * f);
       }
-      __syncwarp();
-    } else if (a.out_dtype == QKV_BF16) {
-      unsigned char* st = s.a[bf][0];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint32_t pk[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 2 * e]) * f,
-                                                          __uint_as_float(v[8 * q + 2 * e + 1]) * f);
-          pk[e] = *reinterpret_cast<const uint32_t*>(&b2);
-        }
-        *reinterpret_cast<uint4*>(st + chunk_off(trow, q)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    };
+    // Wait for the products of the tile in accumulator `acc_buf`; false once the tensor core has been given up.
+    uint32_t phase[2] = {0u, 0u};
+    auto wait_products = [&](int acc_buf) -> bool {
+      bool ok = *reinterpret_cast<volatile int*>(s.dead) == 0;
+      if (ok) {
+        ok = umma::mbar_wait(&s.mbar[acc_buf], phase[acc_buf]);
+        phase[acc_buf] ^= 1u;
+        if (!ok) { *reinterpret_cast<volatile int*>(s.dead) = 1; atomicAdd(&g_dec_umma_timeouts, 1u); }
       }
-      __syncwarp();
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int r = 8 * j + rr;
-        const uint4 o = *reinterpret_cast<const uint4*>(st + chunk_off(rbase + r, rq));
-        if (n0 + r < a.n_vec)
-          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.out) + (n0 + r) * a.out_pitch + 32 * blk + 8 * rq) = o;
-      }
-      __syncwarp();
-    } else if (live) {
-#pragma unroll
-      for (int c = 0; c < 32; ++c)
-        store_float(a.out, a.out_dtype, n * a.out_pitch + 32 * blk + c, __uint_as_float(v[c]) * f);
-    }
-  };
-
-  // ---- pipeline: decode(i); issue(i); wait(i-1); epilogue(i-1)   (decode overlaps the MMAs of tile i-1) -----
-  uint32_t phase[2] = {0u, 0u};
-  int64_t prev_tile = -1;
-  int i = 0;
-  float norm_cur = 0.f, norm_prev = 0.f;
-  fetch(blockIdx.x);
-  for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++i) {
-    const int bf = i & 1;                   // A buffer and accumulator of tile i
-    decode_tile(bf);
-    norm_prev = norm_cur;
-    norm_cur = nnorm;
-    fetch(tile + gridDim.x);                // the next tile's words travel while this one is multiplied and stored
-    umma::fence_smem_to_async();
-    umma::fence_before_sync();
-    __syncthreads();                        // A(i) written; epilogue(i-2) has left accumulator bf
-    if (tid == 0 && *s.dead == 0) {
       umma::fence_after_sync();
-      issue_mmas(bf, bf);
+      return ok;
+    };
+
+    // ---- workers: decode(i); arrive; wait(i-1); epilogue(i-1)   (decode overlaps the MMAs of tile i-1) ---------
+    // A(i+1) goes into the buffer of tile i-1, whose products this thread has waited for; accumulator (i+1) & 1 is
+    // overwritten only after every worker has arrived for tile i+1, that is after its epilogue of tile i-1.
+    int64_t prev_tile = -1;
+    int i = 0;
+    float norm_cur = 0.f, norm_prev = 0.f;
+    fetch(blockIdx.x);
+    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++i) {
+      const int bf = i & 1;                   // A buffer and accumulator of tile i
+      decode_block(0, bf);
+      decode_block(1, bf);
+      norm_prev = norm_cur;
+      norm_cur = nnorm;
+      fetch(tile + gridDim.x);                // the next tile's words travel while this one is multiplied and stored
+      umma::fence_smem_to_async();
+      umma::fence_before_sync();
+      mbar_arrive(&s.mbar[2 + bf]);
+      if (prev_tile >= 0) {
+        const bool ok = wait_products(bf ^ 1);
+        epilogue(prev_tile, bf ^ 1, norm_prev, ok);
+      }
+      prev_tile = tile;
     }
     if (prev_tile >= 0) {
-      bool ok = *s.dead == 0;
-      if (ok) {
-        ok = umma::mbar_wait(&s.mbar[bf ^ 1], phase[bf ^ 1]);
-        phase[bf ^ 1] ^= 1u;
-        if (!ok) { *s.dead = 1; atomicAdd(&g_dec_umma_timeouts, 1u); }
-      }
-      umma::fence_after_sync();
-      epilogue(prev_tile, bf ^ 1, bf ^ 1, norm_prev, ok);
+      const int bf = (i - 1) & 1;
+      const bool ok = wait_products(bf);
+      epilogue(prev_tile, bf, norm_cur, ok);
     }
-    prev_tile = tile;
-  }
-  if (prev_tile >= 0) {
-    const int bf = (i - 1) & 1;
-    bool ok = *s.dead == 0;
-    if (ok) {
-      ok = umma::mbar_wait(&s.mbar[bf], phase[bf]);
-      if (!ok) { *s.dead = 1; atomicAdd(&g_dec_umma_timeouts, 1u); }
-    }
-    umma::fence_after_sync();
-    epilogue(prev_tile, bf, bf, norm_cur, ok);
   }
   umma::fence_before_sync();
   __syncthreads();
