@@ -318,13 +318,38 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
       const int64_t n = tile * kDTile + trow;
       const bool live = tile < n_tiles && n < a.n_vec;
       const int64_t row = live ? row_of(n) : 0;
+      if (MIXED) {
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < 2; ++u)
 #pragma unroll
-        for (int q = 0; q < BMAX; ++q)
-          nw[u][q] = (live && q < bits_c[u]) ? __ldg(codes + row * row_words + word_off[u] + q) : 0u;
-        nw[u][BMAX] = 0u;
-        if (SIGNS) nsw[u] = live ? __ldg(signs + row * (kRD / 32) + blk0 + u) : 0u;
+          for (int q = 0; q < BMAX; ++q)
+            nw[u][q] = (live && q < bits_c[u]) ? __ldg(codes + row * row_words + word_off[u] + q) : 0u;
+      } else {
+        // the two blocks are 2 BITS consecutive words: the widest loads their alignment allows (a warp's rows are
+        // 16 BITS bytes apart, so every load instruction touches the same lines whatever its width)
+        const uint32_t* src = codes + row * row_words + word_off[0];
+        uint32_t w[2 * BITS];
+        if (BITS % 2 == 0) {
+#pragma unroll
+          for (int q = 0; q < BITS / 2; ++q) {
+            const uint4 t = live ? __ldg(reinterpret_cast<const uint4*>(src) + q) : make_uint4(0u, 0u, 0u, 0u);
+            w[4 * q] = t.x; w[4 * q + 1] = t.y; w[4 * q + 2] = t.z; w[4 * q + 3] = t.w;
+          }
+        } else {
+#pragma unroll
+          for (int q = 0; q < BITS; ++q) {
+            const uint2 t = live ? __ldg(reinterpret_cast<const uint2*>(src) + q) : make_uint2(0u, 0u);
+            w[2 * q] = t.x; w[2 * q + 1] = t.y;
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < BITS; ++q) { nw[0][q] = w[q]; nw[1][q] = w[BITS + q]; }
+      }
+      nw[0][BMAX] = 0u;
+      nw[1][BMAX] = 0u;
+      if (SIGNS) {
+        const uint2 t = live ? __ldg(reinterpret_cast<const uint2*>(signs + row * (kRD / 32) + blk0)) : make_uint2(0u, 0u);
+        nsw[0] = t.x; nsw[1] = t.y;
       }
       nnorm = live ? __ldg(a.norms + row) : 0.f;
     };
