@@ -42,7 +42,8 @@ constexpr int kDFirstWorker = 4;                  // warps 4 .. 11 decode and st
 constexpr int kDWorkers = 256;                    // two worker threads per vector: 2 x 32 coordinates each
 constexpr int kDThreads = 32 * kDFirstWorker + kDWorkers;
 constexpr uint32_t kDPlaneBytes = 128 * 128 * 2;  // one fp16 operand tile (two 64-wide K blocks)
-constexpr uint32_t kDTmemCols = 256;
+constexpr uint32_t kDTmemCols = 512;              // accumulators [0, 256), A operands [256, 512)
+constexpr uint32_t kDTmemA = 256;                 // A[buffer][term]: 64 columns each (128 fp16 per row)
 constexpr uint32_t kDTableBytes = 32768;          // pair tables (mixed precision: two halves)
 constexpr int kDProducts = 3;                     // of m*m, m*h, h*m, h*h the last three: the first is below 2^-22
 constexpr int kDTopExp = 14;                      // operands are scaled to a largest magnitude in [2^13, 2^14)
@@ -295,12 +296,12 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
         bool acc = false;
 #pragma unroll
         for (int pr = 4 - kDProducts; pr < 4; ++pr) {
-          const uint32_t a_addr = umma::smem_u32(s.a) + (2 * bf + pa[pr]) * kDPlaneBytes;
+          const uint32_t a_tmem = tmem_base + kDTmemA + (2 * bf + pa[pr]) * 64;
           const uint32_t b_addr = umma::smem_u32(s.b) + pb[pr] * kDPlaneBytes;
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             const uint32_t off = (ks >> 2) * (128 * 128) + (ks & 3) * 32;
-            umma::mma_f16(d, umma::smem_desc_sw128(a_addr + off), umma::smem_desc_sw128(b_addr + off), idesc, acc);
+            umma::mma_f16_ts(d, a_tmem + 8 * ks, umma::smem_desc_sw128(b_addr + off), idesc, acc);
             acc = true;
           }
         }
@@ -354,10 +355,8 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
       nnorm = live ? __ldg(a.norms + row) : 0.f;
     };
 
-    // Offset of the 16-byte chunk q (coordinates 8 q .. 8 q + 7) of column block blk, row `row`, inside a plane.
-    auto chunk_off = [&](int blk, int row, int q) -> uint32_t {
-      return static_cast<uint32_t>((blk >> 1) * (128 * 128) + row * 128 + (((4 * (blk & 1) + q) ^ (row & 7)) << 4));
-    };
+    // this warp's lanes of the A operands in tensor memory (lane = row of the tile)
+    const uint32_t a_tmem_row = tmem_base + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + kDTmemA;
 
     // Decode block u (32 coordinates of row trow) into the two operand planes of A[bf] through the pair table.
     auto decode_table = [&](auto bw_tag, auto rep_tag, int u, int bf) {
@@ -365,27 +364,25 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
       constexpr int L = 3 + ilog2(R);                   // an entry index becomes a byte offset by << L
       constexpr uint32_t FM = ((1u << (2 * BW)) - 1u) << L, SM = 3u << (2 * BW + L);
       const uint32_t sx = nsw[u] ^ smask[u];            // bit c: add (1) or subtract (0) qjl_scale
+      uint32_t hcol[16], mcol[16];                      // a pair is one 32-bit column of each term
 #pragma unroll
-      for (int c8 = 0; c8 < 4; ++c8) {
-        uint2 e[4];
-#pragma unroll
-        for (int p4 = 0; p4 < 4; ++p4) {
-          const int p = 4 * c8 + p4, bit = 2 * BW * p, wi = bit >> 5, sh = bit & 31;
-          uint32_t off;
-          if (sh + 2 * BW > 32) off = __funnelshift_r(nw[u][wi], nw[u][wi + 1], sh - L);
-          else off = sh >= L ? nw[u][wi] >> (sh - L) : nw[u][wi] << (L - sh);
-          off &= FM;
-          if (SIGNS) {
-            const int ss = 2 * p - (2 * BW + L);        // the pair's two sign bits go right above the codes
-            off |= (ss >= 0 ? sx >> ss : sx << -ss) & SM;
-          }
-          e[p4] = *reinterpret_cast<const uint2*>(tabl[u] + off);
+      for (int p = 0; p < 16; ++p) {
+        const int bit = 2 * BW * p, wi = bit >> 5, sh = bit & 31;
+        uint32_t off;
+        if (sh + 2 * BW > 32) off = __funnelshift_r(nw[u][wi], nw[u][wi + 1], sh - L);
+        else off = sh >= L ? nw[u][wi] >> (sh - L) : nw[u][wi] << (L - sh);
+        off &= FM;
+        if (SIGNS) {
+          const int ss = 2 * p - (2 * BW + L);          // the pair's two sign bits go right above the codes
+          off |= (ss >= 0 ? sx >> ss : sx << -ss) & SM;
         }
-        const uint32_t o = chunk_off(blk0 + u, trow, c8);
-        unsigned char* const ap = s.a + 2 * bf * kDPlaneBytes + o;
-        *reinterpret_cast<uint4*>(ap) = make_uint4(e[0].x, e[1].x, e[2].x, e[3].x);
-        *reinterpret_cast<uint4*>(ap + kDPlaneBytes) = make_uint4(e[0].y, e[1].y, e[2].y, e[3].y);
+        const uint2 e = *reinterpret_cast<const uint2*>(tabl[u] + off);
+        hcol[p] = e.x;
+        mcol[p] = e.y;
       }
+      const uint32_t ta = a_tmem_row + 2 * bf * 64 + 16 * (blk0 + u);
+      umma::tmem_st16(ta, hcol);
+      umma::tmem_st16(ta + 64, mcol);
     };
     auto decode_block = [&](int u, int bf) {
       if (MIXED) {
@@ -398,38 +395,33 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
         return;
       }
       // S with other magnitudes than 1: every coordinate by arithmetic
+      uint32_t hcol[16], mcol[16];
 #pragma unroll
-      for (int c8 = 0; c8 < 4; ++c8) {
-        uint32_t packed[2][4];
+      for (int p = 0; p < 16; ++p) {
+        float v[2];
 #pragma unroll
-        for (int p = 0; p < 4; ++p) {
-          float v[2];
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int c = 8 * c8 + 2 * p + h;
-            const int bit = BITS * c, wi = bit >> 5, sh = bit & 31;
-            uint32_t code = nw[u][wi] >> sh;
-            if (sh + BITS > 32) code |= nw[u][wi + 1] << (32 - sh);
-            code &= (1u << BITS) - 1u;
-            float x = cent_s[0][code];
-            if (SIGNS) {
-              const float q = qs_s[32 * (blk0 + u) + c];
-              x += ((nsw[u] >> c) & 1u) ? q : -q;
-            }
-            v[h] = x * scale_a;
+        for (int h = 0; h < 2; ++h) {
+          const int c = 2 * p + h;
+          const int bit = BITS * c, wi = bit >> 5, sh = bit & 31;
+          uint32_t code = nw[u][wi] >> sh;
+          if (sh + BITS > 32) code |= nw[u][wi + 1] << (32 - sh);
+          code &= (1u << BITS) - 1u;
+          float x = cent_s[0][code];
+          if (SIGNS) {
+            const float q = qs_s[32 * (blk0 + u) + c];
+            x += ((nsw[u] >> c) & 1u) ? q : -q;
           }
-          __half h0, m0, h1, m1;
-          split2h(v[0], h0, m0);
-          split2h(v[1], h1, m1);
-          packed[0][p] = pack_h(h0, h1);
-          packed[1][p] = pack_h(m0, m1);
+          v[h] = x * scale_a;
         }
-        const uint32_t o = chunk_off(blk0 + u, trow, c8);
-#pragma unroll
-        for (int t = 0; t < 2; ++t)
-          *reinterpret_cast<uint4*>(s.a + (2 * bf + t) * kDPlaneBytes + o) =
-              make_uint4(packed[t][0], packed[t][1], packed[t][2], packed[t][3]);
+        __half h0, m0, h1, m1;
+        split2h(v[0], h0, m0);
+        split2h(v[1], h1, m1);
+        hcol[p] = pack_h(h0, h1);
+        mcol[p] = pack_h(m0, m1);
       }
+      const uint32_t ta = a_tmem_row + 2 * bf * 64 + 16 * (blk0 + u);
+      umma::tmem_st16(ta, hcol);
+      umma::tmem_st16(ta + 64, mcol);
     };
 
     // Scale this thread's 2 x 32 outputs of row trow by the norm and store them.  A thread holds consecutive outputs
@@ -548,7 +540,7 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
       norm_prev = norm_cur;
       norm_cur = nnorm;
       fetch(tile + gridDim.x);                // the next tile's words travel while this one is multiplied and stored
-      umma::fence_smem_to_async();
+      umma::tmem_st_wait();                   // this thread's part of A(i) is in tensor memory
       umma::fence_before_sync();
       mbar_arrive(&s.mbar[2 + bf]);
       if (prev_tile >= 0) {
