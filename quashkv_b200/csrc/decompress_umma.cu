@@ -46,6 +46,7 @@ constexpr uint32_t kDTmemCols = 512;              // accumulators [0, 256), A op
 constexpr uint32_t kDTmemA = 256;                 // A[buffer][term]: 64 columns each (128 fp16 per row)
 constexpr uint32_t kDTableBytes = 32768;          // pair tables (mixed precision: two halves)
 constexpr int kDProducts = 3;                     // of m*m, m*h, h*m, h*h the last three: the first is below 2^-22
+constexpr uint32_t kDStageRow = 272;              // staging row of a worker thread: 256 bytes + 16
 constexpr int kDTopExp = 14;                      // operands are scaled to a largest magnitude in [2^13, 2^14)
 
 __host__ __device__ constexpr int ilog2(int v) { return v <= 1 ? 0 : 1 + ilog2(v >> 1); }
@@ -94,6 +95,18 @@ __device__ __forceinline__ void split2h(float x, __half& h, __half& m) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_u32(bar)) : "memory");
 }
+
+// Bulk copy shared -> global of `bytes` (a multiple of 16; both addresses 16-byte aligned), tracked by the
+// thread's bulk groups.
+__device__ __forceinline__ void bulk_store(void* dst, const void* src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(dst),
+               "r"(umma::smem_u32(src_smem)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
+// All of this thread's bulk groups have read their source / have completed.
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t pack_h(__half lo, __half hi) {
   return static_cast<uint32_t>(__half_as_ushort(lo)) | (static_cast<uint32_t>(__half_as_ushort(hi)) << 16);
@@ -425,16 +438,20 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
     };
 
     // Scale this thread's 2 x 32 outputs of row trow by the norm and store them.  A thread holds consecutive outputs
-    // of ONE row; stored as they are, a warp instruction would touch 32 rows.  They are transposed through this
-    // warp's own part of the idle A buffer `ab` (rows 32 (w & 3) .., the 128-byte lines of its K half; 16-byte
-    // chunk c of row r at position c ^ (r & 7): conflict-free both ways) and leave as 4 rows x 128 contiguous
-    // bytes per store instruction: whole lines, a quarter of the store wavefronts of 8 rows x 64 bytes.
+    // of ONE row; stored as they are, a warp instruction would touch 32 rows.
+    // fp32: the thread writes its 256 bytes to a staging row of its own (rows 272 bytes apart, so that the eight
+    // lanes served together never meet in a bank) and hands the row to the bulk-copy engine (shared -> global, one
+    // copy per thread and tile): no transposition, no store instruction per 16 bytes, and nobody else ever touches
+    // the staging row; the thread only has to know that its previous copy has been READ before it writes the row
+    // again.  bf16: a row is 128 bytes per thread, and at that size the number of copies binds; the warp
+    // transposes through 32 lines of 128 bytes of its own (16-byte chunk c of row r at position c ^ (r & 7):
+    // conflict-free both ways) and stores 4 rows x 128 contiguous bytes per instruction, whole lines.
     const int rbase = 32 * (warp & 3);
-    const int rr = lane >> 3, rc = lane & 7;           // read side: row 4 j + rr, chunk rc
-    auto line_off = [&](int row, int c) -> uint32_t {
-      return static_cast<uint32_t>((blk0 >> 1) * (128 * 128) + row * 128 + ((c ^ (row & 7)) << 4));
-    };
-    auto epilogue = [&](int64_t tile, int ab, float nrm, bool use_tmem) {
+    unsigned char* const stage = s.a + ((warp - kDFirstWorker) * 32 + lane) * kDStageRow;
+    unsigned char* const lines = s.a + (warp - kDFirstWorker) * (32 * 128);
+    const int rr = lane >> 3, rc = lane & 7;           // read side of the transposition: row 4 j + rr, chunk rc
+    auto line_off = [&](int row, int c) -> uint32_t { return static_cast<uint32_t>(row * 128 + ((c ^ (row & 7)) << 4)); };
+    auto epilogue = [&](int64_t tile, int ab, float nrm, bool use_tmem) {   // ab: accumulator of the tile
       const int64_t n = tile * kDTile + trow;
       const bool live = n < a.n_vec;
       uint32_t v[64];
@@ -460,33 +477,17 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
         }
         for (int c = 0; c < 64; ++c) v[c] = __float_as_uint(decompress_chain(vrow, a.Pi, 32 * blk0 + c));
       }
-      const int64_t n0 = tile * kDTile + rbase;
-      unsigned char* const st = s.a + 2 * ab * kDPlaneBytes;
       if (a.out_dtype == QKV_F32) {
+        bulk_wait_read();                                  // the copy of the previous tile has left the staging row
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {                      // block u through plane u: 32 rows x 128 bytes
-          unsigned char* const pl = st + u * kDPlaneBytes;
-#pragma unroll
-          for (int c = 0; c < 8; ++c)
-            *reinterpret_cast<float4*>(pl + line_off(trow, c)) =
-                make_float4(__uint_as_float(v[32 * u + 4 * c]) * f, __uint_as_float(v[32 * u + 4 * c + 1]) * f,
-                            __uint_as_float(v[32 * u + 4 * c + 2]) * f, __uint_as_float(v[32 * u + 4 * c + 3]) * f);
-        }
-        __syncwarp();
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const unsigned char* const pl = st + u * kDPlaneBytes;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int r = 4 * j + rr;
-            const float4 o = *reinterpret_cast<const float4*>(pl + line_off(rbase + r, rc));
-            if (n0 + r < a.n_vec)
-              *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + (n0 + r) * a.out_pitch + 32 * (blk0 + u) +
-                                         4 * rc) = o;
-          }
-        }
-        __syncwarp();
-      } else if (a.out_dtype == QKV_BF16) {                // both blocks are 128 bytes of a row: one plane
+        for (int c = 0; c < 16; ++c)
+          *reinterpret_cast<float4*>(stage + 16 * c) =
+              make_float4(__uint_as_float(v[4 * c]) * f, __uint_as_float(v[4 * c + 1]) * f,
+                          __uint_as_float(v[4 * c + 2]) * f, __uint_as_float(v[4 * c + 3]) * f);
+        umma::fence_smem_to_async();                       // the row is visible to the copy engine
+        if (live) bulk_store(reinterpret_cast<float*>(a.out) + n * a.out_pitch + 32 * blk0, stage, 256u);
+        bulk_commit();
+      } else if (a.out_dtype == QKV_BF16) {
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           uint32_t pk[4];
@@ -496,13 +497,14 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
                                                             __uint_as_float(v[8 * c + 2 * e + 1]) * f);
             pk[e] = *reinterpret_cast<const uint32_t*>(&b2);
           }
-          *reinterpret_cast<uint4*>(st + line_off(trow, c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *reinterpret_cast<uint4*>(lines + line_off(lane, c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         }
         __syncwarp();
+        const int64_t n0 = tile * kDTile + rbase;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const int r = 4 * j + rr;
-          const uint4 o = *reinterpret_cast<const uint4*>(st + line_off(rbase + r, rc));
+          const uint4 o = *reinterpret_cast<const uint4*>(lines + line_off(r, rc));
           if (n0 + r < a.n_vec)
             *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.out) + (n0 + r) * a.out_pitch + 32 * blk0 + 8 * rc) = o;
         }
@@ -554,6 +556,7 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
       const bool ok = wait_products(bf);
       epilogue(prev_tile, bf, norm_cur, ok);
     }
+    bulk_wait_all();
   }
   umma::fence_before_sync();
   __syncthreads();
