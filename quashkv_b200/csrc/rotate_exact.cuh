@@ -89,11 +89,59 @@ static __device__ __noinline__ float exact_chain(const CompressArgs& a, int64_t 
 }
 
 // Same chain from scalars (a kernel that passes its argument block by reference forces the whole block
-// into local memory).
+// into local memory).  The arithmetic is that of exact_chain, coordinate by coordinate in ascending order; only
+// the loads differ: a 16-byte aligned bf16 or fp32 row and the row of Pi are fetched in four parts of 32
+// coordinates with 16-byte loads that are in flight together.  With one load per coordinate the chain was a
+// sequence of sixteen round trips to memory, and a warp that re-derives a few coordinates this way holds up its
+// whole CTA at the next barrier.
 static __device__ __noinline__ float exact_chain_s(const void* x, int x_dtype, int64_t x_pitch, const float* Pi,
                                                    int64_t n, int col, float norm) {
   const float* prow = Pi + col * kRD;
   float z = 0.f;
+  if (x_dtype == QKV_BF16 && ((reinterpret_cast<uintptr_t>(x) | (static_cast<uint64_t>(x_pitch) * 2)) & 15u) == 0) {
+    const uint4* xr = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(x) + n * x_pitch);
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint4 xv[4];
+      float4 pv[8];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) xv[k] = __ldg(xr + 4 * c + k);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) pv[k] = __ldg(reinterpret_cast<const float4*>(prow) + 8 * c + k);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t w[4] = {xv[k].x, xv[k].y, xv[k].z, xv[k].w};
+        const float4 p0 = pv[2 * k], p1 = pv[2 * k + 1];
+        const float pe[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          z = fmaf(__uint_as_float(w[e] << 16) / norm, pe[2 * e], z);
+          z = fmaf(__uint_as_float(w[e] & 0xFFFF0000u) / norm, pe[2 * e + 1], z);
+        }
+      }
+    }
+    return z;
+  }
+  if (x_dtype == QKV_F32 && ((reinterpret_cast<uintptr_t>(x) | (static_cast<uint64_t>(x_pitch) * 4)) & 15u) == 0) {
+    const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + n * x_pitch);
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      float4 xv[8], pv[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        xv[k] = __ldg(xr + 8 * c + k);
+        pv[k] = __ldg(reinterpret_cast<const float4*>(prow) + 8 * c + k);
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        z = fmaf(xv[k].x / norm, pv[k].x, z);
+        z = fmaf(xv[k].y / norm, pv[k].y, z);
+        z = fmaf(xv[k].z / norm, pv[k].z, z);
+        z = fmaf(xv[k].w / norm, pv[k].w, z);
+      }
+    }
+    return z;
+  }
 #pragma unroll 8
   for (int j = 0; j < kRD; ++j) z = fmaf(load_float(x, x_dtype, n * x_pitch + j) / norm, __ldg(prow + j), z);
   return z;

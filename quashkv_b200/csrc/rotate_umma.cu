@@ -317,16 +317,21 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
   };
 
   // Thread 0: the MMAs of one tile, smallest products first (bf16 input: A*l, A*m, A*h; split input:
-  // m*m, l*h, h*l, m*h, h*m, h*h), then the completion arrival on the accumulator's barrier.
-  auto issue_mmas = [&](int abuf, int acc_buf) {
+  // m*m, l*h, h*l, m*h, h*m, h*h), then the completion arrival on the accumulator's barrier.  The queue in
+  // front of the tensor core is short: the thread that issues a whole tile's MMAs in one go is held for about
+  // as long as they execute, and its warp then reaches the next barrier that much later than the others.  So
+  // the products are issued one at a time (`slice` = 0 .. n_prod - 1, the last one commits) at points of the
+  // loop that lie far enough apart for the queue to drain in between.
+  constexpr int n_prod = NT == 1 ? 3 : 6;
+  auto issue_mmas = [&](int abuf, int acc_buf, int slice) {
     constexpr uint32_t idesc = umma::instr_desc(umma::kFmtBF16, 128, 128);
     const uint32_t d = tmem_base + acc_buf * 128;
-    constexpr int n_prod = NT == 1 ? 3 : 6;
     constexpr int pa1[3] = {0, 0, 0}, pb1[3] = {2, 1, 0};
     constexpr int pa3[6] = {1, 2, 0, 1, 0, 0}, pb3[6] = {1, 0, 2, 0, 1, 0};
-    bool acc = false;
 #pragma unroll
     for (int pr = 0; pr < n_prod; ++pr) {
+      if (pr != slice) continue;
+      bool acc = pr != 0;
       const int ta = NT == 1 ? pa1[pr] : pa3[pr], tb = NT == 1 ? pb1[pr] : pb3[pr];
       const uint32_t a_addr = umma::smem_u32(s.a[abuf][ta]), b_addr = umma::smem_u32(s.b[tb]);
 #pragma unroll
@@ -336,7 +341,7 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
         acc = true;
       }
     }
-    umma::commit(&s.mbar[acc_buf]);
+    if (slice == n_prod - 1) umma::commit(&s.mbar[acc_buf]);
   };
 
   // Classify / pack / store this thread's 32 coordinates of row trow of a finished tile.  use_tmem ==
@@ -468,12 +473,18 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
       if (blk == 0) a.norms[row] = nrm;
     }
     __syncwarp();
+  };
+  // The queues are emptied by all warps together: a warp that re-derives its queued coordinates takes a few
+  // thousand cycles, which the others would spend waiting at the next barrier anyway, so one such pause serves
+  // sixteen queues.  `any` comes out of the barrier at the top of the loop (some queue is at least half full);
+  // a queue that overflows before that is handled element by element where it happens.
+  auto drain_all = [&](int any) {
+    if (!any) return;
     const int queued = s.qcount[warp];
-    if (queued >= 32) {
-      drain(queued < kUQueueCap ? queued : kUQueueCap);
-      if (lane == 0) s.qcount[warp] = 0;
-      __syncwarp();
-    }
+    if (queued > 0) drain(queued < kUQueueCap ? queued : kUQueueCap);
+    __syncwarp();
+    if (lane == 0) s.qcount[warp] = 0;
+    __syncwarp();
   };
   auto epilogue = [&](int64_t tile, int buf, float nrm, bool use_tmem) {
     if (MIXED && cls_blk) epilogue_t(std::integral_constant<int, (MIXED ? BITS1 : BITS)>{}, tile, buf, nrm, use_tmem);
@@ -502,10 +513,12 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
       cp_async_wait<0>();
       umma::fence_smem_to_async();
       umma::fence_before_sync();
-      __syncthreads();                    // A(i) complete and visible; epilogue(i-2) has left accumulator `buf`
-      if (tid == 0 && *s.dead == 0 && !(a.test_drop_mma && blockIdx.x == 0 && i == 1)) {
+      // A(i) complete and visible; epilogue(i-2) has left accumulator `buf`
+      const int any = __syncthreads_or(s.qcount[warp] >= kUQueueCap / 2);
+      const bool issuer = tid == 0 && *s.dead == 0 && !(a.test_drop_mma && blockIdx.x == 0 && i == 1);
+      if (issuer) {
         umma::fence_after_sync();
-        issue_mmas(buf, buf);
+        issue_mmas(buf, buf, 0);
       }
       // The MMAs of tile i-1 were issued a whole iteration ago: their barrier is normally complete, so the
       // copy of tile i+1 into the buffer they read starts right away and travels during everything below.
@@ -514,9 +527,12 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
       if (prev_tile >= 0) ok = wait_acc(buf ^ 1);
       if (next < n_tiles) load_tile(next, buf ^ 1);
       const float norm_prev = prev_tile >= 0 ? row_norm(buf ^ 1) : 1.f;   // squares(i-1) were left before the barrier
+      if (issuer) issue_mmas(buf, buf, 1);
+      drain_all(any);
       // the fp64 sums of half the warps go before the epilogue and of the other half after it, so that the
       // sixteen warps do not queue for the fp64 pipe at the same moment
       if (blk < 2) part_squares(buf);
+      if (issuer) issue_mmas(buf, buf, 2);
       if (prev_tile >= 0) epilogue(prev_tile, buf ^ 1, norm_prev, ok);
       if (blk >= 2) part_squares(buf);
       prev_tile = tile;
@@ -530,12 +546,18 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
       load_split_tile(tile, par);
       umma::fence_smem_to_async();
       umma::fence_before_sync();
-      __syncthreads();                    // A(i) and its squares complete; epilogue(i-2) has left accumulator `par`
+      // A(i) and its squares complete; epilogue(i-2) has left accumulator `par`
+      const int any = __syncthreads_or(s.qcount[warp] >= kUQueueCap / 2);
       if (tid == 0 && *s.dead == 0 && !(a.test_drop_mma && blockIdx.x == 0 && i == 1)) {
         umma::fence_after_sync();
-        issue_mmas(0, par);
+#pragma unroll
+        for (int sl = 0; sl < n_prod; ++sl) issue_mmas(0, par, sl);
       }
-      if (prev_tile >= 0) epilogue(prev_tile, par ^ 1, row_norm(par ^ 1), prev_ok);
+      // the norm is read before anything slow: a warp that runs ahead overwrites these partial sums with those
+      // of tile i+1 as soon as it has passed its own epilogue
+      const float norm_prev = prev_tile >= 0 ? row_norm(par ^ 1) : 1.f;
+      drain_all(any);
+      if (prev_tile >= 0) epilogue(prev_tile, par ^ 1, norm_prev, prev_ok);
       prev_tile = tile;
     }
   }
