@@ -368,21 +368,74 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
       uint32_t v[32];
       umma::tmem_ld32(taddr, v);
       uint32_t fm = 0;                           // flag of coordinate c ends up at bit 31 - c
+      float fl_raw = 0.f;                        // the last flagged coordinate of this thread, kept in registers:
+      int fl_c = 0;                              // nearly always its only one
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
         const float raw = __uint_as_float(v[c]);
         const int e = lut_c[bucket_fine<LUTN>(raw, scale)];             // sign-extended: negative when flagged
         fm = __funnelshift_l(static_cast<uint32_t>(e), fm, 1);
+        if (e < 0) { fl_raw = raw; fl_c = c; }
         const uint32_t code = static_cast<uint32_t>(e) & 15u;
         const int bit = BW * c, w = bit >> 5, sh = bit & 31;
         wb[w] += code << sh;                                       // fields are disjoint: add == or
         if (sh + BW > 32) wb[w + 1] += code >> (32 - sh);
         if (IP) R = __funnelshift_l(__float_as_uint(raw * iv - cent_s[code]), R, 1);
       }
-      const uint32_t mine = __brev(fm);
-      uint32_t cols = __reduce_or_sync(QKV_FULL_MASK, mine);      // columns flagged in any lane
+      // A flagged coordinate gets the exact classification from its accumulator value: boundary test, sign of the
+      // residual, and a place in the queue when it lies within the recheck margin.
+      auto resolve = [&](int c, float raw) {
+        const int col = col0 + c;
+        const float y = raw * iv;
+        const uint32_t ec = static_cast<uint8_t>(lut_c[bucket_fine<LUTN>(raw, scale)]);
+        uint32_t code = ec & 15u, sign = 0;
+        bool near = false;
+        if ((ec & 0x60u) == 0x60u) {                 // edge bucket or two features: generic classification
+          const uint32_t r = classify_slow(bnd_c, cent_s, IP ? sgn_s[col] : 0.f, y, NBW, IP ? 1 : 0);
+          code = r & 0xFFu; sign = (r >> 8) & 1u; near = (r >> 16) != 0;
+        } else {
+          if (ec & 0x40u) {                          // one boundary in reach: code = its number, +1 above it
+            const float b = bnd_c[code];
+            near = fabsf(y - b) < kRecheckEps;
+            code += y > b ? 1u : 0u;
+          }
+          if (IP) {
+            const float resid = y - cent_s[code];
+            sign = (resid * sgn_s[col] >= 0.f) ? 1u : 0u;
+            near |= fabsf(resid) < kRecheckEps;
+          }
+        }
+        if (near && live) {
+          const int slot = atomicAdd(&s.qcount[warp], 1);
+          if (slot < kUQueueCap) {
+            queue[slot] = make_uint4(static_cast<uint32_t>(n), col | (code << 8) | (sign << 16),
+                                     __float_as_uint(nrm), 0u);
+          } else {
+            const float z = exact_chain_s(a.x, a.x_dtype, a.x_pitch, a.Pi, n, MIXED ? perm_s[col] : col, nrm);
+            code = count_bounds<BW>(bnd_c, z);
+            if (IP) sign = ((z - cent_s[code]) * sgn_s[col] >= 0.f) ? 1u : 0u;
+          }
+        }
+        fmask |= 1u << c;
+        fval |= sign << c;
+        const uint32_t diff = code ^ (ec & 15u);
+        const int bit = BW * c, w = bit >> 5, sh = bit & 31;
+#pragma unroll
+        for (int q = 0; q <= BW; ++q) {
+          if (q == w) wb[q] ^= diff << sh;
+          if (q == w + 1 && sh + BW > 32) wb[q] ^= diff >> (32 - sh);
+        }
+      };
+      uint32_t mine = __brev(fm);
+      if (__popc(mine) == 1) {                     // the usual case: resolved from the registers, no second read
+        resolve(fl_c, fl_raw);
+        mine = 0u;
+      }
+      __syncwarp();
+      // Threads with several flagged coordinates (rare): the warp walks over the columns concerned, re-reads each
+      // from tensor memory (up to four per round, so that the reads overlap) and the flagged lanes resolve it.
+      uint32_t cols = __reduce_or_sync(QKV_FULL_MASK, mine);
       while (cols) {
-        // up to four flagged columns per round: their reads from tensor memory overlap
         int cc[4]; uint32_t ta[4], rv[4];
         int n_c = 0;
 #pragma unroll
@@ -394,51 +447,10 @@ __global__ void __launch_bounds__(kUThreads, 1) compress_umma_kernel(CompressArg
         umma::tmem_ld1x4(ta, rv);
 #pragma unroll 1
         for (int j = 0; j < n_c; ++j) {
-        const int c = j == 0 ? cc[0] : (j == 1 ? cc[1] : (j == 2 ? cc[2] : cc[3]));
-        const float raw = __uint_as_float(j == 0 ? rv[0] : (j == 1 ? rv[1] : (j == 2 ? rv[2] : rv[3])));
-        if ((mine >> c) & 1u) {
-          const int col = col0 + c;
-          const float y = raw * iv;
-          const uint32_t ec = static_cast<uint8_t>(lut_c[bucket_fine<LUTN>(raw, scale)]);
-          uint32_t code = ec & 15u, sign = 0;
-          bool near = false;
-          if ((ec & 0x60u) == 0x60u) {                 // edge bucket or two features: generic classification
-            const uint32_t r = classify_slow(bnd_c, cent_s, IP ? sgn_s[col] : 0.f, y, NBW, IP ? 1 : 0);
-            code = r & 0xFFu; sign = (r >> 8) & 1u; near = (r >> 16) != 0;
-          } else {
-            if (ec & 0x40u) {                          // one boundary in reach: code = its number, +1 above it
-              const float b = bnd_c[code];
-              near = fabsf(y - b) < kRecheckEps;
-              code += y > b ? 1u : 0u;
-            }
-            if (IP) {
-              const float resid = y - cent_s[code];
-              sign = (resid * sgn_s[col] >= 0.f) ? 1u : 0u;
-              near |= fabsf(resid) < kRecheckEps;
-            }
-          }
-          if (near && live) {
-            const int slot = atomicAdd(&s.qcount[warp], 1);
-            if (slot < kUQueueCap) {
-              queue[slot] = make_uint4(static_cast<uint32_t>(n), col | (code << 8) | (sign << 16),
-                                       __float_as_uint(nrm), 0u);
-            } else {
-              const float z = exact_chain_s(a.x, a.x_dtype, a.x_pitch, a.Pi, n, MIXED ? perm_s[col] : col, nrm);
-              code = count_bounds<BW>(bnd_c, z);
-              if (IP) sign = ((z - cent_s[code]) * sgn_s[col] >= 0.f) ? 1u : 0u;
-            }
-          }
-          fmask |= 1u << c;
-          fval |= sign << c;
-          const uint32_t diff = code ^ (ec & 15u);
-          const int bit = BW * c, w = bit >> 5, sh = bit & 31;
-#pragma unroll
-          for (int q = 0; q <= BW; ++q) {
-            if (q == w) wb[q] ^= diff << sh;
-            if (q == w + 1 && sh + BW > 32) wb[q] ^= diff >> (32 - sh);
-          }
-        }
-        __syncwarp();
+          const int c = j == 0 ? cc[0] : (j == 1 ? cc[1] : (j == 2 ? cc[2] : cc[3]));
+          const float raw = __uint_as_float(j == 0 ? rv[0] : (j == 1 ? rv[1] : (j == 2 ? rv[2] : rv[3])));
+          if ((mine >> c) & 1u) resolve(c, raw);
+          __syncwarp();
         }
       }
     } else {
