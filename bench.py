@@ -227,8 +227,9 @@ def run_reference(args):
 # GPU arm
 # ---------------------------------------------------------------------------------------------------------
 
-def timed(fn, reps=5):
-    """Seconds per call of fn on the current stream (one untimed call first)."""
+def timed(fn, reps=10):
+    """Seconds per call of fn on the current stream (two untimed calls first)."""
+    fn()
     fn()
     torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

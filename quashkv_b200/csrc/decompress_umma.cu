@@ -454,28 +454,31 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
     auto epilogue = [&](int64_t tile, int ab, float nrm, bool use_tmem) {   // ab: accumulator of the tile
       const int64_t n = tile * kDTile + trow;
       const bool live = n < a.n_vec;
+      if (!use_tmem) {                                     // tensor core timed out: fp32 chain from the packed row,
+        if (live) {                                        // stored value by value (kept apart from the registers of
+          const int64_t row = row_of(n);                   // the normal path, which must never be indexed by a variable)
+          float vrow[kRD];
+          for (int i = 0; i < kRD; ++i) {                  // i = stream position; channel = perm[i] when mixed
+            const int ci = i >= n_out ? 1 : 0;
+            const int bit = ci ? n_out * BITS + (i - n_out) * BITS1 : i * BITS;
+            const uint32_t code = read_field(a.codes + row * (row_words * 4), bit, ci ? BITS1 : BITS, row_words * 4);
+            float x = cent_s[ci][code];
+            if (SIGNS) x += ((signs[row * (kRD / 32) + (i >> 5)] >> (i & 31)) & 1u) ? qs_s[i] : -qs_s[i];
+            vrow[MIXED ? perm_s[i] : i] = x;
+          }
+#pragma unroll 1
+          for (int c = 0; c < 64; ++c)
+            store_float(a.out, a.out_dtype, n * a.out_pitch + 32 * blk0 + c, decompress_chain(vrow, a.Pi, 32 * blk0 + c) * nrm);
+        }
+        return;
+      }
       uint32_t v[64];
-      float f = nrm;
-      if (use_tmem) {
-        umma::tmem_ld64(tmem_base + (static_cast<uint32_t>(rbase) << 16) + ab * 128 + 32 * blk0, v);
-        f = nrm * descale;
-        if (!(fabsf(f) >= 1e-30f && fabsf(f) <= 1e30f)) {  // the product would lose bits: take the power of two first
+      umma::tmem_ld64(tmem_base + (static_cast<uint32_t>(rbase) << 16) + ab * 128 + 32 * blk0, v);
+      float f = nrm * descale;
+      if (!(fabsf(f) >= 1e-30f && fabsf(f) <= 1e30f)) {    // the product would lose bits: take the power of two first
 #pragma unroll
-          for (int c = 0; c < 64; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * descale);
-          f = nrm;
-        }
-      } else if (live) {                                   // tensor core timed out: fp32 chain from the packed row
-        const int64_t row = row_of(n);
-        float vrow[kRD];
-        for (int i = 0; i < kRD; ++i) {                    // i = stream position; channel = perm[i] when mixed
-          const int ci = i >= n_out ? 1 : 0;
-          const int bit = ci ? n_out * BITS + (i - n_out) * BITS1 : i * BITS;
-          const uint32_t code = read_field(a.codes + row * (row_words * 4), bit, ci ? BITS1 : BITS, row_words * 4);
-          float x = cent_s[ci][code];
-          if (SIGNS) x += ((signs[row * (kRD / 32) + (i >> 5)] >> (i & 31)) & 1u) ? qs_s[i] : -qs_s[i];
-          vrow[MIXED ? perm_s[i] : i] = x;
-        }
-        for (int c = 0; c < 64; ++c) v[c] = __float_as_uint(decompress_chain(vrow, a.Pi, 32 * blk0 + c));
+        for (int c = 0; c < 64; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * descale);
+        f = nrm;
       }
       if (a.out_dtype == QKV_F32) {
         bulk_wait_read();                                  // the copy of the previous tile has left the staging row
