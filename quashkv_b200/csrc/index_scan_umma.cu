@@ -25,16 +25,19 @@ namespace qkv {
 
 constexpr int kXQ = 64;                      // queries per CTA = MMA N
 constexpr int kXRows = 128;                  // rows per tile = MMA M
-constexpr int kXThreads = 256;               // warp w: row quarter w & 3 (its TMEM lanes), query block w >> 2
+constexpr int kXFirstWorker = 4;             // warp 0 issues the MMAs, warps 1-3 only help with the set-up and the lists
+constexpr int kXWorkers = 256;               // worker warp w: row quarter w & 3 (its TMEM lanes), query block (w - 4) >> 2
+constexpr int kXThreads = 32 * kXFirstWorker + kXWorkers;
 constexpr int kXCap = 40;                    // candidate slots per (row quarter, query)
 constexpr int kXSlack = 24;                  // a buffer is pruned when fewer slots than this are free: a tile can
                                              // add 32 rows at once, a handful in practice once the threshold is up
 constexpr uint32_t kXATile = kXRows * 256 * 2;   // 64 KB: four K blocks of 64 fp16
 constexpr uint32_t kXBTile = kXQ * 256 * 2;      // 32 KB
-constexpr uint32_t kXTmemCols = 128;         // two accumulators of 64 columns
+constexpr uint32_t kXTmemCols = 512;         // two accumulators of 64 columns, two A operands of 128 (256 fp16 per row)
+constexpr uint32_t kXTmemA = 128;            // first column of the A operands
 constexpr int kXMaxK = kXCap - kXSlack - 4;  // k + a few extra rows must fit below the prune mark
 
-constexpr size_t kXSmemBytes = 1024 + 2 * kXATile + kXBTile + static_cast<size_t>(kXQ) * 4 * kXCap * 6 + 2 * 8 + 16;
+constexpr size_t kXSmemBytes = 1024 + 2 * kXATile + kXBTile + static_cast<size_t>(kXQ) * 4 * kXCap * 6 + 4 * 8 + 16;
 
 __device__ unsigned int g_index_umma_timeouts = 0;
 
@@ -51,16 +54,16 @@ __global__ void __launch_bounds__(kXThreads, 1) index_scan_umma_kernel(ScanMmaAr
   __shared__ float quart[4][kXQ];
   __shared__ float nmax_w[kXThreads / 32];
   unsigned char* base = smem_raw + ((1024u - (umma::smem_u32(smem_raw) & 1023u)) & 1023u);
-  unsigned char* a_tile[2] = {base, base + kXATile};
-  unsigned char* b_tile = base + 2 * kXATile;
+  unsigned char* b_tile = base + 2 * kXATile;       // (the first 2 x 64 KB are not used: one CTA per SM, as its 512 tensor-memory columns require)
   float* buf_u = reinterpret_cast<float*>(b_tile + kXBTile);                      // [query][row quarter][kXCap]
   uint16_t* buf_r = reinterpret_cast<uint16_t*>(buf_u + kXQ * 4 * kXCap);
   uint64_t* mbar = reinterpret_cast<uint64_t*>(buf_r + kXQ * 4 * kXCap);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 2);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 4);   // mbar: accumulator 0 / 1 complete, A 0 / 1 written
   int* dead = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int rq = warp & 3, cb = warp >> 2;
+  const bool worker = warp >= kXFirstWorker;
+  const int rq = warp & 3, cb = worker ? (warp - kXFirstWorker) >> 2 : 0;
   const int row = 32 * rq + lane;           // row of the tile = tensor-memory lane
   const int slice = blockIdx.x, q0 = blockIdx.y * kXQ;
   const float inv_sk = __uint_as_float(a.tables[6]);
@@ -84,6 +87,8 @@ __global__ void __launch_bounds__(kXThreads, 1) index_scan_umma_kernel(ScanMmaAr
   if (tid == 0) {
     umma::mbar_init(&mbar[0], 1);
     umma::mbar_init(&mbar[1], 1);
+    umma::mbar_init(&mbar[2], kXWorkers);
+    umma::mbar_init(&mbar[3], kXWorkers);
     *dead = 0;
   }
   __syncthreads();
@@ -127,56 +132,50 @@ __global__ void __launch_bounds__(kXThreads, 1) index_scan_umma_kernel(ScanMmaAr
     kn = ok ? __ldg(a.norms + n) : 0.f;
   };
 
+  // The decoded half row goes straight to tensor memory: 32-bit column c of the A operand holds K elements 2 c and
+  // 2 c + 1, and a 16-byte chunk of the K-major row is four such columns.  Code part: columns 32 cb .. + 31, sign
+  // part: 64 + 32 cb .. + 31 (lane = row).
   auto decode = [&](const uint4& c, const uint2& s, int buf) {
-    unsigned char* arow = a_tile[buf] + row * 128;
+    const uint32_t ta = tmem_base + (static_cast<uint32_t>(32 * rq) << 16) + kXTmemA + buf * 128 + 32 * cb;
     const uint32_t cw[4] = {c.x, c.y, c.z, c.w};
 #pragma unroll
-    for (int wd = 0; wd < 4; ++wd) {
+    for (int hw = 0; hw < 2; ++hw) {
+      uint32_t o[16];
 #pragma unroll
-      for (int gp = 0; gp < 2; ++gp) {
-        uint32_t o[4];
+      for (int w2 = 0; w2 < 2; ++w2) {
+        const int wd = 2 * hw + w2;
 #pragma unroll
-        for (int g2 = 0; g2 < 2; ++g2) {
-          const int g = 2 * gp + g2;
+        for (int g = 0; g < 4; ++g) {
           const uint32_t y = (cw[wd] >> (2 * g)) & 0x03030303u;
           const uint32_t sl = y * 0x22u + 0x10101010u;
-          o[2 * g2] = prmt(kt_a, kt_b, sl);
-          o[2 * g2 + 1] = prmt(kt_a, kt_b, sl >> 16);
+          o[8 * w2 + 2 * g] = prmt(kt_a, kt_b, sl);
+          o[8 * w2 + 2 * g + 1] = prmt(kt_a, kt_b, sl >> 16);
         }
-        const int c16 = 2 * (4 * cb + wd) + gp;            // 16-byte chunk of the row, 0..15
-        *reinterpret_cast<uint4*>(arow + (c16 >> 3) * (kXRows * 128) + (((c16 & 7) ^ (row & 7)) << 4)) =
-            make_uint4(o[0], o[1], o[2], o[3]);
       }
+      umma::tmem_st16(ta + 16 * hw, o);
     }
     const uint32_t sw[2] = {s.x, s.y};
 #pragma unroll
     for (int w2 = 0; w2 < 2; ++w2) {
       const uint32_t cp[4] = {sw[w2], sw[w2] << 7, sw[w2] >> 1, sw[w2] << 13};
+      uint32_t o[16];
 #pragma unroll
-      for (int qd = 0; qd < 4; ++qd) {
-        uint32_t o[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int t = 4 * qd + e;
-          const int cpy = t < 7 ? 0 : (t < 14 ? 1 : t - 12);
-          o[e] = cp[cpy] & (0x00010001u << sign_pos(t));
-        }
-        const int c16 = 16 + 4 * (2 * cb + w2) + qd;       // chunks 16..31: the sign part
-        *reinterpret_cast<uint4*>(arow + (c16 >> 3) * (kXRows * 128) + (((c16 & 7) ^ (row & 7)) << 4)) =
-            make_uint4(o[0], o[1], o[2], o[3]);
+      for (int t = 0; t < 16; ++t) {
+        const int cpy = t < 7 ? 0 : (t < 14 ? 1 : t - 12);
+        o[t] = cp[cpy] & (0x00010001u << sign_pos(t));
       }
+      umma::tmem_st16(ta + 64 + 16 * w2, o);
     }
   };
 
   auto issue_mmas = [&](int buf, int acc) {
     constexpr uint32_t idesc = umma::instr_desc(umma::kFmtF16, kXRows, kXQ);
     const uint32_t d = tmem_base + acc * kXQ;
-    const uint32_t a_addr = umma::smem_u32(a_tile[buf]), b_addr = umma::smem_u32(b_tile);
+    const uint32_t a_tmem = tmem_base + kXTmemA + buf * 128, b_addr = umma::smem_u32(b_tile);
 #pragma unroll
     for (int ks = 0; ks < 16; ++ks) {
-      const uint32_t a_off = (ks >> 2) * (kXRows * 128) + (ks & 3) * 32;
       const uint32_t b_off = (ks >> 2) * (kXQ * 128) + (ks & 3) * 32;
-      umma::mma_f16(d, umma::smem_desc_sw128(a_addr + a_off), umma::smem_desc_sw128(b_addr + b_off), idesc, ks != 0);
+      umma::mma_f16_ts(d, a_tmem + 8 * ks, umma::smem_desc_sw128(b_addr + b_off), idesc, ks != 0);
     }
     umma::commit(&mbar[acc]);
   };
@@ -231,22 +230,40 @@ __global__ void __launch_bounds__(kXThreads, 1) index_scan_umma_kernel(ScanMmaAr
     }
     __syncwarp();
     const int n_sub = tile < 8 ? 4 : 1;              // a warp's first rows arrive in four groups of eight lanes
+    // Which of this row's 32 scores reach their query's threshold: one bit each, computed without a branch.  Then
+    // every lane files its own hits, one per round: the rounds a warp needs are the LARGEST number of hits in one
+    // row, not the number of (row, query) hits of the whole warp as with a branch per query (hits are spread over
+    // rows and queries; the branch per query was 3000 of a tile's 5500 cycles).
+    uint32_t hits = 0;
+#pragma unroll
+    for (int q = 0; q < 32; ++q) {
+      const float2 it = init_thr[32 * cb + q];
+      const float u = (__uint_as_float(v[q]) + it.x) * kn;
+      hits |= (u >= it.y ? 1u : 0u) << q;
+    }
+    if (!valid) hits = 0;
 #pragma unroll 1
     for (int sub = 0; sub < n_sub; ++sub) {
-      const bool active = valid && (n_sub == 1 || (lane >> 3) == sub);
+      uint32_t todo = (n_sub == 1 || (lane >> 3) == sub) ? hits : 0u;
+      while (__any_sync(QKV_FULL_MASK, todo != 0u)) {
+        if (todo) {
+          const int q = __ffs(todo) - 1;
+          todo &= todo - 1;
+          uint32_t raw = v[0];                        // v[q] without a variable register index
 #pragma unroll
-      for (int q = 0; q < 32; ++q) {
-        const float2 it = init_thr[32 * cb + q];
-        const float u = (__uint_as_float(v[q]) + it.x) * kn;
-        if (active && u >= it.y) {
+          for (int j = 1; j < 32; ++j) raw = q == j ? v[j] : raw;
           const int qq = 32 * cb + q;
-          const int pos = atomicAdd(&cnt[rq][qq], 1);
-          if (pos < kXCap) {
-            buf_u[qq * QS + rq * kXCap + pos] = u;
-            buf_r[qq * QS + rq * kXCap + pos] = static_cast<uint16_t>(r);
-          } else {                                    // buffer full before it could be pruned: redo this query
-            if (q0 + qq < a.M) a.flags[q0 + qq] = 1;
-            init_thr[qq].y = INFINITY;
+          const float2 it = init_thr[qq];
+          const float u = (__uint_as_float(raw) + it.x) * kn;
+          if (u >= it.y) {                            // the threshold may have risen since the first look
+            const int pos = atomicAdd(&cnt[rq][qq], 1);
+            if (pos < kXCap) {
+              buf_u[qq * QS + rq * kXCap + pos] = u;
+              buf_r[qq * QS + rq * kXCap + pos] = static_cast<uint16_t>(r);
+            } else {                                  // buffer full before it could be pruned: redo this query
+              if (q0 + qq < a.M) a.flags[q0 + qq] = 1;
+              init_thr[qq].y = INFINITY;
+            }
           }
         }
       }
@@ -255,43 +272,60 @@ __global__ void __launch_bounds__(kXThreads, 1) index_scan_umma_kernel(ScanMmaAr
     }
   };
 
-  // ---- pipeline: decode(i); issue(i); wait(i-1); epilogue(i-1) ------------------------------------------------
-  uint32_t phase[2] = {0u, 0u};
-  uint4 rc; uint2 rs; float kn_next = 0.f, kn_cur = 0.f, kn_prev = 0.f;
-  if (n_tiles > 0) fetch(0, rc, rs, kn_next);
-  for (int i = 0; i < n_tiles; ++i) {
-    const int buf = i & 1;
-    decode(rc, rs, buf);
-    kn_prev = kn_cur;
-    kn_cur = kn_next;
-    if (i + 1 < n_tiles) fetch(i + 1, rc, rs, kn_next);
-    umma::fence_smem_to_async();
-    umma::fence_before_sync();
-    __syncthreads();                       // A(i) written; every warp has left accumulator `buf` (epilogue i-2)
-    if (tid == 0 && *dead == 0) {
-      umma::fence_after_sync();
-      issue_mmas(buf, buf);
+  // ---- warp 0: per tile, wait until every worker has stored its part of A(i), then the 16 MMAs -----------------
+  // (the thread that issues them is held for about as long as they execute; as a worker it would hold the
+  // whole CTA back by that time)
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t full_phase[2] = {0u, 0u};
+      for (int i = 0; i < n_tiles; ++i) {
+        const int buf = i & 1;
+        if (*reinterpret_cast<volatile int*>(dead)) break;
+        if (!umma::mbar_wait(&mbar[2 + buf], full_phase[buf])) { *reinterpret_cast<volatile int*>(dead) = 1; break; }
+        full_phase[buf] ^= 1u;
+        if (*reinterpret_cast<volatile int*>(dead)) break;
+        umma::fence_after_sync();
+        issue_mmas(buf, buf);
+      }
     }
-    if (i > 0) {
-      bool ok = *dead == 0;
+    __syncwarp();
+  }
+  // ---- workers: decode(i); arrive; wait(i-1); epilogue(i-1).  No CTA barrier: A(i+1) goes into the buffer of
+  // tile i-1, whose products this thread has waited for; accumulator (i+1) & 1 is overwritten only after every
+  // worker has arrived for tile i+1, that is after its epilogue of tile i-1.
+  if (worker) {
+    uint32_t phase[2] = {0u, 0u};
+    auto wait_products = [&](int acc) -> bool {
+      bool ok = *reinterpret_cast<volatile int*>(dead) == 0;
       if (ok) {
-        ok = umma::mbar_wait(&mbar[buf ^ 1], phase[buf ^ 1]);
-        phase[buf ^ 1] ^= 1u;
-        if (!ok) *dead = 1;
+        ok = umma::mbar_wait(&mbar[acc], phase[acc]);
+        phase[acc] ^= 1u;
+        if (!ok) *reinterpret_cast<volatile int*>(dead) = 1;
       }
       umma::fence_after_sync();
-      epilogue(i - 1, buf ^ 1, kn_prev, ok);
+      return ok;
+    };
+    uint4 rc; uint2 rs; float kn_next = 0.f, kn_cur = 0.f, kn_prev = 0.f;
+    if (n_tiles > 0) fetch(0, rc, rs, kn_next);
+    for (int i = 0; i < n_tiles; ++i) {
+      const int buf = i & 1;
+      decode(rc, rs, buf);
+      kn_prev = kn_cur;
+      kn_cur = kn_next;
+      if (i + 1 < n_tiles) fetch(i + 1, rc, rs, kn_next);
+      umma::tmem_st_wait();
+      umma::fence_before_sync();
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_u32(&mbar[2 + buf])) : "memory");
+      if (i > 0) {
+        const bool ok = wait_products(buf ^ 1);
+        epilogue(i - 1, buf ^ 1, kn_prev, ok);
+      }
     }
-  }
-  if (n_tiles > 0) {
-    const int buf = (n_tiles - 1) & 1;
-    bool ok = *dead == 0;
-    if (ok) {
-      ok = umma::mbar_wait(&mbar[buf], phase[buf]);
-      if (!ok) *dead = 1;
+    if (n_tiles > 0) {
+      const int buf = (n_tiles - 1) & 1;
+      const bool ok = wait_products(buf);
+      epilogue(n_tiles - 1, buf, kn_cur, ok);
     }
-    umma::fence_after_sync();
-    epilogue(n_tiles - 1, buf, kn_cur, ok);
   }
   {
     float nm = my_nmax;
