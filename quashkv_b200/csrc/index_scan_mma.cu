@@ -370,11 +370,11 @@ struct ScanMmaPlan {
   size_t total() const { return hdr_bytes + flag_bytes + qk_bytes + ls_bytes + li_bytes + fallback_bytes; }
 };
 
-// The tcgen05 scan (index_scan_umma.cu) gives the same results but is slower than the mma.sync scan at
-// present, so it only runs when QUASHKV_B200_INDEX_TCGEN05=1 asks for it.
+// The tcgen05 scan (index_scan_umma.cu) gives the same results and is the faster one where it applies (k <= 12);
+// QUASHKV_B200_INDEX_TCGEN05=0 keeps the mma.sync scan (A/B checks, tests).
 static bool scan_on_tcgen05(int k) {
   const char* e = getenv("QUASHKV_B200_INDEX_TCGEN05");
-  return index_umma_ok(k) && e && e[0] == '1';
+  return index_umma_ok(k) && !(e && e[0] == '0');
 }
 
 static ScanMmaPlan make_mma_plan(int64_t N, int M, int k, bool tcgen05) {
@@ -382,7 +382,7 @@ static ScanMmaPlan make_mma_plan(int64_t N, int M, int k, bool tcgen05) {
   p.n_qtiles = tcgen05 ? index_umma_qtiles(M) : (M + kIQ - 1) / kIQ;
   const int capw = capw_for(k);
   const int ctas_per_sm = capw <= 32 ? 4 : (capw <= 48 ? 3 : 2);
-  int64_t want = tcgen05 ? (4 * kNumSMs) / p.n_qtiles                             // one CTA per SM, four rounds
+  int64_t want = tcgen05 ? (2 * kNumSMs) / p.n_qtiles                             // one CTA per SM, two rounds
                          : (ctas_per_sm * kNumSMs * 2 + p.n_qtiles - 1) / p.n_qtiles;   // about two waves
   const int64_t chunk = 256;
   const int64_t max_by_len = (N + 8 * chunk - 1) / (8 * chunk);

@@ -11,9 +11,12 @@
 // query's threshold.  Decode work per (row, query) pair drops 4x against the mma.sync kernel (one
 // decode serves 64 queries instead of 32 and needs no per-fragment shuffling), the MMAs leave the
 // instruction stream, and the B operand is read by the tensor core instead of by LDS.
-// State: results are identical to the other scans (tests), but with 8 warps per SM and the candidate
-// bookkeeping in the epilogue this first version runs at about half the speed of the mma.sync scan,
-// so it is opt-in (QUASHKV_B200_INDEX_TCGEN05=1).
+// Warp 0 only issues the MMAs (the issuing thread is held for about as long as they execute), warps 4-11 decode
+// and test; the decoded rows go straight to tensor memory (tcgen05.st) and the MMA reads its A operand there;
+// workers and issuer meet on mbarriers, there is no CTA barrier in the loop; three accumulators, so that the
+// products a worker reads were issued two tiles earlier; a row's hits are filed by its own lane, one per round.
+// 1M rows x 1024 queries: 1.67 ms for the whole search against 2.23 ms with the mma.sync scan; default for k <= 12
+// (QUASHKV_B200_INDEX_TCGEN05=0 selects the mma.sync scan).
 //
 // Candidate bookkeeping is the mma.sync kernel's: per (row quarter, query) private buffers, a shared
 // rising threshold, flagged queries redone by the CUDA-core scan.  A warp sees 32 rows per tile, so
@@ -33,11 +36,11 @@ constexpr int kXSlack = 24;                  // a buffer is pruned when fewer sl
                                              // add 32 rows at once, a handful in practice once the threshold is up
 constexpr uint32_t kXATile = kXRows * 256 * 2;   // 64 KB: four K blocks of 64 fp16
 constexpr uint32_t kXBTile = kXQ * 256 * 2;      // 32 KB
-constexpr uint32_t kXTmemCols = 512;         // two accumulators of 64 columns, two A operands of 128 (256 fp16 per row)
-constexpr uint32_t kXTmemA = 128;            // first column of the A operands
+constexpr uint32_t kXTmemCols = 512;         // three accumulators of 64 columns, two A operands of 128 (256 fp16 per row)
+constexpr uint32_t kXTmemA = 256;            // first column of the A operands
 constexpr int kXMaxK = kXCap - kXSlack - 4;  // k + a few extra rows must fit below the prune mark
 
-constexpr size_t kXSmemBytes = 1024 + 2 * kXATile + kXBTile + static_cast<size_t>(kXQ) * 4 * kXCap * 6 + 4 * 8 + 16;
+constexpr size_t kXSmemBytes = 1024 + 2 * kXATile + kXBTile + static_cast<size_t>(kXQ) * 4 * kXCap * 6 + 5 * 8 + 16;
 
 __device__ unsigned int g_index_umma_timeouts = 0;
 
@@ -58,7 +61,7 @@ __global__ void __launch_bounds__(kXThreads, 1) index_scan_umma_kernel(ScanMmaAr
   float* buf_u = reinterpret_cast<float*>(b_tile + kXBTile);                      // [query][row quarter][kXCap]
   uint16_t* buf_r = reinterpret_cast<uint16_t*>(buf_u + kXQ * 4 * kXCap);
   uint64_t* mbar = reinterpret_cast<uint64_t*>(buf_r + kXQ * 4 * kXCap);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 4);   // mbar: accumulator 0 / 1 complete, A 0 / 1 written
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 5);   // mbar: accumulator 0 / 1 / 2 complete, A 0 / 1 written
   int* dead = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -75,7 +78,20 @@ __global__ void __launch_bounds__(kXThreads, 1) index_scan_umma_kernel(ScanMmaAr
     const int m = q0 + tid;
     const float* q = a.qk + static_cast<int64_t>(m < a.M ? m : 0) * 2 * D;
     float q2 = 0.f, ws = 0.f;
-    for (int j = 0; j < D; ++j) { q2 = fmaf(q[j], q[j], q2); ws += q[D + j]; }
+#pragma unroll 1
+    for (int j0 = 0; j0 < D; j0 += 16) {             // sixteen loads of each half in flight, then the sums in order
+      float4 x[4], w[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        x[e] = __ldg(reinterpret_cast<const float4*>(q + j0) + e);
+        w[e] = __ldg(reinterpret_cast<const float4*>(q + D + j0) + e);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        q2 = fmaf(x[e].x, x[e].x, q2); q2 = fmaf(x[e].y, x[e].y, q2); q2 = fmaf(x[e].z, x[e].z, q2); q2 = fmaf(x[e].w, x[e].w, q2);
+        ws += w[e].x; ws += w[e].y; ws += w[e].z; ws += w[e].w;
+      }
+    }
     const float qn = sqrtf(q2);
     const bool usable = m < a.M && qn > 0.f && qn < INFINITY;
     const float inv = usable ? 1.f / qn : 0.f;
@@ -87,12 +103,14 @@ __global__ void __launch_bounds__(kXThreads, 1) index_scan_umma_kernel(ScanMmaAr
   if (tid == 0) {
     umma::mbar_init(&mbar[0], 1);
     umma::mbar_init(&mbar[1], 1);
-    umma::mbar_init(&mbar[2], kXWorkers);
+    umma::mbar_init(&mbar[2], 1);
     umma::mbar_init(&mbar[3], kXWorkers);
+    umma::mbar_init(&mbar[4], kXWorkers);
     *dead = 0;
   }
   __syncthreads();
   // ---- B operand: 64 queries x 256 K, fp16, swizzled K-major (four blocks of 64 K = 8 KB each) ------------
+#pragma unroll 8
   for (int idx = tid; idx < kXQ * 256; idx += kXThreads) {
     const int n = idx >> 8, k = idx & 255;
     const int m = q0 + n;
@@ -217,14 +235,13 @@ __global__ void __launch_bounds__(kXThreads, 1) index_scan_umma_kernel(ScanMmaAr
   };
 
   // Scores of row `row` against this warp's 32 queries: optimistic score (c + kEps - sum w) * norm.
-  auto epilogue = [&](int tile, int acc, float kn, bool use_tmem) {
+  auto epilogue = [&](int tile, int acc, float kn, float g, bool use_tmem) {   // g: the other slices' bound for query `lane`
     const int r = tile * kXRows + row;
     const bool valid = r < n_valid && use_tmem;
     uint32_t v[32];
     if (use_tmem) umma::tmem_ld32(tmem_base + (static_cast<uint32_t>(32 * rq) << 16) + acc * kXQ + 32 * cb, v);
     if (valid) my_nmax = fmaxf(my_nmax, kn);
     if (q0 + 32 * cb + lane < a.M) {                 // the other slices' progress: lane = query
-      const float g = *reinterpret_cast<const volatile float*>(a.gthr + q0 + 32 * cb + lane);
       float* mine = &init_thr[32 * cb + lane].y;
       if (g > *mine && *mine != INFINITY) raise_threshold(mine, g);
     }
@@ -281,50 +298,54 @@ __global__ void __launch_bounds__(kXThreads, 1) index_scan_umma_kernel(ScanMmaAr
       for (int i = 0; i < n_tiles; ++i) {
         const int buf = i & 1;
         if (*reinterpret_cast<volatile int*>(dead)) break;
-        if (!umma::mbar_wait(&mbar[2 + buf], full_phase[buf])) { *reinterpret_cast<volatile int*>(dead) = 1; break; }
+        if (!umma::mbar_wait(&mbar[3 + buf], full_phase[buf])) { *reinterpret_cast<volatile int*>(dead) = 1; break; }
         full_phase[buf] ^= 1u;
         if (*reinterpret_cast<volatile int*>(dead)) break;
         umma::fence_after_sync();
-        issue_mmas(buf, buf);
+        issue_mmas(buf, i % 3);
       }
     }
     __syncwarp();
   }
-  // ---- workers: decode(i); arrive; wait(i-1); epilogue(i-1).  No CTA barrier: A(i+1) goes into the buffer of
-  // tile i-1, whose products this thread has waited for; accumulator (i+1) & 1 is overwritten only after every
-  // worker has arrived for tile i+1, that is after its epilogue of tile i-1.
+  // ---- workers: wait(i-2); decode(i); arrive; epilogue(i-2).  No CTA barrier, and the products a worker waits
+  // for were issued two tiles ago.  A(i) goes into the buffer of tile i-2, whose products this thread has waited
+  // for; accumulator (i+1) % 3 = (i-2) % 3 is overwritten only after every worker has arrived for tile i+1, that
+  // is after its epilogue of tile i-2.
   if (worker) {
-    uint32_t phase[2] = {0u, 0u};
+    uint32_t phase[3] = {0u, 0u, 0u};
     auto wait_products = [&](int acc) -> bool {
       bool ok = *reinterpret_cast<volatile int*>(dead) == 0;
       if (ok) {
-        ok = umma::mbar_wait(&mbar[acc], phase[acc]);
-        phase[acc] ^= 1u;
+        const uint32_t ph = acc == 0 ? phase[0] : (acc == 1 ? phase[1] : phase[2]);
+        ok = umma::mbar_wait(&mbar[acc], ph);
+        if (acc == 0) phase[0] ^= 1u; else if (acc == 1) phase[1] ^= 1u; else phase[2] ^= 1u;
         if (!ok) *reinterpret_cast<volatile int*>(dead) = 1;
       }
       umma::fence_after_sync();
       return ok;
     };
-    uint4 rc; uint2 rs; float kn_next = 0.f, kn_cur = 0.f, kn_prev = 0.f;
+    const bool have_q = q0 + 32 * cb + lane < a.M;
+    uint4 rc; uint2 rs;
+    float kn_next = 0.f, kn0 = 0.f, kn1 = 0.f, kn2 = 0.f;       // norms of tiles i, i-1, i-2
     if (n_tiles > 0) fetch(0, rc, rs, kn_next);
     for (int i = 0; i < n_tiles; ++i) {
       const int buf = i & 1;
+      // the shared bound travels while the tile is decoded
+      const float g = have_q ? *reinterpret_cast<const volatile float*>(a.gthr + q0 + 32 * cb + lane) : -INFINITY;
+      bool ok = true;
+      if (i >= 2) ok = wait_products((i - 2) % 3);
       decode(rc, rs, buf);
-      kn_prev = kn_cur;
-      kn_cur = kn_next;
+      kn2 = kn1; kn1 = kn0; kn0 = kn_next;
       if (i + 1 < n_tiles) fetch(i + 1, rc, rs, kn_next);
       umma::tmem_st_wait();
       umma::fence_before_sync();
-      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_u32(&mbar[2 + buf])) : "memory");
-      if (i > 0) {
-        const bool ok = wait_products(buf ^ 1);
-        epilogue(i - 1, buf ^ 1, kn_prev, ok);
-      }
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_u32(&mbar[3 + buf])) : "memory");
+      if (i >= 2) epilogue(i - 2, (i - 2) % 3, kn2, g, ok);
     }
-    if (n_tiles > 0) {
-      const int buf = (n_tiles - 1) & 1;
-      const bool ok = wait_products(buf);
-      epilogue(n_tiles - 1, buf, kn_cur, ok);
+    for (int t = n_tiles >= 2 ? n_tiles - 2 : 0; t < n_tiles; ++t) {     // the last two tiles
+      const bool ok = wait_products(t % 3);
+      const float g = have_q ? *reinterpret_cast<const volatile float*>(a.gthr + q0 + 32 * cb + lane) : -INFINITY;
+      epilogue(t, t % 3, t == n_tiles - 1 ? kn0 : kn1, g, ok);
     }
   }
   {

@@ -822,10 +822,10 @@ def _both_scans(monkeypatch, idx, qs, k, id_base=1000):
     monkeypatch.setenv("QUASHKV_B200_CUDA_CORE_SCAN", "1")
     s0, i0 = idx.search(qs, k, id_base=id_base)
     monkeypatch.setenv("QUASHKV_B200_CUDA_CORE_SCAN", "0")
+    monkeypatch.setenv("QUASHKV_B200_INDEX_TCGEN05", "0")
     s1, i1 = idx.search(qs, k, id_base=id_base)                  # mma.sync scan
-    monkeypatch.setenv("QUASHKV_B200_INDEX_TCGEN05", "1")
-    s2, i2 = idx.search(qs, k, id_base=id_base)                  # tcgen05 scan for k <= 12
     monkeypatch.delenv("QUASHKV_B200_INDEX_TCGEN05")
+    s2, i2 = idx.search(qs, k, id_base=id_base)                  # tcgen05 scan for k <= 12 (the default)
     assert torch.equal(i1, i2) and torch.equal(s1, s2), f"k={k}: tcgen05 and mma.sync scans disagree"
     return s0, i0, s1, i1
 
