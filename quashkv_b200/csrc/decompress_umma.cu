@@ -451,7 +451,8 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
     unsigned char* const lines = s.a + (warp - kDFirstWorker) * (32 * 128);
     const int rr = lane >> 3, rc = lane & 7;           // read side of the transposition: row 4 j + rr, chunk rc
     auto line_off = [&](int row, int c) -> uint32_t { return static_cast<uint32_t>(row * 128 + ((c ^ (row & 7)) << 4)); };
-    auto epilogue = [&](int64_t tile, int ab, float nrm, bool use_tmem) {   // ab: accumulator of the tile
+    // The accumulator read is issued early (before the decode of the next tile) and waited for here.
+    auto epilogue = [&](int64_t tile, int ab, float nrm, bool use_tmem, uint32_t (&v)[64]) {   // ab: accumulator of the tile
       const int64_t n = tile * kDTile + trow;
       const bool live = n < a.n_vec;
       if (!use_tmem) {                                     // tensor core timed out: fp32 chain from the packed row,
@@ -472,8 +473,7 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
         }
         return;
       }
-      uint32_t v[64];
-      umma::tmem_ld64(tmem_base + (static_cast<uint32_t>(rbase) << 16) + ab * 128 + 32 * blk0, v);
+      umma::tmem_ld64_wait(v);
       float f = nrm * descale;
       if (!(fabsf(f) >= 1e-30f && fabsf(f) <= 1e30f)) {    // the product would lose bits: take the power of two first
 #pragma unroll
@@ -531,15 +531,25 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
       return ok;
     };
 
-    // ---- workers: decode(i); arrive; wait(i-1); epilogue(i-1)   (decode overlaps the MMAs of tile i-1) ---------
+    // ---- workers: wait(i-1); decode(i); arrive; epilogue(i-1)   (decode overlaps the MMAs of tile i-1) ---------
     // A(i+1) goes into the buffer of tile i-1, whose products this thread has waited for; accumulator (i+1) & 1 is
     // overwritten only after every worker has arrived for tile i+1, that is after its epilogue of tile i-1.
     int64_t prev_tile = -1;
     int i = 0;
     float norm_cur = 0.f, norm_prev = 0.f;
+    const uint32_t acc_row = tmem_base + (static_cast<uint32_t>(rbase) << 16) + 32 * blk0;
+    // The accumulator read of tile i-1 is issued before the decode of tile i and waited for after it, which hides
+    // its latency (fp32 output +7 %; bf16 output -3 %, the same whether or not that case keeps the read next to
+    // its use, so there is one order for both).
     fetch(blockIdx.x);
     for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++i) {
       const int bf = i & 1;                   // A buffer and accumulator of tile i
+      uint32_t v[64];
+      bool ok = true;
+      if (prev_tile >= 0) {                   // the products of tile i-1 were issued a whole decode + epilogue ago
+        ok = wait_products(bf ^ 1);
+        if (ok) umma::tmem_ld64_issue(acc_row + (bf ^ 1) * 128, v);
+      }
       decode_block(0, bf);
       decode_block(1, bf);
       norm_prev = norm_cur;
@@ -548,16 +558,15 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
       umma::tmem_st_wait();                   // this thread's part of A(i) is in tensor memory
       umma::fence_before_sync();
       mbar_arrive(&s.mbar[2 + bf]);
-      if (prev_tile >= 0) {
-        const bool ok = wait_products(bf ^ 1);
-        epilogue(prev_tile, bf ^ 1, norm_prev, ok);
-      }
+      if (prev_tile >= 0) epilogue(prev_tile, bf ^ 1, norm_prev, ok, v);
       prev_tile = tile;
     }
     if (prev_tile >= 0) {
       const int bf = (i - 1) & 1;
+      uint32_t v[64];
       const bool ok = wait_products(bf);
-      epilogue(prev_tile, bf, norm_cur, ok);
+      if (ok) umma::tmem_ld64_issue(acc_row + bf * 128, v);
+      epilogue(prev_tile, bf, norm_cur, ok, v);
     }
     bulk_wait_all();
   }
