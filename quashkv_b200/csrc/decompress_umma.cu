@@ -1,25 +1,29 @@
 // Decompress at d = 128 with the un-rotation on the fifth-generation tensor cores (tcgen05).
 //
 // out = norm * (v @ Pi) with v_i = c[code_i] (+ qjl_scale * S_i * (2 sign_i - 1) for keys): a 128 x 128 x 128
-// contraction per tile of 128 vectors with A = the decoded rows, written by the threads into the 128-byte
-// swizzled K-major operand layout, and B = Pi^T, staged once per CTA.  One CTA of 512 threads per SM; ONE thread
-// issues the tcgen05.mma instructions (M = 128, N = 128, K = 16), the fp32 accumulator lives in tensor memory
-// (two accumulators alternate) and completion arrives on an mbarrier.
+// contraction per tile of 128 vectors with A = the decoded rows and B = Pi^T.  One CTA per SM; the fp32
+// accumulator lives in tensor memory (two accumulators alternate) and completion arrives on an mbarrier.
 //
 //   * Exact fp32 from fp16 MMAs.  Both operands are scaled by a power of two that puts their largest magnitude
 //     just below 2^14 and split into TWO fp16 terms, x = h + m with |m| <= ulp(h) / 2: 22 significand bits, and
-//     the scaling keeps m out of the subnormal range for every value that matters.  Four products (m*m, m*h,
-//     h*m, h*h, smallest first: 32 MMAs per tile) accumulate in fp32; the power of two leaves with the norm.
-//   * Decode by pairs.  With S = +-1 (what the quantiser generates) a pair of neighbouring coordinates takes one
-//     of 2^(2 bits [+ 2]) values, and the packed row holds the two codes side by side: the field (and the two
-//     sign bits) index a shared-memory table of READY operand words (h0 | h1, m0 | m1), repeated per lane so that
-//     every lane of a half warp reads its own banks.  A pair costs a shift, a mask (a shift and a merge more for
-//     the sign bits) and one 8-byte load; four pairs leave as one 16-byte store per plane.
-//   * Two A buffers: the threads decode tile t + 1 while the tensor core multiplies tile t.  The buffer of tile
-//     t - 1 is idle by then, and every warp owns the chunks of it that it wrote itself (32 rows x 64 bytes per
-//     plane): the epilogue uses exactly those chunks to transpose its outputs (a thread holds 32 consecutive
-//     outputs of ONE row; they come back as 8 rows x 64 contiguous bytes per store instruction), so no other
-//     staging memory and no CTA barrier is needed for it.
+//     the scaling keeps m out of the subnormal range for every value that matters.  Three products (m*h, h*m,
+//     h*h, smallest first: 24 MMAs of 128 x 128 x 16 per tile; m*m is below 2^-22) accumulate in fp32; the power
+//     of two leaves with the norm.  B (two planes of Pi^T, 128-byte swizzled K-major) is staged once per CTA.
+//   * Decode by pairs, straight into tensor memory.  With S = +-1 (what the quantiser generates) a pair of
+//     neighbouring coordinates takes one of 2^(2 bits [+ 2]) values, and the packed row holds the two codes side
+//     by side: the field (and the two sign bits) index a shared-memory table of READY operand words (h0 | h1,
+//     m0 | m1), repeated per lane so that every lane of a half warp reads its own banks.  A pair costs a shift,
+//     a mask (a shift and a merge more for the sign bits) and one 8-byte load, and its two words ARE 32-bit
+//     columns of the two A planes in tensor memory (lane = row): sixteen pairs leave as one tcgen05.st per
+//     plane, and the MMA reads A from tensor memory, so the tensor core's shared-memory traffic is B alone.
+//   * Roles.  Warp 0 only issues: its first lane waits until every worker thread has arrived on the "A(i) is
+//     written" barrier, issues the 24 MMAs and commits them (the issuing thread is held for about as long as the
+//     MMAs execute; as a worker it held the whole CTA back by that time).  Warps 4-11 are the workers: two per
+//     lane quadrant of tensor memory, 2 x 32 columns per thread.  There is no CTA barrier in the loop; two A
+//     buffers, so tile i+1 is decoded while tile i is multiplied.
+//   * Output.  A worker issues the read of tile i-1's accumulator, decodes tile i while it travels, then scales
+//     its 64 values by the norm.  fp32: the 256 bytes go to a staging row of the thread's own and leave with ONE
+//     bulk copy (shared -> global); bf16: a warp transposition and stores of 4 rows x 128 bytes.
 //   * The packed words and the norm of a tile are fetched one tile ahead of their use.
 //
 // Every wait on the tensor core is bounded; if one runs out the CTA stops using the tensor core, counts the
@@ -41,7 +45,7 @@ constexpr int kDTile = 128;                       // vectors per tile = MMA M
 constexpr int kDFirstWorker = 4;                  // warps 4 .. 11 decode and store; warp 0 issues the MMAs
 constexpr int kDWorkers = 256;                    // two worker threads per vector: 2 x 32 coordinates each
 constexpr int kDThreads = 32 * kDFirstWorker + kDWorkers;
-constexpr uint32_t kDPlaneBytes = 128 * 128 * 2;  // one fp16 operand tile (two 64-wide K blocks)
+constexpr uint32_t kDPlaneBytes = 128 * 128 * 2;  // one fp16 plane of Pi^T (two 64-wide K blocks)
 constexpr uint32_t kDTmemCols = 512;              // accumulators [0, 256), A operands [256, 512)
 constexpr uint32_t kDTmemA = 256;                 // A[buffer][term]: 64 columns each (128 fp16 per row)
 constexpr uint32_t kDTableBytes = 32768;          // pair tables (mixed precision: two halves)
@@ -63,7 +67,9 @@ __host__ __device__ constexpr int pair_replicas() {
 }
 
 struct DecSmem {
-  unsigned char* a;         // A tiles [buffer][term h, m] (fp16, swizzled), 1024-byte aligned, kDPlaneBytes each
+  unsigned char* scratch;   // output staging: a row of kDStageRow bytes per worker thread (fp32 out) or 32 lines of
+                            // 128 bytes per worker warp (bf16 out); 4 planes, which also keeps the CTA alone on its
+                            // SM (it owns all of tensor memory)
   unsigned char* b;         // Pi^T planes h, m
   unsigned char* tab;       // pair tables
   uint64_t* mbar;           // [4]: accumulator 0 / 1 complete, A buffer 0 / 1 written
@@ -76,7 +82,7 @@ constexpr size_t dec_smem_bytes() { return 1024 + 6 * kDPlaneBytes + kDTableByte
 __device__ __forceinline__ DecSmem carve_dec(unsigned char* raw) {
   DecSmem s;
   unsigned char* p = raw + ((1024u - (umma::smem_u32(raw) & 1023u)) & 1023u);
-  s.a = p; p += 4 * kDPlaneBytes;
+  s.scratch = p; p += 4 * kDPlaneBytes;
   s.b = p; p += 2 * kDPlaneBytes;
   s.tab = p; p += kDTableBytes;
   s.mbar = reinterpret_cast<uint64_t*>(p); p += 32;
@@ -133,7 +139,7 @@ __device__ __noinline__ float decompress_chain(const float* vrow, const float* P
 // one table; needs the outlier count to be a multiple of 32, otherwise the CTA returns and the CUDA-core
 // kernel launched behind it does the work (same device-side test, inverted).
 //
-// Warps: 0 = the issuing warp (its first lane waits for "A(i) is written", issues the 32 MMAs of tile i and
+// Warps: 0 = the issuing warp (its first lane waits for "A(i) is written", issues the 24 MMAs of tile i and
 // commits them to the accumulator's barrier), 1-3 take part in the set-up only, 4-11 = workers.  Worker warp w
 // owns rows 32 (w & 3) .. + 31 (the tensor-memory lanes its warp may read) and columns 64 ((w - 4) >> 2) .. + 63
 // as two blocks of 32; a worker thread decodes and later stores 2 x 32 coordinates of ONE row.  Workers never wait
@@ -447,8 +453,8 @@ __global__ void __launch_bounds__(kDThreads, 1) decompress_umma_kernel(Decompres
     // transposes through 32 lines of 128 bytes of its own (16-byte chunk c of row r at position c ^ (r & 7):
     // conflict-free both ways) and stores 4 rows x 128 contiguous bytes per instruction, whole lines.
     const int rbase = 32 * (warp & 3);
-    unsigned char* const stage = s.a + ((warp - kDFirstWorker) * 32 + lane) * kDStageRow;
-    unsigned char* const lines = s.a + (warp - kDFirstWorker) * (32 * 128);
+    unsigned char* const stage = s.scratch + ((warp - kDFirstWorker) * 32 + lane) * kDStageRow;
+    unsigned char* const lines = s.scratch + (warp - kDFirstWorker) * (32 * 128);
     const int rr = lane >> 3, rc = lane & 7;           // read side of the transposition: row 4 j + rr, chunk rc
     auto line_off = [&](int row, int c) -> uint32_t { return static_cast<uint32_t>(row * 128 + ((c ^ (row & 7)) << 4)); };
     // The accumulator read is issued early (before the decode of the next tile) and waited for here.

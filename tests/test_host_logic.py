@@ -334,3 +334,11 @@ def test_hf_cache_plumbing_with_a_stand_in_engine():
             assert model.config._attn_implementation == previous
             assert torch.allclose(o1.logits, ref.logits, atol=1e-5) and torch.allclose(o2.logits, ref2.logits, atol=1e-5)
             assert cache.get_seq_length() == 8
+
+
+def test_every_cuda_source_is_part_of_the_build():
+    """A source file that is not in the build list would silently drop its kernels from the library."""
+    import os
+    from quashkv_b200 import _build
+    on_disk = sorted(f for f in os.listdir(_build.CSRC) if f.endswith(".cu"))
+    assert sorted(_build.SOURCES) == on_disk
