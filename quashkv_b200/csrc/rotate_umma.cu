@@ -11,12 +11,15 @@
 //     buffered); products A*l, A*m, A*h accumulate smallest first: 24 MMAs per tile;
 //   * two accumulators (2 x 128 tensor-memory columns) alternate, so the MMAs of tile t run while
 //     the threads classify tile t-1.
-// The 128 threads then each own one vector: thread r reads row r of the accumulator with
-// tcgen05.ld (32 columns at a time), scales by 1/norm (fp64 sum of squares, as in the CUDA-core
-// kernel), classifies every coordinate through the bucket table, packs 32 codes into whole words
-// and stores the packed row.  Coordinates within kRecheckEps of a decision boundary go to a per-warp
-// queue and are recomputed with the sequential fp32 FMA chain, exactly as in the mma.sync kernel,
-// so the bytes are identical to the CUDA-core kernel's.
+// Four threads then share one vector (512 threads per CTA): a thread reads 32 columns of its row of the
+// accumulator with tcgen05.ld, scales by 1/norm (fp64 sum of squares, as in the CUDA-core kernel), classifies
+// every coordinate through the bucket table, packs the 32 codes into whole words and stores its part of the
+// packed row.  A coordinate whose bucket holds a decision boundary is classified exactly from a register copy
+// (tensor memory is re-read only for threads with several such coordinates); coordinates within kRecheckEps of a
+// boundary go to a per-warp queue and are recomputed with the sequential fp32 FMA chain, exactly as in the
+// mma.sync kernel, so the bytes are identical to the CUDA-core kernel's.  The queues are emptied by all warps
+// together (a flag out of the tile barrier), and the products of a tile are issued one at a time between the
+// phases of the loop, because the issuing thread is held for about as long as its MMAs execute.
 //
 // Every wait on the tensor core is bounded; if one runs out the CTA stops using the tensor core,
 // counts the event and derives its remaining tiles with the fp32 chain alone (slow, still exact).
