@@ -345,6 +345,34 @@ def test_tcgen05_rotation_edge_shapes(golden, monkeypatch):
     assert _lib.lib().qkv_tensor_core_timeouts() == TIMEOUTS[0]
 
 
+def test_tcgen05_decompress_all_widths_and_outputs(golden, monkeypatch):
+    """The tcgen05 decompress kernel at every bit width (its pair tables differ in size and in the number of
+    copies), with and without the sign term, for fp32 / bf16 / fp16 output (bulk copies, warp transposition,
+    plain stores) and for batches of exactly one tile count, one row more, and a ragged end.  Reference: the
+    CUDA-core kernel (env switch), which the other tests pin to the oracle."""
+    c = golden("constants")
+    Pi, S = t(c["Pi_d128_s42"]).to(DEV), t(c["S_d128_s42"]).to(DEV)
+    gen = torch.Generator().manual_seed(11)
+    for n in (1024, 1025, 5000):
+        x = torch.randn(n, 128, generator=gen).to(DEV)
+        for bits in (1, 2, 3, 4):
+            bnd, cent = t(c[f"bnd_d128_b{bits}"]).to(DEV), t(c[f"cent_d128_b{bits}"]).to(DEV)
+            mse, sg, nrm = ops.compress_ip(x, Pi, bnd, cent, S, bits, packed=True)
+            for dt, tol in ((torch.float32, 2e-6), (torch.bfloat16, 3e-3), (torch.float16, 4e-4)):
+                for signs in (None, sg):
+                    kw = dict(packed=True, d=128, out_dtype=dt)
+                    if signs is not None:
+                        kw.update(signs=signs, S=S, qjl_scale=0.05)
+                    fast = ops.decompress(mse, nrm, Pi, cent, bits, **kw)
+                    monkeypatch.setenv("QUASHKV_B200_CUDA_CORE_ROTATION", "1")
+                    slow = ops.decompress(mse, nrm, Pi, cent, bits, **kw)
+                    monkeypatch.delenv("QUASHKV_B200_CUDA_CORE_ROTATION")
+                    err = rel_l2(fast, slow)
+                    assert err < tol, f"n={n} bits={bits} {dt} signs={signs is not None}: {err}"
+    from quashkv_b200 import _lib
+    assert _lib.lib().qkv_tensor_core_timeouts() == TIMEOUTS[0]
+
+
 def test_mixed_precision_tensor_core_equals_cuda_core(golden, monkeypatch):
     """bf16 batches with a multiple of 32 outlier channels compress on the tcgen05 kernel (the rows of
     Pi staged in stream order); the packed bytes and norms must equal the CUDA-core kernel's.  Other
