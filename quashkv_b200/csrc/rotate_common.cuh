@@ -37,6 +37,9 @@ struct DecompressArgs {
   const float* S; float qjl_scale;
   void* out; int out_dtype; int64_t out_pitch;
   int skip_block_aligned;              // mixed, CUDA-core kernel: return if the outlier count is a multiple of 32
+  int test_drop_mma;                   // test hook of the tcgen05 kernel: CTA 0 issues nothing for its second tile, so
+                                       // the bounded wait on that accumulator runs out (nothing is left in flight)
+                                       // and the CTA finishes with the fp32 chain
 };
 
 

@@ -1386,3 +1386,29 @@ def test_tensor_core_wait_that_runs_out_falls_back_to_exact_arithmetic(monkeypat
         assert torch.equal(a, b)
     again = q.compress_packed(x)                             # and the library is as before afterwards
     assert torch.equal(again[0], want[0]) and _lib.lib().qkv_tensor_core_timeouts() == after
+
+
+def test_decompress_wait_that_runs_out_falls_back_to_the_fp32_chain(monkeypatch):
+    """The same hook in the tcgen05 decompress kernel: CTA 0 never multiplies its second tile, the workers' bounded
+    wait for those products gives up, the event is counted and the CTA derives its remaining rows with the fp32
+    chain (plain stores); the output agrees with the undisturbed run.  Nothing faults, hangs or is left in flight."""
+    x = _heavy_tail_rows(148 * 128 * 3 + 11).to(DEV)      # three tiles for every CTA of the persistent grid
+    q = qk.InnerProductQuantizer(128, 3, seed=42)
+    mse, sg, nrm = q.compress_packed(x)
+    mq = q.mse_quantizer
+    args = (mse, nrm, mq.Pi, mq.codebook.centroids, 2)
+    kw = dict(signs=sg, S=q.S, qjl_scale=q.qjl_scale, packed=True, d=128)
+    want = ops.decompress(*args, **kw)
+    before = _lib.lib().qkv_tensor_core_timeouts()
+    monkeypatch.setenv("QUASHKV_B200_TEST_DROP_MMA", "1")
+    got = ops.decompress(*args, **kw)
+    torch.cuda.synchronize()
+    monkeypatch.delenv("QUASHKV_B200_TEST_DROP_MMA")
+    after = _lib.lib().qkv_tensor_core_timeouts()
+    assert after > before, (before, after)
+    TIMEOUTS[0] = after
+    assert rel_l2(got, want) < 2e-6
+    lo = 148 * 128                                          # CTA 0's second tile: the one that was dropped
+    assert rel_l2(got[lo:lo + 128], want[lo:lo + 128]) < 2e-6
+    again = ops.decompress(*args, **kw)
+    assert torch.equal(again, want) and _lib.lib().qkv_tensor_core_timeouts() == after
