@@ -98,7 +98,8 @@ static __device__ __noinline__ float exact_chain_s(const void* x, int x_dtype, i
                                                    int64_t n, int col, float norm) {
   const float* prow = Pi + col * kRD;
   float z = 0.f;
-  if (x_dtype == QKV_BF16 && ((reinterpret_cast<uintptr_t>(x) | (static_cast<uint64_t>(x_pitch) * 2)) & 15u) == 0) {
+  const bool pi16 = (reinterpret_cast<uintptr_t>(Pi) & 15u) == 0;      // rows of Pi are 512 bytes apart
+  if (pi16 && x_dtype == QKV_BF16 && ((reinterpret_cast<uintptr_t>(x) | (static_cast<uint64_t>(x_pitch) * 2)) & 15u) == 0) {
     const uint4* xr = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(x) + n * x_pitch);
 #pragma unroll 1
     for (int c = 0; c < 4; ++c) {
@@ -122,7 +123,7 @@ static __device__ __noinline__ float exact_chain_s(const void* x, int x_dtype, i
     }
     return z;
   }
-  if (x_dtype == QKV_F32 && ((reinterpret_cast<uintptr_t>(x) | (static_cast<uint64_t>(x_pitch) * 4)) & 15u) == 0) {
+  if (pi16 && x_dtype == QKV_F32 && ((reinterpret_cast<uintptr_t>(x) | (static_cast<uint64_t>(x_pitch) * 4)) & 15u) == 0) {
     const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + n * x_pitch);
 #pragma unroll 1
     for (int c = 0; c < 4; ++c) {
