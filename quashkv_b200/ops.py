@@ -506,7 +506,8 @@ def _attention_tiled(q: torch.Tensor, records: torch.Tensor, capacity: int, kv_l
 
 
 class RowAttentionCall:
-    """The C call of the ``attention`` op (row-major packed planes), prepared once for an engine's decode loop:
+    """The C call of the ``attention`` op (row-major packed planes; ``QuashKVEngine.attention``, reference
+    engine.py:204-299), prepared once for an engine's decode loop:
     constants converted once, the workspace kept and grown when needed, no op dispatcher.  A decode step over a
     short cache is a few tens of microseconds of device work; the generic op spends more than that on the
     host.  One instance serves one stream at a time (the workspace is shared by its calls)."""
@@ -544,7 +545,8 @@ class RowAttentionCall:
 
 
 class AppendCall:
-    """Compression of new keys and values into an engine's storage, prepared once: constants converted once,
+    """Compression of new keys and values into an engine's storage (``QuashKVEngine.append``, reference
+    engine.py:145-172), prepared once: constants converted once,
     the staging planes of a tiled cache kept between calls, the library called directly.  The generic ops cost
     80-120 us of host time per one-token append (dispatcher, conversions, five allocations)."""
 
@@ -628,7 +630,8 @@ def cudart():
 
 
 class TiledAttentionCall:
-    """The same C call as the ``attention_tiled`` op, prepared once for an engine's decode loop: constants are
+    """The same C call as the ``attention_tiled`` op (``QuashKVEngine.attention``, reference engine.py:204-299,
+    over a cache kept as tile records), prepared once for an engine's decode loop: constants are
     converted and kept, the workspace is kept between calls and grows when a longer cache needs more, and the
     call goes to the library without passing through the op dispatcher.  A decode step over one KV head of a
     sharded cache lasts tens of microseconds on the device; the per-call host work of the generic op (four
